@@ -1,0 +1,90 @@
+// Shared helpers of the clockwork_b200 kernels (sm_100a only).
+//
+// Conventions of every exported entry point (all are extern "C", loaded with ctypes):
+//   * pointers are device pointers owned by the caller; nothing here allocates;
+//   * `dtype` is 0 for float32 and 1 for bfloat16 and names the type of activations,
+//     matrices and caches; residual streams, logits, norm weights and biases are float32;
+//   * `status` points to CW_STATUS_WORDS int32 words on the device; a kernel that meets an
+//     index outside its table (token id, slot, page id) records the first such event there
+//     and skips the access instead of faulting; the host checks it when it reads results;
+//   * the last argument is the CUDA stream; the return value is a cudaError_t as int
+//     (launch-configuration errors), or a negative CW_ERR_* code for refused sizes.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define CW_STATUS_WORDS 4
+#define CW_OK 0
+#define CW_ERR_BAD_SIZE (-1)
+#define CW_ERR_BAD_DTYPE (-2)
+#define CW_ERR_UNSUPPORTED (-3)
+
+// status[0] codes
+#define CW_ST_TOKEN_RANGE 1
+#define CW_ST_SLOT_RANGE 2
+#define CW_ST_PAGE_RANGE 3
+#define CW_ST_WAIT_TIMEOUT 4
+#define CW_ST_ROW_RANGE 5
+
+typedef __nv_bfloat16 bf16;
+
+__device__ __forceinline__ void cw_report(int* status, int code, int a, int b) {
+    if (status != nullptr && atomicCAS(&status[0], 0, code) == 0) {
+        status[1] = a;
+        status[2] = b;
+    }
+}
+
+__device__ __forceinline__ float to_f(float x) { return x; }
+__device__ __forceinline__ float to_f(bf16 x) { return __bfloat162float(x); }
+template <typename T> __device__ __forceinline__ T from_f(float x);
+template <> __device__ __forceinline__ float from_f<float>(float x) { return x; }
+template <> __device__ __forceinline__ bf16 from_f<bf16>(float x) { return __float2bfloat16_rn(x); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Block-wide reductions with a fixed order (warp tree, then warp 0 over the warp results),
+// so the result for a row never depends on what else is in the batch.
+// `scratch` must hold 33 floats.  All threads receive the result.
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int nwarps = (blockDim.x + 31) >> 5;
+    v = warp_sum(v);
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    if (warp == 0) {
+        float w = lane < nwarps ? scratch[lane] : 0.f;
+        w = warp_sum(w);
+        if (lane == 0) scratch[32] = w;
+    }
+    __syncthreads();
+    return scratch[32];
+}
+__device__ __forceinline__ float block_max(float v, float* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int nwarps = (blockDim.x + 31) >> 5;
+    v = warp_max(v);
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    if (warp == 0) {
+        float w = lane < nwarps ? scratch[lane] : -INFINITY;
+        w = warp_max(w);
+        if (lane == 0) scratch[32] = w;
+    }
+    __syncthreads();
+    return scratch[32];
+}
+
+#define CW_LAUNCH_CHECK() ((int)cudaGetLastError())

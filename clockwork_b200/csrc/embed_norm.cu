@@ -1,0 +1,141 @@
+// Embedding gather and fused residual-add + RMSNorm.
+//
+// Reference formulas: clockwork/engine/model.py:200 (embedding), :44-49 (RMSNorm: float32
+// statistics, x * rsqrt(mean(x^2) + eps), then the weight), :150 and :154 (residual sums).
+// The residual stream is float32 in both run precisions; the normed output has the run's
+// activation type.
+#include "common.cuh"
+
+template <typename T>
+__global__ void embed_kernel(float* __restrict__ out, const T* __restrict__ table,
+                             const int* __restrict__ ids, int H, int V, int* status) {
+    const int row = blockIdx.x;
+    const int id = ids[row];
+    float* o = out + (size_t)row * H;
+    if (id < 0 || id >= V) {
+        if (threadIdx.x == 0) cw_report(status, CW_ST_TOKEN_RANGE, row, id);
+        for (int c = threadIdx.x; c < H; c += blockDim.x) o[c] = 0.f;
+        return;
+    }
+    const T* src = table + (size_t)id * H;
+    for (int c = threadIdx.x; c < H; c += blockDim.x) o[c] = to_f(src[c]);
+}
+
+extern "C" int cw_embed(float* out, const void* table, const int* ids, int N, int H, int V,
+                        int dtype, int* status, cudaStream_t stream) {
+    if (N == 0) return CW_OK;
+    if (N < 0 || H <= 0 || V <= 0) return CW_ERR_BAD_SIZE;
+    const int threads = H >= 1024 ? 256 : 128;
+    if (dtype == 0)
+        embed_kernel<float><<<N, threads, 0, stream>>>(out, (const float*)table, ids, H, V, status);
+    else if (dtype == 1)
+        embed_kernel<bf16><<<N, threads, 0, stream>>>(out, (const bf16*)table, ids, H, V, status);
+    else
+        return CW_ERR_BAD_DTYPE;
+    return CW_LAUNCH_CHECK();
+}
+
+// resid[row] (+= delta[row]); out[r] = weight * (x * rsqrt(mean(x^2)+eps)).
+// With `rows` given, output row r is computed from residual row rows[r] (no add is done).
+template <typename T>
+__global__ void add_rmsnorm_kernel(float* __restrict__ resid, const T* __restrict__ delta,
+                                   const float* __restrict__ weight, T* __restrict__ out,
+                                   const int* __restrict__ rows, int num_resid_rows, float eps,
+                                   int H, int* status) {
+    __shared__ float scratch[33];
+    const int r = blockIdx.x;
+    int src_row = r;
+    if (rows != nullptr) {
+        src_row = rows[r];
+        if (src_row < 0 || src_row >= num_resid_rows) {
+            if (threadIdx.x == 0) cw_report(status, CW_ST_ROW_RANGE, r, src_row);
+            for (int c = threadIdx.x; c < H; c += blockDim.x) out[(size_t)r * H + c] = from_f<T>(0.f);
+            return;
+        }
+    }
+    float* x = resid + (size_t)src_row * H;
+    const T* d = delta ? delta + (size_t)src_row * H : nullptr;
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < H; c += blockDim.x) {
+        float v = x[c];
+        if (d) {
+            v += to_f(d[c]);
+            x[c] = v;
+        }
+        ss = fmaf(v, v, ss);
+    }
+    ss = block_sum(ss, scratch);
+    const float inv = 1.0f / sqrtf(ss / (float)H + eps);
+    T* o = out + (size_t)r * H;
+    for (int c = threadIdx.x; c < H; c += blockDim.x) o[c] = from_f<T>(weight[c] * (x[c] * inv));
+}
+
+extern "C" int cw_add_rmsnorm(float* resid, const void* delta, const float* weight, void* out,
+                              const int* rows, int num_out_rows, int num_resid_rows, int H,
+                              float eps, int dtype, int* status, cudaStream_t stream) {
+    if (num_out_rows == 0) return CW_OK;
+    if (num_out_rows < 0 || H <= 0) return CW_ERR_BAD_SIZE;
+    if (rows != nullptr && delta != nullptr) return CW_ERR_UNSUPPORTED;
+    const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
+    if (dtype == 0)
+        add_rmsnorm_kernel<float><<<num_out_rows, threads, 0, stream>>>(
+            resid, (const float*)delta, weight, (float*)out, rows, num_resid_rows, eps, H, status);
+    else if (dtype == 1)
+        add_rmsnorm_kernel<bf16><<<num_out_rows, threads, 0, stream>>>(
+            resid, (const bf16*)delta, weight, (bf16*)out, rows, num_resid_rows, eps, H, status);
+    else
+        return CW_ERR_BAD_DTYPE;
+    return CW_LAUNCH_CHECK();
+}
+
+// out = silu(gate) * up, gate and up being the two halves of each row of `gate_up` [N, 2*I]
+// (clockwork/engine/model.py:62-63).  Used where the product is not fused into the GEMM.
+template <typename T>
+__global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int I,
+                                size_t total) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    const size_t row = i / I, col = i % I;
+    const float g = to_f(gate_up[row * 2 * I + col]);
+    const float u = to_f(gate_up[row * 2 * I + I + col]);
+    out[i] = from_f<T>(g / (1.0f + expf(-g)) * u);
+}
+
+extern "C" int cw_silu_mul(const void* gate_up, void* out, int N, int I, int dtype,
+                           cudaStream_t stream) {
+    if (N == 0) return CW_OK;
+    if (N < 0 || I <= 0) return CW_ERR_BAD_SIZE;
+    const size_t total = (size_t)N * I;
+    const int threads = 256;
+    const unsigned blocks = (unsigned)((total + threads - 1) / threads);
+    if (dtype == 0)
+        silu_mul_kernel<float><<<blocks, threads, 0, stream>>>((const float*)gate_up, (float*)out, I, total);
+    else if (dtype == 1)
+        silu_mul_kernel<bf16><<<blocks, threads, 0, stream>>>((const bf16*)gate_up, (bf16*)out, I, total);
+    else
+        return CW_ERR_BAD_DTYPE;
+    return CW_LAUNCH_CHECK();
+}
+
+// resid += delta (float32 += T); used where a part returns a delta that no norm follows.
+template <typename T>
+__global__ void add_to_residual_kernel(float* __restrict__ resid, const T* __restrict__ delta,
+                                       size_t total) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < total) resid[i] += to_f(delta[i]);
+}
+
+extern "C" int cw_add_to_residual(float* resid, const void* delta, int N, int H, int dtype,
+                                  cudaStream_t stream) {
+    if (N == 0) return CW_OK;
+    if (N < 0 || H <= 0) return CW_ERR_BAD_SIZE;
+    const size_t total = (size_t)N * H;
+    const unsigned blocks = (unsigned)((total + 255) / 256);
+    if (dtype == 0)
+        add_to_residual_kernel<float><<<blocks, 256, 0, stream>>>(resid, (const float*)delta, total);
+    else if (dtype == 1)
+        add_to_residual_kernel<bf16><<<blocks, 256, 0, stream>>>(resid, (const bf16*)delta, total);
+    else
+        return CW_ERR_BAD_DTYPE;
+    return CW_LAUNCH_CHECK();
+}

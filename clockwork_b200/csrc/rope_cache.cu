@@ -1,0 +1,114 @@
+// Rotary position encoding fused with the slot-mapped write of K and V into the paged cache,
+// and the page copy that copy-on-write needs.
+//
+// Reference: clockwork/engine/model.py:92-95 (q*cos + rotate_half(q)*sin, element j paired
+// with j + rotary_dim/2, cos/sin broadcast over heads), :186-191 (angle = float(position) *
+// inv_freq[j], in float32), clockwork/kvcache/kv_cache.py:37-45 (scatter by slot, slot =
+// page*page_size + position % page_size) and :32-35 (copy of one page in every layer).
+// The rotation is done in float32 from float32 angles in both run precisions.
+#include "common.cuh"
+
+// qkv: [N, (nh + 2*nkv) * hd]; heads 0..nh-1 are q (rotated in place), the next nkv are k
+// (rotated, written to the cache), the last nkv are v (copied to the cache).
+// inv_freq == nullptr: no rotation (a position encoding that leaves q and k alone).
+// slots[t] < 0: the token's K/V are not stored (padding rows of a fixed-shape batch).
+template <typename T>
+__global__ void rope_store_kernel(T* __restrict__ qkv, const int* __restrict__ positions,
+                                  const int* __restrict__ slots, const float* __restrict__ inv_freq,
+                                  T* __restrict__ k_cache, T* __restrict__ v_cache, int nh, int nkv,
+                                  int hd, int rotary_dim, int num_slots, int write_cache,
+                                  int* status) {
+    const int t = blockIdx.x;
+    const int head = blockIdx.y;
+    const int half = rotary_dim >> 1;
+    T* row = qkv + (size_t)t * (nh + 2 * nkv) * hd + (size_t)head * hd;
+    const int slot = slots ? slots[t] : -1;
+    const bool is_q = head < nh, is_k = !is_q && head < nh + nkv;
+    T* dst = nullptr;
+    if (!is_q) {
+        if (!write_cache || slot < 0) {
+            if (!is_k) return;  // v: nothing to do
+        } else if (slot >= num_slots) {
+            if (threadIdx.x == 0) cw_report(status, CW_ST_SLOT_RANGE, t, slot);
+            return;
+        } else {
+            const int kvh = is_k ? head - nh : head - nh - nkv;
+            dst = (is_k ? k_cache : v_cache) + ((size_t)slot * nkv + kvh) * hd;
+        }
+    }
+    if (is_q || is_k) {
+        if (inv_freq != nullptr) {
+            const float pos = (float)positions[t];
+            for (int j = threadIdx.x; j < half; j += blockDim.x) {
+                const float ang = pos * inv_freq[j];
+                const float c = cosf(ang), s = sinf(ang);
+                const float x1 = to_f(row[j]), x2 = to_f(row[j + half]);
+                const T o1 = from_f<T>(x1 * c - x2 * s);
+                const T o2 = from_f<T>(x2 * c + x1 * s);
+                row[j] = o1;  // k keeps its rotated value in the activation too
+                row[j + half] = o2;
+                if (dst) {
+                    dst[j] = o1;
+                    dst[j + half] = o2;
+                }
+            }
+            if (dst)  // beyond the rotary span: pass through
+                for (int j = rotary_dim + threadIdx.x; j < hd; j += blockDim.x) dst[j] = row[j];
+        } else if (dst) {
+            for (int j = threadIdx.x; j < hd; j += blockDim.x) dst[j] = row[j];
+        }
+    } else if (dst) {
+        for (int j = threadIdx.x; j < hd; j += blockDim.x) dst[j] = row[j];
+    }
+}
+
+extern "C" int cw_rope_store(void* qkv, const int* positions, const int* slots,
+                             const float* inv_freq, void* k_cache, void* v_cache, int N, int nh,
+                             int nkv, int hd, int rotary_dim, int num_slots, int write_cache,
+                             int dtype, int* status, cudaStream_t stream) {
+    if (N == 0) return CW_OK;
+    if (N < 0 || nh <= 0 || nkv <= 0 || hd <= 0) return CW_ERR_BAD_SIZE;
+    if (rotary_dim < 0 || rotary_dim > hd || (rotary_dim & 1)) return CW_ERR_BAD_SIZE;
+    if (nh + 2 * nkv > 65535) return CW_ERR_BAD_SIZE;
+    dim3 grid(N, nh + 2 * nkv);
+    int threads = 32;
+    while (threads < hd / 2 && threads < 128) threads <<= 1;
+    if (dtype == 0)
+        rope_store_kernel<float><<<grid, threads, 0, stream>>>(
+            (float*)qkv, positions, slots, inv_freq, (float*)k_cache, (float*)v_cache, nh, nkv, hd,
+            rotary_dim, num_slots, write_cache, status);
+    else if (dtype == 1)
+        rope_store_kernel<bf16><<<grid, threads, 0, stream>>>(
+            (bf16*)qkv, positions, slots, inv_freq, (bf16*)k_cache, (bf16*)v_cache, nh, nkv, hd,
+            rotary_dim, num_slots, write_cache, status);
+    else
+        return CW_ERR_BAD_DTYPE;
+    return CW_LAUNCH_CHECK();
+}
+
+// cache: [planes, num_pages, page_elems]; copies page src->dst in every plane (a plane is one
+// layer's K or V).  pairs: int32 [num_pairs, 2].
+__global__ void copy_pages_kernel(uint4* __restrict__ cache, const int* __restrict__ pairs,
+                                  size_t page_vec, size_t plane_vec, int num_pages, int* status) {
+    const int src = pairs[2 * blockIdx.x], dst = pairs[2 * blockIdx.x + 1];
+    if (src < 0 || src >= num_pages || dst < 0 || dst >= num_pages) {
+        if (threadIdx.x == 0) cw_report(status, CW_ST_PAGE_RANGE, src, dst);
+        return;
+    }
+    uint4* base = cache + (size_t)blockIdx.y * plane_vec;
+    for (size_t i = threadIdx.x; i < page_vec; i += blockDim.x)
+        base[(size_t)dst * page_vec + i] = base[(size_t)src * page_vec + i];
+}
+
+extern "C" int cw_copy_pages(void* cache, const int* pairs, int num_pairs, int planes,
+                             int num_pages, long long page_bytes, int* status,
+                             cudaStream_t stream) {
+    if (num_pairs == 0) return CW_OK;
+    if (num_pairs < 0 || planes <= 0 || planes > 65535 || page_bytes <= 0 || page_bytes % 16)
+        return CW_ERR_BAD_SIZE;
+    const size_t page_vec = (size_t)page_bytes / 16;
+    dim3 grid(num_pairs, planes);
+    copy_pages_kernel<<<grid, 128, 0, stream>>>((uint4*)cache, pairs, page_vec,
+                                                page_vec * (size_t)num_pages, num_pages, status);
+    return CW_LAUNCH_CHECK();
+}

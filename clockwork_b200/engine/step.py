@@ -1,0 +1,166 @@
+"""The step function: one flat batch of (request, its next tokens) through the model.
+
+A step may hold portions of prompts beside single decoded tokens, cut anywhere.  It runs only
+the tokens it is given; everything earlier comes from the cache.  It returns float32 logits at
+the wanted places only.
+
+The reference runs one forward per prefilling sequence and then one batched decode forward
+(``clockwork/engine/model_runner.py:48-58``, ``68-132``), although its model accepts a mixed
+batch (``clockwork/engine/model.py:103-118`` loops over per-sequence query lengths).  Here the
+mixed batch is the only form: a decoded token is a portion of length one.  Inputs per step, as
+in ``model_runner.py:72-91`` and ``98-124``: token ids, positions, slot mapping, block tables,
+context lengths and the rows whose logits are wanted, uploaded in one copy from pinned memory.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+
+import numpy as np
+import torch
+
+from .. import ops
+from ..cache.manager import NO_PAGE, CacheManager
+from ..parts.base import StepContext
+from ..parts.model import DecoderModel
+
+
+@dataclass
+class StepEntry:
+    request_id: str
+    tokens: list[int]  # the request's next tokens, in order
+    want: list[int] = field(default_factory=list)  # places among ``tokens`` whose logits are wanted
+
+
+def _pad4(n: int) -> int:
+    return (n + 3) & ~3
+
+
+class ModelRunner:
+    """Owns nothing but the wiring: the model, the cache manager, and the staging buffers."""
+
+    def __init__(self, model: DecoderModel, cache: CacheManager) -> None:
+        if model.device.type != "cuda":
+            raise RuntimeError("the step function runs on a CUDA device only (there is no CPU path)")
+        ops.library()  # fail now, loudly, if the kernels cannot be built or loaded
+        self.model = model
+        self.cache = cache
+        self.device = model.device
+        self.status = cache.status if cache.status is not None else ops.new_status(self.device)
+        self._pinned: torch.Tensor | None = None
+        self._copy_done: torch.cuda.Event | None = None
+        self.launches = 0  # steps run (for accounting)
+
+    def _staging(self, n_ints: int) -> torch.Tensor:
+        if self._pinned is None or self._pinned.numel() < n_ints:
+            self._pinned = torch.empty(max(n_ints, 4096), dtype=torch.int32, pin_memory=True)
+        return self._pinned
+
+    def step(self, entries: list[StepEntry]) -> torch.Tensor | None:
+        """Run the entries as one batch.  Returns float32 logits [wanted rows, vocab] in the order
+        of the entries and of each entry's ``want``, or None when nothing is wanted."""
+        entries = [e for e in entries if e.tokens]
+        if not entries:
+            return None
+        cache = self.cache
+        reqs = []
+        seen = set()
+        for e in entries:
+            if e.request_id in seen:
+                raise ValueError(f"request {e.request_id!r} appears twice in one step")
+            seen.add(e.request_id)
+            req = cache.get(e.request_id)
+            cache.reserve(req, req.num_computed + len(e.tokens))
+            reqs.append(req)
+            bad = [w for w in e.want if not 0 <= w < len(e.tokens)]
+            if bad:
+                raise ValueError(f"request {e.request_id!r}: wanted places {bad} outside its {len(e.tokens)} tokens")
+
+        S = len(entries)
+        q_lens = [len(e.tokens) for e in entries]
+        N = sum(q_lens)
+        starts = [r.num_computed for r in reqs]
+        ctx_lens = [s + q for s, q in zip(starts, q_lens)]
+        G = len(cache.groups)
+        max_blocks = max(1, max((len(r.tables[g]) for r in reqs for g in range(G)), default=1))
+        R = sum(len(e.want) for e in entries)
+
+        # layout of the one staging buffer (every segment starts on a 16-byte boundary)
+        seg = {}
+        off = 0
+        for name, size in (("tokens", N), ("positions", N), ("tok_seq", N), ("q_start", S + 1),
+                           ("ctx_lens", S), ("rows", R), ("state", S)):
+            seg[name] = (off, size)
+            off += _pad4(size)
+        for g in range(G):
+            seg[f"slots{g}"] = (off, N)
+            off += _pad4(N)
+            seg[f"tables{g}"] = (off, S * max_blocks)
+            off += _pad4(S * max_blocks)
+        if self._copy_done is not None:
+            self._copy_done.synchronize()  # the last step's upload has left the staging buffer
+        host = self._staging(off)
+        h = host.numpy()
+
+        def put(name, values):
+            o, size = seg[name]
+            h[o : o + size] = values
+
+        tokens = np.fromiter((t for e in entries for t in e.tokens), dtype=np.int64, count=N)
+        put("tokens", tokens)
+        put("positions", np.concatenate([np.arange(s, s + q, dtype=np.int32) for s, q in zip(starts, q_lens)]))
+        put("tok_seq", np.repeat(np.arange(S, dtype=np.int32), q_lens))
+        q_start = np.zeros(S + 1, dtype=np.int32)
+        np.cumsum(q_lens, out=q_start[1:])
+        put("q_start", q_start)
+        put("ctx_lens", ctx_lens)
+        rows = [int(q_start[i]) + w for i, e in enumerate(entries) for w in e.want]
+        put("rows", rows)
+        put("state", [r.state_slot if r.state_slot is not None else 0 for r in reqs])
+        ps = cache.page_size
+        for g in range(G):
+            slots = np.empty(N, dtype=np.int32)
+            tables = np.full((S, max_blocks), NO_PAGE, dtype=np.int32)
+            for i, r in enumerate(reqs):
+                table = np.asarray(r.tables[g], dtype=np.int32)
+                tables[i, : len(table)] = table
+                pos = np.arange(starts[i], ctx_lens[i], dtype=np.int32)
+                pages = table[pos // ps]
+                if (pages == NO_PAGE).any():
+                    raise RuntimeError(f"request {r.request_id!r}: a token lands in a page that was given back")
+                slots[q_start[i] : q_start[i + 1]] = pages * ps + pos % ps
+            put(f"slots{g}", slots)
+            put(f"tables{g}", tables.reshape(-1))
+
+        dev = torch.empty(off, dtype=torch.int32, device=self.device)
+        dev.copy_(host[:off], non_blocking=True)
+        if self._copy_done is None:
+            self._copy_done = torch.cuda.Event()
+        self._copy_done.record()
+
+        def view(name):
+            o, size = seg[name]
+            return dev[o : o + size]
+
+        ctx = StepContext(
+            dtype=self.model.dtype, device=self.device, status=self.status, num_tokens=N, num_seqs=S,
+            positions=view("positions"), tok_seq=view("tok_seq"), q_start=view("q_start"),
+            ctx_lens=view("ctx_lens"), q_lens_host=q_lens, ctx_lens_host=ctx_lens,
+            max_q_len=max(q_lens), max_ctx_len=max(ctx_lens),
+        )
+        state_slots = view("state").to(torch.int64) if cache.state.needs else None
+        ctx.views = cache.views(
+            [view(f"tables{g}").view(S, max_blocks) for g in range(G)],
+            [view(f"slots{g}") for g in range(G)],
+            state_slots, [r.state_slot for r in reqs] if cache.state.needs else [],
+        )
+        logits = self.model.forward(ctx, view("tokens"), view("rows") if R else None)
+        self.launches += 1
+        for r, end in zip(reqs, ctx_lens):
+            r.num_computed = end
+            cache.release_behind_window(r, end)
+        return logits
+
+    def check_status(self) -> None:
+        """Raise if any kernel reported an out-of-range index since the last check."""
+        ops.raise_on_status(self.status)

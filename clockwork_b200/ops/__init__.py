@@ -1,0 +1,264 @@
+"""Python faces of the CUDA kernels.  Each checks shapes, dtypes and contiguity, then calls the
+``extern "C"`` entry point on the current CUDA stream.  Tensors must live on a CUDA device;
+nothing here has a CPU path."""
+
+from __future__ import annotations
+
+import torch
+
+from .library import KernelLibraryError, check, library
+
+__all__ = [
+    "KernelLibraryError", "library", "dtype_code", "new_status", "raise_on_status",
+    "embed", "add_rmsnorm", "rmsnorm_rows", "silu_mul", "add_to_residual", "gemm_ref",
+    "gemm_ref_swiglu", "rope_store", "copy_pages", "attention_ref", "argmax", "sample",
+]
+
+STATUS_MESSAGES = {
+    1: "token id outside the vocabulary (row {a}, id {b})",
+    2: "cache slot outside the pool (token {a}, slot {b})",
+    3: "page id outside the pool ({a}, {b})",
+    4: "a device-side wait ran out (kernel {a}, stage {b})",
+    5: "row index outside the batch (row {a}, index {b})",
+}
+
+
+def dtype_code(dtype: torch.dtype) -> int:
+    if dtype == torch.float32:
+        return 0
+    if dtype == torch.bfloat16:
+        return 1
+    raise ValueError(f"unsupported dtype {dtype}; the kernels take float32 and bfloat16")
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _ptr(t: torch.Tensor | None) -> int | None:
+    return None if t is None else t.data_ptr()
+
+
+def _need(t: torch.Tensor, dtype: torch.dtype | None, name: str, ndim: int | None = None) -> None:
+    if not t.is_cuda:
+        raise ValueError(f"{name} must be a CUDA tensor (no CPU path exists)")
+    if dtype is not None and t.dtype != dtype:
+        raise ValueError(f"{name} must be {dtype}, got {t.dtype}")
+    if not t.is_contiguous():
+        raise ValueError(f"{name} must be contiguous")
+    if ndim is not None and t.dim() != ndim:
+        raise ValueError(f"{name} must have {ndim} dims, got shape {tuple(t.shape)}")
+
+
+def new_status(device) -> torch.Tensor:
+    return torch.zeros(4, dtype=torch.int32, device=device)
+
+
+def raise_on_status(status: torch.Tensor) -> None:
+    """Reads the status words (one small device-to-host copy) and raises if a kernel
+    recorded an out-of-range index."""
+    code, a, b, _ = status.tolist()
+    if code != 0:
+        status.zero_()
+        raise RuntimeError("kernel status: " + STATUS_MESSAGES.get(code, f"code {code}").format(a=a, b=b))
+
+
+def embed(table: torch.Tensor, ids: torch.Tensor, status: torch.Tensor) -> torch.Tensor:
+    """float32 [N, H] rows of ``table`` (float32 or bfloat16 [V, H]) for int32 ``ids`` [N]."""
+    _need(table, None, "table", 2)
+    _need(ids, torch.int32, "ids", 1)
+    n, (v, h) = ids.shape[0], table.shape
+    out = torch.empty((n, h), dtype=torch.float32, device=table.device)
+    check(library().cw_embed(_ptr(out), _ptr(table), _ptr(ids), n, h, v, dtype_code(table.dtype), _ptr(status), _stream()), "embed")
+    return out
+
+
+def add_rmsnorm(resid: torch.Tensor, delta: torch.Tensor | None, weight: torch.Tensor, eps: float,
+                out_dtype: torch.dtype, status: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """``resid += delta`` (if given), then returns ``weight * rmsnorm(resid)`` as ``out_dtype``."""
+    _need(resid, torch.float32, "resid", 2)
+    _need(weight, torch.float32, "weight", 1)
+    n, h = resid.shape
+    if weight.shape[0] != h:
+        raise ValueError(f"norm weight has {weight.shape[0]} elements, rows have {h}")
+    if delta is not None:
+        _need(delta, out_dtype, "delta", 2)
+        if delta.shape != resid.shape:
+            raise ValueError(f"delta {tuple(delta.shape)} does not match residual {tuple(resid.shape)}")
+    if out is None:
+        out = torch.empty((n, h), dtype=out_dtype, device=resid.device)
+    check(library().cw_add_rmsnorm(_ptr(resid), _ptr(delta), _ptr(weight), _ptr(out), None, n, n, h, float(eps),
+                                   dtype_code(out_dtype), _ptr(status), _stream()), "add_rmsnorm")
+    return out
+
+
+def rmsnorm_rows(resid: torch.Tensor, rows: torch.Tensor, weight: torch.Tensor, eps: float,
+                 out_dtype: torch.dtype, status: torch.Tensor) -> torch.Tensor:
+    """``weight * rmsnorm(resid[rows])`` as ``out_dtype`` [R, H]."""
+    _need(resid, torch.float32, "resid", 2)
+    _need(rows, torch.int32, "rows", 1)
+    _need(weight, torch.float32, "weight", 1)
+    n, h = resid.shape
+    r = rows.shape[0]
+    out = torch.empty((r, h), dtype=out_dtype, device=resid.device)
+    check(library().cw_add_rmsnorm(_ptr(resid), None, _ptr(weight), _ptr(out), _ptr(rows), r, n, h, float(eps),
+                                   dtype_code(out_dtype), _ptr(status), _stream()), "rmsnorm_rows")
+    return out
+
+
+def silu_mul(gate_up: torch.Tensor) -> torch.Tensor:
+    _need(gate_up, None, "gate_up", 2)
+    n, two_i = gate_up.shape
+    if two_i % 2:
+        raise ValueError("gate_up must have an even number of columns")
+    out = torch.empty((n, two_i // 2), dtype=gate_up.dtype, device=gate_up.device)
+    check(library().cw_silu_mul(_ptr(gate_up), _ptr(out), n, two_i // 2, dtype_code(gate_up.dtype), _stream()), "silu_mul")
+    return out
+
+
+def add_to_residual(resid: torch.Tensor, delta: torch.Tensor) -> None:
+    _need(resid, torch.float32, "resid", 2)
+    _need(delta, None, "delta", 2)
+    if delta.shape != resid.shape:
+        raise ValueError("delta and residual shapes differ")
+    n, h = resid.shape
+    check(library().cw_add_to_residual(_ptr(resid), _ptr(delta), n, h, dtype_code(delta.dtype), _stream()), "add_to_residual")
+
+
+EPILOGUE_STORE, EPILOGUE_ADD_F32, EPILOGUE_STORE_F32 = 0, 1, 2
+
+
+def gemm_ref(a: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None, *,
+             out: torch.Tensor | None = None, epilogue: int = EPILOGUE_STORE) -> torch.Tensor:
+    """``a [M,K] @ w[N,K]^T (+ bias)`` on the CUDA cores with float32 accumulation.
+    ``a`` may be a column slice of a wider matrix (row stride > K).  Epilogues: store in
+    ``a``'s dtype; add into the float32 ``out``; store float32."""
+    if not a.is_cuda or a.dim() != 2 or a.stride(1) != 1:
+        raise ValueError("a must be a 2-d CUDA tensor with unit column stride")
+    _need(w, a.dtype, "w", 2)
+    m, k = a.shape
+    n = w.shape[0]
+    if w.shape[1] != k:
+        raise ValueError(f"inner sizes differ: a has K={k}, w has K={w.shape[1]}")
+    if bias is not None:
+        _need(bias, torch.float32, "bias", 1)
+        if bias.shape[0] != n:
+            raise ValueError("bias length does not match w's rows")
+    want = a.dtype if epilogue == EPILOGUE_STORE else torch.float32
+    if out is None:
+        if epilogue == EPILOGUE_ADD_F32:
+            raise ValueError("the add epilogue needs an output to add into")
+        out = torch.empty((m, n), dtype=want, device=a.device)
+    _need(out, want, "out", 2)
+    if tuple(out.shape) != (m, n):
+        raise ValueError(f"out has shape {tuple(out.shape)}, expected {(m, n)}")
+    lda = a.stride(0) if m > 1 else max(a.stride(0), k)
+    check(library().cw_gemm_ref(_ptr(a), _ptr(w), _ptr(bias), _ptr(out), m, n, k, lda, n, epilogue,
+                                dtype_code(a.dtype), _stream()), "gemm_ref")
+    return out
+
+
+def gemm_ref_swiglu(a: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor) -> torch.Tensor:
+    _need(a, None, "a", 2)
+    _need(w_gate, a.dtype, "w_gate", 2)
+    _need(w_up, a.dtype, "w_up", 2)
+    m, k = a.shape
+    n = w_gate.shape[0]
+    if w_gate.shape != w_up.shape or w_gate.shape[1] != k:
+        raise ValueError("gate and up weights must both be [N, K] with a's K")
+    out = torch.empty((m, n), dtype=a.dtype, device=a.device)
+    check(library().cw_gemm_ref_swiglu(_ptr(a), _ptr(w_gate), _ptr(w_up), _ptr(out), m, n, k,
+                                       dtype_code(a.dtype), _stream()), "gemm_ref_swiglu")
+    return out
+
+
+def rope_store(qkv: torch.Tensor, positions: torch.Tensor, slots: torch.Tensor | None,
+               inv_freq: torch.Tensor | None, k_cache: torch.Tensor | None, v_cache: torch.Tensor | None,
+               num_heads: int, num_kv_heads: int, head_dim: int, rotary_dim: int,
+               status: torch.Tensor, write_cache: bool = True) -> None:
+    """Rotates q and k inside ``qkv`` [N, (nh+2nkv)*hd] in place and stores k, v at ``slots``
+    of the caches ([pages, page_size, nkv, hd] each)."""
+    _need(qkv, None, "qkv", 2)
+    _need(positions, torch.int32, "positions", 1)
+    n = qkv.shape[0]
+    if qkv.shape[1] != (num_heads + 2 * num_kv_heads) * head_dim:
+        raise ValueError("qkv width does not match the head counts")
+    num_slots = 0
+    if write_cache:
+        if k_cache is None or v_cache is None or slots is None:
+            raise ValueError("writing the cache needs k_cache, v_cache and slots")
+        _need(slots, torch.int32, "slots", 1)
+        _need(k_cache, qkv.dtype, "k_cache", 4)
+        _need(v_cache, qkv.dtype, "v_cache", 4)
+        if tuple(k_cache.shape[2:]) != (num_kv_heads, head_dim) or k_cache.shape != v_cache.shape:
+            raise ValueError("cache shape does not match the KV head count and head size")
+        num_slots = k_cache.shape[0] * k_cache.shape[1]
+    if inv_freq is not None:
+        _need(inv_freq, torch.float32, "inv_freq", 1)
+        if inv_freq.shape[0] * 2 != rotary_dim:
+            raise ValueError("inv_freq must hold rotary_dim/2 frequencies")
+    check(library().cw_rope_store(_ptr(qkv), _ptr(positions), _ptr(slots), _ptr(inv_freq), _ptr(k_cache), _ptr(v_cache),
+                                  n, num_heads, num_kv_heads, head_dim, rotary_dim, num_slots,
+                                  1 if write_cache else 0, dtype_code(qkv.dtype), _ptr(status), _stream()), "rope_store")
+
+
+def copy_pages(cache: torch.Tensor, pairs: torch.Tensor, status: torch.Tensor) -> None:
+    """``cache`` [planes, pages, ...]: copies page ``pairs[i,0]`` to ``pairs[i,1]`` in every plane."""
+    _need(cache, None, "cache")
+    _need(pairs, torch.int32, "pairs", 2)
+    planes, pages = cache.shape[0], cache.shape[1]
+    page_bytes = cache[0, 0].numel() * cache.element_size()
+    check(library().cw_copy_pages(_ptr(cache), _ptr(pairs), pairs.shape[0], planes, pages, page_bytes,
+                                  _ptr(status), _stream()), "copy_pages")
+
+
+def attention_ref(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, block_tables: torch.Tensor,
+                  tok_seq: torch.Tensor, positions: torch.Tensor, num_heads: int, num_kv_heads: int,
+                  head_dim: int, scale: float, window: int | None, status: torch.Tensor) -> torch.Tensor:
+    """General paged causal attention.  ``q`` is [N, >= nh*hd] with unit column stride (the
+    first nh*hd columns of each row are the query heads); returns [N, nh*hd]."""
+    if not q.is_cuda or q.dim() != 2 or q.stride(1) != 1:
+        raise ValueError("q must be a 2-d CUDA tensor with unit column stride")
+    _need(k_cache, q.dtype, "k_cache", 4)
+    _need(v_cache, q.dtype, "v_cache", 4)
+    _need(block_tables, torch.int32, "block_tables", 2)
+    _need(tok_seq, torch.int32, "tok_seq", 1)
+    _need(positions, torch.int32, "positions", 1)
+    n = q.shape[0]
+    pages, page_size = k_cache.shape[0], k_cache.shape[1]
+    if tuple(k_cache.shape[2:]) != (num_kv_heads, head_dim):
+        raise ValueError("cache shape does not match the KV head count and head size")
+    if head_dim > 256:
+        raise ValueError(f"head_dim {head_dim} is larger than the attention kernels take (256)")
+    out = torch.empty((n, num_heads * head_dim), dtype=q.dtype, device=q.device)
+    check(library().cw_attention_ref(_ptr(q), q.stride(0), _ptr(out), _ptr(k_cache), _ptr(v_cache), _ptr(block_tables),
+                                     _ptr(tok_seq), _ptr(positions), n, num_heads, num_kv_heads, head_dim, page_size,
+                                     block_tables.shape[1], pages, float(scale), int(window or 0),
+                                     dtype_code(q.dtype), _ptr(status), _stream()), "attention_ref")
+    return out
+
+
+def argmax(logits: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    _need(logits, torch.float32, "logits", 2)
+    r, v = logits.shape
+    if out is None:
+        out = torch.empty((r,), dtype=torch.int32, device=logits.device)
+    check(library().cw_argmax(_ptr(logits), _ptr(out), r, v, v, _stream()), "argmax")
+    return out
+
+
+def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor, top_p: torch.Tensor,
+           uniform: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """One token per row; rows with temperature 0 are greedy."""
+    _need(logits, torch.float32, "logits", 2)
+    r, v = logits.shape
+    for name, t, dt in (("temperature", temperature, torch.float32), ("top_k", top_k, torch.int32),
+                        ("top_p", top_p, torch.float32), ("uniform", uniform, torch.float32)):
+        _need(t, dt, name, 1)
+        if t.shape[0] != r:
+            raise ValueError(f"{name} must have one entry per row")
+    if out is None:
+        out = torch.empty((r,), dtype=torch.int32, device=logits.device)
+    check(library().cw_sample(_ptr(logits), _ptr(temperature), _ptr(top_k), _ptr(top_p), _ptr(uniform), _ptr(out),
+                              r, v, v, _stream()), "sample")
+    return out

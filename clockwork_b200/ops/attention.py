@@ -1,0 +1,26 @@
+"""Chooses the attention kernel for a step.
+
+float32 runs use the general kernel (``cw_attention_ref``) for everything.  bfloat16 runs use
+the split-context decode kernel when every request brings one token and the tensor-core
+prefill kernel for prompt portions, when those kernels take the sizes; otherwise the general
+kernel on bfloat16 data.  All of them read the same cache through the same block tables."""
+
+from __future__ import annotations
+
+import torch
+
+from . import attention_ref
+
+_decode = None  # set by ops.attention_decode when present
+_prefill = None  # set by ops.attention_prefill when present
+
+
+def paged_attention(ctx, qkv: torch.Tensor, view, num_heads: int, num_kv_heads: int, head_dim: int,
+                    scale: float, window: int | None) -> torch.Tensor:
+    if qkv.dtype == torch.bfloat16:
+        if ctx.all_single_token and _decode is not None and _decode.accepts(ctx, view, num_heads, num_kv_heads, head_dim, window):
+            return _decode.run(ctx, qkv, view, num_heads, num_kv_heads, head_dim, scale, window)
+        if not ctx.all_single_token and _prefill is not None and _prefill.accepts(ctx, view, num_heads, num_kv_heads, head_dim, window):
+            return _prefill.run(ctx, qkv, view, num_heads, num_kv_heads, head_dim, scale, window)
+    return attention_ref(qkv, view.k_cache, view.v_cache, view.block_tables, ctx.tok_seq, ctx.positions,
+                         num_heads, num_kv_heads, head_dim, scale, window, ctx.status)

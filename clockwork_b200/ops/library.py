@@ -1,0 +1,79 @@
+"""Loads the kernel library (building it at first use) and declares its C entry points."""
+
+from __future__ import annotations
+
+import ctypes
+import threading
+from ctypes import c_float, c_int, c_longlong, c_void_p
+
+_lock = threading.Lock()
+_lib: ctypes.CDLL | None = None
+
+P, I, F, LL = c_void_p, c_int, c_float, c_longlong
+
+# name -> argument types (the stream is the last c_void_p of each)
+_SIGNATURES: dict[str, list] = {
+    "cw_embed": [P, P, P, I, I, I, I, P, P],
+    "cw_add_rmsnorm": [P, P, P, P, P, I, I, I, F, I, P, P],
+    "cw_silu_mul": [P, P, I, I, I, P],
+    "cw_add_to_residual": [P, P, I, I, I, P],
+    "cw_gemm_ref": [P, P, P, P, I, I, I, I, I, I, I, P],
+    "cw_gemm_ref_swiglu": [P, P, P, P, I, I, I, I, P],
+    "cw_rope_store": [P, P, P, P, P, P, I, I, I, I, I, I, I, I, P, P],
+    "cw_copy_pages": [P, P, I, I, I, LL, P, P],
+    "cw_attention_ref": [P, I, P, P, P, P, P, P, I, I, I, I, I, I, I, F, I, I, P, P],
+    "cw_argmax": [P, P, I, I, LL, P],
+    "cw_sample": [P, P, P, P, P, P, I, I, LL, P],
+}
+_OPTIONAL: dict[str, list] = {}
+
+
+class KernelLibraryError(RuntimeError):
+    pass
+
+
+def register_optional(name: str, argtypes: list) -> None:
+    _OPTIONAL[name] = argtypes
+
+
+def library() -> ctypes.CDLL:
+    """The loaded library.  Raises ``KernelLibraryError`` when it cannot be built or loaded:
+    there is no fallback path."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    with _lock:
+        if _lib is not None:
+            return _lib
+        from ..csrc.build import ensure_built
+
+        try:
+            path = ensure_built()
+            lib = ctypes.CDLL(str(path))
+        except Exception as exc:  # noqa: BLE001
+            raise KernelLibraryError(
+                f"the clockwork_b200 CUDA kernels are unavailable ({exc}); "
+                "they are required: there is no CPU or library fallback"
+            ) from exc
+        for name, argtypes in {**_SIGNATURES, **_OPTIONAL}.items():
+            try:
+                fn = getattr(lib, name)
+            except AttributeError:
+                if name in _OPTIONAL:
+                    continue
+                raise KernelLibraryError(f"{path} does not export {name}") from None
+            fn.argtypes = argtypes
+            fn.restype = c_int
+        _lib = lib
+        return lib
+
+
+ERROR_NAMES = {-1: "refused size", -2: "unknown dtype code", -3: "unsupported combination", -4: "set-up failed"}
+
+
+def check(code: int, what: str) -> None:
+    if code == 0:
+        return
+    if code < 0:
+        raise ValueError(f"{what}: kernel refused the call ({ERROR_NAMES.get(code, code)})")
+    raise RuntimeError(f"{what}: CUDA error {code} at launch")

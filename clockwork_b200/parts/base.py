@@ -1,0 +1,180 @@
+"""Interfaces of the parts a layer is put together from, and what a step hands to them.
+
+A *part* owns some named tensors and one piece of the layer's arithmetic.  Parts are built
+from a ``PartSpec`` (kind + parameters); they never see the model's configuration and do not
+know which model they are in.  The kinds:
+
+* **Norm**      ``forward(stream) -> x``: adds the stream's pending delta into the float32
+  residual, returns the normalised activations in the run's dtype.
+* **PositionEncoding**  ``apply_and_store(ctx, qkv, view, ...)``: encodes positions into q and k
+  and stores k, v into the cache view.
+* **Mixer**     ``forward(ctx, x, view, stream) -> delta | None``: mixes tokens of a request
+  (attention here).  It says what per-request memory it needs with ``cache_need()``: pages
+  (``PagedKVNeed``), a fixed-size state slot (``SlotStateNeed``) or nothing.
+* **FeedForward** ``forward(ctx, x, stream) -> delta | None``.
+* **Block**     ``forward(ctx, stream, view)``: the arrangement of the above in one layer.
+
+A mixer or feed-forward returns its contribution to the residual stream as a tensor in the
+run's dtype (the next norm adds it), or ``None`` when it has already added it into
+``stream.residual`` itself (a fused epilogue).
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Callable, Iterable
+
+import torch
+
+from ..config.model_spec import PartSpec
+from ..weights.decl import TensorDecl
+
+Fetch = Callable[[str], torch.Tensor]
+
+
+@dataclass(frozen=True)
+class PagedKVNeed:
+    """The mixer keeps keys and values per token, in pages.  ``window``: only the last
+    ``window`` tokens are ever read (pages behind it can be given back); None: all."""
+
+    num_kv_heads: int
+    head_dim: int
+    window: int | None = None
+
+
+@dataclass(frozen=True)
+class SlotStateNeed:
+    """The mixer keeps a state of fixed size per request (``shape`` per layer), float32
+    unless said otherwise.  It is zero when a request starts."""
+
+    shape: tuple[int, ...]
+    dtype: torch.dtype = torch.float32
+
+
+@dataclass
+class PagedView:
+    """One cache layer of a paged group as a step sees it."""
+
+    k_cache: torch.Tensor  # [pages, page_size, kv_heads, head_dim]
+    v_cache: torch.Tensor
+    block_tables: torch.Tensor  # int32 [S, max_blocks] of this step's requests (-1: no page)
+    slots: torch.Tensor  # int32 [N]: where each token's k/v go (page*page_size + offset)
+    write: bool = True
+
+    @property
+    def page_size(self) -> int:
+        return self.k_cache.shape[1]
+
+
+@dataclass
+class StateView:
+    """One layer's fixed-size states: ``state[slots[s]]`` belongs to request ``s`` of the step."""
+
+    state: torch.Tensor  # [num_slots, *shape]
+    slots: torch.Tensor  # int64 [S]
+    slots_host: list[int] = field(default_factory=list)
+
+
+@dataclass
+class StepContext:
+    """Everything a part may ask about the step it runs in.  Tokens of all requests are one
+    flat batch of ``num_tokens`` rows; request ``s`` owns rows ``q_start[s]:q_start[s+1]``."""
+
+    dtype: torch.dtype
+    device: torch.device
+    status: torch.Tensor  # int32 status words that kernels report into
+    num_tokens: int
+    num_seqs: int
+    positions: torch.Tensor  # int32 [N] absolute position of each token in its request
+    tok_seq: torch.Tensor  # int32 [N] index of the token's request within this step (-1: padding)
+    q_start: torch.Tensor  # int32 [S+1]
+    ctx_lens: torch.Tensor  # int32 [S] tokens of the request that are in the cache after this step
+    q_lens_host: list[int]
+    ctx_lens_host: list[int]
+    max_q_len: int
+    max_ctx_len: int
+    views: dict[int, PagedView | StateView] = field(default_factory=dict)  # by cache layer
+    extras: dict = field(default_factory=dict)  # scratch that kernels share within a step
+
+    @property
+    def all_single_token(self) -> bool:
+        return self.max_q_len <= 1
+
+
+class ResidualStream:
+    """The float32 residual [N, H] plus at most one contribution not yet added to it."""
+
+    def __init__(self, residual: torch.Tensor) -> None:
+        self.residual = residual
+        self.pending: torch.Tensor | None = None
+
+    def push(self, delta: torch.Tensor | None) -> None:
+        if delta is None:
+            return
+        if self.pending is not None:
+            self.flush()
+        self.pending = delta
+
+    def flush(self) -> None:
+        if self.pending is not None:
+            from .. import ops
+
+            ops.add_to_residual(self.residual, self.pending)
+            self.pending = None
+
+    def residual_after_flush(self) -> torch.Tensor:
+        """The float32 residual with nothing pending: what a fused epilogue adds into."""
+        self.flush()
+        return self.residual
+
+
+class Part:
+    """Base of all parts: a name prefix for its tensors, declarations, and loading."""
+
+    def __init__(self, spec: PartSpec, prefix: str, dtype: torch.dtype, device: torch.device) -> None:
+        self.spec = spec
+        self.prefix = prefix
+        self.dtype = dtype
+        self.device = device
+
+    def name(self, suffix: str) -> str:
+        return f"{self.prefix}.{suffix}" if self.prefix else suffix
+
+    def tensor_decls(self) -> Iterable[TensorDecl]:
+        return ()
+
+    def load_weights(self, fetch: Fetch) -> None:
+        pass
+
+
+class Norm(Part):
+    def forward(self, stream: ResidualStream, status: torch.Tensor) -> torch.Tensor:
+        raise NotImplementedError
+
+    def forward_rows(self, stream: ResidualStream, rows: torch.Tensor, status: torch.Tensor) -> torch.Tensor:
+        """Normalised activations of the selected residual rows only."""
+        raise NotImplementedError
+
+
+class PositionEncoding(Part):
+    pass
+
+
+class Mixer(Part):
+    def cache_need(self) -> PagedKVNeed | SlotStateNeed | None:
+        return None
+
+    def forward(self, ctx: StepContext, x: torch.Tensor, view, stream: ResidualStream) -> torch.Tensor | None:
+        raise NotImplementedError
+
+
+class FeedForward(Part):
+    def forward(self, ctx: StepContext, x: torch.Tensor, stream: ResidualStream) -> torch.Tensor | None:
+        raise NotImplementedError
+
+
+class Block(Part):
+    mixer: Mixer
+
+    def forward(self, ctx: StepContext, stream: ResidualStream, view) -> None:
+        raise NotImplementedError

@@ -1,0 +1,30 @@
+"""A weight matrix in ``nn.Linear`` layout ([out, in], optional float32 bias) and the matrix
+products the parts need from it.  In a float32 run every product is the plain CUDA-core kernel
+(true float32).  In a bfloat16 run products go to the tensor-core kernel when it takes the
+sizes, else to the same plain kernel with bfloat16 operands."""
+
+from __future__ import annotations
+
+import torch
+
+from .. import ops
+from ..ops import gemm as gemm_ops
+
+
+class Linear:
+    def __init__(self, weight: torch.Tensor, bias: torch.Tensor | None = None) -> None:
+        self.weight = weight
+        self.bias = bias
+        self.out_features, self.in_features = weight.shape
+
+    def __call__(self, x: torch.Tensor) -> torch.Tensor:
+        """x [M, K] -> [M, N] in x's dtype."""
+        return gemm_ops.linear(x, self.weight, self.bias)
+
+    def add_into(self, x: torch.Tensor, residual: torch.Tensor) -> None:
+        """residual (float32 [M, N]) += x W^T (+ bias), the sum done in float32."""
+        gemm_ops.linear_add_into(x, self.weight, self.bias, residual)
+
+    def to_float32(self, x: torch.Tensor) -> torch.Tensor:
+        """x W^T as float32 (logits)."""
+        return gemm_ops.linear_f32(x, self.weight, self.bias)
