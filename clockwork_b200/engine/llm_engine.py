@@ -1,0 +1,252 @@
+"""The synchronous engine: requests in, tokens out.
+
+API after the reference's ``clockwork/engine/llm_engine.py:35-177``: ``add_request``, ``step``,
+``generate``, ``abort_request``, ``has_unfinished_requests``, ``stats``.  One ``step`` is: schedule,
+run the scheduled portions as one batch through the step function, sample where a sequence's
+last token was computed, record prompt pages in the prefix cache, detect finished sequences,
+free them (``llm_engine.py:99-125``).  Finish rules are the reference's (``:200-242``): an EOS
+token (unless ``ignore_eos``) or a ``stop_token_ids`` token ends with "stop" and stays in the
+output; stop strings end with "stop" when a tokenizer is present; ``max_tokens`` or
+``max_model_len`` end with "length".
+
+A tokenizer is optional here (the reference requires one, ``:42-43``): without it prompts are
+token ids and texts stay empty.
+"""
+
+from __future__ import annotations
+
+import itertools
+from pathlib import Path
+
+import torch
+
+from ..cache.manager import CacheManager
+from ..cache.prefix import PrefixCache
+from ..config.engine import EngineConfig
+from ..parts.base import PagedKVNeed
+from ..parts.model import DecoderModel
+from ..sampling.params import SamplingParams
+from ..sampling.sampler import Sampler
+from .loading import load_model
+from .scheduler import Scheduler
+from .sequence import RequestOutput, Sequence, SequenceStatus
+from .step import ModelRunner, StepEntry
+
+
+def _eos_ids(tokenizer, spec) -> frozenset[int]:
+    # clockwork/engine/llm_engine.py:24-32: the tokenizer's EOS, else config.json's, else none
+    eos = getattr(tokenizer, "eos_token_id", None) if tokenizer is not None else None
+    if eos is None:
+        return frozenset(spec.eos_token_ids)
+    return frozenset({eos}) if isinstance(eos, int) else frozenset(eos)
+
+
+class LLMEngine:
+    def __init__(self, cfg: EngineConfig, model: DecoderModel | None = None, tokenizer=None,
+                 device: str = "cuda:0") -> None:
+        self.cfg = cfg
+        if model is None:
+            model = load_model(cfg.model.model, cfg.model.dtype, device)
+        self.model = model
+        self.tokenizer = tokenizer
+        needs = model.cache_needs()
+        slots = cfg.cache.num_state_slots or cfg.scheduler.max_num_seqs
+        self.cache = CacheManager(
+            needs, num_pages=cfg.cache.num_blocks, page_size=cfg.cache.block_size, dtype=model.dtype,
+            device=model.device, num_state_slots=slots, watermark=cfg.cache.watermark,
+        )
+        # prefixes can be shared only when one group of full-attention layers holds all state
+        shareable = (
+            len(self.cache.groups) == 1 and self.cache.groups[0].need.window is None
+            and not self.cache.state.needs
+            and all(isinstance(n, PagedKVNeed) for n in needs.values())
+        )
+        self.prefix_cache = PrefixCache(
+            self.cache.groups[0].allocator if self.cache.groups else None, cfg.cache.block_size,
+            enabled=cfg.cache.enable_prefix_cache and shareable,
+        ) if self.cache.groups else None
+        self.scheduler = Scheduler(cfg.scheduler, self.cache, self.prefix_cache)
+        self.runner = ModelRunner(model, self.cache)
+        self.sampler = Sampler(model.device, default_seed=cfg.model.seed)
+        self._eos = _eos_ids(tokenizer, model.spec)
+        self._seqs: dict[str, Sequence] = {}
+        self._texts: dict[str, str] = {}
+        # arrival is a counter, not a clock, so scheduling never depends on wall time
+        # (clockwork/engine/llm_engine.py:57-59)
+        self._arrival = itertools.count()
+        self._generate_counter = itertools.count()
+
+    @classmethod
+    def from_config(cls, cfg: EngineConfig) -> "LLMEngine":
+        return cls(cfg)
+
+    @classmethod
+    def from_model_dir(cls, model_dir: str | Path, **overrides) -> "LLMEngine":
+        return cls(EngineConfig.defaults(str(model_dir), **overrides))
+
+    # ---- requests ---------------------------------------------------------------------------------
+    def add_request(self, request_id: str, prompt: str | None = None,
+                    sampling_params: SamplingParams | None = None,
+                    prompt_token_ids: list[int] | None = None) -> None:
+        """Queue one request; exactly one of ``prompt`` and ``prompt_token_ids``
+        (clockwork/engine/llm_engine.py:67-97)."""
+        if (prompt is None) == (prompt_token_ids is None):
+            raise ValueError("provide exactly one of prompt or prompt_token_ids")
+        if request_id in self._seqs:
+            raise ValueError(f"request id {request_id!r} is already active")
+        if prompt_token_ids is None:
+            if self.tokenizer is None:
+                raise ValueError("a text prompt needs a tokenizer; pass prompt_token_ids instead")
+            prompt_token_ids = self.tokenizer.encode(prompt)
+        prompt_token_ids = [int(t) for t in prompt_token_ids]
+        if not prompt_token_ids:
+            raise ValueError("prompt must contain at least one token")
+        if len(prompt_token_ids) >= self.cfg.model.max_model_len:
+            raise ValueError(
+                f"prompt of {len(prompt_token_ids)} tokens leaves no room to generate "
+                f"within max_model_len {self.cfg.model.max_model_len}"
+            )
+        vocab = self.model.spec.vocab_size
+        bad = [t for t in prompt_token_ids if not 0 <= t < vocab]
+        if bad:
+            raise ValueError(f"prompt holds token ids outside the vocabulary of {vocab}: {bad[:5]}")
+        params = sampling_params if sampling_params is not None else SamplingParams()
+        if params.stop and self.tokenizer is None:
+            raise ValueError("stop strings need a tokenizer; use stop_token_ids")
+        seq = Sequence(request_id, prompt_token_ids, params, arrival_time=float(next(self._arrival)))
+        self._seqs[request_id] = seq
+        self._texts[request_id] = ""
+        self.scheduler.add_seq(seq)
+
+    def has_unfinished_requests(self) -> bool:
+        return self.scheduler.has_unfinished()
+
+    def abort_request(self, request_id: str) -> None:
+        self.scheduler.abort(request_id)
+        self._forget(request_id)
+
+    def _forget(self, request_id: str) -> None:
+        self._seqs.pop(request_id, None)
+        self._texts.pop(request_id, None)
+
+    # ---- one iteration ------------------------------------------------------------------------------
+    def step(self) -> list[RequestOutput]:
+        out = self.scheduler.schedule()
+        if not out.portions:
+            if out.preempted or not self.scheduler.has_unfinished():
+                return []
+            # admission stalled with nothing running: pages held only by the prefix cache are
+            # invisible to the scheduler; reclaim the idle ones and retry once
+            # (clockwork/engine/llm_engine.py:102-113)
+            if self.prefix_cache is not None and self.prefix_cache.evict(self.cache.num_pages) > 0:
+                out = self.scheduler.schedule()
+            if not out.portions:
+                raise RuntimeError("waiting request cannot be admitted even with an empty prefix cache")
+        entries = []
+        sampled_seqs = []
+        for p in out.portions:
+            tokens = p.seq.tokens_between(p.start, p.start + p.num_tokens)
+            entries.append(StepEntry(p.seq.seq_id, tokens, [p.num_tokens - 1] if p.samples else []))
+            if p.samples:
+                sampled_seqs.append(p.seq)
+        logits = self.runner.step(entries)
+        tokens: list[int] = []
+        if sampled_seqs:
+            tokens = self.sampler.sample(
+                logits, [s.sampling_params for s in sampled_seqs], [len(s.output_token_ids) for s in sampled_seqs]
+            )
+        self.runner.check_status()
+        for p in out.portions:
+            p.seq.num_computed_tokens = p.start + p.num_tokens
+        for seq, token in zip(sampled_seqs, tokens):
+            seq.append_token(int(token))
+        if self.prefix_cache is not None and self.prefix_cache.enabled:
+            for seq in out.prefill_seqs:
+                # whole pages of the prompt that are computed by now
+                # (clockwork/engine/llm_engine.py:115-119 inserts after every prefill)
+                n = min(seq.num_computed_tokens, len(seq.prompt_token_ids))
+                req = self.cache.requests.get(seq.seq_id)
+                if req is not None and n >= self.cache.page_size:
+                    self.prefix_cache.insert(seq.prompt_token_ids[:n], req.tables[0])
+        outputs = [self._process(seq) for seq in sampled_seqs]
+        self.scheduler.free_finished()
+        for output in outputs:
+            if output.finished:
+                self._forget(output.request_id)
+        return outputs
+
+    def _process(self, seq: Sequence) -> RequestOutput:
+        params = seq.sampling_params
+        token = seq.output_token_ids[-1]
+        finish_reason = None
+        delta = ""
+        text = self._texts.get(seq.seq_id, "")
+        if (not params.ignore_eos and token in self._eos) or token in params.stop_token_ids:
+            finish_reason = "stop"  # the stopping token stays in token_ids, adds no text
+        elif self.tokenizer is not None:
+            candidate = self.tokenizer.decode(seq.output_token_ids)
+            if params.stop:
+                hits = [pos for pos in (candidate.find(s) for s in params.stop) if pos >= 0]
+                if hits:
+                    candidate = candidate[: min(hits)]
+                    finish_reason = "stop"
+            delta = candidate[len(text):] if candidate.startswith(text) else ""
+            text = candidate
+            self._texts[seq.seq_id] = text
+        if finish_reason is None and (
+            len(seq.output_token_ids) >= params.max_tokens or len(seq) >= self.cfg.model.max_model_len
+        ):
+            finish_reason = "length"
+        if finish_reason == "stop":
+            seq.status = SequenceStatus.FINISHED_STOPPED
+        elif finish_reason == "length":
+            seq.status = SequenceStatus.FINISHED_LENGTH
+        return RequestOutput(
+            request_id=seq.seq_id, prompt_token_ids=list(seq.prompt_token_ids), token_ids=list(seq.output_token_ids),
+            text=text, finished=seq.is_finished(), finish_reason=finish_reason,
+            num_cached_tokens=seq.num_cached_tokens, num_prompt_tokens=len(seq.prompt_token_ids),
+            num_generated_tokens=len(seq.output_token_ids), delta_text=delta,
+        )
+
+    # ---- whole requests -------------------------------------------------------------------------------
+    def generate(self, prompts: list[str] | list[list[int]],
+                 sampling_params: SamplingParams | list[SamplingParams] | None = None) -> list[RequestOutput]:
+        """Run prompts to completion; final outputs in prompt order
+        (clockwork/engine/llm_engine.py:135-159)."""
+        ids: list[str] = []
+        for i, prompt in enumerate(prompts):
+            rid = f"generate-{next(self._generate_counter)}"
+            ids.append(rid)
+            params = sampling_params[i] if isinstance(sampling_params, list) else sampling_params
+            if isinstance(prompt, str):
+                self.add_request(rid, prompt=prompt, sampling_params=params)
+            else:
+                self.add_request(rid, prompt_token_ids=prompt, sampling_params=params)
+        finals: dict[str, RequestOutput] = {}
+        pending = set(ids)
+        while pending:
+            outputs = self.step()
+            for output in outputs:
+                if output.finished and output.request_id in pending:
+                    finals[output.request_id] = output
+                    pending.discard(output.request_id)
+            if not outputs and not self.scheduler.has_unfinished():
+                raise RuntimeError(f"engine drained with unfinished requests: {sorted(pending)}")
+        return [finals[rid] for rid in ids]
+
+    def stats(self) -> dict:
+        sched = self.scheduler.stats
+        out = {
+            "num_waiting": sched.num_waiting,
+            "num_running": sched.num_running,
+            "num_preempted_total": sched.num_preempted_total,
+            "num_scheduled_batches": sched.num_scheduled_batches,
+            "total_prompt_tokens": sched.total_prompt_tokens,
+            "total_cached_tokens": sched.total_cached_tokens,
+            "num_free_blocks": min(self.cache.num_free_pages()) if self.cache.groups else 0,
+        }
+        if self.prefix_cache is not None:
+            cache = self.prefix_cache.stats
+            out.update(prefix_cache_queries=cache.queries, prefix_cache_hit_tokens=cache.hit_tokens,
+                       prefix_cache_prompt_tokens=cache.prompt_tokens, prefix_cache_hit_rate=cache.hit_rate)
+        return out

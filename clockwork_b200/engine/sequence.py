@@ -1,0 +1,84 @@
+"""Per-request state shared by the scheduler and the engine.
+
+Same fields and meanings as the reference's ``clockwork/engine/sequence.py:10-96``; the block
+table lives in the cache manager (``clockwork_b200/cache/manager.py``) instead of here.
+"""
+
+from __future__ import annotations
+
+import time
+from dataclasses import dataclass
+from enum import Enum
+
+from ..sampling.params import SamplingParams
+
+
+class SequenceStatus(Enum):
+    WAITING = "waiting"
+    RUNNING = "running"
+    PREEMPTED = "preempted"
+    FINISHED_STOPPED = "finished_stopped"
+    FINISHED_LENGTH = "finished_length"
+    FINISHED_ABORTED = "finished_aborted"
+
+
+_FINISHED = frozenset(
+    {SequenceStatus.FINISHED_STOPPED, SequenceStatus.FINISHED_LENGTH, SequenceStatus.FINISHED_ABORTED}
+)
+
+
+class Sequence:
+    """One request's tokens and its progress through the cache."""
+
+    def __init__(self, seq_id: str, prompt_token_ids: list[int], sampling_params: SamplingParams | None = None,
+                 arrival_time: float | None = None) -> None:
+        self.seq_id = seq_id
+        self.prompt_token_ids = list(prompt_token_ids)
+        self.output_token_ids: list[int] = []
+        self.sampling_params = sampling_params if sampling_params is not None else SamplingParams()
+        self.status = SequenceStatus.WAITING
+        self.num_computed_tokens = 0  # tokens whose keys/values are in the cache
+        self.num_cached_tokens = 0  # of those, how many came from the prefix cache at admission
+        self.arrival_time = time.monotonic() if arrival_time is None else arrival_time
+
+    def token_ids(self) -> list[int]:
+        return self.prompt_token_ids + self.output_token_ids
+
+    def __len__(self) -> int:
+        return len(self.prompt_token_ids) + len(self.output_token_ids)
+
+    def tokens_between(self, start: int, end: int) -> list[int]:
+        n_prompt = len(self.prompt_token_ids)
+        if end <= n_prompt:
+            return self.prompt_token_ids[start:end]
+        if start >= n_prompt:
+            return self.output_token_ids[start - n_prompt : end - n_prompt]
+        return self.prompt_token_ids[start:] + self.output_token_ids[: end - n_prompt]
+
+    def append_token(self, token_id: int) -> None:
+        self.output_token_ids.append(token_id)
+
+    def is_finished(self) -> bool:
+        return self.status in _FINISHED
+
+    def num_uncomputed_tokens(self) -> int:
+        return len(self) - self.num_computed_tokens
+
+    def reset_for_recompute(self) -> None:
+        """Preemption by recompute keeps the tokens and drops the cache progress
+        (``clockwork/engine/sequence.py:79-82``)."""
+        self.num_computed_tokens = 0
+
+
+@dataclass
+class RequestOutput:
+    request_id: str
+    prompt_token_ids: list[int]
+    token_ids: list[int]
+    text: str
+    finished: bool
+    finish_reason: str | None
+    num_cached_tokens: int
+    num_prompt_tokens: int
+    num_generated_tokens: int
+    delta_text: str = ""

@@ -36,32 +36,34 @@ def _pad4(n: int) -> int:
     return (n + 3) & ~3
 
 
-class ModelRunner:
-    """Owns nothing but the wiring: the model, the cache manager, and the staging buffers."""
+@dataclass
+class PreparedStep:
+    ctx: StepContext
+    token_ids: torch.Tensor  # int32 [N]
+    logit_rows: torch.Tensor | None  # int32 [R]
+    requests: list
+    ctx_lens: list[int]
 
-    def __init__(self, model: DecoderModel, cache: CacheManager) -> None:
-        if model.device.type != "cuda":
-            raise RuntimeError("the step function runs on a CUDA device only (there is no CPU path)")
-        ops.library()  # fail now, loudly, if the kernels cannot be built or loaded
-        self.model = model
+
+class StepBuilder:
+    """Turns entries into the device-side description of a step (one upload from pinned memory)."""
+
+    def __init__(self, cache: CacheManager, dtype: torch.dtype, device, status: torch.Tensor) -> None:
         self.cache = cache
-        self.device = model.device
-        self.status = cache.status if cache.status is not None else ops.new_status(self.device)
+        self.dtype = dtype
+        self.device = torch.device(device)
+        self.status = status
         self._pinned: torch.Tensor | None = None
         self._copy_done: torch.cuda.Event | None = None
-        self.launches = 0  # steps run (for accounting)
 
     def _staging(self, n_ints: int) -> torch.Tensor:
+        if self._copy_done is not None:
+            self._copy_done.synchronize()  # the last step's upload has left the staging buffer
         if self._pinned is None or self._pinned.numel() < n_ints:
             self._pinned = torch.empty(max(n_ints, 4096), dtype=torch.int32, pin_memory=True)
         return self._pinned
 
-    def step(self, entries: list[StepEntry]) -> torch.Tensor | None:
-        """Run the entries as one batch.  Returns float32 logits [wanted rows, vocab] in the order
-        of the entries and of each entry's ``want``, or None when nothing is wanted."""
-        entries = [e for e in entries if e.tokens]
-        if not entries:
-            return None
+    def prepare(self, entries: list[StepEntry]) -> PreparedStep:
         cache = self.cache
         reqs = []
         seen = set()
@@ -97,8 +99,6 @@ class ModelRunner:
             off += _pad4(N)
             seg[f"tables{g}"] = (off, S * max_blocks)
             off += _pad4(S * max_blocks)
-        if self._copy_done is not None:
-            self._copy_done.synchronize()  # the last step's upload has left the staging buffer
         host = self._staging(off)
         h = host.numpy()
 
@@ -106,16 +106,14 @@ class ModelRunner:
             o, size = seg[name]
             h[o : o + size] = values
 
-        tokens = np.fromiter((t for e in entries for t in e.tokens), dtype=np.int64, count=N)
-        put("tokens", tokens)
+        put("tokens", np.fromiter((t for e in entries for t in e.tokens), dtype=np.int64, count=N))
         put("positions", np.concatenate([np.arange(s, s + q, dtype=np.int32) for s, q in zip(starts, q_lens)]))
         put("tok_seq", np.repeat(np.arange(S, dtype=np.int32), q_lens))
         q_start = np.zeros(S + 1, dtype=np.int32)
         np.cumsum(q_lens, out=q_start[1:])
         put("q_start", q_start)
         put("ctx_lens", ctx_lens)
-        rows = [int(q_start[i]) + w for i, e in enumerate(entries) for w in e.want]
-        put("rows", rows)
+        put("rows", [int(q_start[i]) + w for i, e in enumerate(entries) for w in e.want])
         put("state", [r.state_slot if r.state_slot is not None else 0 for r in reqs])
         ps = cache.page_size
         for g in range(G):
@@ -143,7 +141,7 @@ class ModelRunner:
             return dev[o : o + size]
 
         ctx = StepContext(
-            dtype=self.model.dtype, device=self.device, status=self.status, num_tokens=N, num_seqs=S,
+            dtype=self.dtype, device=self.device, status=self.status, num_tokens=N, num_seqs=S,
             positions=view("positions"), tok_seq=view("tok_seq"), q_start=view("q_start"),
             ctx_lens=view("ctx_lens"), q_lens_host=q_lens, ctx_lens_host=ctx_lens,
             max_q_len=max(q_lens), max_ctx_len=max(ctx_lens),
@@ -154,11 +152,39 @@ class ModelRunner:
             [view(f"slots{g}") for g in range(G)],
             state_slots, [r.state_slot for r in reqs] if cache.state.needs else [],
         )
-        logits = self.model.forward(ctx, view("tokens"), view("rows") if R else None)
-        self.launches += 1
-        for r, end in zip(reqs, ctx_lens):
+        return PreparedStep(ctx, view("tokens"), view("rows") if R else None, reqs, ctx_lens)
+
+    def commit(self, prepared: PreparedStep) -> None:
+        """The step's tokens are in the cache now: advance the requests, let windows give pages back."""
+        for r, end in zip(prepared.requests, prepared.ctx_lens):
             r.num_computed = end
-            cache.release_behind_window(r, end)
+            self.cache.release_behind_window(r, end)
+
+
+class ModelRunner:
+    """The step function over a model and a cache manager."""
+
+    def __init__(self, model: DecoderModel, cache: CacheManager) -> None:
+        if model.device.type != "cuda":
+            raise RuntimeError("the step function runs on a CUDA device only (there is no CPU path)")
+        ops.library()  # fail now, loudly, if the kernels cannot be built or loaded
+        self.model = model
+        self.cache = cache
+        self.device = model.device
+        self.status = cache.status if cache.status is not None else ops.new_status(self.device)
+        self.builder = StepBuilder(cache, model.dtype, self.device, self.status)
+        self.steps_run = 0
+
+    def step(self, entries: list[StepEntry]) -> torch.Tensor | None:
+        """Run the entries as one batch.  Returns float32 logits [wanted rows, vocab] in the order
+        of the entries and of each entry's ``want``, or None when nothing is wanted."""
+        entries = [e for e in entries if e.tokens]
+        if not entries:
+            return None
+        prepared = self.builder.prepare(entries)
+        logits = self.model.forward(prepared.ctx, prepared.token_ids, prepared.logit_rows)
+        self.builder.commit(prepared)
+        self.steps_run += 1
         return logits
 
     def check_status(self) -> None:

@@ -89,43 +89,55 @@ def causal_attention(q, k, v, scale, window=None, q_offset=None):
     return torch.einsum("hqk,khd->qhd", probs, v)
 
 
-def attention_block(x, w, prefix, config, positions, window=None):
+def exact(x):
+    return x
+
+
+def to_bfloat16_and_back(x):
+    """Rounds activations the way a bfloat16 run stores them between kernels.  Passing this as
+    ``rnd`` makes the plain implementation show how much bfloat16 storage alone moves the logits of
+    a given model, which is the yardstick for the bfloat16 engine's tolerance in the tests."""
+    return x.to(torch.bfloat16).to(torch.float32)
+
+
+def attention_block(x, w, prefix, config, positions, window=None, rnd=exact):
     # clockwork/engine/model.py:79-128 with kv_cache=None
     nh, nkv, hd = config["num_attention_heads"], config["num_key_value_heads"], head_dim_of(config)
     t = x.shape[0]
-    q = (x @ w[f"{prefix}.q_proj.weight"].T + w[f"{prefix}.q_proj.bias"]).view(t, nh, hd)
-    k = (x @ w[f"{prefix}.k_proj.weight"].T + w[f"{prefix}.k_proj.bias"]).view(t, nkv, hd)
-    v = (x @ w[f"{prefix}.v_proj.weight"].T + w[f"{prefix}.v_proj.bias"]).view(t, nkv, hd)
+    q = rnd(x @ w[f"{prefix}.q_proj.weight"].T + w[f"{prefix}.q_proj.bias"]).view(t, nh, hd)
+    k = rnd(x @ w[f"{prefix}.k_proj.weight"].T + w[f"{prefix}.k_proj.bias"]).view(t, nkv, hd)
+    v = rnd(x @ w[f"{prefix}.v_proj.weight"].T + w[f"{prefix}.v_proj.bias"]).view(t, nkv, hd)
     cos, sin = rope_cos_sin(positions, hd, float(config["rope_theta"]), x.dtype)
-    q, k = apply_rope(q, cos, sin), apply_rope(k, cos, sin)
-    out = causal_attention(q, k, v, hd**-0.5, window=window)
+    q, k = rnd(apply_rope(q, cos, sin)), rnd(apply_rope(k, cos, sin))
+    out = rnd(causal_attention(q, k, v, hd**-0.5, window=window))
     return out.reshape(t, nh * hd) @ w[f"{prefix}.o_proj.weight"].T
 
 
-def swiglu_mlp(x, w, prefix):
+def swiglu_mlp(x, w, prefix, rnd=exact):
     # clockwork/engine/model.py:62-63
     gate = x @ w[f"{prefix}.gate_proj.weight"].T
     up = x @ w[f"{prefix}.up_proj.weight"].T
-    return (torch.nn.functional.silu(gate) * up) @ w[f"{prefix}.down_proj.weight"].T
+    return rnd(torch.nn.functional.silu(gate) * up) @ w[f"{prefix}.down_proj.weight"].T
 
 
-def decoder_layer(h, w, i, config, positions):
+def decoder_layer(h, w, i, config, positions, rnd=exact):
     # clockwork/engine/model.py:147-154
     p = f"model.layers.{i}"
     eps = config["rms_norm_eps"]
-    h = h + attention_block(rms_norm(h, w[f"{p}.input_layernorm.weight"], eps), w, f"{p}.self_attn", config, positions)
-    h = h + swiglu_mlp(rms_norm(h, w[f"{p}.post_attention_layernorm.weight"], eps), w, f"{p}.mlp")
+    h = h + attention_block(rnd(rms_norm(h, w[f"{p}.input_layernorm.weight"], eps)), w, f"{p}.self_attn", config,
+                            positions, rnd=rnd)
+    h = h + swiglu_mlp(rnd(rms_norm(h, w[f"{p}.post_attention_layernorm.weight"], eps)), w, f"{p}.mlp", rnd=rnd)
     return h
 
 
-def all_position_logits(config, w, token_ids):
+def all_position_logits(config, w, token_ids, rnd=exact):
     """[T, vocab] logits of one whole sequence (clockwork/engine/model.py:193-204, 220-233)."""
     ids = torch.as_tensor(token_ids, dtype=torch.long)
     positions = torch.arange(ids.shape[0])
     h = w["model.embed_tokens.weight"][ids]
     for i in range(config["num_hidden_layers"]):
-        h = decoder_layer(h, w, i, config, positions)
-    h = rms_norm(h, w["model.norm.weight"], config["rms_norm_eps"])
+        h = decoder_layer(h, w, i, config, positions, rnd=rnd)
+    h = rnd(rms_norm(h, w["model.norm.weight"], config["rms_norm_eps"]))
     head = w["model.embed_tokens.weight"] if config.get("tie_word_embeddings", False) else w["lm_head.weight"]
     return h @ head.T
 

@@ -1,0 +1,245 @@
+"""Generation through the Python entry point and the command line against the plain
+implementation: single and concurrent requests, portions under a token budget, prefix-cache hits,
+preemption when pages run out, seeded sampling, finish rules, long decoding."""
+
+import json
+import subprocess
+import sys
+
+import pytest
+import torch
+
+from clockwork_b200 import EngineConfig
+from clockwork_b200.engine import LLMEngine, load_model
+from clockwork_b200.sampling import SamplingParams, uniform_for
+from tests.plain import qwen2_plain as plain
+from tests.tiny_configs import TINY, tokens_for
+from tests.trace_tools import ROOT
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def models(tiny_dirs):
+    cache = {}
+
+    def get(name, dtype):
+        if (name, dtype) not in cache:
+            cache[(name, dtype)] = load_model(tiny_dirs[name], dtype)
+        return cache[(name, dtype)]
+
+    return get
+
+
+@pytest.fixture(scope="module")
+def plain_models(tiny_dirs):
+    return {name: plain.read_model_dir(folder) for name, folder in tiny_dirs.items()}
+
+
+def engine(models, tiny_dirs, name, dtype="float32", **overrides):
+    page = TINY[name][2]
+    defaults = dict(dtype=dtype, block_size=page, num_blocks=128, max_model_len=256, max_num_seqs=8,
+                    max_num_batched_tokens=64)
+    defaults.update(overrides)
+    cfg = EngineConfig.defaults(str(tiny_dirs[name]), **defaults)
+    return LLMEngine(cfg, model=models(name, cfg.model.dtype))
+
+
+def assert_greedy(plain_model, prompt, tokens, exact):
+    """float32: the engine's tokens are the plain implementation's.  bfloat16: every token is, given
+    the engine's own history, within rounding of the plain implementation's best (a near-tie may
+    fall either way)."""
+    config, weights = plain_model
+    if exact:
+        assert tokens == plain.greedy_generate(config, weights, prompt, len(tokens))
+        return
+    logits = plain.all_position_logits(config, weights, prompt + tokens)
+    for i, token in enumerate(tokens):
+        row = logits[len(prompt) + i - 1]
+        assert float(row.max() - row[token]) < 5e-2, f"token {i}: {token} is {float(row.max() - row[token]):.3f} below the best"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", sorted(TINY))
+def test_greedy_generate(name, dtype, models, tiny_dirs, plain_models):
+    eng = engine(models, tiny_dirs, name, dtype)
+    prompts = [tokens_for(name, n, salt=n) for n in (5, 11, 17, 1)]
+    outs = eng.generate(prompts, SamplingParams(max_tokens=8, ignore_eos=True))
+    assert [o.prompt_token_ids for o in outs] == prompts
+    for prompt, out in zip(prompts, outs):
+        assert out.finished and out.finish_reason == "length" and out.num_generated_tokens == 8
+        assert_greedy(plain_models[name], prompt, out.token_ids, exact=dtype == "float32")
+    assert not eng.has_unfinished_requests() and eng.cache.requests == {}
+    eng.cache.check_invariants(eng.prefix_cache.references())
+
+
+def test_concurrent_requests_staggered_under_a_small_budget(models, tiny_dirs, plain_models):
+    """Eight requests admitted over several steps with a token budget of 32: each equals the prompt
+    run alone (after the reference's tests/test_llm_engine.py:94-131)."""
+    name = "A"
+    eng = engine(models, tiny_dirs, name, max_num_batched_tokens=32, enable_prefix_cache=False)
+    prompts = [tokens_for(name, n, salt=i) for i, n in enumerate((21, 6, 33, 9, 14, 40, 3, 27))]
+    params = SamplingParams(max_tokens=10, ignore_eos=True)
+    finals = {}
+    pending = list(enumerate(prompts))
+    steps = 0
+    while pending or eng.has_unfinished_requests():
+        for _ in range(2):
+            if pending:
+                i, p = pending.pop(0)
+                eng.add_request(f"req-{i}", prompt_token_ids=p, sampling_params=params)
+        for out in eng.step():
+            if out.finished:
+                finals[out.request_id] = out
+        steps += 1
+        assert steps < 200
+    config, weights = plain_models[name]
+    for i, p in enumerate(prompts):
+        assert finals[f"req-{i}"].token_ids == plain.greedy_generate(config, weights, p, 10)
+    assert eng.stats()["num_scheduled_batches"] == steps and eng.stats()["num_free_blocks"] == 128
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_prompt_portions_of_seven_tokens(dtype, models, tiny_dirs, plain_models):
+    name = "B"
+    eng = engine(models, tiny_dirs, name, dtype, prefill_chunk_size=7)
+    prompts = [tokens_for(name, n, salt=3 * n) for n in (1, 9, 23, 40)]
+    outs = eng.generate(prompts, SamplingParams(max_tokens=12, ignore_eos=True))
+    for prompt, out in zip(prompts, outs):
+        assert_greedy(plain_models[name], prompt, out.token_ids, exact=dtype == "float32")
+    assert eng.stats()["num_scheduled_batches"] == 6 + 11  # six portions of the longest prompt, then 11 decodes
+
+
+def test_prefix_cache_hits_and_shared_prefixes(models, tiny_dirs, plain_models):
+    """A second pass over the same prompts is served from the prefix cache with identical tokens and
+    exact cached-token accounting; three prompts sharing 16 tokens hit 16 each
+    (after tests/test_llm_engine.py:134-200)."""
+    name = "B"  # page size 8
+    eng = engine(models, tiny_dirs, name)
+    prompts = [tokens_for(name, n, salt=n) for n in (23, 40, 9)]
+    params = SamplingParams(max_tokens=6, ignore_eos=True)
+    first = eng.generate(prompts, params)
+    assert [o.num_cached_tokens for o in first] == [0, 0, 0]
+    second = eng.generate(prompts, params)
+    assert [o.token_ids for o in second] == [o.token_ids for o in first]
+    assert [o.num_cached_tokens for o in second] == [16, 32, 8]  # whole pages, never the whole prompt
+    shared = tokens_for(name, 16, salt=99)
+    family = [shared + tokens_for(name, n, salt=50 + n) for n in (5, 9, 13, 2)]
+    outs = eng.generate(family[:1], params) + eng.generate(family[1:], params)
+    assert [o.num_cached_tokens for o in outs] == [0, 16, 16, 16]
+    off = engine(models, tiny_dirs, name, enable_prefix_cache=False)
+    assert [o.token_ids for o in off.generate(family, params)] == [o.token_ids for o in outs]
+    config, weights = plain_models[name]
+    assert outs[2].token_ids == plain.greedy_generate(config, weights, family[2], 6)
+    stats = eng.stats()
+    assert stats["prefix_cache_hit_tokens"] == 16 + 32 + 8 + 48 and stats["total_cached_tokens"] == 104
+    eng.cache.check_invariants(eng.prefix_cache.references())
+
+
+def test_pages_run_out_preemption_keeps_outputs_exact(models, tiny_dirs, plain_models):
+    """Eight pages of four tokens, three sequences growing to 16 tokens: preemption by recompute
+    happens and the outputs stay exact (after tests/test_llm_engine.py:203-219)."""
+    name = "A"
+    eng = engine(models, tiny_dirs, name, num_blocks=8, watermark=0.0, enable_prefix_cache=False)
+    prompts = [tokens_for(name, 4, salt=i) for i in range(3)]
+    outs = eng.generate(prompts, SamplingParams(max_tokens=12, ignore_eos=True))
+    assert eng.stats()["num_preempted_total"] >= 1
+    config, weights = plain_models[name]
+    for prompt, out in zip(prompts, outs):
+        assert out.token_ids == plain.greedy_generate(config, weights, prompt, 12)
+    assert eng.stats()["num_free_blocks"] == 8
+
+
+def test_a_request_that_can_never_fit_is_an_error(models, tiny_dirs):
+    eng = engine(models, tiny_dirs, "A", num_blocks=4, watermark=0.0)
+    eng.add_request("big", prompt_token_ids=tokens_for("A", 30))
+    with pytest.raises(RuntimeError, match="cannot be admitted"):
+        eng.step()
+
+
+def test_seeded_sampling(models, tiny_dirs, plain_models):
+    """Temperature / top-k / top-p sampling is reproducible across engines, differs between seeds,
+    and equals the plain rule given the same uniform numbers (after tests/test_llm_engine.py:222-236)."""
+    name = "B"
+    prompts = [tokens_for(name, n, salt=n) for n in (9, 23, 2)]
+
+    def run(seed, **kw):
+        eng = engine(models, tiny_dirs, name, **kw)
+        params = SamplingParams(max_tokens=12, temperature=0.8, top_k=40, top_p=0.95, seed=seed, ignore_eos=True)
+        return [o.token_ids for o in eng.generate(prompts, params)]
+
+    a, b, c = run(1), run(1, max_num_batched_tokens=8, prefill_chunk_size=5), run(2)
+    assert a == b and a != c
+    config, weights = plain_models[name]
+    for prompt, tokens in zip(prompts, a):
+        logits = plain.all_position_logits(config, weights, prompt + tokens)
+        for i, token in enumerate(tokens):
+            want = plain.sample_with_uniform(logits[len(prompt) + i - 1], 0.8, 40, 0.95, uniform_for(1, i))
+            assert token == want
+    plain_temp = engine(models, tiny_dirs, name).generate(prompts[:1], SamplingParams(max_tokens=5, temperature=0.8, seed=7))
+    assert len(plain_temp[0].token_ids) == 5
+
+
+def test_finish_rules(models, tiny_dirs, plain_models):
+    """EOS, stop ids, ignore_eos, max_tokens, max_model_len (after tests/test_llm_engine.py:239-296)."""
+    name = "A"
+    config, weights = plain_models[name]
+    prompt = tokens_for(name, 7, salt=1)
+    free_run = plain.greedy_generate(config, weights, prompt, 10)
+    stop_at = free_run[4]
+    cut = free_run.index(stop_at) + 1
+    eng = engine(models, tiny_dirs, name)
+    out = eng.generate([prompt], SamplingParams(max_tokens=10, stop_token_ids=[stop_at]))[0]
+    assert out.finish_reason == "stop" and out.token_ids == free_run[:cut]  # the stopping token is kept
+    eng._eos = frozenset({stop_at})
+    out = eng.generate([prompt], SamplingParams(max_tokens=10))[0]
+    assert out.finish_reason == "stop" and out.token_ids == free_run[:cut]
+    out = eng.generate([prompt], SamplingParams(max_tokens=10, ignore_eos=True))[0]
+    assert out.finish_reason == "length" and out.token_ids == free_run
+    short = engine(models, tiny_dirs, name, max_model_len=12)
+    out = short.generate([prompt], SamplingParams(max_tokens=50, ignore_eos=True))[0]
+    assert out.finish_reason == "length" and len(prompt) + len(out.token_ids) == 12
+    with pytest.raises(ValueError, match="leaves no room"):
+        short.add_request("x", prompt_token_ids=list(range(12)))
+    with pytest.raises(ValueError, match="exactly one"):
+        eng.add_request("x")
+    with pytest.raises(ValueError, match="at least one token"):
+        eng.add_request("x", prompt_token_ids=[])
+    with pytest.raises(ValueError, match="outside the vocabulary"):
+        eng.add_request("x", prompt_token_ids=[1, 256])
+    eng.add_request("dup", prompt_token_ids=[1, 2])
+    with pytest.raises(ValueError, match="already active"):
+        eng.add_request("dup", prompt_token_ids=[1, 2])
+    eng.abort_request("dup")
+    assert not eng.has_unfinished_requests()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding_across_many_pages(dtype, models, tiny_dirs, plain_models):
+    name = "B"
+    eng = engine(models, tiny_dirs, name, dtype, max_model_len=512)
+    prompt = tokens_for(name, 9, salt=5)
+    out = eng.generate([prompt], SamplingParams(max_tokens=200, ignore_eos=True))[0]
+    assert out.num_generated_tokens == 200
+    assert_greedy(plain_models[name], prompt, out.token_ids, exact=dtype == "float32")
+
+
+def test_command_line(tiny_dirs, plain_models, tmp_path):
+    name = "A"
+    prompt = tokens_for(name, 6, salt=2)
+    profile = tmp_path / "profile.yaml"
+    profile.write_text(
+        f"model:\n  model: {tiny_dirs[name]}\n  dtype: float32\n  max_model_len: 128\n"
+        "cache:\n  block_size: 4\n  num_blocks: 64\nscheduler:\n  max_num_seqs: 4\n  max_num_batched_tokens: 16\n"
+    )
+    cmd = [sys.executable, "-m", "clockwork_b200", "generate", "--config", str(profile), "--set", "num_blocks=32",
+           "--prompt-ids", ",".join(map(str, prompt)), "--max-tokens", "5", "--ignore-eos", "--stats"]
+    proc = subprocess.run(cmd, capture_output=True, text=True, cwd=ROOT, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    record = json.loads(proc.stdout.strip().splitlines()[-1])
+    config, weights = plain_models[name]
+    assert record["token_ids"] == plain.greedy_generate(config, weights, prompt, 5)
+    # 32 pages by --set; the prompt's one whole page stays in the prefix cache
+    assert json.loads(proc.stderr.strip().splitlines()[-1])["num_free_blocks"] == 31
+    bad = subprocess.run(cmd[:6] + ["--set", "no_such=1"] + cmd[8:], capture_output=True, text=True, cwd=ROOT, timeout=600)
+    assert bad.returncode != 0 and "unknown config override" in bad.stderr

@@ -1,0 +1,298 @@
+"""Each CUDA kernel alone against a plain torch computation of the same operation, at sizes other
+than the engine's tiny models (widths and vocabularies that are no power of two, odd head counts
+and group sizes, head sizes in steps of 16), in float32 and bfloat16."""
+
+import math
+
+import pytest
+import torch
+
+from tests.plain import qwen2_plain as plain
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def tol(dtype, scale=1.0):
+    return dict(rtol=1e-5, atol=1e-5 * scale) if dtype == torch.float32 else dict(rtol=2e-2, atol=2e-2 * scale)
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from clockwork_b200 import ops
+
+    return ops
+
+
+@pytest.fixture()
+def status(ops):
+    return ops.new_status(DEV)
+
+
+def rand(*shape, dtype=torch.float32, scale=1.0, seed=0):
+    g = torch.Generator().manual_seed(seed + sum(shape))
+    return (torch.randn(*shape, generator=g) * scale).to(dtype)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_embed(ops, status, dtype):
+    table = rand(1000, 200, dtype=dtype)
+    ids = torch.tensor([0, 999, 5, 5, 731], dtype=torch.int32)
+    out = ops.embed(table.to(DEV), ids.to(DEV), status)
+    assert out.dtype == torch.float32
+    torch.testing.assert_close(out.cpu(), table.float()[ids.long()], rtol=0, atol=0)
+    ops.raise_on_status(status)
+    out = ops.embed(table.to(DEV), torch.tensor([3, 1000], dtype=torch.int32, device=DEV), status)
+    assert float(out[1].abs().max()) == 0.0
+    with pytest.raises(RuntimeError, match="token id outside the vocabulary"):
+        ops.raise_on_status(status)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("h", [7, 200, 1536, 3000])
+def test_add_rmsnorm(ops, status, dtype, h):
+    n, eps = 5, 1e-5
+    resid = rand(n, h, scale=3.0)
+    delta = rand(n, h, dtype=dtype, seed=1)
+    weight = (1 + 0.1 * rand(h, seed=2)).float()
+    r = resid.to(DEV).clone()
+    out = ops.add_rmsnorm(r, delta.to(DEV), weight.to(DEV), eps, dtype, status)
+    want_resid = resid + delta.float()
+    torch.testing.assert_close(r.cpu(), want_resid, rtol=0, atol=0)  # one float32 add per element
+    torch.testing.assert_close(out.float().cpu(), plain.rms_norm(want_resid, weight, eps), **tol(dtype, 3))
+    # without a delta the residual is left alone
+    r2 = resid.to(DEV).clone()
+    out2 = ops.add_rmsnorm(r2, None, weight.to(DEV), eps, dtype, status)
+    assert torch.equal(r2.cpu(), resid)
+    torch.testing.assert_close(out2.float().cpu(), plain.rms_norm(resid, weight, eps), **tol(dtype, 3))
+    # selected rows
+    rows = torch.tensor([4, 0, 4], dtype=torch.int32, device=DEV)
+    out3 = ops.rmsnorm_rows(r2, rows, weight.to(DEV), eps, dtype, status)
+    assert torch.equal(out3, out2[[4, 0, 4]])
+    ops.raise_on_status(status)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_gemm_ref_shapes_epilogues_and_row_independence(ops, dtype):
+    m, n, k = 37, 129, 200
+    a, w, bias = rand(m, k, dtype=dtype), rand(n, k, dtype=dtype, scale=0.1, seed=1), rand(n, seed=2)
+    want = a.float() @ w.float().T + bias
+    ad, wd, bd = a.to(DEV), w.to(DEV), bias.to(DEV)
+    out = ops.gemm_ref(ad, wd, bd)
+    assert out.dtype == dtype
+    torch.testing.assert_close(out.float().cpu(), want, **tol(dtype, 4))
+    # float32 output, and accumulation into a float32 matrix
+    out32 = ops.gemm_ref(ad, wd, bd, epilogue=ops.EPILOGUE_STORE_F32)
+    torch.testing.assert_close(out32.cpu(), want, rtol=1e-5, atol=5e-5)
+    base = rand(m, n, seed=3)
+    acc = base.to(DEV).clone()
+    ops.gemm_ref(ad, wd, bd, out=acc, epilogue=ops.EPILOGUE_ADD_F32)
+    torch.testing.assert_close(acc.cpu(), base + want, rtol=1e-5, atol=5e-5)
+    # a row's result does not depend on the rest of the batch (bitwise)
+    single = ops.gemm_ref(ad[11:12].contiguous(), wd, bd, epilogue=ops.EPILOGUE_STORE_F32)
+    assert torch.equal(single[0], out32[11])
+    # a column slice of a wider matrix as the left operand
+    wide = rand(m, k + 24, dtype=dtype, seed=4).to(DEV)
+    sliced = ops.gemm_ref(wide[:, 8 : 8 + k], wd, None, epilogue=ops.EPILOGUE_STORE_F32)
+    torch.testing.assert_close(sliced.cpu(), wide[:, 8 : 8 + k].float().cpu() @ w.float().T, rtol=1e-5, atol=5e-5)
+    with pytest.raises(ValueError, match="inner sizes differ"):
+        ops.gemm_ref(ad, wd[:, :-1].contiguous())
+
+
+def test_gemm_ref_is_true_float32(ops):
+    """Operands that need 13 mantissa bits, chosen so that every product and every partial sum is
+    exact in float32 (22 bits at most) whatever the order of summation: the result must equal the
+    float64 one bit for bit.  TF32 (10 bits) or bfloat16 (8 bits) operands could not give that."""
+    m, n, k = 8, 16, 256
+    g = torch.Generator().manual_seed(0)
+    a = 1 + torch.randint(0, 4096, (m, k), generator=g).float() / 4096
+    w = torch.randint(1, 3, (n, k), generator=g).float()
+    got = ops.gemm_ref(a.to(DEV), w.to(DEV)).double().cpu()
+    assert torch.equal(got, a.double() @ w.double().T)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_gemm_ref_swiglu_and_silu_mul(ops, dtype):
+    m, n, k = 9, 200, 96
+    a, wg, wu = rand(m, k, dtype=dtype), rand(n, k, dtype=dtype, scale=0.2, seed=1), rand(n, k, dtype=dtype, scale=0.2, seed=2)
+    g, u = a.float() @ wg.float().T, a.float() @ wu.float().T
+    want = torch.nn.functional.silu(g) * u
+    got = ops.gemm_ref_swiglu(a.to(DEV), wg.to(DEV), wu.to(DEV))
+    torch.testing.assert_close(got.float().cpu(), want, **tol(dtype, 2))
+    gu = torch.cat([g, u], dim=1).to(dtype)
+    got2 = ops.silu_mul(gu.to(DEV))
+    torch.testing.assert_close(got2.float().cpu(), torch.nn.functional.silu(gu[:, :n].float()) * gu[:, n:].float(), **tol(dtype, 2))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nh,nkv,hd,rot", [(5, 1, 48, 48), (4, 2, 64, 32), (3, 3, 16, 16)])
+def test_rope_store(ops, status, dtype, nh, nkv, hd, rot):
+    n, pages, ps, theta = 6, 5, 4, 1e6
+    qkv = rand(n, (nh + 2 * nkv) * hd, dtype=dtype)
+    positions = torch.tensor([0, 1, 4000, 17, 2, 3], dtype=torch.int32)
+    slots = torch.tensor([19, 0, 7, -1, 12, 3], dtype=torch.int32)  # -1: not stored
+    inv_freq = 1.0 / (theta ** (torch.arange(0, rot, 2, dtype=torch.float32) / rot))
+    k_cache = torch.full((pages, ps, nkv, hd), 100.0, dtype=dtype, device=DEV)
+    v_cache = torch.full((pages, ps, nkv, hd), 100.0, dtype=dtype, device=DEV)
+    x = qkv.to(DEV).clone()
+    ops.rope_store(x, positions.to(DEV), slots.to(DEV), inv_freq.to(DEV), k_cache, v_cache, nh, nkv, hd, rot, status)
+    ops.raise_on_status(status)
+    q = qkv.float()[:, : nh * hd].view(n, nh, hd)
+    k = qkv.float()[:, nh * hd : (nh + nkv) * hd].view(n, nkv, hd)
+    v = qkv.float()[:, (nh + nkv) * hd :].view(n, nkv, hd)
+    cos, sin = plain.rope_cos_sin(positions, rot, theta, torch.float32)
+
+    def rotate(t):
+        out = t.clone()
+        out[..., :rot] = plain.apply_rope(t[..., :rot], cos, sin)
+        return out
+
+    t = tol(dtype, 3)
+    got = x.float().cpu()
+    torch.testing.assert_close(got[:, : nh * hd].view(n, nh, hd), rotate(q), **t)
+    flat_k, flat_v = k_cache.float().cpu().view(-1, nkv, hd), v_cache.float().cpu().view(-1, nkv, hd)
+    stored = slots >= 0
+    torch.testing.assert_close(flat_k[slots[stored].long()], rotate(k)[stored], **t)
+    torch.testing.assert_close(flat_v[slots[stored].long()], v[stored].to(dtype).float(), rtol=0, atol=0)
+    untouched = torch.ones(pages * ps, dtype=torch.bool)
+    untouched[slots[stored].long()] = False
+    assert bool((flat_k[untouched] == 100.0).all()) and bool((flat_v[untouched] == 100.0).all())
+    # a slot outside the pool is reported, not written
+    bad = torch.tensor([pages * ps] + [0] * (n - 1), dtype=torch.int32, device=DEV)
+    ops.rope_store(qkv.to(DEV), positions.to(DEV), bad, inv_freq.to(DEV), k_cache, v_cache, nh, nkv, hd, rot, status)
+    with pytest.raises(RuntimeError, match="cache slot outside the pool"):
+        ops.raise_on_status(status)
+
+
+def paged_setup(seq_lens, nkv, hd, ps, dtype, seed=0, extra_pages=3):
+    """Random K/V for several requests scattered over shuffled pages; padding filled with 100.0
+    (the reference's poison trick, tests/test_triton_kernel.py:33-34)."""
+    g = torch.Generator().manual_seed(seed)
+    blocks = [(n + ps - 1) // ps for n in seq_lens]
+    total = sum(blocks) + extra_pages
+    order = torch.randperm(total, generator=g).tolist()
+    k_cache = torch.full((total, ps, nkv, hd), 100.0)
+    v_cache = torch.full((total, ps, nkv, hd), 100.0)
+    tables = torch.full((len(seq_lens), max(blocks) + 1), -1, dtype=torch.int32)
+    ks, vs = [], []
+    for s, n in enumerate(seq_lens):
+        k, v = torch.randn(n, nkv, hd, generator=g), torch.randn(n, nkv, hd, generator=g)
+        k, v = k.to(dtype).float(), v.to(dtype).float()
+        ks.append(k)
+        vs.append(v)
+        for b in range(blocks[s]):
+            page = order.pop()
+            tables[s, b] = page
+            chunk = slice(b * ps, min((b + 1) * ps, n))
+            k_cache[page, : chunk.stop - chunk.start] = k[chunk]
+            v_cache[page, : chunk.stop - chunk.start] = v[chunk]
+    return k_cache.to(dtype), v_cache.to(dtype), tables, ks, vs
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nh,nkv,hd,ps,window", [(6, 2, 128, 16, None), (5, 5, 48, 8, None), (8, 1, 16, 4, 37), (3, 1, 256, 16, None)])
+def test_attention_ref_mixed_batch(ops, status, dtype, nh, nkv, hd, ps, window):
+    # three requests: a prompt portion in the middle of a context, a single decoded token, a whole prompt
+    ctx_lens, q_lens = [150, 333, 41], [23, 1, 41]
+    k_cache, v_cache, tables, ks, vs = paged_setup(ctx_lens, nkv, hd, ps, dtype)
+    scale = hd**-0.5
+    g = torch.Generator().manual_seed(5)
+    qs = [torch.randn(q, nh, hd, generator=g).to(dtype).float() * 2 for q in q_lens]
+    n = sum(q_lens)
+    q_flat = torch.cat(qs).view(n, nh * hd)
+    wide = torch.zeros(n, (nh + 2 * nkv) * hd)  # queries live inside a [q|k|v] row
+    wide[:, : nh * hd] = q_flat
+    tok_seq = torch.cat([torch.full((q,), s, dtype=torch.int32) for s, q in enumerate(q_lens)])
+    positions = torch.cat([torch.arange(c - q, c, dtype=torch.int32) for c, q in zip(ctx_lens, q_lens)])
+    out = ops.attention_ref(wide.to(dtype).to(DEV), k_cache.to(DEV), v_cache.to(DEV), tables.to(DEV), tok_seq.to(DEV),
+                            positions.to(DEV), nh, nkv, hd, scale, window, status)
+    ops.raise_on_status(status)
+    want = torch.cat([plain.causal_attention(q, k, v, scale, window=window) for q, k, v in zip(qs, ks, vs)])
+    torch.testing.assert_close(out.float().cpu().view(n, nh, hd), want, **tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_attention_ref_finds_one_far_key_and_the_windows_edge(ops, status, dtype):
+    """One key among hundreds gets a score that stands out; the output must be that key's value.
+    Then a window that ends exactly one short of it: the output must not contain it."""
+    nh, nkv, hd, ps, ctx = 2, 1, 32, 16, 700
+    k_cache, v_cache, tables, ks, vs = paged_setup([ctx], nkv, hd, ps, dtype, seed=3)
+    far = 37  # in the third page
+    q = torch.zeros(1, nh, hd)
+    q[0, :, 0] = 30.0
+    kc = k_cache.float()
+    page, off = int(tables[0, far // ps]), far % ps
+    kc[page, off, 0, :] = 0.0
+    kc[page, off, 0, 0] = 30.0  # score 900 * scale, everything else ~ N(0, 30^2) * scale
+    ks[0][far] = kc[page, off]
+    wide = torch.zeros(1, (nh + 2) * hd)
+    wide[0, : nh * hd] = q.view(-1)
+    args = (kc.to(dtype).to(DEV), v_cache.to(DEV), tables.to(DEV), torch.zeros(1, dtype=torch.int32, device=DEV),
+            torch.tensor([ctx - 1], dtype=torch.int32, device=DEV), nh, nkv, hd, hd**-0.5)
+    out = ops.attention_ref(wide.to(dtype).to(DEV), *args, None, status)
+    torch.testing.assert_close(out.float().cpu().view(nh, hd)[0], vs[0][far, 0], **tol(dtype))
+    for window, sees in ((ctx - far, True), (ctx - far - 1, False)):
+        out = ops.attention_ref(wide.to(dtype).to(DEV), *args, window, status)
+        want = plain.causal_attention(q, ks[0], vs[0], hd**-0.5, window=window)
+        torch.testing.assert_close(out.float().cpu().view(1, nh, hd), want, **tol(dtype))
+        close = torch.allclose(out.float().cpu().view(nh, hd)[0], vs[0][far, 0], atol=0.05)
+        assert close == sees
+    ops.raise_on_status(status)
+
+
+def test_attention_ref_reports_pages_outside_the_pool(ops, status):
+    k_cache, v_cache, tables, _, _ = paged_setup([20], 1, 16, 4, torch.float32)
+    tables[0, 2] = 999
+    q = torch.zeros(1, 3 * 16, device=DEV)
+    ops.attention_ref(q, k_cache.to(DEV), v_cache.to(DEV), tables.to(DEV), torch.zeros(1, dtype=torch.int32, device=DEV),
+                      torch.tensor([19], dtype=torch.int32, device=DEV), 1, 1, 16, 0.25, None, status)
+    with pytest.raises(RuntimeError, match="page id outside the pool"):
+        ops.raise_on_status(status)
+
+
+def test_copy_pages(ops, status):
+    cache = torch.randn(6, 9, 4, 2, 16, device=DEV)  # [planes, pages, page_size, kv_heads, head_dim]
+    before = cache.clone()
+    pairs = torch.tensor([[2, 7], [0, 5]], dtype=torch.int32, device=DEV)
+    ops.copy_pages(cache, pairs, status)
+    assert torch.equal(cache[:, 7], before[:, 2]) and torch.equal(cache[:, 5], before[:, 0])
+    keep = [0, 1, 2, 3, 4, 6, 8]
+    assert torch.equal(cache[:, keep], before[:, keep])
+    ops.raise_on_status(status)
+
+
+def test_argmax_first_maximum_and_odd_vocabulary(ops):
+    logits = rand(7, 1003)
+    logits[2, 500] = logits[2, 17] = 50.0  # a tie: the first index wins (model_runner.py:136-137)
+    logits[5] = -1e30
+    got = ops.argmax(logits.to(DEV)).cpu()
+    want = logits.argmax(dim=-1)
+    want[2] = 17
+    want[5] = 0
+    assert got.tolist() == want.tolist()
+
+
+@pytest.mark.parametrize("temperature,top_k,top_p", [(0.8, -1, 1.0), (1.3, 5, 1.0), (0.7, -1, 0.6), (1.0, 40, 0.9), (0.0, 3, 0.5)])
+def test_sample_matches_the_plain_rule(ops, temperature, top_k, top_p):
+    r, v = 24, 1003
+    logits = rand(r, v, scale=2.0, seed=4)
+    u = (torch.arange(r, dtype=torch.float32) + 0.37) / r
+    dev = lambda t: t.to(DEV)
+    got = ops.sample(dev(logits), dev(torch.full((r,), temperature)), dev(torch.full((r,), max(top_k, 0), dtype=torch.int32)),
+                     dev(torch.full((r,), top_p)), dev(u)).cpu().tolist()
+    want = [plain.sample_with_uniform(logits[i], temperature, top_k, top_p, float(u[i])) for i in range(r)]
+    assert got == want
+
+
+def test_sample_rows_carry_their_own_parameters(ops):
+    r, v = 6, 320
+    logits = rand(r, v, scale=3.0, seed=9)
+    temps = torch.tensor([0.0, 0.5, 1.0, 0.0, 2.0, 0.9])
+    ks = torch.tensor([0, 0, 7, 0, 0, 2], dtype=torch.int32)
+    ps = torch.tensor([1.0, 0.8, 1.0, 1.0, 0.3, 1.0])
+    u = torch.tensor([0.5, 0.1, 0.99, 0.2, 0.6, 0.45])
+    got = ops.sample(logits.to(DEV), temps.to(DEV), ks.to(DEV), ps.to(DEV), u.to(DEV)).cpu().tolist()
+    want = [plain.sample_with_uniform(logits[i], float(temps[i]), int(ks[i]) or -1, float(ps[i]), float(u[i])) for i in range(r)]
+    assert got == want
