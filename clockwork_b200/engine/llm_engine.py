@@ -234,6 +234,15 @@ class LLMEngine:
                 raise RuntimeError(f"engine drained with unfinished requests: {sorted(pending)}")
         return [finals[rid] for rid in ids]
 
+    def decode_step_device(self, request_ids: list[str], tokens: list[list[int]]) -> torch.Tensor:
+        """One step for requests that are already in the cache, with the given next tokens, sampled
+        greedily on the device and not read back: the step function and sampler without the
+        scheduler's bookkeeping (used to time the device work alone)."""
+        from .. import ops
+
+        entries = [StepEntry(rid, toks, [len(toks) - 1]) for rid, toks in zip(request_ids, tokens)]
+        return ops.argmax(self.runner.step(entries))
+
     def stats(self) -> dict:
         sched = self.scheduler.stats
         out = {

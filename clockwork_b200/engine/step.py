@@ -55,6 +55,7 @@ class StepBuilder:
         self.status = status
         self._pinned: torch.Tensor | None = None
         self._copy_done: torch.cuda.Event | None = None
+        self.last_upload_bytes = 0
 
     def _staging(self, n_ints: int) -> torch.Tensor:
         if self._copy_done is not None:
@@ -132,6 +133,7 @@ class StepBuilder:
 
         dev = torch.empty(off, dtype=torch.int32, device=self.device)
         dev.copy_(host[:off], non_blocking=True)
+        self.last_upload_bytes = off * 4
         if self._copy_done is None:
             self._copy_done = torch.cuda.Event()
         self._copy_done.record()

@@ -71,7 +71,17 @@ def library() -> ctypes.CDLL:
 ERROR_NAMES = {-1: "refused size", -2: "unknown dtype code", -3: "unsupported combination", -4: "set-up failed"}
 
 
+_launches = 0
+
+
+def launch_count() -> int:
+    """Kernel launches made through this library so far (each entry point launches one kernel)."""
+    return _launches
+
+
 def check(code: int, what: str) -> None:
+    global _launches
+    _launches += 1
     if code == 0:
         return
     if code < 0:
