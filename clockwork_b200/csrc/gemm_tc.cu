@@ -1,0 +1,457 @@
+// bfloat16 matrix products on the 5th-generation tensor cores (tcgen05), operands staged by TMA,
+// accumulators in tensor memory.
+//
+//   C[T, N] = X[T, K] * W[N, K]^T (+ bias[N])       W in nn.Linear layout, X the activations
+//   (reference: clockwork/engine/model.py:58-60, 74-77, 88-90, 128, 216; SwiGLU :62-63)
+//
+// The weights ride the MMA's M dimension: one CTA owns 128 rows of W (128 output features) and a
+// tile of BN tokens, so the instruction is M=128 x N=BN x K=16 with both operands K-major in
+// shared memory (128-byte swizzle) and D[feature, token] in TMEM.  This one shape serves decode
+// (BN = 16..64 tokens, the step is a stream of weight tiles from HBM) and prefill (BN = 128/256).
+// When the grid would leave SMs idle the K dimension is split over blockIdx.z; partial tiles go
+// through a float32 workspace and the CTA that finishes last adds them in split order and runs
+// the epilogue, so the result does not depend on which CTA came last.
+//
+// Warp roles (128 threads): warp 0 lane 0 issues TMA loads, warp 1 lane 0 issues the MMAs, warp 2
+// allocates and frees TMEM; all four warps run the epilogue (warp w reads TMEM lanes 32w..32w+31).
+// Epilogues: 0 store bf16; 1 add into the float32 residual; 2 store float32; SWIGLU computes
+// silu(X Wg^T) * (X Wu^T) from two accumulators.
+//
+// Every wait on an mbarrier is bounded: when it runs out the kernel records CW_ST_WAIT_TIMEOUT in
+// the status words, the producer waits (bounded again) for the copies it has in flight, TMEM is
+// freed and the kernel returns.
+#include "common.cuh"
+#include <cuda.h>
+
+#define BM 128
+#define BK 64
+#define THREADS 128
+#define WAIT_CYCLES 4000000000LL
+
+// ---------------------------------------------------------------------------------------------
+// PTX wrappers
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok;
+}
+// Bounded wait.  Returns false when the wait ran out or another thread gave up.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* give_up) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    while (!mbar_try_wait(bar, parity)) {
+        if (*give_up) return false;
+        if (clock64() - t0 > WAIT_CYCLES) {
+            *give_up = 1;
+            return false;
+        }
+    }
+    return true;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y,
+                                            uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t result_slot, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(result_slot),
+                 "r"(cols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols)
+                 : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() {
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after() {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc,
+                                          uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* v) {
+    uint32_t r[16];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr)
+        : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes (64 bf16) with the
+// 128-byte swizzle: 8-row groups are 1024 bytes apart (stride byte offset), the leading byte offset
+// is not used by swizzled K-major layouts (encoded 1), version 1, layout type 2 (SWIZZLE_128B).
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((addr >> 4) & 0x3FFF);
+    d |= (uint64_t)1 << 16;
+    d |= (uint64_t)(1024 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+// Instruction descriptor: D float32 (1 at bit 4), A and B bfloat16 (1 at bits 7 and 10), both
+// K-major, N >> 3 at bit 17, M >> 4 at bit 24.
+__host__ __device__ constexpr uint32_t instr_desc(int m, int n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+struct GemmParams {
+    int T, N, K;          // tokens, output features, inner size
+    int ldc;              // row stride of C in elements
+    int epilogue;         // 0 bf16 store, 1 float32 add, 2 float32 store (ignored for SWIGLU)
+    int num_kb;           // ceil(K / 64)
+    int kb_per_split;     // k-blocks per blockIdx.z
+    int splits;
+    const float* bias;    // [N] or null
+    void* C;
+    float* workspace;     // [tiles][splits][columns][128] float32 partial tiles (splits > 1)
+    int* counters;        // [tiles] arrival counters, zero between launches
+    int* status;
+};
+
+template <int BN, bool SWIGLU>
+struct Cfg {
+    static constexpr int A_BYTES = BM * BK * 2;                     // 16 KB
+    static constexpr int B_BYTES = BN * BK * 2;
+    static constexpr int STAGE_BYTES = A_BYTES * (SWIGLU ? 2 : 1) + B_BYTES;
+    // small token tiles (decode): few stages, so that two CTAs share an SM and one CTA's set-up
+    // and epilogue hide behind the other's stream of weight tiles
+    static constexpr int MAX_STAGES = (200 * 1024) / STAGE_BYTES;
+    static constexpr int WANT_STAGES = BN <= 32 ? 5 : (BN <= 64 ? 4 : 8);
+    static constexpr int STAGES = MAX_STAGES > WANT_STAGES ? WANT_STAGES : MAX_STAGES;
+    static constexpr int ACC_COLS = BN * (SWIGLU ? 2 : 1);
+    static constexpr int TMEM_COLS = ACC_COLS <= 32 ? 32 : (ACC_COLS <= 64 ? 64 : (ACC_COLS <= 128 ? 128 : (ACC_COLS <= 256 ? 256 : 512)));
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment*/ + 256 /*barriers*/;
+};
+
+template <int BN, bool SWIGLU>
+__global__ void __launch_bounds__(THREADS)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_w2,
+               const __grid_constant__ CUtensorMap map_x, const GemmParams p) {
+    using C = Cfg<BN, SWIGLU>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint64_t* bars = (uint64_t*)(smem + C::STAGES * C::STAGE_BYTES);
+    // bars[0..S): full, bars[S..2S): empty, bars[2S]: accumulator ready
+    uint32_t* tmem_slot = (uint32_t*)(bars + 2 * C::STAGES + 1);
+    volatile int* give_up = (volatile int*)(tmem_slot + 1);
+    int* last_flag = (int*)(tmem_slot + 2);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int m0 = blockIdx.x * BM, n0 = blockIdx.y * BN, split = blockIdx.z;
+    const int kb0 = split * p.kb_per_split;
+    const int kb1 = min(p.num_kb, kb0 + p.kb_per_split);
+    const int my_kb = kb1 - kb0;
+    const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + C::STAGES);
+    const uint32_t acc_bar = smem_u32(bars + 2 * C::STAGES);
+
+    if (tid == 0) {
+        for (int s = 0; s < C::STAGES; ++s) {
+            mbar_init(full0 + 8 * s, 1);
+            mbar_init(empty0 + 8 * s, 1);
+        }
+        mbar_init(acc_bar, 1);
+        *give_up = 0;
+        *last_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 2) tmem_alloc(smem_u32(tmem_slot), C::TMEM_COLS);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    int issued = 0;
+    if (warp == 0 && lane == 0) {
+        // ---- TMA producer ----------------------------------------------------------------------
+        for (int i = 0; i < my_kb; ++i) {
+            const int s = i % C::STAGES;
+            const uint32_t parity = ((i / C::STAGES) & 1) ^ 1;
+            if (!mbar_wait(empty0 + 8 * s, parity, give_up)) break;
+            const uint32_t a_dst = smem_u32(smem + s * C::STAGE_BYTES);
+            const uint32_t bar = full0 + 8 * s;
+            mbar_expect_tx(bar, C::STAGE_BYTES);
+            const int kx = (kb0 + i) * BK;
+            tma_load_2d(a_dst, &map_w, kx, m0, bar);
+            if (SWIGLU) tma_load_2d(a_dst + C::A_BYTES, &map_w2, kx, m0, bar);
+            tma_load_2d(a_dst + C::A_BYTES * (SWIGLU ? 2 : 1), &map_x, kx, n0, bar);
+            ++issued;
+        }
+    } else if (warp == 1 && lane == 0) {
+        // ---- MMA issuer ------------------------------------------------------------------------
+        constexpr uint32_t idesc = instr_desc(BM, BN);
+        bool ok = true;
+        for (int i = 0; i < my_kb && ok; ++i) {
+            const int s = i % C::STAGES;
+            ok = mbar_wait(full0 + 8 * s, (i / C::STAGES) & 1, give_up);
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t a_addr = smem_u32(smem + s * C::STAGE_BYTES);
+            const uint64_t adesc = smem_desc_sw128(a_addr);
+            const uint64_t a2desc = smem_desc_sw128(a_addr + C::A_BYTES);
+            const uint64_t bdesc = smem_desc_sw128(a_addr + C::A_BYTES * (SWIGLU ? 2 : 1));
+#pragma unroll
+            for (int k = 0; k < BK / 16; ++k) {
+                // 16 bf16 = 32 bytes further along K inside the swizzle atom: +2 in 16-byte units
+                const uint32_t acc = (i > 0 || k > 0) ? 1u : 0u;
+                umma_bf16(tmem_base, adesc + 2 * k, bdesc + 2 * k, idesc, acc);
+                if (SWIGLU) umma_bf16(tmem_base + BN, a2desc + 2 * k, bdesc + 2 * k, idesc, acc);
+            }
+            umma_commit(empty0 + 8 * s);  // frees the stage when these MMAs have read it
+        }
+        if (ok) umma_commit(acc_bar);
+    }
+    __syncwarp();
+    // ---- epilogue: every thread owns one output feature (TMEM lane) -----------------------------
+    const bool acc_ready = mbar_wait(acc_bar, 0, give_up);
+    tc_fence_after();
+    __syncwarp();
+    const int row = warp * 32 + lane;  // feature within the tile
+    const int f = m0 + row;
+    const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16);
+    const int tile = blockIdx.y * gridDim.x + blockIdx.x;
+    bool run_epilogue = acc_ready;
+    if (acc_ready && p.splits > 1) {
+        float* ws = p.workspace + ((size_t)tile * p.splits + split) * C::ACC_COLS * BM;
+        for (int c = 0; c < C::ACC_COLS; c += 16) {
+            float v[16];
+            tmem_ld16(taddr + c, v);
+#pragma unroll
+            for (int j = 0; j < 16; ++j) ws[(size_t)(c + j) * BM + row] = v[j];
+        }
+        __threadfence();
+        __syncthreads();
+        if (tid == 0) {
+            const int prev = atomicAdd(&p.counters[tile], 1);
+            if (prev == p.splits - 1) {
+                p.counters[tile] = 0;  // ready for the next launch
+                *last_flag = 1;
+            }
+        }
+        __syncthreads();
+        run_epilogue = *last_flag != 0;
+        if (run_epilogue) __threadfence();
+    }
+    if (run_epilogue) {
+        const float bias = (p.bias != nullptr && f < p.N) ? p.bias[f] : 0.f;
+        const float* ws = p.workspace + (size_t)tile * p.splits * C::ACC_COLS * BM;
+        for (int c = 0; c < BN; c += 16) {
+            float g[16], u[16];
+            if (p.splits == 1) {
+                tmem_ld16(taddr + c, g);
+                if (SWIGLU) tmem_ld16(taddr + BN + c, u);
+            } else {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    float sg = 0.f, su = 0.f;
+                    for (int s = 0; s < p.splits; ++s) {
+                        const float* part = ws + (size_t)s * C::ACC_COLS * BM;
+                        sg += part[(size_t)(c + j) * BM + row];
+                        if (SWIGLU) su += part[(size_t)(BN + c + j) * BM + row];
+                    }
+                    g[j] = sg;
+                    u[j] = su;
+                }
+            }
+            if (f < p.N) {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    const int t = n0 + c + j;
+                    if (t >= p.T) break;
+                    const size_t idx = (size_t)t * p.ldc + f;
+                    const float v = g[j] + bias;
+                    if (SWIGLU) {
+                        ((bf16*)p.C)[idx] = __float2bfloat16_rn(v / (1.0f + expf(-v)) * u[j]);
+                    } else if (p.epilogue == 0) {
+                        ((bf16*)p.C)[idx] = __float2bfloat16_rn(v);
+                    } else if (p.epilogue == 1) {
+                        ((float*)p.C)[idx] += v;
+                    } else {
+                        ((float*)p.C)[idx] = v;
+                    }
+                }
+            }
+        }
+    }
+    // ---- teardown ---------------------------------------------------------------------------------
+    if (*give_up) {
+        if (tid == 0) cw_report(p.status, CW_ST_WAIT_TIMEOUT, blockIdx.x, blockIdx.z);
+        if (warp == 0 && lane == 0) {
+            // wait, bounded, for the copies still in flight before the CTA's shared memory goes away
+            for (int i = max(0, issued - C::STAGES); i < issued; ++i) {
+                const uint32_t bar = full0 + 8 * (i % C::STAGES);
+                const long long t0 = clock64();
+                while (!mbar_try_wait(bar, (i / C::STAGES) & 1) && clock64() - t0 < WAIT_CYCLES) {
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 2) tmem_dealloc(tmem_base, C::TMEM_COLS);
+}
+
+// ---------------------------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+static EncodeTiledFn g_encode = nullptr;
+
+static int load_encode() {
+    if (g_encode) return 0;
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess || fn == nullptr)
+        return -1;
+    g_encode = (EncodeTiledFn)fn;
+    return 0;
+}
+
+// A [rows, K] bf16 matrix with row stride `ld` elements, read in boxes of `box_rows` x 64.
+static int make_map(CUtensorMap* map, const void* ptr, int rows, int K, long long ld, int box_rows) {
+    const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    const cuuint32_t box[2] = {BK, (cuuint32_t)box_rows};
+    const cuuint32_t elem[2] = {1, 1};
+    const CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides,
+                                box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : -1;
+}
+
+struct Plan {
+    int bn, splits, kb_per_split, tiles, acc_cols;
+};
+
+static Plan make_plan(int T, int N, int K, bool swiglu, int sm_count) {
+    Plan pl;
+    const int cap = swiglu ? 128 : 256;
+    pl.bn = T <= 16 ? 16 : (T <= 32 ? 32 : (T <= 64 ? 64 : (T <= 128 ? 128 : cap)));
+    pl.acc_cols = pl.bn * (swiglu ? 2 : 1);
+    pl.tiles = ((N + BM - 1) / BM) * ((T + pl.bn - 1) / pl.bn);
+    const int num_kb = (K + BK - 1) / BK;
+    int splits = 1;
+    if (pl.tiles < sm_count) {
+        // enough CTAs to give every SM work, each with at least four k-blocks to stream
+        splits = (2 * sm_count + pl.tiles - 1) / pl.tiles;
+        const int max_by_k = num_kb / 4 > 0 ? num_kb / 4 : 1;
+        if (splits > max_by_k) splits = max_by_k;
+        if (splits > 16) splits = 16;
+        if (splits < 1) splits = 1;
+    }
+    pl.kb_per_split = (num_kb + splits - 1) / splits;
+    pl.splits = (num_kb + pl.kb_per_split - 1) / pl.kb_per_split;  // no empty split
+    return pl;
+}
+
+template <int BN, bool SWIGLU>
+static int launch(const CUtensorMap& mw, const CUtensorMap& mw2, const CUtensorMap& mx, const GemmParams& p,
+                  dim3 grid, cudaStream_t stream) {
+    using C = Cfg<BN, SWIGLU>;
+    static bool configured = false;
+    if (!configured) {
+        if (cudaFuncSetAttribute(gemm_tc_kernel<BN, SWIGLU>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 C::SMEM_BYTES) != cudaSuccess)
+            return (int)cudaGetLastError();
+        configured = true;
+    }
+    gemm_tc_kernel<BN, SWIGLU><<<grid, THREADS, C::SMEM_BYTES, stream>>>(mw, mw2, mx, p);
+    return CW_LAUNCH_CHECK();
+}
+
+// Bytes of workspace and number of counters a call may need (0 when it will not split).
+extern "C" int cw_gemm_tc_workspace(int T, int N, int K, int swiglu, int sm_count, long long* bytes,
+                                    int* counters) {
+    const Plan pl = make_plan(T, N, K, swiglu != 0, sm_count);
+    *bytes = pl.splits > 1 ? (long long)pl.tiles * pl.splits * pl.acc_cols * BM * 4 : 0;
+    *counters = pl.splits > 1 ? pl.tiles : 0;
+    return CW_OK;
+}
+
+// X [T, K] (row stride ldx), W [N, K] (and W2 for SwiGLU), C [T, ldc].  K must be a multiple of 8
+// and all bases 16-byte aligned (TMA); returns CW_ERR_UNSUPPORTED otherwise so the caller can
+// use the plain kernel.
+extern "C" int cw_gemm_tc(const void* X, const void* W, const void* W2, const float* bias, void* C, int T,
+                          int N, int K, int ldx, int ldc, int epilogue, void* workspace,
+                          long long workspace_bytes, int* counters, int num_counters, int sm_count,
+                          int* status, cudaStream_t stream) {
+    if (T == 0 || N == 0) return CW_OK;
+    if (T < 0 || N < 0 || K <= 0 || ldx < K || ldc < N) return CW_ERR_BAD_SIZE;
+    if (epilogue < 0 || epilogue > 2) return CW_ERR_UNSUPPORTED;
+    if (K % 8 != 0 || ldx % 8 != 0 || ((uintptr_t)X & 15) || ((uintptr_t)W & 15) || ((uintptr_t)W2 & 15))
+        return CW_ERR_UNSUPPORTED;
+    if (load_encode() != 0) return CW_ERR_UNSUPPORTED;
+    const bool swiglu = W2 != nullptr;
+    const Plan pl = make_plan(T, N, K, swiglu, sm_count);
+    if (pl.splits > 1) {
+        const long long need = (long long)pl.tiles * pl.splits * pl.acc_cols * BM * 4;
+        if (workspace == nullptr || counters == nullptr || workspace_bytes < need || num_counters < pl.tiles)
+            return CW_ERR_BAD_SIZE;
+    }
+    CUtensorMap mw, mw2, mx;
+    if (make_map(&mw, W, N, K, K, BM) != 0) return CW_ERR_UNSUPPORTED;
+    if (make_map(&mw2, swiglu ? W2 : W, N, K, K, BM) != 0) return CW_ERR_UNSUPPORTED;
+    if (make_map(&mx, X, T, K, ldx, pl.bn) != 0) return CW_ERR_UNSUPPORTED;
+    GemmParams p;
+    p.T = T; p.N = N; p.K = K; p.ldc = ldc; p.epilogue = epilogue;
+    p.num_kb = (K + BK - 1) / BK; p.kb_per_split = pl.kb_per_split; p.splits = pl.splits;
+    p.bias = bias; p.C = C; p.workspace = (float*)workspace; p.counters = counters; p.status = status;
+    dim3 grid((N + BM - 1) / BM, (T + pl.bn - 1) / pl.bn, pl.splits);
+    if (grid.y > 65535) return CW_ERR_BAD_SIZE;
+#define CW_CASE(bn)                                                                       \
+    case bn:                                                                              \
+        return swiglu ? launch<bn, true>(mw, mw2, mx, p, grid, stream)                    \
+                      : launch<bn, false>(mw, mw2, mx, p, grid, stream);
+    switch (pl.bn) {
+        CW_CASE(16)
+        CW_CASE(32)
+        CW_CASE(64)
+        CW_CASE(128)
+        case 256:
+            return launch<256, false>(mw, mw2, mx, p, grid, stream);
+    }
+#undef CW_CASE
+    return CW_ERR_UNSUPPORTED;
+}

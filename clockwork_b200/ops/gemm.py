@@ -10,7 +10,7 @@ import torch
 
 from . import EPILOGUE_ADD_F32, EPILOGUE_STORE, EPILOGUE_STORE_F32, gemm_ref, gemm_ref_swiglu
 
-_tc = None  # set by ops.gemm_tc when the tensor-core kernels are present
+_tc = None  # set by ops.gemm_tc (imported at the end of this module)
 
 
 def _use_tc(x: torch.Tensor, w: torch.Tensor) -> bool:
@@ -41,3 +41,6 @@ def swiglu(x: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor) -> torch.T
     if _use_tc(x, w_gate):
         return _tc.gemm_swiglu(x, w_gate, w_up)
     return gemm_ref_swiglu(x, w_gate, w_up)
+
+
+from . import gemm_tc as _gemm_tc_module  # noqa: E402,F401  (registers itself as ``_tc``)

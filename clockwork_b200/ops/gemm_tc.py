@@ -1,0 +1,128 @@
+"""Python face of the tcgen05 matrix-product kernel (``csrc/gemm_tc.cu``).
+
+The kernel may split the inner dimension over several CTAs; the partial tiles then go through a
+float32 workspace owned by this module (one per device, allocated once, so that a captured CUDA
+graph can replay the calls)."""
+
+from __future__ import annotations
+
+from ctypes import POINTER, byref, c_int, c_longlong, c_void_p
+
+import torch
+
+from . import EPILOGUE_STORE, _need, _ptr, _stream, gemm as gemm_dispatch, new_status
+from .library import check, library
+
+WORKSPACE_BYTES = 64 << 20
+NUM_COUNTERS = 8192
+
+_state: dict[int, dict] = {}
+_configured = False
+
+
+def _configure() -> None:
+    global _configured
+    if _configured:
+        return
+    lib = library()
+    P, I, LL = c_void_p, c_int, c_longlong
+    lib.cw_gemm_tc.argtypes = [P, P, P, P, P, I, I, I, I, I, I, P, LL, P, I, I, P, P]
+    lib.cw_gemm_tc.restype = c_int
+    lib.cw_gemm_tc_workspace.argtypes = [I, I, I, I, I, POINTER(c_longlong), POINTER(c_int)]
+    lib.cw_gemm_tc_workspace.restype = c_int
+    _configured = True
+
+
+def _device_state(device: torch.device) -> dict:
+    index = device.index if device.index is not None else torch.cuda.current_device()
+    st = _state.get(index)
+    if st is None:
+        st = {
+            "workspace": torch.empty(WORKSPACE_BYTES, dtype=torch.uint8, device=device),
+            "counters": torch.zeros(NUM_COUNTERS, dtype=torch.int32, device=device),
+            "status": new_status(device),
+            "sms": torch.cuda.get_device_properties(device).multi_processor_count,
+        }
+        _state[index] = st
+    return st
+
+
+def status(device) -> torch.Tensor:
+    return _device_state(torch.device(device))["status"]
+
+
+def workspace_need(t: int, n: int, k: int, swiglu: bool, device) -> tuple[int, int]:
+    _configure()
+    b, c = c_longlong(0), c_int(0)
+    library().cw_gemm_tc_workspace(t, n, k, 1 if swiglu else 0, _device_state(torch.device(device))["sms"], byref(b), byref(c))
+    return b.value, c.value
+
+
+def accepts(x: torch.Tensor, w: torch.Tensor) -> bool:
+    """Sizes and alignments the TMA descriptors allow: rows of 16-byte multiples at 16-byte bases."""
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or x.dim() != 2 or w.dim() != 2:
+        return False
+    k = x.shape[1]
+    if k % 8 or x.stride(1) != 1 or (x.shape[0] > 1 and x.stride(0) % 8) or x.data_ptr() % 16 or w.data_ptr() % 16:
+        return False
+    if not w.is_contiguous():
+        return False
+    need, counters = workspace_need(x.shape[0], w.shape[0], k, False, x.device)
+    need2, counters2 = workspace_need(x.shape[0], w.shape[0], k, True, x.device)
+    return max(need, need2) <= WORKSPACE_BYTES and max(counters, counters2) <= NUM_COUNTERS
+
+
+def _run(x, w, w2, bias, out, epilogue) -> None:
+    _configure()
+    st = _device_state(x.device)
+    t, k = x.shape
+    n = w.shape[0]
+    ldx = x.stride(0) if t > 1 else max(x.stride(0), k)
+    if ldx % 8:
+        ldx = k
+    check(library().cw_gemm_tc(_ptr(x), _ptr(w), _ptr(w2), _ptr(bias), _ptr(out), t, n, k, ldx, out.stride(0), epilogue,
+                               _ptr(st["workspace"]), WORKSPACE_BYTES, _ptr(st["counters"]), NUM_COUNTERS, st["sms"],
+                               _ptr(st["status"]), _stream()), "gemm_tc")
+
+
+def gemm(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None, *, out: torch.Tensor | None = None,
+         epilogue: int = EPILOGUE_STORE) -> torch.Tensor:
+    """``x [T,K] @ w[N,K]^T (+ bias)`` in bfloat16 on the tensor cores, float32 accumulation.
+    Epilogues as for ``gemm_ref``: store bfloat16, add into float32 ``out``, store float32."""
+    _need(w, torch.bfloat16, "w", 2)
+    t, k = x.shape
+    n = w.shape[0]
+    if w.shape[1] != k:
+        raise ValueError(f"inner sizes differ: x has K={k}, w has K={w.shape[1]}")
+    if bias is not None:
+        _need(bias, torch.float32, "bias", 1)
+    want = torch.bfloat16 if epilogue == EPILOGUE_STORE else torch.float32
+    if out is None:
+        if epilogue == 1:
+            raise ValueError("the add epilogue needs an output to add into")
+        out = torch.empty((t, n), dtype=want, device=x.device)
+    _need(out, want, "out", 2)
+    if tuple(out.shape) != (t, n):
+        raise ValueError(f"out has shape {tuple(out.shape)}, expected {(t, n)}")
+    _run(x, w, None, bias, out, epilogue)
+    return out
+
+
+def gemm_swiglu(x: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor) -> torch.Tensor:
+    _need(w_gate, torch.bfloat16, "w_gate", 2)
+    _need(w_up, torch.bfloat16, "w_up", 2)
+    if w_gate.shape != w_up.shape or w_gate.shape[1] != x.shape[1]:
+        raise ValueError("gate and up weights must both be [N, K] with x's K")
+    out = torch.empty((x.shape[0], w_gate.shape[0]), dtype=torch.bfloat16, device=x.device)
+    _run(x, w_gate, w_up, None, out, 0)
+    return out
+
+
+def enable() -> None:
+    """Route the product path's bfloat16 products to this kernel."""
+    import sys
+
+    gemm_dispatch._tc = sys.modules[__name__]
+
+
+enable()

@@ -296,3 +296,77 @@ def test_sample_rows_carry_their_own_parameters(ops):
     got = ops.sample(logits.to(DEV), temps.to(DEV), ks.to(DEV), ps.to(DEV), u.to(DEV)).cpu().tolist()
     want = [plain.sample_with_uniform(logits[i], float(temps[i]), int(ks[i]) or -1, float(ps[i]), float(u[i])) for i in range(r)]
     assert got == want
+
+
+# ---- tcgen05 matrix products -------------------------------------------------------------------------
+TC_SHAPES = [
+    # T, N, K: decode sizes (inner dimension split over CTAs), ragged edges, prefill sizes
+    (1, 2048, 1536), (8, 1536, 8960), (8, 200, 72), (16, 1536, 1536), (17, 384, 200), (64, 2048, 1536),
+    (100, 130, 264), (300, 1000, 512), (512, 1536, 1536), (2048, 2048, 1536),
+]
+
+
+@pytest.fixture(scope="module")
+def gemm_tc():
+    from clockwork_b200.ops import gemm_tc
+
+    return gemm_tc
+
+
+def bf16_product(x, w):
+    return (x.double() @ w.double().T).float()
+
+
+@pytest.mark.parametrize("t,n,k", TC_SHAPES)
+def test_gemm_tc_against_float64(ops, gemm_tc, t, n, k):
+    x, w, bias = rand(t, k, dtype=torch.bfloat16), rand(n, k, dtype=torch.bfloat16, scale=0.1, seed=1), rand(n, seed=2)
+    xd, wd, bd = x.to(DEV), w.to(DEV), bias.to(DEV)
+    assert gemm_tc.accepts(xd, wd)
+    want = bf16_product(x, w) + bias
+    scale = max(1.0, float(want.abs().max()))
+    out32 = gemm_tc.gemm(xd, wd, bd, epilogue=ops.EPILOGUE_STORE_F32)
+    torch.testing.assert_close(out32.cpu(), want, rtol=1e-4, atol=1e-5 * scale)
+    out = gemm_tc.gemm(xd, wd, bd)
+    assert out.dtype == torch.bfloat16
+    torch.testing.assert_close(out.float().cpu(), want, rtol=1e-2, atol=1e-2 * scale)
+    base = rand(t, n, seed=3)
+    acc = base.to(DEV).clone()
+    gemm_tc.gemm(xd, wd, None, out=acc, epilogue=ops.EPILOGUE_ADD_F32)
+    torch.testing.assert_close(acc.cpu(), base + bf16_product(x, w), rtol=1e-4, atol=1e-5 * scale)
+    # twice in a row: the split counters are back at zero after a call
+    again = gemm_tc.gemm(xd, wd, bd, epilogue=ops.EPILOGUE_STORE_F32)
+    assert torch.equal(again, out32)
+    ops.raise_on_status(gemm_tc.status(DEV))
+
+
+@pytest.mark.parametrize("t,n,k", [(8, 8960, 1536), (33, 200, 96), (64, 1000, 1536), (700, 520, 256)])
+def test_gemm_tc_swiglu(ops, gemm_tc, t, n, k):
+    x = rand(t, k, dtype=torch.bfloat16)
+    wg, wu = rand(n, k, dtype=torch.bfloat16, scale=0.05, seed=1), rand(n, k, dtype=torch.bfloat16, scale=0.05, seed=2)
+    want = torch.nn.functional.silu(bf16_product(x, wg)) * bf16_product(x, wu)
+    got = gemm_tc.gemm_swiglu(x.to(DEV), wg.to(DEV), wu.to(DEV))
+    torch.testing.assert_close(got.float().cpu(), want, rtol=1e-2, atol=1e-2 * max(1.0, float(want.abs().max())))
+    ops.raise_on_status(gemm_tc.status(DEV))
+
+
+def test_gemm_tc_rows_do_not_depend_on_the_batch(ops, gemm_tc):
+    """The same token gives the same bits alone, in a batch of 8 and in a batch of 64 (the split of
+    the inner dimension may differ between those, the order of the float32 sums inside a split does not)."""
+    k, n = 1536, 2048
+    x, w = rand(64, k, dtype=torch.bfloat16).to(DEV), rand(n, k, dtype=torch.bfloat16, scale=0.1, seed=1).to(DEV)
+    full = gemm_tc.gemm(x, w, epilogue=ops.EPILOGUE_STORE_F32)
+    for rows in (1, 8):
+        part = gemm_tc.gemm(x[:rows].contiguous(), w, epilogue=ops.EPILOGUE_STORE_F32)
+        torch.testing.assert_close(part, full[:rows], rtol=1e-5, atol=1e-5)
+
+
+def test_gemm_tc_refuses_what_tma_cannot_address(ops, gemm_tc):
+    x, w = rand(4, 100, dtype=torch.bfloat16).to(DEV), rand(32, 100, dtype=torch.bfloat16).to(DEV)
+    assert not gemm_tc.accepts(x, w)  # rows of 200 bytes are no multiple of 16
+    from clockwork_b200.ops import gemm as dispatch
+
+    out = dispatch.linear(x, w, None)  # the product path falls back to the plain kernel
+    torch.testing.assert_close(out.float().cpu(), bf16_product(x.cpu(), w.cpu()), rtol=1e-2, atol=1e-2)
+    wide = rand(4, 128, dtype=torch.bfloat16).to(DEV)
+    assert gemm_tc.accepts(wide[:, 8:72], rand(32, 64, dtype=torch.bfloat16).to(DEV))  # an aligned column slice
+    assert not gemm_tc.accepts(wide[:, 4:68], rand(32, 64, dtype=torch.bfloat16).to(DEV))
