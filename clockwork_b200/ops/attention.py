@@ -24,3 +24,6 @@ def paged_attention(ctx, qkv: torch.Tensor, view, num_heads: int, num_kv_heads: 
             return _prefill.run(ctx, qkv, view, num_heads, num_kv_heads, head_dim, scale, window)
     return attention_ref(qkv, view.k_cache, view.v_cache, view.block_tables, ctx.tok_seq, ctx.positions,
                          num_heads, num_kv_heads, head_dim, scale, window, ctx.status)
+
+
+from . import attention_fast as _attention_fast_module  # noqa: E402,F401  (registers the bfloat16 kernels)

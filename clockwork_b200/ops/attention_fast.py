@@ -1,0 +1,144 @@
+"""Python faces of the bfloat16 attention kernels: split-context decode (``csrc/attention_decode.cu``)
+and tensor-core prefill (``csrc/attention_prefill.cu``).  ``ops.attention.paged_attention`` picks
+them when a step's sizes allow."""
+
+from __future__ import annotations
+
+import sys
+from ctypes import POINTER, byref, c_float, c_int, c_longlong, c_void_p
+
+import numpy as np
+import torch
+
+from . import _need, _ptr, _stream, attention as dispatch
+from .library import check, library
+
+DECODE_HEAD_DIMS = (16, 32, 48, 64, 80, 96, 112, 128, 160, 192, 256)
+PREFILL_HEAD_DIMS = (16, 32, 48, 64, 80, 96, 112, 128)
+QUERY_TILE = 64
+
+_configured = False
+_scratch: dict[int, dict] = {}
+
+
+def _configure() -> None:
+    global _configured
+    if _configured:
+        return
+    lib = library()
+    P, I, F, LL = c_void_p, c_int, c_float, c_longlong
+    lib.cw_attention_decode.argtypes = [P, I, P, P, P, P, P, I, I, I, I, I, I, I, F, I, I, P, P, P, P, P]
+    lib.cw_attention_decode.restype = c_int
+    lib.cw_attention_decode_workspace.argtypes = [I, I, I, I, I, POINTER(LL), POINTER(LL), POINTER(I)]
+    lib.cw_attention_decode_workspace.restype = c_int
+    lib.cw_attention_prefill.argtypes = [P, I, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, I, P, P]
+    lib.cw_attention_prefill.restype = c_int
+    _configured = True
+
+
+def _decode_scratch(device: torch.device, part_o: int, part_lse: int, counters: int) -> dict:
+    index = device.index if device.index is not None else torch.cuda.current_device()
+    st = _scratch.get(index)
+    if st is None or st["part_o"].numel() < part_o or st["part_lse"].numel() < part_lse or st["counters"].numel() < counters:
+        st = {
+            "part_o": torch.empty(max(part_o, 1 << 20), dtype=torch.float32, device=device),
+            "part_lse": torch.empty(max(part_lse, 1 << 14), dtype=torch.float32, device=device),
+            "counters": torch.zeros(max(counters, 1 << 12), dtype=torch.int32, device=device),
+        }
+        _scratch[index] = st
+    return st
+
+
+class _Decode:
+    @staticmethod
+    def accepts(ctx, view, num_heads, num_kv_heads, head_dim, window) -> bool:
+        return head_dim in DECODE_HEAD_DIMS and ctx.num_tokens == ctx.num_seqs
+
+    @staticmethod
+    def run(ctx, qkv, view, num_heads, num_kv_heads, head_dim, scale, window, max_ctx: int | None = None) -> torch.Tensor:
+        return attention_decode(qkv, view.k_cache, view.v_cache, view.block_tables, ctx.ctx_lens, num_heads,
+                                num_kv_heads, head_dim, scale, window, max_ctx or ctx.max_ctx_len, ctx.status)
+
+
+def attention_decode(q, k_cache, v_cache, block_tables, ctx_lens, num_heads, num_kv_heads, head_dim, scale, window,
+                     max_ctx: int, status) -> torch.Tensor:
+    """One query token per request: ``q`` [S, >= nh*hd] (row s belongs to request s), ``ctx_lens`` [S]
+    the tokens of each request in the cache (its own included).  Returns [S, nh*hd]."""
+    _configure()
+    if q.dtype != torch.bfloat16 or q.dim() != 2 or q.stride(1) != 1:
+        raise ValueError("q must be a 2-d bfloat16 tensor with unit column stride")
+    _need(k_cache, torch.bfloat16, "k_cache", 4)
+    _need(v_cache, torch.bfloat16, "v_cache", 4)
+    _need(block_tables, torch.int32, "block_tables", 2)
+    _need(ctx_lens, torch.int32, "ctx_lens", 1)
+    if head_dim not in DECODE_HEAD_DIMS:
+        raise ValueError(f"head_dim {head_dim} is not one of {DECODE_HEAD_DIMS}")
+    s = q.shape[0]
+    po, pl, pc = c_longlong(0), c_longlong(0), c_int(0)
+    library().cw_attention_decode_workspace(s, num_heads, num_kv_heads, head_dim, max_ctx, byref(po), byref(pl), byref(pc))
+    st = _decode_scratch(q.device, po.value, pl.value, pc.value)
+    out = torch.empty((s, num_heads * head_dim), dtype=torch.bfloat16, device=q.device)
+    check(library().cw_attention_decode(
+        _ptr(q), q.stride(0), _ptr(out), _ptr(k_cache), _ptr(v_cache), _ptr(block_tables), _ptr(ctx_lens), s, num_heads,
+        num_kv_heads, head_dim, k_cache.shape[1], block_tables.shape[1], k_cache.shape[0], float(scale), int(window or 0),
+        int(max_ctx), _ptr(st["part_o"]), _ptr(st["part_lse"]), _ptr(st["counters"]), _ptr(status), _stream()), "attention_decode")
+    return out
+
+
+def _work_items(ctx) -> tuple[torch.Tensor, torch.Tensor, int]:
+    """(request index, first query row) per 64 query rows of each portion; built once per step and
+    shared by all layers."""
+    cached = ctx.extras.get("prefill_items")
+    if cached is None:
+        seqs, q0s = [], []
+        for s, n in enumerate(ctx.q_lens_host):
+            for q0 in range(0, n, QUERY_TILE):
+                seqs.append(s)
+                q0s.append(q0)
+        host = torch.from_numpy(np.array([seqs, q0s], dtype=np.int32))
+        dev = host.to(ctx.device, non_blocking=False)
+        cached = (dev[0].contiguous(), dev[1].contiguous(), len(seqs))
+        ctx.extras["prefill_items"] = cached
+    return cached
+
+
+class _Prefill:
+    @staticmethod
+    def accepts(ctx, view, num_heads, num_kv_heads, head_dim, window) -> bool:
+        return head_dim in PREFILL_HEAD_DIMS and ctx.q_start is not None
+
+    @staticmethod
+    def run(ctx, qkv, view, num_heads, num_kv_heads, head_dim, scale, window) -> torch.Tensor:
+        item_seq, item_q0, items = _work_items(ctx)
+        return attention_prefill(qkv, view.k_cache, view.v_cache, view.block_tables, ctx.q_start, ctx.ctx_lens,
+                                 item_seq, item_q0, items, num_heads, num_kv_heads, head_dim, scale, window, ctx.status)
+
+
+def attention_prefill(q, k_cache, v_cache, block_tables, q_start, ctx_lens, item_seq, item_q0, items, num_heads,
+                      num_kv_heads, head_dim, scale, window, status) -> torch.Tensor:
+    """Any mixture of portions: ``q`` [N, >= nh*hd]; request s owns rows q_start[s]:q_start[s+1] and has
+    ctx_lens[s] tokens in the cache, its portion at the end.  Returns [N, nh*hd]."""
+    _configure()
+    if q.dtype != torch.bfloat16 or q.dim() != 2 or q.stride(1) != 1:
+        raise ValueError("q must be a 2-d bfloat16 tensor with unit column stride")
+    _need(k_cache, torch.bfloat16, "k_cache", 4)
+    _need(v_cache, torch.bfloat16, "v_cache", 4)
+    _need(block_tables, torch.int32, "block_tables", 2)
+    for name, t in (("q_start", q_start), ("ctx_lens", ctx_lens), ("item_seq", item_seq), ("item_q0", item_q0)):
+        _need(t, torch.int32, name, 1)
+    if head_dim not in PREFILL_HEAD_DIMS:
+        raise ValueError(f"head_dim {head_dim} is not one of {PREFILL_HEAD_DIMS}")
+    out = torch.empty((q.shape[0], num_heads * head_dim), dtype=torch.bfloat16, device=q.device)
+    check(library().cw_attention_prefill(
+        _ptr(q), q.stride(0), _ptr(out), _ptr(k_cache), _ptr(v_cache), _ptr(block_tables), _ptr(q_start), _ptr(ctx_lens),
+        _ptr(item_seq), _ptr(item_q0), items, num_heads, num_kv_heads, head_dim, k_cache.shape[1], block_tables.shape[1],
+        k_cache.shape[0], float(scale), int(window or 0), _ptr(status), _stream()), "attention_prefill")
+    return out
+
+
+def enable() -> None:
+    dispatch._decode = _Decode
+    dispatch._prefill = _Prefill
+
+
+enable()

@@ -370,3 +370,114 @@ def test_gemm_tc_refuses_what_tma_cannot_address(ops, gemm_tc):
     wide = rand(4, 128, dtype=torch.bfloat16).to(DEV)
     assert gemm_tc.accepts(wide[:, 8:72], rand(32, 64, dtype=torch.bfloat16).to(DEV))  # an aligned column slice
     assert not gemm_tc.accepts(wide[:, 4:68], rand(32, 64, dtype=torch.bfloat16).to(DEV))
+
+
+# ---- bfloat16 attention kernels ------------------------------------------------------------------------
+@pytest.fixture(scope="module")
+def fast():
+    from clockwork_b200.ops import attention_fast
+
+    return attention_fast
+
+
+@pytest.mark.parametrize("nh,nkv,hd,ps,window", [(12, 2, 128, 16, None), (5, 5, 48, 8, None), (32, 1, 64, 16, None),
+                                                (6, 2, 16, 4, None), (4, 2, 32, 8, 300), (3, 1, 256, 16, None)])
+def test_attention_decode_kernel(ops, status, fast, nh, nkv, hd, ps, window):
+    """Contexts that end inside the first tile, on a tile's edge, one past a split's edge and deep
+    into several splits; padding filled with 100.0 must not leak; a request of length 0 is padding."""
+    ctx_lens = [1, 17, 64, 256, 257, 700, 1300, 0]
+    dtype = torch.bfloat16
+    real = [c for c in ctx_lens if c > 0]
+    k_cache, v_cache, tables, ks, vs = paged_setup(real, nkv, hd, ps, dtype, seed=11)
+    tables = torch.cat([tables, torch.full((1, tables.shape[1]), -1, dtype=torch.int32)])
+    g = torch.Generator().manual_seed(2)
+    scale = hd**-0.5
+    qs = [(torch.randn(1, nh, hd, generator=g) * 2).to(dtype).float() for _ in ctx_lens]
+    wide = torch.zeros(len(ctx_lens), (nh + 2 * nkv) * hd)
+    wide[:, : nh * hd] = torch.cat(qs).view(len(ctx_lens), -1)
+    out = fast.attention_decode(wide.to(dtype).to(DEV), k_cache.to(DEV), v_cache.to(DEV), tables.to(DEV),
+                                torch.tensor(ctx_lens, dtype=torch.int32, device=DEV), nh, nkv, hd, scale, window,
+                                max(ctx_lens), status).float().cpu().view(len(ctx_lens), nh, hd)
+    ops.raise_on_status(status)
+    for i, n in enumerate(real):
+        want = plain.causal_attention(qs[i], ks[i], vs[i], scale, window=window)[0]
+        torch.testing.assert_close(out[i], want, rtol=2e-2, atol=2e-2, msg=lambda m: f"context {n}: {m}")
+    assert float(out[-1].abs().max()) == 0.0
+    # the grid's bound on the context changes nothing
+    again = fast.attention_decode(wide.to(dtype).to(DEV), k_cache.to(DEV), v_cache.to(DEV), tables.to(DEV),
+                                  torch.tensor(ctx_lens, dtype=torch.int32, device=DEV), nh, nkv, hd, scale, window,
+                                  4096, status).float().cpu().view(len(ctx_lens), nh, hd)
+    assert torch.equal(again, out)
+
+
+def test_attention_decode_finds_one_far_key(ops, status, fast):
+    nh, nkv, hd, ps, ctx = 4, 1, 64, 16, 1000
+    for far in (3, 255, 256, 777, 999):
+        k_cache, v_cache, tables, ks, vs = paged_setup([ctx], nkv, hd, ps, torch.bfloat16, seed=far)
+        q = torch.zeros(1, nh, hd)
+        q[0, :, 5] = 24.0
+        kc = k_cache.float()
+        page, off = int(tables[0, far // ps]), far % ps
+        kc[page, off, 0, :] = 0.0
+        kc[page, off, 0, 5] = 24.0
+        wide = torch.zeros(1, (nh + 2) * hd)
+        wide[0, : nh * hd] = q.view(-1)
+        out = fast.attention_decode(wide.bfloat16().to(DEV), kc.bfloat16().to(DEV), v_cache.to(DEV), tables.to(DEV),
+                                    torch.tensor([ctx], dtype=torch.int32, device=DEV), nh, nkv, hd, hd**-0.5, None, ctx, status)
+        torch.testing.assert_close(out.float().cpu().view(nh, hd)[2], vs[0][far, 0], rtol=2e-2, atol=2e-2)
+    ops.raise_on_status(status)
+
+
+@pytest.mark.parametrize("nh,nkv,hd,ps,window", [(12, 2, 128, 16, None), (5, 5, 48, 8, None), (8, 1, 16, 4, 37),
+                                                (4, 2, 32, 8, 100), (6, 3, 64, 16, None)])
+def test_attention_prefill_kernel_mixed_batch(ops, status, fast, nh, nkv, hd, ps, window):
+    """Portions in the middle of a context, whole prompts (shorter and longer than a tile, ending on
+    and off tile edges), and single decoded tokens, all in one launch."""
+    ctx_lens, q_lens = [150, 333, 41, 200, 1000, 64, 65, 129], [23, 1, 41, 200, 130, 64, 2, 128]
+    dtype = torch.bfloat16
+    k_cache, v_cache, tables, ks, vs = paged_setup(ctx_lens, nkv, hd, ps, dtype, seed=5)
+    scale = hd**-0.5
+    g = torch.Generator().manual_seed(6)
+    qs = [(torch.randn(q, nh, hd, generator=g) * 2).to(dtype).float() for q in q_lens]
+    n = sum(q_lens)
+    wide = torch.zeros(n, (nh + 2 * nkv) * hd)
+    wide[:, : nh * hd] = torch.cat(qs).view(n, nh * hd)
+    q_start = torch.tensor([0] + torch.tensor(q_lens).cumsum(0).tolist(), dtype=torch.int32)
+    items = [(s, q0) for s, q in enumerate(q_lens) for q0 in range(0, q, 64)]
+    item_seq = torch.tensor([i[0] for i in items], dtype=torch.int32)
+    item_q0 = torch.tensor([i[1] for i in items], dtype=torch.int32)
+    out = fast.attention_prefill(wide.to(dtype).to(DEV), k_cache.to(DEV), v_cache.to(DEV), tables.to(DEV), q_start.to(DEV),
+                                 torch.tensor(ctx_lens, dtype=torch.int32, device=DEV), item_seq.to(DEV), item_q0.to(DEV),
+                                 len(items), nh, nkv, hd, scale, window, status).float().cpu().view(n, nh, hd)
+    ops.raise_on_status(status)
+    row = 0
+    for i, (q, k, v) in enumerate(zip(qs, ks, vs)):
+        want = plain.causal_attention(q, k, v, scale, window=window)
+        torch.testing.assert_close(out[row : row + q.shape[0]], want, rtol=2e-2, atol=2e-2,
+                                   msg=lambda m: f"request {i} (context {ctx_lens[i]}, {q_lens[i]} queries): {m}")
+        row += q.shape[0]
+
+
+def test_attention_prefill_sees_the_diagonal_and_nothing_after_it(ops, status, fast):
+    """Each query's own key carries a score that stands out, so each output must be its own value;
+    if the mask were off by one either way the output would be a neighbour's."""
+    nh, nkv, hd, ps, n = 2, 1, 32, 16, 150
+    k_cache, v_cache, tables, ks, vs = paged_setup([n], nkv, hd, ps, torch.bfloat16, seed=9)
+    kc = k_cache.float()
+    q = torch.zeros(n, nh, hd)
+    for pos in range(n):
+        page, off = int(tables[0, pos // ps]), pos % ps
+        code = torch.tensor([1.0 if (pos >> b) & 1 else -1.0 for b in range(8)]) * 6.0
+        kc[page, off, 0, :] = 0.0
+        kc[page, off, 0, :8] = code
+        q[pos, :, :8] = code
+    wide = torch.zeros(n, (nh + 2) * hd)
+    wide[:, : nh * hd] = q.view(n, -1)
+    items = list(range(0, n, 64))
+    out = fast.attention_prefill(wide.bfloat16().to(DEV), kc.bfloat16().to(DEV), v_cache.to(DEV), tables.to(DEV),
+                                 torch.tensor([0, n], dtype=torch.int32, device=DEV), torch.tensor([n], dtype=torch.int32, device=DEV),
+                                 torch.zeros(len(items), dtype=torch.int32, device=DEV), torch.tensor(items, dtype=torch.int32, device=DEV),
+                                 len(items), nh, nkv, hd, 1.0, None, status).float().cpu().view(n, nh, hd)
+    ops.raise_on_status(status)
+    # own score 8*36 = 288; any other key differs in at least one bit: at most 288 - 72
+    torch.testing.assert_close(out[:, 0], vs[0][:, 0], rtol=2e-2, atol=2e-2)
