@@ -133,6 +133,8 @@ def main() -> int:
     ap.add_argument("--shape", default="qwen2.5-1.5b")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--skip-points", action="store_true", help="leave out batch 1 / 64 and prefill (quick runs)")
+    ap.add_argument("--only", choices=["decode", "prefill"], default=None,
+                    help="run one part only and print its figures (for profiling runs under ncu)")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm()
@@ -193,15 +195,15 @@ def main() -> int:
         for _ in range(warmup):
             engine.step()
         torch.cuda.synchronize()
-        l0 = launch_count()
+        l0 = launch_count() + runner.graph_kernel_launches
         t0 = time.perf_counter()
         for _ in range(steps):
             outs = engine.step()
             assert len(outs) == batch
         torch.cuda.synchronize()
         e2e_s = time.perf_counter() - t0
-        e2e_launches = launch_count() - l0
-        h2d = engine.runner.builder.last_upload_bytes
+        e2e_launches = launch_count() + runner.graph_kernel_launches - l0
+        h2d = engine.runner.last_upload_bytes
         # ---- device-timed: the same steps enqueued back to back ---------------------------------------
         tokens = [[rng.randrange(vocab)] for _ in range(batch)]
         ctx_now = cache.get(ids[0]).num_computed
@@ -209,7 +211,7 @@ def main() -> int:
         for _ in range(warmup):
             step_fn(ids, tokens)
         torch.cuda.synchronize()
-        l0 = launch_count()
+        l0 = launch_count() + runner.graph_kernel_launches
         start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         with ClockSampler() as clocks:
             start.record()
@@ -218,7 +220,7 @@ def main() -> int:
             end.record()
             torch.cuda.synchronize()
         dev_ms = start.elapsed_time(end)
-        launches = launch_count() - l0
+        launches = launch_count() + runner.graph_kernel_launches - l0
         runner.check_status()
         ctx_mid = ctx_now + warmup + steps // 2
         kv_bytes = batch * ctx_mid * cache.bytes_per_token()
@@ -266,7 +268,14 @@ def main() -> int:
         return {"value": PREFILL_LEN / (ms / 1e3), "tokens": PREFILL_LEN, "ms": ms,
                 "frac": flops / (ms / 1e3) / (peak["bf16_tflops"] * 1e12), "tflops": flops / (ms / 1e3) / 1e12}
 
+    if args.only == "prefill":
+        print(json.dumps({"impl": "ours", "prefill": time_prefill(reps=1)}))
+        return 0
     main_run = time_decode(args.batch, args.steps, args.warmup)
+    if args.only == "decode":
+        print(json.dumps({"impl": "ours", "batch": args.batch, "ms_per_step": main_run["ms_per_step"],
+                          "tok_s": main_run["tok_s"], "e2e_tok_s": main_run["e2e_tok_s"], "launches": main_run["launches"]}))
+        return 0
     out = {
         "metric": "decode tokens/s (Qwen2.5-1.5B shape, random weights)",
         "value": main_run["tok_s"], "unit": "tok/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,

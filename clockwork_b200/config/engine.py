@@ -36,6 +36,7 @@ class ModelConfig:
     dtype: str = "bfloat16"
     max_model_len: int = 4096
     seed: int = 0
+    cuda_graphs: bool = True  # replay captured graphs for steps in which every request decodes one token
 
     def __post_init__(self) -> None:
         self.dtype = normalise_dtype(self.dtype)

@@ -21,7 +21,7 @@ struct DecodeParams {
     bf16* out;
     const bf16* k_cache; const bf16* v_cache;
     const int* block_tables; const int* ctx_lens;
-    int nh, nkv, qgroups, page_size, max_blocks, num_pages;
+    int nh, nkv, qgroups, page_size, page_shift, max_blocks, num_pages;
     float scale; int window;
     float* part_o;   // [S, nh, max_splits, HD]
     float* part_lse; // [S, nh, max_splits]
@@ -61,6 +61,7 @@ attn_decode_kernel(const DecodeParams p) {
     if (sp < first_split || sp >= nsplits) return;
     const int t0 = sp * SPLIT, t1 = min(ctx, t0 + SPLIT);
     const int* table = p.block_tables + (size_t)s * p.max_blocks;
+    const float scale_log2 = p.scale * 1.4426950408889634f;  // softmax in base 2: exp(x) = 2^(x log2 e)
 
     // ---- Q rows of this group into shared memory, then into A fragments ----------------------------
     for (int i = tid; i < 16 * (HD / 8); i += blockDim.x) {
@@ -79,13 +80,14 @@ attn_decode_kernel(const DecodeParams p) {
             bool ok = pos < t1;
             size_t src = 0;
             if (ok) {
-                const int blk = pos / p.page_size;
+                const int blk = p.page_shift >= 0 ? pos >> p.page_shift : pos / p.page_size;
                 const int page = blk < p.max_blocks ? table[blk] : -1;
                 if (page < 0 || page >= p.num_pages) {
                     if (pos >= kv_begin) cw_report(p.status, CW_ST_PAGE_RANGE, s, page);
                     ok = false;
                 } else {
-                    src = (((size_t)page * p.page_size + pos % p.page_size) * p.nkv + kvh) * HD + c * 8;
+                    const int off = p.page_shift >= 0 ? pos & (p.page_size - 1) : pos % p.page_size;
+                    src = (((size_t)page * p.page_size + off) * p.nkv + kvh) * HD + c * 8;
                 }
             }
             if (ok) {
@@ -141,7 +143,7 @@ attn_decode_kernel(const DecodeParams p) {
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
                     const int pos = tok0 + 8 * j + 2 * t + (e & 1);
-                    const float v = (pos >= kv_begin && pos < t1) ? sc[j][e] * p.scale : -INFINITY;
+                    const float v = (pos >= kv_begin && pos < t1) ? sc[j][e] * scale_log2 : -INFINITY;
                     sc[j][e] = v;
                     mx[e >> 1] = fmaxf(mx[e >> 1], v);
                 }
@@ -152,14 +154,14 @@ attn_decode_kernel(const DecodeParams p) {
                 mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
                 mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
                 const float m_new = fmaxf(m_run[r], mx[r]);
-                alpha[r] = (m_run[r] == -INFINITY) ? 0.f : expf(m_run[r] - m_new);
+                alpha[r] = (m_run[r] == -INFINITY) ? 0.f : exp2f(m_run[r] - m_new);
                 float sum = 0.f;
 #pragma unroll
                 for (int j = 0; j < 2; ++j)
 #pragma unroll
                     for (int e = 0; e < 2; ++e) {
                         const float v = sc[j][2 * r + e];
-                        const float pr = (m_new == -INFINITY) ? 0.f : expf(v - m_new);
+                        const float pr = (m_new == -INFINITY) ? 0.f : exp2f(v - m_new);
                         sc[j][2 * r + e] = pr;
                         sum += pr;
                     }
@@ -216,7 +218,7 @@ attn_decode_kernel(const DecodeParams p) {
 #pragma unroll
             for (int w = 0; w < NWARPS; ++w) {
                 const float mw = ml_s[w][r][0];
-                const float e = (mw == -INFINITY) ? 0.f : expf(mw - m);
+                const float e = (mw == -INFINITY) ? 0.f : exp2f(mw - m);
                 L += e * ml_s[w][r][1];
                 O += e * Om[((size_t)w * 16 + r) * HD + d];
             }
@@ -227,7 +229,7 @@ attn_decode_kernel(const DecodeParams p) {
             p.out[((size_t)s * p.nh + h) * HD + d] = __float2bfloat16_rn(val);
         } else {
             p.part_o[(((size_t)s * p.nh + h) * p.max_splits + sp) * HD + d] = val;
-            if (d == 0) p.part_lse[((size_t)s * p.nh + h) * p.max_splits + sp] = L > 0.f ? m + logf(L) : -INFINITY;
+            if (d == 0) p.part_lse[((size_t)s * p.nh + h) * p.max_splits + sp] = L > 0.f ? m + log2f(L) : -INFINITY;  // base 2
         }
     }
     if (active == 1) return;
@@ -252,7 +254,7 @@ attn_decode_kernel(const DecodeParams p) {
         float W = 0.f, O = 0.f;
         if (m != -INFINITY)
             for (int k = first_split; k < nsplits; ++k) {
-                const float e = (lse[k] == -INFINITY) ? 0.f : expf(lse[k] - m);
+                const float e = (lse[k] == -INFINITY) ? 0.f : exp2f(lse[k] - m);
                 W += e;
                 O += e * po[(size_t)k * HD + d];
             }
@@ -306,7 +308,7 @@ extern "C" int cw_attention_decode(const void* q, int q_stride, void* out, const
     p.k_cache = (const bf16*)k_cache; p.v_cache = (const bf16*)v_cache;
     p.block_tables = block_tables; p.ctx_lens = ctx_lens;
     p.nh = nh; p.nkv = nkv; p.qgroups = (nh / nkv + 15) / 16;
-    p.page_size = page_size; p.max_blocks = max_blocks; p.num_pages = num_pages;
+    p.page_size = page_size; p.page_shift = (page_size & (page_size - 1)) == 0 ? __builtin_ctz(page_size) : -1; p.max_blocks = max_blocks; p.num_pages = num_pages;
     p.scale = scale; p.window = window;
     p.part_o = part_o; p.part_lse = part_lse; p.counters = counters; p.status = status;
     const int splits = (max_ctx + SPLIT - 1) / SPLIT;

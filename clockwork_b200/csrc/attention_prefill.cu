@@ -21,7 +21,7 @@ struct PrefillParams {
     const bf16* k_cache; const bf16* v_cache;
     const int* block_tables; const int* q_start; const int* ctx_lens;
     const int* item_seq; const int* item_q0;
-    int nh, nkv, page_size, max_blocks, num_pages;
+    int nh, nkv, page_size, page_shift, max_blocks, num_pages;
     float scale; int window;
     int* status;
 };
@@ -47,6 +47,7 @@ attn_prefill_kernel(const PrefillParams p) {
     const int kv_lo = p.window > 0 ? max(0, pos0 + 1 - p.window) : 0;
     const int tile_lo = kv_lo / TILE * TILE;
     const int* table = p.block_tables + (size_t)s * p.max_blocks;
+    const float scale_log2 = p.scale * 1.4426950408889634f;  // softmax in base 2: exp(x) = 2^(x log2 e)
 
     for (int i = tid; i < QT * (HD / 8); i += blockDim.x) {
         const int r = i / (HD / 8), c = i % (HD / 8);
@@ -64,13 +65,14 @@ attn_prefill_kernel(const PrefillParams p) {
             bool ok = pos < kv_hi && pos >= kv_lo;
             size_t src = 0;
             if (ok) {
-                const int blk = pos / p.page_size;
+                const int blk = p.page_shift >= 0 ? pos >> p.page_shift : pos / p.page_size;
                 const int page = blk < p.max_blocks ? table[blk] : -1;
                 if (page < 0 || page >= p.num_pages) {
                     cw_report(p.status, CW_ST_PAGE_RANGE, s, page);
                     ok = false;
                 } else {
-                    src = (((size_t)page * p.page_size + pos % p.page_size) * p.nkv + kvh) * HD + c * 8;
+                    const int off = p.page_shift >= 0 ? pos & (p.page_size - 1) : pos % p.page_size;
+                    src = (((size_t)page * p.page_size + off) * p.nkv + kvh) * HD + c * 8;
                 }
             }
             if (ok) {
@@ -137,7 +139,7 @@ attn_prefill_kernel(const PrefillParams p) {
                     const int pos = tile0 + 8 * j + 2 * t + (e & 1);
                     const int qp = qpos[e >> 1];
                     const bool vis = pos <= qp && pos >= kv_lo && (p.window <= 0 || pos > qp - p.window);
-                    const float v = vis ? sc[j][e] * p.scale : -INFINITY;
+                    const float v = vis ? sc[j][e] * scale_log2 : -INFINITY;
                     sc[j][e] = v;
                     mx[e >> 1] = fmaxf(mx[e >> 1], v);
                 }
@@ -147,13 +149,13 @@ attn_prefill_kernel(const PrefillParams p) {
                 mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
                 mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
                 const float m_new = fmaxf(m_run[r], mx[r]);
-                alpha[r] = (m_run[r] == -INFINITY) ? 0.f : expf(m_run[r] - m_new);
+                alpha[r] = (m_run[r] == -INFINITY) ? 0.f : exp2f(m_run[r] - m_new);
                 float sum = 0.f;
 #pragma unroll
                 for (int j = 0; j < TILE / 8; ++j)
 #pragma unroll
                     for (int e = 0; e < 2; ++e) {
-                        const float pr = (m_new == -INFINITY) ? 0.f : expf(sc[j][2 * r + e] - m_new);
+                        const float pr = (m_new == -INFINITY) ? 0.f : exp2f(sc[j][2 * r + e] - m_new);
                         sc[j][2 * r + e] = pr;
                         sum += pr;
                     }
@@ -237,7 +239,7 @@ extern "C" int cw_attention_prefill(const void* q, int q_stride, void* out, cons
     p.k_cache = (const bf16*)k_cache; p.v_cache = (const bf16*)v_cache;
     p.block_tables = block_tables; p.q_start = q_start; p.ctx_lens = ctx_lens;
     p.item_seq = item_seq; p.item_q0 = item_q0;
-    p.nh = nh; p.nkv = nkv; p.page_size = page_size; p.max_blocks = max_blocks; p.num_pages = num_pages;
+    p.nh = nh; p.nkv = nkv; p.page_size = page_size; p.page_shift = (page_size & (page_size - 1)) == 0 ? __builtin_ctz(page_size) : -1; p.max_blocks = max_blocks; p.num_pages = num_pages;
     p.scale = scale; p.window = window; p.status = status;
     switch (hd) {
         case 16: return launch_prefill<16>(p, items, stream);

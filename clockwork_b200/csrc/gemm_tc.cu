@@ -292,20 +292,27 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 }
             }
             if (f < p.N) {
+                const int t_base = n0 + c;
+                float* c32 = (float*)p.C + (size_t)t_base * p.ldc + f;
+                bf16* c16 = (bf16*)p.C + (size_t)t_base * p.ldc + f;
+                float old[16];
+                if (!SWIGLU && p.epilogue == 1) {
+                    // all 16 loads first: issued back to back instead of one load-add-store chain each
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) old[j] = (t_base + j < p.T) ? c32[(size_t)j * p.ldc] : 0.f;
+                }
 #pragma unroll
                 for (int j = 0; j < 16; ++j) {
-                    const int t = n0 + c + j;
-                    if (t >= p.T) break;
-                    const size_t idx = (size_t)t * p.ldc + f;
+                    if (t_base + j >= p.T) break;
                     const float v = g[j] + bias;
                     if (SWIGLU) {
-                        ((bf16*)p.C)[idx] = __float2bfloat16_rn(v / (1.0f + expf(-v)) * u[j]);
+                        c16[(size_t)j * p.ldc] = __float2bfloat16_rn(v / (1.0f + expf(-v)) * u[j]);
                     } else if (p.epilogue == 0) {
-                        ((bf16*)p.C)[idx] = __float2bfloat16_rn(v);
+                        c16[(size_t)j * p.ldc] = __float2bfloat16_rn(v);
                     } else if (p.epilogue == 1) {
-                        ((float*)p.C)[idx] += v;
+                        c32[(size_t)j * p.ldc] = old[j] + v;
                     } else {
-                        ((float*)p.C)[idx] = v;
+                        c32[(size_t)j * p.ldc] = v;
                     }
                 }
             }

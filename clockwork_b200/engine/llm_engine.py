@@ -68,6 +68,8 @@ class LLMEngine:
         self.scheduler = Scheduler(cfg.scheduler, self.cache, self.prefix_cache)
         self.runner = ModelRunner(model, self.cache)
         self.sampler = Sampler(model.device, default_seed=cfg.model.seed)
+        self.uses_graphs = bool(cfg.model.cuda_graphs) and self.runner.enable_graphs(
+            cfg.model.max_model_len, cfg.scheduler.max_num_seqs)
         self._eos = _eos_ids(tokenizer, model.spec)
         self._seqs: dict[str, Sequence] = {}
         self._texts: dict[str, str] = {}
@@ -149,12 +151,18 @@ class LLMEngine:
             entries.append(StepEntry(p.seq.seq_id, tokens, [p.num_tokens - 1] if p.samples else []))
             if p.samples:
                 sampled_seqs.append(p.seq)
-        logits = self.runner.step(entries)
         tokens: list[int] = []
-        if sampled_seqs:
-            tokens = self.sampler.sample(
-                logits, [s.sampling_params for s in sampled_seqs], [len(s.output_token_ids) for s in sampled_seqs]
-            )
+        if len(sampled_seqs) == len(entries) and self.runner.can_use_graph(entries):
+            # every request decodes one token: replay the captured graph (forward pass + sampling)
+            sampling = self.sampler.host_params(
+                [s.sampling_params for s in sampled_seqs], [len(s.output_token_ids) for s in sampled_seqs])
+            tokens = self.runner.decode_with_graph(entries, sampling).tolist()
+        else:
+            logits = self.runner.step(entries)
+            if sampled_seqs:
+                tokens = self.sampler.sample(
+                    logits, [s.sampling_params for s in sampled_seqs], [len(s.output_token_ids) for s in sampled_seqs]
+                )
         self.runner.check_status()
         for p in out.portions:
             p.seq.num_computed_tokens = p.start + p.num_tokens
@@ -241,6 +249,8 @@ class LLMEngine:
         from .. import ops
 
         entries = [StepEntry(rid, toks, [len(toks) - 1]) for rid, toks in zip(request_ids, tokens)]
+        if self.runner.can_use_graph(entries):
+            return self.runner.decode_with_graph(entries, None)
         return ops.argmax(self.runner.step(entries))
 
     def stats(self) -> dict:

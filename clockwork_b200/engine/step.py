@@ -21,6 +21,7 @@ import torch
 
 from .. import ops
 from ..cache.manager import NO_PAGE, CacheManager
+from ..ops.library import launch_count
 from ..parts.base import StepContext
 from ..parts.model import DecoderModel
 
@@ -163,6 +164,124 @@ class StepBuilder:
             self.cache.release_behind_window(r, end)
 
 
+class DecodeGraph:
+    """One captured CUDA graph of the model's forward pass plus sampling for a fixed number of
+    single-token requests.  Its inputs live in one static int32 buffer that is refilled (one upload)
+    before every replay; rows beyond the live requests are padding (context length 0, slot -1)."""
+
+    def __init__(self, runner: "ModelRunner", batch: int, max_ctx: int, greedy: bool) -> None:
+        cache, model = runner.cache, runner.model
+        self.batch, self.greedy = batch, greedy
+        self.max_blocks = (max_ctx + cache.page_size - 1) // cache.page_size
+        G = len(cache.groups)
+        seg, off = {}, 0
+        for name, size in (("tokens", batch), ("positions", batch), ("tok_seq", batch), ("q_start", batch + 1),
+                           ("ctx_lens", batch), ("rows", batch), ("temperature", batch), ("top_k", batch),
+                           ("top_p", batch), ("uniform", batch)):
+            seg[name] = (off, size)
+            off += _pad4(size)
+        for g in range(G):
+            seg[f"slots{g}"] = (off, batch)
+            off += _pad4(batch)
+            seg[f"tables{g}"] = (off, batch * self.max_blocks)
+            off += _pad4(batch * self.max_blocks)
+        self.seg, self.size = seg, off
+        self.host = torch.zeros(off, dtype=torch.int32, pin_memory=True)
+        self.dev = torch.zeros(off, dtype=torch.int32, device=runner.device)
+        h = self.host.numpy()
+        self.h = {name: h[o : o + n] for name, (o, n) in seg.items()}
+        self.hf = {name: h[o : o + n].view(np.float32) for name, (o, n) in seg.items()
+                   if name in ("temperature", "top_p", "uniform")}
+        for g in range(G):
+            self.h[f"tables{g}"] = self.h[f"tables{g}"].reshape(batch, self.max_blocks)
+        self.h["q_start"][:] = np.arange(batch + 1)
+        self.h["rows"][:] = np.arange(batch)
+        self.upload_bytes = off * 4
+        self._uploaded = torch.cuda.Event()
+        # which request's table each row holds and how much of it, so that a step writes only the
+        # pages a request gained since its last step
+        self._row_owner: list[tuple[str, int] | None] = [None] * batch
+
+        def view(name):
+            o, n = seg[name]
+            return self.dev[o : o + n]
+
+        ctx = StepContext(
+            dtype=model.dtype, device=runner.device, status=runner.status, num_tokens=batch, num_seqs=batch,
+            positions=view("positions"), tok_seq=view("tok_seq"), q_start=view("q_start"), ctx_lens=view("ctx_lens"),
+            q_lens_host=[1] * batch, ctx_lens_host=[max_ctx] * batch, max_q_len=1, max_ctx_len=max_ctx,
+        )
+        ctx.views = cache.views([view(f"tables{g}").view(batch, self.max_blocks) for g in range(G)],
+                                [view(f"slots{g}") for g in range(G)], None, [])
+
+        def run():
+            logits = model.forward(ctx, view("tokens"), view("rows"))
+            if greedy:
+                return ops.argmax(logits)
+            return ops.sample(logits, view("temperature").view(torch.float32), view("top_k"),
+                              view("top_p").view(torch.float32), view("uniform").view(torch.float32))
+
+        self._fill_padding(0)
+        self.dev.copy_(self.host)
+        before = launch_count()
+        run()  # eager warm-up: scratch buffers and kernel attributes are set up outside the capture
+        self.kernels = launch_count() - before
+        torch.cuda.synchronize()
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph):
+            self.out = run()
+        torch.cuda.synchronize()
+
+    def _fill_padding(self, live: int) -> None:
+        h = self.h
+        h["tokens"][live:] = 0
+        h["positions"][live:] = 0
+        h["tok_seq"][live:] = -1
+        h["ctx_lens"][live:] = 0
+        for name in h:
+            if name.startswith("slots"):
+                h[name][live:] = -1
+
+    def replay(self, cache: CacheManager, reqs, tokens: list[int], sampling=None) -> torch.Tensor:
+        """Refill the inputs for these requests (each brings one token, its slot already
+        reserved), upload them in one copy, replay.  ``sampling``: (temperature, top_k, top_p,
+        uniform) lists for a graph that samples.  Returns the sampled tokens of the live rows."""
+        n = len(reqs)
+        self._uploaded.synchronize()  # the last upload has left the pinned buffer
+        h, ps = self.h, cache.page_size
+        h["tokens"][:n] = tokens
+        pos = np.fromiter((r.num_computed for r in reqs), dtype=np.int32, count=n)
+        h["positions"][:n] = pos
+        h["tok_seq"][:n] = np.arange(n, dtype=np.int32)
+        h["ctx_lens"][:n] = pos + 1
+        for g in range(len(cache.groups)):
+            tables, slots = h[f"tables{g}"], h[f"slots{g}"]
+            for i, r in enumerate(reqs):
+                table = r.tables[g]
+                owner = self._row_owner[i] if g == 0 else None
+                have = owner[1] if owner is not None and owner[0] == r.request_id and owner[1] <= len(table) else 0
+                if have < len(table):
+                    tables[i, have : len(table)] = table[have:]
+                if g == 0:
+                    self._row_owner[i] = (r.request_id, len(table)) if len(cache.groups) == 1 else None
+                page = table[pos[i] // ps]
+                if page == NO_PAGE:
+                    raise RuntimeError(f"request {r.request_id!r}: a token lands in a page that was given back")
+                slots[i] = page * ps + pos[i] % ps
+        if sampling is not None:
+            temperature, top_k, top_p, uniform = sampling
+            self.hf["temperature"][:n] = temperature
+            h["top_k"][:n] = top_k
+            self.hf["top_p"][:n] = top_p
+            self.hf["uniform"][:n] = uniform
+            self.hf["temperature"][n:] = 0.0
+        self._fill_padding(n)
+        self.dev.copy_(self.host, non_blocking=True)
+        self._uploaded.record()
+        self.graph.replay()
+        return self.out[:n]
+
+
 class ModelRunner:
     """The step function over a model and a cache manager."""
 
@@ -176,6 +295,52 @@ class ModelRunner:
         self.status = cache.status if cache.status is not None else ops.new_status(self.device)
         self.builder = StepBuilder(cache, model.dtype, self.device, self.status)
         self.steps_run = 0
+        self.graphs: dict[tuple[int, bool], DecodeGraph] = {}
+        self.graph_max_ctx = 0  # set by enable_graphs
+        self.graph_max_batch = 0
+        self.graph_kernel_launches = 0  # kernels replayed through graphs (for accounting)
+        self.last_upload_bytes = 0
+
+    def enable_graphs(self, max_ctx: int, max_batch: int) -> bool:
+        """Let steps in which every request brings exactly one token replay a captured CUDA graph
+        (one per batch-size bucket).  Only for models whose parts are all safe to capture."""
+        if not self.model.graph_safe() or self.cache.state.needs:
+            return False
+        self.graph_max_ctx, self.graph_max_batch = max_ctx, max_batch
+        return True
+
+    def can_use_graph(self, entries: list[StepEntry]) -> bool:
+        return (self.graph_max_batch > 0 and 0 < len(entries) <= self.graph_max_batch
+                and all(len(e.tokens) == 1 for e in entries))
+
+    def decode_with_graph(self, entries: list[StepEntry], sampling=None) -> torch.Tensor:
+        """One single-token step for every entry through the captured graph, sampling included.
+        Returns the sampled tokens (device int32 [len(entries)])."""
+        cache = self.cache
+        reqs = []
+        for e in entries:
+            req = cache.get(e.request_id)
+            cache.reserve(req, req.num_computed + 1)
+            if req.num_computed + 1 > self.graph_max_ctx:
+                raise ValueError(f"request {e.request_id!r} outgrew the context the decode graphs were captured for")
+            reqs.append(req)
+        n = len(entries)
+        bucket = 1
+        while bucket < n:
+            bucket *= 2
+        bucket = min(bucket, max(self.graph_max_batch, n))
+        key = (bucket, sampling is None)
+        graph = self.graphs.get(key)
+        if graph is None:
+            graph = self.graphs[key] = DecodeGraph(self, bucket, self.graph_max_ctx, greedy=sampling is None)
+        out = graph.replay(cache, reqs, [e.tokens[0] for e in entries], sampling)
+        self.graph_kernel_launches += graph.kernels
+        self.last_upload_bytes = graph.upload_bytes
+        for r in reqs:
+            r.num_computed += 1
+            cache.release_behind_window(r, r.num_computed)
+        self.steps_run += 1
+        return out
 
     def step(self, entries: list[StepEntry]) -> torch.Tensor | None:
         """Run the entries as one batch.  Returns float32 logits [wanted rows, vocab] in the order
@@ -186,6 +351,7 @@ class ModelRunner:
         prepared = self.builder.prepare(entries)
         logits = self.model.forward(prepared.ctx, prepared.token_ids, prepared.logit_rows)
         self.builder.commit(prepared)
+        self.last_upload_bytes = self.builder.last_upload_bytes
         self.steps_run += 1
         return logits
 

@@ -41,6 +41,7 @@ class Attention(Mixer):
         if self.window is not None and int(self.window) <= 0:
             raise ValueError("window must be positive or None")
         self.position = build_part("position", p["position"], prefix, dtype, device)
+        self.graph_safe = bool(self.position.graph_safe)
         self.qkv: Linear | None = None
         self.o: Linear | None = None
 

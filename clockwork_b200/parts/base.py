@@ -140,6 +140,9 @@ class Part:
     def name(self, suffix: str) -> str:
         return f"{self.prefix}.{suffix}" if self.prefix else suffix
 
+    graph_safe = False  # True when forward only launches kernels on the current stream (no host
+    # reads of device data, no Python-side loops over step contents): it may be captured in a CUDA graph
+
     def tensor_decls(self) -> Iterable[TensorDecl]:
         return ()
 

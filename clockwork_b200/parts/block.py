@@ -26,6 +26,10 @@ class PreNormResidualBlock(Block):
     def parts(self):
         return (self.mixer_norm, self.mixer, self.ffn_norm, self.ffn)
 
+    @property
+    def graph_safe(self) -> bool:
+        return all(part.graph_safe for part in self.parts())
+
     def tensor_decls(self):
         for part in self.parts():
             yield from part.tensor_decls()

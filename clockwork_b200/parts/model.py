@@ -49,6 +49,10 @@ class DecoderModel:
                 )
         return needs
 
+    def graph_safe(self) -> bool:
+        """Whether a step of this model may be captured in a CUDA graph."""
+        return all(block.graph_safe for block in self.blocks) and self.final_norm.graph_safe
+
     # ---- weights ---------------------------------------------------------------------------
     def tensor_decls(self) -> list[TensorDecl]:
         spec = self.spec

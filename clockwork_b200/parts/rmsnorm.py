@@ -16,6 +16,8 @@ from .registry import register_norm
 
 
 class RMSNorm(Norm):
+    graph_safe = True
+
     def __init__(self, spec, prefix, dtype, device) -> None:
         super().__init__(spec, prefix, dtype, device)
         self.size = int(spec["size"])

@@ -19,6 +19,8 @@ from .registry import register_position
 
 
 class RotaryNeox(PositionEncoding):
+    graph_safe = True
+
     def __init__(self, spec, prefix, dtype, device) -> None:
         super().__init__(spec, prefix, dtype, device)
         self.theta = float(spec["theta"])
@@ -40,6 +42,8 @@ class RotaryNeox(PositionEncoding):
 
 
 class NoPosition(PositionEncoding):
+    graph_safe = True
+
     def apply_and_store(self, ctx, qkv, view, num_heads, num_kv_heads, head_dim) -> None:
         if view is not None and view.write:
             ops.rope_store(qkv, ctx.positions, view.slots, None, view.k_cache, view.v_cache,

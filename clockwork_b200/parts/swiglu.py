@@ -16,6 +16,8 @@ from .registry import register_ffn
 
 
 class SwiGLU(FeedForward):
+    graph_safe = True
+
     def __init__(self, spec, prefix, dtype, device) -> None:
         super().__init__(spec, prefix, dtype, device)
         self.hidden_size = int(spec["hidden_size"])

