@@ -30,17 +30,31 @@ struct DecodeParams {
     int* status;
 };
 
-template <int HD>
+__device__ __forceinline__ void cp_async_wait_upto(int n) {
+    switch (n) {
+        case 0: cp_async_wait<0>(); break;
+        case 1: cp_async_wait<1>(); break;
+        case 2: cp_async_wait<2>(); break;
+        default: cp_async_wait<3>(); break;
+    }
+}
+
+// ST: tiles in flight.  4 puts a whole split (256 tokens) in flight at once, for steps with few
+// CTAs where latency is everything; 2 halves the shared memory so that two CTAs share an SM.
+template <int HD, int ST>
 __global__ void __launch_bounds__(NWARPS * 32)
 attn_decode_kernel(const DecodeParams p) {
     constexpr int LD = HD + 8;  // padded row (elements): consecutive rows fall into different banks
     extern __shared__ __align__(16) uint8_t smem_raw[];
     bf16* Qs = (bf16*)smem_raw;                 // [16][LD]
-    bf16* Ks = Qs + 16 * LD;                    // [2][TILE][LD]
-    bf16* Vs = Ks + 2 * TILE * LD;              // [2][TILE][LD]
+    bf16* Ks = Qs + 16 * LD;                    // [ST][TILE][LD]
+    bf16* Vs = Ks + ST * TILE * LD;             // [ST][TILE][LD]
     __shared__ float ml_s[NWARPS][16][2];
+    __shared__ int slot_s[SPLIT];               // cache slot of every token of this split (-1: none)
     __shared__ int last_flag;
 
+    pdl_launch_dependents();
+    pdl_wait();
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g = lane >> 2, t = lane & 3;
     const int kvh = blockIdx.x / p.qgroups, qg = blockIdx.x % p.qgroups;
@@ -71,26 +85,31 @@ attn_decode_kernel(const DecodeParams p) {
         *reinterpret_cast<uint4*>(Qs + r * LD + c * 8) = v;
     }
 
-    auto load_tile = [&](int tile0, int buf) {
-        bf16* kd = Ks + buf * TILE * LD;
-        bf16* vd = Vs + buf * TILE * LD;
+    // slots of the split's tokens, looked up once: tile loads then depend on shared memory only
+    for (int i = tid; i < SPLIT; i += blockDim.x) {
+        const int pos = t0 + i;
+        int slot = -1;
+        if (pos < t1 && pos >= kv_begin) {
+            const int blk = p.page_shift >= 0 ? pos >> p.page_shift : pos / p.page_size;
+            const int page = blk < p.max_blocks ? table[blk] : -1;
+            if (page < 0 || page >= p.num_pages) {
+                cw_report(p.status, CW_ST_PAGE_RANGE, s, page);
+            } else {
+                slot = page * p.page_size + (p.page_shift >= 0 ? pos & (p.page_size - 1) : pos % p.page_size);
+            }
+        }
+        slot_s[i] = slot;
+    }
+    __syncthreads();  // Qs and slot_s visible
+
+    auto load_tile = [&](int tile_idx) {
+        bf16* kd = Ks + (tile_idx % ST) * TILE * LD;
+        bf16* vd = Vs + (tile_idx % ST) * TILE * LD;
         for (int i = tid; i < TILE * (HD / 8); i += blockDim.x) {
             const int r = i / (HD / 8), c = i % (HD / 8);
-            const int pos = tile0 + r;
-            bool ok = pos < t1;
-            size_t src = 0;
-            if (ok) {
-                const int blk = p.page_shift >= 0 ? pos >> p.page_shift : pos / p.page_size;
-                const int page = blk < p.max_blocks ? table[blk] : -1;
-                if (page < 0 || page >= p.num_pages) {
-                    if (pos >= kv_begin) cw_report(p.status, CW_ST_PAGE_RANGE, s, page);
-                    ok = false;
-                } else {
-                    const int off = p.page_shift >= 0 ? pos & (p.page_size - 1) : pos % p.page_size;
-                    src = (((size_t)page * p.page_size + off) * p.nkv + kvh) * HD + c * 8;
-                }
-            }
-            if (ok) {
+            const int slot = slot_s[tile_idx * TILE + r];
+            if (slot >= 0) {
+                const size_t src = ((size_t)slot * p.nkv + kvh) * HD + c * 8;
                 cp_async16(kd + r * LD + c * 8, p.k_cache + src);
                 cp_async16(vd + r * LD + c * 8, p.v_cache + src);
             } else {
@@ -102,8 +121,7 @@ attn_decode_kernel(const DecodeParams p) {
     };
 
     const int ntiles = (t1 - t0 + TILE - 1) / TILE;
-    load_tile(t0, 0);
-    __syncthreads();  // Qs visible
+    for (int i = 0; i < ST && i < ntiles; ++i) load_tile(i);
     uint32_t qa[HD / 16][4];
 #pragma unroll
     for (int ks = 0; ks < HD / 16; ++ks)
@@ -116,13 +134,8 @@ attn_decode_kernel(const DecodeParams p) {
     float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
 
     for (int it = 0; it < ntiles; ++it) {
-        const int buf = it & 1;
-        if (it + 1 < ntiles) {
-            load_tile(t0 + (it + 1) * TILE, buf ^ 1);
-            cp_async_wait<1>();
-        } else {
-            cp_async_wait<0>();
-        }
+        const int buf = it % ST;
+        cp_async_wait_upto(min(ntiles - it - 1, ST - 1));  // tile `it` has landed; later ones may fly
         __syncthreads();
         const bf16* kt = Ks + buf * TILE * LD + warp * 16 * LD;
         const bf16* vt = Vs + buf * TILE * LD + warp * 16 * LD;
@@ -186,6 +199,7 @@ attn_decode_kernel(const DecodeParams p) {
             }
         }
         __syncthreads();  // everyone is done with this buffer before it is refilled
+        if (it + ST < ntiles) load_tile(it + ST);
     }
     // ---- merge the four warps (each saw a quarter of every tile) -----------------------------------
 #pragma unroll
@@ -248,36 +262,59 @@ attn_decode_kernel(const DecodeParams p) {
     for (int i = tid; i < rows * HD; i += blockDim.x) {
         const int r = i / HD, d = i % HD, h = h0 + r;
         const float* lse = p.part_lse + ((size_t)s * p.nh + h) * p.max_splits;
-        const float* po = p.part_o + ((size_t)s * p.nh + h) * p.max_splits * HD;
+        const float* po = p.part_o + ((size_t)s * p.nh + h) * p.max_splits * HD + d;
         float m = -INFINITY;
-        for (int k = first_split; k < nsplits; ++k) m = fmaxf(m, lse[k]);
+        for (int k0 = first_split; k0 < nsplits; k0 += 8) {  // eight independent loads at a time
+            float l8[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) l8[j] = (k0 + j < nsplits) ? __ldcg(lse + k0 + j) : -INFINITY;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) m = fmaxf(m, l8[j]);
+        }
         float W = 0.f, O = 0.f;
         if (m != -INFINITY)
-            for (int k = first_split; k < nsplits; ++k) {
-                const float e = (lse[k] == -INFINITY) ? 0.f : exp2f(lse[k] - m);
-                W += e;
-                O += e * po[(size_t)k * HD + d];
+            for (int k0 = first_split; k0 < nsplits; k0 += 8) {
+                float l8[8], o8[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const bool in = k0 + j < nsplits;
+                    l8[j] = in ? __ldcg(lse + k0 + j) : -INFINITY;
+                    o8[j] = in ? __ldcg(po + (size_t)(k0 + j) * HD) : 0.f;
+                }
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {  // split order
+                    const float e = (l8[j] == -INFINITY) ? 0.f : exp2f(l8[j] - m);
+                    W += e;
+                    O += e * o8[j];
+                }
             }
         p.out[((size_t)s * p.nh + h) * HD + d] = __float2bfloat16_rn(W > 0.f ? O / W : 0.f);
     }
 }
 
-template <int HD>
-static int launch_decode(const DecodeParams& p, int S, int splits, cudaStream_t stream) {
+template <int HD, int ST>
+static int launch_decode_st(const DecodeParams& p, int S, int splits, cudaStream_t stream) {
     constexpr int LD = HD + 8;
-    constexpr int SMEM = (16 * LD + 4 * TILE * LD) * 2;
+    constexpr int SMEM = (16 * LD + 2 * ST * TILE * LD) * 2;
     constexpr int MERGE = NWARPS * 16 * HD * 4;
-    static_assert(MERGE <= 2 * TILE * LD * 2, "the merge buffer must fit over the K buffers");
+    static_assert(MERGE <= ST * TILE * LD * 2, "the merge buffer must fit over the K buffers");
     static bool configured = false;
     if (!configured) {
         if (SMEM > 48 * 1024 &&
-            cudaFuncSetAttribute(attn_decode_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess)
+            cudaFuncSetAttribute(attn_decode_kernel<HD, ST>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess)
             return (int)cudaGetLastError();
         configured = true;
     }
     dim3 grid(p.nkv * p.qgroups, S, splits);
-    attn_decode_kernel<HD><<<grid, NWARPS * 32, SMEM, stream>>>(p);
-    return CW_LAUNCH_CHECK();
+    return cw_launch(attn_decode_kernel<HD, ST>, grid, dim3(NWARPS * 32), SMEM, stream, 1, p);
+}
+
+template <int HD>
+static int launch_decode(const DecodeParams& p, int S, int splits, cudaStream_t stream) {
+    // few CTAs: a whole split in flight per CTA; many CTAs: two CTAs per SM instead
+    const long long ctas = (long long)p.nkv * p.qgroups * S * splits;
+    if (HD <= 128 && ctas <= 2 * 148) return launch_decode_st<HD, (HD <= 128 ? 4 : 2)>(p, S, splits, stream);
+    return launch_decode_st<HD, 2>(p, S, splits, stream);
 }
 
 // Workspace a call needs: part_o floats, part_lse floats, counters.

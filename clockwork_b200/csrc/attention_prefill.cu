@@ -35,6 +35,8 @@ attn_prefill_kernel(const PrefillParams p) {
     bf16* Ks = Qs + QT * LD;         // [2][TILE][LD]
     bf16* Vs = Ks + 2 * TILE * LD;   // [2][TILE][LD]
 
+    pdl_launch_dependents();
+    pdl_wait();
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g = lane >> 2, t = lane & 3;
     const int s = p.item_seq[blockIdx.x], q0 = p.item_q0[blockIdx.x];
@@ -218,8 +220,7 @@ static int launch_prefill(const PrefillParams& p, int items, cudaStream_t stream
         configured = true;
     }
     dim3 grid(items, p.nh);
-    attn_prefill_kernel<HD><<<grid, NWARPS * 32, SMEM, stream>>>(p);
-    return CW_LAUNCH_CHECK();
+    return cw_launch(attn_prefill_kernel<HD>, grid, dim3(NWARPS * 32), SMEM, stream, 1, p);
 }
 
 // q: [N, >= nh*hd] rows of the flat batch; out: [N, nh*hd]; item_seq/item_q0: one entry per 64

@@ -88,3 +88,45 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
 }
 
 #define CW_LAUNCH_CHECK() ((int)cudaGetLastError())
+
+// ---- programmatic dependent launch --------------------------------------------------------------
+// Every kernel of the step is launched with the "programmatic stream serialization" attribute:
+// it may be scheduled while its predecessor in the stream is still running.  The contract that
+// keeps this correct: a kernel calls pdl_wait() before it reads anything a predecessor wrote and
+// before it writes global memory at all; what it does before that (set-up, prefetching weights,
+// which no kernel of the step writes) overlaps the predecessor's tail.  pdl_launch_dependents()
+// at the top lets the successor do the same.  Both are no-ops in a kernel launched the plain way.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+// 1: launch with the attribute (default); 0: plain launches.  Set through cw_set_pdl().
+extern "C" int cw_pdl_enabled();
+
+template <typename... KArgs, typename... Args>
+static inline int cw_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                            unsigned cluster_z, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    int n = 0;
+    if (cw_pdl_enabled()) {
+        attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[n].val.programmaticStreamSerializationAllowed = 1;
+        ++n;
+    }
+    if (cluster_z > 1) {
+        attr[n].id = cudaLaunchAttributeClusterDimension;
+        attr[n].val.clusterDim.x = 1;
+        attr[n].val.clusterDim.y = 1;
+        attr[n].val.clusterDim.z = cluster_z;
+        ++n;
+    }
+    cfg.attrs = attr;
+    cfg.numAttrs = n;
+    const cudaError_t err = cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+    if (err != cudaSuccess) return (int)err;
+    return (int)cudaGetLastError();
+}

@@ -9,6 +9,8 @@
 template <typename T>
 __global__ void embed_kernel(float* __restrict__ out, const T* __restrict__ table,
                              const int* __restrict__ ids, int H, int V, int* status) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int row = blockIdx.x;
     const int id = ids[row];
     float* o = out + (size_t)row * H;
@@ -27,12 +29,10 @@ extern "C" int cw_embed(float* out, const void* table, const int* ids, int N, in
     if (N < 0 || H <= 0 || V <= 0) return CW_ERR_BAD_SIZE;
     const int threads = H >= 1024 ? 256 : 128;
     if (dtype == 0)
-        embed_kernel<float><<<N, threads, 0, stream>>>(out, (const float*)table, ids, H, V, status);
-    else if (dtype == 1)
-        embed_kernel<bf16><<<N, threads, 0, stream>>>(out, (const bf16*)table, ids, H, V, status);
-    else
-        return CW_ERR_BAD_DTYPE;
-    return CW_LAUNCH_CHECK();
+        return cw_launch(embed_kernel<float>, dim3(N), dim3(threads), 0, stream, 1, out, (const float*)table, ids, H, V, status);
+    if (dtype == 1)
+        return cw_launch(embed_kernel<bf16>, dim3(N), dim3(threads), 0, stream, 1, out, (const bf16*)table, ids, H, V, status);
+    return CW_ERR_BAD_DTYPE;
 }
 
 // resid[row] (+= delta[row]); out[r] = weight * (x * rsqrt(mean(x^2)+eps)).
@@ -43,6 +43,8 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const T* __restric
                                    const int* __restrict__ rows, int num_resid_rows, float eps,
                                    int H, int* status) {
     __shared__ float scratch[33];
+    pdl_launch_dependents();
+    pdl_wait();
     const int r = blockIdx.x;
     int src_row = r;
     if (rows != nullptr) {
@@ -78,14 +80,12 @@ extern "C" int cw_add_rmsnorm(float* resid, const void* delta, const float* weig
     if (rows != nullptr && delta != nullptr) return CW_ERR_UNSUPPORTED;
     const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
     if (dtype == 0)
-        add_rmsnorm_kernel<float><<<num_out_rows, threads, 0, stream>>>(
-            resid, (const float*)delta, weight, (float*)out, rows, num_resid_rows, eps, H, status);
-    else if (dtype == 1)
-        add_rmsnorm_kernel<bf16><<<num_out_rows, threads, 0, stream>>>(
-            resid, (const bf16*)delta, weight, (bf16*)out, rows, num_resid_rows, eps, H, status);
-    else
-        return CW_ERR_BAD_DTYPE;
-    return CW_LAUNCH_CHECK();
+        return cw_launch(add_rmsnorm_kernel<float>, dim3(num_out_rows), dim3(threads), 0, stream, 1, resid,
+                         (const float*)delta, weight, (float*)out, rows, num_resid_rows, eps, H, status);
+    if (dtype == 1)
+        return cw_launch(add_rmsnorm_kernel<bf16>, dim3(num_out_rows), dim3(threads), 0, stream, 1, resid,
+                         (const bf16*)delta, weight, (bf16*)out, rows, num_resid_rows, eps, H, status);
+    return CW_ERR_BAD_DTYPE;
 }
 
 // out = silu(gate) * up, gate and up being the two halves of each row of `gate_up` [N, 2*I]
@@ -139,3 +139,7 @@ extern "C" int cw_add_to_residual(float* resid, const void* delta, int N, int H,
         return CW_ERR_BAD_DTYPE;
     return CW_LAUNCH_CHECK();
 }
+
+static int g_pdl = 1;
+extern "C" int cw_pdl_enabled() { return g_pdl; }
+extern "C" int cw_set_pdl(int on) { g_pdl = on ? 1 : 0; return CW_OK; }

@@ -8,9 +8,11 @@
 // tile of BN tokens, so the instruction is M=128 x N=BN x K=16 with both operands K-major in
 // shared memory (128-byte swizzle) and D[feature, token] in TMEM.  This one shape serves decode
 // (BN = 16..64 tokens, the step is a stream of weight tiles from HBM) and prefill (BN = 128/256).
-// When the grid would leave SMs idle the K dimension is split over blockIdx.z; partial tiles go
-// through a float32 workspace and the CTA that finishes last adds them in split order and runs
-// the epilogue, so the result does not depend on which CTA came last.
+// When the grid would leave SMs idle the K dimension is split over blockIdx.z and the CTAs of one
+// tile are launched as a thread-block cluster: each stages its partial accumulator in its own
+// shared memory, and after a cluster barrier every CTA finishes a slice of the tile's columns,
+// adding the partials of all ranks in rank order through distributed shared memory.  No global
+// scratch, no atomics, and the result does not depend on which CTA finished first.
 //
 // Warp roles (128 threads): warp 0 lane 0 issues TMA loads, warp 1 lane 0 issues the MMAs, warp 2
 // allocates and frees TMEM; all four warps run the epilogue (warp w reads TMEM lanes 32w..32w+31).
@@ -114,6 +116,23 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* v) {
     for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
 }
 
+__device__ __forceinline__ uint32_t cluster_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// One float from the shared memory of the CTA with the given rank in this cluster.
+__device__ __forceinline__ float ld_dsmem(uint32_t local_addr, uint32_t rank) {
+    uint32_t remote;
+    float v;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+    return v;
+}
+
 // Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes (64 bf16) with the
 // 128-byte swizzle: 8-row groups are 1024 bytes apart (stride byte offset), the leading byte offset
 // is not used by swizzled K-major layouts (encoded 1), version 1, layout type 2 (SWIZZLE_128B).
@@ -141,8 +160,6 @@ struct GemmParams {
     int splits;
     const float* bias;    // [N] or null
     void* C;
-    float* workspace;     // [tiles][splits][columns][128] float32 partial tiles (splits > 1)
-    int* counters;        // [tiles] arrival counters, zero between launches
     int* status;
 };
 
@@ -151,11 +168,10 @@ struct Cfg {
     static constexpr int A_BYTES = BM * BK * 2;                     // 16 KB
     static constexpr int B_BYTES = BN * BK * 2;
     static constexpr int STAGE_BYTES = A_BYTES * (SWIGLU ? 2 : 1) + B_BYTES;
-    // small token tiles (decode): few stages, so that two CTAs share an SM and one CTA's set-up
-    // and epilogue hide behind the other's stream of weight tiles
+    // as many stages as fit (at most 8): a decode CTA is alone on its SM and keeps that many weight
+    // tiles in flight from HBM
     static constexpr int MAX_STAGES = (200 * 1024) / STAGE_BYTES;
-    static constexpr int WANT_STAGES = BN <= 32 ? 5 : (BN <= 64 ? 4 : 8);
-    static constexpr int STAGES = MAX_STAGES > WANT_STAGES ? WANT_STAGES : MAX_STAGES;
+    static constexpr int STAGES = MAX_STAGES > 8 ? 8 : MAX_STAGES;
     static constexpr int ACC_COLS = BN * (SWIGLU ? 2 : 1);
     static constexpr int TMEM_COLS = ACC_COLS <= 32 ? 32 : (ACC_COLS <= 64 ? 64 : (ACC_COLS <= 128 ? 128 : (ACC_COLS <= 256 ? 256 : 512)));
     static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment*/ + 256 /*barriers*/;
@@ -172,8 +188,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     // bars[0..S): full, bars[S..2S): empty, bars[2S]: accumulator ready
     uint32_t* tmem_slot = (uint32_t*)(bars + 2 * C::STAGES + 1);
     volatile int* give_up = (volatile int*)(tmem_slot + 1);
-    int* last_flag = (int*)(tmem_slot + 2);
 
+    pdl_launch_dependents();
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int m0 = blockIdx.x * BM, n0 = blockIdx.y * BN, split = blockIdx.z;
     const int kb0 = split * p.kb_per_split;
@@ -189,7 +205,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         }
         mbar_init(acc_bar, 1);
         *give_up = 0;
-        *last_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
@@ -202,7 +217,25 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     int issued = 0;
     if (warp == 0 && lane == 0) {
         // ---- TMA producer ----------------------------------------------------------------------
-        for (int i = 0; i < my_kb; ++i) {
+        // Weight tiles of the first stages go out before the wait on the preceding kernel: no
+        // kernel of the step writes weights, so they stream while that kernel finishes.  The
+        // activation tiles (which it may still be writing) follow after the wait.
+        const int early = min(my_kb, C::STAGES);
+        for (int i = 0; i < early; ++i) {
+            const uint32_t a_dst = smem_u32(smem + i * C::STAGE_BYTES);
+            const uint32_t bar = full0 + 8 * i;
+            mbar_expect_tx(bar, C::STAGE_BYTES);
+            const int kx = (kb0 + i) * BK;
+            tma_load_2d(a_dst, &map_w, kx, m0, bar);
+            if (SWIGLU) tma_load_2d(a_dst + C::A_BYTES, &map_w2, kx, m0, bar);
+        }
+        pdl_wait();
+        for (int i = 0; i < early; ++i) {
+            const uint32_t a_dst = smem_u32(smem + i * C::STAGE_BYTES);
+            tma_load_2d(a_dst + C::A_BYTES * (SWIGLU ? 2 : 1), &map_x, (kb0 + i) * BK, n0, full0 + 8 * i);
+            ++issued;
+        }
+        for (int i = early; i < my_kb; ++i) {
             const int s = i % C::STAGES;
             const uint32_t parity = ((i / C::STAGES) & 1) ^ 1;
             if (!mbar_wait(empty0 + 8 * s, parity, give_up)) break;
@@ -242,82 +275,99 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     __syncwarp();
     // ---- epilogue: every thread owns one output feature (TMEM lane) -----------------------------
     const bool acc_ready = mbar_wait(acc_bar, 0, give_up);
+    pdl_wait();  // the epilogue reads and writes what preceding kernels wrote
     tc_fence_after();
     __syncwarp();
     const int row = warp * 32 + lane;  // feature within the tile
     const int f = m0 + row;
     const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16);
-    const int tile = blockIdx.y * gridDim.x + blockIdx.x;
-    bool run_epilogue = acc_ready;
-    if (acc_ready && p.splits > 1) {
-        float* ws = p.workspace + ((size_t)tile * p.splits + split) * C::ACC_COLS * BM;
+    // With the inner dimension split, the CTAs of one tile form a cluster.  Each stages its partial
+    // accumulator in its own shared memory (the operand stages are free by now), the cluster
+    // synchronises, and every CTA then finishes a slice of the tile's columns: it adds the partials
+    // of all ranks in rank order, read through distributed shared memory, and runs the epilogue.
+    float* stage = (float*)smem;  // [ACC_COLS][BM]
+    const uint32_t stage_addr = smem_u32(stage);
+    int c_begin = 0, c_end = BN;
+    if (p.splits > 1) {
         for (int c = 0; c < C::ACC_COLS; c += 16) {
             float v[16];
-            tmem_ld16(taddr + c, v);
-#pragma unroll
-            for (int j = 0; j < 16; ++j) ws[(size_t)(c + j) * BM + row] = v[j];
-        }
-        __threadfence();
-        __syncthreads();
-        if (tid == 0) {
-            const int prev = atomicAdd(&p.counters[tile], 1);
-            if (prev == p.splits - 1) {
-                p.counters[tile] = 0;  // ready for the next launch
-                *last_flag = 1;
-            }
-        }
-        __syncthreads();
-        run_epilogue = *last_flag != 0;
-        if (run_epilogue) __threadfence();
-    }
-    if (run_epilogue) {
-        const float bias = (p.bias != nullptr && f < p.N) ? p.bias[f] : 0.f;
-        const float* ws = p.workspace + (size_t)tile * p.splits * C::ACC_COLS * BM;
-        for (int c = 0; c < BN; c += 16) {
-            float g[16], u[16];
-            if (p.splits == 1) {
-                tmem_ld16(taddr + c, g);
-                if (SWIGLU) tmem_ld16(taddr + BN + c, u);
+            if (acc_ready) {
+                tmem_ld16(taddr + c, v);
             } else {
 #pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                    float sg = 0.f, su = 0.f;
-                    for (int s = 0; s < p.splits; ++s) {
-                        const float* part = ws + (size_t)s * C::ACC_COLS * BM;
-                        sg += part[(size_t)(c + j) * BM + row];
-                        if (SWIGLU) su += part[(size_t)(BN + c + j) * BM + row];
-                    }
-                    g[j] = sg;
-                    u[j] = su;
+                for (int j = 0; j < 16; ++j) v[j] = 0.f;
+            }
+#pragma unroll
+            for (int j = 0; j < 16; ++j) stage[(c + j) * BM + row] = v[j];
+        }
+        cluster_sync();
+        const int per = (BN + p.splits - 1) / p.splits;
+        c_begin = min(BN, (int)cluster_rank() * per);
+        c_end = min(BN, c_begin + per);
+    }
+    const float bias = (p.bias != nullptr && f < p.N) ? p.bias[f] : 0.f;
+    for (int c = c_begin; c < c_end && (acc_ready || p.splits > 1); c += 16) {
+        const int ncols = min(16, c_end - c);
+        float g[16], u[16];
+        if (p.splits == 1) {
+            tmem_ld16(taddr + c, g);
+            if (SWIGLU) tmem_ld16(taddr + BN + c, u);
+        } else {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) g[j] = u[j] = 0.f;
+            // eight columns of two ranks at a time: up to 16 (32) remote loads in flight
+#pragma unroll
+            for (int j0 = 0; j0 < 16; j0 += 8) {
+                if (j0 >= ncols) break;
+                for (int s0 = 0; s0 < p.splits; s0 += 2) {
+                    float vg[2][8], vu[2][8];
+#pragma unroll
+                    for (int ds = 0; ds < 2; ++ds)
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            const bool in = s0 + ds < p.splits && j0 + j < ncols;
+                            const uint32_t a = stage_addr + (uint32_t)(((c + j0 + j) * BM + row) * 4);
+                            vg[ds][j] = in ? ld_dsmem(a, s0 + ds) : 0.f;
+                            if (SWIGLU) vu[ds][j] = in ? ld_dsmem(a + (uint32_t)(BN * BM * 4), s0 + ds) : 0.f;
+                        }
+#pragma unroll
+                    for (int ds = 0; ds < 2; ++ds)  // rank order
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            g[j0 + j] += vg[ds][j];
+                            if (SWIGLU) u[j0 + j] += vu[ds][j];
+                        }
                 }
             }
-            if (f < p.N) {
-                const int t_base = n0 + c;
-                float* c32 = (float*)p.C + (size_t)t_base * p.ldc + f;
-                bf16* c16 = (bf16*)p.C + (size_t)t_base * p.ldc + f;
-                float old[16];
-                if (!SWIGLU && p.epilogue == 1) {
-                    // all 16 loads first: issued back to back instead of one load-add-store chain each
+        }
+        if (f < p.N) {
+            const int t_base = n0 + c;
+            float* c32 = (float*)p.C + (size_t)t_base * p.ldc + f;
+            bf16* c16 = (bf16*)p.C + (size_t)t_base * p.ldc + f;
+            float old[16];
+            if (!SWIGLU && p.epilogue == 1) {
+                // all loads first: issued back to back instead of one load-add-store chain each
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) old[j] = (t_base + j < p.T) ? c32[(size_t)j * p.ldc] : 0.f;
-                }
+                for (int j = 0; j < 16; ++j)
+                    old[j] = (j < ncols && t_base + j < p.T) ? c32[(size_t)j * p.ldc] : 0.f;
+            }
 #pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                    if (t_base + j >= p.T) break;
-                    const float v = g[j] + bias;
-                    if (SWIGLU) {
-                        c16[(size_t)j * p.ldc] = __float2bfloat16_rn(v / (1.0f + expf(-v)) * u[j]);
-                    } else if (p.epilogue == 0) {
-                        c16[(size_t)j * p.ldc] = __float2bfloat16_rn(v);
-                    } else if (p.epilogue == 1) {
-                        c32[(size_t)j * p.ldc] = old[j] + v;
-                    } else {
-                        c32[(size_t)j * p.ldc] = v;
-                    }
+            for (int j = 0; j < 16; ++j) {
+                if (j >= ncols || t_base + j >= p.T) break;
+                const float v = g[j] + bias;
+                if (SWIGLU) {
+                    c16[(size_t)j * p.ldc] = __float2bfloat16_rn(v / (1.0f + expf(-v)) * u[j]);
+                } else if (p.epilogue == 0) {
+                    c16[(size_t)j * p.ldc] = __float2bfloat16_rn(v);
+                } else if (p.epilogue == 1) {
+                    c32[(size_t)j * p.ldc] = old[j] + v;
+                } else {
+                    c32[(size_t)j * p.ldc] = v;
                 }
             }
         }
     }
+    if (p.splits > 1) cluster_sync();  // peers may still be reading this CTA's staged partials
     // ---- teardown ---------------------------------------------------------------------------------
     if (*give_up) {
         if (tid == 0) cw_report(p.status, CW_ST_WAIT_TIMEOUT, blockIdx.x, blockIdx.z);
@@ -369,23 +419,26 @@ static int make_map(CUtensorMap* map, const void* ptr, int rows, int K, long lon
 }
 
 struct Plan {
-    int bn, splits, kb_per_split, tiles, acc_cols;
+    int bn, splits, kb_per_split, tiles;
 };
+
+#define MAX_SPLITS 8  // the portable cluster size
 
 static Plan make_plan(int T, int N, int K, bool swiglu, int sm_count) {
     Plan pl;
     const int cap = swiglu ? 128 : 256;
     pl.bn = T <= 16 ? 16 : (T <= 32 ? 32 : (T <= 64 ? 64 : (T <= 128 ? 128 : cap)));
-    pl.acc_cols = pl.bn * (swiglu ? 2 : 1);
     pl.tiles = ((N + BM - 1) / BM) * ((T + pl.bn - 1) / pl.bn);
     const int num_kb = (K + BK - 1) / BK;
     int splits = 1;
-    if (pl.tiles < sm_count) {
-        // enough CTAs to give every SM work, each with at least four k-blocks to stream
-        splits = (2 * sm_count + pl.tiles - 1) / pl.tiles;
+    if (pl.tiles * 2 <= sm_count) {
+        // One wave: as many CTAs as SMs at most, each with as much of K as possible.  A CTA costs a
+        // few microseconds of set-up and epilogue whatever it streams, so fewer, longer CTAs win
+        // as long as every SM has one.
+        splits = sm_count / pl.tiles;
         const int max_by_k = num_kb / 4 > 0 ? num_kb / 4 : 1;
         if (splits > max_by_k) splits = max_by_k;
-        if (splits > 16) splits = 16;
+        if (splits > MAX_SPLITS) splits = MAX_SPLITS;
         if (splits < 1) splits = 1;
     }
     pl.kb_per_split = (num_kb + splits - 1) / splits;
@@ -397,6 +450,7 @@ template <int BN, bool SWIGLU>
 static int launch(const CUtensorMap& mw, const CUtensorMap& mw2, const CUtensorMap& mx, const GemmParams& p,
                   dim3 grid, cudaStream_t stream) {
     using C = Cfg<BN, SWIGLU>;
+    static_assert(C::ACC_COLS * BM * 4 <= C::STAGES * C::STAGE_BYTES, "staged partials must fit in the operand stages");
     static bool configured = false;
     if (!configured) {
         if (cudaFuncSetAttribute(gemm_tc_kernel<BN, SWIGLU>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -404,16 +458,15 @@ static int launch(const CUtensorMap& mw, const CUtensorMap& mw2, const CUtensorM
             return (int)cudaGetLastError();
         configured = true;
     }
-    gemm_tc_kernel<BN, SWIGLU><<<grid, THREADS, C::SMEM_BYTES, stream>>>(mw, mw2, mx, p);
-    return CW_LAUNCH_CHECK();
+    return cw_launch(gemm_tc_kernel<BN, SWIGLU>, grid, dim3(THREADS), C::SMEM_BYTES, stream, grid.z, mw, mw2, mx, p);
 }
 
-// Bytes of workspace and number of counters a call may need (0 when it will not split).
-extern "C" int cw_gemm_tc_workspace(int T, int N, int K, int swiglu, int sm_count, long long* bytes,
-                                    int* counters) {
+// How a call would be tiled: token tile, splits of the inner dimension (= cluster size), CTAs.
+extern "C" int cw_gemm_tc_plan(int T, int N, int K, int swiglu, int sm_count, int* bn, int* splits, int* ctas) {
     const Plan pl = make_plan(T, N, K, swiglu != 0, sm_count);
-    *bytes = pl.splits > 1 ? (long long)pl.tiles * pl.splits * pl.acc_cols * BM * 4 : 0;
-    *counters = pl.splits > 1 ? pl.tiles : 0;
+    *bn = pl.bn;
+    *splits = pl.splits;
+    *ctas = pl.tiles * pl.splits;
     return CW_OK;
 }
 
@@ -421,9 +474,8 @@ extern "C" int cw_gemm_tc_workspace(int T, int N, int K, int swiglu, int sm_coun
 // and all bases 16-byte aligned (TMA); returns CW_ERR_UNSUPPORTED otherwise so the caller can
 // use the plain kernel.
 extern "C" int cw_gemm_tc(const void* X, const void* W, const void* W2, const float* bias, void* C, int T,
-                          int N, int K, int ldx, int ldc, int epilogue, void* workspace,
-                          long long workspace_bytes, int* counters, int num_counters, int sm_count,
-                          int* status, cudaStream_t stream) {
+                          int N, int K, int ldx, int ldc, int epilogue, int sm_count, int* status,
+                          cudaStream_t stream) {
     if (T == 0 || N == 0) return CW_OK;
     if (T < 0 || N < 0 || K <= 0 || ldx < K || ldc < N) return CW_ERR_BAD_SIZE;
     if (epilogue < 0 || epilogue > 2) return CW_ERR_UNSUPPORTED;
@@ -432,11 +484,6 @@ extern "C" int cw_gemm_tc(const void* X, const void* W, const void* W2, const fl
     if (load_encode() != 0) return CW_ERR_UNSUPPORTED;
     const bool swiglu = W2 != nullptr;
     const Plan pl = make_plan(T, N, K, swiglu, sm_count);
-    if (pl.splits > 1) {
-        const long long need = (long long)pl.tiles * pl.splits * pl.acc_cols * BM * 4;
-        if (workspace == nullptr || counters == nullptr || workspace_bytes < need || num_counters < pl.tiles)
-            return CW_ERR_BAD_SIZE;
-    }
     CUtensorMap mw, mw2, mx;
     if (make_map(&mw, W, N, K, K, BM) != 0) return CW_ERR_UNSUPPORTED;
     if (make_map(&mw2, swiglu ? W2 : W, N, K, K, BM) != 0) return CW_ERR_UNSUPPORTED;
@@ -444,7 +491,7 @@ extern "C" int cw_gemm_tc(const void* X, const void* W, const void* W2, const fl
     GemmParams p;
     p.T = T; p.N = N; p.K = K; p.ldc = ldc; p.epilogue = epilogue;
     p.num_kb = (K + BK - 1) / BK; p.kb_per_split = pl.kb_per_split; p.splits = pl.splits;
-    p.bias = bias; p.C = C; p.workspace = (float*)workspace; p.counters = counters; p.status = status;
+    p.bias = bias; p.C = C; p.status = status;
     dim3 grid((N + BM - 1) / BM, (T + pl.bn - 1) / pl.bn, pl.splits);
     if (grid.y > 65535) return CW_ERR_BAD_SIZE;
 #define CW_CASE(bn)                                                                       \

@@ -18,6 +18,8 @@ __global__ void rope_store_kernel(T* __restrict__ qkv, const int* __restrict__ p
                                   T* __restrict__ k_cache, T* __restrict__ v_cache, int nh, int nkv,
                                   int hd, int rotary_dim, int num_slots, int write_cache,
                                   int* status) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int t = blockIdx.x;
     const int head = blockIdx.y;
     const int half = rotary_dim >> 1;
@@ -74,16 +76,14 @@ extern "C" int cw_rope_store(void* qkv, const int* positions, const int* slots,
     int threads = 32;
     while (threads < hd / 2 && threads < 128) threads <<= 1;
     if (dtype == 0)
-        rope_store_kernel<float><<<grid, threads, 0, stream>>>(
-            (float*)qkv, positions, slots, inv_freq, (float*)k_cache, (float*)v_cache, nh, nkv, hd,
-            rotary_dim, num_slots, write_cache, status);
-    else if (dtype == 1)
-        rope_store_kernel<bf16><<<grid, threads, 0, stream>>>(
-            (bf16*)qkv, positions, slots, inv_freq, (bf16*)k_cache, (bf16*)v_cache, nh, nkv, hd,
-            rotary_dim, num_slots, write_cache, status);
-    else
-        return CW_ERR_BAD_DTYPE;
-    return CW_LAUNCH_CHECK();
+        return cw_launch(rope_store_kernel<float>, grid, dim3(threads), 0, stream, 1, (float*)qkv, positions, slots,
+                         inv_freq, (float*)k_cache, (float*)v_cache, nh, nkv, hd, rotary_dim, num_slots,
+                         write_cache, status);
+    if (dtype == 1)
+        return cw_launch(rope_store_kernel<bf16>, grid, dim3(threads), 0, stream, 1, (bf16*)qkv, positions, slots,
+                         inv_freq, (bf16*)k_cache, (bf16*)v_cache, nh, nkv, hd, rotary_dim, num_slots,
+                         write_cache, status);
+    return CW_ERR_BAD_DTYPE;
 }
 
 // cache: [planes, num_pages, page_elems]; copies page src->dst in every plane (a plane is one

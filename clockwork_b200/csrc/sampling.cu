@@ -24,6 +24,8 @@ __global__ void __launch_bounds__(ST)
 argmax_kernel(const float* __restrict__ logits, int* __restrict__ out, int V, size_t row_stride) {
     __shared__ float bv[32];
     __shared__ int bi[32];
+    pdl_launch_dependents();
+    pdl_wait();
     const float* row = logits + (size_t)blockIdx.x * row_stride;
     float best = -INFINITY;
     int idx = 0x7fffffff;
@@ -57,8 +59,7 @@ extern "C" int cw_argmax(const float* logits, int* out, int R, int V, long long 
                          cudaStream_t stream) {
     if (R == 0) return CW_OK;
     if (R < 0 || V <= 0 || row_stride < V) return CW_ERR_BAD_SIZE;
-    argmax_kernel<<<R, ST, 0, stream>>>(logits, out, V, (size_t)row_stride);
-    return CW_LAUNCH_CHECK();
+    return cw_launch(argmax_kernel, dim3(R), dim3(ST), 0, stream, 1, logits, out, V, (size_t)row_stride);
 }
 
 __device__ __forceinline__ float block_sum_1024(float v, float* scratch) { return block_sum(v, scratch); }
@@ -70,6 +71,8 @@ sample_kernel(const float* __restrict__ logits, const float* __restrict__ temper
     __shared__ float scratch[33];
     __shared__ float warp_tot[32];
     __shared__ int first_thread, last_thread;
+    pdl_launch_dependents();
+    pdl_wait();
     const int r = blockIdx.x, tid = threadIdx.x;
     const float* row = logits + (size_t)r * row_stride;
     const float temp = temperature[r];
@@ -187,7 +190,6 @@ extern "C" int cw_sample(const float* logits, const float* temperature, const in
                          long long row_stride, cudaStream_t stream) {
     if (R == 0) return CW_OK;
     if (R < 0 || V <= 0 || row_stride < V) return CW_ERR_BAD_SIZE;
-    sample_kernel<<<R, ST, 0, stream>>>(logits, temperature, top_k, top_p, uniform, out, V,
-                                        (size_t)row_stride);
-    return CW_LAUNCH_CHECK();
+    return cw_launch(sample_kernel, dim3(R), dim3(ST), 0, stream, 1, logits, temperature, top_k, top_p, uniform, out, V,
+                     (size_t)row_stride);
 }

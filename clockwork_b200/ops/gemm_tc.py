@@ -1,8 +1,7 @@
 """Python face of the tcgen05 matrix-product kernel (``csrc/gemm_tc.cu``).
 
-The kernel may split the inner dimension over several CTAs; the partial tiles then go through a
-float32 workspace owned by this module (one per device, allocated once, so that a captured CUDA
-graph can replay the calls)."""
+The kernel may split the inner dimension over the CTAs of a thread-block cluster; the partial tiles
+meet in distributed shared memory, so a call needs no scratch memory."""
 
 from __future__ import annotations
 
@@ -12,9 +11,6 @@ import torch
 
 from . import EPILOGUE_STORE, _need, _ptr, _stream, gemm as gemm_dispatch, new_status
 from .library import check, library
-
-WORKSPACE_BYTES = 64 << 20
-NUM_COUNTERS = 8192
 
 _state: dict[int, dict] = {}
 _configured = False
@@ -26,10 +22,10 @@ def _configure() -> None:
         return
     lib = library()
     P, I, LL = c_void_p, c_int, c_longlong
-    lib.cw_gemm_tc.argtypes = [P, P, P, P, P, I, I, I, I, I, I, P, LL, P, I, I, P, P]
+    lib.cw_gemm_tc.argtypes = [P, P, P, P, P, I, I, I, I, I, I, I, P, P]
     lib.cw_gemm_tc.restype = c_int
-    lib.cw_gemm_tc_workspace.argtypes = [I, I, I, I, I, POINTER(c_longlong), POINTER(c_int)]
-    lib.cw_gemm_tc_workspace.restype = c_int
+    lib.cw_gemm_tc_plan.argtypes = [I, I, I, I, I, POINTER(c_int), POINTER(c_int), POINTER(c_int)]
+    lib.cw_gemm_tc_plan.restype = c_int
     _configured = True
 
 
@@ -38,8 +34,6 @@ def _device_state(device: torch.device) -> dict:
     st = _state.get(index)
     if st is None:
         st = {
-            "workspace": torch.empty(WORKSPACE_BYTES, dtype=torch.uint8, device=device),
-            "counters": torch.zeros(NUM_COUNTERS, dtype=torch.int32, device=device),
             "status": new_status(device),
             "sms": torch.cuda.get_device_properties(device).multi_processor_count,
         }
@@ -51,11 +45,13 @@ def status(device) -> torch.Tensor:
     return _device_state(torch.device(device))["status"]
 
 
-def workspace_need(t: int, n: int, k: int, swiglu: bool, device) -> tuple[int, int]:
+def plan(t: int, n: int, k: int, swiglu: bool, device) -> dict:
+    """How a call would be tiled: token tile, splits of the inner dimension (cluster size), CTAs."""
     _configure()
-    b, c = c_longlong(0), c_int(0)
-    library().cw_gemm_tc_workspace(t, n, k, 1 if swiglu else 0, _device_state(torch.device(device))["sms"], byref(b), byref(c))
-    return b.value, c.value
+    bn, splits, ctas = c_int(0), c_int(0), c_int(0)
+    library().cw_gemm_tc_plan(t, n, k, 1 if swiglu else 0, _device_state(torch.device(device))["sms"],
+                              byref(bn), byref(splits), byref(ctas))
+    return {"token_tile": bn.value, "splits": splits.value, "ctas": ctas.value}
 
 
 def accepts(x: torch.Tensor, w: torch.Tensor) -> bool:
@@ -65,11 +61,7 @@ def accepts(x: torch.Tensor, w: torch.Tensor) -> bool:
     k = x.shape[1]
     if k % 8 or x.stride(1) != 1 or (x.shape[0] > 1 and x.stride(0) % 8) or x.data_ptr() % 16 or w.data_ptr() % 16:
         return False
-    if not w.is_contiguous():
-        return False
-    need, counters = workspace_need(x.shape[0], w.shape[0], k, False, x.device)
-    need2, counters2 = workspace_need(x.shape[0], w.shape[0], k, True, x.device)
-    return max(need, need2) <= WORKSPACE_BYTES and max(counters, counters2) <= NUM_COUNTERS
+    return w.is_contiguous()
 
 
 def _run(x, w, w2, bias, out, epilogue) -> None:
@@ -81,8 +73,7 @@ def _run(x, w, w2, bias, out, epilogue) -> None:
     if ldx % 8:
         ldx = k
     check(library().cw_gemm_tc(_ptr(x), _ptr(w), _ptr(w2), _ptr(bias), _ptr(out), t, n, k, ldx, out.stride(0), epilogue,
-                               _ptr(st["workspace"]), WORKSPACE_BYTES, _ptr(st["counters"]), NUM_COUNTERS, st["sms"],
-                               _ptr(st["status"]), _stream()), "gemm_tc")
+                               st["sms"], _ptr(st["status"]), _stream()), "gemm_tc")
 
 
 def gemm(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None, *, out: torch.Tensor | None = None,

@@ -333,7 +333,7 @@ def test_gemm_tc_against_float64(ops, gemm_tc, t, n, k):
     acc = base.to(DEV).clone()
     gemm_tc.gemm(xd, wd, None, out=acc, epilogue=ops.EPILOGUE_ADD_F32)
     torch.testing.assert_close(acc.cpu(), base + bf16_product(x, w), rtol=1e-4, atol=1e-5 * scale)
-    # twice in a row: the split counters are back at zero after a call
+    # twice in a row gives the same bits
     again = gemm_tc.gemm(xd, wd, bd, epilogue=ops.EPILOGUE_STORE_F32)
     assert torch.equal(again, out32)
     ops.raise_on_status(gemm_tc.status(DEV))
