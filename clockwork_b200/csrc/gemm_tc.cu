@@ -116,6 +116,18 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* v) {
     for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
 }
 
+// Tile [rows][128] in shared memory -> global, through the tensor map of C; rows and columns past
+// the matrix's edge are dropped by the hardware.  `add`: float32 reduce-add instead of a store.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t src, int x, int y, bool add) {
+    if (add)
+        asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.bulk_group [%0, {%2, %3}], [%1];"
+                     ::"l"(map), "r"(src), "r"(x), "r"(y) : "memory");
+    else
+        asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+                     ::"l"(map), "r"(src), "r"(x), "r"(y) : "memory");
+    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+    asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");  // shared memory may be reused / freed
+}
 __device__ __forceinline__ uint32_t cluster_rank() {
     uint32_t r;
     asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
@@ -158,6 +170,7 @@ struct GemmParams {
     int num_kb;           // ceil(K / 64)
     int kb_per_split;     // k-blocks per blockIdx.z
     int splits;
+    int tma_store;        // 1: unsplit tiles leave through shared memory and one TMA store / reduce-add
     const float* bias;    // [N] or null
     void* C;
     int* status;
@@ -180,7 +193,8 @@ struct Cfg {
 template <int BN, bool SWIGLU>
 __global__ void __launch_bounds__(THREADS)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_w2,
-               const __grid_constant__ CUtensorMap map_x, const GemmParams p) {
+               const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_c,
+               const GemmParams p) {
     using C = Cfg<BN, SWIGLU>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -306,6 +320,30 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         c_end = min(BN, c_begin + per);
     }
     const float bias = (p.bias != nullptr && f < p.N) ? p.bias[f] : 0.f;
+    if (p.splits == 1 && p.tma_store && acc_ready) {
+        // The whole tile goes to shared memory as [token][feature] in C's type, then leaves in one
+        // TMA store (or float32 reduce-add into the residual): full-line writes, no read-modify-write
+        // round trips from the SM, and no per-element address arithmetic.
+        const bool wide = !SWIGLU && p.epilogue != 0;  // float32 C
+        for (int c = 0; c < BN; c += 16) {
+            float g[16], u[16];
+            tmem_ld16(taddr + c, g);
+            if (SWIGLU) tmem_ld16(taddr + BN + c, u);
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+                float v = g[j] + bias;
+                if (SWIGLU) v = __fdividef(v, 1.0f + __expf(-v)) * u[j];
+                if (wide)
+                    stage[(c + j) * BM + row] = v;
+                else
+                    ((bf16*)stage)[(c + j) * BM + row] = __float2bfloat16_rn(v);
+            }
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes -> TMA
+        __syncthreads();
+        if (tid == 0) tma_store_2d(&map_c, stage_addr, m0, n0, !SWIGLU && p.epilogue == 1);
+        c_begin = c_end = 0;  // nothing left for the direct path
+    }
     for (int c = c_begin; c < c_end && (acc_ready || p.splits > 1); c += 16) {
         const int ncols = min(16, c_end - c);
         float g[16], u[16];
@@ -353,16 +391,21 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             }
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
-                if (j >= ncols || t_base + j >= p.T) break;
+                // no early exit from this loop: the 16 columns are independent and the compiler
+                // interleaves their arithmetic only when the loop is straight-line
+                const bool live = j < ncols && t_base + j < p.T;
                 const float v = g[j] + bias;
                 if (SWIGLU) {
-                    c16[(size_t)j * p.ldc] = __float2bfloat16_rn(v / (1.0f + expf(-v)) * u[j]);
+                    // silu(v) * u with the fast exponential and division: the result is rounded to
+                    // bfloat16 (8 bits) right after, their 2^-21 relative error does not show
+                    const float act = __fdividef(v, 1.0f + __expf(-v)) * u[j];
+                    if (live) c16[(size_t)j * p.ldc] = __float2bfloat16_rn(act);
                 } else if (p.epilogue == 0) {
-                    c16[(size_t)j * p.ldc] = __float2bfloat16_rn(v);
+                    if (live) c16[(size_t)j * p.ldc] = __float2bfloat16_rn(v);
                 } else if (p.epilogue == 1) {
-                    c32[(size_t)j * p.ldc] = old[j] + v;
+                    if (live) c32[(size_t)j * p.ldc] = old[j] + v;
                 } else {
-                    c32[(size_t)j * p.ldc] = v;
+                    if (live) c32[(size_t)j * p.ldc] = v;
                 }
             }
         }
@@ -418,6 +461,19 @@ static int make_map(CUtensorMap* map, const void* ptr, int rows, int K, long lon
     return r == CUDA_SUCCESS ? 0 : -1;
 }
 
+// C [T, N] (row stride ldc elements) written in boxes of `box_rows` tokens x 128 features, no swizzle.
+static int make_map_c(CUtensorMap* map, const void* ptr, int T, int N, long long ldc, int box_rows, bool f32) {
+    const cuuint64_t dims[2] = {(cuuint64_t)N, (cuuint64_t)T};
+    const cuuint64_t strides[1] = {(cuuint64_t)ldc * (f32 ? 4 : 2)};
+    const cuuint32_t box[2] = {BM, (cuuint32_t)box_rows};
+    const cuuint32_t elem[2] = {1, 1};
+    const CUresult r = g_encode(map, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
+                                const_cast<void*>(ptr), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : -1;
+}
+
 struct Plan {
     int bn, splits, kb_per_split, tiles;
 };
@@ -447,8 +503,8 @@ static Plan make_plan(int T, int N, int K, bool swiglu, int sm_count) {
 }
 
 template <int BN, bool SWIGLU>
-static int launch(const CUtensorMap& mw, const CUtensorMap& mw2, const CUtensorMap& mx, const GemmParams& p,
-                  dim3 grid, cudaStream_t stream) {
+static int launch(const CUtensorMap& mw, const CUtensorMap& mw2, const CUtensorMap& mx, const CUtensorMap& mc,
+                  const GemmParams& p, dim3 grid, cudaStream_t stream) {
     using C = Cfg<BN, SWIGLU>;
     static_assert(C::ACC_COLS * BM * 4 <= C::STAGES * C::STAGE_BYTES, "staged partials must fit in the operand stages");
     static bool configured = false;
@@ -458,7 +514,7 @@ static int launch(const CUtensorMap& mw, const CUtensorMap& mw2, const CUtensorM
             return (int)cudaGetLastError();
         configured = true;
     }
-    return cw_launch(gemm_tc_kernel<BN, SWIGLU>, grid, dim3(THREADS), C::SMEM_BYTES, stream, grid.z, mw, mw2, mx, p);
+    return cw_launch(gemm_tc_kernel<BN, SWIGLU>, grid, dim3(THREADS), C::SMEM_BYTES, stream, grid.z, mw, mw2, mx, mc, p);
 }
 
 // How a call would be tiled: token tile, splits of the inner dimension (= cluster size), CTAs.
@@ -488,7 +544,14 @@ extern "C" int cw_gemm_tc(const void* X, const void* W, const void* W2, const fl
     if (make_map(&mw, W, N, K, K, BM) != 0) return CW_ERR_UNSUPPORTED;
     if (make_map(&mw2, swiglu ? W2 : W, N, K, K, BM) != 0) return CW_ERR_UNSUPPORTED;
     if (make_map(&mx, X, T, K, ldx, pl.bn) != 0) return CW_ERR_UNSUPPORTED;
+    // C leaves through TMA when its rows are 16-byte multiples at a 16-byte base and the tile is not split
+    const bool c_f32 = !swiglu && epilogue != 0;
+    const long long c_row_bytes = (long long)ldc * (c_f32 ? 4 : 2);
+    const bool tma_store = pl.splits == 1 && c_row_bytes % 16 == 0 && ((uintptr_t)C & 15) == 0;
+    CUtensorMap mc = mx;
+    if (tma_store && make_map_c(&mc, C, T, N, ldc, pl.bn, c_f32) != 0) return CW_ERR_UNSUPPORTED;
     GemmParams p;
+    p.tma_store = tma_store ? 1 : 0;
     p.T = T; p.N = N; p.K = K; p.ldc = ldc; p.epilogue = epilogue;
     p.num_kb = (K + BK - 1) / BK; p.kb_per_split = pl.kb_per_split; p.splits = pl.splits;
     p.bias = bias; p.C = C; p.status = status;
@@ -496,15 +559,15 @@ extern "C" int cw_gemm_tc(const void* X, const void* W, const void* W2, const fl
     if (grid.y > 65535) return CW_ERR_BAD_SIZE;
 #define CW_CASE(bn)                                                                       \
     case bn:                                                                              \
-        return swiglu ? launch<bn, true>(mw, mw2, mx, p, grid, stream)                    \
-                      : launch<bn, false>(mw, mw2, mx, p, grid, stream);
+        return swiglu ? launch<bn, true>(mw, mw2, mx, mc, p, grid, stream)                \
+                      : launch<bn, false>(mw, mw2, mx, mc, p, grid, stream);
     switch (pl.bn) {
         CW_CASE(16)
         CW_CASE(32)
         CW_CASE(64)
         CW_CASE(128)
         case 256:
-            return launch<256, false>(mw, mw2, mx, p, grid, stream);
+            return launch<256, false>(mw, mw2, mx, mc, p, grid, stream);
     }
 #undef CW_CASE
     return CW_ERR_UNSUPPORTED;

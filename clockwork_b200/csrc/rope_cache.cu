@@ -12,55 +12,63 @@
 // (rotated, written to the cache), the last nkv are v (copied to the cache).
 // inv_freq == nullptr: no rotation (a position encoding that leaves q and k alone).
 // slots[t] < 0: the token's K/V are not stored (padding rows of a fixed-shape batch).
+// One block per token: the rotary_dim/2 angles are computed once and serve every head.
 template <typename T>
 __global__ void rope_store_kernel(T* __restrict__ qkv, const int* __restrict__ positions,
                                   const int* __restrict__ slots, const float* __restrict__ inv_freq,
                                   T* __restrict__ k_cache, T* __restrict__ v_cache, int nh, int nkv,
                                   int hd, int rotary_dim, int num_slots, int write_cache,
                                   int* status) {
+    extern __shared__ float cs[];  // cos[half], sin[half]
     pdl_launch_dependents();
     pdl_wait();
     const int t = blockIdx.x;
-    const int head = blockIdx.y;
     const int half = rotary_dim >> 1;
-    T* row = qkv + (size_t)t * (nh + 2 * nkv) * hd + (size_t)head * hd;
-    const int slot = slots ? slots[t] : -1;
-    const bool is_q = head < nh, is_k = !is_q && head < nh + nkv;
-    T* dst = nullptr;
-    if (!is_q) {
-        if (!write_cache || slot < 0) {
-            if (!is_k) return;  // v: nothing to do
-        } else if (slot >= num_slots) {
-            if (threadIdx.x == 0) cw_report(status, CW_ST_SLOT_RANGE, t, slot);
-            return;
-        } else {
-            const int kvh = is_k ? head - nh : head - nh - nkv;
-            dst = (is_k ? k_cache : v_cache) + ((size_t)slot * nkv + kvh) * hd;
+    if (inv_freq != nullptr) {
+        const float pos = (float)positions[t];
+        for (int j = threadIdx.x; j < half; j += blockDim.x) {
+            const float ang = pos * inv_freq[j];
+            cs[j] = cosf(ang);
+            cs[half + j] = sinf(ang);
         }
     }
-    if (is_q || is_k) {
-        if (inv_freq != nullptr) {
-            const float pos = (float)positions[t];
-            for (int j = threadIdx.x; j < half; j += blockDim.x) {
-                const float ang = pos * inv_freq[j];
-                const float c = cosf(ang), s = sinf(ang);
-                const float x1 = to_f(row[j]), x2 = to_f(row[j + half]);
-                const T o1 = from_f<T>(x1 * c - x2 * s);
-                const T o2 = from_f<T>(x2 * c + x1 * s);
-                row[j] = o1;  // k keeps its rotated value in the activation too
-                row[j + half] = o2;
-                if (dst) {
-                    dst[j] = o1;
-                    dst[j + half] = o2;
-                }
+    __syncthreads();
+    int slot = slots ? slots[t] : -1;
+    if (!write_cache) slot = -1;
+    if (slot >= num_slots) {
+        if (threadIdx.x == 0) cw_report(status, CW_ST_SLOT_RANGE, t, slot);
+        slot = -1;
+    }
+    T* row0 = qkv + (size_t)t * (nh + 2 * nkv) * hd;
+    // q and k heads: rotate pairs (j, j + half); k also goes to the cache
+    const int rot_heads = nh + nkv;
+    if (inv_freq != nullptr) {
+        for (int i = threadIdx.x; i < rot_heads * half; i += blockDim.x) {
+            const int head = i / half, j = i % half;
+            T* row = row0 + (size_t)head * hd;
+            const float c = cs[j], s = cs[half + j];
+            const float x1 = to_f(row[j]), x2 = to_f(row[j + half]);
+            const T o1 = from_f<T>(x1 * c - x2 * s);
+            const T o2 = from_f<T>(x2 * c + x1 * s);
+            row[j] = o1;  // k keeps its rotated value in the activation too
+            row[j + half] = o2;
+            if (head >= nh && slot >= 0) {
+                T* dst = k_cache + ((size_t)slot * nkv + (head - nh)) * hd;
+                dst[j] = o1;
+                dst[j + half] = o2;
             }
-            if (dst)  // beyond the rotary span: pass through
-                for (int j = rotary_dim + threadIdx.x; j < hd; j += blockDim.x) dst[j] = row[j];
-        } else if (dst) {
-            for (int j = threadIdx.x; j < hd; j += blockDim.x) dst[j] = row[j];
         }
-    } else if (dst) {
-        for (int j = threadIdx.x; j < hd; j += blockDim.x) dst[j] = row[j];
+    }
+    if (slot >= 0) {
+        // what rotation did not touch of k (beyond the rotary span, or everything without rotation)
+        const int from = inv_freq != nullptr ? rotary_dim : 0;
+        const int span = hd - from;
+        for (int i = threadIdx.x; i < nkv * span; i += blockDim.x) {
+            const int kvh = i / span, d = from + i % span;
+            k_cache[((size_t)slot * nkv + kvh) * hd + d] = row0[(size_t)(nh + kvh) * hd + d];
+        }
+        for (int i = threadIdx.x; i < nkv * hd; i += blockDim.x)
+            v_cache[(size_t)slot * nkv * hd + i] = row0[(size_t)(nh + nkv) * hd + i];
     }
 }
 
@@ -71,16 +79,16 @@ extern "C" int cw_rope_store(void* qkv, const int* positions, const int* slots,
     if (N == 0) return CW_OK;
     if (N < 0 || nh <= 0 || nkv <= 0 || hd <= 0) return CW_ERR_BAD_SIZE;
     if (rotary_dim < 0 || rotary_dim > hd || (rotary_dim & 1)) return CW_ERR_BAD_SIZE;
-    if (nh + 2 * nkv > 65535) return CW_ERR_BAD_SIZE;
-    dim3 grid(N, nh + 2 * nkv);
-    int threads = 32;
-    while (threads < hd / 2 && threads < 128) threads <<= 1;
+    const dim3 grid(N);
+    const int work = (nh + nkv) * (hd / 2);
+    const int threads = work >= 1024 ? 256 : (work >= 256 ? 128 : 64);
+    const size_t smem = (size_t)rotary_dim * sizeof(float);
     if (dtype == 0)
-        return cw_launch(rope_store_kernel<float>, grid, dim3(threads), 0, stream, 1, (float*)qkv, positions, slots,
+        return cw_launch(rope_store_kernel<float>, grid, dim3(threads), smem, stream, 1, (float*)qkv, positions, slots,
                          inv_freq, (float*)k_cache, (float*)v_cache, nh, nkv, hd, rotary_dim, num_slots,
                          write_cache, status);
     if (dtype == 1)
-        return cw_launch(rope_store_kernel<bf16>, grid, dim3(threads), 0, stream, 1, (bf16*)qkv, positions, slots,
+        return cw_launch(rope_store_kernel<bf16>, grid, dim3(threads), smem, stream, 1, (bf16*)qkv, positions, slots,
                          inv_freq, (bf16*)k_cache, (bf16*)v_cache, nh, nkv, hd, rotary_dim, num_slots,
                          write_cache, status);
     return CW_ERR_BAD_DTYPE;
