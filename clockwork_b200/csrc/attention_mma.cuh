@@ -36,3 +36,11 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&v);
 }
+
+// 2^x on the special-function unit (ex2.approx: relative error about 2^-22, -inf gives 0); the
+// probabilities it feeds are rounded to bfloat16 right after.
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}

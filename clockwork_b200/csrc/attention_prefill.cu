@@ -1,4 +1,4 @@
-// Paged causal attention for prompt portions in bfloat16 (flash-attention style): a CTA owns 64
+// Paged causal attention for prompt portions in bfloat16 (flash-attention style): a CTA owns 128
 // query tokens of one request and one query head, streams the request's keys and values from the
 // cache in tiles of 64 tokens (through the block table), and keeps scores, softmax statistics and
 // the output accumulator in registers.  QK^T and P.V run on the tensor cores (mma.sync m16n8k16),
@@ -7,13 +7,13 @@
 // Reference: clockwork/kernels/attention.py:68-96 (gather the context through one block table, then
 // dense causal attention with the query aligned to the end of the context, :45-65) and
 // clockwork/engine/model.py:103-118 (one call per sequence of the batch).  Here one launch covers
-// every portion of the batch: the host lists (request, first query row) work items, one per 64 query
+// every portion of the batch: the host lists (request, first query row) work items, one per 128 query
 // tokens.  A decoded token is a portion of length one and may ride along.
 #include "attention_mma.cuh"
 
-#define QT 64    // query rows per CTA
+#define QT 128   // query rows per CTA (16 per warp)
 #define TILE 64  // keys per staged tile
-#define NWARPS 4
+#define NWARPS 8
 
 struct PrefillParams {
     const bf16* q; int q_stride;
@@ -133,31 +133,46 @@ attn_prefill_kernel(const PrefillParams p) {
                     mma_bf16(sc[2 * j2 + 1], qa, b2, b3);
                 }
             }
+            // only tiles that touch the diagonal, the window's lower edge or the context's end need
+            // the per-element test; the others are wholly visible to all 16 rows of the warp
+            const int w_first = pos0 + qrow;
+            const bool all_visible = tile0 + TILE - 1 <= w_first && tile0 >= kv_lo &&
+                                     (p.window <= 0 || tile0 > w_last - p.window);
             float mx[2] = {-INFINITY, -INFINITY};
+            if (all_visible) {
 #pragma unroll
-            for (int j = 0; j < TILE / 8; ++j)
+                for (int j = 0; j < TILE / 8; ++j)
 #pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const int pos = tile0 + 8 * j + 2 * t + (e & 1);
-                    const int qp = qpos[e >> 1];
-                    const bool vis = pos <= qp && pos >= kv_lo && (p.window <= 0 || pos > qp - p.window);
-                    const float v = vis ? sc[j][e] * scale_log2 : -INFINITY;
-                    sc[j][e] = v;
-                    mx[e >> 1] = fmaxf(mx[e >> 1], v);
-                }
+                    for (int e = 0; e < 4; ++e) {
+                        sc[j][e] *= scale_log2;
+                        mx[e >> 1] = fmaxf(mx[e >> 1], sc[j][e]);
+                    }
+            } else {
+#pragma unroll
+                for (int j = 0; j < TILE / 8; ++j)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int pos = tile0 + 8 * j + 2 * t + (e & 1);
+                        const int qp = qpos[e >> 1];
+                        const bool vis = pos <= qp && pos >= kv_lo && (p.window <= 0 || pos > qp - p.window);
+                        const float v = vis ? sc[j][e] * scale_log2 : -INFINITY;
+                        sc[j][e] = v;
+                        mx[e >> 1] = fmaxf(mx[e >> 1], v);
+                    }
+            }
             float alpha[2];
 #pragma unroll
             for (int r = 0; r < 2; ++r) {
                 mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
                 mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
                 const float m_new = fmaxf(m_run[r], mx[r]);
-                alpha[r] = (m_run[r] == -INFINITY) ? 0.f : exp2f(m_run[r] - m_new);
+                alpha[r] = (m_run[r] == -INFINITY) ? 0.f : fast_exp2(m_run[r] - m_new);
                 float sum = 0.f;
 #pragma unroll
                 for (int j = 0; j < TILE / 8; ++j)
 #pragma unroll
                     for (int e = 0; e < 2; ++e) {
-                        const float pr = (m_new == -INFINITY) ? 0.f : exp2f(sc[j][2 * r + e] - m_new);
+                        const float pr = (m_new == -INFINITY) ? 0.f : fast_exp2(sc[j][2 * r + e] - m_new);
                         sc[j][2 * r + e] = pr;
                         sum += pr;
                     }
@@ -223,7 +238,7 @@ static int launch_prefill(const PrefillParams& p, int items, cudaStream_t stream
     return cw_launch(attn_prefill_kernel<HD>, grid, dim3(NWARPS * 32), SMEM, stream, 1, p);
 }
 
-// q: [N, >= nh*hd] rows of the flat batch; out: [N, nh*hd]; item_seq/item_q0: one entry per 64
+// q: [N, >= nh*hd] rows of the flat batch; out: [N, nh*hd]; item_seq/item_q0: one entry per 128
 // query rows of each request (request index within the step, first query row within its portion).
 extern "C" int cw_attention_prefill(const void* q, int q_stride, void* out, const void* k_cache, const void* v_cache,
                                     const int* block_tables, const int* q_start, const int* ctx_lens,

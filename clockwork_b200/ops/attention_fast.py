@@ -15,7 +15,7 @@ from .library import check, library
 
 DECODE_HEAD_DIMS = (16, 32, 48, 64, 80, 96, 112, 128, 160, 192, 256)
 PREFILL_HEAD_DIMS = (16, 32, 48, 64, 80, 96, 112, 128)
-QUERY_TILE = 64
+QUERY_TILE = 128
 
 _configured = False
 _scratch: dict[int, dict] = {}
@@ -86,7 +86,7 @@ def attention_decode(q, k_cache, v_cache, block_tables, ctx_lens, num_heads, num
 
 
 def _work_items(ctx) -> tuple[torch.Tensor, torch.Tensor, int]:
-    """(request index, first query row) per 64 query rows of each portion; built once per step and
+    """(request index, first query row) per 128 query rows of each portion; built once per step and
     shared by all layers."""
     cached = ctx.extras.get("prefill_items")
     if cached is None:

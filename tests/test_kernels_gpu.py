@@ -443,7 +443,7 @@ def test_attention_prefill_kernel_mixed_batch(ops, status, fast, nh, nkv, hd, ps
     wide = torch.zeros(n, (nh + 2 * nkv) * hd)
     wide[:, : nh * hd] = torch.cat(qs).view(n, nh * hd)
     q_start = torch.tensor([0] + torch.tensor(q_lens).cumsum(0).tolist(), dtype=torch.int32)
-    items = [(s, q0) for s, q in enumerate(q_lens) for q0 in range(0, q, 64)]
+    items = [(s, q0) for s, q in enumerate(q_lens) for q0 in range(0, q, fast.QUERY_TILE)]
     item_seq = torch.tensor([i[0] for i in items], dtype=torch.int32)
     item_q0 = torch.tensor([i[1] for i in items], dtype=torch.int32)
     out = fast.attention_prefill(wide.to(dtype).to(DEV), k_cache.to(DEV), v_cache.to(DEV), tables.to(DEV), q_start.to(DEV),
@@ -473,7 +473,7 @@ def test_attention_prefill_sees_the_diagonal_and_nothing_after_it(ops, status, f
         q[pos, :, :8] = code
     wide = torch.zeros(n, (nh + 2) * hd)
     wide[:, : nh * hd] = q.view(n, -1)
-    items = list(range(0, n, 64))
+    items = list(range(0, n, fast.QUERY_TILE))
     out = fast.attention_prefill(wide.bfloat16().to(DEV), kc.bfloat16().to(DEV), v_cache.to(DEV), tables.to(DEV),
                                  torch.tensor([0, n], dtype=torch.int32, device=DEV), torch.tensor([n], dtype=torch.int32, device=DEV),
                                  torch.zeros(len(items), dtype=torch.int32, device=DEV), torch.tensor(items, dtype=torch.int32, device=DEV),
