@@ -1,6 +1,8 @@
 // Paged decode attention in bfloat16: every request brings one query token and reads its whole
 // context from the cache.  The step is a stream of K/V pages from HBM, so the context of a request
-// is split over CTAs (256 tokens each) and all query heads of one KV head share each K/V tile.
+// is split over CTAs and all query heads of one KV head share each K/V tile.  The split size is a
+// run-time value (a multiple of 64, at least 256): with few requests the context is cut finely so
+// that every SM has a CTA; with many requests a CTA walks a whole context and nothing is merged.
 //
 // Reference: clockwork/kernels/attention.py:113-134 (masking keys >= ctx_len, softmax, P.V) and the
 // Triton kernel clockwork/kernels/triton_paged_attn.py:16-106 (online softmax over one page per
@@ -13,7 +15,7 @@
 #include "attention_mma.cuh"
 
 #define TILE 64
-#define SPLIT 256
+#define MIN_SPLIT 256  // smallest context split (tokens per CTA); the grid's z extent is sized for it
 #define NWARPS 4
 
 struct DecodeParams {
@@ -26,6 +28,9 @@ struct DecodeParams {
     float* part_o;   // [S, nh, max_splits, HD]
     float* part_lse; // [S, nh, max_splits]
     int max_splits;
+    int split;            // tokens per CTA, used when split_ptr is null
+    const int* split_ptr; // the same on the device (so that a captured graph can change it per step)
+    int max_split_pages;  // page ids a split may need (sizes the shared-memory page list)
     int* counters;   // [S * nkv * qgroups]
     int* status;
 };
@@ -49,8 +54,9 @@ attn_decode_kernel(const DecodeParams p) {
     bf16* Qs = (bf16*)smem_raw;                 // [16][LD]
     bf16* Ks = Qs + 16 * LD;                    // [ST][TILE][LD]
     bf16* Vs = Ks + ST * TILE * LD;             // [ST][TILE][LD]
+    int* page_s = (int*)(Vs + ST * TILE * LD);  // [max_split_pages] page of every block of this split
     __shared__ float ml_s[NWARPS][16][2];
-    __shared__ int slot_s[SPLIT];               // cache slot of every token of this split (-1: none)
+    __shared__ float w_s[16][16];               // final merge: weight of each split per query row
     __shared__ int last_flag;
 
     pdl_launch_dependents();
@@ -69,6 +75,7 @@ attn_decode_kernel(const DecodeParams p) {
                 p.out[((size_t)s * p.nh + h0 + i / HD) * HD + i % HD] = __float2bfloat16_rn(0.f);
         return;
     }
+    const int SPLIT = p.split_ptr != nullptr ? *p.split_ptr : p.split;
     const int kv_begin = p.window > 0 ? max(0, ctx - p.window) : 0;
     const int nsplits = (ctx + SPLIT - 1) / SPLIT;
     const int first_split = kv_begin / SPLIT;
@@ -85,29 +92,31 @@ attn_decode_kernel(const DecodeParams p) {
         *reinterpret_cast<uint4*>(Qs + r * LD + c * 8) = v;
     }
 
-    // slots of the split's tokens, looked up once: tile loads then depend on shared memory only
-    for (int i = tid; i < SPLIT; i += blockDim.x) {
-        const int pos = t0 + i;
-        int slot = -1;
-        if (pos < t1 && pos >= kv_begin) {
-            const int blk = p.page_shift >= 0 ? pos >> p.page_shift : pos / p.page_size;
-            const int page = blk < p.max_blocks ? table[blk] : -1;
-            if (page < 0 || page >= p.num_pages) {
-                cw_report(p.status, CW_ST_PAGE_RANGE, s, page);
-            } else {
-                slot = page * p.page_size + (p.page_shift >= 0 ? pos & (p.page_size - 1) : pos % p.page_size);
-            }
-        }
-        slot_s[i] = slot;
+    // page ids of the split's blocks, looked up once: tile loads then depend on shared memory only
+    const int blk0 = p.page_shift >= 0 ? t0 >> p.page_shift : t0 / p.page_size;
+    const int blk1 = p.page_shift >= 0 ? (t1 - 1) >> p.page_shift : (t1 - 1) / p.page_size;
+    for (int i = tid; i <= blk1 - blk0 && i < p.max_split_pages; i += blockDim.x) {
+        const int blk = blk0 + i;
+        int page = blk < p.max_blocks ? table[blk] : -1;
+        if (page >= p.num_pages) page = -1;
+        if (page < 0 && (blk + 1) * p.page_size > kv_begin) cw_report(p.status, CW_ST_PAGE_RANGE, s, page);
+        page_s[i] = page;
     }
-    __syncthreads();  // Qs and slot_s visible
+    __syncthreads();  // Qs and page_s visible
 
     auto load_tile = [&](int tile_idx) {
         bf16* kd = Ks + (tile_idx % ST) * TILE * LD;
         bf16* vd = Vs + (tile_idx % ST) * TILE * LD;
         for (int i = tid; i < TILE * (HD / 8); i += blockDim.x) {
             const int r = i / (HD / 8), c = i % (HD / 8);
-            const int slot = slot_s[tile_idx * TILE + r];
+            const int pos = t0 + tile_idx * TILE + r;
+            int slot = -1;
+            if (pos < t1 && pos >= kv_begin) {
+                const int blk = p.page_shift >= 0 ? pos >> p.page_shift : pos / p.page_size;
+                const int page = blk - blk0 < p.max_split_pages ? page_s[blk - blk0] : -1;
+                if (page >= 0)
+                    slot = page * p.page_size + (p.page_shift >= 0 ? pos & (p.page_size - 1) : pos % p.page_size);
+            }
             if (slot >= 0) {
                 const size_t src = ((size_t)slot * p.nkv + kvh) * HD + c * 8;
                 cp_async16(kd + r * LD + c * 8, p.k_cache + src);
@@ -222,28 +231,36 @@ attn_decode_kernel(const DecodeParams p) {
     }
     __syncthreads();
     const int active = nsplits - first_split;
-    for (int i = tid; i < rows * HD; i += blockDim.x) {
-        const int r = i / HD, d = i % HD;
+    // per query row: the warps' shares (normalised) and the split's log2-sum-exp, computed once
+    if (tid < 16) {
+        const int r = tid;
         float m = -INFINITY;
 #pragma unroll
         for (int w = 0; w < NWARPS; ++w) m = fmaxf(m, ml_s[w][r][0]);
-        float L = 0.f, O = 0.f;
-        if (m != -INFINITY) {
+        float e[NWARPS], L = 0.f;
 #pragma unroll
-            for (int w = 0; w < NWARPS; ++w) {
-                const float mw = ml_s[w][r][0];
-                const float e = (mw == -INFINITY) ? 0.f : exp2f(mw - m);
-                L += e * ml_s[w][r][1];
-                O += e * Om[((size_t)w * 16 + r) * HD + d];
-            }
+        for (int w = 0; w < NWARPS; ++w) {
+            const float mw = ml_s[w][r][0];
+            e[w] = (mw == -INFINITY || m == -INFINITY) ? 0.f : exp2f(mw - m);
+            L += e[w] * ml_s[w][r][1];
         }
-        const float val = L > 0.f ? O / L : 0.f;
+        const float inv = L > 0.f ? 1.f / L : 0.f;
+#pragma unroll
+        for (int w = 0; w < NWARPS; ++w) w_s[r][w] = e[w] * inv;
+        w_s[r][NWARPS] = L > 0.f ? m + log2f(L) : -INFINITY;  // base 2
+    }
+    __syncthreads();
+    for (int i = tid; i < rows * HD; i += blockDim.x) {
+        const int r = i / HD, d = i % HD;
+        float val = 0.f;
+#pragma unroll
+        for (int w = 0; w < NWARPS; ++w) val = fmaf(w_s[r][w], Om[((size_t)w * 16 + r) * HD + d], val);
         const int h = h0 + r;
         if (active == 1) {
             p.out[((size_t)s * p.nh + h) * HD + d] = __float2bfloat16_rn(val);
         } else {
             p.part_o[(((size_t)s * p.nh + h) * p.max_splits + sp) * HD + d] = val;
-            if (d == 0) p.part_lse[((size_t)s * p.nh + h) * p.max_splits + sp] = L > 0.f ? m + log2f(L) : -INFINITY;  // base 2
+            if (d == 0) p.part_lse[((size_t)s * p.nh + h) * p.max_splits + sp] = w_s[r][NWARPS];
         }
     }
     if (active == 1) return;
@@ -259,34 +276,73 @@ attn_decode_kernel(const DecodeParams p) {
     __syncthreads();
     if (!last_flag) return;
     __threadfence();
+    // weights of the splits per query row, once: w = 2^(lse_k - max) / sum
+    const int nact = min(active, 16);
+    for (int i = tid; i < 16 * 16; i += blockDim.x) {
+        const int r = i >> 4, k = i & 15;
+        float w = 0.f;
+        if (r < rows && k < nact) {
+            const float* lse = p.part_lse + ((size_t)s * p.nh + h0 + r) * p.max_splits + first_split;
+            float l16[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) l16[j] = j < nact ? __ldcg(lse + j) : -INFINITY;
+            float m = -INFINITY;
+#pragma unroll
+            for (int j = 0; j < 16; ++j) m = fmaxf(m, l16[j]);
+            float W = 0.f;
+#pragma unroll
+            for (int j = 0; j < 16; ++j) W += (l16[j] == -INFINITY) ? 0.f : exp2f(l16[j] - m);  // split order
+            w = (m == -INFINITY || l16[k] == -INFINITY) ? 0.f : exp2f(l16[k] - m) / W;
+        }
+        w_s[r][k] = w;
+    }
+    __syncthreads();
+    if (active <= 16) {
+        // four outputs at a time, all their splits' partials in flight together
+        for (int i0 = tid; i0 < rows * HD; i0 += 4 * blockDim.x) {
+            float acc[4] = {0.f, 0.f, 0.f, 0.f};
+            for (int k0 = 0; k0 < nact; k0 += 4) {
+                float v[4][4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const int i = i0 + u * blockDim.x;
+                    const int r = i / HD, d = i % HD;
+                    const float* po = p.part_o + (((size_t)s * p.nh + h0 + r) * p.max_splits + first_split) * HD + d;
+#pragma unroll
+                    for (int k = 0; k < 4; ++k)
+                        v[u][k] = (i < rows * HD && k0 + k < nact) ? __ldcg(po + (size_t)(k0 + k) * HD) : 0.f;
+                }
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const int i = i0 + u * blockDim.x;
+                    const int r = min(i / HD, 15);
+#pragma unroll
+                    for (int k = 0; k < 4; ++k)  // split order
+                        if (k0 + k < nact) acc[u] = fmaf(w_s[r][k0 + k], v[u][k], acc[u]);
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int i = i0 + u * blockDim.x;
+                if (i < rows * HD) p.out[((size_t)s * p.nh + h0 + i / HD) * HD + i % HD] = __float2bfloat16_rn(acc[u]);
+            }
+        }
+        return;
+    }
+    // more than 16 live splits (very long contexts): the plain form
     for (int i = tid; i < rows * HD; i += blockDim.x) {
         const int r = i / HD, d = i % HD, h = h0 + r;
         const float* lse = p.part_lse + ((size_t)s * p.nh + h) * p.max_splits;
         const float* po = p.part_o + ((size_t)s * p.nh + h) * p.max_splits * HD + d;
         float m = -INFINITY;
-        for (int k0 = first_split; k0 < nsplits; k0 += 8) {  // eight independent loads at a time
-            float l8[8];
-#pragma unroll
-            for (int j = 0; j < 8; ++j) l8[j] = (k0 + j < nsplits) ? __ldcg(lse + k0 + j) : -INFINITY;
-#pragma unroll
-            for (int j = 0; j < 8; ++j) m = fmaxf(m, l8[j]);
-        }
+        for (int k = first_split; k < nsplits; ++k) m = fmaxf(m, __ldcg(lse + k));
         float W = 0.f, O = 0.f;
         if (m != -INFINITY)
-            for (int k0 = first_split; k0 < nsplits; k0 += 8) {
-                float l8[8], o8[8];
-#pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    const bool in = k0 + j < nsplits;
-                    l8[j] = in ? __ldcg(lse + k0 + j) : -INFINITY;
-                    o8[j] = in ? __ldcg(po + (size_t)(k0 + j) * HD) : 0.f;
-                }
-#pragma unroll
-                for (int j = 0; j < 8; ++j) {  // split order
-                    const float e = (l8[j] == -INFINITY) ? 0.f : exp2f(l8[j] - m);
-                    W += e;
-                    O += e * o8[j];
-                }
+            for (int k = first_split; k < nsplits; ++k) {
+                const float l = __ldcg(lse + k);
+                const float e = (l == -INFINITY) ? 0.f : exp2f(l - m);
+                W += e;
+                O += e * __ldcg(po + (size_t)k * HD);
             }
         p.out[((size_t)s * p.nh + h) * HD + d] = __float2bfloat16_rn(W > 0.f ? O / W : 0.f);
     }
@@ -295,15 +351,15 @@ attn_decode_kernel(const DecodeParams p) {
 template <int HD, int ST>
 static int launch_decode_st(const DecodeParams& p, int S, int splits, cudaStream_t stream) {
     constexpr int LD = HD + 8;
-    constexpr int SMEM = (16 * LD + 2 * ST * TILE * LD) * 2;
+    const int SMEM = (16 * LD + 2 * ST * TILE * LD) * 2 + p.max_split_pages * 4;
     constexpr int MERGE = NWARPS * 16 * HD * 4;
     static_assert(MERGE <= ST * TILE * LD * 2, "the merge buffer must fit over the K buffers");
-    static bool configured = false;
-    if (!configured) {
+    static int configured = 0;
+    if (SMEM > configured) {
         if (SMEM > 48 * 1024 &&
             cudaFuncSetAttribute(attn_decode_kernel<HD, ST>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess)
             return (int)cudaGetLastError();
-        configured = true;
+        configured = SMEM;
     }
     dim3 grid(p.nkv * p.qgroups, S, splits);
     return cw_launch(attn_decode_kernel<HD, ST>, grid, dim3(NWARPS * 32), SMEM, stream, 1, p);
@@ -311,16 +367,15 @@ static int launch_decode_st(const DecodeParams& p, int S, int splits, cudaStream
 
 template <int HD>
 static int launch_decode(const DecodeParams& p, int S, int splits, cudaStream_t stream) {
-    // few CTAs: a whole split in flight per CTA; many CTAs: two CTAs per SM instead
-    const long long ctas = (long long)p.nkv * p.qgroups * S * splits;
-    if (HD <= 128 && ctas <= 2 * 148) return launch_decode_st<HD, (HD <= 128 ? 4 : 2)>(p, S, splits, stream);
-    return launch_decode_st<HD, 2>(p, S, splits, stream);
+    // Four tiles in flight per CTA (one CTA per SM) where shared memory allows: the split policy
+    // aims at about one CTA per SM, and a CTA that walks a long context needs the deep pipeline.
+    return launch_decode_st<HD, (HD <= 128 ? 4 : 2)>(p, S, splits, stream);
 }
 
 // Workspace a call needs: part_o floats, part_lse floats, counters.
 extern "C" int cw_attention_decode_workspace(int S, int nh, int nkv, int hd, int max_ctx, long long* part_o_floats,
                                              long long* part_lse_floats, int* counters) {
-    const int splits = (max_ctx + SPLIT - 1) / SPLIT;
+    const int splits = (max_ctx + MIN_SPLIT - 1) / MIN_SPLIT;
     const int G = nh / (nkv > 0 ? nkv : 1);
     *part_o_floats = (long long)S * nh * splits * hd;
     *part_lse_floats = (long long)S * nh * splits;
@@ -329,11 +384,12 @@ extern "C" int cw_attention_decode_workspace(int S, int nh, int nkv, int hd, int
 }
 
 // q: [S, >= nh*hd] rows (row stride q_stride), one query token per request; out: [S, nh*hd].
-// max_ctx bounds every ctx_lens[s]; it fixes the grid, not the result.
+// max_ctx bounds every ctx_lens[s]; it fixes the grid, not the result.  split (or *split_ptr): tokens
+// per CTA, a multiple of 64 and at least 256.
 extern "C" int cw_attention_decode(const void* q, int q_stride, void* out, const void* k_cache, const void* v_cache,
                                    const int* block_tables, const int* ctx_lens, int S, int nh, int nkv, int hd,
                                    int page_size, int max_blocks, int num_pages, float scale, int window, int max_ctx,
-                                   float* part_o, float* part_lse, int* counters, int* status, cudaStream_t stream) {
+                                   int split, const int* split_ptr, float* part_o, float* part_lse, int* counters, int* status, cudaStream_t stream) {
     if (S == 0) return CW_OK;
     if (S < 0 || nh <= 0 || nkv <= 0 || nh % nkv != 0 || page_size <= 0 || max_blocks <= 0 || max_ctx <= 0)
         return CW_ERR_BAD_SIZE;
@@ -348,8 +404,14 @@ extern "C" int cw_attention_decode(const void* q, int q_stride, void* out, const
     p.page_size = page_size; p.page_shift = (page_size & (page_size - 1)) == 0 ? __builtin_ctz(page_size) : -1; p.max_blocks = max_blocks; p.num_pages = num_pages;
     p.scale = scale; p.window = window;
     p.part_o = part_o; p.part_lse = part_lse; p.counters = counters; p.status = status;
-    const int splits = (max_ctx + SPLIT - 1) / SPLIT;
+    // the grid is sized for the smallest split; a larger run-time split leaves the later CTAs idle
+    if (split_ptr == nullptr && (split < MIN_SPLIT || split % TILE != 0)) return CW_ERR_BAD_SIZE;
+    const int splits = (max_ctx + MIN_SPLIT - 1) / MIN_SPLIT;
     p.max_splits = splits;
+    p.split = split; p.split_ptr = split_ptr;
+    // a split may span the whole context when split_ptr decides at run time
+    const int span = split_ptr != nullptr ? max_ctx : (split < max_ctx ? split : max_ctx);
+    p.max_split_pages = (span + page_size - 1) / page_size + 1;
     if (splits > 65535) return CW_ERR_BAD_SIZE;
     switch (hd) {
         case 16: return launch_decode<16>(p, S, splits, stream);

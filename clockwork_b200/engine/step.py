@@ -177,7 +177,7 @@ class DecodeGraph:
         seg, off = {}, 0
         for name, size in (("tokens", batch), ("positions", batch), ("tok_seq", batch), ("q_start", batch + 1),
                            ("ctx_lens", batch), ("rows", batch), ("temperature", batch), ("top_k", batch),
-                           ("top_p", batch), ("uniform", batch)):
+                           ("top_p", batch), ("uniform", batch), ("decode_split", 1)):
             seg[name] = (off, size)
             off += _pad4(size)
         for g in range(G):
@@ -213,6 +213,10 @@ class DecodeGraph:
         )
         ctx.views = cache.views([view(f"tables{g}").view(batch, self.max_blocks) for g in range(G)],
                                 [view(f"slots{g}") for g in range(G)], None, [])
+        # how finely attention cuts contexts is decided per step from the live requests
+        ctx.extras["decode_split"] = view("decode_split")
+        self.h["decode_split"][0] = max_ctx
+        self._split_policy = model.decode_split_policy()
 
         def run():
             logits = model.forward(ctx, view("tokens"), view("rows"))
@@ -276,6 +280,7 @@ class DecodeGraph:
             self.hf["uniform"][:n] = uniform
             self.hf["temperature"][n:] = 0.0
         self._fill_padding(n)
+        h["decode_split"][0] = self._split_policy(n, int(pos.max()) + 1)
         self.dev.copy_(self.host, non_blocking=True)
         self._uploaded.record()
         self.graph.replay()

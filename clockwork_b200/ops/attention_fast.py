@@ -27,7 +27,7 @@ def _configure() -> None:
         return
     lib = library()
     P, I, F, LL = c_void_p, c_int, c_float, c_longlong
-    lib.cw_attention_decode.argtypes = [P, I, P, P, P, P, P, I, I, I, I, I, I, I, F, I, I, P, P, P, P, P]
+    lib.cw_attention_decode.argtypes = [P, I, P, P, P, P, P, I, I, I, I, I, I, I, F, I, I, I, P, P, P, P, P, P]
     lib.cw_attention_decode.restype = c_int
     lib.cw_attention_decode_workspace.argtypes = [I, I, I, I, I, POINTER(LL), POINTER(LL), POINTER(I)]
     lib.cw_attention_decode_workspace.restype = c_int
@@ -49,6 +49,25 @@ def _decode_scratch(device: torch.device, part_o: int, part_lse: int, counters: 
     return st
 
 
+MIN_SPLIT = 256
+_SMS: dict[int, int] = {}
+
+
+def decode_split(num_seqs: int, num_heads: int, num_kv_heads: int, max_live_ctx: int, device=None) -> int:
+    """Tokens per CTA for a decode step: cut contexts so that about every SM gets a CTA, never finer
+    than 256 tokens; with many requests a CTA walks a whole context and no merge is needed.  The
+    result depends on the number of live requests and their longest context only."""
+    index = torch.cuda.current_device() if device is None or device.index is None else device.index
+    sms = _SMS.get(index)
+    if sms is None:
+        sms = _SMS[index] = torch.cuda.get_device_properties(index).multi_processor_count
+    groups = -(-(num_heads // num_kv_heads) // 16)
+    pairs = max(1, num_seqs * num_kv_heads * groups)
+    per_seq = max(1, sms // pairs)
+    split = -(-max(1, max_live_ctx) // per_seq)
+    return max(MIN_SPLIT, -(-split // 64) * 64)
+
+
 class _Decode:
     @staticmethod
     def accepts(ctx, view, num_heads, num_kv_heads, head_dim, window) -> bool:
@@ -56,14 +75,19 @@ class _Decode:
 
     @staticmethod
     def run(ctx, qkv, view, num_heads, num_kv_heads, head_dim, scale, window, max_ctx: int | None = None) -> torch.Tensor:
+        split_dev = ctx.extras.get("decode_split")  # a device scalar that a captured graph refreshes per step
+        split = None if split_dev is not None else decode_split(ctx.num_seqs, num_heads, num_kv_heads, ctx.max_ctx_len, qkv.device)
         return attention_decode(qkv, view.k_cache, view.v_cache, view.block_tables, ctx.ctx_lens, num_heads,
-                                num_kv_heads, head_dim, scale, window, max_ctx or ctx.max_ctx_len, ctx.status)
+                                num_kv_heads, head_dim, scale, window, max_ctx or ctx.max_ctx_len, ctx.status,
+                                split=split, split_dev=split_dev)
 
 
 def attention_decode(q, k_cache, v_cache, block_tables, ctx_lens, num_heads, num_kv_heads, head_dim, scale, window,
-                     max_ctx: int, status) -> torch.Tensor:
+                     max_ctx: int, status, split: int | None = None, split_dev: torch.Tensor | None = None) -> torch.Tensor:
     """One query token per request: ``q`` [S, >= nh*hd] (row s belongs to request s), ``ctx_lens`` [S]
-    the tokens of each request in the cache (its own included).  Returns [S, nh*hd]."""
+    the tokens of each request in the cache (its own included).  ``split``: tokens per CTA (a multiple
+    of 64, at least 256; default: chosen by ``decode_split``), or ``split_dev``, the same as an int32
+    device scalar.  Returns [S, nh*hd]."""
     _configure()
     if q.dtype != torch.bfloat16 or q.dim() != 2 or q.stride(1) != 1:
         raise ValueError("q must be a 2-d bfloat16 tensor with unit column stride")
@@ -74,6 +98,8 @@ def attention_decode(q, k_cache, v_cache, block_tables, ctx_lens, num_heads, num
     if head_dim not in DECODE_HEAD_DIMS:
         raise ValueError(f"head_dim {head_dim} is not one of {DECODE_HEAD_DIMS}")
     s = q.shape[0]
+    if split_dev is None and split is None:
+        split = decode_split(s, num_heads, num_kv_heads, max_ctx, q.device)
     po, pl, pc = c_longlong(0), c_longlong(0), c_int(0)
     library().cw_attention_decode_workspace(s, num_heads, num_kv_heads, head_dim, max_ctx, byref(po), byref(pl), byref(pc))
     st = _decode_scratch(q.device, po.value, pl.value, pc.value)
@@ -81,7 +107,7 @@ def attention_decode(q, k_cache, v_cache, block_tables, ctx_lens, num_heads, num
     check(library().cw_attention_decode(
         _ptr(q), q.stride(0), _ptr(out), _ptr(k_cache), _ptr(v_cache), _ptr(block_tables), _ptr(ctx_lens), s, num_heads,
         num_kv_heads, head_dim, k_cache.shape[1], block_tables.shape[1], k_cache.shape[0], float(scale), int(window or 0),
-        int(max_ctx), _ptr(st["part_o"]), _ptr(st["part_lse"]), _ptr(st["counters"]), _ptr(status), _stream()), "attention_decode")
+        int(max_ctx), int(split or 0), _ptr(split_dev), _ptr(st["part_o"]), _ptr(st["part_lse"]), _ptr(st["counters"]), _ptr(status), _stream()), "attention_decode")
     return out
 
 

@@ -53,6 +53,22 @@ class DecoderModel:
         """Whether a step of this model may be captured in a CUDA graph."""
         return all(block.graph_safe for block in self.blocks) and self.final_norm.graph_safe
 
+    def decode_split_policy(self):
+        """f(live requests, longest live context) -> tokens per CTA for the decode attention of a
+        captured step (the layers' mixers share one value; the finest wish wins)."""
+        from ..ops.attention_fast import MIN_SPLIT, decode_split
+
+        shapes = {(b.mixer.num_heads, b.mixer.num_kv_heads) for b in self.blocks
+                  if hasattr(b.mixer, "num_kv_heads")}
+        device = self.device
+
+        def policy(num_seqs: int, max_ctx: int) -> int:
+            if not shapes:
+                return MIN_SPLIT
+            return min(decode_split(num_seqs, nh, nkv, max_ctx, device) for nh, nkv in shapes)
+
+        return policy
+
     # ---- weights ---------------------------------------------------------------------------
     def tensor_decls(self) -> list[TensorDecl]:
         spec = self.spec

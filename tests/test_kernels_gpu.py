@@ -397,7 +397,7 @@ def test_attention_decode_kernel(ops, status, fast, nh, nkv, hd, ps, window):
     wide[:, : nh * hd] = torch.cat(qs).view(len(ctx_lens), -1)
     out = fast.attention_decode(wide.to(dtype).to(DEV), k_cache.to(DEV), v_cache.to(DEV), tables.to(DEV),
                                 torch.tensor(ctx_lens, dtype=torch.int32, device=DEV), nh, nkv, hd, scale, window,
-                                max(ctx_lens), status).float().cpu().view(len(ctx_lens), nh, hd)
+                                max(ctx_lens), status, split=256).float().cpu().view(len(ctx_lens), nh, hd)
     ops.raise_on_status(status)
     for i, n in enumerate(real):
         want = plain.causal_attention(qs[i], ks[i], vs[i], scale, window=window)[0]
@@ -406,8 +406,22 @@ def test_attention_decode_kernel(ops, status, fast, nh, nkv, hd, ps, window):
     # the grid's bound on the context changes nothing
     again = fast.attention_decode(wide.to(dtype).to(DEV), k_cache.to(DEV), v_cache.to(DEV), tables.to(DEV),
                                   torch.tensor(ctx_lens, dtype=torch.int32, device=DEV), nh, nkv, hd, scale, window,
-                                  4096, status).float().cpu().view(len(ctx_lens), nh, hd)
+                                  4096, status, split=256).float().cpu().view(len(ctx_lens), nh, hd)
     assert torch.equal(again, out)
+    # other ways of cutting the contexts (coarser, whole, chosen by the policy, given on the device)
+    for kw in (dict(split=512), dict(split=1344), dict(), dict(split_dev=torch.tensor([320], dtype=torch.int32, device=DEV))):
+        other = fast.attention_decode(wide.to(dtype).to(DEV), k_cache.to(DEV), v_cache.to(DEV), tables.to(DEV),
+                                      torch.tensor(ctx_lens, dtype=torch.int32, device=DEV), nh, nkv, hd, scale, window,
+                                      2048, status, **kw).float().cpu().view(len(ctx_lens), nh, hd)
+        for i, n in enumerate(real):
+            want = plain.causal_attention(qs[i], ks[i], vs[i], scale, window=window)[0]
+            torch.testing.assert_close(other[i], want, rtol=2e-2, atol=2e-2, msg=lambda m: f"{kw}, context {n}: {m}")
+    # a bound far beyond the contexts only adds idle CTAs
+    far = fast.attention_decode(wide.to(dtype).to(DEV), k_cache.to(DEV), v_cache.to(DEV), tables.to(DEV),
+                                torch.tensor(ctx_lens, dtype=torch.int32, device=DEV), nh, nkv, hd, scale, window,
+                                6000, status, split=256).float().cpu().view(len(ctx_lens), nh, hd)
+    assert torch.equal(far, out)
+    ops.raise_on_status(status)
 
 
 def test_attention_decode_finds_one_far_key(ops, status, fast):
