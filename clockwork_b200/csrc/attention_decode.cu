@@ -104,27 +104,41 @@ attn_decode_kernel(const DecodeParams p) {
     }
     __syncthreads();  // Qs and page_s visible
 
+    // Every thread copies the same 16-byte column of several rows: the row's cache slot is worked
+    // out once per row and the rest of the addressing is compile-time strides.
+    constexpr int CH = HD / 8;                                  // 16-byte chunks per row
+    constexpr bool EVEN = (NWARPS * 32) % CH == 0;              // threads split evenly over a row's chunks
+    constexpr int RPP = EVEN ? (NWARPS * 32) / CH : 1;          // rows per pass
+    auto slot_of = [&](int pos) -> int {
+        if (pos >= t1 || pos < kv_begin) return -1;
+        const int blk = p.page_shift >= 0 ? pos >> p.page_shift : pos / p.page_size;
+        const int page = blk - blk0 < p.max_split_pages ? page_s[blk - blk0] : -1;
+        if (page < 0) return -1;
+        return page * p.page_size + (p.page_shift >= 0 ? pos & (p.page_size - 1) : pos % p.page_size);
+    };
+    auto copy_chunk = [&](bf16* kd, bf16* vd, int r, int c, int slot) {
+        if (slot >= 0) {
+            const size_t src = ((size_t)slot * p.nkv + kvh) * HD + c * 8;
+            cp_async16(kd + r * LD + c * 8, p.k_cache + src);
+            cp_async16(vd + r * LD + c * 8, p.v_cache + src);
+        } else {
+            *reinterpret_cast<uint4*>(kd + r * LD + c * 8) = make_uint4(0, 0, 0, 0);
+            *reinterpret_cast<uint4*>(vd + r * LD + c * 8) = make_uint4(0, 0, 0, 0);
+        }
+    };
     auto load_tile = [&](int tile_idx) {
         bf16* kd = Ks + (tile_idx % ST) * TILE * LD;
         bf16* vd = Vs + (tile_idx % ST) * TILE * LD;
-        for (int i = tid; i < TILE * (HD / 8); i += blockDim.x) {
-            const int r = i / (HD / 8), c = i % (HD / 8);
-            const int pos = t0 + tile_idx * TILE + r;
-            int slot = -1;
-            if (pos < t1 && pos >= kv_begin) {
-                const int blk = p.page_shift >= 0 ? pos >> p.page_shift : pos / p.page_size;
-                const int page = blk - blk0 < p.max_split_pages ? page_s[blk - blk0] : -1;
-                if (page >= 0)
-                    slot = page * p.page_size + (p.page_shift >= 0 ? pos & (p.page_size - 1) : pos % p.page_size);
+        const int pos0 = t0 + tile_idx * TILE;
+        if (EVEN) {
+            const int c = tid % CH, r0 = tid / CH;
+#pragma unroll
+            for (int k = 0; k < (TILE + RPP - 1) / RPP; ++k) {
+                const int r = r0 + k * RPP;
+                if (r < TILE) copy_chunk(kd, vd, r, c, slot_of(pos0 + r));
             }
-            if (slot >= 0) {
-                const size_t src = ((size_t)slot * p.nkv + kvh) * HD + c * 8;
-                cp_async16(kd + r * LD + c * 8, p.k_cache + src);
-                cp_async16(vd + r * LD + c * 8, p.v_cache + src);
-            } else {
-                *reinterpret_cast<uint4*>(kd + r * LD + c * 8) = make_uint4(0, 0, 0, 0);
-                *reinterpret_cast<uint4*>(vd + r * LD + c * 8) = make_uint4(0, 0, 0, 0);
-            }
+        } else {
+            for (int i = tid; i < TILE * CH; i += blockDim.x) copy_chunk(kd, vd, i / CH, i % CH, slot_of(pos0 + i / CH));
         }
         cp_async_commit();
     };

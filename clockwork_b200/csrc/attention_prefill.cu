@@ -58,32 +58,43 @@ attn_prefill_kernel(const PrefillParams p) {
         *reinterpret_cast<uint4*>(Qs + r * LD + c * 8) = v;
     }
 
+    // Every thread copies the same 16-byte column of several rows: the row's cache slot is worked
+    // out once per row and the rest of the addressing is compile-time strides.
+    constexpr int CH = HD / 8;
+    constexpr bool EVEN = (NWARPS * 32) % CH == 0;
+    constexpr int RPP = EVEN ? (NWARPS * 32) / CH : 1;
+    auto slot_of = [&](int pos) -> int {
+        if (pos >= kv_hi || pos < kv_lo) return -1;
+        const int blk = p.page_shift >= 0 ? pos >> p.page_shift : pos / p.page_size;
+        const int page = blk < p.max_blocks ? table[blk] : -1;
+        if (page < 0 || page >= p.num_pages) {
+            cw_report(p.status, CW_ST_PAGE_RANGE, s, page);
+            return -1;
+        }
+        return page * p.page_size + (p.page_shift >= 0 ? pos & (p.page_size - 1) : pos % p.page_size);
+    };
+    auto copy_chunk = [&](bf16* kd, bf16* vd, int r, int c, int slot) {
+        if (slot >= 0) {
+            const size_t src = ((size_t)slot * p.nkv + kvh) * HD + c * 8;
+            cp_async16(kd + r * LD + c * 8, p.k_cache + src);
+            cp_async16(vd + r * LD + c * 8, p.v_cache + src);
+        } else {
+            *reinterpret_cast<uint4*>(kd + r * LD + c * 8) = make_uint4(0, 0, 0, 0);
+            *reinterpret_cast<uint4*>(vd + r * LD + c * 8) = make_uint4(0, 0, 0, 0);
+        }
+    };
     auto load_tile = [&](int tile0, int buf) {
         bf16* kd = Ks + buf * TILE * LD;
         bf16* vd = Vs + buf * TILE * LD;
-        for (int i = tid; i < TILE * (HD / 8); i += blockDim.x) {
-            const int r = i / (HD / 8), c = i % (HD / 8);
-            const int pos = tile0 + r;
-            bool ok = pos < kv_hi && pos >= kv_lo;
-            size_t src = 0;
-            if (ok) {
-                const int blk = p.page_shift >= 0 ? pos >> p.page_shift : pos / p.page_size;
-                const int page = blk < p.max_blocks ? table[blk] : -1;
-                if (page < 0 || page >= p.num_pages) {
-                    cw_report(p.status, CW_ST_PAGE_RANGE, s, page);
-                    ok = false;
-                } else {
-                    const int off = p.page_shift >= 0 ? pos & (p.page_size - 1) : pos % p.page_size;
-                    src = (((size_t)page * p.page_size + off) * p.nkv + kvh) * HD + c * 8;
-                }
+        if (EVEN) {
+            const int c = tid % CH, r0 = tid / CH;
+#pragma unroll
+            for (int k = 0; k < (TILE + RPP - 1) / RPP; ++k) {
+                const int r = r0 + k * RPP;
+                if (r < TILE) copy_chunk(kd, vd, r, c, slot_of(tile0 + r));
             }
-            if (ok) {
-                cp_async16(kd + r * LD + c * 8, p.k_cache + src);
-                cp_async16(vd + r * LD + c * 8, p.v_cache + src);
-            } else {
-                *reinterpret_cast<uint4*>(kd + r * LD + c * 8) = make_uint4(0, 0, 0, 0);
-                *reinterpret_cast<uint4*>(vd + r * LD + c * 8) = make_uint4(0, 0, 0, 0);
-            }
+        } else {
+            for (int i = tid; i < TILE * CH; i += blockDim.x) copy_chunk(kd, vd, i / CH, i % CH, slot_of(tile0 + i / CH));
         }
         cp_async_commit();
     };
