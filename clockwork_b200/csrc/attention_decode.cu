@@ -442,3 +442,64 @@ extern "C" int cw_attention_decode(const void* q, int q_stride, void* out, const
     }
     return CW_ERR_UNSUPPORTED;
 }
+
+// ---------------------------------------------------------------------------------------------
+// The entry point that allocates nothing (declared and described in clockwork_b200.h).
+// ---------------------------------------------------------------------------------------------
+#include "clockwork_b200.h"
+
+// Scratch of cw_attention_decode_noalloc: counters first, then the partial log-sum-exps, then the
+// partial outputs.  Device code could name this array directly; host code cannot use the name as an
+// address and asks the runtime for it once per device (below).
+static __device__ __align__(256) unsigned char cw_noalloc_scratch[CW_NOALLOC_SCRATCH_BYTES];
+
+#define CW_MAX_DEVICES 64
+static void* g_noalloc_ptr[CW_MAX_DEVICES];  // device address of cw_noalloc_scratch, per device
+
+static size_t align256(size_t n) { return (n + 255) & ~(size_t)255; }
+
+extern "C" const char* cw_error_string(int code) {
+    switch (code) {
+        case CW_OK: return "success";
+        case CW_ERR_BAD_SIZE: return "a size or stride argument is out of range";
+        case CW_ERR_BAD_DTYPE: return "unknown dtype code";
+        case CW_ERR_UNSUPPORTED: return "this combination of sizes or alignments is not supported";
+        case CW_ERR_SETUP: return "set-up failed (no current device, or the scratch symbol could not be resolved)";
+        case CW_ERR_SCRATCH_LIMIT: return "the call needs more scratch than the library's built-in CW_NOALLOC_SCRATCH_BYTES";
+    }
+    return code > 0 ? cudaGetErrorString((cudaError_t)code) : "unknown clockwork_b200 error code";
+}
+
+extern "C" int cw_attention_decode_noalloc(const void* q, int q_stride, void* out, const void* k_cache,
+                                           const void* v_cache, const int* block_tables, const int* ctx_lens, int S,
+                                           int nh, int nkv, int hd, int page_size, int max_blocks, int num_pages,
+                                           float scale, int window, int max_ctx, int split, int* status,
+                                           cudaStream_t stream) {
+    if (S == 0) return CW_OK;
+    if (S < 0 || nh <= 0 || nkv <= 0 || nh % nkv != 0 || hd <= 0 || max_ctx <= 0) return CW_ERR_BAD_SIZE;
+    long long part_o_floats = 0, part_lse_floats = 0;
+    int counters = 0;
+    cw_attention_decode_workspace(S, nh, nkv, hd, max_ctx, &part_o_floats, &part_lse_floats, &counters);
+    const size_t counters_bytes = align256((size_t)counters * sizeof(int));
+    const size_t lse_bytes = align256((size_t)part_lse_floats * sizeof(float));
+    const size_t o_bytes = (size_t)part_o_floats * sizeof(float);
+    if (counters_bytes + lse_bytes + o_bytes > (size_t)CW_NOALLOC_SCRATCH_BYTES) return CW_ERR_SCRATCH_LIMIT;
+
+    // once per device, with that device current: the array's device address
+    int device = -1;
+    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= CW_MAX_DEVICES) return CW_ERR_SETUP;
+    if (g_noalloc_ptr[device] == nullptr) {
+        void* ptr = nullptr;
+        const cudaError_t err = cudaGetSymbolAddress(&ptr, cw_noalloc_scratch);
+        if (err != cudaSuccess || ptr == nullptr) return err != cudaSuccess ? (int)err : CW_ERR_SETUP;
+        g_noalloc_ptr[device] = ptr;
+    }
+    unsigned char* base = (unsigned char*)g_noalloc_ptr[device];
+    // the array keeps the last call's contents: the counters must start at zero
+    const cudaError_t err = cudaMemsetAsync(base, 0, counters_bytes, stream);
+    if (err != cudaSuccess) return (int)err;
+    return cw_attention_decode(q, q_stride, out, k_cache, v_cache, block_tables, ctx_lens, S, nh, nkv, hd, page_size,
+                               max_blocks, num_pages, scale, window, max_ctx, split, nullptr,
+                               (float*)(base + counters_bytes + lse_bytes), (float*)(base + counters_bytes),
+                               (int*)base, status, stream);
+}

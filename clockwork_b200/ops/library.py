@@ -68,7 +68,8 @@ def library() -> ctypes.CDLL:
         return lib
 
 
-ERROR_NAMES = {-1: "refused size", -2: "unknown dtype code", -3: "unsupported combination", -4: "set-up failed"}
+ERROR_NAMES = {-1: "refused size", -2: "unknown dtype code", -3: "unsupported combination", -4: "set-up failed",
+               -5: "needs more scratch than the built-in maximum"}
 
 
 _launches = 0
