@@ -33,6 +33,14 @@ struct DecodeParams {
     int max_split_pages;  // page ids a split may need (sizes the shared-memory page list)
     int* counters;   // [S * nkv * qgroups]
     int* status;
+    // Fused position encoding and cache write (kv_new != null): q, and the new token's k and v, are
+    // taken raw from the [q | k | v] rows; q and k are rotated here, k and v stored at slots[s].
+    const bf16* kv_new;      // the [q | k | v] rows (row stride q_stride), or null
+    const float* inv_freq;   // [rotary_dim / 2] or null (no rotation)
+    int rotary_dim;
+    const int* slots;        // [S] cache slot of the new token (-1: not stored)
+    bf16* k_cache_w; bf16* v_cache_w;
+    int num_slots;
 };
 
 __device__ __forceinline__ void cp_async_wait_upto(int n) {
@@ -42,6 +50,10 @@ __device__ __forceinline__ void cp_async_wait_upto(int n) {
         case 2: cp_async_wait<2>(); break;
         default: cp_async_wait<3>(); break;
     }
+}
+
+__device__ __forceinline__ bool mine_newest(int newest, int t0, int t1, int kv_begin) {
+    return newest >= t0 && newest < t1 && newest >= kv_begin;
 }
 
 // ST: tiles in flight.  4 puts a whole split (256 tokens) in flight at once, for steps with few
@@ -57,10 +69,15 @@ attn_decode_kernel(const DecodeParams p) {
     int* page_s = (int*)(Vs + ST * TILE * LD);  // [max_split_pages] page of every block of this split
     __shared__ float ml_s[NWARPS][16][2];
     __shared__ float w_s[16][16];               // final merge: weight of each split per query row
+    __shared__ __align__(16) bf16 new_s[2 * HD]; // the newest token's k and v
+    __shared__ float cs_s[HD];                  // cos, sin of the newest position (fused rotation)
     __shared__ int last_flag;
 
+    // Nothing below reads what the preceding kernels of this step wrote until pdl_wait(): context
+    // lengths, block tables, positions and the split size are inputs of the step, and cached keys and
+    // values of earlier tokens were written by earlier steps.  So the page list and the first tiles
+    // are fetched while the preceding kernel finishes; only q and the newest token's k/v come after.
     pdl_launch_dependents();
-    pdl_wait();
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g = lane >> 2, t = lane & 3;
     const int kvh = blockIdx.x / p.qgroups, qg = blockIdx.x % p.qgroups;
@@ -70,6 +87,7 @@ attn_decode_kernel(const DecodeParams p) {
     const int rows = min(16, G - qg * 16);
     const int ctx = p.ctx_lens[s];
     if (ctx <= 0) {  // a padding row of a fixed-shape batch
+        pdl_wait();
         if (sp == 0)
             for (int i = tid; i < rows * HD; i += blockDim.x)
                 p.out[((size_t)s * p.nh + h0 + i / HD) * HD + i % HD] = __float2bfloat16_rn(0.f);
@@ -84,14 +102,6 @@ attn_decode_kernel(const DecodeParams p) {
     const int* table = p.block_tables + (size_t)s * p.max_blocks;
     const float scale_log2 = p.scale * 1.4426950408889634f;  // softmax in base 2: exp(x) = 2^(x log2 e)
 
-    // ---- Q rows of this group into shared memory, then into A fragments ----------------------------
-    for (int i = tid; i < 16 * (HD / 8); i += blockDim.x) {
-        const int r = i / (HD / 8), c = i % (HD / 8);
-        uint4 v = make_uint4(0, 0, 0, 0);
-        if (r < rows) v = *reinterpret_cast<const uint4*>(p.q + (size_t)s * p.q_stride + (size_t)(h0 + r) * HD + c * 8);
-        *reinterpret_cast<uint4*>(Qs + r * LD + c * 8) = v;
-    }
-
     // page ids of the split's blocks, looked up once: tile loads then depend on shared memory only
     const int blk0 = p.page_shift >= 0 ? t0 >> p.page_shift : t0 / p.page_size;
     const int blk1 = p.page_shift >= 0 ? (t1 - 1) >> p.page_shift : (t1 - 1) / p.page_size;
@@ -102,15 +112,16 @@ attn_decode_kernel(const DecodeParams p) {
         if (page < 0 && (blk + 1) * p.page_size > kv_begin) cw_report(p.status, CW_ST_PAGE_RANGE, s, page);
         page_s[i] = page;
     }
-    __syncthreads();  // Qs and page_s visible
+    __syncthreads();  // page_s visible
 
     // Every thread copies the same 16-byte column of several rows: the row's cache slot is worked
     // out once per row and the rest of the addressing is compile-time strides.
     constexpr int CH = HD / 8;                                  // 16-byte chunks per row
     constexpr bool EVEN = (NWARPS * 32) % CH == 0;              // threads split evenly over a row's chunks
     constexpr int RPP = EVEN ? (NWARPS * 32) / CH : 1;          // rows per pass
+    const int newest = ctx - 1;  // its k/v are written by this step: they arrive after pdl_wait()
     auto slot_of = [&](int pos) -> int {
-        if (pos >= t1 || pos < kv_begin) return -1;
+        if (pos >= t1 || pos < kv_begin || pos == newest) return -1;
         const int blk = p.page_shift >= 0 ? pos >> p.page_shift : pos / p.page_size;
         const int page = blk - blk0 < p.max_split_pages ? page_s[blk - blk0] : -1;
         if (page < 0) return -1;
@@ -145,6 +156,73 @@ attn_decode_kernel(const DecodeParams p) {
 
     const int ntiles = (t1 - t0 + TILE - 1) / TILE;
     for (int i = 0; i < ST && i < ntiles; ++i) load_tile(i);
+    // cos/sin of the new token's position (an input of the step), for the fused rotation
+    const int half = p.rotary_dim >> 1;
+    if (p.kv_new != nullptr && p.inv_freq != nullptr)
+        for (int j = tid; j < half; j += blockDim.x) {
+            const float ang = (float)newest * p.inv_freq[j];
+            cs_s[j] = cosf(ang);
+            cs_s[half + j] = sinf(ang);
+        }
+
+    pdl_wait();
+    // ---- Q rows of this group into shared memory ----------------------------------------------------
+    for (int i = tid; i < 16 * CH; i += blockDim.x) {
+        const int r = i / CH, c = i % CH;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (r < rows) v = *reinterpret_cast<const uint4*>(p.q + (size_t)s * p.q_stride + (size_t)(h0 + r) * HD + c * 8);
+        *reinterpret_cast<uint4*>(Qs + r * LD + c * 8) = v;
+    }
+    // ---- the newest token's k and v: from the [q|k|v] row (rotating k, storing both) or from the cache
+    const bool has_newest = mine_newest(newest, t0, t1, kv_begin);
+    if (has_newest) {
+        if (p.kv_new != nullptr) {
+            const bf16* krow = p.kv_new + (size_t)s * p.q_stride + (size_t)(p.nh + kvh) * HD;
+            const bf16* vrow = p.kv_new + (size_t)s * p.q_stride + (size_t)(p.nh + p.nkv + kvh) * HD;
+            for (int i = tid; i < 2 * CH; i += blockDim.x) {
+                const bf16* src = (i < CH ? krow : vrow) + (i % CH) * 8;
+                *reinterpret_cast<uint4*>(new_s + (i < CH ? 0 : HD) + (i % CH) * 8) = *reinterpret_cast<const uint4*>(src);
+            }
+        } else {
+            const int blk = p.page_shift >= 0 ? newest >> p.page_shift : newest / p.page_size;
+            const int page = blk - blk0 < p.max_split_pages ? page_s[blk - blk0] : -1;
+            if (page >= 0) {
+                const int slot = page * p.page_size + (p.page_shift >= 0 ? newest & (p.page_size - 1) : newest % p.page_size);
+                const size_t src = ((size_t)slot * p.nkv + kvh) * HD;
+                for (int i = tid; i < 2 * CH; i += blockDim.x)
+                    *reinterpret_cast<uint4*>(new_s + (i < CH ? 0 : HD) + (i % CH) * 8) =
+                        *reinterpret_cast<const uint4*>((i < CH ? p.k_cache : p.v_cache) + src + (i % CH) * 8);
+            } else {
+                for (int i = tid; i < 2 * HD; i += blockDim.x) new_s[i] = __float2bfloat16_rn(0.f);
+            }
+        }
+    }
+    __syncthreads();  // Qs and new_s visible
+    if (p.kv_new != nullptr && p.inv_freq != nullptr) {
+        // rotate q rows and the new k in shared memory: element j pairs with j + rotary_dim/2
+        for (int i = tid; i < (rows + (has_newest ? 1 : 0)) * half; i += blockDim.x) {
+            const int r = i / half, j = i % half;
+            bf16* row = r < rows ? Qs + r * LD : new_s;
+            const float c = cs_s[j], sn = cs_s[half + j];
+            const float x1 = __bfloat162float(row[j]), x2 = __bfloat162float(row[j + half]);
+            row[j] = __float2bfloat16_rn(x1 * c - x2 * sn);
+            row[j + half] = __float2bfloat16_rn(x2 * c + x1 * sn);
+        }
+        __syncthreads();
+    }
+    if (p.kv_new != nullptr && has_newest && qg == 0) {
+        // one CTA per (request, KV head) stores the new token
+        const int slot = p.slots != nullptr ? p.slots[s] : -1;
+        if (slot >= p.num_slots) {
+            if (tid == 0) cw_report(p.status, CW_ST_SLOT_RANGE, s, slot);
+        } else if (slot >= 0) {
+            const size_t dst = ((size_t)slot * p.nkv + kvh) * HD;
+            for (int i = tid; i < 2 * CH; i += blockDim.x)
+                *reinterpret_cast<uint4*>((i < CH ? p.k_cache_w : p.v_cache_w) + dst + (i % CH) * 8) =
+                    *reinterpret_cast<const uint4*>(new_s + (i < CH ? 0 : HD) + (i % CH) * 8);
+        }
+    }
+    const int newest_tile = has_newest ? (newest - t0) / TILE : -1;
     uint32_t qa[HD / 16][4];
 #pragma unroll
     for (int ks = 0; ks < HD / 16; ++ks)
@@ -159,6 +237,12 @@ attn_decode_kernel(const DecodeParams p) {
     for (int it = 0; it < ntiles; ++it) {
         const int buf = it % ST;
         cp_async_wait_upto(min(ntiles - it - 1, ST - 1));  // tile `it` has landed; later ones may fly
+        if (it == newest_tile) {
+            const int r = newest - t0 - it * TILE;
+            for (int i = tid; i < 2 * CH; i += blockDim.x)
+                *reinterpret_cast<uint4*>((i < CH ? Ks : Vs) + (buf * TILE + r) * LD + (i % CH) * 8) =
+                    *reinterpret_cast<const uint4*>(new_s + (i < CH ? 0 : HD) + (i % CH) * 8);
+        }
         __syncthreads();
         const bf16* kt = Ks + buf * TILE * LD + warp * 16 * LD;
         const bf16* vt = Vs + buf * TILE * LD + warp * 16 * LD;
@@ -400,10 +484,31 @@ extern "C" int cw_attention_decode_workspace(int S, int nh, int nkv, int hd, int
 // q: [S, >= nh*hd] rows (row stride q_stride), one query token per request; out: [S, nh*hd].
 // max_ctx bounds every ctx_lens[s]; it fixes the grid, not the result.  split (or *split_ptr): tokens
 // per CTA, a multiple of 64 and at least 256.
+extern "C" int cw_attention_decode_fused(const void* q, int q_stride, void* out, void* k_cache, void* v_cache,
+                                         const int* block_tables, const int* ctx_lens, int S, int nh, int nkv, int hd,
+                                         int page_size, int max_blocks, int num_pages, float scale, int window,
+                                         int max_ctx, int split, const int* split_ptr, float* part_o, float* part_lse,
+                                         int* counters, int fuse_store, const float* inv_freq, int rotary_dim,
+                                         const int* slots, int* status, cudaStream_t stream);
+
 extern "C" int cw_attention_decode(const void* q, int q_stride, void* out, const void* k_cache, const void* v_cache,
                                    const int* block_tables, const int* ctx_lens, int S, int nh, int nkv, int hd,
                                    int page_size, int max_blocks, int num_pages, float scale, int window, int max_ctx,
                                    int split, const int* split_ptr, float* part_o, float* part_lse, int* counters, int* status, cudaStream_t stream) {
+    return cw_attention_decode_fused(q, q_stride, out, const_cast<void*>(k_cache), const_cast<void*>(v_cache), block_tables,
+                                     ctx_lens, S, nh, nkv, hd, page_size, max_blocks, num_pages, scale, window, max_ctx,
+                                     split, split_ptr, part_o, part_lse, counters, 0, nullptr, 0, nullptr, status, stream);
+}
+
+// As cw_attention_decode; with fuse_store != 0, q is the [q | k | v] row buffer that the QKV product
+// wrote (raw): q and the new k are rotated here (inv_freq null: left alone) and the new token's k and
+// v are stored at slots[s] before they are used, so no separate position/cache-write kernel runs.
+extern "C" int cw_attention_decode_fused(const void* q, int q_stride, void* out, void* k_cache, void* v_cache,
+                                         const int* block_tables, const int* ctx_lens, int S, int nh, int nkv, int hd,
+                                         int page_size, int max_blocks, int num_pages, float scale, int window,
+                                         int max_ctx, int split, const int* split_ptr, float* part_o, float* part_lse,
+                                         int* counters, int fuse_store, const float* inv_freq, int rotary_dim,
+                                         const int* slots, int* status, cudaStream_t stream) {
     if (S == 0) return CW_OK;
     if (S < 0 || nh <= 0 || nkv <= 0 || nh % nkv != 0 || page_size <= 0 || max_blocks <= 0 || max_ctx <= 0)
         return CW_ERR_BAD_SIZE;
@@ -418,6 +523,12 @@ extern "C" int cw_attention_decode(const void* q, int q_stride, void* out, const
     p.page_size = page_size; p.page_shift = (page_size & (page_size - 1)) == 0 ? __builtin_ctz(page_size) : -1; p.max_blocks = max_blocks; p.num_pages = num_pages;
     p.scale = scale; p.window = window;
     p.part_o = part_o; p.part_lse = part_lse; p.counters = counters; p.status = status;
+    if (fuse_store && (rotary_dim < 0 || rotary_dim > hd || (rotary_dim & 1))) return CW_ERR_BAD_SIZE;
+    p.kv_new = fuse_store ? (const bf16*)q : nullptr;
+    p.inv_freq = fuse_store ? inv_freq : nullptr;
+    p.rotary_dim = fuse_store && inv_freq != nullptr ? rotary_dim : 0;
+    p.slots = slots; p.k_cache_w = (bf16*)k_cache; p.v_cache_w = (bf16*)v_cache;
+    p.num_slots = num_pages * page_size;
     // the grid is sized for the smallest split; a larger run-time split leaves the later CTAs idle
     if (split_ptr == nullptr && (split < MIN_SPLIT || split % TILE != 0)) return CW_ERR_BAD_SIZE;
     const int splits = (max_ctx + MIN_SPLIT - 1) / MIN_SPLIT;

@@ -15,11 +15,25 @@ _decode = None  # set by ops.attention_decode when present
 _prefill = None  # set by ops.attention_prefill when present
 
 
+def decode_kernel_takes(ctx, qkv: torch.Tensor, view, num_heads: int, num_kv_heads: int, head_dim: int,
+                        window: int | None) -> bool:
+    """Whether this step's attention will run in the split-context decode kernel (which can also do
+    the position encoding and the cache write of the new token itself)."""
+    return (qkv.dtype == torch.bfloat16 and ctx.all_single_token and _decode is not None
+            and _decode.accepts(ctx, view, num_heads, num_kv_heads, head_dim, window))
+
+
 def paged_attention(ctx, qkv: torch.Tensor, view, num_heads: int, num_kv_heads: int, head_dim: int,
-                    scale: float, window: int | None) -> torch.Tensor:
+                    scale: float, window: int | None, fused_position=None) -> torch.Tensor:
+    """``fused_position`` = (inv_freq or None, rotary_dim): q and k in ``qkv`` are still raw and the new
+    token is not in the cache yet; only valid when ``decode_kernel_takes`` said yes."""
     if qkv.dtype == torch.bfloat16:
         if ctx.all_single_token and _decode is not None and _decode.accepts(ctx, view, num_heads, num_kv_heads, head_dim, window):
-            return _decode.run(ctx, qkv, view, num_heads, num_kv_heads, head_dim, scale, window)
+            return _decode.run(ctx, qkv, view, num_heads, num_kv_heads, head_dim, scale, window,
+                               fused_position=fused_position)
+    if fused_position is not None:
+        raise RuntimeError("fused position encoding was asked of a kernel that does not do it")
+    if qkv.dtype == torch.bfloat16:
         if not ctx.all_single_token and _prefill is not None and _prefill.accepts(ctx, view, num_heads, num_kv_heads, head_dim, window):
             return _prefill.run(ctx, qkv, view, num_heads, num_kv_heads, head_dim, scale, window)
     return attention_ref(qkv, view.k_cache, view.v_cache, view.block_tables, ctx.tok_seq, ctx.positions,

@@ -29,6 +29,8 @@ def _configure() -> None:
     P, I, F, LL = c_void_p, c_int, c_float, c_longlong
     lib.cw_attention_decode.argtypes = [P, I, P, P, P, P, P, I, I, I, I, I, I, I, F, I, I, I, P, P, P, P, P, P]
     lib.cw_attention_decode.restype = c_int
+    lib.cw_attention_decode_fused.argtypes = [P, I, P, P, P, P, P, I, I, I, I, I, I, I, F, I, I, I, P, P, P, P, I, P, I, P, P, P]
+    lib.cw_attention_decode_fused.restype = c_int
     lib.cw_attention_decode_workspace.argtypes = [I, I, I, I, I, POINTER(LL), POINTER(LL), POINTER(I)]
     lib.cw_attention_decode_workspace.restype = c_int
     lib.cw_attention_prefill.argtypes = [P, I, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, I, P, P]
@@ -74,20 +76,25 @@ class _Decode:
         return head_dim in DECODE_HEAD_DIMS and ctx.num_tokens == ctx.num_seqs
 
     @staticmethod
-    def run(ctx, qkv, view, num_heads, num_kv_heads, head_dim, scale, window, max_ctx: int | None = None) -> torch.Tensor:
+    def run(ctx, qkv, view, num_heads, num_kv_heads, head_dim, scale, window, max_ctx: int | None = None,
+            fused_position=None) -> torch.Tensor:
         split_dev = ctx.extras.get("decode_split")  # a device scalar that a captured graph refreshes per step
         split = None if split_dev is not None else decode_split(ctx.num_seqs, num_heads, num_kv_heads, ctx.max_ctx_len, qkv.device)
         return attention_decode(qkv, view.k_cache, view.v_cache, view.block_tables, ctx.ctx_lens, num_heads,
                                 num_kv_heads, head_dim, scale, window, max_ctx or ctx.max_ctx_len, ctx.status,
-                                split=split, split_dev=split_dev)
+                                split=split, split_dev=split_dev,
+                                fused=None if fused_position is None else (*fused_position, view.slots))
 
 
 def attention_decode(q, k_cache, v_cache, block_tables, ctx_lens, num_heads, num_kv_heads, head_dim, scale, window,
-                     max_ctx: int, status, split: int | None = None, split_dev: torch.Tensor | None = None) -> torch.Tensor:
+                     max_ctx: int, status, split: int | None = None, split_dev: torch.Tensor | None = None,
+                     fused: tuple | None = None) -> torch.Tensor:
     """One query token per request: ``q`` [S, >= nh*hd] (row s belongs to request s), ``ctx_lens`` [S]
     the tokens of each request in the cache (its own included).  ``split``: tokens per CTA (a multiple
     of 64, at least 256; default: chosen by ``decode_split``), or ``split_dev``, the same as an int32
-    device scalar.  Returns [S, nh*hd]."""
+    device scalar.  ``fused``: (inv_freq or None, rotary_dim, slots): ``q`` is then the raw [q | k | v]
+    rows; q and the new k are rotated inside the kernel and the new token's k and v stored at ``slots``
+    (so no separate position-encoding / cache-write kernel is needed).  Returns [S, nh*hd]."""
     _configure()
     if q.dtype != torch.bfloat16 or q.dim() != 2 or q.stride(1) != 1:
         raise ValueError("q must be a 2-d bfloat16 tensor with unit column stride")
@@ -104,10 +111,20 @@ def attention_decode(q, k_cache, v_cache, block_tables, ctx_lens, num_heads, num
     library().cw_attention_decode_workspace(s, num_heads, num_kv_heads, head_dim, max_ctx, byref(po), byref(pl), byref(pc))
     st = _decode_scratch(q.device, po.value, pl.value, pc.value)
     out = torch.empty((s, num_heads * head_dim), dtype=torch.bfloat16, device=q.device)
-    check(library().cw_attention_decode(
+    inv_freq, rotary_dim, slots = fused if fused is not None else (None, 0, None)
+    if fused is not None:
+        if q.shape[1] != (num_heads + 2 * num_kv_heads) * head_dim:
+            raise ValueError("the fused form needs the whole [q | k | v] rows")
+        _need(slots, torch.int32, "slots", 1)
+        if inv_freq is not None:
+            _need(inv_freq, torch.float32, "inv_freq", 1)
+            if inv_freq.shape[0] * 2 != rotary_dim:
+                raise ValueError("inv_freq must hold rotary_dim/2 frequencies")
+    check(library().cw_attention_decode_fused(
         _ptr(q), q.stride(0), _ptr(out), _ptr(k_cache), _ptr(v_cache), _ptr(block_tables), _ptr(ctx_lens), s, num_heads,
         num_kv_heads, head_dim, k_cache.shape[1], block_tables.shape[1], k_cache.shape[0], float(scale), int(window or 0),
-        int(max_ctx), int(split or 0), _ptr(split_dev), _ptr(st["part_o"]), _ptr(st["part_lse"]), _ptr(st["counters"]), _ptr(status), _stream()), "attention_decode")
+        int(max_ctx), int(split or 0), _ptr(split_dev), _ptr(st["part_o"]), _ptr(st["part_lse"]), _ptr(st["counters"]),
+        1 if fused is not None else 0, _ptr(inv_freq), int(rotary_dim), _ptr(slots), _ptr(status), _stream()), "attention_decode")
     return out
 
 

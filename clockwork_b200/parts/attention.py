@@ -70,9 +70,17 @@ class Attention(Mixer):
 
     def forward(self, ctx: StepContext, x: torch.Tensor, view: PagedView, stream: ResidualStream):
         qkv = self.qkv(x)  # [N, (nh + 2 nkv) hd]
-        self.position.apply_and_store(ctx, qkv, view, self.num_heads, self.num_kv_heads, self.head_dim)
+        # When every request decodes one token, the attention kernel itself rotates q and the new k and
+        # stores the new k, v (one kernel less per layer), provided the position part can hand its
+        # constants over; otherwise the position part runs its own kernel first.
+        fused = None
+        if view.write and hasattr(self.position, "fused_decode_args") and attention_ops.decode_kernel_takes(
+                ctx, qkv, view, self.num_heads, self.num_kv_heads, self.head_dim, self.window):
+            fused = self.position.fused_decode_args(self.head_dim)
+        if fused is None:
+            self.position.apply_and_store(ctx, qkv, view, self.num_heads, self.num_kv_heads, self.head_dim)
         out = attention_ops.paged_attention(ctx, qkv, view, self.num_heads, self.num_kv_heads,
-                                            self.head_dim, self.scale, self.window)
+                                            self.head_dim, self.scale, self.window, fused_position=fused)
         self.o.add_into(out, stream.residual_after_flush())
         return None
 

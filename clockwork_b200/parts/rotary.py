@@ -41,8 +41,16 @@ class RotaryNeox(PositionEncoding):
                        num_heads, num_kv_heads, head_dim, self.rotary_dim, ctx.status, write_cache=write)
 
 
+    def fused_decode_args(self, head_dim: int):
+        """(inv_freq, rotary_dim) for kernels that apply this encoding themselves, or None."""
+        return (self.inv_freq, self.rotary_dim) if self.rotary_dim <= head_dim else None
+
+
 class NoPosition(PositionEncoding):
     graph_safe = True
+
+    def fused_decode_args(self, head_dim: int):
+        return (None, 0)
 
     def apply_and_store(self, ctx, qkv, view, num_heads, num_kv_heads, head_dim) -> None:
         if view is not None and view.write:

@@ -495,3 +495,31 @@ def test_attention_prefill_sees_the_diagonal_and_nothing_after_it(ops, status, f
     ops.raise_on_status(status)
     # own score 8*36 = 288; any other key differs in at least one bit: at most 288 - 72
     torch.testing.assert_close(out[:, 0], vs[0][:, 0], rtol=2e-2, atol=2e-2)
+
+
+@pytest.mark.parametrize("nh,nkv,hd,ps,rot", [(12, 2, 128, 16, 128), (5, 5, 48, 8, 32), (32, 1, 64, 16, 64), (4, 2, 32, 8, 0)])
+def test_attention_decode_fused_position_and_store(ops, status, fast, nh, nkv, hd, ps, rot):
+    """The decode kernel doing the rotation of q and the new k and the cache write itself == the
+    position kernel followed by the plain decode kernel, bit for bit, cache included."""
+    ctx_lens = [1, 17, 64, 256, 257, 700, 1300]
+    dtype = torch.bfloat16
+    k_cache, v_cache, tables, _, _ = paged_setup(ctx_lens, nkv, hd, ps, dtype, seed=21)
+    n = len(ctx_lens)
+    qkv = rand(n, (nh + 2 * nkv) * hd, dtype=dtype, scale=2.0, seed=3).to(DEV)
+    positions = torch.tensor([c - 1 for c in ctx_lens], dtype=torch.int32, device=DEV)
+    slots = torch.tensor([int(tables[i, (c - 1) // ps]) * ps + (c - 1) % ps for i, c in enumerate(ctx_lens)],
+                         dtype=torch.int32, device=DEV)
+    inv_freq = (1.0 / (1e4 ** (torch.arange(0, rot, 2, dtype=torch.float32) / rot))).to(DEV) if rot else None
+    ctx = torch.tensor(ctx_lens, dtype=torch.int32, device=DEV)
+    scale = hd**-0.5
+    # the two-kernel way
+    k1, v1, x1 = k_cache.to(DEV).clone(), v_cache.to(DEV).clone(), qkv.clone()
+    ops.rope_store(x1, positions, slots, inv_freq, k1, v1, nh, nkv, hd, rot, status)
+    want = fast.attention_decode(x1, k1, v1, tables.to(DEV), ctx, nh, nkv, hd, scale, None, max(ctx_lens), status, split=256)
+    # the fused way
+    k2, v2 = k_cache.to(DEV).clone(), v_cache.to(DEV).clone()
+    got = fast.attention_decode(qkv, k2, v2, tables.to(DEV), ctx, nh, nkv, hd, scale, None, max(ctx_lens), status, split=256,
+                                fused=(inv_freq, rot, slots))
+    ops.raise_on_status(status)
+    assert torch.equal(k2, k1) and torch.equal(v2, v1)
+    assert torch.equal(got, want)
