@@ -31,6 +31,7 @@ struct DecodeParams {
     int split;            // tokens per CTA, used when split_ptr is null
     const int* split_ptr; // the same on the device (so that a captured graph can change it per step)
     int max_split_pages;  // page ids a split may need (sizes the shared-memory page list)
+    int stages;           // tiles in flight per CTA: 4 (default) or 2
     int* counters;   // [S * nkv * qgroups]
     int* status;
     // Fused position encoding and cache write (kv_new != null): q, and the new token's k and v, are
@@ -465,9 +466,11 @@ static int launch_decode_st(const DecodeParams& p, int S, int splits, cudaStream
 
 template <int HD>
 static int launch_decode(const DecodeParams& p, int S, int splits, cudaStream_t stream) {
-    // Four tiles in flight per CTA (one CTA per SM) where shared memory allows: the split policy
-    // aims at about one CTA per SM, and a CTA that walks a long context needs the deep pipeline.
-    return launch_decode_st<HD, (HD <= 128 ? 4 : 2)>(p, S, splits, stream);
+    // Four tiles in flight per CTA (one CTA per SM) suit steps with few CTAs, where latency is
+    // everything; with many CTAs two tiles in flight leave room for two or three CTAs per SM, and
+    // the warps of the others cover each CTA's stalls.
+    if (HD <= 128 && p.stages != 2) return launch_decode_st<HD, (HD <= 128 ? 4 : 2)>(p, S, splits, stream);
+    return launch_decode_st<HD, 2>(p, S, splits, stream);
 }
 
 // Workspace a call needs: part_o floats, part_lse floats, counters.
@@ -489,7 +492,7 @@ extern "C" int cw_attention_decode_fused(const void* q, int q_stride, void* out,
                                          int page_size, int max_blocks, int num_pages, float scale, int window,
                                          int max_ctx, int split, const int* split_ptr, float* part_o, float* part_lse,
                                          int* counters, int fuse_store, const float* inv_freq, int rotary_dim,
-                                         const int* slots, int* status, cudaStream_t stream);
+                                         const int* slots, int stages, int* status, cudaStream_t stream);
 
 extern "C" int cw_attention_decode(const void* q, int q_stride, void* out, const void* k_cache, const void* v_cache,
                                    const int* block_tables, const int* ctx_lens, int S, int nh, int nkv, int hd,
@@ -497,7 +500,7 @@ extern "C" int cw_attention_decode(const void* q, int q_stride, void* out, const
                                    int split, const int* split_ptr, float* part_o, float* part_lse, int* counters, int* status, cudaStream_t stream) {
     return cw_attention_decode_fused(q, q_stride, out, const_cast<void*>(k_cache), const_cast<void*>(v_cache), block_tables,
                                      ctx_lens, S, nh, nkv, hd, page_size, max_blocks, num_pages, scale, window, max_ctx,
-                                     split, split_ptr, part_o, part_lse, counters, 0, nullptr, 0, nullptr, status, stream);
+                                     split, split_ptr, part_o, part_lse, counters, 0, nullptr, 0, nullptr, 0, status, stream);
 }
 
 // As cw_attention_decode; with fuse_store != 0, q is the [q | k | v] row buffer that the QKV product
@@ -508,7 +511,7 @@ extern "C" int cw_attention_decode_fused(const void* q, int q_stride, void* out,
                                          int page_size, int max_blocks, int num_pages, float scale, int window,
                                          int max_ctx, int split, const int* split_ptr, float* part_o, float* part_lse,
                                          int* counters, int fuse_store, const float* inv_freq, int rotary_dim,
-                                         const int* slots, int* status, cudaStream_t stream) {
+                                         const int* slots, int stages, int* status, cudaStream_t stream) {
     if (S == 0) return CW_OK;
     if (S < 0 || nh <= 0 || nkv <= 0 || nh % nkv != 0 || page_size <= 0 || max_blocks <= 0 || max_ctx <= 0)
         return CW_ERR_BAD_SIZE;
@@ -529,6 +532,7 @@ extern "C" int cw_attention_decode_fused(const void* q, int q_stride, void* out,
     p.rotary_dim = fuse_store && inv_freq != nullptr ? rotary_dim : 0;
     p.slots = slots; p.k_cache_w = (bf16*)k_cache; p.v_cache_w = (bf16*)v_cache;
     p.num_slots = num_pages * page_size;
+    p.stages = stages;
     // the grid is sized for the smallest split; a larger run-time split leaves the later CTAs idle
     if (split_ptr == nullptr && (split < MIN_SPLIT || split % TILE != 0)) return CW_ERR_BAD_SIZE;
     const int splits = (max_ctx + MIN_SPLIT - 1) / MIN_SPLIT;

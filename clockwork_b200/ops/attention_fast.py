@@ -29,7 +29,7 @@ def _configure() -> None:
     P, I, F, LL = c_void_p, c_int, c_float, c_longlong
     lib.cw_attention_decode.argtypes = [P, I, P, P, P, P, P, I, I, I, I, I, I, I, F, I, I, I, P, P, P, P, P, P]
     lib.cw_attention_decode.restype = c_int
-    lib.cw_attention_decode_fused.argtypes = [P, I, P, P, P, P, P, I, I, I, I, I, I, I, F, I, I, I, P, P, P, P, I, P, I, P, P, P]
+    lib.cw_attention_decode_fused.argtypes = [P, I, P, P, P, P, P, I, I, I, I, I, I, I, F, I, I, I, P, P, P, P, I, P, I, P, I, P, P]
     lib.cw_attention_decode_fused.restype = c_int
     lib.cw_attention_decode_workspace.argtypes = [I, I, I, I, I, POINTER(LL), POINTER(LL), POINTER(I)]
     lib.cw_attention_decode_workspace.restype = c_int
@@ -55,19 +55,33 @@ MIN_SPLIT = 256
 _SMS: dict[int, int] = {}
 
 
-def decode_split(num_seqs: int, num_heads: int, num_kv_heads: int, max_live_ctx: int, device=None) -> int:
-    """Tokens per CTA for a decode step: cut contexts so that about every SM gets a CTA, never finer
-    than 256 tokens; with many requests a CTA walks a whole context and no merge is needed.  The
-    result depends on the number of live requests and their longest context only."""
+def _pairs(num_seqs: int, num_heads: int, num_kv_heads: int) -> int:
+    groups = -(-(num_heads // num_kv_heads) // 16)
+    return max(1, num_seqs * num_kv_heads * groups)
+
+
+def _sm_count(device=None) -> int:
     index = torch.cuda.current_device() if device is None or device.index is None else device.index
     sms = _SMS.get(index)
     if sms is None:
         sms = _SMS[index] = torch.cuda.get_device_properties(index).multi_processor_count
-    groups = -(-(num_heads // num_kv_heads) // 16)
-    pairs = max(1, num_seqs * num_kv_heads * groups)
-    per_seq = max(1, sms // pairs)
+    return sms
+
+
+def decode_split(num_seqs: int, num_heads: int, num_kv_heads: int, max_live_ctx: int, device=None) -> int:
+    """Tokens per CTA for a decode step: cut contexts so that there are about three CTAs per SM (a
+    CTA has four warps; the others' warps cover its stalls), never finer than 256 tokens.  Measured
+    on B200 at contexts of about 1,150 tokens: 256 is best up to 32 requests, 384 at 64 and more.
+    The result depends on the number of live requests and their longest context only."""
+    per_seq = max(1, 3 * _sm_count(device) // _pairs(num_seqs, num_heads, num_kv_heads))
     split = -(-max(1, max_live_ctx) // per_seq)
     return max(MIN_SPLIT, -(-split // 64) * 64)
+
+
+def decode_stages(num_seqs: int, num_heads: int, num_kv_heads: int) -> int:
+    """Tiles in flight per CTA: four (one CTA per SM, lowest latency) while the step has few CTAs,
+    two (room for several CTAs per SM) from 16 requests of two KV heads on."""
+    return 4 if _pairs(num_seqs, num_heads, num_kv_heads) <= 16 else 2
 
 
 class _Decode:
@@ -83,12 +97,13 @@ class _Decode:
         return attention_decode(qkv, view.k_cache, view.v_cache, view.block_tables, ctx.ctx_lens, num_heads,
                                 num_kv_heads, head_dim, scale, window, max_ctx or ctx.max_ctx_len, ctx.status,
                                 split=split, split_dev=split_dev,
-                                fused=None if fused_position is None else (*fused_position, view.slots))
+                                fused=None if fused_position is None else (*fused_position, view.slots),
+                                stages=decode_stages(ctx.num_seqs, num_heads, num_kv_heads))
 
 
 def attention_decode(q, k_cache, v_cache, block_tables, ctx_lens, num_heads, num_kv_heads, head_dim, scale, window,
                      max_ctx: int, status, split: int | None = None, split_dev: torch.Tensor | None = None,
-                     fused: tuple | None = None) -> torch.Tensor:
+                     fused: tuple | None = None, stages: int = 0) -> torch.Tensor:
     """One query token per request: ``q`` [S, >= nh*hd] (row s belongs to request s), ``ctx_lens`` [S]
     the tokens of each request in the cache (its own included).  ``split``: tokens per CTA (a multiple
     of 64, at least 256; default: chosen by ``decode_split``), or ``split_dev``, the same as an int32
@@ -124,7 +139,7 @@ def attention_decode(q, k_cache, v_cache, block_tables, ctx_lens, num_heads, num
         _ptr(q), q.stride(0), _ptr(out), _ptr(k_cache), _ptr(v_cache), _ptr(block_tables), _ptr(ctx_lens), s, num_heads,
         num_kv_heads, head_dim, k_cache.shape[1], block_tables.shape[1], k_cache.shape[0], float(scale), int(window or 0),
         int(max_ctx), int(split or 0), _ptr(split_dev), _ptr(st["part_o"]), _ptr(st["part_lse"]), _ptr(st["counters"]),
-        1 if fused is not None else 0, _ptr(inv_freq), int(rotary_dim), _ptr(slots), _ptr(status), _stream()), "attention_decode")
+        1 if fused is not None else 0, _ptr(inv_freq), int(rotary_dim), _ptr(slots), int(stages), _ptr(status), _stream()), "attention_decode")
     return out
 
 
