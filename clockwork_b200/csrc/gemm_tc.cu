@@ -9,10 +9,10 @@
 // shared memory (128-byte swizzle) and D[feature, token] in TMEM.  This one shape serves decode
 // (BN = 16..64 tokens, the step is a stream of weight tiles from HBM) and prefill (BN = 128/256).
 // When the grid would leave SMs idle the K dimension is split over blockIdx.z and the CTAs of one
-// tile are launched as a thread-block cluster: each stages its partial accumulator in its own
-// shared memory, and after a cluster barrier every CTA finishes a slice of the tile's columns,
-// adding the partials of all ranks in rank order through distributed shared memory.  No global
-// scratch, no atomics, and the result does not depend on which CTA finished first.
+// tile are launched as a thread-block cluster: each pushes the columns of its partial accumulator
+// into the shared memory of the column's owner (distributed shared memory), and after one cluster
+// barrier every CTA adds what it received, in rank order, and finishes its slice of columns.  No
+// global scratch, no atomics, and the result does not depend on which CTA finished first.
 //
 // Warp roles (128 threads): warp 0 lane 0 issues TMA loads, warp 1 lane 0 issues the MMAs, warp 2
 // allocates and frees TMEM; all four warps run the epilogue (warp w reads TMEM lanes 32w..32w+31).
@@ -29,6 +29,7 @@
 #define BK 64
 #define THREADS 128
 #define WAIT_CYCLES 4000000000LL
+#define MAX_SPLITS 8  // the portable cluster size
 
 // ---------------------------------------------------------------------------------------------
 // PTX wrappers
@@ -136,13 +137,14 @@ __device__ __forceinline__ uint32_t cluster_rank() {
 __device__ __forceinline__ void cluster_sync() {
     asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
-// One float from the shared memory of the CTA with the given rank in this cluster.
-__device__ __forceinline__ float ld_dsmem(uint32_t local_addr, uint32_t rank) {
+// The address, in the cluster's shared window, of `local_addr` inside the CTA with the given rank.
+__device__ __forceinline__ uint32_t dsmem_addr(uint32_t local_addr, uint32_t rank) {
     uint32_t remote;
-    float v;
     asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
-    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
-    return v;
+    return remote;
+}
+__device__ __forceinline__ void st_dsmem(uint32_t remote_addr, float v) {
+    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote_addr), "f"(v) : "memory");
 }
 
 // Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes (64 bf16) with the
@@ -181,13 +183,18 @@ struct Cfg {
     static constexpr int A_BYTES = BM * BK * 2;                     // 16 KB
     static constexpr int B_BYTES = BN * BK * 2;
     static constexpr int STAGE_BYTES = A_BYTES * (SWIGLU ? 2 : 1) + B_BYTES;
+    static constexpr int ACC_COLS = BN * (SWIGLU ? 2 : 1);
+    // Split-K inbox: the partial columns that the other CTAs of the cluster push into this CTA.  It
+    // must not overlap the operand stages (a peer may push while this CTA's MMAs still read them).
+    // Tiles too large to leave room for it are never split.
+    static constexpr bool CAN_SPLIT = BN <= 64 || (BN == 128 && !SWIGLU);
+    static constexpr int INBOX_BYTES = CAN_SPLIT ? (BN + MAX_SPLITS) * (SWIGLU ? 2 : 1) * BM * 4 : 0;
     // as many stages as fit (at most 8): a decode CTA is alone on its SM and keeps that many weight
     // tiles in flight from HBM
-    static constexpr int MAX_STAGES = (200 * 1024) / STAGE_BYTES;
+    static constexpr int MAX_STAGES = (200 * 1024 - INBOX_BYTES) / STAGE_BYTES;
     static constexpr int STAGES = MAX_STAGES > 8 ? 8 : MAX_STAGES;
-    static constexpr int ACC_COLS = BN * (SWIGLU ? 2 : 1);
     static constexpr int TMEM_COLS = ACC_COLS <= 32 ? 32 : (ACC_COLS <= 64 ? 64 : (ACC_COLS <= 128 ? 128 : (ACC_COLS <= 256 ? 256 : 512)));
-    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment*/ + 256 /*barriers*/;
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + INBOX_BYTES + 1024 /*alignment*/ + 1024 /*barriers*/;
 };
 
 template <int BN, bool SWIGLU>
@@ -295,28 +302,39 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     const int row = warp * 32 + lane;  // feature within the tile
     const int f = m0 + row;
     const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16);
-    // With the inner dimension split, the CTAs of one tile form a cluster.  Each stages its partial
-    // accumulator in its own shared memory (the operand stages are free by now), the cluster
-    // synchronises, and every CTA then finishes a slice of the tile's columns: it adds the partials
-    // of all ranks in rank order, read through distributed shared memory, and runs the epilogue.
-    float* stage = (float*)smem;  // [ACC_COLS][BM]
+    // With the inner dimension split, the CTAs of one tile form a cluster and each finishes a slice of
+    // the tile's columns.  A CTA pushes every column of its partial accumulator into the inbox of the
+    // column's owner (distributed shared memory, slot = sender's rank), the cluster synchronises once,
+    // and each owner adds the partials it received in rank order.  After the barrier nobody touches
+    // another CTA's memory, so CTAs leave independently.
+    float* stage = (float*)smem;  // unsplit tiles: [token][feature] staging for the TMA store
     const uint32_t stage_addr = smem_u32(stage);
+    float* inbox = (float*)(smem + C::STAGES * C::STAGE_BYTES + 1024);  // [rank][column slot][BM]
     int c_begin = 0, c_end = BN;
+    const int per = (BN + p.splits - 1) / p.splits;        // columns per owner
+    const int slots = per * (SWIGLU ? 2 : 1);              // inbox column slots per sender
     if (p.splits > 1) {
-        for (int c = 0; c < C::ACC_COLS; c += 16) {
-            float v[16];
+        const uint32_t my_rank = cluster_rank();
+        const uint32_t inbox_addr = smem_u32(inbox);
+        for (int c = 0; c < BN; c += 16) {
+            float v[16], v2[16];
             if (acc_ready) {
                 tmem_ld16(taddr + c, v);
+                if (SWIGLU) tmem_ld16(taddr + BN + c, v2);
             } else {
 #pragma unroll
-                for (int j = 0; j < 16; ++j) v[j] = 0.f;
+                for (int j = 0; j < 16; ++j) v[j] = v2[j] = 0.f;
             }
 #pragma unroll
-            for (int j = 0; j < 16; ++j) stage[(c + j) * BM + row] = v[j];
+            for (int j = 0; j < 16; ++j) {
+                const int col = c + j, owner = col / per, local = col - owner * per;
+                const uint32_t a = dsmem_addr(inbox_addr + (uint32_t)(((my_rank * slots + local) * BM + row) * 4), owner);
+                st_dsmem(a, v[j]);
+                if (SWIGLU) st_dsmem(a + (uint32_t)(per * BM * 4), v2[j]);
+            }
         }
         cluster_sync();
-        const int per = (BN + p.splits - 1) / p.splits;
-        c_begin = min(BN, (int)cluster_rank() * per);
+        c_begin = min(BN, (int)my_rank * per);
         c_end = min(BN, c_begin + per);
     }
     const float bias = (p.bias != nullptr && f < p.N) ? p.bias[f] : 0.f;
@@ -353,28 +371,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         } else {
 #pragma unroll
             for (int j = 0; j < 16; ++j) g[j] = u[j] = 0.f;
-            // eight columns of two ranks at a time: up to 16 (32) remote loads in flight
+            for (int s = 0; s < p.splits; ++s) {  // rank order; all reads are of this CTA's own inbox
+                const float* part = inbox + ((size_t)s * slots + (c - c_begin)) * BM + row;
 #pragma unroll
-            for (int j0 = 0; j0 < 16; j0 += 8) {
-                if (j0 >= ncols) break;
-                for (int s0 = 0; s0 < p.splits; s0 += 2) {
-                    float vg[2][8], vu[2][8];
-#pragma unroll
-                    for (int ds = 0; ds < 2; ++ds)
-#pragma unroll
-                        for (int j = 0; j < 8; ++j) {
-                            const bool in = s0 + ds < p.splits && j0 + j < ncols;
-                            const uint32_t a = stage_addr + (uint32_t)(((c + j0 + j) * BM + row) * 4);
-                            vg[ds][j] = in ? ld_dsmem(a, s0 + ds) : 0.f;
-                            if (SWIGLU) vu[ds][j] = in ? ld_dsmem(a + (uint32_t)(BN * BM * 4), s0 + ds) : 0.f;
-                        }
-#pragma unroll
-                    for (int ds = 0; ds < 2; ++ds)  // rank order
-#pragma unroll
-                        for (int j = 0; j < 8; ++j) {
-                            g[j0 + j] += vg[ds][j];
-                            if (SWIGLU) u[j0 + j] += vu[ds][j];
-                        }
+                for (int j = 0; j < 16; ++j) {
+                    if (j < ncols) {
+                        g[j] += part[j * BM];
+                        if (SWIGLU) u[j] += part[(per + j) * BM];
+                    }
                 }
             }
         }
@@ -410,7 +414,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             }
         }
     }
-    if (p.splits > 1) cluster_sync();  // peers may still be reading this CTA's staged partials
     // ---- teardown ---------------------------------------------------------------------------------
     if (*give_up) {
         if (tid == 0) cw_report(p.status, CW_ST_WAIT_TIMEOUT, blockIdx.x, blockIdx.z);
@@ -478,8 +481,6 @@ struct Plan {
     int bn, splits, kb_per_split, tiles;
 };
 
-#define MAX_SPLITS 8  // the portable cluster size
-
 static Plan make_plan(int T, int N, int K, bool swiglu, int sm_count) {
     Plan pl;
     const int cap = swiglu ? 128 : 256;
@@ -487,7 +488,8 @@ static Plan make_plan(int T, int N, int K, bool swiglu, int sm_count) {
     pl.tiles = ((N + BM - 1) / BM) * ((T + pl.bn - 1) / pl.bn);
     const int num_kb = (K + BK - 1) / BK;
     int splits = 1;
-    if (pl.tiles * 2 <= sm_count) {
+    const bool can_split = pl.bn <= 64 || (pl.bn == 128 && !swiglu);  // Cfg::CAN_SPLIT
+    if (can_split && pl.tiles * 2 <= sm_count) {
         // One wave: as many CTAs as SMs at most, each with as much of K as possible.  A CTA costs a
         // few microseconds of set-up and epilogue whatever it streams, so fewer, longer CTAs win
         // as long as every SM has one.
@@ -506,7 +508,9 @@ template <int BN, bool SWIGLU>
 static int launch(const CUtensorMap& mw, const CUtensorMap& mw2, const CUtensorMap& mx, const CUtensorMap& mc,
                   const GemmParams& p, dim3 grid, cudaStream_t stream) {
     using C = Cfg<BN, SWIGLU>;
-    static_assert(C::ACC_COLS * BM * 4 <= C::STAGES * C::STAGE_BYTES, "staged partials must fit in the operand stages");
+    static_assert(C::ACC_COLS * BM * 4 <= C::STAGES * C::STAGE_BYTES, "a staged tile must fit in the operand stages");
+    static_assert(C::STAGES >= 2, "too few operand stages");
+    if (grid.z > 1 && !C::CAN_SPLIT) return CW_ERR_UNSUPPORTED;
     static bool configured = false;
     if (!configured) {
         if (cudaFuncSetAttribute(gemm_tc_kernel<BN, SWIGLU>, cudaFuncAttributeMaxDynamicSharedMemorySize,
