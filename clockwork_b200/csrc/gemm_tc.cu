@@ -172,6 +172,7 @@ struct GemmParams {
     int num_kb;           // ceil(K / 64)
     int kb_per_split;     // k-blocks per blockIdx.z
     int splits;
+    int bn;               // persistent kernel: token-tile width chosen at run time (multiple of 16)
     int tma_store;        // 1: unsplit tiles leave through shared memory and one TMA store / reduce-add
     const float* bias;    // [N] or null
     void* C;
@@ -433,6 +434,203 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 }
 
 // ---------------------------------------------------------------------------------------------
+// Persistent form for large problems (more output tiles than SMs, no split): one CTA per SM walks
+// tiles; the accumulator is double-buffered in TMEM so that the epilogue of one tile (TMEM ->
+// registers -> shared memory -> TMA store / reduce-add, 16 tokens at a time) runs while the MMAs of
+// the next tile proceed.  Warps: 0 TMA producer, 1 MMA issuer and TMEM owner, 2..5 epilogue.
+// ---------------------------------------------------------------------------------------------
+#define P_THREADS 192
+#define P_CHUNK 16  // tokens per epilogue store
+#define MAX_SMEM_BYTES (227 * 1024)
+
+template <int BN, bool SWIGLU>
+struct PCfg {
+    static constexpr int A_BYTES = BM * BK * 2;
+    static constexpr int B_BYTES = BN * BK * 2;
+    static constexpr int STAGE_BYTES = A_BYTES * (SWIGLU ? 2 : 1) + B_BYTES;
+    static constexpr int ACC_COLS = BN * (SWIGLU ? 2 : 1);
+    static constexpr int TMEM_COLS = 2 * ACC_COLS <= 256 ? 256 : 512;
+    static constexpr int OUT_BYTES = 2 * P_CHUNK * BM * 4;  // two staging buffers of [16 tokens][128 features]
+    static constexpr int STAGES = (MAX_SMEM_BYTES - 2048 - OUT_BYTES) / STAGE_BYTES;
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + OUT_BYTES + 1024 + 1024;
+    static_assert(2 * ACC_COLS <= 512, "two accumulators must fit in tensor memory");
+    static_assert(STAGES >= 3, "too few operand stages");
+};
+
+template <int BN, bool SWIGLU>
+__global__ void __launch_bounds__(P_THREADS)
+gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_w2,
+                          const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_c,
+                          const GemmParams p) {
+    using C = PCfg<BN, SWIGLU>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint8_t* out_s = smem + C::STAGES * C::STAGE_BYTES;
+    uint64_t* bars = (uint64_t*)(out_s + C::OUT_BYTES);
+    // bars: full[S], empty[S], acc_full[2], acc_empty[2]
+    uint32_t* tmem_slot = (uint32_t*)(bars + 2 * C::STAGES + 4);
+    volatile int* give_up = (volatile int*)(tmem_slot + 1);
+
+    pdl_launch_dependents();
+    pdl_wait();
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + C::STAGES);
+    const uint32_t accf0 = smem_u32(bars + 2 * C::STAGES), acce0 = smem_u32(bars + 2 * C::STAGES + 2);
+    const int bn = p.bn;  // <= BN; the accumulators keep their places for the widest tile
+    const int m_tiles = (p.N + BM - 1) / BM, n_tiles = (p.T + bn - 1) / bn;
+    const uint32_t stage_tx = C::A_BYTES * (SWIGLU ? 2 : 1) + bn * BK * 2;
+    const int tiles = m_tiles * n_tiles;
+
+    if (tid == 0) {
+        for (int s = 0; s < C::STAGES; ++s) {
+            mbar_init(full0 + 8 * s, 1);
+            mbar_init(empty0 + 8 * s, 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(accf0 + 8 * b, 1);
+            mbar_init(acce0 + 8 * b, 1);
+        }
+        *give_up = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) tmem_alloc(smem_u32(tmem_slot), C::TMEM_COLS);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0 && lane == 0) {
+        // ---- TMA producer: runs ahead over tiles, bounded by the ring only ----------------------------
+        int i = 0;  // k-blocks issued so far (over all tiles)
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
+            const int m0 = (tile % m_tiles) * BM, n0 = (tile / m_tiles) * bn;
+            for (int kb = 0; kb < p.num_kb; ++kb, ++i) {
+                const int s = i % C::STAGES;
+                ok = mbar_wait(empty0 + 8 * s, ((i / C::STAGES) & 1) ^ 1, give_up);
+                if (!ok) break;
+                const uint32_t a_dst = smem_u32(smem + s * C::STAGE_BYTES);
+                const uint32_t bar = full0 + 8 * s;
+                mbar_expect_tx(bar, stage_tx);
+                tma_load_2d(a_dst, &map_w, kb * BK, m0, bar);
+                if (SWIGLU) tma_load_2d(a_dst + C::A_BYTES, &map_w2, kb * BK, m0, bar);
+                tma_load_2d(a_dst + C::A_BYTES * (SWIGLU ? 2 : 1), &map_x, kb * BK, n0, bar);
+            }
+        }
+        if (*give_up) {
+            // wait, bounded, for the copies still in flight before the CTA's shared memory goes away
+            for (int k = max(0, i - C::STAGES); k < i; ++k) {
+                const uint32_t bar = full0 + 8 * (k % C::STAGES);
+                const long long t0 = clock64();
+                while (!mbar_try_wait(bar, (k / C::STAGES) & 1) && clock64() - t0 < WAIT_CYCLES) {
+                }
+            }
+        }
+    } else if (warp == 1 && lane == 0) {
+        // ---- MMA issuer: tile `it` accumulates into TMEM buffer it & 1 -------------------------------
+        const uint32_t idesc = instr_desc(BM, bn);
+        int i = 0, it = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, ++it) {
+            const int buf = it & 1;
+            ok = mbar_wait(acce0 + 8 * buf, ((it >> 1) & 1) ^ 1, give_up);  // the epilogue has drained it
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t acc = tmem_base + buf * C::ACC_COLS;
+            for (int kb = 0; kb < p.num_kb; ++kb, ++i) {
+                const int s = i % C::STAGES;
+                ok = mbar_wait(full0 + 8 * s, (i / C::STAGES) & 1, give_up);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t a_addr = smem_u32(smem + s * C::STAGE_BYTES);
+                const uint64_t adesc = smem_desc_sw128(a_addr);
+                const uint64_t a2desc = smem_desc_sw128(a_addr + C::A_BYTES);
+                const uint64_t bdesc = smem_desc_sw128(a_addr + C::A_BYTES * (SWIGLU ? 2 : 1));
+#pragma unroll
+                for (int k = 0; k < BK / 16; ++k) {
+                    const uint32_t accumulate = (kb > 0 || k > 0) ? 1u : 0u;
+                    umma_bf16(acc, adesc + 2 * k, bdesc + 2 * k, idesc, accumulate);
+                    if (SWIGLU) umma_bf16(acc + BN, a2desc + 2 * k, bdesc + 2 * k, idesc, accumulate);
+                }
+                umma_commit(empty0 + 8 * s);
+            }
+            if (ok) umma_commit(accf0 + 8 * buf);
+        }
+    } else if (warp >= 2) {
+        // ---- epilogue warps: warp w reads TMEM lanes 32 (w % 4) .. +31 -------------------------------
+        const int quarter = warp & 3;
+        const int row = quarter * 32 + lane;
+        const int etid = tid - 64;  // 0..127 among the epilogue threads
+        const bool wide = !SWIGLU && p.epilogue != 0;
+        int it = 0, chunk_no = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, ++it) {
+            const int buf = it & 1;
+            const int m0 = (tile % m_tiles) * BM, n0 = (tile / m_tiles) * bn;
+            const int f = m0 + row;
+            ok = mbar_wait(accf0 + 8 * buf, (it >> 1) & 1, give_up);
+            {
+                // one decision for all 128 threads: they meet at named barriers below
+                uint32_t all_ok;
+                asm volatile(
+                    "{ .reg .pred p, q; setp.ne.u32 q, %1, 0; bar.red.and.pred p, 3, 128, q; selp.u32 %0, 1, 0, p; }"
+                    : "=r"(all_ok)
+                    : "r"((uint32_t)ok)
+                    : "memory");
+                ok = all_ok != 0;
+            }
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t taddr = tmem_base + buf * C::ACC_COLS + ((uint32_t)(quarter * 32) << 16);
+            const float bias = (p.bias != nullptr && f < p.N) ? p.bias[f] : 0.f;
+            for (int c = 0; c < bn; c += P_CHUNK, ++chunk_no) {
+                float g[16], u[16];
+                tmem_ld16(taddr + c, g);
+                if (SWIGLU) tmem_ld16(taddr + BN + c, u);
+                if (c + P_CHUNK >= bn) {
+                    // the accumulator has been read out: hand the buffer back to the MMA warp
+                    tc_fence_before();
+                    asm volatile("bar.sync 1, 128;" ::: "memory");
+                    if (etid == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(acce0 + 8 * buf) : "memory");
+                }
+                float* st32 = (float*)(out_s + (chunk_no & 1) * (C::OUT_BYTES / 2));
+                // the store that used this staging buffer two chunks ago must have read it
+                if (etid == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+                asm volatile("bar.sync 2, 128;" ::: "memory");
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    float v = g[j] + bias;
+                    if (SWIGLU) v = __fdividef(v, 1.0f + __expf(-v)) * u[j];
+                    if (wide)
+                        st32[j * BM + row] = v;
+                    else
+                        ((bf16*)st32)[j * BM + row] = __float2bfloat16_rn(v);
+                }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (etid == 0 && n0 + c < p.T) {
+                    const bool add = !SWIGLU && p.epilogue == 1;
+                    if (add)
+                        asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.bulk_group [%0, {%2, %3}], [%1];"
+                                     ::"l"(&map_c), "r"(smem_u32(st32)), "r"(m0), "r"(n0 + c) : "memory");
+                    else
+                        asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+                                     ::"l"(&map_c), "r"(smem_u32(st32)), "r"(m0), "r"(n0 + c) : "memory");
+                    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                }
+            }
+        }
+        if (etid == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");  // all stores done before exit
+    }
+    __syncwarp();
+    if (*give_up && tid == 0) cw_report(p.status, CW_ST_WAIT_TIMEOUT, blockIdx.x, -1);
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem_base, C::TMEM_COLS);
+}
+
+// ---------------------------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -479,17 +677,40 @@ static int make_map_c(CUtensorMap* map, const void* ptr, int T, int N, long long
 
 struct Plan {
     int bn, splits, kb_per_split, tiles;
+    bool persistent;  // bn is then any multiple of 16 and the persistent kernel runs
 };
 
-static Plan make_plan(int T, int N, int K, bool swiglu, int sm_count) {
+// Token-tile width for the persistent kernel.  A k-block costs a tile about 256 + 2 bn cycles of
+// shared-memory traffic (the weight tile is loaded whatever bn is, SwiGLU loads two) and the CTAs
+// run ceil(tiles / SMs) rounds; the width with the least rounds x cost wins, the wider on a tie.
+static int balanced_bn(int T, int N, bool swiglu, int sm_count) {
+    const int cap = swiglu ? 128 : 256;
+    const int m_tiles = (N + BM - 1) / BM;
+    long long best_cost = -1;
+    int best = cap;
+    for (int bn = cap; bn >= 64; bn -= 16) {
+        const long long tiles = (long long)m_tiles * ((T + bn - 1) / bn);
+        const long long rounds = (tiles + sm_count - 1) / sm_count;
+        const long long cost = rounds * ((swiglu ? 512 : 256) + 2 * bn);
+        if (best_cost < 0 || cost < best_cost) {
+            best_cost = cost;
+            best = bn;
+        }
+    }
+    return best;
+}
+
+static Plan make_plan(int T, int N, int K, bool swiglu, int sm_count, bool c_by_tma = true) {
     Plan pl;
     const int cap = swiglu ? 128 : 256;
+    pl.persistent = T > 256 && sm_count > 0 && c_by_tma;  // its epilogue has no other way out than TMA
     pl.bn = T <= 16 ? 16 : (T <= 32 ? 32 : (T <= 64 ? 64 : (T <= 128 ? 128 : cap)));
+    if (pl.persistent) pl.bn = balanced_bn(T, N, swiglu, sm_count);
     pl.tiles = ((N + BM - 1) / BM) * ((T + pl.bn - 1) / pl.bn);
     const int num_kb = (K + BK - 1) / BK;
     int splits = 1;
     const bool can_split = pl.bn <= 64 || (pl.bn == 128 && !swiglu);  // Cfg::CAN_SPLIT
-    if (can_split && pl.tiles * 2 <= sm_count) {
+    if (!pl.persistent && can_split && pl.tiles * 2 <= sm_count) {
         // One wave: as many CTAs as SMs at most, each with as much of K as possible.  A CTA costs a
         // few microseconds of set-up and epilogue whatever it streams, so fewer, longer CTAs win
         // as long as every SM has one.
@@ -521,6 +742,21 @@ static int launch(const CUtensorMap& mw, const CUtensorMap& mw2, const CUtensorM
     return cw_launch(gemm_tc_kernel<BN, SWIGLU>, grid, dim3(THREADS), C::SMEM_BYTES, stream, grid.z, mw, mw2, mx, mc, p);
 }
 
+template <int BN, bool SWIGLU>
+static int launch_persistent(const CUtensorMap& mw, const CUtensorMap& mw2, const CUtensorMap& mx,
+                             const CUtensorMap& mc, const GemmParams& p, int ctas, cudaStream_t stream) {
+    using C = PCfg<BN, SWIGLU>;
+    static bool configured = false;
+    if (!configured) {
+        if (cudaFuncSetAttribute(gemm_tc_persistent_kernel<BN, SWIGLU>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 C::SMEM_BYTES) != cudaSuccess)
+            return (int)cudaGetLastError();
+        configured = true;
+    }
+    return cw_launch(gemm_tc_persistent_kernel<BN, SWIGLU>, dim3(ctas), dim3(P_THREADS), C::SMEM_BYTES, stream, 1, mw, mw2,
+                     mx, mc, p);
+}
+
 // How a call would be tiled: token tile, splits of the inner dimension (= cluster size), CTAs.
 extern "C" int cw_gemm_tc_plan(int T, int N, int K, int swiglu, int sm_count, int* bn, int* splits, int* ctas) {
     const Plan pl = make_plan(T, N, K, swiglu != 0, sm_count);
@@ -543,24 +779,32 @@ extern "C" int cw_gemm_tc(const void* X, const void* W, const void* W2, const fl
         return CW_ERR_UNSUPPORTED;
     if (load_encode() != 0) return CW_ERR_UNSUPPORTED;
     const bool swiglu = W2 != nullptr;
-    const Plan pl = make_plan(T, N, K, swiglu, sm_count);
+    // C leaves through TMA when its rows are 16-byte multiples at a 16-byte base and the tile is not split
+    const bool c_f32 = !swiglu && epilogue != 0;
+    const long long c_row_bytes = (long long)ldc * (c_f32 ? 4 : 2);
+    const bool c_by_tma = c_row_bytes % 16 == 0 && ((uintptr_t)C & 15) == 0;
+    const Plan pl = make_plan(T, N, K, swiglu, sm_count, c_by_tma);
     CUtensorMap mw, mw2, mx;
     if (make_map(&mw, W, N, K, K, BM) != 0) return CW_ERR_UNSUPPORTED;
     if (make_map(&mw2, swiglu ? W2 : W, N, K, K, BM) != 0) return CW_ERR_UNSUPPORTED;
     if (make_map(&mx, X, T, K, ldx, pl.bn) != 0) return CW_ERR_UNSUPPORTED;
-    // C leaves through TMA when its rows are 16-byte multiples at a 16-byte base and the tile is not split
-    const bool c_f32 = !swiglu && epilogue != 0;
-    const long long c_row_bytes = (long long)ldc * (c_f32 ? 4 : 2);
-    const bool tma_store = pl.splits == 1 && c_row_bytes % 16 == 0 && ((uintptr_t)C & 15) == 0;
+    const bool tma_store = pl.splits == 1 && c_by_tma;
+    // prompt portions: the persistent kernel, whose epilogue overlaps the next tile's MMAs
+    const bool persistent = pl.persistent;
     CUtensorMap mc = mx;
-    if (tma_store && make_map_c(&mc, C, T, N, ldc, pl.bn, c_f32) != 0) return CW_ERR_UNSUPPORTED;
+    if (tma_store && make_map_c(&mc, C, T, N, ldc, persistent ? P_CHUNK : pl.bn, c_f32) != 0) return CW_ERR_UNSUPPORTED;
     GemmParams p;
     p.tma_store = tma_store ? 1 : 0;
     p.T = T; p.N = N; p.K = K; p.ldc = ldc; p.epilogue = epilogue;
     p.num_kb = (K + BK - 1) / BK; p.kb_per_split = pl.kb_per_split; p.splits = pl.splits;
-    p.bias = bias; p.C = C; p.status = status;
+    p.bias = bias; p.C = C; p.status = status; p.bn = pl.bn;
     dim3 grid((N + BM - 1) / BM, (T + pl.bn - 1) / pl.bn, pl.splits);
     if (grid.y > 65535) return CW_ERR_BAD_SIZE;
+    if (persistent) {
+        const int ctas = pl.tiles < sm_count ? pl.tiles : sm_count;
+        return swiglu ? launch_persistent<128, true>(mw, mw2, mx, mc, p, ctas, stream)
+                      : launch_persistent<256, false>(mw, mw2, mx, mc, p, ctas, stream);
+    }
 #define CW_CASE(bn)                                                                       \
     case bn:                                                                              \
         return swiglu ? launch<bn, true>(mw, mw2, mx, mc, p, grid, stream)                \

@@ -303,6 +303,8 @@ TC_SHAPES = [
     # T, N, K: decode sizes (inner dimension split over CTAs), ragged edges, prefill sizes
     (1, 2048, 1536), (8, 1536, 8960), (8, 200, 72), (16, 1536, 1536), (17, 384, 200), (64, 2048, 1536),
     (100, 130, 264), (300, 1000, 512), (512, 1536, 1536), (2048, 2048, 1536),
+    # more tiles than SMs: the persistent kernel, two to three tiles per CTA, ragged in both directions
+    (2100, 3000, 264), (2048, 5000, 512),
 ]
 
 
@@ -339,7 +341,8 @@ def test_gemm_tc_against_float64(ops, gemm_tc, t, n, k):
     ops.raise_on_status(gemm_tc.status(DEV))
 
 
-@pytest.mark.parametrize("t,n,k", [(8, 8960, 1536), (33, 200, 96), (64, 1000, 1536), (700, 520, 256)])
+@pytest.mark.parametrize("t,n,k", [(8, 8960, 1536), (33, 200, 96), (64, 1000, 1536), (700, 520, 256),
+                                   (2100, 5000, 264)])
 def test_gemm_tc_swiglu(ops, gemm_tc, t, n, k):
     x = rand(t, k, dtype=torch.bfloat16)
     wg, wu = rand(n, k, dtype=torch.bfloat16, scale=0.05, seed=1), rand(n, k, dtype=torch.bfloat16, scale=0.05, seed=2)
