@@ -1,0 +1,430 @@
+// Paged causal attention for prompt portions on the 5th-generation tensor cores (tcgen05).
+//
+// A CTA owns 128 query tokens of one request and one query head (the 128 lanes of tensor memory)
+// and walks the request's keys in tiles of 128 tokens, fetched page by page from the cache by TMA
+// through the block table.  Per tile:
+//
+//     S  = Q K^T           tcgen05.mma, Q and K both K-major in shared memory, S in TMEM
+//     P  = 2^(S c - m)     softmax warps: one thread per query row reads its row of S from TMEM
+//                          (no shuffles), float32 statistics, P rounded to bfloat16 into shared memory
+//     O' = P V             tcgen05.mma, P K-major, V as it lies in the cache (head dimension
+//                          contiguous = MN-major B operand), O' in TMEM
+//     O  = (O + O'_prev) * 2^(m_prev - m)   in registers of the row's thread
+//
+// S and O' are double buffered in TMEM (2 x 128 + 2 x HD columns), so that the MMAs of tile j+1 and
+// the loads of later tiles run while the softmax warps work on tile j.  K and V tiles share one ring
+// of shared-memory slots.  Warps (192 threads): 0 TMA producer, 1 MMA issuer and TMEM owner, 2..5
+// softmax (warp w owns TMEM lanes 32 (w % 4) .. +31).
+//
+// Reference: clockwork/kernels/attention.py:68-96 (gather the context through one block table, then
+// dense causal attention with the query aligned to the end of the context, :45-65) and
+// clockwork/engine/model.py:103-118.  One launch covers every portion of the batch: the host lists
+// (request, first query row) work items, one per 128 query tokens; a decoded token is a portion of
+// length one and may ride along.
+//
+// Key slots past the end of a request's context are fetched from page 0 and multiplied by
+// probabilities that are exactly zero; the cache pool is zero-initialised and only ever holds
+// finite values, so they cannot leak.  Every wait is bounded (CW_ST_WAIT_TIMEOUT in the status
+// words, then the kernel frees TMEM and returns).
+#include "tc_common.cuh"
+
+#define AQ 128  // query rows per CTA
+#define AK 128  // keys per tile
+#define A_THREADS 192
+#define A_MAX_SMEM (227 * 1024)
+
+struct PrefillTcParams {
+    bf16* out;
+    const int* block_tables; const int* q_start; const int* ctx_lens;
+    const int* item_seq; const int* item_q0;
+    int nh, nkv, page_size, page_shift, max_blocks, num_pages;
+    float scale; int window;
+    int* status;
+};
+
+template <int HD>
+struct ACfg {
+    static constexpr int CB = HD / 64;                  // 64-element (128-byte) column blocks per row
+    static constexpr int BLOCK_BYTES = 128 * 128;       // [128 rows][64 bf16], 128-byte swizzle
+    static constexpr int Q_BYTES = CB * BLOCK_BYTES;
+    static constexpr int P_BYTES = (AK / 64) * BLOCK_BYTES;
+    static constexpr int SLOT_BYTES = CB * BLOCK_BYTES;  // one K or one V tile
+    static constexpr int FIT = (A_MAX_SMEM - 2048 - Q_BYTES - P_BYTES) / SLOT_BYTES;
+    static constexpr int NSLOTS = FIT > 8 ? 8 : FIT;
+    static constexpr int SMEM_BYTES = Q_BYTES + P_BYTES + NSLOTS * SLOT_BYTES + 2048;
+    static constexpr int O_COL = 2 * AK;                 // S buffers at columns 0 and 128, O' after them
+    static constexpr int TMEM_COLS = 512;
+    static_assert(NSLOTS >= 4, "too few key/value slots");
+    static_assert(O_COL + 2 * HD <= TMEM_COLS, "accumulators do not fit in tensor memory");
+};
+
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int x, int y, int z, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y), "r"(z)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float* v) {
+    uint32_t r[32];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+// Descriptor of an MN-major operand with the 128-byte swizzle: rows of the K dimension are 128 bytes
+// (64 contiguous elements of the MN dimension), groups of 8 rows are 1024 bytes apart (stride byte
+// offset) and the next 64 elements of the MN dimension lie `mn_block_bytes` further (leading byte offset).
+__device__ __forceinline__ uint64_t smem_desc_mn_sw128(uint32_t addr, uint32_t mn_block_bytes) {
+    uint64_t d = 0;
+    d |= (uint64_t)((addr >> 4) & 0x3FFF);
+    d |= (uint64_t)((mn_block_bytes >> 4) & 0x3FFF) << 16;
+    d |= (uint64_t)(1024 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+template <int HD>
+__global__ void __launch_bounds__(A_THREADS)
+attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                       const __grid_constant__ CUtensorMap map_v, const PrefillTcParams p) {
+    using C = ACfg<HD>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint8_t* q_s = smem;
+    uint8_t* p_s = q_s + C::Q_BYTES;
+    uint8_t* slots = p_s + C::P_BYTES;
+    uint64_t* bars = (uint64_t*)(slots + C::NSLOTS * C::SLOT_BYTES);
+    // bars: q_full, p_full, s_full[2], o_full[2], full[NSLOTS], empty[NSLOTS]
+    uint32_t* tmem_slot = (uint32_t*)(bars + 6 + 2 * C::NSLOTS);
+    volatile int* give_up = (volatile int*)(tmem_slot + 1);
+
+    pdl_launch_dependents();
+    pdl_wait();
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int h = blockIdx.x, item = blockIdx.y;
+    const int s = p.item_seq[item], q0 = p.item_q0[item];
+    const int kvh = h / (p.nh / p.nkv);
+    const int row0 = p.q_start[s], q_len = p.q_start[s + 1] - row0;
+    const int ctx = p.ctx_lens[s];
+    const int pos0 = ctx - q_len + q0;           // position of the tile's first query
+    const int nq = min(AQ, q_len - q0);          // query rows in this tile
+    const int kv_hi = pos0 + nq;                 // keys [.., kv_hi) are visible to the last row
+    const int kv_lo = p.window > 0 ? max(0, pos0 + 1 - p.window) : 0;
+    const int tile_lo = kv_lo / AK * AK;         // key tiles start at multiples of 128 whatever the portion
+    const int ntiles = (kv_hi - tile_lo + AK - 1) / AK;
+
+    const uint32_t q_full = smem_u32(bars), p_full = smem_u32(bars + 1);
+    const uint32_t s_full0 = smem_u32(bars + 2), o_full0 = smem_u32(bars + 4);
+    const uint32_t full0 = smem_u32(bars + 6), empty0 = smem_u32(bars + 6 + C::NSLOTS);
+    if (tid == 0) {
+        mbar_init(q_full, 1);
+        mbar_init(p_full, 128);
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(s_full0 + 8 * b, 1);
+            mbar_init(o_full0 + 8 * b, 1);
+        }
+        for (int i = 0; i < C::NSLOTS; ++i) {
+            mbar_init(full0 + 8 * i, 1);
+            mbar_init(empty0 + 8 * i, 1);
+        }
+        *give_up = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) tmem_alloc(smem_u32(tmem_slot), C::TMEM_COLS);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0 && lane == 0) {
+        // ---- TMA producer: Q once, then K_0, V_0, K_1, V_1, ... into the slot ring --------------------
+        mbar_expect_tx(q_full, C::Q_BYTES);
+        for (int cb = 0; cb < C::CB; ++cb)
+            tma_load_2d(smem_u32(q_s + cb * C::BLOCK_BYTES), &map_q, h * HD + cb * 64, row0 + q0, q_full);
+        const int* table = p.block_tables + (size_t)s * p.max_blocks;
+        const int pages_per_tile = AK >> p.page_shift;
+        int t = 0;
+        bool ok = true;
+        for (int j = 0; j < ntiles && ok; ++j) {
+            const int tile0 = tile_lo + j * AK;
+            for (int kv = 0; kv < 2; ++kv, ++t) {
+                const int slot = t % C::NSLOTS;
+                ok = mbar_wait(empty0 + 8 * slot, ((t / C::NSLOTS) & 1) ^ 1, give_up);
+                if (!ok) break;
+                const uint32_t bar = full0 + 8 * slot;
+                const uint32_t dst0 = smem_u32(slots + slot * C::SLOT_BYTES);
+                mbar_expect_tx(bar, C::SLOT_BYTES);
+                for (int pg = 0; pg < pages_per_tile; ++pg) {
+                    const int pos = tile0 + pg * p.page_size;
+                    int page = 0;  // slots past the context: any finite data, their probabilities are zero
+                    if (pos < kv_hi) {
+                        const int blk = pos >> p.page_shift;
+                        page = blk < p.max_blocks ? table[blk] : -1;
+                        if (page < 0 || page >= p.num_pages) {
+                            cw_report(p.status, CW_ST_PAGE_RANGE, s, page);
+                            page = 0;
+                        }
+                    }
+                    for (int cb = 0; cb < C::CB; ++cb)
+                        tma_load_3d(dst0 + cb * C::BLOCK_BYTES + pg * p.page_size * 128, kv ? &map_v : &map_k, cb * 64, kvh,
+                                    page * p.page_size, bar);
+                }
+            }
+        }
+        if (*give_up) {
+            // wait, bounded, for the copies still in flight before the CTA's shared memory goes away
+            for (int k = max(0, t - C::NSLOTS); k < t; ++k) {
+                const uint32_t bar = full0 + 8 * (k % C::NSLOTS);
+                const long long t0 = clock64();
+                while (!mbar_try_wait(bar, (k / C::NSLOTS) & 1) && clock64() - t0 < WAIT_CYCLES) {
+                }
+            }
+        }
+    } else if (warp == 1 && lane == 0) {
+        // ---- MMA issuer --------------------------------------------------------------------------------
+        constexpr uint32_t idesc_s = instr_desc(AQ, AK);
+        constexpr uint32_t idesc_o = instr_desc(AQ, HD) | (1u << 16);  // B (= V) is MN-major
+        bool ok = mbar_wait(q_full, 0, give_up);
+        auto issue_s = [&](int j) -> bool {
+            const int t = 2 * j, slot = t % C::NSLOTS;
+            if (!mbar_wait(full0 + 8 * slot, (t / C::NSLOTS) & 1, give_up)) return false;
+            tc_fence_after();
+            const uint32_t k_addr = smem_u32(slots + slot * C::SLOT_BYTES);
+#pragma unroll
+            for (int ks = 0; ks < HD / 16; ++ks) {
+                const uint64_t a = smem_desc_sw128(smem_u32(q_s) + (ks / 4) * C::BLOCK_BYTES) + 2 * (ks % 4);
+                const uint64_t b = smem_desc_sw128(k_addr + (ks / 4) * C::BLOCK_BYTES) + 2 * (ks % 4);
+                umma_bf16(tmem_base + (j & 1) * AK, a, b, idesc_s, ks > 0 ? 1u : 0u);
+            }
+            umma_commit(empty0 + 8 * slot);       // K_j may be overwritten when these have read it
+            umma_commit(s_full0 + 8 * (j & 1));
+            return true;
+        };
+        if (ok) ok = issue_s(0);
+        for (int j = 0; j < ntiles && ok; ++j) {
+            // S of the next tile first: it runs while the softmax warps work on this one.  Its buffer
+            // was read for the last time before P of tile j-1 was announced.
+            if (j + 1 < ntiles) ok = issue_s(j + 1);
+            if (!ok) break;
+            ok = mbar_wait(p_full, j & 1, give_up);
+            if (!ok) break;
+            const int t = 2 * j + 1, slot = t % C::NSLOTS;
+            ok = mbar_wait(full0 + 8 * slot, (t / C::NSLOTS) & 1, give_up);
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t v_addr = smem_u32(slots + slot * C::SLOT_BYTES);
+#pragma unroll
+            for (int kk = 0; kk < AK / 16; ++kk) {
+                const uint64_t a = smem_desc_sw128(smem_u32(p_s) + (kk / 4) * C::BLOCK_BYTES) + 2 * (kk % 4);
+                const uint64_t b = smem_desc_mn_sw128(v_addr + kk * 16 * 128, C::BLOCK_BYTES);
+                umma_bf16(tmem_base + C::O_COL + (j & 1) * HD, a, b, idesc_o, kk > 0 ? 1u : 0u);
+            }
+            umma_commit(empty0 + 8 * slot);
+            umma_commit(o_full0 + 8 * (j & 1));   // O'_j is ready and P may be overwritten
+        }
+    } else if (warp >= 2) {
+        // ---- softmax warps: one thread per query row ---------------------------------------------------
+        const int quarter = warp & 3;
+        const int row = quarter * 32 + lane;
+        const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+        const int qp = pos0 + row;                                     // this row's position
+        const int lo = p.window > 0 ? max(0, qp + 1 - p.window) : 0;   // its first visible key
+        const float scale_log2 = p.scale * 1.4426950408889634f;        // softmax in base 2
+        float o_acc[HD];
+#pragma unroll
+        for (int i = 0; i < HD; ++i) o_acc[i] = 0.f;
+        float m_run = -INFINITY, l_run = 0.f;
+        bool ok = true;
+        for (int j = 0; j < ntiles; ++j) {
+            const int tile0 = tile_lo + j * AK;
+            ok = mbar_wait(s_full0 + 8 * (j & 1), (j >> 1) & 1, give_up);
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t s_addr = lane_addr + (j & 1) * AK;
+            // tiles wholly visible to all 128 rows skip the per-element test
+            const bool all_visible = tile0 + AK - 1 <= pos0 && (p.window <= 0 || tile0 > pos0 + AQ - 1 - p.window);
+            float mx = -INFINITY;
+#pragma unroll
+            for (int c = 0; c < AK / 32; ++c) {
+                float v[32];
+                tmem_ld32(s_addr + 32 * c, v);
+                if (all_visible) {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) mx = fmaxf(mx, v[i]);
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        const int pos = tile0 + 32 * c + i;
+                        if (pos <= qp && pos >= lo) mx = fmaxf(mx, v[i]);
+                    }
+                }
+            }
+            const float m_new = fmaxf(m_run, mx * scale_log2);
+            const float alpha = (m_run == -INFINITY) ? 0.f : ex2(m_run - m_new);
+            const float base = (m_new == -INFINITY) ? 0.f : m_new;
+            if (j > 0) {
+                // PV of the previous tile is complete: P may be overwritten, O'_{j-1} may be read
+                ok = mbar_wait(o_full0 + 8 * ((j - 1) & 1), ((j - 1) >> 1) & 1, give_up);
+                if (!ok) break;
+                tc_fence_after();
+            }
+            float sum = 0.f;
+#pragma unroll
+            for (int c = 0; c < AK / 32; ++c) {
+                float v[32];
+                tmem_ld32(s_addr + 32 * c, v);
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    const int pos = tile0 + 32 * c + i;
+                    const bool vis = all_visible || (pos <= qp && pos >= lo);
+                    const float pr = vis ? ex2(fmaf(v[i], scale_log2, -base)) : 0.f;
+                    v[i] = pr;
+                    sum += pr;
+                }
+#pragma unroll
+                for (int q4 = 0; q4 < 4; ++q4) {
+                    // 8 keys = one 16-byte chunk of this row in the K-major, 128-byte-swizzled P tile
+                    const int chunk = 4 * c + q4;  // of 16 in the row; 8 per 64-key block
+                    const uint32_t addr = smem_u32(p_s) + (chunk >> 3) * C::BLOCK_BYTES + row * 128 +
+                                          (((chunk & 7) ^ (row & 7)) << 4);
+                    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr),
+                                 "r"(pack2(v[8 * q4], v[8 * q4 + 1])), "r"(pack2(v[8 * q4 + 2], v[8 * q4 + 3])),
+                                 "r"(pack2(v[8 * q4 + 4], v[8 * q4 + 5])), "r"(pack2(v[8 * q4 + 6], v[8 * q4 + 7]))
+                                 : "memory");
+                }
+            }
+            l_run = l_run * alpha + sum;
+            m_run = m_new;
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // P is read by the tensor core's proxy
+            tc_fence_before();
+            asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(p_full) : "memory");
+            if (j > 0) {
+                const uint32_t o_addr = lane_addr + C::O_COL + ((j - 1) & 1) * HD;
+#pragma unroll
+                for (int c = 0; c < HD / 32; ++c) {
+                    float v[32];
+                    tmem_ld32(o_addr + 32 * c, v);
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) o_acc[32 * c + i] = (o_acc[32 * c + i] + v[i]) * alpha;
+                }
+            }
+        }
+        if (ok) ok = mbar_wait(o_full0 + 8 * ((ntiles - 1) & 1), ((ntiles - 1) >> 1) & 1, give_up);
+        if (ok) {
+            tc_fence_after();
+            const uint32_t o_addr = lane_addr + C::O_COL + ((ntiles - 1) & 1) * HD;
+            const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+            bf16* o = p.out + ((size_t)(row0 + q0 + row) * p.nh + h) * HD;
+#pragma unroll
+            for (int c = 0; c < HD / 32; ++c) {
+                float v[32];
+                tmem_ld32(o_addr + 32 * c, v);
+                if (row < nq) {
+#pragma unroll
+                    for (int q4 = 0; q4 < 4; ++q4) {
+                        uint4 w;
+                        w.x = pack2((o_acc[32 * c + 8 * q4 + 0] + v[8 * q4 + 0]) * inv, (o_acc[32 * c + 8 * q4 + 1] + v[8 * q4 + 1]) * inv);
+                        w.y = pack2((o_acc[32 * c + 8 * q4 + 2] + v[8 * q4 + 2]) * inv, (o_acc[32 * c + 8 * q4 + 3] + v[8 * q4 + 3]) * inv);
+                        w.z = pack2((o_acc[32 * c + 8 * q4 + 4] + v[8 * q4 + 4]) * inv, (o_acc[32 * c + 8 * q4 + 5] + v[8 * q4 + 5]) * inv);
+                        w.w = pack2((o_acc[32 * c + 8 * q4 + 6] + v[8 * q4 + 6]) * inv, (o_acc[32 * c + 8 * q4 + 7] + v[8 * q4 + 7]) * inv);
+                        *reinterpret_cast<uint4*>(o + 32 * c + 8 * q4) = w;
+                    }
+                }
+            }
+        }
+    }
+    __syncwarp();
+    if (*give_up && tid == 0) cw_report(p.status, CW_ST_WAIT_TIMEOUT, blockIdx.x, blockIdx.y);
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem_base, C::TMEM_COLS);
+}
+
+// ---------------------------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------------------------
+template <int HD>
+static int launch_prefill_tc(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv,
+                             const PrefillTcParams& p, int items, cudaStream_t stream) {
+    using C = ACfg<HD>;
+    static bool configured = false;
+    if (!configured) {
+        if (cudaFuncSetAttribute(attn_prefill_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 C::SMEM_BYTES) != cudaSuccess)
+            return (int)cudaGetLastError();
+        configured = true;
+    }
+    return cw_launch(attn_prefill_tc_kernel<HD>, dim3(p.nh, items), dim3(A_THREADS), C::SMEM_BYTES, stream, 1, mq, mk, mv, p);
+}
+
+// q: [q_rows, q_cols] rows of the flat batch (row stride q_stride, head h at columns h*hd..), out:
+// [q_rows, nh*hd]; item_seq/item_q0: one entry per 128 query rows of each request.  Takes head sizes
+// 64 and 128 and pages of 8..128 tokens (a power of two); CW_ERR_UNSUPPORTED otherwise, so that the
+// caller can use the mma.sync kernel.
+extern "C" int cw_attention_prefill_tc(const void* q, int q_stride, int q_cols, int q_rows, void* out,
+                                       const void* k_cache, const void* v_cache, const int* block_tables,
+                                       const int* q_start, const int* ctx_lens, const int* item_seq,
+                                       const int* item_q0, int items, int nh, int nkv, int hd, int page_size,
+                                       int max_blocks, int num_pages, float scale, int window, int* status,
+                                       cudaStream_t stream) {
+    if (items == 0) return CW_OK;
+    if (items < 0 || nh <= 0 || nkv <= 0 || nh % nkv != 0 || page_size <= 0 || max_blocks <= 0 || num_pages <= 0 ||
+        q_rows <= 0 || q_cols < nh * hd)
+        return CW_ERR_BAD_SIZE;
+    if (hd != 64 && hd != 128) return CW_ERR_UNSUPPORTED;
+    if ((page_size & (page_size - 1)) != 0 || page_size < 8 || page_size > AK) return CW_ERR_UNSUPPORTED;
+    if (q_stride % 8 != 0 || ((uintptr_t)q & 15) || ((uintptr_t)k_cache & 15) || ((uintptr_t)v_cache & 15) ||
+        ((uintptr_t)out & 15))
+        return CW_ERR_UNSUPPORTED;
+    if (nh > 65535 || items > 65535) return CW_ERR_BAD_SIZE;
+    if (load_encode() != 0) return CW_ERR_UNSUPPORTED;
+    CUtensorMap mq, mk, mv;
+    {
+        const cuuint64_t dims[2] = {(cuuint64_t)q_cols, (cuuint64_t)q_rows};
+        const cuuint64_t strides[1] = {(cuuint64_t)q_stride * 2};
+        const cuuint32_t box[2] = {64, AQ};
+        const cuuint32_t elem[2] = {1, 1};
+        if (g_encode(&mq, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(q), dims, strides, box, elem,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            return CW_ERR_UNSUPPORTED;
+    }
+    for (int kv = 0; kv < 2; ++kv) {
+        // the cache as [slot][kv head][hd]: a box is one page of one head, 64 elements wide
+        const cuuint64_t dims[3] = {(cuuint64_t)hd, (cuuint64_t)nkv, (cuuint64_t)num_pages * page_size};
+        const cuuint64_t strides[2] = {(cuuint64_t)hd * 2, (cuuint64_t)nkv * hd * 2};
+        const cuuint32_t box[3] = {64, 1, (cuuint32_t)page_size};
+        const cuuint32_t elem[3] = {1, 1, 1};
+        if (g_encode(kv ? &mv : &mk, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(kv ? v_cache : k_cache), dims,
+                     strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            return CW_ERR_UNSUPPORTED;
+    }
+    PrefillTcParams p;
+    p.out = (bf16*)out;
+    p.block_tables = block_tables; p.q_start = q_start; p.ctx_lens = ctx_lens;
+    p.item_seq = item_seq; p.item_q0 = item_q0;
+    p.nh = nh; p.nkv = nkv; p.page_size = page_size; p.page_shift = __builtin_ctz(page_size);
+    p.max_blocks = max_blocks; p.num_pages = num_pages;
+    p.scale = scale; p.window = window; p.status = status;
+    return hd == 64 ? launch_prefill_tc<64>(mq, mk, mv, p, items, stream) : launch_prefill_tc<128>(mq, mk, mv, p, items, stream);
+}

@@ -1,5 +1,6 @@
 """Python faces of the bfloat16 attention kernels: split-context decode (``csrc/attention_decode.cu``)
-and tensor-core prefill (``csrc/attention_prefill.cu``).  ``ops.attention.paged_attention`` picks
+and prefill on the tensor cores (``csrc/attention_prefill_tc.cu``: tcgen05, head sizes 64 and 128;
+``csrc/attention_prefill.cu``: mma.sync, the other sizes).  ``ops.attention.paged_attention`` picks
 them when a step's sizes allow."""
 
 from __future__ import annotations
@@ -15,7 +16,12 @@ from .library import check, library
 
 DECODE_HEAD_DIMS = (16, 32, 48, 64, 80, 96, 112, 128, 160, 192, 256)
 PREFILL_HEAD_DIMS = (16, 32, 48, 64, 80, 96, 112, 128)
+PREFILL_TC_HEAD_DIMS = (64, 128)  # the tcgen05 kernel; pages of 8..128 tokens, a power of two
 QUERY_TILE = 128
+
+
+def prefill_tc_takes(head_dim: int, page_size: int) -> bool:
+    return head_dim in PREFILL_TC_HEAD_DIMS and 8 <= page_size <= 128 and page_size & (page_size - 1) == 0
 
 _configured = False
 _scratch: dict[int, dict] = {}
@@ -35,6 +41,8 @@ def _configure() -> None:
     lib.cw_attention_decode_workspace.restype = c_int
     lib.cw_attention_prefill.argtypes = [P, I, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, I, P, P]
     lib.cw_attention_prefill.restype = c_int
+    lib.cw_attention_prefill_tc.argtypes = [P, I, I, I, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, I, P, P]
+    lib.cw_attention_prefill_tc.restype = c_int
     _configured = True
 
 
@@ -148,11 +156,13 @@ def _work_items(ctx) -> tuple[torch.Tensor, torch.Tensor, int]:
     shared by all layers."""
     cached = ctx.extras.get("prefill_items")
     if cached is None:
-        seqs, q0s = [], []
-        for s, n in enumerate(ctx.q_lens_host):
+        items = []
+        for s, (n, c) in enumerate(zip(ctx.q_lens_host, ctx.ctx_lens_host)):
             for q0 in range(0, n, QUERY_TILE):
-                seqs.append(s)
-                q0s.append(q0)
+                items.append((c - n + min(q0 + QUERY_TILE, n), s, q0))  # keys the tile's last row sees
+        # longest first: CTAs are handed to SMs in this order, so the short ones fill the tail
+        items.sort(key=lambda it: -it[0])
+        seqs, q0s = [it[1] for it in items], [it[2] for it in items]
         host = torch.from_numpy(np.array([seqs, q0s], dtype=np.int32))
         dev = host.to(ctx.device, non_blocking=False)
         cached = (dev[0].contiguous(), dev[1].contiguous(), len(seqs))
@@ -173,9 +183,10 @@ class _Prefill:
 
 
 def attention_prefill(q, k_cache, v_cache, block_tables, q_start, ctx_lens, item_seq, item_q0, items, num_heads,
-                      num_kv_heads, head_dim, scale, window, status) -> torch.Tensor:
+                      num_kv_heads, head_dim, scale, window, status, use_tc: bool | None = None) -> torch.Tensor:
     """Any mixture of portions: ``q`` [N, >= nh*hd]; request s owns rows q_start[s]:q_start[s+1] and has
-    ctx_lens[s] tokens in the cache, its portion at the end.  Returns [N, nh*hd]."""
+    ctx_lens[s] tokens in the cache, its portion at the end.  Returns [N, nh*hd].  ``use_tc``: the
+    tcgen05 kernel (default: whenever it takes the head size and the page size) or the mma.sync one."""
     _configure()
     if q.dtype != torch.bfloat16 or q.dim() != 2 or q.stride(1) != 1:
         raise ValueError("q must be a 2-d bfloat16 tensor with unit column stride")
@@ -187,6 +198,15 @@ def attention_prefill(q, k_cache, v_cache, block_tables, q_start, ctx_lens, item
     if head_dim not in PREFILL_HEAD_DIMS:
         raise ValueError(f"head_dim {head_dim} is not one of {PREFILL_HEAD_DIMS}")
     out = torch.empty((q.shape[0], num_heads * head_dim), dtype=torch.bfloat16, device=q.device)
+    if use_tc is None:
+        use_tc = prefill_tc_takes(head_dim, k_cache.shape[1])
+    if use_tc:
+        check(library().cw_attention_prefill_tc(
+            _ptr(q), q.stride(0), q.shape[1], q.shape[0], _ptr(out), _ptr(k_cache), _ptr(v_cache), _ptr(block_tables),
+            _ptr(q_start), _ptr(ctx_lens), _ptr(item_seq), _ptr(item_q0), items, num_heads, num_kv_heads, head_dim,
+            k_cache.shape[1], block_tables.shape[1], k_cache.shape[0], float(scale), int(window or 0), _ptr(status),
+            _stream()), "attention_prefill_tc")
+        return out
     check(library().cw_attention_prefill(
         _ptr(q), q.stride(0), _ptr(out), _ptr(k_cache), _ptr(v_cache), _ptr(block_tables), _ptr(q_start), _ptr(ctx_lens),
         _ptr(item_seq), _ptr(item_q0), items, num_heads, num_kv_heads, head_dim, k_cache.shape[1], block_tables.shape[1],

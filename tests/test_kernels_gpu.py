@@ -445,11 +445,16 @@ def test_attention_decode_finds_one_far_key(ops, status, fast):
     ops.raise_on_status(status)
 
 
-@pytest.mark.parametrize("nh,nkv,hd,ps,window", [(12, 2, 128, 16, None), (5, 5, 48, 8, None), (8, 1, 16, 4, 37),
-                                                (4, 2, 32, 8, 100), (6, 3, 64, 16, None)])
-def test_attention_prefill_kernel_mixed_batch(ops, status, fast, nh, nkv, hd, ps, window):
+@pytest.mark.parametrize("kernel,nh,nkv,hd,ps,window", [
+    ("mma", 12, 2, 128, 16, None), ("mma", 5, 5, 48, 8, None), ("mma", 8, 1, 16, 4, 37), ("mma", 4, 2, 32, 8, 100),
+    ("mma", 6, 3, 64, 16, None),
+    ("tc", 12, 2, 128, 16, None), ("tc", 6, 3, 64, 16, None), ("tc", 4, 2, 64, 8, 100), ("tc", 3, 1, 128, 32, 300),
+    ("tc", 2, 1, 64, 128, None), ("tc", 5, 5, 128, 64, 37)])
+def test_attention_prefill_kernel_mixed_batch(ops, status, fast, kernel, nh, nkv, hd, ps, window):
     """Portions in the middle of a context, whole prompts (shorter and longer than a tile, ending on
-    and off tile edges), and single decoded tokens, all in one launch."""
+    and off tile edges), and single decoded tokens, all in one launch; the mma.sync kernel and the
+    tcgen05 kernel."""
+    assert kernel == "mma" or fast.prefill_tc_takes(hd, ps)
     ctx_lens, q_lens = [150, 333, 41, 200, 1000, 64, 65, 129], [23, 1, 41, 200, 130, 64, 2, 128]
     dtype = torch.bfloat16
     k_cache, v_cache, tables, ks, vs = paged_setup(ctx_lens, nkv, hd, ps, dtype, seed=5)
@@ -465,7 +470,7 @@ def test_attention_prefill_kernel_mixed_batch(ops, status, fast, nh, nkv, hd, ps
     item_q0 = torch.tensor([i[1] for i in items], dtype=torch.int32)
     out = fast.attention_prefill(wide.to(dtype).to(DEV), k_cache.to(DEV), v_cache.to(DEV), tables.to(DEV), q_start.to(DEV),
                                  torch.tensor(ctx_lens, dtype=torch.int32, device=DEV), item_seq.to(DEV), item_q0.to(DEV),
-                                 len(items), nh, nkv, hd, scale, window, status).float().cpu().view(n, nh, hd)
+                                 len(items), nh, nkv, hd, scale, window, status, use_tc=kernel == "tc").float().cpu().view(n, nh, hd)
     ops.raise_on_status(status)
     row = 0
     for i, (q, k, v) in enumerate(zip(qs, ks, vs)):
@@ -475,19 +480,21 @@ def test_attention_prefill_kernel_mixed_batch(ops, status, fast, nh, nkv, hd, ps
         row += q.shape[0]
 
 
-def test_attention_prefill_sees_the_diagonal_and_nothing_after_it(ops, status, fast):
+@pytest.mark.parametrize("hd,n", [(32, 150), (64, 150), (128, 300)])
+def test_attention_prefill_sees_the_diagonal_and_nothing_after_it(ops, status, fast, hd, n):
     """Each query's own key carries a score that stands out, so each output must be its own value;
-    if the mask were off by one either way the output would be a neighbour's."""
-    nh, nkv, hd, ps, n = 2, 1, 32, 16, 150
+    if the mask were off by one either way the output would be a neighbour's.  (Head size 32 runs the
+    mma.sync kernel, 64 and 128 the tcgen05 kernel.)"""
+    nh, nkv, ps = 2, 1, 16
     k_cache, v_cache, tables, ks, vs = paged_setup([n], nkv, hd, ps, torch.bfloat16, seed=9)
     kc = k_cache.float()
     q = torch.zeros(n, nh, hd)
     for pos in range(n):
         page, off = int(tables[0, pos // ps]), pos % ps
-        code = torch.tensor([1.0 if (pos >> b) & 1 else -1.0 for b in range(8)]) * 6.0
+        code = torch.tensor([1.0 if (pos >> b) & 1 else -1.0 for b in range(9)]) * 6.0
         kc[page, off, 0, :] = 0.0
-        kc[page, off, 0, :8] = code
-        q[pos, :, :8] = code
+        kc[page, off, 0, :9] = code
+        q[pos, :, :9] = code
     wide = torch.zeros(n, (nh + 2) * hd)
     wide[:, : nh * hd] = q.view(n, -1)
     items = list(range(0, n, fast.QUERY_TILE))
@@ -496,7 +503,7 @@ def test_attention_prefill_sees_the_diagonal_and_nothing_after_it(ops, status, f
                                  torch.zeros(len(items), dtype=torch.int32, device=DEV), torch.tensor(items, dtype=torch.int32, device=DEV),
                                  len(items), nh, nkv, hd, 1.0, None, status).float().cpu().view(n, nh, hd)
     ops.raise_on_status(status)
-    # own score 8*36 = 288; any other key differs in at least one bit: at most 288 - 72
+    # own score 9*36 = 324; any other key differs in at least one bit: at most 324 - 72
     torch.testing.assert_close(out[:, 0], vs[0][:, 0], rtol=2e-2, atol=2e-2)
 
 
