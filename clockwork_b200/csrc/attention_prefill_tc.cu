@@ -5,7 +5,7 @@
 // through the block table.  Per tile:
 //
 //     S  = Q K^T           tcgen05.mma, Q and K both K-major in shared memory, S in TMEM
-//     P  = 2^(S c - m)     softmax warps: one thread per query row reads its row of S from TMEM
+//     P  = 2^(S c - m)     softmax warps: two threads per query row read its row of S from TMEM
 //                          (no shuffles), float32 statistics, P rounded to bfloat16 into shared memory
 //     O' = P V             tcgen05.mma, P K-major, V as it lies in the cache (head dimension
 //                          contiguous = MN-major B operand), O' in TMEM
@@ -13,8 +13,8 @@
 //
 // S and O' are double buffered in TMEM (2 x 128 + 2 x HD columns), so that the MMAs of tile j+1 and
 // the loads of later tiles run while the softmax warps work on tile j.  K and V tiles share one ring
-// of shared-memory slots.  Warps (192 threads): 0 TMA producer, 1 MMA issuer and TMEM owner, 2..5
-// softmax (warp w owns TMEM lanes 32 (w % 4) .. +31).
+// of shared-memory slots.  Warps (320 threads): 0 TMA producer, 1 MMA issuer and TMEM owner, 2..9
+// softmax (warp w owns TMEM lanes 32 (w % 4) .. +31; two warps share a lane quarter and split the columns).
 //
 // Reference: clockwork/kernels/attention.py:68-96 (gather the context through one block table, then
 // dense causal attention with the query aligned to the end of the context, :45-65) and
@@ -30,7 +30,7 @@
 
 #define AQ 128  // query rows per CTA
 #define AK 128  // keys per tile
-#define A_THREADS 192
+#define A_THREADS 320  // TMA producer, MMA issuer, 8 softmax warps
 #define A_MAX_SMEM (227 * 1024)
 
 struct PrefillTcParams {
@@ -49,9 +49,10 @@ struct ACfg {
     static constexpr int Q_BYTES = CB * BLOCK_BYTES;
     static constexpr int P_BYTES = (AK / 64) * BLOCK_BYTES;
     static constexpr int SLOT_BYTES = CB * BLOCK_BYTES;  // one K or one V tile
-    static constexpr int FIT = (A_MAX_SMEM - 2048 - Q_BYTES - P_BYTES) / SLOT_BYTES;
+    static constexpr int TAIL_BYTES = 256 + 2048;  // barriers, exchange of row statistics
+    static constexpr int FIT = (A_MAX_SMEM - TAIL_BYTES - Q_BYTES - P_BYTES) / SLOT_BYTES;
     static constexpr int NSLOTS = FIT > 8 ? 8 : FIT;
-    static constexpr int SMEM_BYTES = Q_BYTES + P_BYTES + NSLOTS * SLOT_BYTES + 2048;
+    static constexpr int SMEM_BYTES = Q_BYTES + P_BYTES + NSLOTS * SLOT_BYTES + TAIL_BYTES;
     static constexpr int O_COL = 2 * AK;                 // S buffers at columns 0 and 128, O' after them
     static constexpr int TMEM_COLS = 512;
     static_assert(NSLOTS >= 4, "too few key/value slots");
@@ -106,8 +107,13 @@ __global__ void __launch_bounds__(A_THREADS)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                        const __grid_constant__ CUtensorMap map_v, const PrefillTcParams p) {
     using C = ACfg<HD>;
-    extern __shared__ uint8_t smem_raw[];
-    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    // the swizzled tiles need a 1024-byte aligned base; the declaration asks for it and the kernel
+    // checks it instead of rounding up, because the tiles leave no kilobyte to spare
+    extern __shared__ __align__(1024) uint8_t smem[];
+    if (smem_u32(smem) & 1023) {
+        if (threadIdx.x == 0) cw_report(p.status, CW_ST_SMEM_ALIGN, blockIdx.x, (int)(smem_u32(smem) & 1023));
+        return;
+    }
     uint8_t* q_s = smem;
     uint8_t* p_s = q_s + C::Q_BYTES;
     uint8_t* slots = p_s + C::P_BYTES;
@@ -115,6 +121,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     // bars: q_full, p_full, s_full[2], o_full[2], full[NSLOTS], empty[NSLOTS]
     uint32_t* tmem_slot = (uint32_t*)(bars + 6 + 2 * C::NSLOTS);
     volatile int* give_up = (volatile int*)(tmem_slot + 1);
+    float* xchg = (float*)(bars + 32);  // [2][2][128]: row maxima and, at the end, row sums (tile parity x half)
 
     pdl_launch_dependents();
     pdl_wait();
@@ -136,7 +143,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     const uint32_t full0 = smem_u32(bars + 6), empty0 = smem_u32(bars + 6 + C::NSLOTS);
     if (tid == 0) {
         mbar_init(q_full, 1);
-        mbar_init(p_full, 128);
+        mbar_init(p_full, 256);
         for (int b = 0; b < 2; ++b) {
             mbar_init(s_full0 + 8 * b, 1);
             mbar_init(o_full0 + 8 * b, 1);
@@ -155,42 +162,51 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
-    if (warp == 0 && lane == 0) {
+    if (warp == 0) {
         // ---- TMA producer: Q once, then K_0, V_0, K_1, V_1, ... into the slot ring --------------------
-        mbar_expect_tx(q_full, C::Q_BYTES);
-        for (int cb = 0; cb < C::CB; ++cb)
-            tma_load_2d(smem_u32(q_s + cb * C::BLOCK_BYTES), &map_q, h * HD + cb * 64, row0 + q0, q_full);
+        // Lane i fetches page i of a tile: it reads the page's number from the block table one tile
+        // ahead (so that the read's latency is hidden) and issues that page's copies itself.
+        if (lane == 0) {
+            mbar_expect_tx(q_full, C::Q_BYTES);
+            for (int cb = 0; cb < C::CB; ++cb)
+                tma_load_2d(smem_u32(q_s + cb * C::BLOCK_BYTES), &map_q, h * HD + cb * 64, row0 + q0, q_full);
+        }
         const int* table = p.block_tables + (size_t)s * p.max_blocks;
-        const int pages_per_tile = AK >> p.page_shift;
+        const int pages_per_tile = AK >> p.page_shift;  // at most 16
+        auto page_of = [&](int tile0) -> int {
+            // slots past the context: any finite data will do, their probabilities are zero
+            const int pos = tile0 + lane * p.page_size;
+            const int blk = pos >> p.page_shift;
+            return (lane < pages_per_tile && pos < kv_hi && blk < p.max_blocks) ? table[blk] : 0;
+        };
+        int page_next = page_of(tile_lo);
         int t = 0;
         bool ok = true;
         for (int j = 0; j < ntiles && ok; ++j) {
             const int tile0 = tile_lo + j * AK;
+            int page = page_next;
+            if (j + 1 < ntiles) page_next = page_of(tile0 + AK);
+            if (page < 0 || page >= p.num_pages) {
+                cw_report(p.status, CW_ST_PAGE_RANGE, s, page);
+                page = 0;
+            }
             for (int kv = 0; kv < 2; ++kv, ++t) {
                 const int slot = t % C::NSLOTS;
                 ok = mbar_wait(empty0 + 8 * slot, ((t / C::NSLOTS) & 1) ^ 1, give_up);
+                ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
                 const uint32_t bar = full0 + 8 * slot;
                 const uint32_t dst0 = smem_u32(slots + slot * C::SLOT_BYTES);
-                mbar_expect_tx(bar, C::SLOT_BYTES);
-                for (int pg = 0; pg < pages_per_tile; ++pg) {
-                    const int pos = tile0 + pg * p.page_size;
-                    int page = 0;  // slots past the context: any finite data, their probabilities are zero
-                    if (pos < kv_hi) {
-                        const int blk = pos >> p.page_shift;
-                        page = blk < p.max_blocks ? table[blk] : -1;
-                        if (page < 0 || page >= p.num_pages) {
-                            cw_report(p.status, CW_ST_PAGE_RANGE, s, page);
-                            page = 0;
-                        }
-                    }
+                if (lane == 0) mbar_expect_tx(bar, C::SLOT_BYTES);
+                __syncwarp();
+                if (lane < pages_per_tile) {
                     for (int cb = 0; cb < C::CB; ++cb)
-                        tma_load_3d(dst0 + cb * C::BLOCK_BYTES + pg * p.page_size * 128, kv ? &map_v : &map_k, cb * 64, kvh,
+                        tma_load_3d(dst0 + cb * C::BLOCK_BYTES + lane * p.page_size * 128, kv ? &map_v : &map_k, cb * 64, kvh,
                                     page * p.page_size, bar);
                 }
             }
         }
-        if (*give_up) {
+        if (*give_up && lane == 0) {
             // wait, bounded, for the copies still in flight before the CTA's shared memory goes away
             for (int k = max(0, t - C::NSLOTS); k < t; ++k) {
                 const uint32_t bar = full0 + 8 * (k % C::NSLOTS);
@@ -242,42 +258,54 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             umma_commit(o_full0 + 8 * (j & 1));   // O'_j is ready and P may be overwritten
         }
     } else if (warp >= 2) {
-        // ---- softmax warps: one thread per query row ---------------------------------------------------
+        // ---- softmax warps: two threads per query row, each with half of the row's columns -----------
+        // Warps w and w + 4 own the same 32 TMEM lanes; `half` says which half of S's 128 columns and of
+        // O's HD columns a thread works on.  The two exchange their partial row maxima through shared
+        // memory once per tile; sums stay partial until the end.
         const int quarter = warp & 3;
+        const int half = (warp - 2) >> 2;
         const int row = quarter * 32 + lane;
+        constexpr int SC = AK / 2;   // S columns per thread
+        constexpr int OC = HD / 2;   // O columns per thread
         const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
         const int qp = pos0 + row;                                     // this row's position
         const int lo = p.window > 0 ? max(0, qp + 1 - p.window) : 0;   // its first visible key
         const float scale_log2 = p.scale * 1.4426950408889634f;        // softmax in base 2
-        float o_acc[HD];
+        const int pair_bar = 1 + quarter;                              // named barrier of the 64 threads of a quarter
+        float o_acc[OC];
 #pragma unroll
-        for (int i = 0; i < HD; ++i) o_acc[i] = 0.f;
+        for (int i = 0; i < OC; ++i) o_acc[i] = 0.f;
         float m_run = -INFINITY, l_run = 0.f;
         bool ok = true;
         for (int j = 0; j < ntiles; ++j) {
             const int tile0 = tile_lo + j * AK;
+            const int col0 = tile0 + half * SC;  // position of this thread's first key
             ok = mbar_wait(s_full0 + 8 * (j & 1), (j >> 1) & 1, give_up);
             if (!ok) break;
             tc_fence_after();
-            const uint32_t s_addr = lane_addr + (j & 1) * AK;
+            const uint32_t s_addr = lane_addr + (j & 1) * AK + half * SC;
             // tiles wholly visible to all 128 rows skip the per-element test
             const bool all_visible = tile0 + AK - 1 <= pos0 && (p.window <= 0 || tile0 > pos0 + AQ - 1 - p.window);
-            float mx = -INFINITY;
+            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};  // four chains: one warp per scheduler has only ILP
 #pragma unroll
-            for (int c = 0; c < AK / 32; ++c) {
+            for (int c = 0; c < SC / 32; ++c) {
                 float v[32];
                 tmem_ld32(s_addr + 32 * c, v);
                 if (all_visible) {
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) mx = fmaxf(mx, v[i]);
+                    for (int i = 0; i < 32; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], v[i]);
                 } else {
 #pragma unroll
                     for (int i = 0; i < 32; ++i) {
-                        const int pos = tile0 + 32 * c + i;
-                        if (pos <= qp && pos >= lo) mx = fmaxf(mx, v[i]);
+                        const int pos = col0 + 32 * c + i;
+                        if (pos <= qp && pos >= lo) mx4[i & 3] = fmaxf(mx4[i & 3], v[i]);
                     }
                 }
             }
+            float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+            xchg[((j & 1) * 2 + half) * AQ + row] = mx;
+            asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");
+            mx = fmaxf(mx, xchg[((j & 1) * 2 + (half ^ 1)) * AQ + row]);
             const float m_new = fmaxf(m_run, mx * scale_log2);
             const float alpha = (m_run == -INFINITY) ? 0.f : ex2(m_run - m_new);
             const float base = (m_new == -INFINITY) ? 0.f : m_new;
@@ -287,40 +315,40 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 if (!ok) break;
                 tc_fence_after();
             }
-            float sum = 0.f;
+            float sum4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-            for (int c = 0; c < AK / 32; ++c) {
+            for (int c = 0; c < SC / 32; ++c) {
                 float v[32];
                 tmem_ld32(s_addr + 32 * c, v);
 #pragma unroll
                 for (int i = 0; i < 32; ++i) {
-                    const int pos = tile0 + 32 * c + i;
+                    const int pos = col0 + 32 * c + i;
                     const bool vis = all_visible || (pos <= qp && pos >= lo);
                     const float pr = vis ? ex2(fmaf(v[i], scale_log2, -base)) : 0.f;
                     v[i] = pr;
-                    sum += pr;
+                    sum4[i & 3] += pr;
                 }
 #pragma unroll
                 for (int q4 = 0; q4 < 4; ++q4) {
-                    // 8 keys = one 16-byte chunk of this row in the K-major, 128-byte-swizzled P tile
-                    const int chunk = 4 * c + q4;  // of 16 in the row; 8 per 64-key block
-                    const uint32_t addr = smem_u32(p_s) + (chunk >> 3) * C::BLOCK_BYTES + row * 128 +
-                                          (((chunk & 7) ^ (row & 7)) << 4);
+                    // 8 keys = one 16-byte chunk of this row in the K-major, 128-byte-swizzled P tile;
+                    // this thread's 64 keys are the 64-key block `half`
+                    const int chunk = 4 * c + q4;
+                    const uint32_t addr = smem_u32(p_s) + half * C::BLOCK_BYTES + row * 128 + (((chunk & 7) ^ (row & 7)) << 4);
                     asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr),
                                  "r"(pack2(v[8 * q4], v[8 * q4 + 1])), "r"(pack2(v[8 * q4 + 2], v[8 * q4 + 3])),
                                  "r"(pack2(v[8 * q4 + 4], v[8 * q4 + 5])), "r"(pack2(v[8 * q4 + 6], v[8 * q4 + 7]))
                                  : "memory");
                 }
             }
-            l_run = l_run * alpha + sum;
+            l_run = l_run * alpha + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
             m_run = m_new;
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // P is read by the tensor core's proxy
             tc_fence_before();
             asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(p_full) : "memory");
             if (j > 0) {
-                const uint32_t o_addr = lane_addr + C::O_COL + ((j - 1) & 1) * HD;
+                const uint32_t o_addr = lane_addr + C::O_COL + ((j - 1) & 1) * HD + half * OC;
 #pragma unroll
-                for (int c = 0; c < HD / 32; ++c) {
+                for (int c = 0; c < OC / 32; ++c) {
                     float v[32];
                     tmem_ld32(o_addr + 32 * c, v);
 #pragma unroll
@@ -328,14 +356,18 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 }
             }
         }
+        // the row's sum: both halves (a thread that gave up still meets its partner here)
+        xchg[((ntiles & 1) * 2 + half) * AQ + row] = l_run;
+        asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");
+        l_run += xchg[((ntiles & 1) * 2 + (half ^ 1)) * AQ + row];
         if (ok) ok = mbar_wait(o_full0 + 8 * ((ntiles - 1) & 1), ((ntiles - 1) >> 1) & 1, give_up);
         if (ok) {
             tc_fence_after();
-            const uint32_t o_addr = lane_addr + C::O_COL + ((ntiles - 1) & 1) * HD;
+            const uint32_t o_addr = lane_addr + C::O_COL + ((ntiles - 1) & 1) * HD + half * OC;
             const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-            bf16* o = p.out + ((size_t)(row0 + q0 + row) * p.nh + h) * HD;
+            bf16* o = p.out + ((size_t)(row0 + q0 + row) * p.nh + h) * HD + half * OC;
 #pragma unroll
-            for (int c = 0; c < HD / 32; ++c) {
+            for (int c = 0; c < OC / 32; ++c) {
                 float v[32];
                 tmem_ld32(o_addr + 32 * c, v);
                 if (row < nq) {

@@ -26,6 +26,7 @@
 #define CW_ST_PAGE_RANGE 3
 #define CW_ST_WAIT_TIMEOUT 4
 #define CW_ST_ROW_RANGE 5
+#define CW_ST_SMEM_ALIGN 6
 
 typedef __nv_bfloat16 bf16;
 

@@ -20,6 +20,7 @@ STATUS_MESSAGES = {
     3: "page id outside the pool ({a}, {b})",
     4: "a device-side wait ran out (kernel {a}, stage {b})",
     5: "row index outside the batch (row {a}, index {b})",
+    6: "shared memory of block {a} is not 1024-byte aligned (offset {b})",
 }
 
 
