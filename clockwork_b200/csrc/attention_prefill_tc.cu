@@ -11,7 +11,7 @@
 //                          contiguous = MN-major B operand), O' in TMEM
 //     O  = (O + O'_prev) * 2^(m_prev - m)   in registers of the row's thread
 //
-// S and O' are double buffered in TMEM (2 x 128 + 2 x HD columns), so that the MMAs of tile j+1 and
+// S and O' are double buffered in TMEM (2 x 128 + 2 x HD columns) and P in shared memory, so that the MMAs of tile j+1 and
 // the loads of later tiles run while the softmax warps work on tile j.  K and V tiles share one ring
 // of shared-memory slots.  Warps (320 threads): 0 TMA producer, 1 MMA issuer and TMEM owner, 2..9
 // softmax (warp w owns TMEM lanes 32 (w % 4) .. +31; two warps share a lane quarter and split the columns).
@@ -47,12 +47,12 @@ struct ACfg {
     static constexpr int CB = HD / 64;                  // 64-element (128-byte) column blocks per row
     static constexpr int BLOCK_BYTES = 128 * 128;       // [128 rows][64 bf16], 128-byte swizzle
     static constexpr int Q_BYTES = CB * BLOCK_BYTES;
-    static constexpr int P_BYTES = (AK / 64) * BLOCK_BYTES;
+    static constexpr int P_BYTES = (AK / 64) * BLOCK_BYTES;  // one P tile; there are two
     static constexpr int SLOT_BYTES = CB * BLOCK_BYTES;  // one K or one V tile
     static constexpr int TAIL_BYTES = 256 + 2048;  // barriers, exchange of row statistics
-    static constexpr int FIT = (A_MAX_SMEM - TAIL_BYTES - Q_BYTES - P_BYTES) / SLOT_BYTES;
+    static constexpr int FIT = (A_MAX_SMEM - TAIL_BYTES - Q_BYTES - 2 * P_BYTES) / SLOT_BYTES;
     static constexpr int NSLOTS = FIT > 8 ? 8 : FIT;
-    static constexpr int SMEM_BYTES = Q_BYTES + P_BYTES + NSLOTS * SLOT_BYTES + TAIL_BYTES;
+    static constexpr int SMEM_BYTES = Q_BYTES + 2 * P_BYTES + NSLOTS * SLOT_BYTES + TAIL_BYTES;
     static constexpr int O_COL = 2 * AK;                 // S buffers at columns 0 and 128, O' after them
     static constexpr int TMEM_COLS = 512;
     static_assert(NSLOTS >= 4, "too few key/value slots");
@@ -116,7 +116,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     }
     uint8_t* q_s = smem;
     uint8_t* p_s = q_s + C::Q_BYTES;
-    uint8_t* slots = p_s + C::P_BYTES;
+    uint8_t* slots = p_s + 2 * C::P_BYTES;
     uint64_t* bars = (uint64_t*)(slots + C::NSLOTS * C::SLOT_BYTES);
     // bars: q_full, p_full, s_full[2], o_full[2], full[NSLOTS], empty[NSLOTS]
     uint32_t* tmem_slot = (uint32_t*)(bars + 6 + 2 * C::NSLOTS);
@@ -250,12 +250,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             const uint32_t v_addr = smem_u32(slots + slot * C::SLOT_BYTES);
 #pragma unroll
             for (int kk = 0; kk < AK / 16; ++kk) {
-                const uint64_t a = smem_desc_sw128(smem_u32(p_s) + (kk / 4) * C::BLOCK_BYTES) + 2 * (kk % 4);
+                const uint64_t a = smem_desc_sw128(smem_u32(p_s) + (j & 1) * C::P_BYTES + (kk / 4) * C::BLOCK_BYTES) + 2 * (kk % 4);
                 const uint64_t b = smem_desc_mn_sw128(v_addr + kk * 16 * 128, C::BLOCK_BYTES);
                 umma_bf16(tmem_base + C::O_COL + (j & 1) * HD, a, b, idesc_o, kk > 0 ? 1u : 0u);
             }
             umma_commit(empty0 + 8 * slot);
-            umma_commit(o_full0 + 8 * (j & 1));   // O'_j is ready and P may be overwritten
+            umma_commit(o_full0 + 8 * (j & 1));   // O'_j is ready and P buffer j & 1 may be overwritten
         }
     } else if (warp >= 2) {
         // ---- softmax warps: two threads per query row, each with half of the row's columns -----------
@@ -298,7 +298,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 #pragma unroll
                     for (int i = 0; i < 32; ++i) {
                         const int pos = col0 + 32 * c + i;
-                        if (pos <= qp && pos >= lo) mx4[i & 3] = fmaxf(mx4[i & 3], v[i]);
+                        mx4[i & 3] = fmaxf(mx4[i & 3], (pos <= qp && pos >= lo) ? v[i] : -INFINITY);
                     }
                 }
             }
@@ -309,31 +309,35 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             const float m_new = fmaxf(m_run, mx * scale_log2);
             const float alpha = (m_run == -INFINITY) ? 0.f : ex2(m_run - m_new);
             const float base = (m_new == -INFINITY) ? 0.f : m_new;
-            if (j > 0) {
-                // PV of the previous tile is complete: P may be overwritten, O'_{j-1} may be read
-                ok = mbar_wait(o_full0 + 8 * ((j - 1) & 1), ((j - 1) >> 1) & 1, give_up);
-                if (!ok) break;
-                tc_fence_after();
-            }
+            // P goes to buffer j & 1, last read by PV of tile j-2, whose completion this thread awaited
+            // before it consumed O'_{j-2} in the previous iteration.
             float sum4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
             for (int c = 0; c < SC / 32; ++c) {
                 float v[32];
                 tmem_ld32(s_addr + 32 * c, v);
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    const int pos = col0 + 32 * c + i;
-                    const bool vis = all_visible || (pos <= qp && pos >= lo);
-                    const float pr = vis ? ex2(fmaf(v[i], scale_log2, -base)) : 0.f;
-                    v[i] = pr;
-                    sum4[i & 3] += pr;
+                // straight-line code in both forms (selects, no branches), so that the 32 exponentials
+                // are in flight together; 2^-inf is exactly 0
+                if (all_visible) {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) v[i] = ex2(fmaf(v[i], scale_log2, -base));
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        const int pos = col0 + 32 * c + i;
+                        const float x = fmaf(v[i], scale_log2, -base);
+                        v[i] = ex2((pos <= qp && pos >= lo) ? x : -INFINITY);
+                    }
                 }
+#pragma unroll
+                for (int i = 0; i < 32; ++i) sum4[i & 3] += v[i];
 #pragma unroll
                 for (int q4 = 0; q4 < 4; ++q4) {
                     // 8 keys = one 16-byte chunk of this row in the K-major, 128-byte-swizzled P tile;
                     // this thread's 64 keys are the 64-key block `half`
                     const int chunk = 4 * c + q4;
-                    const uint32_t addr = smem_u32(p_s) + half * C::BLOCK_BYTES + row * 128 + (((chunk & 7) ^ (row & 7)) << 4);
+                    const uint32_t addr = smem_u32(p_s) + (j & 1) * C::P_BYTES + half * C::BLOCK_BYTES + row * 128 + (((chunk & 7) ^ (row & 7)) << 4);
                     asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr),
                                  "r"(pack2(v[8 * q4], v[8 * q4 + 1])), "r"(pack2(v[8 * q4 + 2], v[8 * q4 + 3])),
                                  "r"(pack2(v[8 * q4 + 4], v[8 * q4 + 5])), "r"(pack2(v[8 * q4 + 6], v[8 * q4 + 7]))
@@ -346,6 +350,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             tc_fence_before();
             asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(p_full) : "memory");
             if (j > 0) {
+                // O'_{j-1}: PV of the previous tile ran while this tile's P was computed
+                ok = mbar_wait(o_full0 + 8 * ((j - 1) & 1), ((j - 1) >> 1) & 1, give_up);
+                if (!ok) break;
+                tc_fence_after();
                 const uint32_t o_addr = lane_addr + C::O_COL + ((j - 1) & 1) * HD + half * OC;
 #pragma unroll
                 for (int c = 0; c < OC / 32; ++c) {
