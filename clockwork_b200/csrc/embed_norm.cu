@@ -72,12 +72,101 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const T* __restric
     for (int c = threadIdx.x; c < H; c += blockDim.x) o[c] = from_f<T>(weight[c] * (x[c] * inv));
 }
 
+// The same for many rows (prompt portions): one warp per row, the row held in registers between the
+// sum of squares and the scaling, 16-byte accesses, no block-level synchronisation.  H must be a
+// multiple of 4 and at most 128 * NV.
+template <typename T>
+struct Vec4;
+template <>
+struct Vec4<float> {
+    static __device__ __forceinline__ float4 load(const float* p) { return *reinterpret_cast<const float4*>(p); }
+    static __device__ __forceinline__ void store(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+};
+template <>
+struct Vec4<bf16> {
+    static __device__ __forceinline__ float4 load(const bf16* p) {
+        const uint2 r = *reinterpret_cast<const uint2*>(p);
+        const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&r.x), b = *reinterpret_cast<const __nv_bfloat162*>(&r.y);
+        return make_float4(__low2float(a), __high2float(a), __low2float(b), __high2float(b));
+    }
+    static __device__ __forceinline__ void store(bf16* p, float4 v) {
+        const __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+        uint2 r;
+        r.x = *reinterpret_cast<const uint32_t*>(&a);
+        r.y = *reinterpret_cast<const uint32_t*>(&b);
+        *reinterpret_cast<uint2*>(p) = r;
+    }
+};
+
+template <typename T, int NV>
+__global__ void __launch_bounds__(256)
+add_rmsnorm_warp_kernel(float* __restrict__ resid, const T* __restrict__ delta, const float* __restrict__ weight,
+                        T* __restrict__ out, int num_rows, float eps, int H) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int lane = threadIdx.x & 31;
+    const int r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (r >= num_rows) return;
+    float* x = resid + (size_t)r * H;
+    const T* d = delta ? delta + (size_t)r * H : nullptr;
+    float4 v[NV];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        const int c = (i * 32 + lane) * 4;
+        if (c < H) {
+            v[i] = Vec4<float>::load(x + c);
+            if (d) {
+                const float4 dv = Vec4<T>::load(d + c);
+                v[i].x += dv.x; v[i].y += dv.y; v[i].z += dv.z; v[i].w += dv.w;
+                Vec4<float>::store(x + c, v[i]);
+            }
+            ss = fmaf(v[i].x, v[i].x, ss); ss = fmaf(v[i].y, v[i].y, ss);
+            ss = fmaf(v[i].z, v[i].z, ss); ss = fmaf(v[i].w, v[i].w, ss);
+        }
+    }
+    ss = warp_sum(ss);
+    const float inv = 1.0f / sqrtf(ss / (float)H + eps);
+    T* o = out + (size_t)r * H;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        const int c = (i * 32 + lane) * 4;
+        if (c < H) {
+            const float4 w = Vec4<float>::load(weight + c);
+            Vec4<T>::store(o + c, make_float4(w.x * (v[i].x * inv), w.y * (v[i].y * inv), w.z * (v[i].z * inv), w.w * (v[i].w * inv)));
+        }
+    }
+}
+
+template <typename T>
+static int launch_rmsnorm_warp(float* resid, const T* delta, const float* weight, T* out, int rows, int H, float eps,
+                               cudaStream_t stream) {
+    const int warps = 8;
+    const dim3 grid((rows + warps - 1) / warps), block(warps * 32);
+    const int nv = (H + 127) / 128;
+#define CW_NV(n) \
+    if (nv <= n) return cw_launch(add_rmsnorm_warp_kernel<T, n>, grid, block, 0, stream, 1, resid, delta, weight, out, rows, eps, H);
+    CW_NV(4) CW_NV(8) CW_NV(12) CW_NV(16) CW_NV(24) CW_NV(32)
+#undef CW_NV
+    return CW_ERR_UNSUPPORTED;
+}
+
 extern "C" int cw_add_rmsnorm(float* resid, const void* delta, const float* weight, void* out,
                               const int* rows, int num_out_rows, int num_resid_rows, int H,
                               float eps, int dtype, int* status, cudaStream_t stream) {
     if (num_out_rows == 0) return CW_OK;
     if (num_out_rows < 0 || H <= 0) return CW_ERR_BAD_SIZE;
     if (rows != nullptr && delta != nullptr) return CW_ERR_UNSUPPORTED;
+    // many rows: a warp per row; few rows (decode): a block per row, for the latency of the one row
+    const bool aligned = H % 4 == 0 && H <= 4096 && ((uintptr_t)resid & 15) == 0 && ((uintptr_t)weight & 15) == 0 &&
+                         ((uintptr_t)out & 15) == 0 && ((uintptr_t)delta & 15) == 0;
+    if (rows == nullptr && num_out_rows >= 256 && aligned) {
+        if (dtype == 0)
+            return launch_rmsnorm_warp<float>(resid, (const float*)delta, weight, (float*)out, num_out_rows, H, eps, stream);
+        if (dtype == 1)
+            return launch_rmsnorm_warp<bf16>(resid, (const bf16*)delta, weight, (bf16*)out, num_out_rows, H, eps, stream);
+        return CW_ERR_BAD_DTYPE;
+    }
     const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
     if (dtype == 0)
         return cw_launch(add_rmsnorm_kernel<float>, dim3(num_out_rows), dim3(threads), 0, stream, 1, resid,

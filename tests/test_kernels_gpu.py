@@ -51,9 +51,11 @@ def test_embed(ops, status, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("h", [7, 200, 1536, 3000])
-def test_add_rmsnorm(ops, status, dtype, h):
-    n, eps = 5, 1e-5
+@pytest.mark.parametrize("n,h", [(5, 7), (5, 200), (5, 1536), (5, 3000),
+                                 # many rows: the warp-per-row kernel (row widths that fill, and do not fill, its vectors)
+                                 (300, 1536), (257, 200), (300, 3000), (260, 4096), (260, 4100), (300, 6)])
+def test_add_rmsnorm(ops, status, dtype, n, h):
+    eps = 1e-5
     resid = rand(n, h, scale=3.0)
     delta = rand(n, h, dtype=dtype, seed=1)
     weight = (1 + 0.1 * rand(h, seed=2)).float()
@@ -127,7 +129,9 @@ def test_gemm_ref_swiglu_and_silu_mul(ops, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("nh,nkv,hd,rot", [(5, 1, 48, 48), (4, 2, 64, 32), (3, 3, 16, 16)])
+@pytest.mark.parametrize("nh,nkv,hd,rot", [(5, 1, 48, 48), (4, 2, 64, 32), (3, 3, 16, 16), (12, 2, 128, 128),
+                                           # sizes that the 16-byte kernel does not take (scalar kernel)
+                                           (3, 1, 20, 10), (2, 2, 24, 8)])
 def test_rope_store(ops, status, dtype, nh, nkv, hd, rot):
     n, pages, ps, theta = 6, 5, 4, 1e6
     qkv = rand(n, (nh + 2 * nkv) * hd, dtype=dtype)
