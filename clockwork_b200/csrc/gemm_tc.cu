@@ -43,6 +43,8 @@ struct GemmParams {
     int* status;
 };
 
+#include "gemm_tc_pair.cuh"
+
 template <int BN, bool SWIGLU>
 struct Cfg {
     static constexpr int A_BYTES = BM * BK * 2;                     // 16 KB
@@ -322,7 +324,7 @@ struct PCfg {
 };
 
 template <int BN, bool SWIGLU>
-__global__ void __launch_bounds__(P_THREADS)
+__global__ void __launch_bounds__(P_THREADS, 1)
 gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_w2,
                           const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_c,
                           const GemmParams p) {
@@ -525,7 +527,26 @@ static int make_map_c(CUtensorMap* map, const void* ptr, int T, int N, long long
 struct Plan {
     int bn, splits, kb_per_split, tiles;
     bool persistent;  // bn is then any multiple of 16 and the persistent kernel runs
+    bool pair;        // ... on CTA pairs: tiles of 256 features
 };
+
+// Token-tile width for CTA pairs: per k-block a pair-tile costs about max(2 bn, 256 + bn) cycles (MMA
+// time, shared-memory traffic) and the pairs run ceil(tiles / pairs) rounds.
+static int balanced_bn_pair(int T, int N, int sm_count) {
+    const int m_tiles = (N + 2 * BM - 1) / (2 * BM), pairs = sm_count / 2;
+    long long best_cost = -1;
+    int best = 256;
+    for (int bn = 256; bn >= 64; bn -= 16) {
+        const long long tiles = (long long)m_tiles * ((T + bn - 1) / bn);
+        const long long rounds = (tiles + pairs - 1) / pairs;
+        const long long cost = rounds * (2 * bn > 256 + bn ? 2 * bn : 256 + bn);
+        if (best_cost < 0 || cost < best_cost) {
+            best_cost = cost;
+            best = bn;
+        }
+    }
+    return best;
+}
 
 // Token-tile width for the persistent kernel.  A k-block costs a tile about 256 + 2 bn cycles of
 // shared-memory traffic (the weight tile is loaded whatever bn is, SwiGLU loads two) and the CTAs
@@ -547,13 +568,18 @@ static int balanced_bn(int T, int N, bool swiglu, int sm_count) {
     return best;
 }
 
+static int g_pair_enabled = 1;
+// Switches the CTA-pair kernel off or on (measurements, tests of the single-CTA persistent kernel).
+extern "C" int cw_gemm_tc_set_pair(int on) { g_pair_enabled = on ? 1 : 0; return CW_OK; }
+
 static Plan make_plan(int T, int N, int K, bool swiglu, int sm_count, bool c_by_tma = true) {
     Plan pl;
     const int cap = swiglu ? 128 : 256;
     pl.persistent = T > 256 && sm_count > 0 && c_by_tma;  // its epilogue has no other way out than TMA
     pl.bn = T <= 16 ? 16 : (T <= 32 ? 32 : (T <= 64 ? 64 : (T <= 128 ? 128 : cap)));
-    if (pl.persistent) pl.bn = balanced_bn(T, N, swiglu, sm_count);
-    pl.tiles = ((N + BM - 1) / BM) * ((T + pl.bn - 1) / pl.bn);
+    pl.pair = pl.persistent && !swiglu && sm_count >= 2 && g_pair_enabled;
+    if (pl.persistent) pl.bn = pl.pair ? balanced_bn_pair(T, N, sm_count) : balanced_bn(T, N, swiglu, sm_count);
+    pl.tiles = pl.pair ? ((N + 2 * BM - 1) / (2 * BM)) * ((T + pl.bn - 1) / pl.bn) : ((N + BM - 1) / BM) * ((T + pl.bn - 1) / pl.bn);
     const int num_kb = (K + BK - 1) / BK;
     int splits = 1;
     const bool can_split = pl.bn <= 64 || (pl.bn == 128 && !swiglu);  // Cfg::CAN_SPLIT
@@ -609,7 +635,7 @@ extern "C" int cw_gemm_tc_plan(int T, int N, int K, int swiglu, int sm_count, in
     const Plan pl = make_plan(T, N, K, swiglu != 0, sm_count);
     *bn = pl.bn;
     *splits = pl.splits;
-    *ctas = pl.tiles * pl.splits;
+    *ctas = pl.pair ? 2 * pl.tiles : pl.tiles * pl.splits;
     return CW_OK;
 }
 
@@ -634,7 +660,7 @@ extern "C" int cw_gemm_tc(const void* X, const void* W, const void* W2, const fl
     CUtensorMap mw, mw2, mx;
     if (make_map(&mw, W, N, K, K, BM) != 0) return CW_ERR_UNSUPPORTED;
     if (make_map(&mw2, swiglu ? W2 : W, N, K, K, BM) != 0) return CW_ERR_UNSUPPORTED;
-    if (make_map(&mx, X, T, K, ldx, pl.bn) != 0) return CW_ERR_UNSUPPORTED;
+    if (make_map(&mx, X, T, K, ldx, pl.pair ? pl.bn / 2 : pl.bn) != 0) return CW_ERR_UNSUPPORTED;
     const bool tma_store = pl.splits == 1 && c_by_tma;
     // prompt portions: the persistent kernel, whose epilogue overlaps the next tile's MMAs
     const bool persistent = pl.persistent;
@@ -647,6 +673,17 @@ extern "C" int cw_gemm_tc(const void* X, const void* W, const void* W2, const fl
     p.bias = bias; p.C = C; p.status = status; p.bn = pl.bn;
     dim3 grid((N + BM - 1) / BM, (T + pl.bn - 1) / pl.bn, pl.splits);
     if (grid.y > 65535) return CW_ERR_BAD_SIZE;
+    if (pl.pair) {
+        static bool configured = false;
+        if (!configured) {
+            if (cudaFuncSetAttribute(gemm_tc_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PairCfg::SMEM_BYTES) !=
+                cudaSuccess)
+                return (int)cudaGetLastError();
+            configured = true;
+        }
+        const int pairs = pl.tiles < sm_count / 2 ? pl.tiles : sm_count / 2;
+        return cw_launch(gemm_tc_pair_kernel, dim3(2 * pairs), dim3(PAIR_THREADS), PairCfg::SMEM_BYTES, stream, 1, mw, mx, mc, p);
+    }
     if (persistent) {
         const int ctas = pl.tiles < sm_count ? pl.tiles : sm_count;
         return swiglu ? launch_persistent<128, true>(mw, mw2, mx, mc, p, ctas, stream)

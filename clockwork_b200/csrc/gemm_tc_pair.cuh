@@ -1,0 +1,241 @@
+// The matrix product for prompt portions on CTA pairs (tcgen05 cta_group::2).
+//
+// Two CTAs of a cluster, on neighbouring SMs, share one tile of 256 output features x bn tokens:
+// each loads its own 128 rows of W and only half of the token tile, and the leader's one thread
+// issues MMAs of M = 256 that run on both SMs' tensor cores and read the token tile from both
+// shared memories.  Against two independent 128 x bn tiles that halves the token-operand traffic
+// per SM (TMA writes and tensor-core reads of shared memory), which is what bounds the single-CTA
+// kernel.  Each CTA keeps the accumulator of its own 128 features in its own tensor memory (two
+// buffers: the epilogue of one tile overlaps the MMAs of the next) and stores it itself.
+//
+// Barriers: `full[s]` lives in the leader and counts one arrive.expect_tx per CTA plus the bytes
+// of both CTAs' copies (the peer's copies signal it through the cluster's shared-memory window);
+// `empty[s]` and `acc_full[b]` are signalled in both CTAs at once by a multicast tcgen05.commit;
+// `acc_empty[b]` lives in the leader and counts one arrival per CTA's epilogue.  Every wait is
+// bounded; a CTA that gives up records CW_ST_WAIT_TIMEOUT, and both CTAs meet at the cluster
+// barrier before tensor memory is freed.
+#pragma once
+#include "tc_common.cuh"
+
+#define PAIR_THREADS 192
+#define PAIR_CHUNK 16            // tokens per epilogue store
+#define PAIR_MAX_SMEM (227 * 1024)
+
+struct PairCfg {
+    static constexpr int BN_MAX = 256;                           // BM = 128 and BK = 64 as in the single-CTA kernels
+    static constexpr int A_BYTES = BM * BK * 2;                  // this CTA's 128 rows of W
+    static constexpr int B_BYTES = (BN_MAX / 2) * BK * 2;        // its half of the token tile
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    static constexpr int OUT_BYTES = 2 * PAIR_CHUNK * BM * 4;    // two staging buffers of [16 tokens][128 features]
+    static constexpr int STAGES = (PAIR_MAX_SMEM - 2048 - OUT_BYTES) / STAGE_BYTES;
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + OUT_BYTES + 1024 + 1024;
+    static constexpr int TMEM_COLS = 512;                        // two accumulators of up to 256 columns
+    static_assert(STAGES >= 4, "too few operand stages");
+};
+
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t result_slot, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(result_slot), "r"(cols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void umma_bf16_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                               uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// Arrives, when the MMAs issued so far are complete, on the barrier at this offset in both CTAs.
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
+    asm volatile(
+        "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+        ::"r"(bar), "h"((uint16_t)3)
+        : "memory");
+}
+// A tile copy whose completion bytes go to a barrier that may lie in the other CTA of the pair.
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t cluster_bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(map), "r"(cluster_bar), "r"(x), "r"(y)
+        : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx_cluster(uint32_t cluster_bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cluster.b64 _, [%0], %1;" ::"r"(cluster_bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar) {
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
+}
+
+// Tiles: 256 features x p.bn tokens per pair; p.bn is a multiple of 16 (each CTA holds p.bn / 2 token
+// rows, whole swizzle atoms of 8).  map_x's box is p.bn / 2 rows, map_c's box [16 tokens][128 features].
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1)
+gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+                    const __grid_constant__ CUtensorMap map_c, const GemmParams p) {
+    using C = PairCfg;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint8_t* out_s = smem + C::STAGES * C::STAGE_BYTES;
+    uint64_t* bars = (uint64_t*)(out_s + C::OUT_BYTES);
+    // bars: full[S], empty[S], acc_full[2], acc_empty[2]
+    uint32_t* tmem_slot = (uint32_t*)(bars + 2 * C::STAGES + 4);
+    volatile int* give_up = (volatile int*)(tmem_slot + 1);
+
+    pdl_launch_dependents();
+    pdl_wait();
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const uint32_t rank = cluster_rank();  // 0: the leader, which issues the MMAs
+    const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + C::STAGES);
+    const uint32_t accf0 = smem_u32(bars + 2 * C::STAGES), acce0 = smem_u32(bars + 2 * C::STAGES + 2);
+    const int bn = p.bn, half_bn = bn >> 1;
+    const int m_tiles = (p.N + 2 * BM - 1) / (2 * BM), n_tiles = (p.T + bn - 1) / bn;
+    const int tiles = m_tiles * n_tiles;
+    const int pair = blockIdx.x >> 1, pairs = gridDim.x >> 1;
+
+    if (tid == 0) {
+        for (int s = 0; s < C::STAGES; ++s) {
+            mbar_init(full0 + 8 * s, 2);   // one arrive.expect_tx per CTA (used in the leader only)
+            mbar_init(empty0 + 8 * s, 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(accf0 + 8 * b, 1);
+            mbar_init(acce0 + 8 * b, 2);   // one arrival per CTA's epilogue (used in the leader only)
+        }
+        *give_up = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) tmem_alloc_pair(smem_u32(tmem_slot), C::TMEM_COLS);
+    tc_fence_before();
+    cluster_sync();  // both CTAs' barriers are initialised before either signals the other's
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0 && lane == 0) {
+        // ---- TMA producer (both CTAs): own rows of W, own half of the token tile ------------------------
+        const uint32_t stage_tx = C::A_BYTES + half_bn * BK * 2;
+        int i = 0;
+        bool ok = true;
+        for (int tile = pair; tile < tiles && ok; tile += pairs) {
+            const int m0 = (tile % m_tiles) * 2 * BM + (int)rank * BM;
+            const int n0 = (tile / m_tiles) * bn + (int)rank * half_bn;
+            for (int kb = 0; kb < p.num_kb; ++kb, ++i) {
+                const int s = i % C::STAGES;
+                ok = mbar_wait(empty0 + 8 * s, ((i / C::STAGES) & 1) ^ 1, give_up);
+                if (!ok) break;
+                const uint32_t a_dst = smem_u32(smem + s * C::STAGE_BYTES);
+                const uint32_t bar = dsmem_addr(full0 + 8 * s, 0);  // the leader's barrier
+                mbar_expect_tx_cluster(bar, stage_tx);
+                tma_load_2d_pair(a_dst, &map_w, kb * BK, m0, bar);
+                tma_load_2d_pair(a_dst + C::A_BYTES, &map_x, kb * BK, n0, bar);
+            }
+        }
+        if (*give_up) {
+            // copies may still be in flight into this CTA's shared memory, and their barrier lies in the
+            // leader: let them land before the CTA goes on to the final barrier and leaves
+            const long long t0 = clock64();
+            while (clock64() - t0 < 2000000LL) {
+            }
+        }
+    } else if (warp == 1 && lane == 0 && rank == 0) {
+        // ---- MMA issuer (leader only): tile `it` accumulates into TMEM buffer it & 1 of both CTAs ---------
+        const uint32_t idesc = instr_desc(2 * BM, bn);
+        int i = 0, it = 0;
+        bool ok = true;
+        for (int tile = pair; tile < tiles && ok; tile += pairs, ++it) {
+            const int buf = it & 1;
+            ok = mbar_wait(acce0 + 8 * buf, ((it >> 1) & 1) ^ 1, give_up);  // both epilogues have drained it
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t acc = tmem_base + buf * C::BN_MAX;
+            for (int kb = 0; kb < p.num_kb; ++kb, ++i) {
+                const int s = i % C::STAGES;
+                ok = mbar_wait(full0 + 8 * s, (i / C::STAGES) & 1, give_up);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t a_addr = smem_u32(smem + s * C::STAGE_BYTES);
+                const uint64_t adesc = smem_desc_sw128(a_addr);
+                const uint64_t bdesc = smem_desc_sw128(a_addr + C::A_BYTES);
+#pragma unroll
+                for (int k = 0; k < BK / 16; ++k)
+                    umma_bf16_pair(acc, adesc + 2 * k, bdesc + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                umma_commit_pair(empty0 + 8 * s);  // the stage is free in both CTAs
+            }
+            if (ok) umma_commit_pair(accf0 + 8 * buf);
+        }
+    } else if (warp >= 2) {
+        // ---- epilogue warps (both CTAs): warp w reads TMEM lanes 32 (w % 4) .. +31 of its own CTA --------
+        const int quarter = warp & 3;
+        const int row = quarter * 32 + lane;
+        const int etid = tid - 64;
+        const bool wide = p.epilogue != 0;
+        const uint32_t acce_leader = dsmem_addr(acce0, 0);
+        int it = 0, chunk_no = 0;
+        bool ok = true;
+        for (int tile = pair; tile < tiles && ok; tile += pairs, ++it) {
+            const int buf = it & 1;
+            const int m0 = (tile % m_tiles) * 2 * BM + (int)rank * BM;
+            const int n0 = (tile / m_tiles) * bn;
+            const int f = m0 + row;
+            ok = mbar_wait(accf0 + 8 * buf, (it >> 1) & 1, give_up);
+            {
+                // one decision for all 128 threads: they meet at named barriers below
+                uint32_t all_ok;
+                asm volatile(
+                    "{ .reg .pred p, q; setp.ne.u32 q, %1, 0; bar.red.and.pred p, 3, 128, q; selp.u32 %0, 1, 0, p; }"
+                    : "=r"(all_ok)
+                    : "r"((uint32_t)ok)
+                    : "memory");
+                ok = all_ok != 0;
+            }
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t taddr = tmem_base + buf * C::BN_MAX + ((uint32_t)(quarter * 32) << 16);
+            const float bias = (p.bias != nullptr && f < p.N) ? p.bias[f] : 0.f;
+            for (int c = 0; c < bn; c += PAIR_CHUNK, ++chunk_no) {
+                float g[16];
+                tmem_ld16(taddr + c, g);
+                if (c + PAIR_CHUNK >= bn) {
+                    // the accumulator has been read out: hand the buffer back to the leader's MMA thread
+                    tc_fence_before();
+                    asm volatile("bar.sync 1, 128;" ::: "memory");
+                    if (etid == 0) mbar_arrive_cluster(acce_leader + 8 * buf);
+                }
+                float* st32 = (float*)(out_s + (chunk_no & 1) * (C::OUT_BYTES / 2));
+                // the store that used this staging buffer two chunks ago must have read it
+                if (etid == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+                asm volatile("bar.sync 2, 128;" ::: "memory");
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    const float v = g[j] + bias;
+                    if (wide)
+                        st32[j * BM + row] = v;
+                    else
+                        ((bf16*)st32)[j * BM + row] = __float2bfloat16_rn(v);
+                }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (etid == 0 && n0 + c < p.T && m0 < p.N) {
+                    if (p.epilogue == 1)
+                        asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.bulk_group [%0, {%2, %3}], [%1];"
+                                     ::"l"(&map_c), "r"(smem_u32(st32)), "r"(m0), "r"(n0 + c) : "memory");
+                    else
+                        asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+                                     ::"l"(&map_c), "r"(smem_u32(st32)), "r"(m0), "r"(n0 + c) : "memory");
+                    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                }
+            }
+        }
+        if (etid == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");  // all stores done before exit
+    }
+    __syncwarp();
+    if (*give_up && tid == 0) cw_report(p.status, CW_ST_WAIT_TIMEOUT, blockIdx.x, -2);
+    // Neither CTA leaves, or frees tensor memory, while the other may still signal its barriers or
+    // while MMAs that read its shared memory may be in flight.
+    tc_fence_before();
+    cluster_sync();
+    if (warp == 1) tmem_dealloc_pair(tmem_base, C::TMEM_COLS);
+}

@@ -26,7 +26,16 @@ def _configure() -> None:
     lib.cw_gemm_tc.restype = c_int
     lib.cw_gemm_tc_plan.argtypes = [I, I, I, I, I, POINTER(c_int), POINTER(c_int), POINTER(c_int)]
     lib.cw_gemm_tc_plan.restype = c_int
+    lib.cw_gemm_tc_set_pair.argtypes = [I]
+    lib.cw_gemm_tc_set_pair.restype = c_int
     _configured = True
+
+
+def set_pair_kernel(on: bool) -> None:
+    """Prompt-portion products run on CTA pairs (tcgen05 cta_group::2) by default; ``False`` keeps them
+    on the single-CTA persistent kernel (for measurements and for testing that kernel)."""
+    _configure()
+    library().cw_gemm_tc_set_pair(1 if on else 0)
 
 
 def _device_state(device: torch.device) -> dict:

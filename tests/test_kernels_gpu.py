@@ -308,7 +308,7 @@ TC_SHAPES = [
     (1, 2048, 1536), (8, 1536, 8960), (8, 200, 72), (16, 1536, 1536), (17, 384, 200), (64, 2048, 1536),
     (100, 130, 264), (300, 1000, 512), (512, 1536, 1536), (2048, 2048, 1536),
     # more tiles than SMs: the persistent kernel, two to three tiles per CTA, ragged in both directions
-    (2100, 3000, 264), (2048, 5000, 512),
+    (2100, 3000, 264), (2048, 5000, 512), (2048, 1536, 8960), (1000, 130, 200), (260, 2048, 1536),
 ]
 
 
@@ -321,6 +321,16 @@ def gemm_tc():
 
 def bf16_product(x, w):
     return (x.double() @ w.double().T).float()
+
+
+@pytest.mark.parametrize("t,n,k", [(300, 1000, 512), (2100, 3000, 264), (2048, 5000, 512)])
+def test_gemm_tc_single_cta_persistent_kernel(ops, gemm_tc, t, n, k):
+    """Prompt portions run on CTA pairs by default; the single-CTA persistent kernel stays reachable."""
+    gemm_tc.set_pair_kernel(False)
+    try:
+        test_gemm_tc_against_float64(ops, gemm_tc, t, n, k)
+    finally:
+        gemm_tc.set_pair_kernel(True)
 
 
 @pytest.mark.parametrize("t,n,k", TC_SHAPES)
