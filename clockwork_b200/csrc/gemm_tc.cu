@@ -41,6 +41,18 @@ struct GemmParams {
     const float* bias;    // [N] or null
     void* C;
     int* status;
+    // An RMSNorm between two products, split over them (gemm_tc_kernel only, token tiles up to 128).
+    // The product before the norm (epilogue 1, the new residual C in hand) also writes
+    // emit_x[t, f] = bf16(C[t, f] * emit_g[f]) and, per 128-feature tile, emit_part[t, tile] = the sum of
+    // C[t, f]^2 over the tile's features.  The product after the norm takes emit_x as X and finishes
+    // the norm in its epilogue: acc * rsqrt(sum(scale_part[t, :]) / scale_dim + scale_eps) (+ bias).
+    const float* scale_part;  // [T, scale_parts] or null
+    int scale_parts;
+    float scale_eps;
+    int scale_dim;
+    const float* emit_g;      // [N] or null
+    bf16* emit_x;             // [T, N]
+    float* emit_part;         // [T, gridDim.x]
 };
 
 #include "gemm_tc_pair.cuh"
@@ -162,8 +174,22 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     }
     __syncwarp();
     // ---- epilogue: every thread owns one output feature (TMEM lane) -----------------------------
-    const bool acc_ready = mbar_wait(acc_bar, 0, give_up);
+    const bool acc_ready = __syncthreads_and(mbar_wait(acc_bar, 0, give_up) ? 1 : 0) != 0;  // one answer for the CTA
     pdl_wait();  // the epilogue reads and writes what preceding kernels wrote
+    constexpr bool NORM_OK = BN <= 128;  // the shared arrays below hold 128 tokens
+    float* inv_s = (float*)((uint8_t*)bars + 256);  // [128] the tokens' 1/rms, when a norm is finished here
+    float* red_s = inv_s + 128;                     // [4][16] per-warp sums of squares, when one is begun here
+    const bool scaled = NORM_OK && p.scale_part != nullptr;
+    if (scaled) {
+        if (tid < BN) {
+            const int t = n0 + tid;
+            float ssq = 0.f;
+            if (t < p.T)
+                for (int i = 0; i < p.scale_parts; ++i) ssq += p.scale_part[(size_t)t * p.scale_parts + i];
+            inv_s[tid] = 1.0f / sqrtf(ssq / (float)p.scale_dim + p.scale_eps);
+        }
+        __syncthreads();
+    }
     tc_fence_after();
     __syncwarp();
     const int row = warp * 32 + lane;  // feature within the tile
@@ -216,8 +242,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             if (SWIGLU) tmem_ld16(taddr + BN + c, u);
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
-                float v = g[j] + bias;
-                if (SWIGLU) v = __fdividef(v, 1.0f + __expf(-v)) * u[j];
+                const float sc = scaled ? inv_s[c + j] : 1.0f;
+                float v = g[j] * sc + bias;
+                if (SWIGLU) v = __fdividef(v, 1.0f + __expf(-v)) * (u[j] * sc);
                 if (wide)
                     stage[(c + j) * BM + row] = v;
                 else
@@ -229,6 +256,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         if (tid == 0) tma_store_2d(&map_c, stage_addr, m0, n0, !SWIGLU && p.epilogue == 1);
         c_begin = c_end = 0;  // nothing left for the direct path
     }
+    const bool emit = !SWIGLU && NORM_OK && p.emit_x != nullptr && p.epilogue == 1;  // the same in the whole CTA
+    const float emit_gf = (emit && f < p.N) ? p.emit_g[f] : 0.f;
     for (int c = c_begin; c < c_end && (acc_ready || p.splits > 1); c += 16) {
         const int ncols = min(16, c_end - c);
         float g[16], u[16];
@@ -249,8 +278,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 }
             }
         }
+        const int t_base = n0 + c;
+        float sq[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) sq[j] = 0.f;
         if (f < p.N) {
-            const int t_base = n0 + c;
             float* c32 = (float*)p.C + (size_t)t_base * p.ldc + f;
             bf16* c16 = (bf16*)p.C + (size_t)t_base * p.ldc + f;
             float old[16];
@@ -265,20 +297,41 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 // no early exit from this loop: the 16 columns are independent and the compiler
                 // interleaves their arithmetic only when the loop is straight-line
                 const bool live = j < ncols && t_base + j < p.T;
-                const float v = g[j] + bias;
+                const float sc = scaled ? inv_s[(c + j) & (BN - 1)] : 1.0f;
+                const float v = g[j] * sc + bias;
                 if (SWIGLU) {
                     // silu(v) * u with the fast exponential and division: the result is rounded to
                     // bfloat16 (8 bits) right after, their 2^-21 relative error does not show
-                    const float act = __fdividef(v, 1.0f + __expf(-v)) * u[j];
+                    const float act = __fdividef(v, 1.0f + __expf(-v)) * (u[j] * sc);
                     if (live) c16[(size_t)j * p.ldc] = __float2bfloat16_rn(act);
                 } else if (p.epilogue == 0) {
                     if (live) c16[(size_t)j * p.ldc] = __float2bfloat16_rn(v);
                 } else if (p.epilogue == 1) {
-                    if (live) c32[(size_t)j * p.ldc] = old[j] + v;
+                    const float nv = old[j] + v;
+                    if (live) {
+                        c32[(size_t)j * p.ldc] = nv;
+                        if (emit) {
+                            p.emit_x[(size_t)(t_base + j) * p.N + f] = __float2bfloat16_rn(nv * emit_gf);
+                            sq[j] = nv * nv;
+                        }
+                    }
                 } else {
                     if (live) c32[(size_t)j * p.ldc] = v;
                 }
             }
+        }
+        if (emit) {
+            // the tile's share of each token's sum of squares: over the warp, then over the four warps
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+                const float w = warp_sum(sq[j]);
+                if (lane == 0) red_s[warp * 16 + j] = w;
+            }
+            __syncthreads();
+            if (tid < ncols && t_base + tid < p.T)
+                p.emit_part[(size_t)(t_base + tid) * gridDim.x + blockIdx.x] =
+                    (red_s[tid] + red_s[16 + tid]) + (red_s[32 + tid] + red_s[48 + tid]);
+            __syncthreads();
         }
     }
     // ---- teardown ---------------------------------------------------------------------------------
@@ -569,6 +622,13 @@ static int balanced_bn(int T, int N, bool swiglu, int sm_count) {
 }
 
 static int g_pair_enabled = 1;
+static int g_forced_bn = 0;
+// Forces the token-tile width of the prompt-portion kernels (0: chosen automatically); for measurements.
+extern "C" int cw_gemm_tc_set_tile(int bn) {
+    if (bn != 0 && (bn < 64 || bn > 256 || bn % 16 != 0)) return CW_ERR_BAD_SIZE;
+    g_forced_bn = bn;
+    return CW_OK;
+}
 // Switches the CTA-pair kernel off or on (measurements, tests of the single-CTA persistent kernel).
 extern "C" int cw_gemm_tc_set_pair(int on) { g_pair_enabled = on ? 1 : 0; return CW_OK; }
 
@@ -579,6 +639,7 @@ static Plan make_plan(int T, int N, int K, bool swiglu, int sm_count, bool c_by_
     pl.bn = T <= 16 ? 16 : (T <= 32 ? 32 : (T <= 64 ? 64 : (T <= 128 ? 128 : cap)));
     pl.pair = pl.persistent && !swiglu && sm_count >= 2 && g_pair_enabled;
     if (pl.persistent) pl.bn = pl.pair ? balanced_bn_pair(T, N, sm_count) : balanced_bn(T, N, swiglu, sm_count);
+    if (pl.persistent && g_forced_bn != 0 && (!swiglu || g_forced_bn <= 128)) pl.bn = g_forced_bn;
     pl.tiles = pl.pair ? ((N + 2 * BM - 1) / (2 * BM)) * ((T + pl.bn - 1) / pl.bn) : ((N + BM - 1) / BM) * ((T + pl.bn - 1) / pl.bn);
     const int num_kb = (K + BK - 1) / BK;
     int splits = 1;
@@ -642,9 +703,29 @@ extern "C" int cw_gemm_tc_plan(int T, int N, int K, int swiglu, int sm_count, in
 // X [T, K] (row stride ldx), W [N, K] (and W2 for SwiGLU), C [T, ldc].  K must be a multiple of 8
 // and all bases 16-byte aligned (TMA); returns CW_ERR_UNSUPPORTED otherwise so the caller can
 // use the plain kernel.
+//
+// The `_norm` form splits an RMSNorm over two products (see GemmParams): with `scale_part` this
+// product finishes a norm whose un-normalised, weight-multiplied rows it got as X; with `emit_x`
+// (epilogue 1 only) it begins the norm that follows it.  Both need at most 128 tokens
+// (CW_ERR_UNSUPPORTED otherwise).
+extern "C" int cw_gemm_tc_norm(const void* X, const void* W, const void* W2, const float* bias, void* C, int T,
+                               int N, int K, int ldx, int ldc, int epilogue, int sm_count,
+                               const float* scale_part, int scale_parts, float scale_eps, int scale_dim,
+                               const float* emit_g, void* emit_x, float* emit_part, int* status,
+                               cudaStream_t stream);
+
 extern "C" int cw_gemm_tc(const void* X, const void* W, const void* W2, const float* bias, void* C, int T,
                           int N, int K, int ldx, int ldc, int epilogue, int sm_count, int* status,
                           cudaStream_t stream) {
+    return cw_gemm_tc_norm(X, W, W2, bias, C, T, N, K, ldx, ldc, epilogue, sm_count, nullptr, 0, 0.f, 1, nullptr,
+                           nullptr, nullptr, status, stream);
+}
+
+extern "C" int cw_gemm_tc_norm(const void* X, const void* W, const void* W2, const float* bias, void* C, int T,
+                               int N, int K, int ldx, int ldc, int epilogue, int sm_count,
+                               const float* scale_part, int scale_parts, float scale_eps, int scale_dim,
+                               const float* emit_g, void* emit_x, float* emit_part, int* status,
+                               cudaStream_t stream) {
     if (T == 0 || N == 0) return CW_OK;
     if (T < 0 || N < 0 || K <= 0 || ldx < K || ldc < N) return CW_ERR_BAD_SIZE;
     if (epilogue < 0 || epilogue > 2) return CW_ERR_UNSUPPORTED;
@@ -657,11 +738,17 @@ extern "C" int cw_gemm_tc(const void* X, const void* W, const void* W2, const fl
     const long long c_row_bytes = (long long)ldc * (c_f32 ? 4 : 2);
     const bool c_by_tma = c_row_bytes % 16 == 0 && ((uintptr_t)C & 15) == 0;
     const Plan pl = make_plan(T, N, K, swiglu, sm_count, c_by_tma);
+    const bool emits = emit_x != nullptr;
+    if (scale_part != nullptr || emits) {
+        if (pl.persistent || pl.bn > 128) return CW_ERR_UNSUPPORTED;
+        if (scale_part != nullptr && (scale_parts <= 0 || scale_dim <= 0)) return CW_ERR_BAD_SIZE;
+        if (emits && (epilogue != 1 || swiglu || emit_g == nullptr || emit_part == nullptr)) return CW_ERR_UNSUPPORTED;
+    }
     CUtensorMap mw, mw2, mx;
     if (make_map(&mw, W, N, K, K, BM) != 0) return CW_ERR_UNSUPPORTED;
     if (make_map(&mw2, swiglu ? W2 : W, N, K, K, BM) != 0) return CW_ERR_UNSUPPORTED;
     if (make_map(&mx, X, T, K, ldx, pl.pair ? pl.bn / 2 : pl.bn) != 0) return CW_ERR_UNSUPPORTED;
-    const bool tma_store = pl.splits == 1 && c_by_tma;
+    const bool tma_store = pl.splits == 1 && c_by_tma && !emits;  // beginning a norm needs the new values in hand
     // prompt portions: the persistent kernel, whose epilogue overlaps the next tile's MMAs
     const bool persistent = pl.persistent;
     CUtensorMap mc = mx;
@@ -671,6 +758,8 @@ extern "C" int cw_gemm_tc(const void* X, const void* W, const void* W2, const fl
     p.T = T; p.N = N; p.K = K; p.ldc = ldc; p.epilogue = epilogue;
     p.num_kb = (K + BK - 1) / BK; p.kb_per_split = pl.kb_per_split; p.splits = pl.splits;
     p.bias = bias; p.C = C; p.status = status; p.bn = pl.bn;
+    p.scale_part = scale_part; p.scale_parts = scale_parts; p.scale_eps = scale_eps; p.scale_dim = scale_dim;
+    p.emit_g = emit_g; p.emit_x = (bf16*)emit_x; p.emit_part = emit_part;
     dim3 grid((N + BM - 1) / BM, (T + pl.bn - 1) / pl.bn, pl.splits);
     if (grid.y > 65535) return CW_ERR_BAD_SIZE;
     if (pl.pair) {

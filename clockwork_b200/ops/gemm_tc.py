@@ -5,7 +5,7 @@ meet in distributed shared memory, so a call needs no scratch memory."""
 
 from __future__ import annotations
 
-from ctypes import POINTER, byref, c_int, c_longlong, c_void_p
+from ctypes import POINTER, byref, c_float, c_int, c_longlong, c_void_p
 
 import torch
 
@@ -24,11 +24,21 @@ def _configure() -> None:
     P, I, LL = c_void_p, c_int, c_longlong
     lib.cw_gemm_tc.argtypes = [P, P, P, P, P, I, I, I, I, I, I, I, P, P]
     lib.cw_gemm_tc.restype = c_int
+    lib.cw_gemm_tc_norm.argtypes = [P, P, P, P, P, I, I, I, I, I, I, I, P, I, c_float, I, P, P, P, P, P]
+    lib.cw_gemm_tc_norm.restype = c_int
     lib.cw_gemm_tc_plan.argtypes = [I, I, I, I, I, POINTER(c_int), POINTER(c_int), POINTER(c_int)]
     lib.cw_gemm_tc_plan.restype = c_int
     lib.cw_gemm_tc_set_pair.argtypes = [I]
     lib.cw_gemm_tc_set_pair.restype = c_int
+    lib.cw_gemm_tc_set_tile.argtypes = [I]
+    lib.cw_gemm_tc_set_tile.restype = c_int
     _configured = True
+
+
+def set_token_tile(bn: int) -> None:
+    """Forces the token-tile width of the prompt-portion kernels (a multiple of 16 in 64..256; 0: automatic)."""
+    _configure()
+    check(library().cw_gemm_tc_set_tile(int(bn)), "gemm_tc_set_tile")
 
 
 def set_pair_kernel(on: bool) -> None:
@@ -73,7 +83,16 @@ def accepts(x: torch.Tensor, w: torch.Tensor) -> bool:
     return w.is_contiguous()
 
 
-def _run(x, w, w2, bias, out, epilogue) -> None:
+NORM_SPLIT_MAX_TOKENS = 128  # the kernel that can begin or finish a norm takes token tiles up to this
+
+
+def norm_tiles(n: int) -> int:
+    """Partial sums of squares per token that a product with N = ``n`` output features writes when it
+    begins a norm: one per tile of 128 features."""
+    return (n + 127) // 128
+
+
+def _run(x, w, w2, bias, out, epilogue, row_scale=None, emit=None) -> None:
     _configure()
     st = _device_state(x.device)
     t, k = x.shape
@@ -81,14 +100,39 @@ def _run(x, w, w2, bias, out, epilogue) -> None:
     ldx = x.stride(0) if t > 1 else max(x.stride(0), k)
     if ldx % 8:
         ldx = k
-    check(library().cw_gemm_tc(_ptr(x), _ptr(w), _ptr(w2), _ptr(bias), _ptr(out), t, n, k, ldx, out.stride(0), epilogue,
-                               st["sms"], _ptr(st["status"]), _stream()), "gemm_tc")
+    if row_scale is None and emit is None:
+        check(library().cw_gemm_tc(_ptr(x), _ptr(w), _ptr(w2), _ptr(bias), _ptr(out), t, n, k, ldx, out.stride(0), epilogue,
+                                   st["sms"], _ptr(st["status"]), _stream()), "gemm_tc")
+        return
+    parts, eps, dim = row_scale if row_scale is not None else (None, 0.0, 1)
+    if parts is not None:
+        _need(parts, torch.float32, "row_scale parts", 2)
+        if parts.shape[0] != t or not parts.is_contiguous():
+            raise ValueError("row_scale parts must be a contiguous [T, P] tensor")
+    g, ex, ep = emit if emit is not None else (None, None, None)
+    if emit is not None:
+        _need(g, torch.float32, "emit weight", 1)
+        _need(ex, torch.bfloat16, "emit x", 2)
+        _need(ep, torch.float32, "emit parts", 2)
+        if g.shape[0] != n or tuple(ex.shape) != (t, n) or tuple(ep.shape) != (t, norm_tiles(n)) or not (
+                ex.is_contiguous() and ep.is_contiguous()):
+            raise ValueError("emit buffers must be weight [N], x [T, N], parts [T, ceil(N / 128)], contiguous")
+    check(library().cw_gemm_tc_norm(
+        _ptr(x), _ptr(w), _ptr(w2), _ptr(bias), _ptr(out), t, n, k, ldx, out.stride(0), epilogue, st["sms"],
+        _ptr(parts), 0 if parts is None else parts.shape[1], float(eps), int(dim), _ptr(g), _ptr(ex), _ptr(ep),
+        _ptr(st["status"]), _stream()), "gemm_tc_norm")
 
 
 def gemm(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None, *, out: torch.Tensor | None = None,
-         epilogue: int = EPILOGUE_STORE) -> torch.Tensor:
+         epilogue: int = EPILOGUE_STORE, row_scale: tuple | None = None, emit: tuple | None = None) -> torch.Tensor:
     """``x [T,K] @ w[N,K]^T (+ bias)`` in bfloat16 on the tensor cores, float32 accumulation.
-    Epilogues as for ``gemm_ref``: store bfloat16, add into float32 ``out``, store float32."""
+    Epilogues as for ``gemm_ref``: store bfloat16, add into float32 ``out``, store float32.
+
+    An RMSNorm between two products can be split over them (at most ``NORM_SPLIT_MAX_TOKENS`` rows).
+    ``emit=(g, xg, parts)`` with the add epilogue: beside ``out += ...`` the kernel writes
+    ``xg = bf16(out * g)`` and per-token partial sums of ``out**2`` into ``parts [T, norm_tiles(N)]``.
+    ``row_scale=(parts, eps, dim)``: ``x`` is such an ``xg`` and the product is multiplied, row by row,
+    by ``rsqrt(parts.sum(1) / dim + eps)`` before the bias is added."""
     _need(w, torch.bfloat16, "w", 2)
     t, k = x.shape
     n = w.shape[0]
@@ -104,17 +148,17 @@ def gemm(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None, *, 
     _need(out, want, "out", 2)
     if tuple(out.shape) != (t, n):
         raise ValueError(f"out has shape {tuple(out.shape)}, expected {(t, n)}")
-    _run(x, w, None, bias, out, epilogue)
+    _run(x, w, None, bias, out, epilogue, row_scale, emit)
     return out
 
 
-def gemm_swiglu(x: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor) -> torch.Tensor:
+def gemm_swiglu(x: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor, row_scale: tuple | None = None) -> torch.Tensor:
     _need(w_gate, torch.bfloat16, "w_gate", 2)
     _need(w_up, torch.bfloat16, "w_up", 2)
     if w_gate.shape != w_up.shape or w_gate.shape[1] != x.shape[1]:
         raise ValueError("gate and up weights must both be [N, K] with x's K")
     out = torch.empty((x.shape[0], w_gate.shape[0]), dtype=torch.bfloat16, device=x.device)
-    _run(x, w_gate, w_up, None, out, 0)
+    _run(x, w_gate, w_up, None, out, 0, row_scale)
     return out
 
 

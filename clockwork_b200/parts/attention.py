@@ -23,6 +23,8 @@ from .registry import build_part, register_mixer
 
 
 class Attention(Mixer):
+    takes_half_normed = True  # x only feeds the q/k/v product
+
     def __init__(self, spec, prefix, dtype, device) -> None:
         super().__init__(spec, prefix, dtype, device)
         p = spec.params
@@ -81,7 +83,7 @@ class Attention(Mixer):
             self.position.apply_and_store(ctx, qkv, view, self.num_heads, self.num_kv_heads, self.head_dim)
         out = attention_ops.paged_attention(ctx, qkv, view, self.num_heads, self.num_kv_heads,
                                             self.head_dim, self.scale, self.window, fused_position=fused)
-        self.o.add_into(out, stream.residual_after_flush())
+        self.o.add_into(out, stream.residual_after_flush(), stream)
         return None
 
 

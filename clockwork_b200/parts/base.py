@@ -102,11 +102,18 @@ class StepContext:
 
 
 class ResidualStream:
-    """The float32 residual [N, H] plus at most one contribution not yet added to it."""
+    """The float32 residual [N, H] plus at most one contribution not yet added to it.
+
+    A norm between two matrix products can be split over them (``ops.gemm.RowScaled``): the block
+    names the norm that comes next in ``next_norm``; a product that adds into the residual may then
+    begin that norm in its epilogue and leave the result in ``half_norm``; the norm hands it on to a
+    consumer that can finish it, or ignores it.  Whoever changes the residual drops ``half_norm``."""
 
     def __init__(self, residual: torch.Tensor) -> None:
         self.residual = residual
         self.pending: torch.Tensor | None = None
+        self.next_norm = None   # the Norm part that will read the residual next, if the block knows it
+        self.half_norm = None   # (norm weight, x * weight in bfloat16, per-row partial sums of squares)
 
     def push(self, delta: torch.Tensor | None) -> None:
         if delta is None:
@@ -114,6 +121,7 @@ class ResidualStream:
         if self.pending is not None:
             self.flush()
         self.pending = delta
+        self.half_norm = None
 
     def flush(self) -> None:
         if self.pending is not None:
@@ -121,11 +129,18 @@ class ResidualStream:
 
             ops.add_to_residual(self.residual, self.pending)
             self.pending = None
+            self.half_norm = None
 
     def residual_after_flush(self) -> torch.Tensor:
         """The float32 residual with nothing pending: what a fused epilogue adds into."""
         self.flush()
+        self.half_norm = None  # the caller is about to change the residual
         return self.residual
+
+    def norm_weight_to_begin(self) -> torch.Tensor | None:
+        """The weight of the norm that follows, if that norm can be split over two products."""
+        norm = self.next_norm
+        return norm.split_weight() if norm is not None and hasattr(norm, "split_weight") else None
 
 
 class Part:
@@ -151,7 +166,8 @@ class Part:
 
 
 class Norm(Part):
-    def forward(self, stream: ResidualStream, status: torch.Tensor) -> torch.Tensor:
+    def forward(self, stream: ResidualStream, status: torch.Tensor, lazy: bool = False):
+        """The normalised activations.  ``lazy``: the consumer also takes an ``ops.gemm.RowScaled``."""
         raise NotImplementedError
 
     def forward_rows(self, stream: ResidualStream, rows: torch.Tensor, status: torch.Tensor) -> torch.Tensor:
@@ -164,6 +180,8 @@ class PositionEncoding(Part):
 
 
 class Mixer(Part):
+    takes_half_normed = False  # True: ``x`` may be an ``ops.gemm.RowScaled`` (it only feeds matrix products)
+
     def cache_need(self) -> PagedKVNeed | SlotStateNeed | None:
         return None
 
@@ -172,6 +190,8 @@ class Mixer(Part):
 
 
 class FeedForward(Part):
+    takes_half_normed = False
+
     def forward(self, ctx: StepContext, x: torch.Tensor, stream: ResidualStream) -> torch.Tensor | None:
         raise NotImplementedError
 
@@ -179,5 +199,11 @@ class FeedForward(Part):
 class Block(Part):
     mixer: Mixer
 
-    def forward(self, ctx: StepContext, stream: ResidualStream, view) -> None:
+    def forward(self, ctx: StepContext, stream: ResidualStream, view, following_norm=None) -> None:
+        """``following_norm``: the norm that reads the residual after this block (the next block's
+        first norm), when the model knows it; a hint for fusion, never needed for correctness."""
         raise NotImplementedError
+
+    def first_norm(self):
+        """The norm this block applies to the incoming residual first, or None."""
+        return None

@@ -38,11 +38,23 @@ class PreNormResidualBlock(Block):
         for part in self.parts():
             part.load_weights(fetch)
 
-    def forward(self, ctx: StepContext, stream: ResidualStream, view) -> None:
-        x = self.mixer_norm.forward(stream, ctx.status)
+    def first_norm(self):
+        return self.mixer_norm
+
+    @staticmethod
+    def _normed(norm, consumer, stream: ResidualStream, status):
+        if getattr(consumer, "takes_half_normed", False) and hasattr(norm, "split_weight"):
+            return norm.forward(stream, status, lazy=True)
+        return norm.forward(stream, status)
+
+    def forward(self, ctx: StepContext, stream: ResidualStream, view, following_norm=None) -> None:
+        x = self._normed(self.mixer_norm, self.mixer, stream, ctx.status)
+        stream.next_norm = self.ffn_norm  # what the mixer's output product may begin
         stream.push(self.mixer.forward(ctx, x, view, stream))
-        x = self.ffn_norm.forward(stream, ctx.status)
+        x = self._normed(self.ffn_norm, self.ffn, stream, ctx.status)
+        stream.next_norm = following_norm
         stream.push(self.ffn.forward(ctx, x, stream))
+        stream.next_norm = None
 
 
 register_block("prenorm_residual", PreNormResidualBlock, replace=True)

@@ -21,9 +21,13 @@ class Linear:
         """x [M, K] -> [M, N] in x's dtype."""
         return gemm_ops.linear(x, self.weight, self.bias)
 
-    def add_into(self, x: torch.Tensor, residual: torch.Tensor) -> None:
-        """residual (float32 [M, N]) += x W^T (+ bias), the sum done in float32."""
-        gemm_ops.linear_add_into(x, self.weight, self.bias, residual)
+    def add_into(self, x: torch.Tensor, residual: torch.Tensor, stream=None) -> None:
+        """residual (float32 [M, N]) += x W^T (+ bias), the sum done in float32.  With the residual
+        stream given, the product also begins the norm that the stream says comes next, when it can."""
+        begin = stream.norm_weight_to_begin() if stream is not None else None
+        half = gemm_ops.linear_add_into(x, self.weight, self.bias, residual, begin_norm=begin)
+        if stream is not None:
+            stream.half_norm = None if half is None else (begin, *half)
 
     def to_float32(self, x: torch.Tensor) -> torch.Tensor:
         """x W^T as float32 (logits)."""

@@ -117,11 +117,19 @@ class DecoderModel:
         """token_ids int32 [N]; logit_rows int32 [R] (rows of the flat batch whose logits are
         wanted).  Returns float32 [R, vocab], or None when no row is wanted."""
         stream = ResidualStream(ops.embed(self.embedding, token_ids, ctx.status))
-        for step in self.spec.schedule:
+        schedule = self.spec.schedule
+        for i, step in enumerate(schedule):
             view = ctx.views.get(step.resolved_cache_layer())
             if view is not None and hasattr(view, "write"):
                 view.write = step.write_cache
-            self.blocks[step.layer].forward(ctx, stream, view)
+            block = self.blocks[step.layer]
+            # the norm that reads the residual next, for blocks that can fuse its first half into their
+            # last product (the final norm reads selected rows only and is left alone)
+            following = self.blocks[schedule[i + 1].layer].first_norm() if i + 1 < len(schedule) else None
+            if following is not None:
+                block.forward(ctx, stream, view, following_norm=following)
+            else:
+                block.forward(ctx, stream, view)
         if logit_rows is None or logit_rows.numel() == 0:
             stream.flush()
             return None

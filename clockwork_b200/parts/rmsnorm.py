@@ -10,6 +10,7 @@ from __future__ import annotations
 import torch
 
 from .. import ops
+from ..ops.gemm import RowScaled
 from ..weights.decl import TensorDecl
 from .base import Norm, ResidualStream
 from .registry import register_norm
@@ -30,7 +31,17 @@ class RMSNorm(Norm):
     def load_weights(self, fetch) -> None:
         self.weight = fetch(self.name("weight"))
 
-    def forward(self, stream: ResidualStream, status: torch.Tensor) -> torch.Tensor:
+    def split_weight(self) -> torch.Tensor | None:
+        """The weight a preceding product multiplies into the residual when it begins this norm."""
+        return self.weight if self.dtype == torch.bfloat16 else None
+
+    def forward(self, stream: ResidualStream, status: torch.Tensor, lazy: bool = False):
+        half, stream.half_norm = stream.half_norm, None
+        if lazy and half is not None and stream.pending is None and half[0] is self.weight:
+            # the product that wrote the residual began this norm; the product that reads it finishes it
+            residual, weight, eps, dtype = stream.residual, self.weight, self.eps, self.dtype
+            return RowScaled(half[1], half[2], eps, self.size,
+                             lambda: ops.add_rmsnorm(residual, None, weight, eps, dtype, status))
         delta, stream.pending = stream.pending, None
         return ops.add_rmsnorm(stream.residual, delta, self.weight, self.eps, self.dtype, status)
 

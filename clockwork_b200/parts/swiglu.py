@@ -17,6 +17,7 @@ from .registry import register_ffn
 
 class SwiGLU(FeedForward):
     graph_safe = True
+    takes_half_normed = True  # x only feeds the gate/up product
 
     def __init__(self, spec, prefix, dtype, device) -> None:
         super().__init__(spec, prefix, dtype, device)
@@ -38,7 +39,7 @@ class SwiGLU(FeedForward):
 
     def forward(self, ctx: StepContext, x, stream: ResidualStream):
         act = gemm_ops.swiglu(x, self.w_gate, self.w_up)
-        self.down.add_into(act, stream.residual_after_flush())
+        self.down.add_into(act, stream.residual_after_flush(), stream)
         return None
 
 

@@ -366,6 +366,38 @@ def test_gemm_tc_swiglu(ops, gemm_tc, t, n, k):
     ops.raise_on_status(gemm_tc.status(DEV))
 
 
+@pytest.mark.parametrize("t,n,k,n2", [(1, 1536, 8960, 2048), (8, 1536, 1536, 8960), (37, 200, 264, 130), (128, 1536, 512, 384),
+                                      (64, 384, 8960, 1000)])
+def test_gemm_tc_splits_a_norm_over_two_products(ops, gemm_tc, t, n, k, n2):
+    """The product that adds into the residual also writes bf16(residual * g) and per-tile sums of
+    squares; the next product, fed with that, finishes the RMSNorm in its epilogue."""
+    eps = 1e-5
+    x, w = rand(t, k, dtype=torch.bfloat16), rand(n, k, dtype=torch.bfloat16, scale=0.1, seed=1)
+    base, g = rand(t, n, seed=3, scale=2.0), (1 + 0.1 * rand(n, seed=4)).float()
+    resid = base.to(DEV).clone()
+    xg = torch.full((t, n), 7.0, dtype=torch.bfloat16, device=DEV)
+    parts = torch.full((t, gemm_tc.norm_tiles(n)), -1.0, device=DEV)
+    gemm_tc.gemm(x.to(DEV), w.to(DEV), None, out=resid, epilogue=ops.EPILOGUE_ADD_F32, emit=(g.to(DEV), xg, parts))
+    want_resid = base + bf16_product(x, w)
+    scale = max(1.0, float(want_resid.abs().max()))
+    torch.testing.assert_close(resid.cpu(), want_resid, rtol=1e-4, atol=1e-5 * scale)
+    got_resid = resid.cpu()
+    assert torch.equal(xg.cpu(), (got_resid * g).bfloat16())  # from the very values that were stored
+    torch.testing.assert_close(parts.sum(1).cpu(), (got_resid.double() ** 2).sum(1).float(), rtol=1e-5, atol=0)
+    # the consumer: plain with bias, and SwiGLU
+    w2, bias2 = rand(n2, n, dtype=torch.bfloat16, scale=0.05, seed=5), rand(n2, seed=6)
+    inv = 1.0 / torch.sqrt((got_resid.double() ** 2).mean(1, keepdim=True) + eps)
+    want = ((xg.cpu().double() @ w2.double().T) * inv).float() + bias2
+    got = gemm_tc.gemm(xg, w2.to(DEV), bias2.to(DEV), epilogue=ops.EPILOGUE_STORE_F32, row_scale=(parts, eps, n))
+    torch.testing.assert_close(got.cpu(), want, rtol=1e-4, atol=1e-5 * max(1.0, float(want.abs().max())))
+    w3 = rand(n2, n, dtype=torch.bfloat16, scale=0.05, seed=7)
+    gate, up = ((xg.cpu().double() @ w2.double().T) * inv).float(), ((xg.cpu().double() @ w3.double().T) * inv).float()
+    want_act = torch.nn.functional.silu(gate) * up
+    got_act = gemm_tc.gemm_swiglu(xg, w2.to(DEV), w3.to(DEV), row_scale=(parts, eps, n))
+    torch.testing.assert_close(got_act.float().cpu(), want_act, rtol=1e-2, atol=1e-2 * max(1.0, float(want_act.abs().max())))
+    ops.raise_on_status(gemm_tc.status(DEV))
+
+
 def test_gemm_tc_rows_do_not_depend_on_the_batch(ops, gemm_tc):
     """The same token gives the same bits alone, in a batch of 8 and in a batch of 64 (the split of
     the inner dimension may differ between those, the order of the float32 sums inside a split does not)."""
