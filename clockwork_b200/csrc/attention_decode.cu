@@ -98,7 +98,7 @@ attn_decode_kernel(const DecodeParams p) {
     const int kv_begin = p.window > 0 ? max(0, ctx - p.window) : 0;
     const int nsplits = (ctx + SPLIT - 1) / SPLIT;
     const int first_split = kv_begin / SPLIT;
-    if (sp < first_split || sp >= nsplits) return;
+    if (sp < first_split || sp >= nsplits) return;  // (no end record: these CTAs do nothing)
     const int t0 = sp * SPLIT, t1 = min(ctx, t0 + SPLIT);
     const int* table = p.block_tables + (size_t)s * p.max_blocks;
     const float scale_log2 = p.scale * 1.4426950408889634f;  // softmax in base 2: exp(x) = 2^(x log2 e)
@@ -362,7 +362,10 @@ attn_decode_kernel(const DecodeParams p) {
             if (d == 0) p.part_lse[((size_t)s * p.nh + h) * p.max_splits + sp] = w_s[r][NWARPS];
         }
     }
-    if (active == 1) return;
+    if (active == 1) {
+        cw_trace_end();
+        return;
+    }
     // ---- the CTA that finishes last merges the splits, in split order ------------------------------
     __threadfence();
     __syncthreads();
@@ -373,7 +376,10 @@ attn_decode_kernel(const DecodeParams p) {
         if (last_flag) *counter = 0;
     }
     __syncthreads();
-    if (!last_flag) return;
+    if (!last_flag) {
+        cw_trace_end();
+        return;
+    }
     __threadfence();
     // weights of the splits per query row, once: w = 2^(lse_k - max) / sum
     const int nact = min(active, 16);
@@ -426,6 +432,7 @@ attn_decode_kernel(const DecodeParams p) {
                 if (i < rows * HD) p.out[((size_t)s * p.nh + h0 + i / HD) * HD + i % HD] = __float2bfloat16_rn(acc[u]);
             }
         }
+        cw_trace_end();
         return;
     }
     // more than 16 live splits (very long contexts): the plain form
@@ -445,6 +452,7 @@ attn_decode_kernel(const DecodeParams p) {
             }
         p.out[((size_t)s * p.nh + h) * HD + d] = __float2bfloat16_rn(W > 0.f ? O / W : 0.f);
     }
+    cw_trace_end();
 }
 
 template <int HD, int ST>
@@ -618,3 +626,5 @@ extern "C" int cw_attention_decode_noalloc(const void* q, int q_stride, void* ou
                                (float*)(base + counters_bytes + lse_bytes), (float*)(base + counters_bytes),
                                (int*)base, status, stream);
 }
+
+CW_TRACE_TU(attention_decode)

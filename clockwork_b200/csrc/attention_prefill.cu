@@ -280,3 +280,5 @@ extern "C" int cw_attention_prefill(const void* q, int q_stride, void* out, cons
     }
     return CW_ERR_UNSUPPORTED;
 }
+
+CW_TRACE_TU(attention_prefill)

@@ -123,8 +123,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     volatile int* give_up = (volatile int*)(tmem_slot + 1);
     float* xchg = (float*)(bars + 32);  // [2][2][128]: row maxima and, at the end, row sums (tile parity x half)
 
-    pdl_launch_dependents();
-    pdl_wait();
+    // (the plain instructions, not the helpers: the helpers' timeline notes take static shared memory,
+    // which would push the 1024-byte aligned dynamic part over the limit)
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int h = blockIdx.x, item = blockIdx.y;
     const int s = p.item_seq[item], q0 = p.item_q0[item];
@@ -468,3 +470,5 @@ extern "C" int cw_attention_prefill_tc(const void* q, int q_stride, int q_cols, 
     p.scale = scale; p.window = window; p.status = status;
     return hd == 64 ? launch_prefill_tc<64>(mq, mk, mv, p, items, stream) : launch_prefill_tc<128>(mq, mk, mv, p, items, stream);
 }
+
+CW_TRACE_TU(attention_prefill_tc)

@@ -112,3 +112,5 @@ extern "C" int cw_attention_ref(const void* q, int q_stride, void* out, const vo
         return CW_ERR_BAD_DTYPE;
     return CW_LAUNCH_CHECK();
 }
+
+CW_TRACE_TU(attention_ref)

@@ -97,8 +97,65 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
 // before it writes global memory at all; what it does before that (set-up, prefetching weights,
 // which no kernel of the step writes) overlaps the predecessor's tail.  pdl_launch_dependents()
 // at the top lets the successor do the same.  Both are no-ops in a kernel launched the plain way.
-__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
-__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+//
+// Step timeline: when a trace buffer is set (cw_trace_set_* in every translation unit, normally null),
+// thread 0 of every CTA notes the global timer at its start (in pdl_launch_dependents) and when a
+// wait on the preceding kernel returns (in pdl_wait: the first time and the last time), and the
+// kernels that call cw_trace_end() append one record when the CTA is done:
+// {start, first release, last release, end, gridDim, blockIdx}.  The notes are kept in shared memory
+// and the one atomic comes last, so that the timeline is not disturbed.  buf[0] counts records,
+// buf[1] is the capacity, records of 8 words start at buf[8].
+static __constant__ unsigned long long* cw_trace_ptr;
+__device__ __forceinline__ unsigned long long* cw_trace_notes() {
+    __shared__ unsigned long long notes[3];
+    return notes;
+}
+__device__ __forceinline__ unsigned long long cw_globaltimer() {
+    unsigned long long now;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+    return now;
+}
+__device__ __forceinline__ void cw_trace(unsigned phase) {
+    if (cw_trace_ptr == nullptr || threadIdx.x != 0) return;
+    unsigned long long* notes = cw_trace_notes();
+    const unsigned long long now = cw_globaltimer();
+    if (phase == 0) {
+        notes[0] = now;
+        notes[1] = notes[2] = 0;
+    } else {
+        if (notes[1] == 0) notes[1] = now;
+        notes[2] = now;
+    }
+}
+__device__ __forceinline__ void cw_trace_end() {
+    unsigned long long* buf = cw_trace_ptr;
+    if (buf == nullptr || threadIdx.x != 0) return;
+    const unsigned long long* notes = cw_trace_notes();
+    const unsigned long long now = cw_globaltimer();
+    const unsigned long long i = atomicAdd(buf, 1ULL);
+    if (i >= buf[1]) return;
+    unsigned long long* rec = buf + 8 + 8 * i;
+    rec[0] = notes[0];
+    rec[1] = notes[1];
+    rec[2] = notes[2];
+    rec[3] = now;
+    rec[4] = (unsigned long long)gridDim.x | ((unsigned long long)gridDim.y << 20) | ((unsigned long long)gridDim.z << 40);
+    rec[5] = (unsigned long long)blockIdx.x | ((unsigned long long)blockIdx.y << 20) | ((unsigned long long)blockIdx.z << 40);
+}
+static inline int cw_trace_set_tu(void* buf) {
+    return (int)cudaMemcpyToSymbol(cw_trace_ptr, &buf, sizeof(buf));
+}
+#define CW_TRACE_TU(name) \
+    extern "C" int cw_trace_set_##name(void* buf) { return cw_trace_set_tu(buf); }
+
+__device__ __forceinline__ void pdl_wait() {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    cw_trace(1);
+}
+__device__ __forceinline__ void pdl_launch_dependents() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    cw_trace(0);
+}
 
 // 1: launch with the attribute (default); 0: plain launches.  Set through cw_set_pdl().
 extern "C" int cw_pdl_enabled();

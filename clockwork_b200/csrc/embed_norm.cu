@@ -232,3 +232,5 @@ extern "C" int cw_add_to_residual(float* resid, const void* delta, int N, int H,
 static int g_pdl = 1;
 extern "C" int cw_pdl_enabled() { return g_pdl; }
 extern "C" int cw_set_pdl(int on) { g_pdl = on ? 1 : 0; return CW_OK; }
+
+CW_TRACE_TU(embed_norm)

@@ -126,3 +126,5 @@ extern "C" int cw_gemm_ref_swiglu(const void* A, const void* Wgate, const void* 
         return CW_ERR_BAD_DTYPE;
     return CW_LAUNCH_CHECK();
 }
+
+CW_TRACE_TU(gemm_ref)

@@ -350,6 +350,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     tc_fence_before();
     __syncthreads();
     if (warp == 2) tmem_dealloc(tmem_base, C::TMEM_COLS);
+    cw_trace_end();
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -793,3 +794,5 @@ extern "C" int cw_gemm_tc_norm(const void* X, const void* W, const void* W2, con
 #undef CW_CASE
     return CW_ERR_UNSUPPORTED;
 }
+
+CW_TRACE_TU(gemm_tc)

@@ -220,3 +220,5 @@ extern "C" int cw_copy_pages(void* cache, const int* pairs, int num_pairs, int p
                                                 page_vec * (size_t)num_pages, num_pages, status);
     return CW_LAUNCH_CHECK();
 }
+
+CW_TRACE_TU(rope_cache)

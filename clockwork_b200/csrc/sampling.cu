@@ -193,3 +193,5 @@ extern "C" int cw_sample(const float* logits, const float* temperature, const in
     return cw_launch(sample_kernel, dim3(R), dim3(ST), 0, stream, 1, logits, temperature, top_k, top_p, uniform, out, V,
                      (size_t)row_stride);
 }
+
+CW_TRACE_TU(sampling)
