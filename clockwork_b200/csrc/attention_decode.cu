@@ -144,7 +144,7 @@ attn_decode_kernel(const DecodeParams p) {
         const int pos0 = t0 + tile_idx * TILE;
         if (EVEN) {
             const int c = tid % CH, r0 = tid / CH;
-#pragma unroll
+#pragma unroll 2
             for (int k = 0; k < (TILE + RPP - 1) / RPP; ++k) {
                 const int r = r0 + k * RPP;
                 if (r < TILE) copy_chunk(kd, vd, r, c, slot_of(pos0 + r));
@@ -156,6 +156,7 @@ attn_decode_kernel(const DecodeParams p) {
     };
 
     const int ntiles = (t1 - t0 + TILE - 1) / TILE;
+#pragma unroll 1
     for (int i = 0; i < ST && i < ntiles; ++i) load_tile(i);
     // cos/sin of the new token's position (an input of the step), for the fused rotation
     const int half = p.rotary_dim >> 1;

@@ -150,6 +150,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         }
     } else if (warp == 1 && lane == 0) {
         // ---- MMA issuer ------------------------------------------------------------------------
+        pdl_wait();  // blocked here a thread costs nothing; polling a barrier takes issue slots
         constexpr uint32_t idesc = instr_desc(BM, BN);
         bool ok = true;
         for (int i = 0; i < my_kb && ok; ++i) {
@@ -174,26 +175,56 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     }
     __syncwarp();
     // ---- epilogue: every thread owns one output feature (TMEM lane) -----------------------------
-    const bool acc_ready = __syncthreads_and(mbar_wait(acc_bar, 0, give_up) ? 1 : 0) != 0;  // one answer for the CTA
-    pdl_wait();  // the epilogue reads and writes what preceding kernels wrote
+    // First the wait on the preceding kernel (the epilogue reads and writes what it wrote), then every
+    // load that does not depend on the accumulator: they are in flight while the main loop runs, so
+    // that after the accumulator is ready nothing waits on global memory again.
+    pdl_wait();
+    const int row = warp * 32 + lane;  // feature within the tile
+    const int f = m0 + row;
     constexpr bool NORM_OK = BN <= 128;  // the shared arrays below hold 128 tokens
     float* inv_s = (float*)((uint8_t*)bars + 256);  // [128] the tokens' 1/rms, when a norm is finished here
     float* red_s = inv_s + 128;                     // [4][16] per-warp sums of squares, when one is begun here
     const bool scaled = NORM_OK && p.scale_part != nullptr;
-    if (scaled) {
-        if (tid < BN) {
-            const int t = n0 + tid;
-            float ssq = 0.f;
-            if (t < p.T)
-                for (int i = 0; i < p.scale_parts; ++i) ssq += p.scale_part[(size_t)t * p.scale_parts + i];
-            inv_s[tid] = 1.0f / sqrtf(ssq / (float)p.scale_dim + p.scale_eps);
-        }
-        __syncthreads();
+    const bool emit = !SWIGLU && NORM_OK && p.emit_x != nullptr && p.epilogue == 1;  // the same in the whole CTA
+    const float bias = (p.bias != nullptr && f < p.N) ? p.bias[f] : 0.f;
+    const float emit_gf = (emit && f < p.N) ? p.emit_g[f] : 0.f;
+    // the slice of the tile's columns that this CTA finishes (all of them when the tile is not split)
+    const int per = (BN + p.splits - 1) / p.splits;        // columns per owner
+    const int slots = per * (SWIGLU ? 2 : 1);              // inbox column slots per sender
+    const uint32_t my_rank = p.splits > 1 ? cluster_rank() : 0;
+    int c_begin = p.splits > 1 ? min(BN, (int)my_rank * per) : 0;
+    int c_end = p.splits > 1 ? min(BN, c_begin + per) : BN;
+    // the residual's old values of the slice's first 16 columns (the whole slice, for decode sizes)
+    float old0[16];
+    const bool rmw = !SWIGLU && p.epilogue == 1 && !p.tma_store;
+    if (rmw) {
+        const float* c32 = (const float*)p.C + (size_t)(n0 + c_begin) * p.ldc + f;
+#pragma unroll
+        for (int j = 0; j < 16; ++j)
+            old0[j] = (f < p.N && c_begin + j < c_end && n0 + c_begin + j < p.T) ? c32[(size_t)j * p.ldc] : 0.f;
     }
+    if (scaled && warp >= 2) {
+        for (int i = tid - 64; i < BN; i += 64) {
+            const int t = n0 + i;
+            float ssq = 0.f;
+            if (t < p.T) {
+                // sixteen loads in flight at a time (a loop of one load and one add each would pay the
+                // L2's latency once per term), summed in index order
+                const float* part = p.scale_part + (size_t)t * p.scale_parts;
+                for (int i0 = 0; i0 < p.scale_parts; i0 += 16) {
+                    float v[16];
+#pragma unroll
+                    for (int k = 0; k < 16; ++k) v[k] = i0 + k < p.scale_parts ? part[i0 + k] : 0.f;
+#pragma unroll
+                    for (int k = 0; k < 16; ++k) ssq += v[k];
+                }
+            }
+            inv_s[i] = 1.0f / sqrtf(ssq / (float)p.scale_dim + p.scale_eps);
+        }
+    }
+    const bool acc_ready = __syncthreads_and(mbar_wait(acc_bar, 0, give_up) ? 1 : 0) != 0;  // one answer for the CTA; inv_s visible
     tc_fence_after();
     __syncwarp();
-    const int row = warp * 32 + lane;  // feature within the tile
-    const int f = m0 + row;
     const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16);
     // With the inner dimension split, the CTAs of one tile form a cluster and each finishes a slice of
     // the tile's columns.  A CTA pushes every column of its partial accumulator into the inbox of the
@@ -203,11 +234,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     float* stage = (float*)smem;  // unsplit tiles: [token][feature] staging for the TMA store
     const uint32_t stage_addr = smem_u32(stage);
     float* inbox = (float*)(smem + C::STAGES * C::STAGE_BYTES + 1024);  // [rank][column slot][BM]
-    int c_begin = 0, c_end = BN;
-    const int per = (BN + p.splits - 1) / p.splits;        // columns per owner
-    const int slots = per * (SWIGLU ? 2 : 1);              // inbox column slots per sender
     if (p.splits > 1) {
-        const uint32_t my_rank = cluster_rank();
         const uint32_t inbox_addr = smem_u32(inbox);
         for (int c = 0; c < BN; c += 16) {
             float v[16], v2[16];
@@ -227,10 +254,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             }
         }
         cluster_sync();
-        c_begin = min(BN, (int)my_rank * per);
-        c_end = min(BN, c_begin + per);
     }
-    const float bias = (p.bias != nullptr && f < p.N) ? p.bias[f] : 0.f;
     if (p.splits == 1 && p.tma_store && acc_ready) {
         // The whole tile goes to shared memory as [token][feature] in C's type, then leaves in one
         // TMA store (or float32 reduce-add into the residual): full-line writes, no read-modify-write
@@ -256,8 +280,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         if (tid == 0) tma_store_2d(&map_c, stage_addr, m0, n0, !SWIGLU && p.epilogue == 1);
         c_begin = c_end = 0;  // nothing left for the direct path
     }
-    const bool emit = !SWIGLU && NORM_OK && p.emit_x != nullptr && p.epilogue == 1;  // the same in the whole CTA
-    const float emit_gf = (emit && f < p.N) ? p.emit_g[f] : 0.f;
+    const int c_first = c_begin;
     for (int c = c_begin; c < c_end && (acc_ready || p.splits > 1); c += 16) {
         const int ncols = min(16, c_end - c);
         float g[16], u[16];
@@ -287,10 +310,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             bf16* c16 = (bf16*)p.C + (size_t)t_base * p.ldc + f;
             float old[16];
             if (!SWIGLU && p.epilogue == 1) {
-                // all loads first: issued back to back instead of one load-add-store chain each
+                if (c == c_first) {  // fetched before the accumulator was ready
 #pragma unroll
-                for (int j = 0; j < 16; ++j)
-                    old[j] = (j < ncols && t_base + j < p.T) ? c32[(size_t)j * p.ldc] : 0.f;
+                    for (int j = 0; j < 16; ++j) old[j] = old0[j];
+                } else {
+                    // all loads first: issued back to back instead of one load-add-store chain each
+#pragma unroll
+                    for (int j = 0; j < 16; ++j)
+                        old[j] = (j < ncols && t_base + j < p.T) ? c32[(size_t)j * p.ldc] : 0.f;
+                }
             }
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
