@@ -59,6 +59,10 @@ __device__ __forceinline__ bool mine_newest(int newest, int t0, int t1, int kv_b
 
 // ST: tiles in flight.  4 puts a whole split (256 tokens) in flight at once, for steps with few
 // CTAs where latency is everything; 2 halves the shared memory so that two CTAs share an SM.
+// Position -> (block, offset) for page sizes that are no power of two: out of line, so that the
+// division's instruction sequence exists once in the kernel instead of at every use.
+__device__ __noinline__ int2 block_and_offset(int pos, int page_size) { return make_int2(pos / page_size, pos % page_size); }
+
 template <int HD, int ST>
 __global__ void __launch_bounds__(NWARPS * 32)
 attn_decode_kernel(const DecodeParams p) {
@@ -123,10 +127,18 @@ attn_decode_kernel(const DecodeParams p) {
     const int newest = ctx - 1;  // its k/v are written by this step: they arrive after pdl_wait()
     auto slot_of = [&](int pos) -> int {
         if (pos >= t1 || pos < kv_begin || pos == newest) return -1;
-        const int blk = p.page_shift >= 0 ? pos >> p.page_shift : pos / p.page_size;
+        int blk, off;
+        if (p.page_shift >= 0) {
+            blk = pos >> p.page_shift;
+            off = pos & (p.page_size - 1);
+        } else {
+            const int2 bo = block_and_offset(pos, p.page_size);
+            blk = bo.x;
+            off = bo.y;
+        }
         const int page = blk - blk0 < p.max_split_pages ? page_s[blk - blk0] : -1;
         if (page < 0) return -1;
-        return page * p.page_size + (p.page_shift >= 0 ? pos & (p.page_size - 1) : pos % p.page_size);
+        return page * p.page_size + off;
     };
     auto copy_chunk = [&](bf16* kd, bf16* vd, int r, int c, int slot) {
         if (slot >= 0) {
@@ -163,8 +175,7 @@ attn_decode_kernel(const DecodeParams p) {
     if (p.kv_new != nullptr && p.inv_freq != nullptr)
         for (int j = tid; j < half; j += blockDim.x) {
             const float ang = (float)newest * p.inv_freq[j];
-            cs_s[j] = cosf(ang);
-            cs_s[half + j] = sinf(ang);
+            sincosf(ang, &cs_s[half + j], &cs_s[j]);  // one argument reduction for both
         }
 
     pdl_wait();
@@ -382,76 +393,46 @@ attn_decode_kernel(const DecodeParams p) {
         return;
     }
     __threadfence();
-    // weights of the splits per query row, once: w = 2^(lse_k - max) / sum
-    const int nact = min(active, 16);
-    for (int i = tid; i < 16 * 16; i += blockDim.x) {
-        const int r = i >> 4, k = i & 15;
-        float w = 0.f;
-        if (r < rows && k < nact) {
-            const float* lse = p.part_lse + ((size_t)s * p.nh + h0 + r) * p.max_splits + first_split;
-            float l16[16];
-#pragma unroll
-            for (int j = 0; j < 16; ++j) l16[j] = j < nact ? __ldcg(lse + j) : -INFINITY;
-            float m = -INFINITY;
-#pragma unroll
-            for (int j = 0; j < 16; ++j) m = fmaxf(m, l16[j]);
-            float W = 0.f;
-#pragma unroll
-            for (int j = 0; j < 16; ++j) W += (l16[j] == -INFINITY) ? 0.f : exp2f(l16[j] - m);  // split order
-            w = (m == -INFINITY || l16[k] == -INFINITY) ? 0.f : exp2f(l16[k] - m) / W;
-        }
-        w_s[r][k] = w;
+    // One compact form for any number of splits (this code runs once per group of CTAs: its size
+    // matters as much as its instruction count).  The log-sum-exps of every (row, split) come into
+    // shared memory in one trip; one thread per row turns them into weights w_k = 2^(lse_k - max) /
+    // sum, splits in order; then every thread merges groups of four outputs, four splits' partials in
+    // flight at a time.
+    float* w_all = (float*)Ks;  // [rows][active], over the K buffers (all reads of them are done)
+    for (int i = tid; i < rows * active; i += blockDim.x) {
+        const int r = i / active, k = i - r * active;
+        w_all[i] = __ldcg(p.part_lse + ((size_t)s * p.nh + h0 + r) * p.max_splits + first_split + k);
     }
     __syncthreads();
-    if (active <= 16) {
-        // four outputs at a time, all their splits' partials in flight together
-        for (int i0 = tid; i0 < rows * HD; i0 += 4 * blockDim.x) {
-            float acc[4] = {0.f, 0.f, 0.f, 0.f};
-            for (int k0 = 0; k0 < nact; k0 += 4) {
-                float v[4][4];
-#pragma unroll
-                for (int u = 0; u < 4; ++u) {
-                    const int i = i0 + u * blockDim.x;
-                    const int r = i / HD, d = i % HD;
-                    const float* po = p.part_o + (((size_t)s * p.nh + h0 + r) * p.max_splits + first_split) * HD + d;
-#pragma unroll
-                    for (int k = 0; k < 4; ++k)
-                        v[u][k] = (i < rows * HD && k0 + k < nact) ? __ldcg(po + (size_t)(k0 + k) * HD) : 0.f;
-                }
-#pragma unroll
-                for (int u = 0; u < 4; ++u) {
-                    const int i = i0 + u * blockDim.x;
-                    const int r = min(i / HD, 15);
-#pragma unroll
-                    for (int k = 0; k < 4; ++k)  // split order
-                        if (k0 + k < nact) acc[u] = fmaf(w_s[r][k0 + k], v[u][k], acc[u]);
-                }
-            }
-#pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                const int i = i0 + u * blockDim.x;
-                if (i < rows * HD) p.out[((size_t)s * p.nh + h0 + i / HD) * HD + i % HD] = __float2bfloat16_rn(acc[u]);
-            }
-        }
-        cw_trace_end();
-        return;
-    }
-    // more than 16 live splits (very long contexts): the plain form
-    for (int i = tid; i < rows * HD; i += blockDim.x) {
-        const int r = i / HD, d = i % HD, h = h0 + r;
-        const float* lse = p.part_lse + ((size_t)s * p.nh + h) * p.max_splits;
-        const float* po = p.part_o + ((size_t)s * p.nh + h) * p.max_splits * HD + d;
+    if (tid < rows) {
+        float* l = w_all + tid * active;
         float m = -INFINITY;
-        for (int k = first_split; k < nsplits; ++k) m = fmaxf(m, __ldcg(lse + k));
-        float W = 0.f, O = 0.f;
-        if (m != -INFINITY)
-            for (int k = first_split; k < nsplits; ++k) {
-                const float l = __ldcg(lse + k);
-                const float e = (l == -INFINITY) ? 0.f : exp2f(l - m);
-                W += e;
-                O += e * __ldcg(po + (size_t)k * HD);
-            }
-        p.out[((size_t)s * p.nh + h) * HD + d] = __float2bfloat16_rn(W > 0.f ? O / W : 0.f);
+#pragma unroll 1
+        for (int k = 0; k < active; ++k) m = fmaxf(m, l[k]);
+        float W = 0.f;
+#pragma unroll 1
+        for (int k = 0; k < active; ++k) W += (l[k] == -INFINITY) ? 0.f : exp2f(l[k] - m);
+#pragma unroll 1
+        for (int k = 0; k < active; ++k) l[k] = (m == -INFINITY || l[k] == -INFINITY) ? 0.f : exp2f(l[k] - m) / W;
+    }
+    __syncthreads();
+    constexpr int Q4 = HD / 4;
+    for (int item = tid; item < rows * Q4; item += blockDim.x) {
+        const int r = item / Q4, d = (item % Q4) * 4;
+        const float4* po = reinterpret_cast<const float4*>(
+            p.part_o + (((size_t)s * p.nh + h0 + r) * p.max_splits + first_split) * HD + d);
+        const float* w = w_all + r * active;
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 4
+        for (int k = 0; k < active; ++k) {
+            const float4 v = __ldcg(po + (size_t)k * Q4);
+            acc.x = fmaf(w[k], v.x, acc.x); acc.y = fmaf(w[k], v.y, acc.y);
+            acc.z = fmaf(w[k], v.z, acc.z); acc.w = fmaf(w[k], v.w, acc.w);
+        }
+        uint2 o;
+        o.x = pack_bf16(acc.x, acc.y);
+        o.y = pack_bf16(acc.z, acc.w);
+        *reinterpret_cast<uint2*>(p.out + ((size_t)s * p.nh + h0 + r) * HD + d) = o;
     }
     cw_trace_end();
 }
@@ -462,6 +443,8 @@ static int launch_decode_st(const DecodeParams& p, int S, int splits, cudaStream
     const int SMEM = (16 * LD + 2 * ST * TILE * LD) * 2 + p.max_split_pages * 4;
     constexpr int MERGE = NWARPS * 16 * HD * 4;
     static_assert(MERGE <= ST * TILE * LD * 2, "the merge buffer must fit over the K buffers");
+    // the cross-split merge keeps one weight per (row, split) over the K buffers
+    if ((long long)16 * splits * 4 > (long long)ST * TILE * LD * 2) return CW_ERR_UNSUPPORTED;
     static int configured = 0;
     if (SMEM > configured) {
         if (SMEM > 48 * 1024 &&
