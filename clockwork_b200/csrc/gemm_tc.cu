@@ -23,6 +23,7 @@
 // the status words, the producer waits (bounded again) for the copies it has in flight, TMEM is
 // freed and the kernel returns.
 #include "tc_common.cuh"
+#include <type_traits>
 
 #define BM 128
 #define BK 64
@@ -194,14 +195,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     const uint32_t my_rank = p.splits > 1 ? cluster_rank() : 0;
     int c_begin = p.splits > 1 ? min(BN, (int)my_rank * per) : 0;
     int c_end = p.splits > 1 ? min(BN, c_begin + per) : BN;
-    // the residual's old values of the slice's first 16 columns (the whole slice, for decode sizes)
-    float old0[16];
-    const bool rmw = !SWIGLU && p.epilogue == 1 && !p.tma_store;
-    if (rmw) {
+    // A slice of at most four columns (decode: few tokens, the inner dimension split over many CTAs)
+    // is finished by a four-column form of the code below, and the residual's old values for it are
+    // fetched here.  The instruction footprint matters as much as the instruction count: each CTA
+    // runs its epilogue once, straight from the instruction cache's misses.
+    const bool small_slice = p.splits > 1 && c_end - c_begin <= 4;
+    float old0[4] = {0.f, 0.f, 0.f, 0.f};
+    if (small_slice && !SWIGLU && p.epilogue == 1 && f < p.N) {
         const float* c32 = (const float*)p.C + (size_t)(n0 + c_begin) * p.ldc + f;
 #pragma unroll
-        for (int j = 0; j < 16; ++j)
-            old0[j] = (f < p.N && c_begin + j < c_end && n0 + c_begin + j < p.T) ? c32[(size_t)j * p.ldc] : 0.f;
+        for (int j = 0; j < 4; ++j)
+            if (c_begin + j < c_end && n0 + c_begin + j < p.T) old0[j] = c32[(size_t)j * p.ldc];
     }
     if (scaled && warp >= 2) {
         for (int i = tid - 64; i < BN; i += 64) {
@@ -236,6 +240,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     float* inbox = (float*)(smem + C::STAGES * C::STAGE_BYTES + 1024);  // [rank][column slot][BM]
     if (p.splits > 1) {
         const uint32_t inbox_addr = smem_u32(inbox);
+        int owner = 0, local = 0;
         for (int c = 0; c < BN; c += 16) {
             float v[16], v2[16];
             if (acc_ready) {
@@ -247,10 +252,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             }
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
-                const int col = c + j, owner = col / per, local = col - owner * per;
+                // column c + j belongs to `owner`, as its column `local` (counted up: no division here)
                 const uint32_t a = dsmem_addr(inbox_addr + (uint32_t)(((my_rank * slots + local) * BM + row) * 4), owner);
                 st_dsmem(a, v[j]);
                 if (SWIGLU) st_dsmem(a + (uint32_t)(per * BM * 4), v2[j]);
+                if (++local == per) {
+                    local = 0;
+                    ++owner;
+                }
             }
         }
         cluster_sync();
@@ -280,88 +289,106 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         if (tid == 0) tma_store_2d(&map_c, stage_addr, m0, n0, !SWIGLU && p.epilogue == 1);
         c_begin = c_end = 0;  // nothing left for the direct path
     }
-    const int c_first = c_begin;
-    for (int c = c_begin; c < c_end && (acc_ready || p.splits > 1); c += 16) {
-        const int ncols = min(16, c_end - c);
-        float g[16], u[16];
-        if (p.splits == 1) {
-            tmem_ld16(taddr + c, g);
-            if (SWIGLU) tmem_ld16(taddr + BN + c, u);
-        } else {
+    auto finish = [&](auto width) {
+        constexpr int NC = decltype(width)::value;  // columns per pass: 4 (small slices) or 16
+        for (int c = c_begin; c < c_end && (acc_ready || p.splits > 1); c += NC) {
+            const int ncols = min(NC, c_end - c);
+            float g[NC], u[NC];
+            if (NC == 16 && p.splits == 1) {
+                float g16[16], u16[16];
+                tmem_ld16(taddr + c, g16);
+                if (SWIGLU) tmem_ld16(taddr + BN + c, u16);
 #pragma unroll
-            for (int j = 0; j < 16; ++j) g[j] = u[j] = 0.f;
-            for (int s = 0; s < p.splits; ++s) {  // rank order; all reads are of this CTA's own inbox
-                const float* part = inbox + ((size_t)s * slots + (c - c_begin)) * BM + row;
+                for (int j = 0; j < NC; ++j) {
+                    g[j] = g16[j & 15];
+                    u[j] = SWIGLU ? u16[j & 15] : 0.f;
+                }
+            } else {
 #pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                    if (j < ncols) {
-                        g[j] += part[j * BM];
-                        if (SWIGLU) u[j] += part[(per + j) * BM];
+                for (int j = 0; j < NC; ++j) g[j] = u[j] = 0.f;
+                for (int s = 0; s < p.splits; ++s) {  // rank order; all reads are of this CTA's own inbox
+                    const float* part = inbox + ((size_t)s * slots + (c - c_begin)) * BM + row;
+#pragma unroll
+                    for (int j = 0; j < NC; ++j) {
+                        if (j < ncols) {
+                            g[j] += part[j * BM];
+                            if (SWIGLU) u[j] += part[(per + j) * BM];
+                        }
                     }
                 }
             }
-        }
-        const int t_base = n0 + c;
-        float sq[16];
+            const int t_base = n0 + c;
+            float sq[NC];
 #pragma unroll
-        for (int j = 0; j < 16; ++j) sq[j] = 0.f;
-        if (f < p.N) {
-            float* c32 = (float*)p.C + (size_t)t_base * p.ldc + f;
-            bf16* c16 = (bf16*)p.C + (size_t)t_base * p.ldc + f;
-            float old[16];
-            if (!SWIGLU && p.epilogue == 1) {
-                if (c == c_first) {  // fetched before the accumulator was ready
-#pragma unroll
-                    for (int j = 0; j < 16; ++j) old[j] = old0[j];
-                } else {
-                    // all loads first: issued back to back instead of one load-add-store chain each
-#pragma unroll
-                    for (int j = 0; j < 16; ++j)
-                        old[j] = (j < ncols && t_base + j < p.T) ? c32[(size_t)j * p.ldc] : 0.f;
-                }
-            }
-#pragma unroll
-            for (int j = 0; j < 16; ++j) {
-                // no early exit from this loop: the 16 columns are independent and the compiler
-                // interleaves their arithmetic only when the loop is straight-line
-                const bool live = j < ncols && t_base + j < p.T;
+            for (int j = 0; j < NC; ++j) {
+                sq[j] = 0.f;
                 const float sc = scaled ? inv_s[(c + j) & (BN - 1)] : 1.0f;
-                const float v = g[j] * sc + bias;
+                g[j] = g[j] * sc + bias;
+                if (SWIGLU) u[j] *= sc;
+            }
+            // one loop per kind of epilogue (not one loop with the kinds inside): only the one that runs
+            // is fetched.  The columns are independent and the loops straight-line, so that the
+            // compiler interleaves their arithmetic.
+            if (f < p.N) {
+                float* c32 = (float*)p.C + (size_t)t_base * p.ldc + f;
+                bf16* c16 = (bf16*)p.C + (size_t)t_base * p.ldc + f;
                 if (SWIGLU) {
                     // silu(v) * u with the fast exponential and division: the result is rounded to
                     // bfloat16 (8 bits) right after, their 2^-21 relative error does not show
-                    const float act = __fdividef(v, 1.0f + __expf(-v)) * (u[j] * sc);
-                    if (live) c16[(size_t)j * p.ldc] = __float2bfloat16_rn(act);
+#pragma unroll
+                    for (int j = 0; j < NC; ++j)
+                        if (j < ncols && t_base + j < p.T)
+                            c16[(size_t)j * p.ldc] = __float2bfloat16_rn(__fdividef(g[j], 1.0f + __expf(-g[j])) * u[j]);
                 } else if (p.epilogue == 0) {
-                    if (live) c16[(size_t)j * p.ldc] = __float2bfloat16_rn(v);
+#pragma unroll
+                    for (int j = 0; j < NC; ++j)
+                        if (j < ncols && t_base + j < p.T) c16[(size_t)j * p.ldc] = __float2bfloat16_rn(g[j]);
                 } else if (p.epilogue == 1) {
-                    const float nv = old[j] + v;
-                    if (live) {
-                        c32[(size_t)j * p.ldc] = nv;
-                        if (emit) {
-                            p.emit_x[(size_t)(t_base + j) * p.N + f] = __float2bfloat16_rn(nv * emit_gf);
-                            sq[j] = nv * nv;
+                    float old[NC];
+                    // all loads first: issued back to back instead of one load-add-store chain each
+#pragma unroll
+                    for (int j = 0; j < NC; ++j) {
+                        if (NC == 4)
+                            old[j] = old0[j & 3];  // fetched before the accumulator was ready
+                        else
+                            old[j] = (j < ncols && t_base + j < p.T) ? c32[(size_t)j * p.ldc] : 0.f;
+                    }
+#pragma unroll
+                    for (int j = 0; j < NC; ++j) {
+                        const float nv = old[j] + g[j];
+                        if (j < ncols && t_base + j < p.T) {
+                            c32[(size_t)j * p.ldc] = nv;
+                            if (emit) {
+                                p.emit_x[(size_t)(t_base + j) * p.N + f] = __float2bfloat16_rn(nv * emit_gf);
+                                sq[j] = nv * nv;
+                            }
                         }
                     }
                 } else {
-                    if (live) c32[(size_t)j * p.ldc] = v;
+#pragma unroll
+                    for (int j = 0; j < NC; ++j)
+                        if (j < ncols && t_base + j < p.T) c32[(size_t)j * p.ldc] = g[j];
                 }
             }
-        }
-        if (emit) {
-            // the tile's share of each token's sum of squares: over the warp, then over the four warps
+            if (emit) {
+                // the tile's share of each token's sum of squares: over the warp, then over the four warps
 #pragma unroll
-            for (int j = 0; j < 16; ++j) {
-                const float w = warp_sum(sq[j]);
-                if (lane == 0) red_s[warp * 16 + j] = w;
+                for (int j = 0; j < NC; ++j) {
+                    const float w = warp_sum(sq[j]);
+                    if (lane == 0) red_s[warp * 16 + j] = w;
+                }
+                __syncthreads();
+                if (tid < ncols && t_base + tid < p.T)
+                    p.emit_part[(size_t)(t_base + tid) * gridDim.x + blockIdx.x] =
+                        (red_s[tid] + red_s[16 + tid]) + (red_s[32 + tid] + red_s[48 + tid]);
+                __syncthreads();
             }
-            __syncthreads();
-            if (tid < ncols && t_base + tid < p.T)
-                p.emit_part[(size_t)(t_base + tid) * gridDim.x + blockIdx.x] =
-                    (red_s[tid] + red_s[16 + tid]) + (red_s[32 + tid] + red_s[48 + tid]);
-            __syncthreads();
         }
-    }
+    };
+    if (small_slice)
+        finish(std::integral_constant<int, 4>{});
+    else
+        finish(std::integral_constant<int, 16>{});
     // ---- teardown ---------------------------------------------------------------------------------
     if (*give_up) {
         if (tid == 0) cw_report(p.status, CW_ST_WAIT_TIMEOUT, blockIdx.x, blockIdx.z);
