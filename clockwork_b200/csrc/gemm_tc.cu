@@ -200,6 +200,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     // fetched here.  The instruction footprint matters as much as the instruction count: each CTA
     // runs its epilogue once, straight from the instruction cache's misses.
     const bool small_slice = p.splits > 1 && c_end - c_begin <= 4;
+    const bool medium_slice = p.splits > 1 && c_end - c_begin <= 8;
     float old0[4] = {0.f, 0.f, 0.f, 0.f};
     if (small_slice && !SWIGLU && p.epilogue == 1 && f < p.N) {
         const float* c32 = (const float*)p.C + (size_t)(n0 + c_begin) * p.ldc + f;
@@ -387,6 +388,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     };
     if (small_slice)
         finish(std::integral_constant<int, 4>{});
+    else if (medium_slice)
+        finish(std::integral_constant<int, 8>{});
     else
         finish(std::integral_constant<int, 16>{});
     // ---- teardown ---------------------------------------------------------------------------------
