@@ -213,13 +213,14 @@ attn_decode_kernel(const DecodeParams p) {
     __syncthreads();  // Qs and new_s visible
     if (p.kv_new != nullptr && p.inv_freq != nullptr) {
         // rotate q rows and the new k in shared memory: element j pairs with j + rotary_dim/2
-        for (int i = tid; i < (rows + (has_newest ? 1 : 0)) * half; i += blockDim.x) {
-            const int r = i / half, j = i % half;
+        for (int r = warp; r < rows + (has_newest ? 1 : 0); r += NWARPS) {  // a row per warp at a time
             bf16* row = r < rows ? Qs + r * LD : new_s;
-            const float c = cs_s[j], sn = cs_s[half + j];
-            const float x1 = __bfloat162float(row[j]), x2 = __bfloat162float(row[j + half]);
-            row[j] = __float2bfloat16_rn(x1 * c - x2 * sn);
-            row[j + half] = __float2bfloat16_rn(x2 * c + x1 * sn);
+            for (int j = lane; j < half; j += 32) {
+                const float c = cs_s[j], sn = cs_s[half + j];
+                const float x1 = __bfloat162float(row[j]), x2 = __bfloat162float(row[j + half]);
+                row[j] = __float2bfloat16_rn(x1 * c - x2 * sn);
+                row[j + half] = __float2bfloat16_rn(x2 * c + x1 * sn);
+            }
         }
         __syncthreads();
     }
@@ -287,14 +288,14 @@ attn_decode_kernel(const DecodeParams p) {
                 mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
                 mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
                 const float m_new = fmaxf(m_run[r], mx[r]);
-                alpha[r] = (m_run[r] == -INFINITY) ? 0.f : exp2f(m_run[r] - m_new);
+                alpha[r] = (m_run[r] == -INFINITY) ? 0.f : fast_exp2(m_run[r] - m_new);
                 float sum = 0.f;
 #pragma unroll
                 for (int j = 0; j < 2; ++j)
 #pragma unroll
                     for (int e = 0; e < 2; ++e) {
                         const float v = sc[j][2 * r + e];
-                        const float pr = (m_new == -INFINITY) ? 0.f : exp2f(v - m_new);
+                        const float pr = (m_new == -INFINITY) ? 0.f : fast_exp2(v - m_new);
                         sc[j][2 * r + e] = pr;
                         sum += pr;
                     }
@@ -352,7 +353,7 @@ attn_decode_kernel(const DecodeParams p) {
 #pragma unroll
         for (int w = 0; w < NWARPS; ++w) {
             const float mw = ml_s[w][r][0];
-            e[w] = (mw == -INFINITY || m == -INFINITY) ? 0.f : exp2f(mw - m);
+            e[w] = (mw == -INFINITY || m == -INFINITY) ? 0.f : fast_exp2(mw - m);
             L += e[w] * ml_s[w][r][1];
         }
         const float inv = L > 0.f ? 1.f / L : 0.f;
@@ -411,9 +412,9 @@ attn_decode_kernel(const DecodeParams p) {
         for (int k = 0; k < active; ++k) m = fmaxf(m, l[k]);
         float W = 0.f;
 #pragma unroll 1
-        for (int k = 0; k < active; ++k) W += (l[k] == -INFINITY) ? 0.f : exp2f(l[k] - m);
+        for (int k = 0; k < active; ++k) W += (l[k] == -INFINITY) ? 0.f : fast_exp2(l[k] - m);
 #pragma unroll 1
-        for (int k = 0; k < active; ++k) l[k] = (m == -INFINITY || l[k] == -INFINITY) ? 0.f : exp2f(l[k] - m) / W;
+        for (int k = 0; k < active; ++k) l[k] = (m == -INFINITY || l[k] == -INFINITY) ? 0.f : fast_exp2(l[k] - m) / W;
     }
     __syncthreads();
     constexpr int Q4 = HD / 4;
