@@ -15,7 +15,7 @@
 #include "attention_mma.cuh"
 
 #define TILE 64
-#define MIN_SPLIT 256  // smallest context split (tokens per CTA); the grid's z extent is sized for it
+#define MIN_SPLIT 128  // smallest context split (tokens per CTA); the grid's z extent is sized for it
 #define NWARPS 4
 
 struct DecodeParams {

@@ -71,7 +71,10 @@ struct Cfg {
     static constexpr int INBOX_BYTES = CAN_SPLIT ? (BN + MAX_SPLITS) * (SWIGLU ? 2 : 1) * BM * 4 : 0;
     // as many stages as fit (at most 8): a decode CTA is alone on its SM and keeps that many weight
     // tiles in flight from HBM
-    static constexpr int MAX_STAGES = (200 * 1024 - INBOX_BYTES) / STAGE_BYTES;
+    // Small token tiles without SwiGLU (the decode products around attention) leave room for a CTA of
+    // the decode attention kernel beside them, so that its prologue runs while this kernel finishes.
+    static constexpr int BUDGET = (BN <= 64 && !SWIGLU) ? 140 * 1024 : 200 * 1024;
+    static constexpr int MAX_STAGES = (BUDGET - INBOX_BYTES) / STAGE_BYTES;
     static constexpr int STAGES = MAX_STAGES > 8 ? 8 : MAX_STAGES;
     static constexpr int TMEM_COLS = ACC_COLS <= 32 ? 32 : (ACC_COLS <= 64 ? 64 : (ACC_COLS <= 128 ? 128 : (ACC_COLS <= 256 ? 256 : 512)));
     static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + INBOX_BYTES + 1024 /*alignment*/ + 1024 /*barriers*/;

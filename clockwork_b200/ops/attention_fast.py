@@ -59,7 +59,7 @@ def _decode_scratch(device: torch.device, part_o: int, part_lse: int, counters: 
     return st
 
 
-MIN_SPLIT = 256
+MIN_SPLIT = 128
 _SMS: dict[int, int] = {}
 
 
@@ -76,20 +76,30 @@ def _sm_count(device=None) -> int:
     return sms
 
 
+def _splits_wanted(num_seqs: int, num_heads: int, num_kv_heads: int, device=None) -> int:
+    """Context splits per request that give about three CTAs per SM."""
+    return max(1, 3 * _sm_count(device) // _pairs(num_seqs, num_heads, num_kv_heads))
+
+
 def decode_split(num_seqs: int, num_heads: int, num_kv_heads: int, max_live_ctx: int, device=None) -> int:
     """Tokens per CTA for a decode step: cut contexts so that there are about three CTAs per SM (a
-    CTA has four warps; the others' warps cover its stalls), never finer than 256 tokens.  Measured
-    on B200 at contexts of about 1,150 tokens: 256 is best up to 32 requests, 384 at 64 and more.
-    The result depends on the number of live requests and their longest context only."""
-    per_seq = max(1, 3 * _sm_count(device) // _pairs(num_seqs, num_heads, num_kv_heads))
-    split = -(-max(1, max_live_ctx) // per_seq)
+    CTA has four warps; the others' warps cover its stalls), never finer than 128 tokens.  Measured
+    on B200 at contexts of about 1,150 tokens: 128 is best up to 8 requests, 256 up to 32, 384 at 64
+    and more.  The result depends on the number of live requests and their longest context only."""
+    split = -(-max(1, max_live_ctx) // _splits_wanted(num_seqs, num_heads, num_kv_heads, device))
     return max(MIN_SPLIT, -(-split // 64) * 64)
 
 
-def decode_stages(num_seqs: int, num_heads: int, num_kv_heads: int) -> int:
-    """Tiles in flight per CTA: four (one CTA per SM, lowest latency) while the step has few CTAs,
-    two (room for several CTAs per SM) from 16 requests of two KV heads on."""
-    return 4 if _pairs(num_seqs, num_heads, num_kv_heads) <= 16 else 2
+def decode_stages(num_seqs: int, num_heads: int, num_kv_heads: int, max_ctx: int | None = None, device=None) -> int:
+    """Tiles of 64 tokens in flight per CTA.  Two when the step has many CTAs (from 16 requests of two
+    KV heads on: room for several CTAs per SM), and when no context up to ``max_ctx`` makes a split
+    longer than two tiles (then two hold a whole split, and the CTA is small enough to start beside
+    a CTA of the preceding product); else four."""
+    if _pairs(num_seqs, num_heads, num_kv_heads) > 16:
+        return 2
+    if max_ctx is not None and decode_split(num_seqs, num_heads, num_kv_heads, max_ctx, device) <= 2 * 64:
+        return 2
+    return 4
 
 
 class _Decode:
@@ -106,7 +116,7 @@ class _Decode:
                                 num_kv_heads, head_dim, scale, window, max_ctx or ctx.max_ctx_len, ctx.status,
                                 split=split, split_dev=split_dev,
                                 fused=None if fused_position is None else (*fused_position, view.slots),
-                                stages=decode_stages(ctx.num_seqs, num_heads, num_kv_heads))
+                                stages=decode_stages(ctx.num_seqs, num_heads, num_kv_heads, max_ctx or ctx.max_ctx_len, qkv.device))
 
 
 def attention_decode(q, k_cache, v_cache, block_tables, ctx_lens, num_heads, num_kv_heads, head_dim, scale, window,
@@ -114,7 +124,7 @@ def attention_decode(q, k_cache, v_cache, block_tables, ctx_lens, num_heads, num
                      fused: tuple | None = None, stages: int = 0) -> torch.Tensor:
     """One query token per request: ``q`` [S, >= nh*hd] (row s belongs to request s), ``ctx_lens`` [S]
     the tokens of each request in the cache (its own included).  ``split``: tokens per CTA (a multiple
-    of 64, at least 256; default: chosen by ``decode_split``), or ``split_dev``, the same as an int32
+    of 64, at least 128; default: chosen by ``decode_split``), or ``split_dev``, the same as an int32
     device scalar.  ``fused``: (inv_freq or None, rotary_dim, slots): ``q`` is then the raw [q | k | v]
     rows; q and the new k are rotated inside the kernel and the new token's k and v stored at ``slots``
     (so no separate position-encoding / cache-write kernel is needed).  Returns [S, nh*hd]."""
