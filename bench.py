@@ -135,6 +135,8 @@ def main() -> int:
     ap.add_argument("--skip-points", action="store_true", help="leave out batch 1 / 64 and prefill (quick runs)")
     ap.add_argument("--only", choices=["decode", "prefill"], default=None,
                     help="run one part only and print its figures (for profiling runs under ncu)")
+    ap.add_argument("--timeline", action="store_true",
+                    help="with --only decode: also print one step's kernel timeline (device-side records, ops/trace.py)")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm()
@@ -222,6 +224,8 @@ def main() -> int:
         dev_ms = start.elapsed_time(end)
         launches = launch_count() + runner.graph_kernel_launches - l0
         runner.check_status()
+        if args.timeline:
+            print_timeline(step_fn, ids, tokens)
         ctx_mid = ctx_now + warmup + steps // 2
         kv_bytes = batch * ctx_mid * cache.bytes_per_token()
         result = {
@@ -234,6 +238,24 @@ def main() -> int:
         del engine
         torch.cuda.empty_cache()
         return result
+
+    def print_timeline(step_fn, ids, tokens) -> None:
+        """One decode step, kernel by kernel: when the first and last CTA started, when the wait on the
+        preceding kernel returned, and when the last CTA was done (microseconds from the step's start)."""
+        from clockwork_b200.ops import trace
+
+        trace.enable()
+        step_fn(ids, tokens)
+        trace.reset()
+        step_fn(ids, tokens)
+        launches = trace.collect()
+        trace.disable()
+        print(f"# timeline of one decode step: {len(launches)} traced launches (matrix products and decode attention)")
+        print("# grid            ctas   start first..last     released first..last   end first..last   (us)")
+        for l in launches:
+            f = lambda key: l.get(key, 0) / 1000.0  # noqa: E731
+            print(f"# {str(l['grid']):15s} {l['ctas']:4d}  {f('start_first'):9.2f}..{f('start_last'):9.2f}  "
+                  f"{f('released_first'):9.2f}..{f('released_last'):9.2f}  {f('end_first'):9.2f}..{f('end_last'):9.2f}")
 
     def time_prefill(reps: int = 3) -> dict:
         engine = make_engine(1)
