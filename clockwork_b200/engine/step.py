@@ -300,7 +300,7 @@ class ModelRunner:
         self.status = cache.status if cache.status is not None else ops.new_status(self.device)
         self.builder = StepBuilder(cache, model.dtype, self.device, self.status)
         self.steps_run = 0
-        self.graphs: dict[tuple[int, bool], DecodeGraph] = {}
+        self.graphs: dict[tuple[int, bool, int], DecodeGraph] = {}  # (batch bucket, greedy, context tier)
         self.graph_max_ctx = 0  # set by enable_graphs
         self.graph_max_batch = 0
         self.graph_kernel_launches = 0  # kernels replayed through graphs (for accounting)
@@ -334,10 +334,19 @@ class ModelRunner:
         while bucket < n:
             bucket *= 2
         bucket = min(bucket, max(self.graph_max_batch, n))
-        key = (bucket, sampling is None)
+        # Graphs are captured per context tier (a power of two, at least 1024): the tier bounds the
+        # attention grid and the block-table width, and lets short contexts run the attention variant
+        # whose CTAs are small enough to start beside the preceding product's.  A request that grows
+        # past its tier moves the step to the next tier's graph (captured on first use).
+        longest = max(r.num_computed + 1 for r in reqs)
+        tier = 1024
+        while tier < longest:
+            tier *= 2
+        tier = min(tier, self.graph_max_ctx)
+        key = (bucket, sampling is None, tier)
         graph = self.graphs.get(key)
         if graph is None:
-            graph = self.graphs[key] = DecodeGraph(self, bucket, self.graph_max_ctx, greedy=sampling is None)
+            graph = self.graphs[key] = DecodeGraph(self, bucket, tier, greedy=sampling is None)
         out = graph.replay(cache, reqs, [e.tokens[0] for e in entries], sampling)
         self.graph_kernel_launches += graph.kernels
         self.last_upload_bytes = graph.upload_bytes
