@@ -394,45 +394,53 @@ attn_decode_kernel(const DecodeParams p) {
         return;
     }
     __threadfence();
-    // One compact form for any number of splits (this code runs once per group of CTAs: its size
-    // matters as much as its instruction count).  The log-sum-exps of every (row, split) come into
-    // shared memory in one trip; one thread per row turns them into weights w_k = 2^(lse_k - max) /
-    // sum, splits in order; then every thread merges groups of four outputs, four splits' partials in
-    // flight at a time.
-    float* w_all = (float*)Ks;  // [rows][active], over the K buffers (all reads of them are done)
-    for (int i = tid; i < rows * active; i += blockDim.x) {
-        const int r = i / active, k = i - r * active;
-        w_all[i] = __ldcg(p.part_lse + ((size_t)s * p.nh + h0 + r) * p.max_splits + first_split + k);
-    }
-    __syncthreads();
-    if (tid < rows) {
-        float* l = w_all + tid * active;
-        float m = -INFINITY;
-#pragma unroll 1
-        for (int k = 0; k < active; ++k) m = fmaxf(m, l[k]);
-        float W = 0.f;
-#pragma unroll 1
-        for (int k = 0; k < active; ++k) W += (l[k] == -INFINITY) ? 0.f : fast_exp2(l[k] - m);
-#pragma unroll 1
-        for (int k = 0; k < active; ++k) l[k] = (m == -INFINITY || l[k] == -INFINITY) ? 0.f : fast_exp2(l[k] - m) / W;
-    }
-    __syncthreads();
+    // Every thread merges groups of four outputs: weights w_k = 2^(lse_k - max) and the weighted sum of
+    // the splits' partials, divided by the sum of the weights at the end, splits in order.  Up to 12
+    // splits, all loads (the row's log-sum-exps and the partials) are issued before any is used: one
+    // trip to the L2.  More splits take the loop form below (small code: it runs once per group).
     constexpr int Q4 = HD / 4;
+    constexpr int KC = 12;
     for (int item = tid; item < rows * Q4; item += blockDim.x) {
         const int r = item / Q4, d = (item % Q4) * 4;
+        const float* lp = p.part_lse + ((size_t)s * p.nh + h0 + r) * p.max_splits + first_split;
         const float4* po = reinterpret_cast<const float4*>(
             p.part_o + (((size_t)s * p.nh + h0 + r) * p.max_splits + first_split) * HD + d);
-        const float* w = w_all + r * active;
+        float m = -INFINITY, W = 0.f;
         float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (active <= KC) {
+            float l[KC];
+            float4 v[KC];
+#pragma unroll
+            for (int k = 0; k < KC; ++k) {
+                l[k] = k < active ? __ldcg(lp + k) : -INFINITY;
+                v[k] = k < active ? __ldcg(po + (size_t)k * Q4) : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+#pragma unroll
+            for (int k = 0; k < KC; ++k) m = fmaxf(m, l[k]);
+#pragma unroll
+            for (int k = 0; k < KC; ++k) {
+                const float w = (l[k] == -INFINITY) ? 0.f : fast_exp2(l[k] - m);
+                W += w;
+                acc.x = fmaf(w, v[k].x, acc.x); acc.y = fmaf(w, v[k].y, acc.y);
+                acc.z = fmaf(w, v[k].z, acc.z); acc.w = fmaf(w, v[k].w, acc.w);
+            }
+        } else {
+#pragma unroll 1
+            for (int k = 0; k < active; ++k) m = fmaxf(m, __ldcg(lp + k));
 #pragma unroll 4
-        for (int k = 0; k < active; ++k) {
-            const float4 v = __ldcg(po + (size_t)k * Q4);
-            acc.x = fmaf(w[k], v.x, acc.x); acc.y = fmaf(w[k], v.y, acc.y);
-            acc.z = fmaf(w[k], v.z, acc.z); acc.w = fmaf(w[k], v.w, acc.w);
+            for (int k = 0; k < active; ++k) {
+                const float lk = __ldcg(lp + k);
+                const float4 x = __ldcg(po + (size_t)k * Q4);
+                const float w = (lk == -INFINITY) ? 0.f : fast_exp2(lk - m);
+                W += w;
+                acc.x = fmaf(w, x.x, acc.x); acc.y = fmaf(w, x.y, acc.y);
+                acc.z = fmaf(w, x.z, acc.z); acc.w = fmaf(w, x.w, acc.w);
+            }
         }
+        const float inv = W > 0.f ? 1.f / W : 0.f;
         uint2 o;
-        o.x = pack_bf16(acc.x, acc.y);
-        o.y = pack_bf16(acc.z, acc.w);
+        o.x = pack_bf16(acc.x * inv, acc.y * inv);
+        o.y = pack_bf16(acc.z * inv, acc.w * inv);
         *reinterpret_cast<uint2*>(p.out + ((size_t)s * p.nh + h0 + r) * HD + d) = o;
     }
     cw_trace_end();
@@ -444,8 +452,6 @@ static int launch_decode_st(const DecodeParams& p, int S, int splits, cudaStream
     const int SMEM = (16 * LD + 2 * ST * TILE * LD) * 2 + p.max_split_pages * 4;
     constexpr int MERGE = NWARPS * 16 * HD * 4;
     static_assert(MERGE <= ST * TILE * LD * 2, "the merge buffer must fit over the K buffers");
-    // the cross-split merge keeps one weight per (row, split) over the K buffers
-    if ((long long)16 * splits * 4 > (long long)ST * TILE * LD * 2) return CW_ERR_UNSUPPORTED;
     static int configured = 0;
     if (SMEM > configured) {
         if (SMEM > 48 * 1024 &&
