@@ -380,11 +380,14 @@ attn_decode_kernel(const DecodeParams p) {
         return;
     }
     // ---- the CTA that finishes last merges the splits, in split order ------------------------------
-    __threadfence();
+    // Release / acquire through the counter: the barrier orders every thread's partial stores before
+    // thread 0's release at GPU scope, and the last CTA's acquire, followed by its barrier, orders its
+    // threads' loads after all groups' stores.  (One scoped atomic instead of a fence in every thread.)
     __syncthreads();
     if (tid == 0) {
         int* counter = p.counters + ((size_t)s * p.nkv + kvh) * p.qgroups + qg;
-        const int prev = atomicAdd(counter, 1);
+        int prev;
+        asm volatile("atom.add.acq_rel.gpu.global.s32 %0, [%1], 1;" : "=r"(prev) : "l"(counter) : "memory");
         last_flag = (prev == active - 1);
         if (last_flag) *counter = 0;
     }
@@ -393,7 +396,6 @@ attn_decode_kernel(const DecodeParams p) {
         cw_trace_end();
         return;
     }
-    __threadfence();
     // Every thread merges groups of four outputs: weights w_k = 2^(lse_k - max) and the weighted sum of
     // the splits' partials, divided by the sum of the weights at the end, splits in order.  Up to 12
     // splits, all loads (the row's log-sum-exps and the partials) are issued before any is used: one
