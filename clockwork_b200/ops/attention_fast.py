@@ -77,15 +77,15 @@ def _sm_count(device=None) -> int:
 
 
 def _splits_wanted(num_seqs: int, num_heads: int, num_kv_heads: int, device=None) -> int:
-    """Context splits per request that give about three CTAs per SM."""
-    return max(1, 3 * _sm_count(device) // _pairs(num_seqs, num_heads, num_kv_heads))
+    """Context splits per request that fill the SMs once: two CTAs of the two-tile variant are resident
+    per SM (shared memory), and a CTA that has to wait for a slot starts a whole CTA-time late."""
+    return max(1, 2 * _sm_count(device) // _pairs(num_seqs, num_heads, num_kv_heads))
 
 
 def decode_split(num_seqs: int, num_heads: int, num_kv_heads: int, max_live_ctx: int, device=None) -> int:
-    """Tokens per CTA for a decode step: cut contexts so that there are about three CTAs per SM (a
-    CTA has four warps; the others' warps cover its stalls), never finer than 128 tokens.  Measured
-    on B200 at contexts of about 1,150 tokens: 128 is best up to 8 requests, 256 up to 32, 384 at 64
-    and more.  The result depends on the number of live requests and their longest context only."""
+    """Tokens per CTA for a decode step: cut contexts so that all CTAs are resident at once (two per
+    SM), never finer than 128 tokens.  The result depends on the number of live requests and their
+    longest context only."""
     split = -(-max(1, max_live_ctx) // _splits_wanted(num_seqs, num_heads, num_kv_heads, device))
     return max(MIN_SPLIT, -(-split // 64) * 64)
 
