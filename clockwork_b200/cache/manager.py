@@ -64,6 +64,7 @@ class RequestCache:
     shared_prefix_pages: int = 0  # leading pages of group 0 owned through the prefix cache
     state_slot: int | None = None
     live_from: list[int] = field(default_factory=list)  # per group: first logical block still held
+    writable_len: int = 0  # positions below this need neither a new page nor a copy: the request owns their pages alone
 
 
 class StateSlots:
@@ -185,6 +186,8 @@ class CacheManager:
     def can_reserve(self, req: RequestCache, new_len: int, keep_watermark: bool = False) -> bool:
         """clockwork/kvcache/block_manager.py:31-36 (admission leaves the watermark free) and
         :48-54 (growth needs the pages only)."""
+        if new_len <= req.writable_len:
+            return True  # the common decode step: the next token lands in a page the request owns alone
         floor = self.watermark_pages if keep_watermark else 0
         return all(
             group.allocator.num_free - n >= floor
@@ -205,6 +208,9 @@ class CacheManager:
         (clockwork/kvcache/block_manager.py:56-75).  All or nothing."""
         if new_len <= req.num_tokens:
             return
+        if new_len <= req.writable_len:
+            req.num_tokens = new_len
+            return
         if not self.can_reserve(req, new_len):
             raise OutOfPages(f"request {req.request_id!r}: not enough free pages to reach {new_len} tokens")
         for g, group in enumerate(self.groups):
@@ -222,6 +228,9 @@ class CacheManager:
             if missing > 0:
                 table.extend(group.allocator.allocate_many(missing))
         req.num_tokens = new_len
+        # From the page that new_len - 1 falls into onwards, every page was allocated or copied for this
+        # request just now or earlier, so nobody else holds it (until a fork, which resets this).
+        req.writable_len = min(len(t) for t in req.tables) * self.page_size if req.tables else new_len
 
     def _copy_page(self, group: PageGroup, src: int, dst: int) -> None:
         if group.kv is None:
@@ -263,6 +272,7 @@ class CacheManager:
             for page in child.tables[g]:
                 if page != NO_PAGE:
                     group.allocator.incref(page)
+        parent.writable_len = 0  # its pages are shared now: the next write must look (and copy)
         if self.state.needs:
             child.state_slot = self.state.take(child_id)
             self.state.copy(parent.state_slot, child.state_slot)

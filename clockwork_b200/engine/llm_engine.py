@@ -77,6 +77,7 @@ class LLMEngine:
         # (clockwork/engine/llm_engine.py:57-59)
         self._arrival = itertools.count()
         self._generate_counter = itertools.count()
+        self._unchecked_steps = 0
 
     @classmethod
     def from_config(cls, cfg: EngineConfig) -> "LLMEngine":
@@ -132,6 +133,8 @@ class LLMEngine:
         self._texts.pop(request_id, None)
 
     # ---- one iteration ------------------------------------------------------------------------------
+    STATUS_CHECK_EVERY = 16
+
     def step(self) -> list[RequestOutput]:
         out = self.scheduler.schedule()
         if not out.portions:
@@ -157,13 +160,20 @@ class LLMEngine:
             sampling = self.sampler.host_params(
                 [s.sampling_params for s in sampled_seqs], [len(s.output_token_ids) for s in sampled_seqs])
             tokens = self.runner.decode_with_graph(entries, sampling).tolist()
+            self._unchecked_steps += 1
         else:
+            self._unchecked_steps = self.STATUS_CHECK_EVERY  # steps with prompt portions are checked at once
             logits = self.runner.step(entries)
             if sampled_seqs:
                 tokens = self.sampler.sample(
                     logits, [s.sampling_params for s in sampled_seqs], [len(s.output_token_ids) for s in sampled_seqs]
                 )
-        self.runner.check_status()
+        # The kernels' status words cost a device-to-host read of their own: after a captured decode step
+        # they are read every STATUS_CHECK_EVERY steps (a kernel that met an index out of range has skipped
+        # the access and goes on reporting; the error is raised a few steps late, never lost).
+        if self._unchecked_steps >= self.STATUS_CHECK_EVERY:
+            self.runner.check_status()
+            self._unchecked_steps = 0
         for p in out.portions:
             p.seq.num_computed_tokens = p.start + p.num_tokens
         for seq, token in zip(sampled_seqs, tokens):
@@ -181,6 +191,9 @@ class LLMEngine:
         for output in outputs:
             if output.finished:
                 self._forget(output.request_id)
+        if self._unchecked_steps and any(output.finished for output in outputs):
+            self.runner.check_status()  # no request ends with an unread status
+            self._unchecked_steps = 0
         return outputs
 
     def _process(self, seq: Sequence) -> RequestOutput:
@@ -210,7 +223,7 @@ class LLMEngine:
         elif finish_reason == "length":
             seq.status = SequenceStatus.FINISHED_LENGTH
         return RequestOutput(
-            request_id=seq.seq_id, prompt_token_ids=list(seq.prompt_token_ids), token_ids=list(seq.output_token_ids),
+            request_id=seq.seq_id, prompt_token_ids=seq.prompt_token_ids, token_ids=seq.output_token_ids,
             text=text, finished=seq.is_finished(), finish_reason=finish_reason,
             num_cached_tokens=seq.num_cached_tokens, num_prompt_tokens=len(seq.prompt_token_ids),
             num_generated_tokens=len(seq.output_token_ids), delta_text=delta,

@@ -70,15 +70,36 @@ class Sequence:
         self.num_computed_tokens = 0
 
 
-@dataclass
 class RequestOutput:
-    request_id: str
-    prompt_token_ids: list[int]
-    token_ids: list[int]
-    text: str
-    finished: bool
-    finish_reason: str | None
-    num_cached_tokens: int
-    num_prompt_tokens: int
-    num_generated_tokens: int
-    delta_text: str = ""
+    """What ``LLMEngine.step`` reports for a request that sampled a token (the reference's
+    ``clockwork/engine/sequence.py`` RequestOutput: ids, text, finish state, counts).
+
+    ``prompt_token_ids`` is the request's own prompt list and ``token_ids`` a view of its output
+    list as long as it was when this output was made (the list only ever grows), so that a step
+    costs the same however long the prompt and the output are.  Treat both as read-only."""
+
+    __slots__ = ("request_id", "prompt_token_ids", "_output", "text", "finished", "finish_reason", "num_cached_tokens",
+                 "num_prompt_tokens", "num_generated_tokens", "delta_text")
+
+    def __init__(self, request_id: str, prompt_token_ids: list[int], token_ids: list[int], text: str, finished: bool,
+                 finish_reason: str | None, num_cached_tokens: int, num_prompt_tokens: int,
+                 num_generated_tokens: int, delta_text: str = "") -> None:
+        self.request_id = request_id
+        self.prompt_token_ids = prompt_token_ids
+        self._output = token_ids
+        self.text = text
+        self.finished = finished
+        self.finish_reason = finish_reason
+        self.num_cached_tokens = num_cached_tokens
+        self.num_prompt_tokens = num_prompt_tokens
+        self.num_generated_tokens = num_generated_tokens
+        self.delta_text = delta_text
+
+    @property
+    def token_ids(self) -> list[int]:
+        out = self._output
+        return out if len(out) == self.num_generated_tokens else out[: self.num_generated_tokens]
+
+    def __repr__(self) -> str:
+        return (f"RequestOutput(request_id={self.request_id!r}, token_ids={self.token_ids!r}, text={self.text!r}, "
+                f"finished={self.finished}, finish_reason={self.finish_reason!r})")
