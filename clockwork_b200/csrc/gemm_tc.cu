@@ -90,7 +90,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint64_t* bars = (uint64_t*)(smem + C::STAGES * C::STAGE_BYTES);
     // bars[0..S): full, bars[S..2S): empty, bars[2S]: accumulator ready
-    uint32_t* tmem_slot = (uint32_t*)(bars + 2 * C::STAGES + 1);
+    uint32_t* tmem_slot = (uint32_t*)(bars + 2 * C::STAGES + 2);
     volatile int* give_up = (volatile int*)(tmem_slot + 1);
 
     pdl_launch_dependents();
@@ -101,6 +101,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     const int my_kb = kb1 - kb0;
     const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + C::STAGES);
     const uint32_t acc_bar = smem_u32(bars + 2 * C::STAGES);
+    const uint32_t inbox_bar = smem_u32(bars + 2 * C::STAGES + 1);  // counts the bytes that the cluster pushes into this CTA's inbox
 
     if (tid == 0) {
         for (int s = 0; s < C::STAGES; ++s) {
@@ -108,6 +109,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             mbar_init(empty0 + 8 * s, 1);
         }
         mbar_init(acc_bar, 1);
+        mbar_init(inbox_bar, 1);
+        if (p.splits > 1) {
+            // this CTA finishes columns [rank * per, ...) of the tile: every CTA of the cluster, itself
+            // included, sends it those columns of its partial accumulator, 4 bytes per feature
+            const int per0 = (BN + p.splits - 1) / p.splits;
+            const int first = min(BN, (int)cluster_rank() * per0);
+            const int owned = min(BN, first + per0) - first;
+            mbar_expect_tx(inbox_bar, (uint32_t)(p.splits * owned * (SWIGLU ? 2 : 1) * BM * 4));
+        }
         *give_up = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -117,6 +127,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    // Every inbox barrier of the cluster is initialised before any CTA can push (long before: the
+    // pushes come after the main loop).  This is the kernel's only cluster-wide barrier, and it falls
+    // into the time before the preceding kernel has finished.
+    if (p.splits > 1) cluster_sync();
 
     int issued = 0;
     if (warp == 0 && lane == 0) {
@@ -236,9 +250,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16);
     // With the inner dimension split, the CTAs of one tile form a cluster and each finishes a slice of
     // the tile's columns.  A CTA pushes every column of its partial accumulator into the inbox of the
-    // column's owner (distributed shared memory, slot = sender's rank), the cluster synchronises once,
-    // and each owner adds the partials it received in rank order.  After the barrier nobody touches
-    // another CTA's memory, so CTAs leave independently.
+    // column's owner (st.async into distributed shared memory, slot = sender's rank; each store adds
+    // its 4 bytes to the owner's inbox barrier), and each owner waits for its own inbox only, then adds
+    // the partials it received in rank order.  Nobody waits for the whole cluster, and a CTA whose
+    // inbox is complete touches nobody else's memory again, so CTAs leave independently.
     float* stage = (float*)smem;  // unsplit tiles: [token][feature] staging for the TMA store
     const uint32_t stage_addr = smem_u32(stage);
     float* inbox = (float*)(smem + C::STAGES * C::STAGE_BYTES + 1024);  // [rank][column slot][BM]
@@ -258,15 +273,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             for (int j = 0; j < 16; ++j) {
                 // column c + j belongs to `owner`, as its column `local` (counted up: no division here)
                 const uint32_t a = dsmem_addr(inbox_addr + (uint32_t)(((my_rank * slots + local) * BM + row) * 4), owner);
-                st_dsmem(a, v[j]);
-                if (SWIGLU) st_dsmem(a + (uint32_t)(per * BM * 4), v2[j]);
+                const uint32_t b = dsmem_addr(inbox_bar, owner);
+                st_async_dsmem(a, v[j], b);
+                if (SWIGLU) st_async_dsmem(a + (uint32_t)(per * BM * 4), v2[j], b);
                 if (++local == per) {
                     local = 0;
                     ++owner;
                 }
             }
         }
-        cluster_sync();
+        if (c_end > c_begin) mbar_wait(inbox_bar, 0, give_up);  // (a timeout is reported at teardown)
     }
     if (p.splits == 1 && p.tma_store && acc_ready) {
         // The whole tile goes to shared memory as [token][feature] in C's type, then leaves in one

@@ -119,6 +119,13 @@ __device__ __forceinline__ uint32_t dsmem_addr(uint32_t local_addr, uint32_t ran
     asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
     return remote;
 }
+// A 4-byte store into another CTA's shared memory that adds its size to a transaction barrier of
+// that CTA when it has landed (the receiver waits on its own barrier, nobody on the whole cluster).
+__device__ __forceinline__ void st_async_dsmem(uint32_t remote_addr, float v, uint32_t remote_bar) {
+    asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.b32 [%0], %1, [%2];"
+                 ::"r"(remote_addr), "r"(__float_as_uint(v)), "r"(remote_bar)
+                 : "memory");
+}
 __device__ __forceinline__ void st_dsmem(uint32_t remote_addr, float v) {
     asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote_addr), "f"(v) : "memory");
 }
