@@ -362,16 +362,24 @@ attn_decode_kernel(const DecodeParams p) {
         w_s[r][NWARPS] = L > 0.f ? m + log2f(L) : -INFINITY;  // base 2
     }
     __syncthreads();
-    for (int i = tid; i < rows * HD; i += blockDim.x) {
-        const int r = i / HD, d = i % HD;
-        float val = 0.f;
+    for (int item = tid; item < rows * (HD / 4); item += blockDim.x) {  // four outputs per thread and pass
+        const int r = item / (HD / 4), d = (item % (HD / 4)) * 4;
+        float4 val = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-        for (int w = 0; w < NWARPS; ++w) val = fmaf(w_s[r][w], Om[((size_t)w * 16 + r) * HD + d], val);
+        for (int w = 0; w < NWARPS; ++w) {
+            const float4 x = *reinterpret_cast<const float4*>(Om + ((size_t)w * 16 + r) * HD + d);
+            const float ww = w_s[r][w];
+            val.x = fmaf(ww, x.x, val.x); val.y = fmaf(ww, x.y, val.y);
+            val.z = fmaf(ww, x.z, val.z); val.w = fmaf(ww, x.w, val.w);
+        }
         const int h = h0 + r;
         if (active == 1) {
-            p.out[((size_t)s * p.nh + h) * HD + d] = __float2bfloat16_rn(val);
+            uint2 o;
+            o.x = pack_bf16(val.x, val.y);
+            o.y = pack_bf16(val.z, val.w);
+            *reinterpret_cast<uint2*>(p.out + ((size_t)s * p.nh + h) * HD + d) = o;
         } else {
-            p.part_o[(((size_t)s * p.nh + h) * p.max_splits + sp) * HD + d] = val;
+            *reinterpret_cast<float4*>(p.part_o + (((size_t)s * p.nh + h) * p.max_splits + sp) * HD + d) = val;
             if (d == 0) p.part_lse[((size_t)s * p.nh + h) * p.max_splits + sp] = w_s[r][NWARPS];
         }
     }
