@@ -64,6 +64,7 @@ class RequestCache:
     shared_prefix_pages: int = 0  # leading pages of group 0 owned through the prefix cache
     state_slot: int | None = None
     live_from: list[int] = field(default_factory=list)  # per group: first logical block still held
+    table_epoch: int = 0  # counts changes of existing table entries (a copied page): holders of a copy of the table compare it
     writable_len: int = 0  # positions below this need neither a new page nor a copy: the request owns their pages alone
 
 
@@ -222,6 +223,7 @@ class CacheManager:
                     src, dst = cow
                     self._copy_page(group, src, dst)
                     table[blk] = dst
+                    req.table_epoch += 1
                     if g == 0 and blk < req.shared_prefix_pages:
                         req.shared_prefix_pages = blk  # no longer the prefix cache's page
             missing = self._blocks_for(new_len) - len(table)

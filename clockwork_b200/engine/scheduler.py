@@ -121,8 +121,38 @@ class Scheduler:
             n = min(n, self.cfg.prefill_chunk_size)
         return max(n, 0)
 
+    def _all_decode(self, ordered: list[Sequence], out: SchedulerOutput) -> bool:
+        """The common step of a running batch, decided without the general machinery: every running
+        sequence decodes one token, and the pages for that are there (mostly the token's slot lies in
+        a page the sequence already owns alone; the others get their page here).  Makes the plan the
+        general path would make; returns False, with nothing planned, when a sequence is in the
+        middle of its prompt or the pages run out (the general path then decides whom to preempt;
+        reservations made here stay and are what it would have made first)."""
+        cache = self.cache
+        requests = cache.requests
+        portions = []
+        for seq in ordered:
+            n = len(seq.prompt_token_ids) + len(seq.output_token_ids)
+            req = requests.get(seq.seq_id)
+            if req is None or seq.status is not SequenceStatus.RUNNING or n - seq.num_computed_tokens != 1:
+                return False
+            if n <= req.writable_len:
+                if n > req.num_tokens:
+                    req.num_tokens = n  # what CacheManager.reserve does when nothing has to be allocated
+            elif cache.can_reserve(req, n):
+                cache.reserve(req, n)
+            else:
+                return False
+            portions.append(ScheduledPortion(seq, n - 1, 1, True))
+        out.portions.extend(portions)
+        out.decode_seqs.extend(ordered)
+        out.num_batched_tokens += len(ordered)
+        return True
+
     def _schedule_running(self, out: SchedulerOutput) -> list[Sequence]:
         ordered = sorted(self.running, key=self._priority)
+        if ordered and self._all_decode(ordered, out):
+            return ordered
         kept: list[Sequence] = []
         # pass 1: decodes, in priority order, each reserving its slot at once so that a later
         # sequence sees the true pool

@@ -200,7 +200,7 @@ class DecodeGraph:
         self._uploaded = torch.cuda.Event()
         # which request's table each row holds and how much of it, so that a step writes only the
         # pages a request gained since its last step
-        self._row_owner: list[tuple[str, int] | None] = [None] * batch
+        self._row_owner: list[list] = [[None] * batch for _ in range(G)]  # per group and row: (request, table length held, its table_epoch)
 
         def view(name):
             o, n = seg[name]
@@ -258,20 +258,26 @@ class DecodeGraph:
         h["positions"][:n] = pos
         h["tok_seq"][:n] = np.arange(n, dtype=np.int32)
         h["ctx_lens"][:n] = pos + 1
+        rows = np.arange(n)
         for g in range(len(cache.groups)):
             tables, slots = h[f"tables{g}"], h[f"slots{g}"]
+            owners = self._row_owner[g]
             for i, r in enumerate(reqs):
+                # a row is rewritten only from where the request's table grew since the row last held it
+                # (most steps: nowhere)
                 table = r.tables[g]
-                owner = self._row_owner[i] if g == 0 else None
-                have = owner[1] if owner is not None and owner[0] == r.request_id and owner[1] <= len(table) else 0
-                if have < len(table):
-                    tables[i, have : len(table)] = table[have:]
-                if g == 0:
-                    self._row_owner[i] = (r.request_id, len(table)) if len(cache.groups) == 1 else None
-                page = table[pos[i] // ps]
-                if page == NO_PAGE:
-                    raise RuntimeError(f"request {r.request_id!r}: a token lands in a page that was given back")
-                slots[i] = page * ps + pos[i] % ps
+                owner = owners[i]
+                if owner is not None and owner[0] is r and owner[1] == len(table) and owner[2] == r.table_epoch:
+                    continue
+                same = owner is not None and owner[0] is r and owner[2] == r.table_epoch and owner[1] <= len(table)
+                have = owner[1] if same else 0
+                tables[i, have : len(table)] = table[have:]
+                owners[i] = (r, len(table), r.table_epoch)
+            pages = tables[rows, pos // ps]
+            if (pages == NO_PAGE).any():
+                bad = reqs[int(np.argmax(pages == NO_PAGE))]
+                raise RuntimeError(f"request {bad.request_id!r}: a token lands in a page that was given back")
+            slots[:n] = pages * ps + pos % ps
         if sampling is not None:
             temperature, top_k, top_p, uniform = sampling
             self.hf["temperature"][:n] = temperature
