@@ -32,6 +32,7 @@ struct DecodeParams {
     const int* split_ptr; // the same on the device (so that a captured graph can change it per step)
     int max_split_pages;  // page ids a split may need (sizes the shared-memory page list)
     int stages;           // tiles in flight per CTA: 4 (default) or 2
+    int swizzle;          // with 2 tiles in flight: the unpadded, swizzled K/V layout (three CTAs per SM)
     int* counters;   // [S * nkv * qgroups]
     int* status;
     // Fused position encoding and cache write (kv_new != null): q, and the new token's k and v, are
@@ -63,15 +64,22 @@ __device__ __forceinline__ bool mine_newest(int newest, int t0, int t1, int kv_b
 // division's instruction sequence exists once in the kernel instead of at every use.
 __device__ __noinline__ int2 block_and_offset(int pos, int page_size) { return make_int2(pos / page_size, pos % page_size); }
 
-template <int HD, int ST>
+template <int HD, int ST, bool SWIZZLE>
 __global__ void __launch_bounds__(NWARPS * 32)
 attn_decode_kernel(const DecodeParams p) {
-    constexpr int LD = HD + 8;  // padded row (elements): consecutive rows fall into different banks
+    constexpr int LD = HD + 8;  // padded q row (elements): consecutive rows fall into different banks
+    // K/V tiles, two layouts.  Padded rows (as for q): plain addressing, the smallest instruction count,
+    // for steps with few CTAs.  SWIZZLE (head sizes that are multiples of 64): unpadded rows with their
+    // 16-byte chunks XOR-swizzled by the row (chunk c of row r lies at chunk c ^ (r & 7)), as free of
+    // bank conflicts and small enough for three CTAs per SM, for steps with many CTAs.
+    constexpr bool SWZ = SWIZZLE && HD % 64 == 0;
+    constexpr int LDK = SWZ ? HD : HD + 8;
+    auto kv_off = [](int r, int c) -> int { return r * LDK + (SWZ ? ((c ^ (r & 7)) << 3) : (c << 3)); };
     extern __shared__ __align__(16) uint8_t smem_raw[];
-    bf16* Qs = (bf16*)smem_raw;                 // [16][LD]
-    bf16* Ks = Qs + 16 * LD;                    // [ST][TILE][LD]
-    bf16* Vs = Ks + ST * TILE * LD;             // [ST][TILE][LD]
-    int* page_s = (int*)(Vs + ST * TILE * LD);  // [max_split_pages] page of every block of this split
+    bf16* Qs = (bf16*)smem_raw;                  // [16][LD]
+    bf16* Ks = Qs + 16 * LD;                     // [ST][TILE][LDK]
+    bf16* Vs = Ks + ST * TILE * LDK;             // [ST][TILE][LDK]
+    int* page_s = (int*)(Vs + ST * TILE * LDK);  // [max_split_pages] page of every block of this split
     __shared__ float ml_s[NWARPS][16][2];
     __shared__ float w_s[16][16];               // final merge: weight of each split per query row
     __shared__ __align__(16) bf16 new_s[2 * HD]; // the newest token's k and v
@@ -143,16 +151,16 @@ attn_decode_kernel(const DecodeParams p) {
     auto copy_chunk = [&](bf16* kd, bf16* vd, int r, int c, int slot) {
         if (slot >= 0) {
             const size_t src = ((size_t)slot * p.nkv + kvh) * HD + c * 8;
-            cp_async16(kd + r * LD + c * 8, p.k_cache + src);
-            cp_async16(vd + r * LD + c * 8, p.v_cache + src);
+            cp_async16(kd + kv_off(r, c), p.k_cache + src);
+            cp_async16(vd + kv_off(r, c), p.v_cache + src);
         } else {
-            *reinterpret_cast<uint4*>(kd + r * LD + c * 8) = make_uint4(0, 0, 0, 0);
-            *reinterpret_cast<uint4*>(vd + r * LD + c * 8) = make_uint4(0, 0, 0, 0);
+            *reinterpret_cast<uint4*>(kd + kv_off(r, c)) = make_uint4(0, 0, 0, 0);
+            *reinterpret_cast<uint4*>(vd + kv_off(r, c)) = make_uint4(0, 0, 0, 0);
         }
     };
     auto load_tile = [&](int tile_idx) {
-        bf16* kd = Ks + (tile_idx % ST) * TILE * LD;
-        bf16* vd = Vs + (tile_idx % ST) * TILE * LD;
+        bf16* kd = Ks + (tile_idx % ST) * TILE * LDK;
+        bf16* vd = Vs + (tile_idx % ST) * TILE * LDK;
         const int pos0 = t0 + tile_idx * TILE;
         if (EVEN) {
             const int c = tid % CH, r0 = tid / CH;
@@ -254,19 +262,19 @@ attn_decode_kernel(const DecodeParams p) {
         if (it == newest_tile) {
             const int r = newest - t0 - it * TILE;
             for (int i = tid; i < 2 * CH; i += blockDim.x)
-                *reinterpret_cast<uint4*>((i < CH ? Ks : Vs) + (buf * TILE + r) * LD + (i % CH) * 8) =
+                *reinterpret_cast<uint4*>((i < CH ? Ks : Vs) + buf * TILE * LDK + kv_off(r, i % CH)) =
                     *reinterpret_cast<const uint4*>(new_s + (i < CH ? 0 : HD) + (i % CH) * 8);
         }
         __syncthreads();
-        const bf16* kt = Ks + buf * TILE * LD + warp * 16 * LD;
-        const bf16* vt = Vs + buf * TILE * LD + warp * 16 * LD;
+        const bf16* kt = Ks + buf * TILE * LDK + warp * 16 * LDK;  // (16 rows: a row's swizzle is the same from here)
+        const bf16* vt = Vs + buf * TILE * LDK + warp * 16 * LDK;
         const int tok0 = t0 + it * TILE + warp * 16;  // first token of this warp's 16
         if (tok0 < t1) {
             float sc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
 #pragma unroll
             for (int ks = 0; ks < HD / 16; ++ks) {
                 uint32_t b0, b1, b2, b3;
-                ldmatrix_x4(smem_addr(kt + ((lane & 7) + 8 * (lane >> 4)) * LD + ks * 16 + 8 * ((lane >> 3) & 1)),
+                ldmatrix_x4(smem_addr(kt + kv_off((lane & 7) + 8 * (lane >> 4), 2 * ks + ((lane >> 3) & 1))),
                             b0, b1, b2, b3);
                 mma_bf16(sc[0], qa[ks], b0, b1);
                 mma_bf16(sc[1], qa[ks], b2, b3);
@@ -309,7 +317,7 @@ attn_decode_kernel(const DecodeParams p) {
 #pragma unroll
             for (int n2 = 0; n2 < HD / 16; ++n2) {
                 uint32_t v0, v1, v2, v3;
-                ldmatrix_x4_trans(smem_addr(vt + ((lane & 7) + 8 * ((lane >> 3) & 1)) * LD + n2 * 16 + 8 * (lane >> 4)),
+                ldmatrix_x4_trans(smem_addr(vt + kv_off((lane & 7) + 8 * ((lane >> 3) & 1), 2 * n2 + (lane >> 4))),
                                   v0, v1, v2, v3);
                 float* oa = o_acc[2 * n2];
                 float* ob = o_acc[2 * n2 + 1];
@@ -456,21 +464,22 @@ attn_decode_kernel(const DecodeParams p) {
     cw_trace_end();
 }
 
-template <int HD, int ST>
+template <int HD, int ST, bool SWIZZLE>
 static int launch_decode_st(const DecodeParams& p, int S, int splits, cudaStream_t stream) {
     constexpr int LD = HD + 8;
-    const int SMEM = (16 * LD + 2 * ST * TILE * LD) * 2 + p.max_split_pages * 4;
+    constexpr int LDK = (SWIZZLE && HD % 64 == 0) ? HD : HD + 8;
+    const int SMEM = (16 * LD + 2 * ST * TILE * LDK) * 2 + p.max_split_pages * 4;
     constexpr int MERGE = NWARPS * 16 * HD * 4;
-    static_assert(MERGE <= ST * TILE * LD * 2, "the merge buffer must fit over the K buffers");
+    static_assert(MERGE <= 2 * ST * TILE * LDK * 2, "the merge buffer must fit over the K and V buffers");
     static int configured = 0;
     if (SMEM > configured) {
         if (SMEM > 48 * 1024 &&
-            cudaFuncSetAttribute(attn_decode_kernel<HD, ST>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess)
+            cudaFuncSetAttribute(attn_decode_kernel<HD, ST, SWIZZLE>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess)
             return (int)cudaGetLastError();
         configured = SMEM;
     }
     dim3 grid(p.nkv * p.qgroups, S, splits);
-    return cw_launch(attn_decode_kernel<HD, ST>, grid, dim3(NWARPS * 32), SMEM, stream, 1, p);
+    return cw_launch(attn_decode_kernel<HD, ST, SWIZZLE>, grid, dim3(NWARPS * 32), SMEM, stream, 1, p);
 }
 
 template <int HD>
@@ -478,8 +487,9 @@ static int launch_decode(const DecodeParams& p, int S, int splits, cudaStream_t 
     // Four tiles in flight per CTA (one CTA per SM) suit steps with few CTAs, where latency is
     // everything; with many CTAs two tiles in flight leave room for two or three CTAs per SM, and
     // the warps of the others cover each CTA's stalls.
-    if (HD <= 128 && p.stages != 2) return launch_decode_st<HD, (HD <= 128 ? 4 : 2)>(p, S, splits, stream);
-    return launch_decode_st<HD, 2>(p, S, splits, stream);
+    if (HD <= 128 && p.stages != 2) return launch_decode_st<HD, (HD <= 128 ? 4 : 2), false>(p, S, splits, stream);
+    if (HD % 64 == 0 && p.swizzle) return launch_decode_st<HD, 2, (HD % 64 == 0)>(p, S, splits, stream);
+    return launch_decode_st<HD, 2, false>(p, S, splits, stream);
 }
 
 // Workspace a call needs: part_o floats, part_lse floats, counters.
@@ -541,7 +551,8 @@ extern "C" int cw_attention_decode_fused(const void* q, int q_stride, void* out,
     p.rotary_dim = fuse_store && inv_freq != nullptr ? rotary_dim : 0;
     p.slots = slots; p.k_cache_w = (bf16*)k_cache; p.v_cache_w = (bf16*)v_cache;
     p.num_slots = num_pages * page_size;
-    p.stages = stages;
+    p.stages = stages & 0xFF;        // tiles in flight
+    p.swizzle = (stages >> 8) & 1;   // bit 8: the unpadded, swizzled K/V layout (with two tiles in flight)
     // the grid is sized for the smallest split; a larger run-time split leaves the later CTAs idle
     if (split_ptr == nullptr && (split < MIN_SPLIT || split % TILE != 0)) return CW_ERR_BAD_SIZE;
     const int splits = (max_ctx + MIN_SPLIT - 1) / MIN_SPLIT;

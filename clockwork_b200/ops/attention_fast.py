@@ -60,6 +60,7 @@ def _decode_scratch(device: torch.device, part_o: int, part_lse: int, counters: 
 
 
 MIN_SPLIT = 128
+SWIZZLED = 0x100  # flag in the `stages` argument of the decode kernel
 _SMS: dict[int, int] = {}
 
 
@@ -76,28 +77,41 @@ def _sm_count(device=None) -> int:
     return sms
 
 
-def _splits_wanted(num_seqs: int, num_heads: int, num_kv_heads: int, device=None) -> int:
-    """Context splits per request that fill the SMs once: two CTAs of the two-tile variant are resident
-    per SM (shared memory), and a CTA that has to wait for a slot starts a whole CTA-time late."""
-    return max(1, 2 * _sm_count(device) // _pairs(num_seqs, num_heads, num_kv_heads))
+def _resident_ctas(head_dim: int, stages: int = 2, swizzled: bool = True) -> int:
+    """CTAs of the decode kernel that one SM holds: shared memory (q tile, `stages` K and V tiles of
+    64 tokens, unpadded when the head size is a multiple of 64, and about 4 KB besides), at most
+    three by registers."""
+    ldk = head_dim if head_dim % 64 == 0 and swizzled else head_dim + 8
+    smem = (16 * (head_dim + 8) + 2 * stages * 64 * ldk) * 2 + 4096
+    return max(1, min(3, (227 * 1024) // smem))
 
 
-def decode_split(num_seqs: int, num_heads: int, num_kv_heads: int, max_live_ctx: int, device=None) -> int:
-    """Tokens per CTA for a decode step: cut contexts so that all CTAs are resident at once (two per
-    SM), never finer than 128 tokens.  The result depends on the number of live requests and their
-    longest context only."""
-    split = -(-max(1, max_live_ctx) // _splits_wanted(num_seqs, num_heads, num_kv_heads, device))
+def _splits_wanted(num_seqs: int, num_heads: int, num_kv_heads: int, device=None, head_dim: int = 128) -> int:
+    """Context splits per request that fill the SMs once with resident CTAs of the two-tile variant:
+    a CTA that has to wait for a slot starts a whole CTA-time late."""
+    pairs = _pairs(num_seqs, num_heads, num_kv_heads)
+    return max(1, _resident_ctas(head_dim, swizzled=pairs > 16) * _sm_count(device) // pairs)
+
+
+def decode_split(num_seqs: int, num_heads: int, num_kv_heads: int, max_live_ctx: int, device=None,
+                 head_dim: int = 128) -> int:
+    """Tokens per CTA for a decode step: cut contexts so that all CTAs are resident at once, never
+    finer than 128 tokens.  The result depends on the number of live requests and their longest
+    context only."""
+    split = -(-max(1, max_live_ctx) // _splits_wanted(num_seqs, num_heads, num_kv_heads, device, head_dim))
     return max(MIN_SPLIT, -(-split // 64) * 64)
 
 
-def decode_stages(num_seqs: int, num_heads: int, num_kv_heads: int, max_ctx: int | None = None, device=None) -> int:
+def decode_stages(num_seqs: int, num_heads: int, num_kv_heads: int, max_ctx: int | None = None, device=None,
+                  head_dim: int = 128) -> int:
     """Tiles of 64 tokens in flight per CTA.  Two when the step has many CTAs (from 16 requests of two
     KV heads on: room for several CTAs per SM), and when no context up to ``max_ctx`` makes a split
     longer than two tiles (then two hold a whole split, and the CTA is small enough to start beside
     a CTA of the preceding product); else four."""
     if _pairs(num_seqs, num_heads, num_kv_heads) > 16:
-        return 2
-    if max_ctx is not None and decode_split(num_seqs, num_heads, num_kv_heads, max_ctx, device) <= 2 * 64:
+        # many CTAs: the unpadded, swizzled K/V tiles (flag 0x100) make room for a third CTA per SM
+        return 2 | SWIZZLED if head_dim % 64 == 0 else 2
+    if max_ctx is not None and decode_split(num_seqs, num_heads, num_kv_heads, max_ctx, device, head_dim) <= 2 * 64:
         return 2
     return 4
 
@@ -111,12 +125,12 @@ class _Decode:
     def run(ctx, qkv, view, num_heads, num_kv_heads, head_dim, scale, window, max_ctx: int | None = None,
             fused_position=None) -> torch.Tensor:
         split_dev = ctx.extras.get("decode_split")  # a device scalar that a captured graph refreshes per step
-        split = None if split_dev is not None else decode_split(ctx.num_seqs, num_heads, num_kv_heads, ctx.max_ctx_len, qkv.device)
+        split = None if split_dev is not None else decode_split(ctx.num_seqs, num_heads, num_kv_heads, ctx.max_ctx_len, qkv.device, head_dim)
         return attention_decode(qkv, view.k_cache, view.v_cache, view.block_tables, ctx.ctx_lens, num_heads,
                                 num_kv_heads, head_dim, scale, window, max_ctx or ctx.max_ctx_len, ctx.status,
                                 split=split, split_dev=split_dev,
                                 fused=None if fused_position is None else (*fused_position, view.slots),
-                                stages=decode_stages(ctx.num_seqs, num_heads, num_kv_heads, max_ctx or ctx.max_ctx_len, qkv.device))
+                                stages=decode_stages(ctx.num_seqs, num_heads, num_kv_heads, max_ctx or ctx.max_ctx_len, qkv.device, head_dim))
 
 
 def attention_decode(q, k_cache, v_cache, block_tables, ctx_lens, num_heads, num_kv_heads, head_dim, scale, window,
@@ -139,7 +153,7 @@ def attention_decode(q, k_cache, v_cache, block_tables, ctx_lens, num_heads, num
         raise ValueError(f"head_dim {head_dim} is not one of {DECODE_HEAD_DIMS}")
     s = q.shape[0]
     if split_dev is None and split is None:
-        split = decode_split(s, num_heads, num_kv_heads, max_ctx, q.device)
+        split = decode_split(s, num_heads, num_kv_heads, max_ctx, q.device, head_dim)
     po, pl, pc = c_longlong(0), c_longlong(0), c_int(0)
     library().cw_attention_decode_workspace(s, num_heads, num_kv_heads, head_dim, max_ctx, byref(po), byref(pl), byref(pc))
     st = _decode_scratch(q.device, po.value, pl.value, pc.value)

@@ -58,14 +58,14 @@ class DecoderModel:
         captured step (the layers' mixers share one value; the finest wish wins)."""
         from ..ops.attention_fast import MIN_SPLIT, decode_split
 
-        shapes = {(b.mixer.num_heads, b.mixer.num_kv_heads) for b in self.blocks
+        shapes = {(b.mixer.num_heads, b.mixer.num_kv_heads, getattr(b.mixer, "head_dim", 128)) for b in self.blocks
                   if hasattr(b.mixer, "num_kv_heads")}
         device = self.device
 
         def policy(num_seqs: int, max_ctx: int) -> int:
             if not shapes:
                 return MIN_SPLIT
-            return min(decode_split(num_seqs, nh, nkv, max_ctx, device) for nh, nkv in shapes)
+            return min(decode_split(num_seqs, nh, nkv, max_ctx, device, hd) for nh, nkv, hd in shapes)
 
         return policy
 

@@ -458,7 +458,10 @@ def test_attention_decode_kernel(ops, status, fast, nh, nkv, hd, ps, window):
                                   4096, status, split=256).float().cpu().view(len(ctx_lens), nh, hd)
     assert torch.equal(again, out)
     # other ways of cutting the contexts (coarser, whole, chosen by the policy, given on the device)
-    for kw in (dict(split=512), dict(split=1344), dict(), dict(split_dev=torch.tensor([320], dtype=torch.int32, device=DEV))):
+    # ... and the other variants of the kernel: two tiles in flight, padded and swizzled K/V tiles
+    for kw in (dict(split=512), dict(split=1344), dict(), dict(split_dev=torch.tensor([320], dtype=torch.int32, device=DEV)),
+               dict(split=128, stages=2), dict(split=128, stages=2 | fast.SWIZZLED), dict(split=384, stages=2 | fast.SWIZZLED),
+               dict(stages=2 | fast.SWIZZLED)):
         other = fast.attention_decode(wide.to(dtype).to(DEV), k_cache.to(DEV), v_cache.to(DEV), tables.to(DEV),
                                       torch.tensor(ctx_lens, dtype=torch.int32, device=DEV), nh, nkv, hd, scale, window,
                                       2048, status, **kw).float().cpu().view(len(ctx_lens), nh, hd)
