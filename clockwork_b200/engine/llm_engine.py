@@ -78,6 +78,9 @@ class LLMEngine:
         self._arrival = itertools.count()
         self._generate_counter = itertools.count()
         self._unchecked_steps = 0
+        self._ahead = None  # (plan, sequences, prepared graph inputs) of the next step, made while a step ran
+        self.plan_ahead = True  # False: every step is planned after the one before it was read back
+        self.steps_planned_ahead = 0
 
     @classmethod
     def from_config(cls, cfg: EngineConfig) -> "LLMEngine":
@@ -119,12 +122,14 @@ class LLMEngine:
         seq = Sequence(request_id, prompt_token_ids, params, arrival_time=float(next(self._arrival)))
         self._seqs[request_id] = seq
         self._texts[request_id] = ""
+        self._ahead = None  # a plan made for the running batch alone no longer holds
         self.scheduler.add_seq(seq)
 
     def has_unfinished_requests(self) -> bool:
         return self.scheduler.has_unfinished()
 
     def abort_request(self, request_id: str) -> None:
+        self._ahead = None
         self.scheduler.abort(request_id)
         self._forget(request_id)
 
@@ -136,38 +141,65 @@ class LLMEngine:
     STATUS_CHECK_EVERY = 16
 
     def step(self) -> list[RequestOutput]:
-        out = self.scheduler.schedule()
-        if not out.portions:
-            if out.preempted or not self.scheduler.has_unfinished():
-                return []
-            # admission stalled with nothing running: pages held only by the prefix cache are
-            # invisible to the scheduler; reclaim the idle ones and retry once
-            # (clockwork/engine/llm_engine.py:102-113)
-            if self.prefix_cache is not None and self.prefix_cache.evict(self.cache.num_pages) > 0:
-                out = self.scheduler.schedule()
+        ahead, self._ahead = self._ahead, None
+        prepared = None
+        if ahead is not None:
+            # still true?  (somebody may have stepped the runner directly in between)
+            requests = self.cache.requests
+            for p in ahead[0].portions:
+                req = requests.get(p.seq.seq_id)
+                if req is None or req.num_computed != p.start or len(p.seq) != p.start + 1:
+                    ahead = None
+                    break
+        if ahead is not None:
+            # planned and prepared while the last step ran: every running sequence decodes one token
+            out, sampled_seqs, prepared = ahead
+            self.scheduler.accept_plan(out)
+            self.steps_planned_ahead += 1
+            entries = None
+        else:
+            out = self.scheduler.schedule()
             if not out.portions:
-                raise RuntimeError("waiting request cannot be admitted even with an empty prefix cache")
-        entries = []
-        sampled_seqs = []
-        for p in out.portions:
-            tokens = p.seq.tokens_between(p.start, p.start + p.num_tokens)
-            entries.append(StepEntry(p.seq.seq_id, tokens, [p.num_tokens - 1] if p.samples else []))
-            if p.samples:
-                sampled_seqs.append(p.seq)
+                if out.preempted or not self.scheduler.has_unfinished():
+                    return []
+                # admission stalled with nothing running: pages held only by the prefix cache are
+                # invisible to the scheduler; reclaim the idle ones and retry once
+                # (clockwork/engine/llm_engine.py:102-113)
+                if self.prefix_cache is not None and self.prefix_cache.evict(self.cache.num_pages) > 0:
+                    out = self.scheduler.schedule()
+                if not out.portions:
+                    raise RuntimeError("waiting request cannot be admitted even with an empty prefix cache")
+            entries = []
+            sampled_seqs = []
+            for p in out.portions:
+                tokens = p.seq.tokens_between(p.start, p.start + p.num_tokens)
+                entries.append(StepEntry(p.seq.seq_id, tokens, [p.num_tokens - 1] if p.samples else []))
+                if p.samples:
+                    sampled_seqs.append(p.seq)
         tokens: list[int] = []
-        if len(sampled_seqs) == len(entries) and self.runner.can_use_graph(entries):
+        if prepared is not None or (len(sampled_seqs) == len(entries) and self.runner.can_use_graph(entries)):
             # every request decodes one token: replay the captured graph (forward pass + sampling)
-            sampling = self.sampler.host_params(
-                [s.sampling_params for s in sampled_seqs], [len(s.output_token_ids) for s in sampled_seqs])
-            tokens = self.runner.decode_with_graph(entries, sampling).tolist()
+            if prepared is None:
+                sampling = self.sampler.host_params(
+                    [s.sampling_params for s in sampled_seqs], [len(s.output_token_ids) for s in sampled_seqs])
+                prepared = self.runner.prepare_decode([e.request_id for e in entries], sampling)
+                fed = [e.tokens[0] for e in entries]
+            else:
+                fed = [s.output_token_ids[-1] for s in sampled_seqs]
+            device_tokens = self.runner.launch_decode(prepared, fed)
+            # While the GPU runs this step, the host plans and prepares the next one on the assumption
+            # that every sequence goes on (dropped below if one ends, and whenever a request arrives or
+            # is aborted): the GPU then does not wait for the scheduler and the step builder.
+            self._ahead = self._plan_ahead() if self.plan_ahead else None
+            tokens = device_tokens.tolist()
             self._unchecked_steps += 1
         else:
-            self._unchecked_steps = self.STATUS_CHECK_EVERY  # steps with prompt portions are checked at once
             logits = self.runner.step(entries)
             if sampled_seqs:
                 tokens = self.sampler.sample(
                     logits, [s.sampling_params for s in sampled_seqs], [len(s.output_token_ids) for s in sampled_seqs]
                 )
+            self._unchecked_steps = self.STATUS_CHECK_EVERY  # steps with prompt portions are checked at once
         # The kernels' status words cost a device-to-host read of their own: after a captured decode step
         # they are read every STATUS_CHECK_EVERY steps (a kernel that met an index out of range has skipped
         # the access and goes on reporting; the error is raised a few steps late, never lost).
@@ -191,10 +223,22 @@ class LLMEngine:
         for output in outputs:
             if output.finished:
                 self._forget(output.request_id)
+                self._ahead = None  # the plan assumed that every sequence goes on
         if self._unchecked_steps and any(output.finished for output in outputs):
             self.runner.check_status()  # no request ends with an unread status
             self._unchecked_steps = 0
         return outputs
+
+    def _plan_ahead(self):
+        """The next step's plan and graph inputs, if the next step can be foreseen (see ``step``)."""
+        out = self.scheduler.plan_next_decode(self.cfg.model.max_model_len)
+        if out is None:
+            return None
+        seqs = [p.seq for p in out.portions]
+        if not 0 < len(seqs) <= self.runner.graph_max_batch:
+            return None
+        sampling = self.sampler.host_params([s.sampling_params for s in seqs], [len(s.output_token_ids) + 1 for s in seqs])
+        return out, seqs, self.runner.prepare_decode([s.seq_id for s in seqs], sampling)
 
     def _process(self, seq: Sequence) -> RequestOutput:
         params = seq.sampling_params
@@ -261,6 +305,7 @@ class LLMEngine:
         scheduler's bookkeeping (used to time the device work alone)."""
         from .. import ops
 
+        self._ahead = None
         entries = [StepEntry(rid, toks, [len(toks) - 1]) for rid, toks in zip(request_ids, tokens)]
         if self.runner.can_use_graph(entries):
             return self.runner.decode_with_graph(entries, None)

@@ -149,6 +149,40 @@ class Scheduler:
         out.num_batched_tokens += len(ordered)
         return True
 
+    def plan_next_decode(self, max_model_len: int) -> SchedulerOutput | None:
+        """Called while a decode step of every running sequence is in flight and its tokens are not
+        known yet: the plan of the step after it, under the assumption that no sequence ends and
+        nothing arrives, with the pages it needs reserved; None when that assumption is known to fail
+        (a sequence ends by length, something waits, a sequence is in its prompt, pages run out).
+        The engine drops the plan if the assumption fails after all; the reservations are then
+        what the general path would have made, or belong to sequences that are freed."""
+        if self.waiting or not self.running:
+            return None
+        ordered = sorted(self.running, key=self._priority)
+        cache = self.cache
+        out = SchedulerOutput()
+        for seq in ordered:
+            n = len(seq.prompt_token_ids) + len(seq.output_token_ids)  # without the token in flight
+            req = cache.requests.get(seq.seq_id)
+            if (req is None or seq.status is not SequenceStatus.RUNNING or n - seq.num_computed_tokens != 1
+                    or len(seq.output_token_ids) + 1 >= seq.sampling_params.max_tokens or n + 1 >= max_model_len):
+                return None
+            if n + 1 > req.writable_len:
+                if not cache.can_reserve(req, n + 1):
+                    return None
+                cache.reserve(req, n + 1)
+            elif n + 1 > req.num_tokens:
+                req.num_tokens = n + 1
+            out.portions.append(ScheduledPortion(seq, n, 1, True))
+        out.decode_seqs.extend(ordered)
+        out.num_batched_tokens = len(ordered)
+        return out
+
+    def accept_plan(self, out: SchedulerOutput) -> None:
+        """Bookkeeping of a plan made by ``plan_next_decode`` that the engine now runs as a step."""
+        self.stats.num_scheduled_batches += 1
+        self._refresh_counts()
+
     def _schedule_running(self, out: SchedulerOutput) -> list[Sequence]:
         ordered = sorted(self.running, key=self._priority)
         if ordered and self._all_decode(ordered, out):

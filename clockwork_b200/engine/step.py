@@ -250,10 +250,16 @@ class DecodeGraph:
         """Refill the inputs for these requests (each brings one token, its slot already
         reserved), upload them in one copy, replay.  ``sampling``: (temperature, top_k, top_p,
         uniform) lists for a graph that samples.  Returns the sampled tokens of the live rows."""
-        n = len(reqs)
+        self.fill(cache, reqs, sampling)
+        return self.launch(tokens)
+
+    def fill(self, cache: CacheManager, reqs, sampling=None) -> None:
+        """Everything of a step's inputs but the token ids, written into the pinned buffer: it depends
+        on the requests' positions and pages only, so it can be done while the step before is still
+        running (its upload has long left the buffer)."""
+        n = self._filled = len(reqs)
         self._uploaded.synchronize()  # the last upload has left the pinned buffer
         h, ps = self.h, cache.page_size
-        h["tokens"][:n] = tokens
         pos = np.fromiter((r.num_computed for r in reqs), dtype=np.int32, count=n)
         h["positions"][:n] = pos
         h["tok_seq"][:n] = np.arange(n, dtype=np.int32)
@@ -287,6 +293,11 @@ class DecodeGraph:
             self.hf["temperature"][n:] = 0.0
         self._fill_padding(n)
         h["decode_split"][0] = self._split_policy(n, int(pos.max()) + 1)
+
+    def launch(self, tokens: list[int]) -> torch.Tensor:
+        """The token ids of the filled step, one upload, the replay.  Returns the sampled tokens."""
+        n = self._filled
+        self.h["tokens"][:n] = tokens
         self.dev.copy_(self.host, non_blocking=True)
         self._uploaded.record()
         self.graph.replay()
@@ -327,15 +338,22 @@ class ModelRunner:
     def decode_with_graph(self, entries: list[StepEntry], sampling=None) -> torch.Tensor:
         """One single-token step for every entry through the captured graph, sampling included.
         Returns the sampled tokens (device int32 [len(entries)])."""
+        prepared = self.prepare_decode([e.request_id for e in entries], sampling)
+        return self.launch_decode(prepared, [e.tokens[0] for e in entries])
+
+    def prepare_decode(self, request_ids: list[str], sampling=None):
+        """The first half of ``decode_with_graph``: slots reserved, graph chosen, every input but the
+        token ids written.  It needs the requests' positions only, so the engine may call it for step
+        N+1 while step N runs (after step N's launch: positions are advanced at launch)."""
         cache = self.cache
         reqs = []
-        for e in entries:
-            req = cache.get(e.request_id)
+        for rid in request_ids:
+            req = cache.get(rid)
             cache.reserve(req, req.num_computed + 1)
             if req.num_computed + 1 > self.graph_max_ctx:
-                raise ValueError(f"request {e.request_id!r} outgrew the context the decode graphs were captured for")
+                raise ValueError(f"request {rid!r} outgrew the context the decode graphs were captured for")
             reqs.append(req)
-        n = len(entries)
+        n = len(reqs)
         bucket = 1
         while bucket < n:
             bucket *= 2
@@ -353,7 +371,14 @@ class ModelRunner:
         graph = self.graphs.get(key)
         if graph is None:
             graph = self.graphs[key] = DecodeGraph(self, bucket, tier, greedy=sampling is None)
-        out = graph.replay(cache, reqs, [e.tokens[0] for e in entries], sampling)
+        graph.fill(cache, reqs, sampling)
+        return graph, reqs
+
+    def launch_decode(self, prepared, tokens: list[int]) -> torch.Tensor:
+        """The second half: the token ids, the upload, the replay; positions advance."""
+        graph, reqs = prepared
+        cache = self.cache
+        out = graph.launch(tokens)
         self.graph_kernel_launches += graph.kernels
         self.last_upload_bytes = graph.upload_bytes
         for r in reqs:

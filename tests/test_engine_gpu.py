@@ -266,3 +266,32 @@ def test_captured_decode_graphs_change_nothing(dtype, models, tiny_dirs):
     outs = greedy_only.generate(prompts[:3], SamplingParams(max_tokens=5, ignore_eos=True))
     assert [o.token_ids for o in outs] == [r[:5] for r in (runs[0][0], None, runs[0][2]) if r is not None] + [] or True
     assert {key[1] for key in greedy_only.runner.graphs} == {True}  # only the greedy graphs were captured
+
+
+def test_steps_planned_ahead_change_nothing(models, tiny_dirs):
+    """While a decode step runs, the engine plans and prepares the next one; a sequence that ends, a
+    request that arrives and an abort drop that plan.  Same tokens with and without, sampling included."""
+    def run(plan_ahead):
+        eng = engine(models, tiny_dirs, "B", max_num_seqs=4, max_num_batched_tokens=32, max_model_len=96)
+        eng.plan_ahead = plan_ahead
+        got = {}
+        eng.add_request("greedy", prompt_token_ids=tokens_for("B", 9, 1), sampling_params=SamplingParams(max_tokens=30, ignore_eos=True))
+        eng.add_request("short", prompt_token_ids=tokens_for("B", 5, 2), sampling_params=SamplingParams(max_tokens=7, ignore_eos=True))
+        eng.add_request("sampled", prompt_token_ids=tokens_for("B", 12, 3),
+                        sampling_params=SamplingParams(max_tokens=25, temperature=0.9, top_k=20, seed=7, ignore_eos=True))
+        eng.add_request("gone", prompt_token_ids=tokens_for("B", 6, 4), sampling_params=SamplingParams(max_tokens=40, ignore_eos=True))
+        steps = 0
+        while eng.has_unfinished_requests():
+            for out in eng.step():
+                got[out.request_id] = list(out.token_ids)
+            steps += 1
+            if steps == 12:
+                eng.abort_request("gone")
+            if steps == 15:
+                eng.add_request("late", prompt_token_ids=tokens_for("B", 7, 5), sampling_params=SamplingParams(max_tokens=9, ignore_eos=True))
+        return got, eng.steps_planned_ahead
+
+    with_plan, planned = run(True)
+    without, none_planned = run(False)
+    assert planned > 10 and none_planned == 0
+    assert with_plan == without
