@@ -1,8 +1,10 @@
 // Paged decode attention in bfloat16: every request brings one query token and reads its whole
 // context from the cache.  The step is a stream of K/V pages from HBM, so the context of a request
 // is split over CTAs and all query heads of one KV head share each K/V tile.  The split size is a
-// run-time value (a multiple of 64, at least 256): with few requests the context is cut finely so
+// run-time value (a multiple of 64, at least 128): with few requests the context is cut finely so
 // that every SM has a CTA; with many requests a CTA walks a whole context and nothing is merged.
+// A CTA runs its code once, so the kernel is written for a small instruction footprint (one-shot
+// loops are not unrolled, divisions are out of line, the split merge is one compact form).
 //
 // Reference: clockwork/kernels/attention.py:113-134 (masking keys >= ctx_len, softmax, P.V) and the
 // Triton kernel clockwork/kernels/triton_paged_attn.py:16-106 (online softmax over one page per
@@ -505,7 +507,7 @@ extern "C" int cw_attention_decode_workspace(int S, int nh, int nkv, int hd, int
 
 // q: [S, >= nh*hd] rows (row stride q_stride), one query token per request; out: [S, nh*hd].
 // max_ctx bounds every ctx_lens[s]; it fixes the grid, not the result.  split (or *split_ptr): tokens
-// per CTA, a multiple of 64 and at least 256.
+// per CTA, a multiple of 64 and at least 128.
 extern "C" int cw_attention_decode_fused(const void* q, int q_stride, void* out, void* k_cache, void* v_cache,
                                          const int* block_tables, const int* ctx_lens, int S, int nh, int nkv, int hd,
                                          int page_size, int max_blocks, int num_pages, float scale, int window,

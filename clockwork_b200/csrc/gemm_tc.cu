@@ -6,18 +6,27 @@
 //
 // The weights ride the MMA's M dimension: one CTA owns 128 rows of W (128 output features) and a
 // tile of BN tokens, so the instruction is M=128 x N=BN x K=16 with both operands K-major in
-// shared memory (128-byte swizzle) and D[feature, token] in TMEM.  This one shape serves decode
-// (BN = 16..64 tokens, the step is a stream of weight tiles from HBM) and prefill (BN = 128/256).
-// When the grid would leave SMs idle the K dimension is split over blockIdx.z and the CTAs of one
-// tile are launched as a thread-block cluster: each pushes the columns of its partial accumulator
-// into the shared memory of the column's owner (distributed shared memory), and after one cluster
-// barrier every CTA adds what it received, in rank order, and finishes its slice of columns.  No
-// global scratch, no atomics, and the result does not depend on which CTA finished first.
+// shared memory (128-byte swizzle) and D[feature, token] in TMEM.  Three kernels:
 //
-// Warp roles (128 threads): warp 0 lane 0 issues TMA loads, warp 1 lane 0 issues the MMAs, warp 2
-// allocates and frees TMEM; all four warps run the epilogue (warp w reads TMEM lanes 32w..32w+31).
-// Epilogues: 0 store bf16; 1 add into the float32 residual; 2 store float32; SWIGLU computes
-// silu(X Wg^T) * (X Wu^T) from two accumulators.
+//   gemm_tc_kernel             BN = 16..256, one tile per CTA: decode and short portions.  When the
+//                              grid would leave SMs idle the K dimension is split over blockIdx.z and
+//                              the CTAs of one tile are launched as a thread-block cluster: each
+//                              pushes the columns of its partial accumulator into the shared memory
+//                              of the column's owner (st.async into distributed shared memory, counted
+//                              by a transaction barrier of the owner), and every owner adds what it
+//                              received, in rank order, and finishes its slice of columns.  No global
+//                              scratch, no atomics, no cluster-wide barrier after the main loop, and
+//                              the result does not depend on which CTA finished first.
+//   gemm_tc_persistent_kernel  prompt portions (more than 256 tokens): one CTA per SM walks tiles with
+//                              two TMEM accumulators (the epilogue of a tile overlaps the next one's MMAs)
+//   gemm_tc_pair_kernel        the same on CTA pairs (cta_group::2), in gemm_tc_pair.cuh
+//
+// Warp roles of gemm_tc_kernel (128 threads): warp 0 lane 0 issues TMA loads, warp 1 lane 0 issues the
+// MMAs, warp 2 allocates and frees TMEM; all four warps run the epilogue (warp w reads TMEM lanes
+// 32w..32w+31).  Epilogues: 0 store bf16; 1 add into the float32 residual; 2 store float32; SWIGLU
+// computes silu(X Wg^T) * (X Wu^T) from two accumulators; an RMSNorm can be split over the two products
+// around it (GemmParams).  A decode CTA runs its epilogue exactly once, so the epilogue is written for
+// a small *executed* instruction footprint (forms for 4, 8 and 16 columns, one loop per epilogue kind).
 //
 // Every wait on an mbarrier is bounded: when it runs out the kernel records CW_ST_WAIT_TIMEOUT in
 // the status words, the producer waits (bounded again) for the copies it has in flight, TMEM is

@@ -1,7 +1,9 @@
-"""Python face of the tcgen05 matrix-product kernel (``csrc/gemm_tc.cu``).
+"""Python face of the tcgen05 matrix-product kernels (``csrc/gemm_tc.cu``, ``csrc/gemm_tc_pair.cuh``).
 
-The kernel may split the inner dimension over the CTAs of a thread-block cluster; the partial tiles
-meet in distributed shared memory, so a call needs no scratch memory."""
+One entry point picks the kernel by the number of rows: up to 256 tokens one tile per CTA, the inner
+dimension split over the CTAs of a thread-block cluster when the grid would idle SMs (the partial
+tiles meet in distributed shared memory, so a call needs no scratch memory); more tokens run the
+persistent kernels (CTA pairs without SwiGLU, single CTAs with)."""
 
 from __future__ import annotations
 
