@@ -18,7 +18,8 @@
 //                              scratch, no atomics, no cluster-wide barrier after the main loop, and
 //                              the result does not depend on which CTA finished first.
 //   gemm_tc_persistent_kernel  prompt portions (more than 256 tokens): one CTA per SM walks tiles with
-//                              two TMEM accumulators (the epilogue of a tile overlaps the next one's MMAs)
+//                              two TMEM accumulators (the epilogue of a tile overlaps the next one's MMAs);
+//                              also few tokens against three rounds of weight tiles or more (the logits)
 //   gemm_tc_pair_kernel        the same on CTA pairs (cta_group::2), in gemm_tc_pair.cuh
 //
 // Warp roles of gemm_tc_kernel (128 threads): warp 0 lane 0 issues TMA loads, warp 1 lane 0 issues the
@@ -668,6 +669,7 @@ struct Plan {
     int bn, splits, kb_per_split, tiles;
     bool persistent;  // bn is then any multiple of 16 and the persistent kernel runs
     bool pair;        // ... on CTA pairs: tiles of 256 features
+    bool stream;      // few tokens, many rounds of weight tiles (a vocabulary): the persistent kernel with narrow tiles
 };
 
 // Token-tile width for CTA pairs: per k-block a pair-tile costs about max(2 bn, 256 + bn) cycles (MMA
@@ -718,6 +720,9 @@ extern "C" int cw_gemm_tc_set_tile(int bn) {
 }
 // Switches the CTA-pair kernel off or on (measurements, tests of the single-CTA persistent kernel).
 extern "C" int cw_gemm_tc_set_pair(int on) { g_pair_enabled = on ? 1 : 0; return CW_OK; }
+static int g_stream_enabled = 1;
+// Switches the persistent form of few-token products over very many weight tiles off or on (measurements).
+extern "C" int cw_gemm_tc_set_stream(int on) { g_stream_enabled = on ? 1 : 0; return CW_OK; }
 
 static Plan make_plan(int T, int N, int K, bool swiglu, int sm_count, bool c_by_tma = true) {
     Plan pl;
@@ -725,8 +730,14 @@ static Plan make_plan(int T, int N, int K, bool swiglu, int sm_count, bool c_by_
     pl.persistent = T > 256 && sm_count > 0 && c_by_tma;  // its epilogue has no other way out than TMA
     pl.bn = T <= 16 ? 16 : (T <= 32 ? 32 : (T <= 64 ? 64 : (T <= 128 ? 128 : cap)));
     pl.pair = pl.persistent && !swiglu && sm_count >= 2 && g_pair_enabled;
-    if (pl.persistent) pl.bn = pl.pair ? balanced_bn_pair(T, N, sm_count) : balanced_bn(T, N, swiglu, sm_count);
-    if (pl.persistent && g_forced_bn != 0 && (!swiglu || g_forced_bn <= 128)) pl.bn = g_forced_bn;
+    // Few tokens against so many weight tiles that one CTA per tile would run in three rounds or more
+    // (the logits product): one CTA per SM walks the tiles instead, its loads running on into the
+    // next tile while the epilogue of the last one drains, and no round is left part-filled.
+    pl.stream = !pl.persistent && !swiglu && T <= 64 && sm_count > 0 && c_by_tma &&
+                (long long)((N + BM - 1) / BM) >= 3LL * sm_count && g_stream_enabled;
+    if (pl.stream) pl.persistent = true;
+    if (pl.persistent && !pl.stream) pl.bn = pl.pair ? balanced_bn_pair(T, N, sm_count) : balanced_bn(T, N, swiglu, sm_count);
+    if (pl.persistent && !pl.stream && g_forced_bn != 0 && (!swiglu || g_forced_bn <= 128)) pl.bn = g_forced_bn;
     pl.tiles = pl.pair ? ((N + 2 * BM - 1) / (2 * BM)) * ((T + pl.bn - 1) / pl.bn) : ((N + BM - 1) / BM) * ((T + pl.bn - 1) / pl.bn);
     const int num_kb = (K + BK - 1) / BK;
     int splits = 1;
@@ -824,8 +835,9 @@ extern "C" int cw_gemm_tc_norm(const void* X, const void* W, const void* W2, con
     const bool c_f32 = !swiglu && epilogue != 0;
     const long long c_row_bytes = (long long)ldc * (c_f32 ? 4 : 2);
     const bool c_by_tma = c_row_bytes % 16 == 0 && ((uintptr_t)C & 15) == 0;
-    const Plan pl = make_plan(T, N, K, swiglu, sm_count, c_by_tma);
     const bool emits = emit_x != nullptr;
+    // (a product that finishes or begins a norm has no way out through TMA alone)
+    const Plan pl = make_plan(T, N, K, swiglu, sm_count, c_by_tma && scale_part == nullptr && !emits);
     if (scale_part != nullptr || emits) {
         if (pl.persistent || pl.bn > 128) return CW_ERR_UNSUPPORTED;
         if (scale_part != nullptr && (scale_parts <= 0 || scale_dim <= 0)) return CW_ERR_BAD_SIZE;
@@ -862,6 +874,7 @@ extern "C" int cw_gemm_tc_norm(const void* X, const void* W, const void* W2, con
     }
     if (persistent) {
         const int ctas = pl.tiles < sm_count ? pl.tiles : sm_count;
+        if (pl.stream) return launch_persistent<64, false>(mw, mw2, mx, mc, p, ctas, stream);
         return swiglu ? launch_persistent<128, true>(mw, mw2, mx, mc, p, ctas, stream)
                       : launch_persistent<256, false>(mw, mw2, mx, mc, p, ctas, stream);
     }

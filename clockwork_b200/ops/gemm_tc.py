@@ -32,6 +32,8 @@ def _configure() -> None:
     lib.cw_gemm_tc_plan.restype = c_int
     lib.cw_gemm_tc_set_pair.argtypes = [I]
     lib.cw_gemm_tc_set_pair.restype = c_int
+    lib.cw_gemm_tc_set_stream.argtypes = [I]
+    lib.cw_gemm_tc_set_stream.restype = c_int
     lib.cw_gemm_tc_set_tile.argtypes = [I]
     lib.cw_gemm_tc_set_tile.restype = c_int
     _configured = True
@@ -48,6 +50,13 @@ def set_pair_kernel(on: bool) -> None:
     on the single-CTA persistent kernel (for measurements and for testing that kernel)."""
     _configure()
     library().cw_gemm_tc_set_pair(1 if on else 0)
+
+
+def set_stream_kernel(on: bool) -> None:
+    """Products of few tokens with a very tall weight matrix (the logits) run on the persistent kernel
+    with narrow token tiles by default; ``False`` gives each weight tile a CTA of its own (for measurements)."""
+    _configure()
+    library().cw_gemm_tc_set_stream(1 if on else 0)
 
 
 def _device_state(device: torch.device) -> dict:

@@ -333,6 +333,21 @@ def test_gemm_tc_single_cta_persistent_kernel(ops, gemm_tc, t, n, k):
         gemm_tc.set_pair_kernel(True)
 
 
+@pytest.mark.parametrize("t,n,k", [(1, 57000, 128), (8, 56840, 264), (50, 57096, 136), (64, 60000, 64)])
+def test_gemm_tc_few_tokens_over_many_weight_tiles(ops, gemm_tc, t, n, k):
+    """A logits-like product (three rounds of weight tiles or more) walks its tiles with one CTA per
+    SM; the same sizes with a CTA per tile give the same bits."""
+    test_gemm_tc_against_float64(ops, gemm_tc, t, n, k)
+    x, w = rand(t, k, dtype=torch.bfloat16).to(DEV), rand(n, k, dtype=torch.bfloat16, scale=0.1, seed=1).to(DEV)
+    walked = gemm_tc.gemm(x, w, epilogue=ops.EPILOGUE_STORE_F32)
+    gemm_tc.set_stream_kernel(False)
+    try:
+        per_tile = gemm_tc.gemm(x, w, epilogue=ops.EPILOGUE_STORE_F32)
+    finally:
+        gemm_tc.set_stream_kernel(True)
+    assert torch.equal(walked, per_tile)
+
+
 @pytest.mark.parametrize("t,n,k", TC_SHAPES)
 def test_gemm_tc_against_float64(ops, gemm_tc, t, n, k):
     x, w, bias = rand(t, k, dtype=torch.bfloat16), rand(n, k, dtype=torch.bfloat16, scale=0.1, seed=1), rand(n, seed=2)
