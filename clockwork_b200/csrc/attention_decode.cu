@@ -188,7 +188,47 @@ attn_decode_kernel(const DecodeParams p) {
             sincosf(ang, &cs_s[half + j], &cs_s[j]);  // one argument reduction for both
         }
 
+    // Full rotation (the usual case): q rows and the new k are rotated on their way into shared memory,
+    // each thread taking the two 16-byte chunks that pair up (elements j and j + HD/2), in one pass.
+    const bool has_newest = mine_newest(newest, t0, t1, kv_begin);
+    const bool rotate_on_load = p.kv_new != nullptr && p.inv_freq != nullptr && p.rotary_dim == HD && HD % 16 == 0;
+    if (rotate_on_load) {
+        for (int i = tid; i < (16 - rows) * CH; i += blockDim.x)  // the unused q rows of the MMA tile
+            *reinterpret_cast<uint4*>(Qs + (rows + i / CH) * LD + (i % CH) * 8) = make_uint4(0, 0, 0, 0);
+        __syncthreads();  // cs_s visible
+    }
     pdl_wait();
+    if (rotate_on_load) {
+        constexpr int HC = HD / 16;  // chunk pairs per row
+        const int q_units = rows * HC, k_units = has_newest ? HC : 0, v_units = has_newest ? CH : 0;
+        for (int u = tid; u < q_units + k_units + v_units; u += blockDim.x) {
+            if (u >= q_units + k_units) {  // the new v: a plain copy
+                const int c = u - q_units - k_units;
+                *reinterpret_cast<uint4*>(new_s + HD + c * 8) = *reinterpret_cast<const uint4*>(
+                    p.kv_new + (size_t)s * p.q_stride + (size_t)(p.nh + p.nkv + kvh) * HD + c * 8);
+                continue;
+            }
+            const bool is_q = u < q_units;
+            const int r = is_q ? u / HC : 0, c = is_q ? u % HC : u - q_units;
+            const bf16* src = is_q ? p.q + (size_t)s * p.q_stride + (size_t)(h0 + r) * HD
+                                   : p.kv_new + (size_t)s * p.q_stride + (size_t)(p.nh + kvh) * HD;
+            bf16* dst = is_q ? Qs + r * LD : new_s;
+            uint4 lo = *reinterpret_cast<const uint4*>(src + c * 8);
+            uint4 hi = *reinterpret_cast<const uint4*>(src + HD / 2 + c * 8);
+            bf16* x1 = reinterpret_cast<bf16*>(&lo);
+            bf16* x2 = reinterpret_cast<bf16*>(&hi);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                const float cs = cs_s[c * 8 + e], sn = cs_s[HD / 2 + c * 8 + e];
+                const float a = __bfloat162float(x1[e]), b = __bfloat162float(x2[e]);
+                x1[e] = __float2bfloat16_rn(a * cs - b * sn);
+                x2[e] = __float2bfloat16_rn(b * cs + a * sn);
+            }
+            *reinterpret_cast<uint4*>(dst + c * 8) = lo;
+            *reinterpret_cast<uint4*>(dst + HD / 2 + c * 8) = hi;
+        }
+        __syncthreads();  // Qs and new_s visible
+    } else {
     // ---- Q rows of this group into shared memory ----------------------------------------------------
     for (int i = tid; i < 16 * CH; i += blockDim.x) {
         const int r = i / CH, c = i % CH;
@@ -197,7 +237,6 @@ attn_decode_kernel(const DecodeParams p) {
         *reinterpret_cast<uint4*>(Qs + r * LD + c * 8) = v;
     }
     // ---- the newest token's k and v: from the [q|k|v] row (rotating k, storing both) or from the cache
-    const bool has_newest = mine_newest(newest, t0, t1, kv_begin);
     if (has_newest) {
         if (p.kv_new != nullptr) {
             const bf16* krow = p.kv_new + (size_t)s * p.q_stride + (size_t)(p.nh + kvh) * HD;
@@ -234,6 +273,7 @@ attn_decode_kernel(const DecodeParams p) {
         }
         __syncthreads();
     }
+    }  // (not rotate_on_load)
     if (p.kv_new != nullptr && has_newest && qg == 0) {
         // one CTA per (request, KV head) stores the new token
         const int slot = p.slots != nullptr ? p.slots[s] : -1;
