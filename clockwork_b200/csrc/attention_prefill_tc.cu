@@ -5,16 +5,21 @@
 // through the block table.  Per tile:
 //
 //     S  = Q K^T           tcgen05.mma, Q and K both K-major in shared memory, S in TMEM
-//     P  = 2^(S c - m)     softmax warps: two threads per query row read its row of S from TMEM
-//                          (no shuffles), float32 statistics, P rounded to bfloat16 into shared memory
-//     O' = P V             tcgen05.mma, P K-major, V as it lies in the cache (head dimension
-//                          contiguous = MN-major B operand), O' in TMEM
-//     O  = (O + O'_prev) * 2^(m_prev - m)   in registers of the row's thread
+//     P  = 2^(S c - m)     softmax warps: two threads per query row read its half row of S from TMEM
+//                          once (no shuffles), float32 statistics, P rounded to bfloat16 into shared memory
+//     O += P V             tcgen05.mma, P K-major, V as it lies in the cache (head dimension
+//                          contiguous = MN-major B operand), O accumulated in TMEM over all tiles
 //
-// S and O' are double buffered in TMEM (2 x 128 + 2 x HD columns) and P in shared memory, so that the MMAs of tile j+1 and
-// the loads of later tiles run while the softmax warps work on tile j.  K and V tiles share one ring
-// of shared-memory slots.  Warps (320 threads): 0 TMA producer, 1 MMA issuer and TMEM owner, 2..9
-// softmax (warp w owns TMEM lanes 32 (w % 4) .. +31; two warps share a lane quarter and split the columns).
+// m is the maximum the row's exponentials are taken against.  It follows the row's true maximum
+// lazily: only when a tile exceeds it by more than 2^8 is it moved and the accumulated O (in TMEM)
+// and the row sum rescaled, which after the first tiles of a row hardly ever happens; the result
+// is the same sum, since numerator and denominator carry the same factor.
+//
+// S is double buffered in TMEM (2 x 128 columns, O after them) and P in shared memory, so that the
+// MMAs of tile j+1 and the loads of later tiles run while the softmax warps work on tile j.  K and V
+// tiles share one ring of shared-memory slots.  Warps (320 threads): 0 TMA producer, 1 MMA issuer and
+// TMEM owner, 2..9 softmax (warp w owns TMEM lanes 32 (w % 4) .. +31; two warps share a lane quarter
+// and split the columns).
 //
 // Reference: clockwork/kernels/attention.py:68-96 (gather the context through one block table, then
 // dense causal attention with the query aligned to the end of the context, :45-65) and
@@ -32,6 +37,7 @@
 #define AK 128  // keys per tile
 #define A_THREADS 320  // TMA producer, MMA issuer, 8 softmax warps
 #define A_MAX_SMEM (227 * 1024)
+#define LAZY_STEP 8.0f  // log2 of how far a tile's maximum may exceed the one in use before the row is rescaled
 
 struct PrefillTcParams {
     bf16* out;
@@ -56,7 +62,7 @@ struct ACfg {
     static constexpr int O_COL = 2 * AK;                 // S buffers at columns 0 and 128, O' after them
     static constexpr int TMEM_COLS = 512;
     static_assert(NSLOTS >= 4, "too few key/value slots");
-    static_assert(O_COL + 2 * HD <= TMEM_COLS, "accumulators do not fit in tensor memory");
+    static_assert(O_COL + HD <= TMEM_COLS, "accumulators do not fit in tensor memory");
 };
 
 __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int x, int y, int z, uint32_t bar) {
@@ -79,6 +85,22 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float* v) {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
     for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const float* v) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
+        "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+        ::"r"(taddr), "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])),
+          "r"(__float_as_uint(v[3])), "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])),
+          "r"(__float_as_uint(v[7])), "r"(__float_as_uint(v[8])), "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])),
+          "r"(__float_as_uint(v[11])), "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])),
+          "r"(__float_as_uint(v[15])), "r"(__float_as_uint(v[16])), "r"(__float_as_uint(v[17])), "r"(__float_as_uint(v[18])),
+          "r"(__float_as_uint(v[19])), "r"(__float_as_uint(v[20])), "r"(__float_as_uint(v[21])), "r"(__float_as_uint(v[22])),
+          "r"(__float_as_uint(v[23])), "r"(__float_as_uint(v[24])), "r"(__float_as_uint(v[25])), "r"(__float_as_uint(v[26])),
+          "r"(__float_as_uint(v[27])), "r"(__float_as_uint(v[28])), "r"(__float_as_uint(v[29])), "r"(__float_as_uint(v[30])),
+          "r"(__float_as_uint(v[31]))
+        : "memory");
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
 // Descriptor of an MN-major operand with the 128-byte swizzle: rows of the K dimension are 128 bytes
 // (64 contiguous elements of the MN dimension), groups of 8 rows are 1024 bytes apart (stride byte
@@ -254,10 +276,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             for (int kk = 0; kk < AK / 16; ++kk) {
                 const uint64_t a = smem_desc_sw128(smem_u32(p_s) + (j & 1) * C::P_BYTES + (kk / 4) * C::BLOCK_BYTES) + 2 * (kk % 4);
                 const uint64_t b = smem_desc_mn_sw128(v_addr + kk * 16 * 128, C::BLOCK_BYTES);
-                umma_bf16(tmem_base + C::O_COL + (j & 1) * HD, a, b, idesc_o, kk > 0 ? 1u : 0u);
+                umma_bf16(tmem_base + C::O_COL, a, b, idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
             }
             umma_commit(empty0 + 8 * slot);
-            umma_commit(o_full0 + 8 * (j & 1));   // O'_j is ready and P buffer j & 1 may be overwritten
+            umma_commit(o_full0 + 8 * (j & 1));   // O holds tiles 0..j and P buffer j & 1 may be overwritten
         }
     } else if (warp >= 2) {
         // ---- softmax warps: two threads per query row, each with half of the row's columns -----------
@@ -274,64 +296,63 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         const int lo = p.window > 0 ? max(0, qp + 1 - p.window) : 0;   // its first visible key
         const float scale_log2 = p.scale * 1.4426950408889634f;        // softmax in base 2
         const int pair_bar = 1 + quarter;                              // named barrier of the 64 threads of a quarter
-        float o_acc[OC];
-#pragma unroll
-        for (int i = 0; i < OC; ++i) o_acc[i] = 0.f;
-        float m_run = -INFINITY, l_run = 0.f;
+        float m_used = -INFINITY, l_run = 0.f;  // m_used: the maximum this row's exponentials are taken against
         bool ok = true;
         for (int j = 0; j < ntiles; ++j) {
             const int tile0 = tile_lo + j * AK;
             const int col0 = tile0 + half * SC;  // position of this thread's first key
             ok = mbar_wait(s_full0 + 8 * (j & 1), (j >> 1) & 1, give_up);
+            ok = __all_sync(0xffffffffu, ok);  // one decision per warp: the TMEM accesses below are warp-wide
             if (!ok) break;
             tc_fence_after();
             const uint32_t s_addr = lane_addr + (j & 1) * AK + half * SC;
             // tiles wholly visible to all 128 rows skip the per-element test
             const bool all_visible = tile0 + AK - 1 <= pos0 && (p.window <= 0 || tile0 > pos0 + AQ - 1 - p.window);
-            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};  // four chains: one warp per scheduler has only ILP
+            // this thread's half row of S, read from TMEM once and held in registers
+            float sv[SC];
 #pragma unroll
-            for (int c = 0; c < SC / 32; ++c) {
-                float v[32];
-                tmem_ld32(s_addr + 32 * c, v);
-                if (all_visible) {
+            for (int c = 0; c < SC / 32; ++c) tmem_ld32(s_addr + 32 * c, sv + 32 * c);
+            if (!all_visible) {
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], v[i]);
-                } else {
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        const int pos = col0 + 32 * c + i;
-                        mx4[i & 3] = fmaxf(mx4[i & 3], (pos <= qp && pos >= lo) ? v[i] : -INFINITY);
-                    }
+                for (int i = 0; i < SC; ++i) {
+                    const int pos = col0 + i;
+                    sv[i] = (pos <= qp && pos >= lo) ? sv[i] : -INFINITY;
                 }
             }
+            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};  // four chains: one warp per scheduler has only ILP
+#pragma unroll
+            for (int i = 0; i < SC; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], sv[i]);
             float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
             xchg[((j & 1) * 2 + half) * AQ + row] = mx;
             asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");
             mx = fmaxf(mx, xchg[((j & 1) * 2 + (half ^ 1)) * AQ + row]);
-            const float m_new = fmaxf(m_run, mx * scale_log2);
-            const float alpha = (m_run == -INFINITY) ? 0.f : ex2(m_run - m_new);
-            const float base = (m_new == -INFINITY) ? 0.f : m_new;
-            // P goes to buffer j & 1, last read by PV of tile j-2, whose completion this thread awaited
-            // before it consumed O'_{j-2} in the previous iteration.
+            // The maximum moves only when a tile exceeds it by more than LAZY_STEP: exponentials up to
+            // 2^LAZY_STEP are as exact in bfloat16 and float32 as those up to 1, and the accumulated O
+            // (in tensor memory) then needs rescaling for the first tiles of a row at most.
+            const float m_tile = mx * scale_log2;
+            float alpha = 1.f;
+            bool rescale = false;
+            if (m_tile > m_used + LAZY_STEP) {  // (false for a tile without a visible key: -inf)
+                if (m_used != -INFINITY) {
+                    alpha = ex2(m_used - m_tile);
+                    rescale = true;
+                }
+                m_used = m_tile;
+            }
+            const float base = (m_used == -INFINITY) ? 0.f : m_used;
+            // P goes to buffer j & 1, last read by PV of tile j-2
+            if (j >= 2) {
+                ok = mbar_wait(o_full0 + 8 * (j & 1), ((j - 2) >> 1) & 1, give_up);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+            }
             float sum4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
             for (int c = 0; c < SC / 32; ++c) {
-                float v[32];
-                tmem_ld32(s_addr + 32 * c, v);
+                float* v = sv + 32 * c;
+                // straight-line code, so that the 32 exponentials are in flight together; 2^-inf is exactly 0
 #pragma unroll
-                // straight-line code in both forms (selects, no branches), so that the 32 exponentials
-                // are in flight together; 2^-inf is exactly 0
-                if (all_visible) {
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) v[i] = ex2(fmaf(v[i], scale_log2, -base));
-                } else {
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        const int pos = col0 + 32 * c + i;
-                        const float x = fmaf(v[i], scale_log2, -base);
-                        v[i] = ex2((pos <= qp && pos >= lo) ? x : -INFINITY);
-                    }
-                }
+                for (int i = 0; i < 32; ++i) v[i] = ex2(fmaf(v[i], scale_log2, -base));
 #pragma unroll
                 for (int i = 0; i < 32; ++i) sum4[i & 3] += v[i];
 #pragma unroll
@@ -347,24 +368,26 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 }
             }
             l_run = l_run * alpha + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
-            m_run = m_new;
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // P is read by the tensor core's proxy
-            tc_fence_before();
-            asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(p_full) : "memory");
-            if (j > 0) {
-                // O'_{j-1}: PV of the previous tile ran while this tile's P was computed
+            if (__any_sync(0xffffffffu, rescale)) {
+                // O so far (tiles 0..j-1, all complete once PV of tile j-1 is) times alpha, row by row,
+                // before PV of this tile adds to it: the MMA warp waits for every thread's arrival below
                 ok = mbar_wait(o_full0 + 8 * ((j - 1) & 1), ((j - 1) >> 1) & 1, give_up);
+                ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
                 tc_fence_after();
-                const uint32_t o_addr = lane_addr + C::O_COL + ((j - 1) & 1) * HD + half * OC;
+                const uint32_t o_addr = lane_addr + C::O_COL + half * OC;
 #pragma unroll
                 for (int c = 0; c < OC / 32; ++c) {
                     float v[32];
                     tmem_ld32(o_addr + 32 * c, v);
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) o_acc[32 * c + i] = (o_acc[32 * c + i] + v[i]) * alpha;
+                    for (int i = 0; i < 32; ++i) v[i] *= alpha;
+                    tmem_st32(o_addr + 32 * c, v);
                 }
             }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // P is read by the tensor core's proxy
+            tc_fence_before();
+            asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(p_full) : "memory");
         }
         // the row's sum: both halves (a thread that gave up still meets its partner here)
         xchg[((ntiles & 1) * 2 + half) * AQ + row] = l_run;
@@ -373,7 +396,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         if (ok) ok = mbar_wait(o_full0 + 8 * ((ntiles - 1) & 1), ((ntiles - 1) >> 1) & 1, give_up);
         if (ok) {
             tc_fence_after();
-            const uint32_t o_addr = lane_addr + C::O_COL + ((ntiles - 1) & 1) * HD + half * OC;
+            const uint32_t o_addr = lane_addr + C::O_COL + half * OC;
             const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
             bf16* o = p.out + ((size_t)(row0 + q0 + row) * p.nh + h) * HD + half * OC;
 #pragma unroll
@@ -384,10 +407,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 #pragma unroll
                     for (int q4 = 0; q4 < 4; ++q4) {
                         uint4 w;
-                        w.x = pack2((o_acc[32 * c + 8 * q4 + 0] + v[8 * q4 + 0]) * inv, (o_acc[32 * c + 8 * q4 + 1] + v[8 * q4 + 1]) * inv);
-                        w.y = pack2((o_acc[32 * c + 8 * q4 + 2] + v[8 * q4 + 2]) * inv, (o_acc[32 * c + 8 * q4 + 3] + v[8 * q4 + 3]) * inv);
-                        w.z = pack2((o_acc[32 * c + 8 * q4 + 4] + v[8 * q4 + 4]) * inv, (o_acc[32 * c + 8 * q4 + 5] + v[8 * q4 + 5]) * inv);
-                        w.w = pack2((o_acc[32 * c + 8 * q4 + 6] + v[8 * q4 + 6]) * inv, (o_acc[32 * c + 8 * q4 + 7] + v[8 * q4 + 7]) * inv);
+                        w.x = pack2(v[8 * q4 + 0] * inv, v[8 * q4 + 1] * inv);
+                        w.y = pack2(v[8 * q4 + 2] * inv, v[8 * q4 + 3] * inv);
+                        w.z = pack2(v[8 * q4 + 4] * inv, v[8 * q4 + 5] * inv);
+                        w.w = pack2(v[8 * q4 + 6] * inv, v[8 * q4 + 7] * inv);
                         *reinterpret_cast<uint4*>(o + 32 * c + 8 * q4) = w;
                     }
                 }
