@@ -31,18 +31,25 @@
 // probabilities that are exactly zero; the cache pool is zero-initialised and only ever holds
 // finite values, so they cannot leak.  Every wait is bounded (CW_ST_WAIT_TIMEOUT in the status
 // words, then the kernel frees TMEM and returns).
+#include <type_traits>
 #include "tc_common.cuh"
 
 #define AQ 128  // query rows per CTA
 #define AK 128  // keys per tile
 #define A_THREADS 320  // TMA producer, MMA issuer, 8 softmax warps
 #define A_MAX_SMEM (227 * 1024)
+#define PREFILL_MAX_PARTS 8  // parts that a long row of keys may be cut into
 #define LAZY_STEP 8.0f  // log2 of how far a tile's maximum may exceed the one in use before the row is rescaled
 
 struct PrefillTcParams {
     bf16* out;
     const int* block_tables; const int* q_start; const int* ctx_lens;
     const int* item_seq; const int* item_q0;
+    // Long rows of keys cut into parts (or null: none is).  item_split[i] = (first item of i's group) << 8 |
+    // parts; the group's items are consecutive, item i being part i - first.  A part leaves its
+    // unnormalised O and (m, l) per row in part_o / part_ml (indexed by item and head) and counts itself
+    // in counters[first * nh + head] (zero between launches); the last one to arrive merges them all.
+    const int* item_split; float* part_o; float* part_ml; int* counters;
     int nh, nkv, page_size, page_shift, max_blocks, num_pages;
     float scale; int window;
     int* status;
@@ -143,6 +150,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     // bars: q_full, p_full, s_full[2], o_full[2], full[NSLOTS], empty[NSLOTS]
     uint32_t* tmem_slot = (uint32_t*)(bars + 6 + 2 * C::NSLOTS);
     volatile int* give_up = (volatile int*)(tmem_slot + 1);
+    volatile int* last_part = give_up + 1;
     float* xchg = (float*)(bars + 32);  // [2][2][128]: row maxima and, at the end, row sums (tile parity x half)
 
     // (the plain instructions, not the helpers: the helpers' timeline notes take static shared memory,
@@ -159,8 +167,19 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     const int nq = min(AQ, q_len - q0);          // query rows in this tile
     const int kv_hi = pos0 + nq;                 // keys [.., kv_hi) are visible to the last row
     const int kv_lo = p.window > 0 ? max(0, pos0 + 1 - p.window) : 0;
-    const int tile_lo = kv_lo / AK * AK;         // key tiles start at multiples of 128 whatever the portion
-    const int ntiles = (kv_hi - tile_lo + AK - 1) / AK;
+    int tile_lo = kv_lo / AK * AK;               // key tiles start at multiples of 128 whatever the portion
+    int ntiles = (kv_hi - tile_lo + AK - 1) / AK;
+    const int split_word = p.item_split != nullptr ? p.item_split[item] : (item << 8) | 1;
+    const int parts = split_word & 0xFF, first_item = split_word >> 8;
+    if (parts < 1 || parts > PREFILL_MAX_PARTS || first_item < 0 || first_item > item || item - first_item >= parts) {
+        if (threadIdx.x == 0) cw_report(p.status, CW_ST_SPLIT_RANGE, item, split_word);
+        return;
+    }
+    if (parts > 1) {  // this CTA's share of the tiles (it may be empty)
+        const int per = (ntiles + parts - 1) / parts, begin = (item - first_item) * per;
+        ntiles = max(0, min(ntiles, begin + per) - begin);
+        tile_lo += begin * AK;
+    }
 
     const uint32_t q_full = smem_u32(bars), p_full = smem_u32(bars + 1);
     const uint32_t s_full0 = smem_u32(bars + 2), o_full0 = smem_u32(bars + 4);
@@ -259,7 +278,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             umma_commit(s_full0 + 8 * (j & 1));
             return true;
         };
-        if (ok) ok = issue_s(0);
+        if (ok && ntiles > 0) ok = issue_s(0);
         for (int j = 0; j < ntiles && ok; ++j) {
             // S of the next tile first: it runs while the softmax warps work on this one.  Its buffer
             // was read for the last time before P of tile j-1 was announced.
@@ -393,27 +412,113 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         xchg[((ntiles & 1) * 2 + half) * AQ + row] = l_run;
         asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");
         l_run += xchg[((ntiles & 1) * 2 + (half ^ 1)) * AQ + row];
-        if (ok) ok = mbar_wait(o_full0 + 8 * ((ntiles - 1) & 1), ((ntiles - 1) >> 1) & 1, give_up);
-        if (ok) {
-            tc_fence_after();
-            const uint32_t o_addr = lane_addr + C::O_COL + half * OC;
-            const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-            bf16* o = p.out + ((size_t)(row0 + q0 + row) * p.nh + h) * HD + half * OC;
+        if (ok && ntiles > 0) ok = mbar_wait(o_full0 + 8 * ((ntiles - 1) & 1), ((ntiles - 1) >> 1) & 1, give_up);
+        ok = __all_sync(0xffffffffu, ok);
+        const uint32_t o_addr = lane_addr + C::O_COL + half * OC;
+        bf16* o = p.out + ((size_t)(row0 + q0 + row) * p.nh + h) * HD + half * OC;
+        if (parts == 1) {
+            if (ok) {
+                tc_fence_after();
+                const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+#pragma unroll
+                for (int c = 0; c < OC / 32; ++c) {
+                    float v[32];
+                    tmem_ld32(o_addr + 32 * c, v);
+                    if (row < nq) {
+#pragma unroll
+                        for (int q4 = 0; q4 < 4; ++q4) {
+                            uint4 w;
+                            w.x = pack2(v[8 * q4 + 0] * inv, v[8 * q4 + 1] * inv);
+                            w.y = pack2(v[8 * q4 + 2] * inv, v[8 * q4 + 3] * inv);
+                            w.z = pack2(v[8 * q4 + 4] * inv, v[8 * q4 + 5] * inv);
+                            w.w = pack2(v[8 * q4 + 6] * inv, v[8 * q4 + 7] * inv);
+                            *reinterpret_cast<uint4*>(o + 32 * c + 8 * q4) = w;
+                        }
+                    }
+                }
+            }
+        } else {
+            // ---- one part of a cut row of keys: leave (m, l, unnormalised O), the last part to arrive merges ----
+            // part_o is [item][head][column][row]: a warp's 32 rows lie side by side, so that its stores
+            // here and its loads in the merge are whole 128-byte lines
+            float* my_o = p.part_o + (((size_t)item * p.nh + h) * HD + half * OC) * AQ + row;
+            float* my_ml = p.part_ml + (((size_t)item * p.nh + h) * AQ + row) * 2;
+            if (ok && ntiles > 0) tc_fence_after();
 #pragma unroll
             for (int c = 0; c < OC / 32; ++c) {
                 float v[32];
-                tmem_ld32(o_addr + 32 * c, v);
-                if (row < nq) {
+                if (ok && ntiles > 0) {
+                    tmem_ld32(o_addr + 32 * c, v);
+                } else {
 #pragma unroll
-                    for (int q4 = 0; q4 < 4; ++q4) {
-                        uint4 w;
-                        w.x = pack2(v[8 * q4 + 0] * inv, v[8 * q4 + 1] * inv);
-                        w.y = pack2(v[8 * q4 + 2] * inv, v[8 * q4 + 3] * inv);
-                        w.z = pack2(v[8 * q4 + 4] * inv, v[8 * q4 + 5] * inv);
-                        w.w = pack2(v[8 * q4 + 6] * inv, v[8 * q4 + 7] * inv);
-                        *reinterpret_cast<uint4*>(o + 32 * c + 8 * q4) = w;
-                    }
+                    for (int i = 0; i < 32; ++i) v[i] = 0.f;
                 }
+#pragma unroll
+                for (int i = 0; i < 32; ++i) my_o[(32 * c + i) * AQ] = v[i];
+            }
+            if (half == 0) {
+                my_ml[0] = m_used;
+                my_ml[1] = l_run;
+            }
+            // Release / acquire through the counter: the barrier orders every thread's stores before
+            // thread 64's release, and its acquire before every thread's loads of the other parts.
+            asm volatile("bar.sync 5, 256;" ::: "memory");
+            if (tid == 64) {
+                int* counter = p.counters + (size_t)first_item * p.nh + h;
+                int prev;
+                asm volatile("atom.add.acq_rel.gpu.global.s32 %0, [%1], 1;" : "=r"(prev) : "l"(counter) : "memory");
+                *last_part = (prev == parts - 1);
+                if (prev == parts - 1) *counter = 0;  // ready for the next launch
+            }
+            asm volatile("bar.sync 5, 256;" ::: "memory");
+            if (*last_part && row < nq) {
+                // every load of a round is in flight before the first is used: the (m, l) of all parts,
+                // then O in rounds of 128 / KP columns of KP parts each (in part order whoever came last)
+                const size_t stride_o = (size_t)p.nh * AQ * HD, stride_ml = (size_t)p.nh * AQ * 2;
+                const float* ml0 = p.part_ml + (((size_t)first_item * p.nh + h) * AQ + row) * 2;
+                const float* o0 = p.part_o + (((size_t)first_item * p.nh + h) * HD + half * OC) * AQ + row;
+                float2 ml[PREFILL_MAX_PARTS];
+#pragma unroll
+                for (int k = 0; k < PREFILL_MAX_PARTS; ++k)
+                    ml[k] = k < parts ? *reinterpret_cast<const float2*>(ml0 + k * stride_ml) : make_float2(-INFINITY, 0.f);
+                float M = -INFINITY, L = 0.f, wk[PREFILL_MAX_PARTS];
+#pragma unroll
+                for (int k = 0; k < PREFILL_MAX_PARTS; ++k) M = fmaxf(M, ml[k].x);
+#pragma unroll
+                for (int k = 0; k < PREFILL_MAX_PARTS; ++k) {
+                    wk[k] = (ml[k].x == -INFINITY) ? 0.f : ex2(ml[k].x - M);
+                    L = fmaf(wk[k], ml[k].y, L);
+                }
+                const float inv = L > 0.f ? 1.f / L : 0.f;
+                auto merge = [&](auto kp_tag) {
+                    constexpr int KP = decltype(kp_tag)::value;              // parts unrolled (2, 4 or 8)
+                    constexpr int F = 128 / KP < OC ? 128 / KP : OC;         // columns per round
+#pragma unroll 1
+                    for (int c0 = 0; c0 < OC; c0 += F) {
+                        float v[KP][F];
+#pragma unroll
+                        for (int k = 0; k < KP; ++k)
+#pragma unroll
+                            for (int i = 0; i < F; ++i) v[k][i] = k < parts ? o0[k * stride_o + (size_t)(c0 + i) * AQ] : 0.f;
+#pragma unroll
+                        for (int i = 0; i < F; i += 8) {
+                            float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                            for (int k = 0; k < KP; ++k)
+#pragma unroll
+                                for (int e = 0; e < 8; ++e) acc[e] = fmaf(wk[k], v[k][i + e], acc[e]);
+                            uint4 w;
+                            w.x = pack2(acc[0] * inv, acc[1] * inv);
+                            w.y = pack2(acc[2] * inv, acc[3] * inv);
+                            w.z = pack2(acc[4] * inv, acc[5] * inv);
+                            w.w = pack2(acc[6] * inv, acc[7] * inv);
+                            *reinterpret_cast<uint4*>(o + c0 + i) = w;
+                        }
+                    }
+                };
+                if (parts <= 2) merge(std::integral_constant<int, 2>{});
+                else if (parts <= 4) merge(std::integral_constant<int, 4>{});
+                else merge(std::integral_constant<int, 8>{});
             }
         }
     }
@@ -442,19 +547,23 @@ static int launch_prefill_tc(const CUtensorMap& mq, const CUtensorMap& mk, const
 }
 
 // q: [q_rows, q_cols] rows of the flat batch (row stride q_stride, head h at columns h*hd..), out:
-// [q_rows, nh*hd]; item_seq/item_q0: one entry per 128 query rows of each request.  Takes head sizes
+// [q_rows, nh*hd]; item_seq/item_q0: one entry per 128 query rows of each request, or several (parts
+// of its keys, see PrefillTcParams::item_split; then part_o holds items * nh * 128 * hd floats, part_ml
+// items * nh * 256 and counters items * nh zeros, which the kernel leaves zero).  Takes head sizes
 // 64 and 128 and pages of 8..128 tokens (a power of two); CW_ERR_UNSUPPORTED otherwise, so that the
 // caller can use the mma.sync kernel.
 extern "C" int cw_attention_prefill_tc(const void* q, int q_stride, int q_cols, int q_rows, void* out,
                                        const void* k_cache, const void* v_cache, const int* block_tables,
                                        const int* q_start, const int* ctx_lens, const int* item_seq,
-                                       const int* item_q0, int items, int nh, int nkv, int hd, int page_size,
+                                       const int* item_q0, const int* item_split, float* part_o, float* part_ml,
+                                       int* counters, int items, int nh, int nkv, int hd, int page_size,
                                        int max_blocks, int num_pages, float scale, int window, int* status,
                                        cudaStream_t stream) {
     if (items == 0) return CW_OK;
     if (items < 0 || nh <= 0 || nkv <= 0 || nh % nkv != 0 || page_size <= 0 || max_blocks <= 0 || num_pages <= 0 ||
         q_rows <= 0 || q_cols < nh * hd)
         return CW_ERR_BAD_SIZE;
+    if (item_split != nullptr && (part_o == nullptr || part_ml == nullptr || counters == nullptr)) return CW_ERR_BAD_SIZE;
     if (hd != 64 && hd != 128) return CW_ERR_UNSUPPORTED;
     if ((page_size & (page_size - 1)) != 0 || page_size < 8 || page_size > AK) return CW_ERR_UNSUPPORTED;
     if (q_stride % 8 != 0 || ((uintptr_t)q & 15) || ((uintptr_t)k_cache & 15) || ((uintptr_t)v_cache & 15) ||
@@ -488,6 +597,7 @@ extern "C" int cw_attention_prefill_tc(const void* q, int q_stride, int q_cols, 
     p.out = (bf16*)out;
     p.block_tables = block_tables; p.q_start = q_start; p.ctx_lens = ctx_lens;
     p.item_seq = item_seq; p.item_q0 = item_q0;
+    p.item_split = item_split; p.part_o = part_o; p.part_ml = part_ml; p.counters = counters;
     p.nh = nh; p.nkv = nkv; p.page_size = page_size; p.page_shift = __builtin_ctz(page_size);
     p.max_blocks = max_blocks; p.num_pages = num_pages;
     p.scale = scale; p.window = window; p.status = status;

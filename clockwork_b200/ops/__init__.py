@@ -21,6 +21,7 @@ STATUS_MESSAGES = {
     4: "a device-side wait ran out (kernel {a}, stage {b})",
     5: "row index outside the batch (row {a}, index {b})",
     6: "shared memory of block {a} is not 1024-byte aligned (offset {b})",
+    7: "work item {a} names a cut of its keys that the kernel does not take (word {b})",
 }
 
 

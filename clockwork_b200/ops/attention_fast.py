@@ -41,7 +41,7 @@ def _configure() -> None:
     lib.cw_attention_decode_workspace.restype = c_int
     lib.cw_attention_prefill.argtypes = [P, I, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, I, P, P]
     lib.cw_attention_prefill.restype = c_int
-    lib.cw_attention_prefill_tc.argtypes = [P, I, I, I, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, I, P, P]
+    lib.cw_attention_prefill_tc.argtypes = [P, I, I, I, P, P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, I, P, P]
     lib.cw_attention_prefill_tc.restype = c_int
     _configured = True
 
@@ -175,23 +175,85 @@ def attention_decode(q, k_cache, v_cache, block_tables, ctx_lens, num_heads, num
     return out
 
 
-def _work_items(ctx) -> tuple[torch.Tensor, torch.Tensor, int]:
-    """(request index, first query row) per 128 query rows of each portion; built once per step and
-    shared by all layers."""
-    cached = ctx.extras.get("prefill_items")
+MIN_PART_KEYS = 4 * QUERY_TILE  # no part of a cut row of keys is shorter than this (a cut costs about three tiles' time)
+MAX_PARTS = 8                   # (the kernel's limit)
+
+
+def prefill_work_items(q_lens, ctx_lens, num_heads: int = 0, sm_count: int = 0) -> tuple[list[int], list[int], list[int]]:
+    """Work items of a step's portions: (request index, first query row, split word) per 128 query rows,
+    longest first (CTAs are handed to SMs in this order, so the short ones fill the tail).
+
+    With ``num_heads`` and ``sm_count`` given, a step whose tiles x heads leave SMs idle has the keys
+    of its longest tiles cut into parts, each walked by a CTA of its own and merged by the last to
+    finish: the tile with the most keys per part gets one more part until the CTAs fill the SMs once
+    (a CTA costs several microseconds besides its keys, so a second round of CTAs would cost more
+    than it saves).  A part's item repeats its tile's (request, row); the split word is
+    (index of the tile's first item) << 8 | parts."""
+    groups = []  # [keys the tile's last row sees, request, first row, parts]
+    for s, (n, c) in enumerate(zip(q_lens, ctx_lens)):
+        for q0 in range(0, n, QUERY_TILE):
+            groups.append([c - n + min(q0 + QUERY_TILE, n), s, q0, 1])
+    if num_heads > 0 and sm_count > 0 and groups:
+        room = sm_count // num_heads - len(groups)  # items that can be added within one round of CTAs
+        while room > 0:
+            g = max(groups, key=lambda g: g[0] / g[3])
+            if g[3] >= MAX_PARTS or g[0] / (g[3] + 1) < MIN_PART_KEYS:
+                break
+            g[3] += 1
+            room -= 1
+    groups.sort(key=lambda g: -(g[0] / g[3]))
+    seqs, q0s, words = [], [], []
+    for _, s, q0, parts in groups:
+        first = len(seqs)
+        for _ in range(parts):
+            seqs.append(s)
+            q0s.append(q0)
+            words.append(first << 8 | parts)
+    return seqs, q0s, words
+
+
+_cut_long_rows = True
+
+
+def set_cut_long_rows(on: bool) -> None:
+    """Steps with few work items cut long rows of keys into parts by default; ``False`` gives every query
+    tile one CTA (for measurements)."""
+    global _cut_long_rows
+    _cut_long_rows = bool(on)
+
+
+def _work_items(ctx, num_heads: int) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor | None, int]:
+    """The step's work items on the device; built once per step and head count (``num_heads`` 0: no
+    cuts) and shared by the layers."""
+    key = ("prefill_items", num_heads)
+    cached = ctx.extras.get(key)
     if cached is None:
-        items = []
-        for s, (n, c) in enumerate(zip(ctx.q_lens_host, ctx.ctx_lens_host)):
-            for q0 in range(0, n, QUERY_TILE):
-                items.append((c - n + min(q0 + QUERY_TILE, n), s, q0))  # keys the tile's last row sees
-        # longest first: CTAs are handed to SMs in this order, so the short ones fill the tail
-        items.sort(key=lambda it: -it[0])
-        seqs, q0s = [it[1] for it in items], [it[2] for it in items]
-        host = torch.from_numpy(np.array([seqs, q0s], dtype=np.int32))
+        seqs, q0s, words = prefill_work_items(ctx.q_lens_host, ctx.ctx_lens_host, num_heads, _sm_count(ctx.device) if num_heads else 0)
+        cut = any(w & 0xFF != 1 for w in words)
+        host = torch.from_numpy(np.array([seqs, q0s, words], dtype=np.int32))
         dev = host.to(ctx.device, non_blocking=False)
-        cached = (dev[0].contiguous(), dev[1].contiguous(), len(seqs))
-        ctx.extras["prefill_items"] = cached
+        cached = (dev[0].contiguous(), dev[1].contiguous(), dev[2].contiguous() if cut else None, len(seqs))
+        ctx.extras[key] = cached
     return cached
+
+
+_prefill_scratch_by_device: dict[int, dict] = {}
+
+
+def _prefill_scratch(device: torch.device, items: int, num_heads: int, head_dim: int) -> dict:
+    """Partial results of cut work items (float32 O, (m, l) per row) and their arrival counters, kept
+    per device and grown when a step needs more; the counters are zero between launches."""
+    index = device.index if device.index is not None else torch.cuda.current_device()
+    slots = items * num_heads
+    st = _prefill_scratch_by_device.get(index)
+    if st is None or st["part_o"].numel() < slots * QUERY_TILE * head_dim or st["counters"].numel() < slots:
+        st = {
+            "part_o": torch.empty(slots * QUERY_TILE * head_dim, dtype=torch.float32, device=device),
+            "part_ml": torch.empty(slots * QUERY_TILE * 2, dtype=torch.float32, device=device),
+            "counters": torch.zeros(slots, dtype=torch.int32, device=device),
+        }
+        _prefill_scratch_by_device[index] = st
+    return st
 
 
 class _Prefill:
@@ -201,16 +263,20 @@ class _Prefill:
 
     @staticmethod
     def run(ctx, qkv, view, num_heads, num_kv_heads, head_dim, scale, window) -> torch.Tensor:
-        item_seq, item_q0, items = _work_items(ctx)
+        item_seq, item_q0, item_split, items = _work_items(
+            ctx, num_heads if _cut_long_rows and prefill_tc_takes(head_dim, view.k_cache.shape[1]) else 0)
         return attention_prefill(qkv, view.k_cache, view.v_cache, view.block_tables, ctx.q_start, ctx.ctx_lens,
-                                 item_seq, item_q0, items, num_heads, num_kv_heads, head_dim, scale, window, ctx.status)
+                                 item_seq, item_q0, items, num_heads, num_kv_heads, head_dim, scale, window, ctx.status,
+                                 item_split=item_split)
 
 
 def attention_prefill(q, k_cache, v_cache, block_tables, q_start, ctx_lens, item_seq, item_q0, items, num_heads,
-                      num_kv_heads, head_dim, scale, window, status, use_tc: bool | None = None) -> torch.Tensor:
+                      num_kv_heads, head_dim, scale, window, status, use_tc: bool | None = None,
+                      item_split: torch.Tensor | None = None) -> torch.Tensor:
     """Any mixture of portions: ``q`` [N, >= nh*hd]; request s owns rows q_start[s]:q_start[s+1] and has
     ctx_lens[s] tokens in the cache, its portion at the end.  Returns [N, nh*hd].  ``use_tc``: the
-    tcgen05 kernel (default: whenever it takes the head size and the page size) or the mma.sync one."""
+    tcgen05 kernel (default: whenever it takes the head size and the page size) or the mma.sync one.
+    ``item_split`` (tcgen05 kernel only): the split words of ``prefill_work_items`` when items are parts."""
     _configure()
     if q.dtype != torch.bfloat16 or q.dim() != 2 or q.stride(1) != 1:
         raise ValueError("q must be a 2-d bfloat16 tensor with unit column stride")
@@ -224,10 +290,17 @@ def attention_prefill(q, k_cache, v_cache, block_tables, q_start, ctx_lens, item
     out = torch.empty((q.shape[0], num_heads * head_dim), dtype=torch.bfloat16, device=q.device)
     if use_tc is None:
         use_tc = prefill_tc_takes(head_dim, k_cache.shape[1])
+    if item_split is not None and not use_tc:
+        raise ValueError("only the tcgen05 kernel takes work items that are parts")
     if use_tc:
+        st = {"part_o": None, "part_ml": None, "counters": None}
+        if item_split is not None:
+            _need(item_split, torch.int32, "item_split", 1)
+            st = _prefill_scratch(q.device, items, num_heads, head_dim)
         check(library().cw_attention_prefill_tc(
             _ptr(q), q.stride(0), q.shape[1], q.shape[0], _ptr(out), _ptr(k_cache), _ptr(v_cache), _ptr(block_tables),
-            _ptr(q_start), _ptr(ctx_lens), _ptr(item_seq), _ptr(item_q0), items, num_heads, num_kv_heads, head_dim,
+            _ptr(q_start), _ptr(ctx_lens), _ptr(item_seq), _ptr(item_q0), _ptr(item_split), _ptr(st["part_o"]),
+            _ptr(st["part_ml"]), _ptr(st["counters"]), items, num_heads, num_kv_heads, head_dim,
             k_cache.shape[1], block_tables.shape[1], k_cache.shape[0], float(scale), int(window or 0), _ptr(status),
             _stream()), "attention_prefill_tc")
         return out

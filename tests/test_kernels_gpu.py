@@ -544,6 +544,66 @@ def test_attention_prefill_kernel_mixed_batch(ops, status, fast, kernel, nh, nkv
         row += q.shape[0]
 
 
+@pytest.mark.parametrize("nh,nkv,hd,ps,window", [(12, 2, 128, 16, None), (3, 1, 64, 32, None), (4, 2, 128, 8, 200)])
+def test_attention_prefill_cuts_long_rows_of_keys(ops, status, fast, nh, nkv, hd, ps, window):
+    """Query tiles with long rows of keys can be walked by several CTAs, whose partial results the
+    last one merges: the same values as uncut, the same bits on every run (the counters return to
+    zero), parts without a visible key (a window) included; and one far key that outweighs all
+    others is found from whichever part holds it."""
+    ctx_lens, q_lens = [2500, 1100, 3000, 4200, 600], [300, 1100, 1, 129, 600]
+    dtype = torch.bfloat16
+    k_cache, v_cache, tables, ks, vs = paged_setup(ctx_lens, nkv, hd, ps, dtype, seed=15)
+    scale = hd**-0.5
+    g = torch.Generator().manual_seed(16)
+    qs = [(torch.randn(q, nh, hd, generator=g) * 2).to(dtype).float() for q in q_lens]
+    # request 3: key 70 (in the first part of every tile's keys) scores far above the rest for head 0
+    kc = k_cache.float()
+    page, off = int(tables[3, 70 // ps]), 70 % ps
+    kc[page, off, 0, :] = 0.0
+    kc[page, off, 0, 3] = 24.0
+    qs[3][:, 0, :] = 0.0
+    qs[3][:, 0, 3] = 24.0
+    ks[3][70, 0, :] = kc[page, off, 0, :]
+    n = sum(q_lens)
+    wide = torch.zeros(n, (nh + 2 * nkv) * hd)
+    wide[:, : nh * hd] = torch.cat(qs).view(n, nh * hd)
+    q_start = torch.tensor([0] + torch.tensor(q_lens).cumsum(0).tolist(), dtype=torch.int32)
+
+    def run(split):
+        seqs, q0s, words = fast.prefill_work_items(q_lens, ctx_lens, nh if split else 0, 148 * 4)  # (room for many parts)
+        assert (max(w & 0xFF for w in words) > 3) == split
+        dev = lambda x: torch.tensor(x, dtype=torch.int32, device=DEV)  # noqa: E731
+        out = fast.attention_prefill(wide.to(dtype).to(DEV), kc.to(dtype).to(DEV), v_cache.to(DEV), tables.to(DEV), q_start.to(DEV),
+                                     dev(ctx_lens), dev(seqs), dev(q0s), len(seqs), nh, nkv, hd, scale, window, status,
+                                     item_split=dev(words) if split else None)
+        ops.raise_on_status(status)
+        return out
+
+    cut, again, whole = run(True), run(True), run(False)
+    assert torch.equal(cut, again)
+    torch.testing.assert_close(cut.float(), whole.float(), rtol=2e-2, atol=2e-2)
+    out = cut.float().cpu().view(n, nh, hd)
+    row = 0
+    for i, (q, k, v) in enumerate(zip(qs, ks, vs)):
+        want = plain.causal_attention(q, k, v, scale, window=window)
+        torch.testing.assert_close(out[row : row + q.shape[0]], want, rtol=2e-2, atol=2e-2,
+                                   msg=lambda m: f"request {i} (context {ctx_lens[i]}, {q_lens[i]} queries): {m}")
+        if i == 3 and window is None:
+            torch.testing.assert_close(out[row : row + q.shape[0], 0], vs[3][70, 0].expand(q.shape[0], hd), rtol=2e-2, atol=2e-2)
+        row += q.shape[0]
+
+
+def test_attention_prefill_refuses_a_bad_cut(ops, status, fast):
+    nh, nkv, hd, ps = 2, 1, 64, 16
+    k_cache, v_cache, tables, _, _ = paged_setup([200], nkv, hd, ps, torch.bfloat16, seed=1)
+    wide = torch.zeros(200, (nh + 2) * hd, dtype=torch.bfloat16, device=DEV)
+    dev = lambda x: torch.tensor(x, dtype=torch.int32, device=DEV)  # noqa: E731
+    fast.attention_prefill(wide, k_cache.to(DEV), v_cache.to(DEV), tables.to(DEV), dev([0, 200]), dev([200]), dev([0, 0]),
+                           dev([0, 128]), 2, nh, nkv, hd, 1.0, None, status, item_split=dev([0 << 8 | 1, 1 << 8 | 9]))
+    with pytest.raises(RuntimeError, match="cut of its keys"):
+        ops.raise_on_status(status)
+
+
 @pytest.mark.parametrize("hd,n", [(32, 150), (64, 150), (128, 300)])
 def test_attention_prefill_sees_the_diagonal_and_nothing_after_it(ops, status, fast, hd, n):
     """Each query's own key carries a score that stands out, so each output must be its own value;
