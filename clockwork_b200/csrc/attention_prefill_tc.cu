@@ -155,8 +155,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 
     // (the plain instructions, not the helpers: the helpers' timeline notes take static shared memory,
     // which would push the 1024-byte aligned dynamic part over the limit)
+    // Work items, portion bounds, context lengths and block tables are inputs of the step, written
+    // before its first kernel; only q and the newest keys and values come from the preceding kernels.
+    // So everything up to the first TMA load runs while the preceding kernel finishes, and only the
+    // producer warp, whose loads are the kernel's only reads of that data, waits for it.
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    asm volatile("griddepcontrol.wait;" ::: "memory");
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int h = blockIdx.x, item = blockIdx.y;
     const int s = p.item_seq[item], q0 = p.item_q0[item];
@@ -209,10 +212,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         // ---- TMA producer: Q once, then K_0, V_0, K_1, V_1, ... into the slot ring --------------------
         // Lane i fetches page i of a tile: it reads the page's number from the block table one tile
         // ahead (so that the read's latency is hidden) and issues that page's copies itself.
-        if (lane == 0) {
-            mbar_expect_tx(q_full, C::Q_BYTES);
-            for (int cb = 0; cb < C::CB; ++cb)
-                tma_load_2d(smem_u32(q_s + cb * C::BLOCK_BYTES), &map_q, h * HD + cb * 64, row0 + q0, q_full);
+        if (lane < 3) {
+            const CUtensorMap* m = lane == 0 ? &map_q : (lane == 1 ? &map_k : &map_v);
+            asm volatile("prefetch.tensormap [%0];" ::"l"(m) : "memory");
         }
         const int* table = p.block_tables + (size_t)s * p.max_blocks;
         const int pages_per_tile = AK >> p.page_shift;  // at most 16
@@ -223,6 +225,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             return (lane < pages_per_tile && pos < kv_hi && blk < p.max_blocks) ? table[blk] : 0;
         };
         int page_next = page_of(tile_lo);
+        asm volatile("griddepcontrol.wait;" ::: "memory");
+        if (lane == 0) {
+            mbar_expect_tx(q_full, C::Q_BYTES);
+            for (int cb = 0; cb < C::CB; ++cb)
+                tma_load_2d(smem_u32(q_s + cb * C::BLOCK_BYTES), &map_q, h * HD + cb * 64, row0 + q0, q_full);
+        }
         int t = 0;
         bool ok = true;
         for (int j = 0; j < ntiles && ok; ++j) {

@@ -478,8 +478,10 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
     uint32_t* tmem_slot = (uint32_t*)(bars + 2 * C::STAGES + 4);
     volatile int* give_up = (volatile int*)(tmem_slot + 1);
 
+    // Only the activations come from the preceding kernel, and only the producer thread reads them
+    // (everything else follows from its copies): it alone waits for that kernel, after the set-up and
+    // after the weight tiles of the first stages have gone out.
     pdl_launch_dependents();
-    pdl_wait();
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + C::STAGES);
     const uint32_t accf0 = smem_u32(bars + 2 * C::STAGES), acce0 = smem_u32(bars + 2 * C::STAGES + 2);
@@ -509,11 +511,33 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
 
     if (warp == 0 && lane == 0) {
         // ---- TMA producer: runs ahead over tiles, bounded by the ring only ----------------------------
-        int i = 0;  // k-blocks issued so far (over all tiles)
+        const int my_tiles = (int)blockIdx.x < tiles ? (tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
+        const int total = my_tiles * p.num_kb;  // k-blocks of all this CTA's tiles, in order
+        const int early = min(total, C::STAGES);
+        int i = 0;
         bool ok = true;
-        for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
+        // the first stages: weight tiles before the wait, their activation tiles after it
+        for (int phase = 0; phase < 2; ++phase) {
+            if (phase == 1) pdl_wait();
+            for (i = 0; i < early; ++i) {
+                const int ts = i / p.num_kb, kb = i - ts * p.num_kb, tile = blockIdx.x + ts * gridDim.x;
+                const int m0 = (tile % m_tiles) * BM, n0 = (tile / m_tiles) * bn;
+                const uint32_t a_dst = smem_u32(smem + i * C::STAGE_BYTES);
+                const uint32_t bar = full0 + 8 * i;
+                if (phase == 0) {
+                    mbar_expect_tx(bar, stage_tx);
+                    tma_load_2d(a_dst, &map_w, kb * BK, m0, bar);
+                    if (SWIGLU) tma_load_2d(a_dst + C::A_BYTES, &map_w2, kb * BK, m0, bar);
+                } else {
+                    tma_load_2d(a_dst + C::A_BYTES * (SWIGLU ? 2 : 1), &map_x, kb * BK, n0, bar);
+                }
+            }
+        }
+        // the rest runs ahead over tiles, bounded by the ring only
+        int kb = early % p.num_kb;
+        for (int tile = blockIdx.x + (early / p.num_kb) * gridDim.x; tile < tiles && ok; tile += gridDim.x, kb = 0) {
             const int m0 = (tile % m_tiles) * BM, n0 = (tile / m_tiles) * bn;
-            for (int kb = 0; kb < p.num_kb; ++kb, ++i) {
+            for (; kb < p.num_kb; ++kb, ++i) {
                 const int s = i % C::STAGES;
                 ok = mbar_wait(empty0 + 8 * s, ((i / C::STAGES) & 1) ^ 1, give_up);
                 if (!ok) break;
@@ -536,6 +560,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
         }
     } else if (warp == 1 && lane == 0) {
         // ---- MMA issuer: tile `it` accumulates into TMEM buffer it & 1 -------------------------------
+        pdl_wait();  // (nothing to do before the producer's activations arrive; parked here a thread polls no barrier)
         const uint32_t idesc = instr_desc(BM, bn);
         int i = 0, it = 0;
         bool ok = true;
@@ -566,6 +591,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
         }
     } else if (warp >= 2) {
         // ---- epilogue warps: warp w reads TMEM lanes 32 (w % 4) .. +31 -------------------------------
+        pdl_wait();
         const int quarter = warp & 3;
         const int row = quarter * 32 + lane;
         const int etid = tid - 64;  // 0..127 among the epilogue threads

@@ -84,8 +84,10 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     uint32_t* tmem_slot = (uint32_t*)(bars + 2 * C::STAGES + 4);
     volatile int* give_up = (volatile int*)(tmem_slot + 1);
 
+    // Only the activations come from the preceding kernel, and only the producer threads read them
+    // (everything else follows from their copies): they alone wait for it, after the set-up and after
+    // the weight tiles of the first stages have gone out.
     pdl_launch_dependents();
-    pdl_wait();
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const uint32_t rank = cluster_rank();  // 0: the leader, which issues the MMAs
     const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + C::STAGES);
@@ -117,12 +119,34 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     if (warp == 0 && lane == 0) {
         // ---- TMA producer (both CTAs): own rows of W, own half of the token tile ------------------------
         const uint32_t stage_tx = C::A_BYTES + half_bn * BK * 2;
-        int i = 0;
+        const int my_tiles = pair < tiles ? (tiles - pair + pairs - 1) / pairs : 0;
+        const int total = my_tiles * p.num_kb;  // k-blocks of all this pair's tiles, in order
+        const int early = min(total, C::STAGES);
         bool ok = true;
-        for (int tile = pair; tile < tiles && ok; tile += pairs) {
+        int i = 0;
+        // the first stages: weight tiles before the wait, their activation tiles after it
+        for (int phase = 0; phase < 2; ++phase) {
+            if (phase == 1) pdl_wait();
+            for (i = 0; i < early; ++i) {
+                const int ts = i / p.num_kb, kb = i - ts * p.num_kb, tile = pair + ts * pairs;
+                const int m0 = (tile % m_tiles) * 2 * BM + (int)rank * BM;
+                const int n0 = (tile / m_tiles) * bn + (int)rank * half_bn;
+                const uint32_t a_dst = smem_u32(smem + i * C::STAGE_BYTES);
+                const uint32_t bar = dsmem_addr(full0 + 8 * i, 0);  // the leader's barrier
+                if (phase == 0) {
+                    mbar_expect_tx_cluster(bar, stage_tx);
+                    tma_load_2d_pair(a_dst, &map_w, kb * BK, m0, bar);
+                } else {
+                    tma_load_2d_pair(a_dst + C::A_BYTES, &map_x, kb * BK, n0, bar);
+                }
+            }
+        }
+        // the rest runs ahead over tiles, bounded by the ring only
+        int kb = early % p.num_kb;
+        for (int tile = pair + (early / p.num_kb) * pairs; tile < tiles && ok; tile += pairs, kb = 0) {
             const int m0 = (tile % m_tiles) * 2 * BM + (int)rank * BM;
             const int n0 = (tile / m_tiles) * bn + (int)rank * half_bn;
-            for (int kb = 0; kb < p.num_kb; ++kb, ++i) {
+            for (; kb < p.num_kb; ++kb, ++i) {
                 const int s = i % C::STAGES;
                 ok = mbar_wait(empty0 + 8 * s, ((i / C::STAGES) & 1) ^ 1, give_up);
                 if (!ok) break;
@@ -142,6 +166,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         }
     } else if (warp == 1 && lane == 0 && rank == 0) {
         // ---- MMA issuer (leader only): tile `it` accumulates into TMEM buffer it & 1 of both CTAs ---------
+        pdl_wait();  // (parked here a thread polls no barrier)
         const uint32_t idesc = instr_desc(2 * BM, bn);
         int i = 0, it = 0;
         bool ok = true;
@@ -168,6 +193,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         }
     } else if (warp >= 2) {
         // ---- epilogue warps (both CTAs): warp w reads TMEM lanes 32 (w % 4) .. +31 of its own CTA --------
+        pdl_wait();
         const int quarter = warp & 3;
         const int row = quarter * 32 + lane;
         const int etid = tid - 64;
