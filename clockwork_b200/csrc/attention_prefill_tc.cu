@@ -15,11 +15,14 @@
 // and the row sum rescaled, which after the first tiles of a row hardly ever happens; the result
 // is the same sum, since numerator and denominator carry the same factor.
 //
-// S is double buffered in TMEM (2 x 128 columns, O after them) and P in shared memory, so that the
-// MMAs of tile j+1 and the loads of later tiles run while the softmax warps work on tile j.  K and V
-// tiles share one ring of shared-memory slots.  Warps (320 threads): 0 TMA producer, 1 MMA issuer and
-// TMEM owner, 2..9 softmax (warp w owns TMEM lanes 32 (w % 4) .. +31; two warps share a lane quarter
-// and split the columns).
+// The tiles alternate between two sets of softmax warps, each with its own S buffer and O
+// accumulator in TMEM (2 x 128 + 2 x HD columns), P buffer in shared memory and row statistics: two
+// independent online softmaxes over the even and the odd tiles, merged at the end like the parts of
+// a cut row.  One set's exponentials (the MUFU pipe) run beside the other's passes over S, the MMAs
+// of both and the loads of later tiles.  K and V tiles share one ring of shared-memory slots, filled
+// in the order the MMA warp takes them (scores two tiles ahead of probabilities).  Warps (576
+// threads): 0 TMA producer, 1 MMA issuer and TMEM owner, 2..9 and 10..17 the softmax sets (warp w owns
+// TMEM lanes 32 (w % 4) .. +31; two warps of a set share a lane quarter and split the columns).
 //
 // Reference: clockwork/kernels/attention.py:68-96 (gather the context through one block table, then
 // dense causal attention with the query aligned to the end of the context, :45-65) and
@@ -36,7 +39,7 @@
 
 #define AQ 128  // query rows per CTA
 #define AK 128  // keys per tile
-#define A_THREADS 320  // TMA producer, MMA issuer, 8 softmax warps
+#define A_THREADS 576  // TMA producer, MMA issuer, two sets of 8 softmax warps
 #define A_MAX_SMEM (227 * 1024)
 #define PREFILL_MAX_PARTS 8  // parts that a long row of keys may be cut into
 #define LAZY_STEP 8.0f  // log2 of how far a tile's maximum may exceed the one in use before the row is rescaled
@@ -66,10 +69,10 @@ struct ACfg {
     static constexpr int FIT = (A_MAX_SMEM - TAIL_BYTES - Q_BYTES - 2 * P_BYTES) / SLOT_BYTES;
     static constexpr int NSLOTS = FIT > 8 ? 8 : FIT;
     static constexpr int SMEM_BYTES = Q_BYTES + 2 * P_BYTES + NSLOTS * SLOT_BYTES + TAIL_BYTES;
-    static constexpr int O_COL = 2 * AK;                 // S buffers at columns 0 and 128, O' after them
+    static constexpr int O_COL = 2 * AK;                 // S buffers at columns 0 and 128, the two O accumulators after them
     static constexpr int TMEM_COLS = 512;
     static_assert(NSLOTS >= 4, "too few key/value slots");
-    static_assert(O_COL + HD <= TMEM_COLS, "accumulators do not fit in tensor memory");
+    static_assert(O_COL + 2 * HD <= TMEM_COLS, "accumulators do not fit in tensor memory");
 };
 
 __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int x, int y, int z, uint32_t bar) {
@@ -126,13 +129,46 @@ __device__ __forceinline__ float ex2(float x) {
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const float* v) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+        ::"r"(taddr), "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])),
+          "r"(__float_as_uint(v[3])), "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])),
+          "r"(__float_as_uint(v[7])), "r"(__float_as_uint(v[8])), "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])),
+          "r"(__float_as_uint(v[11])), "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])),
+          "r"(__float_as_uint(v[15]))
+        : "memory");
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+// This lane's row of an accumulator in tensor memory times alpha (rare: a rolled loop over 16 columns
+// at a time, so that it takes few registers from the softmax loop around it).
+template <int COLS>
+__device__ __forceinline__ void rescale_o(uint32_t taddr, float alpha) {
+#pragma unroll 1
+    for (int c = 0; c < COLS; c += 16) {
+        float v[16];
+        tmem_ld16(taddr + c, v);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) v[i] *= alpha;
+        tmem_st16(taddr + c, v);
+    }
+}
+// A named barrier of n threads that also tells every one of them whether all came with `pred` true.
+__device__ __forceinline__ bool bar_and(int id, int n, bool pred) {
+    uint32_t all;
+    asm volatile("{ .reg .pred p, q; setp.ne.u32 q, %3, 0; bar.red.and.pred p, %1, %2, q; selp.u32 %0, 1, 0, p; }"
+                 : "=r"(all)
+                 : "r"(id), "r"(n), "r"((uint32_t)pred)
+                 : "memory");
+    return all != 0;
+}
 __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
 template <int HD>
-__global__ void __launch_bounds__(A_THREADS)
+__global__ void __launch_bounds__(A_THREADS, 1)  // (18 warps: five on one scheduler, whose 16,384 registers allow 96 per thread)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                        const __grid_constant__ CUtensorMap map_v, const PrefillTcParams p) {
     using C = ACfg<HD>;
@@ -147,14 +183,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     uint8_t* p_s = q_s + C::Q_BYTES;
     uint8_t* slots = p_s + 2 * C::P_BYTES;
     uint64_t* bars = (uint64_t*)(slots + C::NSLOTS * C::SLOT_BYTES);
-    // bars: q_full, p_full, s_full[2], o_full[2], full[NSLOTS], empty[NSLOTS]
-    uint32_t* tmem_slot = (uint32_t*)(bars + 6 + 2 * C::NSLOTS);
+    // bars: q_full, -, s_full[2], o_full[2], p_full[2], s_free[2], full[NSLOTS], empty[NSLOTS]
+    uint32_t* tmem_slot = (uint32_t*)(bars + 10 + 2 * C::NSLOTS);
     volatile int* give_up = (volatile int*)(tmem_slot + 1);
     volatile int* last_part = give_up + 1;
-    float* xchg = (float*)(bars + 32);  // [2][2][128]: row maxima and, at the end, row sums (tile parity x half)
+    float* xchg = (float*)(bars + 32);   // [2 sets][2 halves][128]: row maxima and, at the end, row sums and set 1's (m, l)
 
-    // (the plain instructions, not the helpers: the helpers' timeline notes take static shared memory,
-    // which would push the 1024-byte aligned dynamic part over the limit)
     // Work items, portion bounds, context lengths and block tables are inputs of the step, written
     // before its first kernel; only q and the newest keys and values come from the preceding kernels.
     // So everything up to the first TMA load runs while the preceding kernel finishes, and only the
@@ -184,15 +218,17 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         tile_lo += begin * AK;
     }
 
-    const uint32_t q_full = smem_u32(bars), p_full = smem_u32(bars + 1);
+    const uint32_t q_full = smem_u32(bars);
     const uint32_t s_full0 = smem_u32(bars + 2), o_full0 = smem_u32(bars + 4);
-    const uint32_t full0 = smem_u32(bars + 6), empty0 = smem_u32(bars + 6 + C::NSLOTS);
+    const uint32_t p_full0 = smem_u32(bars + 6), s_free0 = smem_u32(bars + 8);
+    const uint32_t full0 = smem_u32(bars + 10), empty0 = smem_u32(bars + 10 + C::NSLOTS);
     if (tid == 0) {
         mbar_init(q_full, 1);
-        mbar_init(p_full, 256);
         for (int b = 0; b < 2; ++b) {
             mbar_init(s_full0 + 8 * b, 1);
             mbar_init(o_full0 + 8 * b, 1);
+            mbar_init(p_full0 + 8 * b, 256);
+            mbar_init(s_free0 + 8 * b, 256);
         }
         for (int i = 0; i < C::NSLOTS; ++i) {
             mbar_init(full0 + 8 * i, 1);
@@ -209,22 +245,23 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     const uint32_t tmem_base = *tmem_slot;
 
     if (warp == 0) {
-        // ---- TMA producer: Q once, then K_0, V_0, K_1, V_1, ... into the slot ring --------------------
-        // Lane i fetches page i of a tile: it reads the page's number from the block table one tile
-        // ahead (so that the read's latency is hidden) and issues that page's copies itself.
+        // ---- TMA producer: Q once, then K and V tiles in the order the MMA warp takes them ------------
+        // K_0, K_1, then (K_{j+2}, V_j) for every tile j: the scores run two tiles ahead of the
+        // probabilities.  Lane i fetches page i of a tile: it reads the page's number from the block
+        // table ahead of its use (so that the read's latency is hidden) and issues that page's copies itself.
         if (lane < 3) {
             const CUtensorMap* m = lane == 0 ? &map_q : (lane == 1 ? &map_k : &map_v);
             asm volatile("prefetch.tensormap [%0];" ::"l"(m) : "memory");
         }
         const int* table = p.block_tables + (size_t)s * p.max_blocks;
         const int pages_per_tile = AK >> p.page_shift;  // at most 16
-        auto page_of = [&](int tile0) -> int {
+        auto page_of = [&](int j) -> int {
             // slots past the context: any finite data will do, their probabilities are zero
-            const int pos = tile0 + lane * p.page_size;
+            const int pos = tile_lo + j * AK + lane * p.page_size;
             const int blk = pos >> p.page_shift;
-            return (lane < pages_per_tile && pos < kv_hi && blk < p.max_blocks) ? table[blk] : 0;
+            return (j < ntiles && lane < pages_per_tile && pos < kv_hi && blk < p.max_blocks) ? table[blk] : 0;
         };
-        int page_next = page_of(tile_lo);
+        int pg_v = page_of(0), pg_1 = page_of(1), pg_2 = page_of(2);  // this lane's page of tiles j, j+1, j+2
         asm volatile("griddepcontrol.wait;" ::: "memory");
         if (lane == 0) {
             mbar_expect_tx(q_full, C::Q_BYTES);
@@ -232,30 +269,37 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 tma_load_2d(smem_u32(q_s + cb * C::BLOCK_BYTES), &map_q, h * HD + cb * 64, row0 + q0, q_full);
         }
         int t = 0;
-        bool ok = true;
-        for (int j = 0; j < ntiles && ok; ++j) {
-            const int tile0 = tile_lo + j * AK;
-            int page = page_next;
-            if (j + 1 < ntiles) page_next = page_of(tile0 + AK);
+        auto load = [&](int page, bool is_v) -> bool {
             if (page < 0 || page >= p.num_pages) {
                 cw_report(p.status, CW_ST_PAGE_RANGE, s, page);
                 page = 0;
             }
-            for (int kv = 0; kv < 2; ++kv, ++t) {
-                const int slot = t % C::NSLOTS;
-                ok = mbar_wait(empty0 + 8 * slot, ((t / C::NSLOTS) & 1) ^ 1, give_up);
-                ok = __all_sync(0xffffffffu, ok);
-                if (!ok) break;
-                const uint32_t bar = full0 + 8 * slot;
-                const uint32_t dst0 = smem_u32(slots + slot * C::SLOT_BYTES);
-                if (lane == 0) mbar_expect_tx(bar, C::SLOT_BYTES);
-                __syncwarp();
-                if (lane < pages_per_tile) {
-                    for (int cb = 0; cb < C::CB; ++cb)
-                        tma_load_3d(dst0 + cb * C::BLOCK_BYTES + lane * p.page_size * 128, kv ? &map_v : &map_k, cb * 64, kvh,
-                                    page * p.page_size, bar);
-                }
+            const int slot = t % C::NSLOTS;
+            bool ok = mbar_wait(empty0 + 8 * slot, ((t / C::NSLOTS) & 1) ^ 1, give_up);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) return false;
+            const uint32_t bar = full0 + 8 * slot;
+            const uint32_t dst0 = smem_u32(slots + slot * C::SLOT_BYTES);
+            if (lane == 0) mbar_expect_tx(bar, C::SLOT_BYTES);
+            __syncwarp();
+            if (lane < pages_per_tile) {
+                for (int cb = 0; cb < C::CB; ++cb)
+                    tma_load_3d(dst0 + cb * C::BLOCK_BYTES + lane * p.page_size * 128, is_v ? &map_v : &map_k, cb * 64, kvh,
+                                page * p.page_size, bar);
             }
+            ++t;
+            return true;
+        };
+        bool ok = true;
+        if (ntiles > 0) ok = load(pg_v, false);
+        if (ok && ntiles > 1) ok = load(pg_1, false);
+        for (int j = 0; j < ntiles && ok; ++j) {
+            const int pg_3 = page_of(j + 3);
+            if (j + 2 < ntiles) ok = load(pg_2, false);
+            if (ok) ok = load(pg_v, true);
+            pg_v = pg_1;
+            pg_1 = pg_2;
+            pg_2 = pg_3;
         }
         if (*give_up && lane == 0) {
             // wait, bounded, for the copies still in flight before the CTA's shared memory goes away
@@ -271,8 +315,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         constexpr uint32_t idesc_s = instr_desc(AQ, AK);
         constexpr uint32_t idesc_o = instr_desc(AQ, HD) | (1u << 16);  // B (= V) is MN-major
         bool ok = mbar_wait(q_full, 0, give_up);
+        int t = 0;  // K/V tiles taken so far, in the producer's order
         auto issue_s = [&](int j) -> bool {
-            const int t = 2 * j, slot = t % C::NSLOTS;
+            const int slot = t % C::NSLOTS;
             if (!mbar_wait(full0 + 8 * slot, (t / C::NSLOTS) & 1, give_up)) return false;
             tc_fence_after();
             const uint32_t k_addr = smem_u32(slots + slot * C::SLOT_BYTES);
@@ -284,17 +329,23 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             }
             umma_commit(empty0 + 8 * slot);       // K_j may be overwritten when these have read it
             umma_commit(s_full0 + 8 * (j & 1));
+            ++t;
             return true;
         };
         if (ok && ntiles > 0) ok = issue_s(0);
+        if (ok && ntiles > 1) ok = issue_s(1);
         for (int j = 0; j < ntiles && ok; ++j) {
-            // S of the next tile first: it runs while the softmax warps work on this one.  Its buffer
-            // was read for the last time before P of tile j-1 was announced.
-            if (j + 1 < ntiles) ok = issue_s(j + 1);
+            if (j + 2 < ntiles) {
+                // S of tile j+2 goes where S of tile j was, as soon as that tile's set holds it in registers
+                ok = mbar_wait(s_free0 + 8 * (j & 1), (j >> 1) & 1, give_up);
+                if (!ok) break;
+                tc_fence_after();
+                ok = issue_s(j + 2);
+                if (!ok) break;
+            }
+            ok = mbar_wait(p_full0 + 8 * (j & 1), (j >> 1) & 1, give_up);
             if (!ok) break;
-            ok = mbar_wait(p_full, j & 1, give_up);
-            if (!ok) break;
-            const int t = 2 * j + 1, slot = t % C::NSLOTS;
+            const int slot = t % C::NSLOTS;
             ok = mbar_wait(full0 + 8 * slot, (t / C::NSLOTS) & 1, give_up);
             if (!ok) break;
             tc_fence_after();
@@ -303,18 +354,23 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             for (int kk = 0; kk < AK / 16; ++kk) {
                 const uint64_t a = smem_desc_sw128(smem_u32(p_s) + (j & 1) * C::P_BYTES + (kk / 4) * C::BLOCK_BYTES) + 2 * (kk % 4);
                 const uint64_t b = smem_desc_mn_sw128(v_addr + kk * 16 * 128, C::BLOCK_BYTES);
-                umma_bf16(tmem_base + C::O_COL, a, b, idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
+                umma_bf16(tmem_base + C::O_COL + (j & 1) * HD, a, b, idesc_o, (j >= 2 || kk > 0) ? 1u : 0u);
             }
             umma_commit(empty0 + 8 * slot);
-            umma_commit(o_full0 + 8 * (j & 1));   // O holds tiles 0..j and P buffer j & 1 may be overwritten
+            umma_commit(o_full0 + 8 * (j & 1));   // O of this set holds its tiles up to j and its P buffer may be overwritten
+            ++t;
         }
     } else if (warp >= 2) {
-        // ---- softmax warps: two threads per query row, each with half of the row's columns -----------
-        // Warps w and w + 4 own the same 32 TMEM lanes; `half` says which half of S's 128 columns and of
-        // O's HD columns a thread works on.  The two exchange their partial row maxima through shared
-        // memory once per tile; sums stay partial until the end.
+        // ---- softmax warps: two sets, each with two threads per query row ------------------------------
+        // Set 0 (warps 2..9) takes the even tiles, set 1 (warps 10..17) the odd ones, each with its own S
+        // buffer, P buffer, O accumulator and row statistics (two independent online softmaxes, merged
+        // at the end), so that one set's exponentials run beside the other's passes over S.  Within a
+        // set, warps w and w + 4 own the same 32 TMEM lanes; `half` says which half of S's 128 columns
+        // and of O's HD columns a thread works on.  The two exchange their partial row maxima through
+        // shared memory once per tile; sums stay partial until the end.
+        const int set = (warp - 2) >> 3;
         const int quarter = warp & 3;
-        const int half = (warp - 2) >> 2;
+        const int half = ((warp - 2) & 7) >> 2;
         const int row = quarter * 32 + lane;
         constexpr int SC = AK / 2;   // S columns per thread
         constexpr int OC = HD / 2;   // O columns per thread
@@ -322,37 +378,44 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         const int qp = pos0 + row;                                     // this row's position
         const int lo = p.window > 0 ? max(0, qp + 1 - p.window) : 0;   // its first visible key
         const float scale_log2 = p.scale * 1.4426950408889634f;        // softmax in base 2
-        const int pair_bar = 1 + quarter;                              // named barrier of the 64 threads of a quarter
+        const int pair_bar = 1 + 4 * set + quarter;                    // named barrier of the 64 threads of a quarter
+        float* my_x = xchg + (2 * set + half) * AQ + row;              // where the partner reads this thread's value
+        float* partner_x = xchg + (2 * set + (half ^ 1)) * AQ + row;
+        const uint32_t s_addr = lane_addr + set * AK + half * SC;
+        const uint32_t o_set = lane_addr + C::O_COL + set * HD + half * OC;
         float m_used = -INFINITY, l_run = 0.f;  // m_used: the maximum this row's exponentials are taken against
         bool ok = true;
-        for (int j = 0; j < ntiles; ++j) {
+        for (int j = set; j < ntiles; j += 2) {
             const int tile0 = tile_lo + j * AK;
             const int col0 = tile0 + half * SC;  // position of this thread's first key
-            ok = mbar_wait(s_full0 + 8 * (j & 1), (j >> 1) & 1, give_up);
+            ok = mbar_wait(s_full0 + 8 * set, (j >> 1) & 1, give_up);
             ok = __all_sync(0xffffffffu, ok);  // one decision per warp: the TMEM accesses below are warp-wide
-            if (!ok) break;
-            tc_fence_after();
-            const uint32_t s_addr = lane_addr + (j & 1) * AK + half * SC;
             // tiles wholly visible to all 128 rows skip the per-element test
             const bool all_visible = tile0 + AK - 1 <= pos0 && (p.window <= 0 || tile0 > pos0 + AQ - 1 - p.window);
             // this thread's half row of S, read from TMEM once and held in registers
             float sv[SC];
+            if (ok) {
+                tc_fence_after();
 #pragma unroll
-            for (int c = 0; c < SC / 32; ++c) tmem_ld32(s_addr + 32 * c, sv + 32 * c);
-            if (!all_visible) {
+                for (int c = 0; c < SC / 32; ++c) tmem_ld32(s_addr + 32 * c, sv + 32 * c);
+                tc_fence_before();
+                asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(s_free0 + 8 * set) : "memory");
+                if (!all_visible) {
 #pragma unroll
-                for (int i = 0; i < SC; ++i) {
-                    const int pos = col0 + i;
-                    sv[i] = (pos <= qp && pos >= lo) ? sv[i] : -INFINITY;
+                    for (int i = 0; i < SC; ++i) {
+                        const int pos = col0 + i;
+                        sv[i] = (pos <= qp && pos >= lo) ? sv[i] : -INFINITY;
+                    }
                 }
-            }
-            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};  // four chains: one warp per scheduler has only ILP
+                float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};  // four chains: ILP for the few warps of a scheduler
 #pragma unroll
-            for (int i = 0; i < SC; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], sv[i]);
-            float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-            xchg[((j & 1) * 2 + half) * AQ + row] = mx;
-            asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");
-            mx = fmaxf(mx, xchg[((j & 1) * 2 + (half ^ 1)) * AQ + row]);
+                for (int i = 0; i < SC; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], sv[i]);
+                *my_x = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+            }
+            // (both threads of a row take every decision to leave together: their barriers stay paired)
+            ok = bar_and(pair_bar, 64, ok);
+            if (!ok) break;
+            const float mx = fmaxf(*my_x, *partner_x);
             // The maximum moves only when a tile exceeds it by more than LAZY_STEP: exponentials up to
             // 2^LAZY_STEP are as exact in bfloat16 and float32 as those up to 1, and the accumulated O
             // (in tensor memory) then needs rescaling for the first tiles of a row at most.
@@ -367,12 +430,14 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 m_used = m_tile;
             }
             const float base = (m_used == -INFINITY) ? 0.f : m_used;
-            // P goes to buffer j & 1, last read by PV of tile j-2
+            // P goes to this set's buffer, last read by PV of the set's previous tile; when that is
+            // complete, O of the set is at rest as well (for the rescaling below)
             if (j >= 2) {
-                ok = mbar_wait(o_full0 + 8 * (j & 1), ((j - 2) >> 1) & 1, give_up);
+                ok = mbar_wait(o_full0 + 8 * set, ((j - 2) >> 1) & 1, give_up);
                 ok = __all_sync(0xffffffffu, ok);
-                if (!ok) break;
             }
+            ok = bar_and(pair_bar, 64, ok);  // (also: the partner has read this thread's maximum)
+            if (!ok) break;
             float sum4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
             for (int c = 0; c < SC / 32; ++c) {
@@ -387,7 +452,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                     // 8 keys = one 16-byte chunk of this row in the K-major, 128-byte-swizzled P tile;
                     // this thread's 64 keys are the 64-key block `half`
                     const int chunk = 4 * c + q4;
-                    const uint32_t addr = smem_u32(p_s) + (j & 1) * C::P_BYTES + half * C::BLOCK_BYTES + row * 128 + (((chunk & 7) ^ (row & 7)) << 4);
+                    const uint32_t addr = smem_u32(p_s) + set * C::P_BYTES + half * C::BLOCK_BYTES + row * 128 + (((chunk & 7) ^ (row & 7)) << 4);
                     asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr),
                                  "r"(pack2(v[8 * q4], v[8 * q4 + 1])), "r"(pack2(v[8 * q4 + 2], v[8 * q4 + 3])),
                                  "r"(pack2(v[8 * q4 + 4], v[8 * q4 + 5])), "r"(pack2(v[8 * q4 + 6], v[8 * q4 + 7]))
@@ -396,137 +461,165 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             }
             l_run = l_run * alpha + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
             if (__any_sync(0xffffffffu, rescale)) {
-                // O so far (tiles 0..j-1, all complete once PV of tile j-1 is) times alpha, row by row,
-                // before PV of this tile adds to it: the MMA warp waits for every thread's arrival below
-                ok = mbar_wait(o_full0 + 8 * ((j - 1) & 1), ((j - 1) >> 1) & 1, give_up);
-                ok = __all_sync(0xffffffffu, ok);
-                if (!ok) break;
+                // O of this set so far times alpha, row by row, before PV of this tile adds to it: the
+                // MMA warp waits for every thread's arrival below
                 tc_fence_after();
-                const uint32_t o_addr = lane_addr + C::O_COL + half * OC;
-#pragma unroll
-                for (int c = 0; c < OC / 32; ++c) {
-                    float v[32];
-                    tmem_ld32(o_addr + 32 * c, v);
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) v[i] *= alpha;
-                    tmem_st32(o_addr + 32 * c, v);
-                }
+                rescale_o<OC>(o_set, alpha);
             }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // P is read by the tensor core's proxy
             tc_fence_before();
-            asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(p_full) : "memory");
+            asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(p_full0 + 8 * set) : "memory");
         }
-        // the row's sum: both halves (a thread that gave up still meets its partner here)
-        xchg[((ntiles & 1) * 2 + half) * AQ + row] = l_run;
+        // ---- the row's sum over both halves; every thread comes here, whatever happened above ----------
+        *my_x = l_run;
         asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");
-        l_run += xchg[((ntiles & 1) * 2 + (half ^ 1)) * AQ + row];
-        if (ok && ntiles > 0) ok = mbar_wait(o_full0 + 8 * ((ntiles - 1) & 1), ((ntiles - 1) >> 1) & 1, give_up);
-        ok = __all_sync(0xffffffffu, ok);
-        const uint32_t o_addr = lane_addr + C::O_COL + half * OC;
-        bf16* o = p.out + ((size_t)(row0 + q0 + row) * p.nh + h) * HD + half * OC;
-        if (parts == 1) {
-            if (ok) {
-                tc_fence_after();
-                const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-#pragma unroll
-                for (int c = 0; c < OC / 32; ++c) {
-                    float v[32];
-                    tmem_ld32(o_addr + 32 * c, v);
-                    if (row < nq) {
-#pragma unroll
-                        for (int q4 = 0; q4 < 4; ++q4) {
-                            uint4 w;
-                            w.x = pack2(v[8 * q4 + 0] * inv, v[8 * q4 + 1] * inv);
-                            w.y = pack2(v[8 * q4 + 2] * inv, v[8 * q4 + 3] * inv);
-                            w.z = pack2(v[8 * q4 + 4] * inv, v[8 * q4 + 5] * inv);
-                            w.w = pack2(v[8 * q4 + 6] * inv, v[8 * q4 + 7] * inv);
-                            *reinterpret_cast<uint4*>(o + 32 * c + 8 * q4) = w;
-                        }
-                    }
-                }
-            }
-        } else {
-            // ---- one part of a cut row of keys: leave (m, l, unnormalised O), the last part to arrive merges ----
-            // part_o is [item][head][column][row]: a warp's 32 rows lie side by side, so that its stores
-            // here and its loads in the merge are whole 128-byte lines
-            float* my_o = p.part_o + (((size_t)item * p.nh + h) * HD + half * OC) * AQ + row;
-            float* my_ml = p.part_ml + (((size_t)item * p.nh + h) * AQ + row) * 2;
-            if (ok && ntiles > 0) tc_fence_after();
-#pragma unroll
-            for (int c = 0; c < OC / 32; ++c) {
-                float v[32];
-                if (ok && ntiles > 0) {
-                    tmem_ld32(o_addr + 32 * c, v);
+        l_run += *partner_x;
+        asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");
+        // this set's last PV
+        const int my_tiles = ntiles > set ? (ntiles - set + 1) / 2 : 0;
+        if (ok && my_tiles > 0) {
+            ok = mbar_wait(o_full0 + 8 * set, (my_tiles - 1) & 1, give_up);
+            ok = __all_sync(0xffffffffu, ok);
+        }
+        // ---- the two sets merge: set 1 leaves (m, l) per row, set 0 reads both accumulators -------------
+        // (in the two exchange slots of set 1's own row, at rest after the pair's barriers above)
+        float* set1_m = xchg + 2 * AQ + row;
+        float* set1_l = xchg + 3 * AQ + row;
+        if (set == 1 && half == 0) {
+            *set1_m = m_used;
+            *set1_l = l_run;
+        }
+        tc_fence_before();
+        ok = bar_and(9, 512, ok);
+        if (set == 0) {
+            tc_fence_after();
+            const float m1 = *set1_m, l1 = *set1_l;
+            const float M = fmaxf(m_used, m1);
+            const float w0 = (m_used == -INFINITY) ? 0.f : ex2(m_used - M);
+            const float w1 = (m1 == -INFINITY) ? 0.f : ex2(m1 - M);
+            const float L = w0 * l_run + w1 * l1;
+            const uint32_t o_addr0 = lane_addr + C::O_COL + half * OC, o_addr1 = o_addr0 + HD;
+            // a half row of the merged, unnormalised O, 32 columns at a time (an accumulator that no tile went into is not read)
+            auto merged = [&](int c, float* v) {
+                float u[32];
+                if (ntiles > 0) {
+                    tmem_ld32(o_addr0 + 32 * c, v);
                 } else {
 #pragma unroll
                     for (int i = 0; i < 32; ++i) v[i] = 0.f;
                 }
+                if (ntiles > 1) {
+                    tmem_ld32(o_addr1 + 32 * c, u);
 #pragma unroll
-                for (int i = 0; i < 32; ++i) my_o[(32 * c + i) * AQ] = v[i];
-            }
-            if (half == 0) {
-                my_ml[0] = m_used;
-                my_ml[1] = l_run;
-            }
-            // Release / acquire through the counter: the barrier orders every thread's stores before
-            // thread 64's release, and its acquire before every thread's loads of the other parts.
-            asm volatile("bar.sync 5, 256;" ::: "memory");
-            if (tid == 64) {
-                int* counter = p.counters + (size_t)first_item * p.nh + h;
-                int prev;
-                asm volatile("atom.add.acq_rel.gpu.global.s32 %0, [%1], 1;" : "=r"(prev) : "l"(counter) : "memory");
-                *last_part = (prev == parts - 1);
-                if (prev == parts - 1) *counter = 0;  // ready for the next launch
-            }
-            asm volatile("bar.sync 5, 256;" ::: "memory");
-            if (*last_part && row < nq) {
-                // every load of a round is in flight before the first is used: the (m, l) of all parts,
-                // then O in rounds of 128 / KP columns of KP parts each (in part order whoever came last)
-                const size_t stride_o = (size_t)p.nh * AQ * HD, stride_ml = (size_t)p.nh * AQ * 2;
-                const float* ml0 = p.part_ml + (((size_t)first_item * p.nh + h) * AQ + row) * 2;
-                const float* o0 = p.part_o + (((size_t)first_item * p.nh + h) * HD + half * OC) * AQ + row;
-                float2 ml[PREFILL_MAX_PARTS];
+                    for (int i = 0; i < 32; ++i) v[i] = fmaf(w1, u[i], w0 * v[i]);
+                } else {
 #pragma unroll
-                for (int k = 0; k < PREFILL_MAX_PARTS; ++k)
-                    ml[k] = k < parts ? *reinterpret_cast<const float2*>(ml0 + k * stride_ml) : make_float2(-INFINITY, 0.f);
-                float M = -INFINITY, L = 0.f, wk[PREFILL_MAX_PARTS];
-#pragma unroll
-                for (int k = 0; k < PREFILL_MAX_PARTS; ++k) M = fmaxf(M, ml[k].x);
-#pragma unroll
-                for (int k = 0; k < PREFILL_MAX_PARTS; ++k) {
-                    wk[k] = (ml[k].x == -INFINITY) ? 0.f : ex2(ml[k].x - M);
-                    L = fmaf(wk[k], ml[k].y, L);
+                    for (int i = 0; i < 32; ++i) v[i] *= w0;
                 }
-                const float inv = L > 0.f ? 1.f / L : 0.f;
-                auto merge = [&](auto kp_tag) {
-                    constexpr int KP = decltype(kp_tag)::value;              // parts unrolled (2, 4 or 8)
-                    constexpr int F = 128 / KP < OC ? 128 / KP : OC;         // columns per round
+            };
+            bf16* o = p.out + ((size_t)(row0 + q0 + row) * p.nh + h) * HD + half * OC;
+            if (parts == 1) {
+                if (ok) {
+                    const float inv = L > 0.f ? 1.f / L : 0.f;
+#pragma unroll
+                    for (int c = 0; c < OC / 32; ++c) {
+                        float v[32];
+                        merged(c, v);
+                        if (row < nq) {
+#pragma unroll
+                            for (int q4 = 0; q4 < 4; ++q4) {
+                                uint4 w;
+                                w.x = pack2(v[8 * q4 + 0] * inv, v[8 * q4 + 1] * inv);
+                                w.y = pack2(v[8 * q4 + 2] * inv, v[8 * q4 + 3] * inv);
+                                w.z = pack2(v[8 * q4 + 4] * inv, v[8 * q4 + 5] * inv);
+                                w.w = pack2(v[8 * q4 + 6] * inv, v[8 * q4 + 7] * inv);
+                                *reinterpret_cast<uint4*>(o + 32 * c + 8 * q4) = w;
+                            }
+                        }
+                    }
+                }
+            } else {
+                // ---- one part of a cut row of keys: leave (m, l, unnormalised O), the last part to arrive merges ----
+                // part_o is [item][head][column][row]: a warp's 32 rows lie side by side, so that its stores
+                // here and its loads in the merge are whole 128-byte lines
+                float* my_o = p.part_o + (((size_t)item * p.nh + h) * HD + half * OC) * AQ + row;
+                float* my_ml = p.part_ml + (((size_t)item * p.nh + h) * AQ + row) * 2;
+#pragma unroll
+                for (int c = 0; c < OC / 32; ++c) {
+                    float v[32];
+                    if (ok) {
+                        merged(c, v);
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) v[i] = 0.f;
+                    }
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) my_o[(32 * c + i) * AQ] = v[i];
+                }
+                if (half == 0) {
+                    my_ml[0] = M;
+                    my_ml[1] = L;
+                }
+                // Release / acquire through the counter: the barrier orders every thread's stores before
+                // thread 64's release, and its acquire before every thread's loads of the other parts.
+                asm volatile("bar.sync 10, 256;" ::: "memory");
+                if (tid == 64) {
+                    int* counter = p.counters + (size_t)first_item * p.nh + h;
+                    int prev;
+                    asm volatile("atom.add.acq_rel.gpu.global.s32 %0, [%1], 1;" : "=r"(prev) : "l"(counter) : "memory");
+                    *last_part = (prev == parts - 1);
+                    if (prev == parts - 1) *counter = 0;  // ready for the next launch
+                }
+                asm volatile("bar.sync 10, 256;" ::: "memory");
+                if (*last_part && row < nq) {
+                    // every load of a round is in flight before the first is used: the (m, l) of all parts,
+                    // then O in rounds of 16 or 8 columns of KP parts each (in part order whoever came last)
+                    const size_t stride_o = (size_t)p.nh * AQ * HD, stride_ml = (size_t)p.nh * AQ * 2;
+                    const float* ml0 = p.part_ml + (((size_t)first_item * p.nh + h) * AQ + row) * 2;
+                    const float* o0 = p.part_o + (((size_t)first_item * p.nh + h) * HD + half * OC) * AQ + row;
+                    float2 ml[PREFILL_MAX_PARTS];
+#pragma unroll
+                    for (int k = 0; k < PREFILL_MAX_PARTS; ++k)
+                        ml[k] = k < parts ? *reinterpret_cast<const float2*>(ml0 + k * stride_ml) : make_float2(-INFINITY, 0.f);
+                    float Mp = -INFINITY, Lp = 0.f, wk[PREFILL_MAX_PARTS];
+#pragma unroll
+                    for (int k = 0; k < PREFILL_MAX_PARTS; ++k) Mp = fmaxf(Mp, ml[k].x);
+#pragma unroll
+                    for (int k = 0; k < PREFILL_MAX_PARTS; ++k) {
+                        wk[k] = (ml[k].x == -INFINITY) ? 0.f : ex2(ml[k].x - Mp);
+                        Lp = fmaf(wk[k], ml[k].y, Lp);
+                    }
+                    const float inv = Lp > 0.f ? 1.f / Lp : 0.f;
+                    auto merge = [&](auto kp_tag) {
+                        constexpr int KP = decltype(kp_tag)::value;            // parts unrolled (2, 4 or 8)
+                        constexpr int F = KP >= 4 ? 8 : 16;                    // columns per round
 #pragma unroll 1
-                    for (int c0 = 0; c0 < OC; c0 += F) {
-                        float v[KP][F];
-#pragma unroll
-                        for (int k = 0; k < KP; ++k)
-#pragma unroll
-                            for (int i = 0; i < F; ++i) v[k][i] = k < parts ? o0[k * stride_o + (size_t)(c0 + i) * AQ] : 0.f;
-#pragma unroll
-                        for (int i = 0; i < F; i += 8) {
-                            float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+                        for (int c0 = 0; c0 < OC; c0 += F) {
+                            float v[KP][F];
 #pragma unroll
                             for (int k = 0; k < KP; ++k)
 #pragma unroll
-                                for (int e = 0; e < 8; ++e) acc[e] = fmaf(wk[k], v[k][i + e], acc[e]);
-                            uint4 w;
-                            w.x = pack2(acc[0] * inv, acc[1] * inv);
-                            w.y = pack2(acc[2] * inv, acc[3] * inv);
-                            w.z = pack2(acc[4] * inv, acc[5] * inv);
-                            w.w = pack2(acc[6] * inv, acc[7] * inv);
-                            *reinterpret_cast<uint4*>(o + c0 + i) = w;
+                                for (int i = 0; i < F; ++i) v[k][i] = k < parts ? o0[k * stride_o + (size_t)(c0 + i) * AQ] : 0.f;
+#pragma unroll
+                            for (int i = 0; i < F; i += 8) {
+                                float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                                for (int k = 0; k < KP; ++k)
+#pragma unroll
+                                    for (int e = 0; e < 8; ++e) acc[e] = fmaf(wk[k], v[k][i + e], acc[e]);
+                                uint4 w;
+                                w.x = pack2(acc[0] * inv, acc[1] * inv);
+                                w.y = pack2(acc[2] * inv, acc[3] * inv);
+                                w.z = pack2(acc[4] * inv, acc[5] * inv);
+                                w.w = pack2(acc[6] * inv, acc[7] * inv);
+                                *reinterpret_cast<uint4*>(o + c0 + i) = w;
+                            }
                         }
-                    }
-                };
-                if (parts <= 2) merge(std::integral_constant<int, 2>{});
-                else if (parts <= 4) merge(std::integral_constant<int, 4>{});
-                else merge(std::integral_constant<int, 8>{});
+                    };
+                    if (parts <= 2) merge(std::integral_constant<int, 2>{});
+                    else if (parts <= 4) merge(std::integral_constant<int, 4>{});
+                    else merge(std::integral_constant<int, 8>{});
+                }
             }
         }
     }
