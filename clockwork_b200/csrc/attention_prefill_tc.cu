@@ -2,7 +2,11 @@
 //
 // A CTA owns 128 query tokens of one request and one query head (the 128 lanes of tensor memory)
 // and walks the request's keys in tiles of 128 tokens, fetched page by page from the cache by TMA
-// through the block table.  Per tile:
+// through the block table: one copy per page for K and one for V, whatever the page size, through
+// tensor maps of rank 5 and 4 that view the cache so that a page lands in the order the MMA
+// descriptors can walk (K: [8 tokens][64-column block][8 x 128 bytes], the groups of 8 keys of a block
+// at one stride over the whole tile; V: [page][block][token][128 bytes], each MMA taking 16 keys of
+// one page).  Per tile:
 //
 //     S  = Q K^T           tcgen05.mma, Q and K both K-major in shared memory, S in TMEM
 //     P  = 2^(S c - m)     softmax warps: two threads per query row read its half row of S from TMEM
@@ -75,10 +79,26 @@ struct ACfg {
     static_assert(O_COL + 2 * HD <= TMEM_COLS, "accumulators do not fit in tensor memory");
 };
 
-__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int x, int y, int z, uint32_t bar) {
+__device__ __forceinline__ void tma_load_5d(uint32_t dst, const CUtensorMap* map, int x, int y, int z, int w, int v, uint32_t bar) {
     asm volatile(
-        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
-        ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y), "r"(z)
+        "cp.async.bulk.tensor.5d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y), "r"(z), "r"(w), "r"(v)
+        : "memory");
+}
+// K-major operand, 128-byte swizzle, with the groups of 8 rows `group_bytes` apart (tc_common's form has 1024).
+__device__ __forceinline__ uint64_t smem_desc_sw128_groups(uint32_t addr, uint32_t group_bytes) {
+    uint64_t d = 0;
+    d |= (uint64_t)((addr >> 4) & 0x3FFF);
+    d |= (uint64_t)1 << 16;
+    d |= (uint64_t)((group_bytes >> 4) & 0x3FFF) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, int x, int y, int z, int w, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y), "r"(z), "r"(w)
         : "memory");
 }
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float* v) {
@@ -113,13 +133,13 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const float* v) {
     asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
 // Descriptor of an MN-major operand with the 128-byte swizzle: rows of the K dimension are 128 bytes
-// (64 contiguous elements of the MN dimension), groups of 8 rows are 1024 bytes apart (stride byte
+// (64 contiguous elements of the MN dimension), groups of 8 rows are `group_bytes` apart (stride byte
 // offset) and the next 64 elements of the MN dimension lie `mn_block_bytes` further (leading byte offset).
-__device__ __forceinline__ uint64_t smem_desc_mn_sw128(uint32_t addr, uint32_t mn_block_bytes) {
+__device__ __forceinline__ uint64_t smem_desc_mn_sw128(uint32_t addr, uint32_t mn_block_bytes, uint32_t group_bytes) {
     uint64_t d = 0;
     d |= (uint64_t)((addr >> 4) & 0x3FFF);
     d |= (uint64_t)((mn_block_bytes >> 4) & 0x3FFF) << 16;
-    d |= (uint64_t)(1024 >> 4) << 32;
+    d |= (uint64_t)((group_bytes >> 4) & 0x3FFF) << 32;
     d |= (uint64_t)1 << 46;
     d |= (uint64_t)2 << 61;
     return d;
@@ -283,9 +303,14 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             if (lane == 0) mbar_expect_tx(bar, C::SLOT_BYTES);
             __syncwarp();
             if (lane < pages_per_tile) {
-                for (int cb = 0; cb < C::CB; ++cb)
-                    tma_load_3d(dst0 + cb * C::BLOCK_BYTES + lane * p.page_size * 128, is_v ? &map_v : &map_k, cb * 64, kvh,
-                                page * p.page_size, bar);
+                if (is_v) {
+                    // a V tile lies page by page, [page][64-column block][token][128 bytes]: one copy per page
+                    tma_load_4d(dst0 + lane * C::CB * p.page_size * 128, &map_v, 0, page * p.page_size, 0, kvh, bar);
+                } else {
+                    // a K tile lies [8 tokens][64-column block][8 x 128 bytes]: the MMA wants the groups of 8
+                    // keys of a block at one stride over all 128 keys; one copy per page here too
+                    tma_load_5d(dst0 + lane * C::CB * p.page_size * 128, &map_k, 0, 0, 0, page * (p.page_size >> 3), kvh, bar);
+                }
             }
             ++t;
             return true;
@@ -324,7 +349,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 #pragma unroll
             for (int ks = 0; ks < HD / 16; ++ks) {
                 const uint64_t a = smem_desc_sw128(smem_u32(q_s) + (ks / 4) * C::BLOCK_BYTES) + 2 * (ks % 4);
-                const uint64_t b = smem_desc_sw128(k_addr + (ks / 4) * C::BLOCK_BYTES) + 2 * (ks % 4);
+                const uint64_t b = smem_desc_sw128_groups(k_addr + (ks / 4) * 1024, C::CB * 1024) + 2 * (ks % 4);
                 umma_bf16(tmem_base + (j & 1) * AK, a, b, idesc_s, ks > 0 ? 1u : 0u);
             }
             umma_commit(empty0 + 8 * slot);       // K_j may be overwritten when these have read it
@@ -353,7 +378,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 #pragma unroll
             for (int kk = 0; kk < AK / 16; ++kk) {
                 const uint64_t a = smem_desc_sw128(smem_u32(p_s) + (j & 1) * C::P_BYTES + (kk / 4) * C::BLOCK_BYTES) + 2 * (kk % 4);
-                const uint64_t b = smem_desc_mn_sw128(v_addr + kk * 16 * 128, C::BLOCK_BYTES);
+                // keys 16 kk .. +15: rows r .. r+15 of page pg (pages of 8 tokens: both groups of 8 are whole pages)
+                const int pg = (16 * kk) >> p.page_shift, r = (16 * kk) & (p.page_size - 1);
+                const uint64_t b = smem_desc_mn_sw128(v_addr + (pg * C::CB * p.page_size + r) * 128, p.page_size * 128,
+                                                      p.page_size >= 16 ? 1024 : C::CB * 1024);
                 umma_bf16(tmem_base + C::O_COL + (j & 1) * HD, a, b, idesc_o, (j >= 2 || kk > 0) ? 1u : 0u);
             }
             umma_commit(empty0 + 8 * slot);
@@ -683,15 +711,29 @@ extern "C" int cw_attention_prefill_tc(const void* q, int q_stride, int q_cols, 
                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
             return CW_ERR_UNSUPPORTED;
     }
-    for (int kv = 0; kv < 2; ++kv) {
-        // the cache as [slot][kv head][hd]: a box is one page of one head, 64 elements wide
-        const cuuint64_t dims[3] = {(cuuint64_t)hd, (cuuint64_t)nkv, (cuuint64_t)num_pages * page_size};
-        const cuuint64_t strides[2] = {(cuuint64_t)hd * 2, (cuuint64_t)nkv * hd * 2};
-        const cuuint32_t box[3] = {64, 1, (cuuint32_t)page_size};
-        const cuuint32_t elem[3] = {1, 1, 1};
-        if (g_encode(kv ? &mv : &mk, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(kv ? v_cache : k_cache), dims,
-                     strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+    {
+        // K: the cache as [64 elements][8 slots][64-element block][groups of 8 slots][kv head]: a box is one page
+        // of one head, landing as [group][block][8 tokens][128 bytes]
+        const cuuint64_t row = (cuuint64_t)nkv * hd * 2;
+        const cuuint64_t dims[5] = {64, 8, (cuuint64_t)(hd / 64), (cuuint64_t)num_pages * page_size / 8, (cuuint64_t)nkv};
+        const cuuint64_t strides[4] = {row, 128, 8 * row, (cuuint64_t)hd * 2};
+        const cuuint32_t box[5] = {64, 8, (cuuint32_t)(hd / 64), (cuuint32_t)(page_size / 8), 1};
+        const cuuint32_t elem[5] = {1, 1, 1, 1, 1};
+        if (g_encode(&mk, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 5, const_cast<void*>(k_cache), dims, strides, box, elem,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            return CW_ERR_UNSUPPORTED;
+    }
+    {
+        // V: the same memory as [64 elements][slot][64-element block][kv head]: a box is one page of one head with
+        // all its blocks, which land one after the other ([block][token][128 bytes])
+        const cuuint64_t dims[4] = {64, (cuuint64_t)num_pages * page_size, (cuuint64_t)(hd / 64), (cuuint64_t)nkv};
+        const cuuint64_t strides[3] = {(cuuint64_t)nkv * hd * 2, 128, (cuuint64_t)hd * 2};
+        const cuuint32_t box[4] = {64, (cuuint32_t)page_size, (cuuint32_t)(hd / 64), 1};
+        const cuuint32_t elem[4] = {1, 1, 1, 1};
+        if (g_encode(&mv, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(v_cache), dims, strides, box, elem,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
             return CW_ERR_UNSUPPORTED;
     }
     PrefillTcParams p;
