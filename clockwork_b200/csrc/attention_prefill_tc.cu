@@ -10,23 +10,26 @@
 //
 //     S  = Q K^T           tcgen05.mma, Q and K both K-major in shared memory, S in TMEM
 //     P  = 2^(S c - m)     softmax warps: two threads per query row read its half row of S from TMEM
-//                          once (no shuffles), float32 statistics, P rounded to bfloat16 into shared memory
-//     O += P V             tcgen05.mma, P K-major, V as it lies in the cache (head dimension
-//                          contiguous = MN-major B operand), O accumulated in TMEM over all tiles
+//                          once (no shuffles), float32 statistics, P rounded to bfloat16 and written
+//                          back to TMEM over the first quarter of S (tcgen05.st, two keys per column)
+//     O += P V             tcgen05.mma with its A operand (P) in TMEM, V as it lies in the cache (head
+//                          dimension contiguous = MN-major B operand), O accumulated in TMEM over all
+//                          tiles.  P never passes through shared memory, whose bandwidth bounds the kernel.
 //
 // m is the maximum the row's exponentials are taken against.  It follows the row's true maximum
 // lazily: only when a tile exceeds it by more than 2^8 is it moved and the accumulated O (in TMEM)
 // and the row sum rescaled, which after the first tiles of a row hardly ever happens; the result
 // is the same sum, since numerator and denominator carry the same factor.
 //
-// The tiles alternate between two sets of softmax warps, each with its own S buffer and O
-// accumulator in TMEM (2 x 128 + 2 x HD columns), P buffer in shared memory and row statistics: two
-// independent online softmaxes over the even and the odd tiles, merged at the end like the parts of
-// a cut row.  One set's exponentials (the MUFU pipe) run beside the other's passes over S, the MMAs
-// of both and the loads of later tiles.  K and V tiles share one ring of shared-memory slots, filled
-// in the order the MMA warp takes them (scores two tiles ahead of probabilities).  Warps (576
-// threads): 0 TMA producer, 1 MMA issuer and TMEM owner, 2..9 and 10..17 the softmax sets (warp w owns
-// TMEM lanes 32 (w % 4) .. +31; two warps of a set share a lane quarter and split the columns).
+// The tiles alternate between two sets of softmax warps, each with its own S/P buffer and O
+// accumulator in TMEM (2 x 128 + 2 x HD columns) and row statistics: two independent online
+// softmaxes over the even and the odd tiles, merged at the end like the parts of a cut row.  One
+// set's exponentials (the MUFU pipe) run beside the other's passes over S, the MMAs of both and the
+// loads of later tiles.  K and V tiles share one ring of shared-memory slots, filled in the order the
+// MMA warp takes them (K_0, K_1, then V_j and K_{j+2}: S of tile j+2 follows PV of tile j into the
+// buffer that held S and P of tile j).  Warps (576 threads): 0 TMA producer, 1 MMA issuer and TMEM
+// owner, 2..9 and 10..17 the softmax sets (warp w owns TMEM lanes 32 (w % 4) .. +31; two warps of a
+// set share a lane quarter and split the columns).
 //
 // Reference: clockwork/kernels/attention.py:68-96 (gather the context through one block table, then
 // dense causal attention with the query aligned to the end of the context, :45-65) and
@@ -67,12 +70,11 @@ struct ACfg {
     static constexpr int CB = HD / 64;                  // 64-element (128-byte) column blocks per row
     static constexpr int BLOCK_BYTES = 128 * 128;       // [128 rows][64 bf16], 128-byte swizzle
     static constexpr int Q_BYTES = CB * BLOCK_BYTES;
-    static constexpr int P_BYTES = (AK / 64) * BLOCK_BYTES;  // one P tile; there are two
     static constexpr int SLOT_BYTES = CB * BLOCK_BYTES;  // one K or one V tile
     static constexpr int TAIL_BYTES = 256 + 2048;  // barriers, exchange of row statistics
-    static constexpr int FIT = (A_MAX_SMEM - TAIL_BYTES - Q_BYTES - 2 * P_BYTES) / SLOT_BYTES;
+    static constexpr int FIT = (A_MAX_SMEM - TAIL_BYTES - Q_BYTES) / SLOT_BYTES;
     static constexpr int NSLOTS = FIT > 8 ? 8 : FIT;
-    static constexpr int SMEM_BYTES = Q_BYTES + 2 * P_BYTES + NSLOTS * SLOT_BYTES + TAIL_BYTES;
+    static constexpr int SMEM_BYTES = Q_BYTES + NSLOTS * SLOT_BYTES + TAIL_BYTES;
     static constexpr int O_COL = 2 * AK;                 // S buffers at columns 0 and 128, the two O accumulators after them
     static constexpr int TMEM_COLS = 512;
     static_assert(NSLOTS >= 4, "too few key/value slots");
@@ -173,6 +175,17 @@ __device__ __forceinline__ void rescale_o(uint32_t taddr, float alpha) {
         tmem_st16(taddr + c, v);
     }
 }
+// D (+)= A B with A in tensor memory: lane i holds row i, a 32-bit column two consecutive bfloat16 of the
+// inner dimension (the lower half first), so 16 of them take 8 columns.
+__device__ __forceinline__ void umma_bf16_a_tmem(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc,
+                                                 uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
 // A named barrier of n threads that also tells every one of them whether all came with `pred` true.
 __device__ __forceinline__ bool bar_and(int id, int n, bool pred) {
     uint32_t all;
@@ -200,10 +213,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         return;
     }
     uint8_t* q_s = smem;
-    uint8_t* p_s = q_s + C::Q_BYTES;
-    uint8_t* slots = p_s + 2 * C::P_BYTES;
+    uint8_t* slots = q_s + C::Q_BYTES;
     uint64_t* bars = (uint64_t*)(slots + C::NSLOTS * C::SLOT_BYTES);
-    // bars: q_full, -, s_full[2], o_full[2], p_full[2], s_free[2], full[NSLOTS], empty[NSLOTS]
+    // bars: q_full, -, s_full[2], o_full[2], p_full[2], -[2], full[NSLOTS], empty[NSLOTS]
     uint32_t* tmem_slot = (uint32_t*)(bars + 10 + 2 * C::NSLOTS);
     volatile int* give_up = (volatile int*)(tmem_slot + 1);
     volatile int* last_part = give_up + 1;
@@ -240,7 +252,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 
     const uint32_t q_full = smem_u32(bars);
     const uint32_t s_full0 = smem_u32(bars + 2), o_full0 = smem_u32(bars + 4);
-    const uint32_t p_full0 = smem_u32(bars + 6), s_free0 = smem_u32(bars + 8);
+    const uint32_t p_full0 = smem_u32(bars + 6);
     const uint32_t full0 = smem_u32(bars + 10), empty0 = smem_u32(bars + 10 + C::NSLOTS);
     if (tid == 0) {
         mbar_init(q_full, 1);
@@ -248,7 +260,6 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             mbar_init(s_full0 + 8 * b, 1);
             mbar_init(o_full0 + 8 * b, 1);
             mbar_init(p_full0 + 8 * b, 256);
-            mbar_init(s_free0 + 8 * b, 256);
         }
         for (int i = 0; i < C::NSLOTS; ++i) {
             mbar_init(full0 + 8 * i, 1);
@@ -266,7 +277,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 
     if (warp == 0) {
         // ---- TMA producer: Q once, then K and V tiles in the order the MMA warp takes them ------------
-        // K_0, K_1, then (K_{j+2}, V_j) for every tile j: the scores run two tiles ahead of the
+        // K_0, K_1, then (V_j, K_{j+2}) for every tile j: the scores run two tiles ahead of the
         // probabilities.  Lane i fetches page i of a tile: it reads the page's number from the block
         // table ahead of its use (so that the read's latency is hidden) and issues that page's copies itself.
         if (lane < 3) {
@@ -320,8 +331,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         if (ok && ntiles > 1) ok = load(pg_1, false);
         for (int j = 0; j < ntiles && ok; ++j) {
             const int pg_3 = page_of(j + 3);
-            if (j + 2 < ntiles) ok = load(pg_2, false);
-            if (ok) ok = load(pg_v, true);
+            ok = load(pg_v, true);
+            if (ok && j + 2 < ntiles) ok = load(pg_2, false);
             pg_v = pg_1;
             pg_1 = pg_2;
             pg_2 = pg_3;
@@ -360,14 +371,6 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         if (ok && ntiles > 0) ok = issue_s(0);
         if (ok && ntiles > 1) ok = issue_s(1);
         for (int j = 0; j < ntiles && ok; ++j) {
-            if (j + 2 < ntiles) {
-                // S of tile j+2 goes where S of tile j was, as soon as that tile's set holds it in registers
-                ok = mbar_wait(s_free0 + 8 * (j & 1), (j >> 1) & 1, give_up);
-                if (!ok) break;
-                tc_fence_after();
-                ok = issue_s(j + 2);
-                if (!ok) break;
-            }
             ok = mbar_wait(p_full0 + 8 * (j & 1), (j >> 1) & 1, give_up);
             if (!ok) break;
             const int slot = t % C::NSLOTS;
@@ -377,16 +380,19 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             const uint32_t v_addr = smem_u32(slots + slot * C::SLOT_BYTES);
 #pragma unroll
             for (int kk = 0; kk < AK / 16; ++kk) {
-                const uint64_t a = smem_desc_sw128(smem_u32(p_s) + (j & 1) * C::P_BYTES + (kk / 4) * C::BLOCK_BYTES) + 2 * (kk % 4);
+                // P_j lies in tensor memory where S_j was (8 columns per 16 keys)
                 // keys 16 kk .. +15: rows r .. r+15 of page pg (pages of 8 tokens: both groups of 8 are whole pages)
                 const int pg = (16 * kk) >> p.page_shift, r = (16 * kk) & (p.page_size - 1);
                 const uint64_t b = smem_desc_mn_sw128(v_addr + (pg * C::CB * p.page_size + r) * 128, p.page_size * 128,
                                                       p.page_size >= 16 ? 1024 : C::CB * 1024);
-                umma_bf16(tmem_base + C::O_COL + (j & 1) * HD, a, b, idesc_o, (j >= 2 || kk > 0) ? 1u : 0u);
+                umma_bf16_a_tmem(tmem_base + C::O_COL + (j & 1) * HD, tmem_base + (j & 1) * AK + 8 * kk, b, idesc_o,
+                                 (j >= 2 || kk > 0) ? 1u : 0u);
             }
             umma_commit(empty0 + 8 * slot);
-            umma_commit(o_full0 + 8 * (j & 1));   // O of this set holds its tiles up to j and its P buffer may be overwritten
+            umma_commit(o_full0 + 8 * (j & 1));   // O of this set holds its tiles up to j
             ++t;
+            // S of tile j+2 goes where S and then P of tile j were: behind PV_j in the tensor pipe
+            if (j + 2 < ntiles) ok = issue_s(j + 2);
         }
     } else if (warp >= 2) {
         // ---- softmax warps: two sets, each with two threads per query row ------------------------------
@@ -426,8 +432,6 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 tc_fence_after();
 #pragma unroll
                 for (int c = 0; c < SC / 32; ++c) tmem_ld32(s_addr + 32 * c, sv + 32 * c);
-                tc_fence_before();
-                asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(s_free0 + 8 * set) : "memory");
                 if (!all_visible) {
 #pragma unroll
                     for (int i = 0; i < SC; ++i) {
@@ -467,6 +471,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             ok = bar_and(pair_bar, 64, ok);  // (also: the partner has read this thread's maximum)
             if (!ok) break;
             float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+            // P as the second MMA's A operand, in tensor memory over the first quarter of this set's S
+            // (which both threads of the row hold in registers by now): pairs of keys per column
 #pragma unroll
             for (int c = 0; c < SC / 32; ++c) {
                 float* v = sv + 32 * c;
@@ -475,17 +481,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 for (int i = 0; i < 32; ++i) v[i] = ex2(fmaf(v[i], scale_log2, -base));
 #pragma unroll
                 for (int i = 0; i < 32; ++i) sum4[i & 3] += v[i];
+                float packed[16];
 #pragma unroll
-                for (int q4 = 0; q4 < 4; ++q4) {
-                    // 8 keys = one 16-byte chunk of this row in the K-major, 128-byte-swizzled P tile;
-                    // this thread's 64 keys are the 64-key block `half`
-                    const int chunk = 4 * c + q4;
-                    const uint32_t addr = smem_u32(p_s) + set * C::P_BYTES + half * C::BLOCK_BYTES + row * 128 + (((chunk & 7) ^ (row & 7)) << 4);
-                    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr),
-                                 "r"(pack2(v[8 * q4], v[8 * q4 + 1])), "r"(pack2(v[8 * q4 + 2], v[8 * q4 + 3])),
-                                 "r"(pack2(v[8 * q4 + 4], v[8 * q4 + 5])), "r"(pack2(v[8 * q4 + 6], v[8 * q4 + 7]))
-                                 : "memory");
-                }
+                for (int i = 0; i < 16; ++i) packed[i] = __uint_as_float(pack2(v[2 * i], v[2 * i + 1]));
+                tmem_st16(lane_addr + set * AK + half * (SC / 2) + 16 * c, packed);
             }
             l_run = l_run * alpha + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
             if (__any_sync(0xffffffffu, rescale)) {
@@ -494,7 +493,6 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 tc_fence_after();
                 rescale_o<OC>(o_set, alpha);
             }
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // P is read by the tensor core's proxy
             tc_fence_before();
             asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(p_full0 + 8 * set) : "memory");
         }
