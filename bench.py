@@ -71,11 +71,21 @@ class ClockSampler:
     def __enter__(self):
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100", "-i", "0"],
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "20", "-i", "0"],
                 stdout=self.file, stderr=subprocess.DEVNULL)
         except OSError:
             self.proc = None
         return self
+
+    def lines(self) -> int:
+        try:
+            return len(Path(self.file.name).read_text().splitlines())
+        except OSError:
+            return 0
+
+    def mark(self) -> None:
+        """What was sampled so far (the tool takes a moment to start) is not of the timed region."""
+        self.skip = self.lines()
 
     def __exit__(self, *exc):
         if self.proc is not None:
@@ -89,7 +99,7 @@ class ClockSampler:
     def summary(self) -> dict:
         sm, mx, reasons = [], [], set()
         try:
-            for line in Path(self.file.name).read_text().splitlines():
+            for line in Path(self.file.name).read_text().splitlines()[getattr(self, "skip", 0):]:
                 cols = [c.strip() for c in line.split(",")]
                 if len(cols) < 9:
                     continue
@@ -210,12 +220,17 @@ def main() -> int:
         tokens = [[rng.randrange(vocab)] for _ in range(batch)]
         ctx_now = cache.get(ids[0]).num_computed
         step_fn = engine.decode_step_device
-        for _ in range(warmup):
-            step_fn(ids, tokens)
-        torch.cuda.synchronize()
-        l0 = launch_count() + runner.graph_kernel_launches
         start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         with ClockSampler() as clocks:
+            # the sampler takes a moment to start reporting: wait for its first line (two seconds at most)
+            waited = time.perf_counter()
+            while clocks.proc is not None and clocks.lines() == 0 and time.perf_counter() - waited < 2.0:
+                time.sleep(0.01)
+            for _ in range(warmup):
+                step_fn(ids, tokens)
+            torch.cuda.synchronize()
+            clocks.mark()
+            l0 = launch_count() + runner.graph_kernel_launches
             start.record()
             for _ in range(steps):
                 step_fn(ids, tokens)
