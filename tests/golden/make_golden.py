@@ -70,4 +70,6 @@ def main(reference_root: str) -> None:
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) < 2:
+        sys.exit("usage: make_golden.py <folder of a checkout of the reference project>")
+    main(sys.argv[1])

@@ -38,7 +38,9 @@ def test_yaml_profile_and_pairs(tmp_path):
 def test_reference_profiles_load():
     import pathlib
 
-    ref = pathlib.Path("/root/reference/configs")
+    from tests.tiny_configs import reference_checkout
+
+    ref = pathlib.Path(reference_checkout(), "configs")
     if not ref.is_dir():
         pytest.skip("reference checkout not present")
     for path in ref.glob("*.yaml"):

@@ -77,13 +77,16 @@ def test_plain_matches_reference_checkout_directly(tiny_dirs):
     import sys
     from types import SimpleNamespace
 
-    if not Path("/root/reference/clockwork/engine/model.py").is_file():
+    from tests.tiny_configs import reference_checkout
+
+    ref = str(reference_checkout())
+    if not Path(ref, "clockwork/engine/model.py").is_file():
         pytest.skip("reference checkout not present")
-    sys.path.insert(0, "/root/reference")
+    sys.path.insert(0, ref)
     try:
         from clockwork.engine.model import Qwen2ForCausalLM
     finally:
-        sys.path.remove("/root/reference")
+        sys.path.remove(ref)
     config, weights = plain.read_model_dir(tiny_dirs["B"])
     model = Qwen2ForCausalLM(SimpleNamespace(**config))
     model.load_state_dict(weights, strict=False)

@@ -34,3 +34,13 @@ def tokens_for(name: str, length: int, salt: int = 0) -> list[int]:
 
 def hash_name(name: str) -> int:
     return sum((i + 1) * ord(c) for i, c in enumerate(name)) * 2654435761 & 0x7FFFFFFF
+
+
+def reference_checkout():
+    """Folder of a checkout of the reference project, for the tests that compare with its own code:
+    the environment variable CLOCKWORK_REFERENCE, else a folder ``reference`` beside this repository."""
+    import os
+    from pathlib import Path
+
+    named = os.environ.get("CLOCKWORK_REFERENCE")
+    return Path(named) if named else Path(__file__).resolve().parents[2] / "reference"
