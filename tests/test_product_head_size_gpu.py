@@ -1,0 +1,90 @@
+"""Trace replay of a third, still small configuration with the head size of the real model (128) and
+contexts of more than a thousand tokens, so that the kernels the product path takes at that size run
+inside the engine and are compared with the plain implementation: the tcgen05 prefill attention over
+many key tiles (with long rows of keys cut into parts, since the few work items leave SMs idle),
+decode attention with its context splits and fused rotation, decoded tokens riding in a step beside
+another request's prompt portion, and the tensor-core products with their split norm.  The tiny
+configurations (head sizes 16 and 32) never reach those kernels."""
+
+import json
+
+import pytest
+import torch
+
+from tests.plain import qwen2_plain as plain
+from tests.test_replay_gpu import check
+from tests.trace_tools import TraceBuilder, cut, round_up, run_trace
+
+pytestmark = pytest.mark.gpu
+
+CONFIG = {
+    "architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2",
+    "num_hidden_layers": 2, "hidden_size": 256, "num_attention_heads": 4, "num_key_value_heads": 2,
+    "head_dim": 128, "intermediate_size": 384, "vocab_size": 512, "rope_theta": 1000000.0,
+    "rms_norm_eps": 1e-6, "tie_word_embeddings": True, "max_position_embeddings": 4096,
+    "hidden_act": "silu", "use_sliding_window": False,
+}
+PAGE = 16
+
+
+def tokens(n: int, salt: int) -> list[int]:
+    state, out = (2654435761 * (salt + 1) + 97 * n) & 0x7FFFFFFF, []
+    for _ in range(n):
+        state = (1103515245 * state + 12345) & 0x7FFFFFFF
+        out.append((state >> 8) % CONFIG["vocab_size"])
+    return out
+
+
+@pytest.fixture(scope="module")
+def model_dir(tmp_path_factory):
+    """Random weights with the q and k projections scaled up, so that attention is peaked and a key
+    that is missed, misplaced or weighted wrongly in a merge moves the logits beyond the tolerance."""
+    from clockwork_b200.weights import save_safetensors, write_random_model
+
+    plain_dir = write_random_model(tmp_path_factory.mktemp("head128"), CONFIG, seed=5)
+    config, weights = plain.read_model_dir(plain_dir, dtype=torch.float32)
+    sharp = {k: ((w * 6.0) if (".q_proj." in k or ".k_proj." in k) else w).to(torch.bfloat16) for k, w in weights.items()}
+    target = tmp_path_factory.mktemp("head128_sharp")
+    (target / "config.json").write_text(json.dumps(config))
+    save_safetensors(target / "model.safetensors", sharp)
+    return target
+
+
+@pytest.fixture(scope="module")
+def references(model_dir):
+    config, weights = plain.read_model_dir(model_dir)
+
+    def get(toks):
+        return (plain.all_position_logits(config, weights, toks),
+                plain.all_position_logits(config, weights, toks, rnd=plain.to_bfloat16_and_back))
+
+    return get
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_contexts_at_head_size_128(dtype, model_dir, references, tmp_path):
+    from clockwork_b200.ops import attention_fast
+
+    a, b = tokens(1500, 1), tokens(700, 2)
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    assert attention_fast.prefill_tc_takes(CONFIG["head_dim"], PAGE)
+    words = attention_fast.prefill_work_items([1300], [1300], CONFIG["num_attention_heads"], sms)[2]
+    assert max(w & 0xFF for w in words) > 1  # the first step's long rows of keys are cut
+    tb = TraceBuilder()
+    tb.step([("a", a[:1300], True)])                          # many key tiles, few work items: cut rows
+    tb.step([("a", a[1300:1468], True), ("b", b[:300], True)])  # a portion deep in a context beside a new prompt
+    portions = cut(b[300:], [70, 2, 129, 40, 3, 17])
+    assert len(portions) < 32
+    for i, t in enumerate(a[1468:]):                          # 32 decoded tokens, b's portions riding along at first
+        step, end = [("a", [t], True)], []
+        if i < len(portions):
+            step.append(("b", portions[i], True))
+            if i == len(portions) - 1:
+                end.append("b")
+        if i == 31:
+            end.append("a")
+        tb.step(step, end=end)
+    out = run_trace(model_dir, dtype, round_up(1500, 64) + round_up(700, 64), tb.steps, tmp_path / "out",
+                    CONFIG["vocab_size"], PAGE)
+    check(tb.gather(out, "a", len(a)), references(a), dtype, f"head size 128, {dtype}, the long request")
+    check(tb.gather(out, "b", len(b)), references(b), dtype, f"head size 128, {dtype}, the request beside it")
