@@ -143,17 +143,11 @@ class LLMEngine:
     def step(self) -> list[RequestOutput]:
         ahead, self._ahead = self._ahead, None
         prepared = None
-        if ahead is not None:
-            # still true?  (somebody may have stepped the runner directly in between)
-            requests = self.cache.requests
-            for p in ahead[0].portions:
-                req = requests.get(p.seq.seq_id)
-                if req is None or req.num_computed != p.start or len(p.seq) != p.start + 1:
-                    ahead = None
-                    break
+        if ahead is not None and ahead[3] != self.runner.steps_run:
+            ahead = None  # somebody has stepped the runner directly in between: the plan's positions are stale
         if ahead is not None:
             # planned and prepared while the last step ran: every running sequence decodes one token
-            out, sampled_seqs, prepared = ahead
+            out, sampled_seqs, prepared, _ = ahead
             self.scheduler.accept_plan(out)
             self.steps_planned_ahead += 1
             entries = None
@@ -238,7 +232,8 @@ class LLMEngine:
         if not 0 < len(seqs) <= self.runner.graph_max_batch:
             return None
         sampling = self.sampler.host_params([s.sampling_params for s in seqs], [len(s.output_token_ids) + 1 for s in seqs])
-        return out, seqs, self.runner.prepare_decode([s.seq_id for s in seqs], sampling)
+        # (the runner's step count says at the next step whether anybody else has stepped it since)
+        return out, seqs, self.runner.prepare_decode([s.seq_id for s in seqs], sampling), self.runner.steps_run
 
     def _process(self, seq: Sequence) -> RequestOutput:
         params = seq.sampling_params
