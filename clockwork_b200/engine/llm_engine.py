@@ -213,14 +213,15 @@ class LLMEngine:
                 if req is not None and n >= self.cache.page_size:
                     self.prefix_cache.insert(seq.prompt_token_ids[:n], req.tables[0])
         outputs = [self._process(seq) for seq in sampled_seqs]
-        self.scheduler.free_finished()
-        for output in outputs:
-            if output.finished:
+        finished = [output for output in outputs if output.finished]
+        if finished:
+            self.scheduler.free_finished()
+            for output in finished:
                 self._forget(output.request_id)
-                self._ahead = None  # the plan assumed that every sequence goes on
-        if self._unchecked_steps and any(output.finished for output in outputs):
-            self.runner.check_status()  # no request ends with an unread status
-            self._unchecked_steps = 0
+            self._ahead = None  # the plan assumed that every sequence goes on
+            if self._unchecked_steps:
+                self.runner.check_status()  # no request ends with an unread status
+                self._unchecked_steps = 0
         return outputs
 
     def _plan_ahead(self):
@@ -235,16 +236,38 @@ class LLMEngine:
         # (the runner's step count says at the next step whether anybody else has stepped it since)
         return out, seqs, self.runner.prepare_decode([s.seq_id for s in seqs], sampling), self.runner.steps_run
 
-    def _process(self, seq: Sequence) -> RequestOutput:
+    def _finish_rules(self, seq: Sequence) -> None:
+        """The request's finish rules in the form the per-step check wants them."""
         params = seq.sampling_params
-        token = seq.output_token_ids[-1]
+        stops = set(params.stop_token_ids)
+        if not params.ignore_eos:
+            stops |= set(self._eos)
+        seq.stop_ids = frozenset(stops) if stops else None
+        seq.length_limit = min(params.max_tokens, self.cfg.model.max_model_len - len(seq.prompt_token_ids))
+
+    def _process(self, seq: Sequence) -> RequestOutput:
+        if seq.length_limit is None:
+            self._finish_rules(seq)
+        out_ids = seq.output_token_ids
+        n_out = len(out_ids)
+        stops = seq.stop_ids
+        if self.tokenizer is None:
+            # the usual case on this path: token rules only, one object per request and step
+            if stops is not None and out_ids[-1] in stops:
+                seq.status = SequenceStatus.FINISHED_STOPPED
+                return RequestOutput(seq, n_out, True, "stop")
+            if n_out >= seq.length_limit:
+                seq.status = SequenceStatus.FINISHED_LENGTH
+                return RequestOutput(seq, n_out, True, "length")
+            return RequestOutput(seq, n_out, False, None)
+        params = seq.sampling_params
         finish_reason = None
         delta = ""
         text = self._texts.get(seq.seq_id, "")
-        if (not params.ignore_eos and token in self._eos) or token in params.stop_token_ids:
+        if stops is not None and out_ids[-1] in stops:
             finish_reason = "stop"  # the stopping token stays in token_ids, adds no text
-        elif self.tokenizer is not None:
-            candidate = self.tokenizer.decode(seq.output_token_ids)
+        else:
+            candidate = self.tokenizer.decode(out_ids)
             if params.stop:
                 hits = [pos for pos in (candidate.find(s) for s in params.stop) if pos >= 0]
                 if hits:
@@ -253,20 +276,13 @@ class LLMEngine:
             delta = candidate[len(text):] if candidate.startswith(text) else ""
             text = candidate
             self._texts[seq.seq_id] = text
-        if finish_reason is None and (
-            len(seq.output_token_ids) >= params.max_tokens or len(seq) >= self.cfg.model.max_model_len
-        ):
+        if finish_reason is None and n_out >= seq.length_limit:
             finish_reason = "length"
         if finish_reason == "stop":
             seq.status = SequenceStatus.FINISHED_STOPPED
         elif finish_reason == "length":
             seq.status = SequenceStatus.FINISHED_LENGTH
-        return RequestOutput(
-            request_id=seq.seq_id, prompt_token_ids=seq.prompt_token_ids, token_ids=seq.output_token_ids,
-            text=text, finished=seq.is_finished(), finish_reason=finish_reason,
-            num_cached_tokens=seq.num_cached_tokens, num_prompt_tokens=len(seq.prompt_token_ids),
-            num_generated_tokens=len(seq.output_token_ids), delta_text=delta,
-        )
+        return RequestOutput(seq, n_out, finish_reason is not None, finish_reason, text, delta)
 
     # ---- whole requests -------------------------------------------------------------------------------
     def generate(self, prompts: list[str] | list[list[int]],

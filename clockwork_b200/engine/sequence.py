@@ -40,6 +40,10 @@ class Sequence:
         self.num_computed_tokens = 0  # tokens whose keys/values are in the cache
         self.num_cached_tokens = 0  # of those, how many came from the prefix cache at admission
         self.arrival_time = time.monotonic() if arrival_time is None else arrival_time
+        # set by the engine when the request is added: the token ids that end it (None: none does) and
+        # the number of generated tokens at which it ends by length
+        self.stop_ids: frozenset[int] | None = None
+        self.length_limit: int | None = None
 
     def token_ids(self) -> list[int]:
         return self.prompt_token_ids + self.output_token_ids
@@ -74,30 +78,42 @@ class RequestOutput:
     """What ``LLMEngine.step`` reports for a request that sampled a token (the reference's
     ``clockwork/engine/sequence.py`` RequestOutput: ids, text, finish state, counts).
 
-    ``prompt_token_ids`` is the request's own prompt list and ``token_ids`` a view of its output
-    list as long as it was when this output was made (the list only ever grows), so that a step
-    costs the same however long the prompt and the output are.  Treat both as read-only."""
+    An output holds what was true when it was made (how many tokens were generated, whether and why
+    the request finished, the text) and reads the rest from its sequence: ``prompt_token_ids`` is the
+    request's own prompt list and ``token_ids`` a view of its output list as long as it was then (the
+    list only ever grows), so that a step costs the same however long the prompt and the output are.
+    Treat both as read-only."""
 
-    __slots__ = ("request_id", "prompt_token_ids", "_output", "text", "finished", "finish_reason", "num_cached_tokens",
-                 "num_prompt_tokens", "num_generated_tokens", "delta_text")
+    __slots__ = ("_seq", "num_generated_tokens", "finished", "finish_reason", "text", "delta_text")
 
-    def __init__(self, request_id: str, prompt_token_ids: list[int], token_ids: list[int], text: str, finished: bool,
-                 finish_reason: str | None, num_cached_tokens: int, num_prompt_tokens: int,
-                 num_generated_tokens: int, delta_text: str = "") -> None:
-        self.request_id = request_id
-        self.prompt_token_ids = prompt_token_ids
-        self._output = token_ids
-        self.text = text
+    def __init__(self, seq: Sequence, num_generated_tokens: int, finished: bool, finish_reason: str | None,
+                 text: str = "", delta_text: str = "") -> None:
+        self._seq = seq
+        self.num_generated_tokens = num_generated_tokens
         self.finished = finished
         self.finish_reason = finish_reason
-        self.num_cached_tokens = num_cached_tokens
-        self.num_prompt_tokens = num_prompt_tokens
-        self.num_generated_tokens = num_generated_tokens
+        self.text = text
         self.delta_text = delta_text
 
     @property
+    def request_id(self) -> str:
+        return self._seq.seq_id
+
+    @property
+    def prompt_token_ids(self) -> list[int]:
+        return self._seq.prompt_token_ids
+
+    @property
+    def num_prompt_tokens(self) -> int:
+        return len(self._seq.prompt_token_ids)
+
+    @property
+    def num_cached_tokens(self) -> int:
+        return self._seq.num_cached_tokens
+
+    @property
     def token_ids(self) -> list[int]:
-        out = self._output
+        out = self._seq.output_token_ids
         return out if len(out) == self.num_generated_tokens else out[: self.num_generated_tokens]
 
     def __repr__(self) -> str:
