@@ -140,7 +140,7 @@ class CacheManager:
         if self.device is not None and self.device.type == "cuda":
             from .. import ops
 
-            self.status = ops.new_status(self.device)
+            self.status = ops.device_status(self.device)
 
     # ---- requests ---------------------------------------------------------------------------
     def open(self, request_id: str, shared_prefix: list[int] | None = None) -> RequestCache:

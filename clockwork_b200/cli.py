@@ -19,31 +19,22 @@ import json
 import sys
 from pathlib import Path
 
-SHAPES = {
-    # config.json contents of the shapes the benchmarks name
-    "qwen2.5-1.5b": dict(num_hidden_layers=28, hidden_size=1536, num_attention_heads=12, num_key_value_heads=2,
-                         head_dim=128, intermediate_size=8960, vocab_size=151936, rope_theta=1000000.0,
-                         rms_norm_eps=1e-6, tie_word_embeddings=True, max_position_embeddings=32768),
-    "qwen2.5-7b": dict(num_hidden_layers=28, hidden_size=3584, num_attention_heads=28, num_key_value_heads=4,
-                       head_dim=128, intermediate_size=18944, vocab_size=152064, rope_theta=1000000.0,
-                       rms_norm_eps=1e-6, tie_word_embeddings=False, max_position_embeddings=32768),
-    "qwen2.5-32b": dict(num_hidden_layers=64, hidden_size=5120, num_attention_heads=40, num_key_value_heads=8,
-                        head_dim=128, intermediate_size=27648, vocab_size=152064, rope_theta=1000000.0,
-                        rms_norm_eps=1e-5, tie_word_embeddings=False, max_position_embeddings=32768),
-    "tiny": dict(num_hidden_layers=2, hidden_size=64, num_attention_heads=4, num_key_value_heads=2, head_dim=16,
-                 intermediate_size=128, vocab_size=256, rope_theta=10000.0, rms_norm_eps=1e-6,
-                 tie_word_embeddings=True, max_position_embeddings=256),
-}
+def shape_names() -> list[str]:
+    from . import models  # noqa: F401  (registers architectures)
+    from .config.registry import named_shapes
+
+    return sorted(named_shapes())
 
 
 def shape_config(name: str, num_layers: int | None = None) -> dict:
-    if name not in SHAPES:
-        raise SystemExit(f"unknown shape {name!r}; known: {sorted(SHAPES)}")
-    raw = dict(SHAPES[name], architectures=["Qwen2ForCausalLM"], model_type="qwen2", hidden_act="silu",
-               use_sliding_window=False)
-    if num_layers is not None:
-        raw["num_hidden_layers"] = num_layers
-    return raw
+    """config.json of a size that a registered architecture knows by name."""
+    from . import models  # noqa: F401
+    from .config import registry
+
+    try:
+        return registry.shape_config(name, num_layers)
+    except ValueError as exc:
+        raise SystemExit(str(exc)) from None
 
 
 def _engine_config(args):
@@ -130,7 +121,7 @@ def main(argv: list[str] | None = None) -> int:
     g.set_defaults(fn=_cmd_generate)
 
     r = sub.add_parser("random-model", help="write config.json + model.safetensors with random weights")
-    r.add_argument("--shape", default="tiny", help=f"one of {sorted(SHAPES)}")
+    r.add_argument("--shape", default="tiny", help=f"one of {shape_names()}")
     r.add_argument("--config-json", help="a config.json to use instead of --shape")
     r.add_argument("--num-layers", type=int, default=None)
     r.add_argument("--seed", type=int, default=0)

@@ -51,6 +51,27 @@ def get_architecture(name: str) -> Architecture:
         ) from None
 
 
+def named_shapes() -> dict[str, dict[str, Any]]:
+    """Every size that a registered architecture knows by name (its optional ``named_shapes``
+    attribute): name -> config.json contents, the architecture's own name inside."""
+    out: dict[str, dict[str, Any]] = {}
+    for arch in _ARCHITECTURES.values():
+        out.update(getattr(arch, "named_shapes", {}))
+    return out
+
+
+def shape_config(name: str, num_layers: int | None = None) -> dict[str, Any]:
+    """The config.json of a named size, optionally with fewer (or more) layers."""
+    shapes = named_shapes()
+    if name not in shapes:
+        raise ValueError(f"unknown shape {name!r}; known: {sorted(shapes)}")
+    raw = dict(shapes[name])
+    if num_layers is not None:
+        arch = get_architecture(architecture_name(raw))
+        raw[getattr(arch, "layer_count_key", "num_hidden_layers")] = num_layers
+    return raw
+
+
 def architecture_name(raw: dict[str, Any]) -> str:
     archs = raw.get("architectures")
     if not isinstance(archs, list) or len(archs) != 1 or not isinstance(archs[0], str):

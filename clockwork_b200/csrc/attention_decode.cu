@@ -647,6 +647,25 @@ extern "C" const char* cw_error_string(int code) {
     return code > 0 ? cudaGetErrorString((cudaError_t)code) : "unknown clockwork_b200 error code";
 }
 
+// The three parts of the scratch a call needs, each rounded up to 256 bytes.
+static void noalloc_layout(int S, int nh, int nkv, int hd, int max_ctx, size_t* counters_bytes, size_t* lse_bytes,
+                           size_t* o_bytes) {
+    long long part_o_floats = 0, part_lse_floats = 0;
+    int counters = 0;
+    cw_attention_decode_workspace(S, nh, nkv, hd, max_ctx, &part_o_floats, &part_lse_floats, &counters);
+    *counters_bytes = align256((size_t)counters * sizeof(int));
+    *lse_bytes = align256((size_t)part_lse_floats * sizeof(float));
+    *o_bytes = align256((size_t)part_o_floats * sizeof(float));
+}
+
+extern "C" int cw_attention_decode_noalloc_fits(int S, int nh, int nkv, int hd, int max_ctx) {
+    if (S < 0 || nh <= 0 || nkv <= 0 || nh % nkv != 0 || hd <= 0 || max_ctx <= 0) return CW_ERR_BAD_SIZE;
+    if (S == 0) return 1;
+    size_t counters_bytes, lse_bytes, o_bytes;
+    noalloc_layout(S, nh, nkv, hd, max_ctx, &counters_bytes, &lse_bytes, &o_bytes);
+    return counters_bytes + lse_bytes + o_bytes <= (size_t)CW_NOALLOC_SCRATCH_BYTES ? 1 : 0;
+}
+
 extern "C" int cw_attention_decode_noalloc(const void* q, int q_stride, void* out, const void* k_cache,
                                            const void* v_cache, const int* block_tables, const int* ctx_lens, int S,
                                            int nh, int nkv, int hd, int page_size, int max_blocks, int num_pages,
@@ -654,12 +673,8 @@ extern "C" int cw_attention_decode_noalloc(const void* q, int q_stride, void* ou
                                            cudaStream_t stream) {
     if (S == 0) return CW_OK;
     if (S < 0 || nh <= 0 || nkv <= 0 || nh % nkv != 0 || hd <= 0 || max_ctx <= 0) return CW_ERR_BAD_SIZE;
-    long long part_o_floats = 0, part_lse_floats = 0;
-    int counters = 0;
-    cw_attention_decode_workspace(S, nh, nkv, hd, max_ctx, &part_o_floats, &part_lse_floats, &counters);
-    const size_t counters_bytes = align256((size_t)counters * sizeof(int));
-    const size_t lse_bytes = align256((size_t)part_lse_floats * sizeof(float));
-    const size_t o_bytes = (size_t)part_o_floats * sizeof(float);
+    size_t counters_bytes, lse_bytes, o_bytes;
+    noalloc_layout(S, nh, nkv, hd, max_ctx, &counters_bytes, &lse_bytes, &o_bytes);
     if (counters_bytes + lse_bytes + o_bytes > (size_t)CW_NOALLOC_SCRATCH_BYTES) return CW_ERR_SCRATCH_LIMIT;
 
     // once per device, with that device current: the array's device address

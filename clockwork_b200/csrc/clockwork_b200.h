@@ -41,13 +41,17 @@ const char* cw_error_string(int code);
  * [S, nh*hd] bfloat16, k_cache / v_cache [num_pages, page_size, nkv, hd] bfloat16, block_tables
  * int32 [S, max_blocks], ctx_lens int32 [S] (tokens of each request in the cache, its own
  * included), max_ctx an upper bound of every ctx_lens[s], split the tokens per thread block (a
- * multiple of 64, at least 256), status 4 int32 words on the device (may be null).  Inputs and
+ * multiple of 64, at least 128), status 4 int32 words on the device (may be null).  Inputs and
  * outputs are still the caller's.
  *
  * Limits and rules:
- *  - The scratch needed is 4 * S * nh * ceil(max_ctx / 256) * (hd + 1) bytes plus 4 bytes per
- *    (request, KV head, group of 16 query heads).  A call that needs more than
- *    CW_NOALLOC_SCRATCH_BYTES returns CW_ERR_SCRATCH_LIMIT and launches nothing.
+ *  - The scratch is sized for the finest cut the kernel allows (128 tokens per thread block),
+ *    whatever `split` is: 4 * S * nh * ceil(max_ctx / 128) * (hd + 1) bytes plus 4 bytes per
+ *    (request, KV head, group of 16 query heads), each of the three parts rounded up to 256 bytes.
+ *    A call that needs more than CW_NOALLOC_SCRATCH_BYTES returns CW_ERR_SCRATCH_LIMIT and
+ *    launches nothing.  cw_attention_decode_noalloc_fits answers the same question without a call:
+ *    for 12 query heads of 128 over 2 KV heads the 8 MiB hold, for instance, 8 requests bounded by
+ *    21,632 tokens or 64 requests bounded by 2,688.
  *  - The first call on each device looks up the array's device address (cudaGetSymbolAddress) with
  *    that device current.  Make that first call before any stream capture begins.
  *  - All calls share the one array and it keeps what the last call left; the counters in it are
@@ -58,6 +62,11 @@ int cw_attention_decode_noalloc(const void* q, int q_stride, void* out, const vo
                                 const int* block_tables, const int* ctx_lens, int S, int nh, int nkv, int hd,
                                 int page_size, int max_blocks, int num_pages, float scale, int window, int max_ctx,
                                 int split, int* status, cudaStream_t stream);
+
+/* 1 when a call of cw_attention_decode_noalloc with these sizes fits the built-in scratch, 0 when it
+ * would return CW_ERR_SCRATCH_LIMIT; CW_ERR_BAD_SIZE for sizes the kernel refuses anyway.  Touches
+ * no device. */
+int cw_attention_decode_noalloc_fits(int S, int nh, int nkv, int hd, int max_ctx);
 
 #ifdef __cplusplus
 }

@@ -2,8 +2,12 @@
 //   C[M,N] = A[M,K] * W[N,K]^T (+ bias[N]),   W in nn.Linear layout (clockwork/engine/model.py:58-60, 74-77)
 // It is the matrix product of the true-float32 path (fmaf only, no tensor cores, no TF32) and
 // the fallback of the bfloat16 path for sizes the tensor-core kernel refuses.
-// Every output element is one fmaf chain over k = 0..K-1 in ascending order, whatever M, N
-// or the tile it falls in, so a row's result does not depend on the rest of the batch.
+// Every output element is summed in the same fixed order whatever M, N or the tile it falls in, so
+// a row's result does not depend on the rest of the batch: fmaf chains over 16 consecutive k, in
+// ascending order, whose results are added up with a compensated (Kahan) running sum.  One plain
+// chain over a long inner dimension would lose more than the 1e-5 that the float32 path is held
+// to: at K = 8960 its rounding error alone is of that order; summed this way the result stays
+// within a few units in the last place of the exact dot product at any K.
 //
 // Epilogues: 0 store as T; 1 add into a float32 matrix (the residual stream); 2 store float32
 // (logits).  The SwiGLU variant computes silu(A Wg^T) * (A Wu^T) (clockwork/engine/model.py:62-63).
@@ -12,6 +16,15 @@
 #define BM 64
 #define BN 64
 #define BK 16
+
+// sum += x with the rounding error of earlier additions carried along in `lost` (Kahan's summation;
+// the order of the operations matters and the compiler keeps it: no fast-math flags are used)
+__device__ __forceinline__ void kahan_add(float& sum, float& lost, float x) {
+    const float y = __fsub_rn(x, lost);
+    const float t = __fadd_rn(sum, y);
+    lost = __fsub_rn(__fsub_rn(t, sum), y);
+    sum = t;
+}
 
 template <typename T, bool SWIGLU>
 __global__ void __launch_bounds__(256)
@@ -24,9 +37,11 @@ gemm_ref_kernel(const T* __restrict__ A, const T* __restrict__ W, const T* __res
     const int tid = threadIdx.x;
     const int tx = tid & 15, ty = tid >> 4;
     const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
-    float acc[4][4] = {};
-    float acc2[4][4] = {};
+    float sum[4][4] = {}, lost[4][4] = {};    // running sums and what their roundings have lost so far
+    float sum2[4][4] = {}, lost2[4][4] = {};
     for (int k0 = 0; k0 < K; k0 += BK) {
+        float acc[4][4] = {};
+        float acc2[4][4] = {};
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             const int e = tid + i * 256;      // 0..1023
@@ -64,6 +79,13 @@ gemm_ref_kernel(const T* __restrict__ A, const T* __restrict__ W, const T* __res
                     if (SWIGLU) acc2[i][j] = fmaf(a[i], w2[j], acc2[i][j]);
                 }
         }
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                kahan_add(sum[i][j], lost[i][j], acc[i][j]);
+                if (SWIGLU) kahan_add(sum2[i][j], lost2[i][j], acc2[i][j]);
+            }
         __syncthreads();
     }
 #pragma unroll
@@ -74,11 +96,11 @@ gemm_ref_kernel(const T* __restrict__ A, const T* __restrict__ W, const T* __res
         for (int j = 0; j < 4; ++j) {
             const int n = n0 + tx * 4 + j;
             if (n >= N) continue;
-            float v = acc[i][j];
+            float v = sum[i][j];
             if (bias) v += bias[n];
             const size_t idx = (size_t)m * ldc + n;
             if (SWIGLU) {
-                const float g = v, u = acc2[i][j];
+                const float g = v, u = sum2[i][j];
                 ((T*)Cout)[idx] = from_f<T>(g / (1.0f + expf(-g)) * u);
             } else if (epilogue == 0) {
                 ((T*)Cout)[idx] = from_f<T>(v);

@@ -617,11 +617,16 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
             tc_fence_after();
             const uint32_t taddr = tmem_base + buf * C::ACC_COLS + ((uint32_t)(quarter * 32) << 16);
             const float bias = (p.bias != nullptr && f < p.N) ? p.bias[f] : 0.f;
-            for (int c = 0; c < bn; c += P_CHUNK, ++chunk_no) {
+            // Only chunks that hold tokens are read out and stored.  Every chunk that runs issues exactly one
+            // store and one bulk group, so that `wait_group.read 1` below means what it says: the store that
+            // read this staging buffer two chunks ago is done with it.  (A chunk that skipped its store but
+            // still filled the buffer would overwrite what the store of two chunks ago may still be reading.)
+            const int c_end = min(bn, p.T - n0);
+            for (int c = 0; c < c_end; c += P_CHUNK, ++chunk_no) {
                 float g[16], u[16];
                 tmem_ld16(taddr + c, g);
                 if (SWIGLU) tmem_ld16(taddr + BN + c, u);
-                if (c + P_CHUNK >= bn) {
+                if (c + P_CHUNK >= c_end) {
                     // the accumulator has been read out: hand the buffer back to the MMA warp
                     tc_fence_before();
                     asm volatile("bar.sync 1, 128;" ::: "memory");
@@ -642,7 +647,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
                 }
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 asm volatile("bar.sync 1, 128;" ::: "memory");
-                if (etid == 0 && n0 + c < p.T) {
+                if (etid == 0) {
                     const bool add = !SWIGLU && p.epilogue == 1;
                     if (add)
                         asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.bulk_group [%0, {%2, %3}], [%1];"

@@ -221,10 +221,14 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             tc_fence_after();
             const uint32_t taddr = tmem_base + buf * C::BN_MAX + ((uint32_t)(quarter * 32) << 16);
             const float bias = (p.bias != nullptr && f < p.N) ? p.bias[f] : 0.f;
-            for (int c = 0; c < bn; c += PAIR_CHUNK, ++chunk_no) {
+            // Only chunks that hold tokens are read out and stored, and every chunk that runs commits exactly
+            // one bulk group (an empty one when this CTA's features lie beyond N), so that `wait_group.read 1`
+            // below means what it says: the store that read this staging buffer two chunks ago is done with it.
+            const int c_end = min(bn, p.T - n0);
+            for (int c = 0; c < c_end; c += PAIR_CHUNK, ++chunk_no) {
                 float g[16];
                 tmem_ld16(taddr + c, g);
-                if (c + PAIR_CHUNK >= bn) {
+                if (c + PAIR_CHUNK >= c_end) {
                     // the accumulator has been read out: hand the buffer back to the leader's MMA thread
                     tc_fence_before();
                     asm volatile("bar.sync 1, 128;" ::: "memory");
@@ -244,13 +248,15 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                 }
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 asm volatile("bar.sync 1, 128;" ::: "memory");
-                if (etid == 0 && n0 + c < p.T && m0 < p.N) {
-                    if (p.epilogue == 1)
-                        asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.bulk_group [%0, {%2, %3}], [%1];"
-                                     ::"l"(&map_c), "r"(smem_u32(st32)), "r"(m0), "r"(n0 + c) : "memory");
-                    else
-                        asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
-                                     ::"l"(&map_c), "r"(smem_u32(st32)), "r"(m0), "r"(n0 + c) : "memory");
+                if (etid == 0) {
+                    if (m0 < p.N) {
+                        if (p.epilogue == 1)
+                            asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.bulk_group [%0, {%2, %3}], [%1];"
+                                         ::"l"(&map_c), "r"(smem_u32(st32)), "r"(m0), "r"(n0 + c) : "memory");
+                        else
+                            asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+                                         ::"l"(&map_c), "r"(smem_u32(st32)), "r"(m0), "r"(n0 + c) : "memory");
+                    }
                     asm volatile("cp.async.bulk.commit_group;" ::: "memory");
                 }
             }

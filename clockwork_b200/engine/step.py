@@ -175,9 +175,12 @@ class DecodeGraph:
         self.max_blocks = (max_ctx + cache.page_size - 1) // cache.page_size
         G = len(cache.groups)
         seg, off = {}, 0
+        # values that the parts' kernels read from device memory and that change with the live requests
+        # (``Part.step_scalars``): one word each, refreshed before every replay
+        self._scalar_rules = model.step_scalars()
         for name, size in (("tokens", batch), ("positions", batch), ("tok_seq", batch), ("q_start", batch + 1),
                            ("ctx_lens", batch), ("rows", batch), ("temperature", batch), ("top_k", batch),
-                           ("top_p", batch), ("uniform", batch), ("decode_split", 1)):
+                           ("top_p", batch), ("uniform", batch), *((f"scalar:{name}", 1) for name in self._scalar_rules)):
             seg[name] = (off, size)
             off += _pad4(size)
         for g in range(G):
@@ -213,13 +216,14 @@ class DecodeGraph:
         )
         ctx.views = cache.views([view(f"tables{g}").view(batch, self.max_blocks) for g in range(G)],
                                 [view(f"slots{g}") for g in range(G)], None, [])
-        # how finely attention cuts contexts is decided per step from the live requests
-        ctx.extras["decode_split"] = view("decode_split")
-        self.h["decode_split"][0] = max_ctx
-        self._split_policy = model.decode_split_policy()
+        for name, rule in self._scalar_rules.items():
+            ctx.extras[name] = view(f"scalar:{name}")
+            self.h[f"scalar:{name}"][0] = rule(batch, max_ctx)
 
         def run():
-            logits = model.forward(ctx, view("tokens"), view("rows"))
+            # the logits of every row stay readable after a replay (trace replay reads them; generation
+            # reads the sampled tokens only)
+            logits = self.logits = model.forward(ctx, view("tokens"), view("rows"))
             if greedy:
                 return ops.argmax(logits)
             return ops.sample(logits, view("temperature").view(torch.float32), view("top_k"),
@@ -292,7 +296,9 @@ class DecodeGraph:
             self.hf["uniform"][:n] = uniform
             self.hf["temperature"][n:] = 0.0
         self._fill_padding(n)
-        h["decode_split"][0] = self._split_policy(n, int(pos.max()) + 1)
+        longest = int(pos.max()) + 1
+        for name, rule in self._scalar_rules.items():
+            h[f"scalar:{name}"][0] = rule(n, longest)
 
     def launch(self, tokens: list[int]) -> torch.Tensor:
         """The token ids of the filled step, one upload, the replay.  Returns the sampled tokens."""
@@ -314,13 +320,14 @@ class ModelRunner:
         self.model = model
         self.cache = cache
         self.device = model.device
-        self.status = cache.status if cache.status is not None else ops.new_status(self.device)
+        self.status = cache.status if cache.status is not None else ops.device_status(self.device)
         self.builder = StepBuilder(cache, model.dtype, self.device, self.status)
         self.steps_run = 0
         self.graphs: dict[tuple[int, bool, int], DecodeGraph] = {}  # (batch bucket, greedy, context tier)
         self.graph_max_ctx = 0  # set by enable_graphs
         self.graph_max_batch = 0
         self.graph_kernel_launches = 0  # kernels replayed through graphs (for accounting)
+        self.last_graph: DecodeGraph | None = None  # the graph of the last captured step that ran
         self.last_upload_bytes = 0
 
     def enable_graphs(self, max_ctx: int, max_batch: int) -> bool:
@@ -329,6 +336,7 @@ class ModelRunner:
         if not self.model.graph_safe() or self.cache.state.needs:
             return False
         self.graph_max_ctx, self.graph_max_batch = max_ctx, max_batch
+        self.model.reserve_for_steps(max_batch, max_ctx)  # scratch that captured graphs point at is set up once
         return True
 
     def can_use_graph(self, entries: list[StepEntry]) -> bool:
@@ -379,6 +387,7 @@ class ModelRunner:
         graph, reqs = prepared
         cache = self.cache
         out = graph.launch(tokens)
+        self.last_graph = graph
         self.graph_kernel_launches += graph.kernels
         self.last_upload_bytes = graph.upload_bytes
         for r in reqs:
@@ -401,5 +410,7 @@ class ModelRunner:
         return logits
 
     def check_status(self) -> None:
-        """Raise if any kernel reported an out-of-range index since the last check."""
+        """Raise if any kernel of a step reported since the last check: an index out of range (which
+        it skipped) or a device-side wait that gave up.  The step's kernels, the tensor-core products
+        included, all report into the device's one status word (``ops.device_status``)."""
         ops.raise_on_status(self.status)

@@ -122,8 +122,29 @@ class Qwen2Config:
         return raw
 
 
+def _shape(**sizes) -> dict[str, Any]:
+    return dict(sizes, architectures=["Qwen2ForCausalLM"], model_type="qwen2", hidden_act="silu", use_sliding_window=False)
+
+
 class Qwen2Architecture:
     name = "Qwen2ForCausalLM"
+
+    # config.json contents of the sizes that the benchmarks and the command line know by name
+    named_shapes = {
+        "qwen2.5-1.5b": _shape(num_hidden_layers=28, hidden_size=1536, num_attention_heads=12, num_key_value_heads=2,
+                               head_dim=128, intermediate_size=8960, vocab_size=151936, rope_theta=1000000.0,
+                               rms_norm_eps=1e-6, tie_word_embeddings=True, max_position_embeddings=32768),
+        "qwen2.5-7b": _shape(num_hidden_layers=28, hidden_size=3584, num_attention_heads=28, num_key_value_heads=4,
+                             head_dim=128, intermediate_size=18944, vocab_size=152064, rope_theta=1000000.0,
+                             rms_norm_eps=1e-6, tie_word_embeddings=False, max_position_embeddings=32768),
+        "qwen2.5-32b": _shape(num_hidden_layers=64, hidden_size=5120, num_attention_heads=40, num_key_value_heads=8,
+                              head_dim=128, intermediate_size=27648, vocab_size=152064, rope_theta=1000000.0,
+                              rms_norm_eps=1e-5, tie_word_embeddings=False, max_position_embeddings=32768),
+        "tiny": _shape(num_hidden_layers=2, hidden_size=64, num_attention_heads=4, num_key_value_heads=2, head_dim=16,
+                       intermediate_size=128, vocab_size=256, rope_theta=10000.0, rms_norm_eps=1e-6,
+                       tie_word_embeddings=True, max_position_embeddings=256),
+    }
+    layer_count_key = "num_hidden_layers"  # the config.json key that a "fewer layers" option changes
 
     def parse_config(self, raw: dict[str, Any]) -> Qwen2Config:
         return Qwen2Config.from_raw(raw)

@@ -9,7 +9,7 @@ import torch
 from .library import KernelLibraryError, check, library
 
 __all__ = [
-    "KernelLibraryError", "library", "dtype_code", "new_status", "raise_on_status",
+    "KernelLibraryError", "library", "dtype_code", "new_status", "device_status", "raise_on_status",
     "embed", "add_rmsnorm", "rmsnorm_rows", "silu_mul", "add_to_residual", "gemm_ref",
     "gemm_ref_swiglu", "rope_store", "copy_pages", "attention_ref", "argmax", "sample",
 ]
@@ -54,6 +54,22 @@ def _need(t: torch.Tensor, dtype: torch.dtype | None, name: str, ndim: int | Non
 
 def new_status(device) -> torch.Tensor:
     return torch.zeros(4, dtype=torch.int32, device=device)
+
+
+_device_status: dict[int, torch.Tensor] = {}
+
+
+def device_status(device) -> torch.Tensor:
+    """The one status word set of a device that the engine's kernels report into: the cache manager,
+    the step function and the tensor-core products all hand this to their kernels, so that one read
+    (``raise_on_status``) sees whatever any of them recorded.  Never freed (captured graphs hold its
+    address)."""
+    device = torch.device(device)
+    index = device.index if device.index is not None else torch.cuda.current_device()
+    status = _device_status.get(index)
+    if status is None:
+        status = _device_status[index] = new_status(torch.device("cuda", index))
+    return status
 
 
 def raise_on_status(status: torch.Tensor) -> None:

@@ -23,6 +23,21 @@ def decode_kernel_takes(ctx, qkv: torch.Tensor, view, num_heads: int, num_kv_hea
             and _decode.accepts(ctx, view, num_heads, num_kv_heads, head_dim, window))
 
 
+def decode_split_name(num_heads: int, num_kv_heads: int, head_dim: int) -> str:
+    """Name of the per-step device scalar (``Part.step_scalars``) that holds the tokens per CTA of the
+    decode kernel for layers of these sizes."""
+    return f"attention_decode_split/{num_heads}/{num_kv_heads}/{head_dim}"
+
+
+def decode_split(num_seqs: int, num_heads: int, num_kv_heads: int, max_ctx: int, device, head_dim: int) -> int:
+    return _attention_fast_module.decode_split(num_seqs, num_heads, num_kv_heads, max_ctx, device, head_dim)
+
+
+def reserve_decode_scratch(device, max_seqs: int, num_heads: int, num_kv_heads: int, head_dim: int, max_ctx: int) -> None:
+    if head_dim in _attention_fast_module.DECODE_HEAD_DIMS:
+        _attention_fast_module.reserve_decode_scratch(device, max_seqs, num_heads, num_kv_heads, head_dim, max_ctx)
+
+
 def paged_attention(ctx, qkv: torch.Tensor, view, num_heads: int, num_kv_heads: int, head_dim: int,
                     scale: float, window: int | None, fused_position=None) -> torch.Tensor:
     """``fused_position`` = (inv_freq or None, rotary_dim): q and k in ``qkv`` are still raw and the new

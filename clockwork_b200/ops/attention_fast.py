@@ -46,10 +46,19 @@ def _configure() -> None:
     _configured = True
 
 
+_retired_scratch: list[dict] = []  # superseded sets: captured graphs may still point at them
+
+
 def _decode_scratch(device: torch.device, part_o: int, part_lse: int, counters: int) -> dict:
+    """The split-merge scratch of the decode kernel (float32 partial outputs and log-sum-exps, arrival
+    counters that are zero between launches), one set per device, replaced by a larger one when a call
+    needs more.  A set that was ever handed out is never freed: a captured CUDA graph has its addresses
+    baked in, and memory given back to the allocator would be handed to other tensors under it."""
     index = device.index if device.index is not None else torch.cuda.current_device()
     st = _scratch.get(index)
     if st is None or st["part_o"].numel() < part_o or st["part_lse"].numel() < part_lse or st["counters"].numel() < counters:
+        if st is not None:
+            _retired_scratch.append(st)
         st = {
             "part_o": torch.empty(max(part_o, 1 << 20), dtype=torch.float32, device=device),
             "part_lse": torch.empty(max(part_lse, 1 << 14), dtype=torch.float32, device=device),
@@ -57,6 +66,17 @@ def _decode_scratch(device: torch.device, part_o: int, part_lse: int, counters: 
         }
         _scratch[index] = st
     return st
+
+
+def reserve_decode_scratch(device, max_seqs: int, num_heads: int, num_kv_heads: int, head_dim: int, max_ctx: int) -> None:
+    """Size the device's scratch once for the largest decode step that will run (called before steps
+    are captured), so that captured graphs share one set."""
+    _configure()
+    device = torch.device(device)
+    po, pl, pc = c_longlong(0), c_longlong(0), c_int(0)
+    library().cw_attention_decode_workspace(int(max_seqs), num_heads, num_kv_heads, head_dim, int(max_ctx),
+                                            byref(po), byref(pl), byref(pc))
+    _decode_scratch(device, po.value, pl.value, pc.value)
 
 
 MIN_SPLIT = 128
@@ -124,7 +144,8 @@ class _Decode:
     @staticmethod
     def run(ctx, qkv, view, num_heads, num_kv_heads, head_dim, scale, window, max_ctx: int | None = None,
             fused_position=None) -> torch.Tensor:
-        split_dev = ctx.extras.get("decode_split")  # a device scalar that a captured graph refreshes per step
+        # a device scalar that a captured step refreshes before every replay, when there is one
+        split_dev = ctx.extras.get(dispatch.decode_split_name(num_heads, num_kv_heads, head_dim))
         split = None if split_dev is not None else decode_split(ctx.num_seqs, num_heads, num_kv_heads, ctx.max_ctx_len, qkv.device, head_dim)
         return attention_decode(qkv, view.k_cache, view.v_cache, view.block_tables, ctx.ctx_lens, num_heads,
                                 num_kv_heads, head_dim, scale, window, max_ctx or ctx.max_ctx_len, ctx.status,

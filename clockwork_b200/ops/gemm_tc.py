@@ -11,7 +11,7 @@ from ctypes import POINTER, byref, c_float, c_int, c_longlong, c_void_p
 
 import torch
 
-from . import EPILOGUE_STORE, _need, _ptr, _stream, gemm as gemm_dispatch, new_status
+from . import EPILOGUE_STORE, _need, _ptr, _stream, device_status, gemm as gemm_dispatch
 from .library import check, library
 
 _state: dict[int, dict] = {}
@@ -64,7 +64,7 @@ def _device_state(device: torch.device) -> dict:
     st = _state.get(index)
     if st is None:
         st = {
-            "status": new_status(device),
+            "status": device_status(device),  # the word the engine reads after its steps
             "sms": torch.cuda.get_device_properties(device).multi_processor_count,
         }
         _state[index] = st

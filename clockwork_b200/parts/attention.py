@@ -50,6 +50,19 @@ class Attention(Mixer):
     def cache_need(self) -> PagedKVNeed:
         return PagedKVNeed(self.num_kv_heads, self.head_dim, int(self.window) if self.window else None)
 
+    def step_scalars(self):
+        """How finely the decode kernel cuts contexts is decided per step from the live requests."""
+        nh, nkv, hd, device = self.num_heads, self.num_kv_heads, self.head_dim, self.device
+        if self.dtype != torch.bfloat16:
+            return {}
+        return {attention_ops.decode_split_name(nh, nkv, hd):
+                lambda num_seqs, max_ctx: attention_ops.decode_split(num_seqs, nh, nkv, max_ctx, device, hd)}
+
+    def reserve_for_steps(self, max_seqs: int, max_ctx: int) -> None:
+        if self.dtype == torch.bfloat16:
+            attention_ops.reserve_decode_scratch(self.device, max_seqs, self.num_heads, self.num_kv_heads,
+                                                 self.head_dim, max_ctx)
+
     def tensor_decls(self):
         q_out, kv_out = self.num_heads * self.head_dim, self.num_kv_heads * self.head_dim
         for proj, out in (("q_proj", q_out), ("k_proj", kv_out), ("v_proj", kv_out)):

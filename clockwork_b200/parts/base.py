@@ -164,6 +164,20 @@ class Part:
     def load_weights(self, fetch: Fetch) -> None:
         pass
 
+    # ---- optional hooks for steps that are captured in CUDA graphs ------------------------------
+    def step_scalars(self) -> dict[str, Callable[[int, int], int]]:
+        """int32 values that the part's kernels read from device memory and that change from step to
+        step: ``name -> f(live requests, longest live context)``.  A captured step keeps one word per
+        name in its input buffer, refreshes it before every replay and hands the word's device view to
+        the parts as ``ctx.extras[name]``; in an uncaptured step the name is absent and the part
+        computes the value on the host.  Parts that want the same value use the same name."""
+        return {}
+
+    def reserve_for_steps(self, max_seqs: int, max_ctx: int) -> None:
+        """Called once before steps are captured: set up whatever scratch memory a single-token step
+        of up to ``max_seqs`` requests with contexts up to ``max_ctx`` needs, so that no buffer a
+        captured graph points at is replaced later."""
+
 
 class Norm(Part):
     def forward(self, stream: ResidualStream, status: torch.Tensor, lazy: bool = False):
@@ -207,3 +221,7 @@ class Block(Part):
     def first_norm(self):
         """The norm this block applies to the incoming residual first, or None."""
         return None
+
+    def parts(self) -> tuple:
+        """The parts the block is made of (for hooks that are collected over a whole model)."""
+        return ()

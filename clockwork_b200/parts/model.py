@@ -53,21 +53,23 @@ class DecoderModel:
         """Whether a step of this model may be captured in a CUDA graph."""
         return all(block.graph_safe for block in self.blocks) and self.final_norm.graph_safe
 
-    def decode_split_policy(self):
-        """f(live requests, longest live context) -> tokens per CTA for the decode attention of a
-        captured step (the layers' mixers share one value; the finest wish wins)."""
-        from ..ops.attention_fast import MIN_SPLIT, decode_split
+    def all_parts(self):
+        """Every part of every block, and the final norm."""
+        for block in self.blocks:
+            yield from block.parts()
+        yield self.final_norm
 
-        shapes = {(b.mixer.num_heads, b.mixer.num_kv_heads, getattr(b.mixer, "head_dim", 128)) for b in self.blocks
-                  if hasattr(b.mixer, "num_kv_heads")}
-        device = self.device
+    def step_scalars(self) -> dict:
+        """The per-step device scalars that the model's parts declare (``Part.step_scalars``), by name."""
+        scalars: dict = {}
+        for part in self.all_parts():
+            for name, rule in part.step_scalars().items():
+                scalars.setdefault(name, rule)
+        return scalars
 
-        def policy(num_seqs: int, max_ctx: int) -> int:
-            if not shapes:
-                return MIN_SPLIT
-            return min(decode_split(num_seqs, nh, nkv, max_ctx, device, hd) for nh, nkv, hd in shapes)
-
-        return policy
+    def reserve_for_steps(self, max_seqs: int, max_ctx: int) -> None:
+        for part in self.all_parts():
+            part.reserve_for_steps(max_seqs, max_ctx)
 
     # ---- weights ---------------------------------------------------------------------------
     def tensor_decls(self) -> list[TensorDecl]:

@@ -130,16 +130,31 @@ def decoder_layer(h, w, i, config, positions, rnd=exact):
     return h
 
 
-def all_position_logits(config, w, token_ids, rnd=exact):
-    """[T, vocab] logits of one whole sequence (clockwork/engine/model.py:193-204, 220-233)."""
+def final_hidden_states(config, w, token_ids, rnd=exact):
+    """[T, hidden] after the last layer and the final norm (clockwork/engine/model.py:193-204)."""
     ids = torch.as_tensor(token_ids, dtype=torch.long)
     positions = torch.arange(ids.shape[0])
     h = w["model.embed_tokens.weight"][ids]
     for i in range(config["num_hidden_layers"]):
         h = decoder_layer(h, w, i, config, positions, rnd=rnd)
-    h = rnd(rms_norm(h, w["model.norm.weight"], config["rms_norm_eps"]))
-    head = w["model.embed_tokens.weight"] if config.get("tie_word_embeddings", False) else w["lm_head.weight"]
-    return h @ head.T
+    return rnd(rms_norm(h, w["model.norm.weight"], config["rms_norm_eps"]))
+
+
+def output_head(config, w):
+    # clockwork/engine/model.py:216-218: the head is the embedding matrix when the model ties them
+    return w["model.embed_tokens.weight"] if config.get("tie_word_embeddings", False) else w["lm_head.weight"]
+
+
+def logits_at(config, w, token_ids, rows, rnd=exact):
+    """[len(rows), vocab] logits of one whole sequence at the given positions only
+    (clockwork/engine/model.py:229-233 applies the head to the selected rows)."""
+    h = final_hidden_states(config, w, token_ids, rnd=rnd)
+    return h[torch.as_tensor(rows, dtype=torch.long)] @ output_head(config, w).T
+
+
+def all_position_logits(config, w, token_ids, rnd=exact):
+    """[T, vocab] logits of one whole sequence (clockwork/engine/model.py:193-204, 220-233)."""
+    return final_hidden_states(config, w, token_ids, rnd=rnd) @ output_head(config, w).T
 
 
 def greedy_generate(config, w, prompt, num_new):

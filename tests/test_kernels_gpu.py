@@ -491,6 +491,52 @@ def test_attention_decode_kernel(ops, status, fast, nh, nkv, hd, ps, window):
     ops.raise_on_status(status)
 
 
+def test_attention_decode_scratch_outlives_captured_graphs(ops, status, fast):
+    """A captured graph has the addresses of the split-merge scratch baked in.  A later, larger call
+    makes the module take a larger scratch set; the set the graph points at must stay alive and its
+    counters intact, so that replaying the older graph still merges its splits (contexts spanning
+    several splits) and equals the uncaptured call."""
+    nh, nkv, hd, ps = 12, 2, 128, 16
+    ctx_lens = [900, 130, 517, 1024]
+    k_cache, v_cache, tables, ks, vs = paged_setup(ctx_lens, nkv, hd, ps, torch.bfloat16, seed=21)
+    g = torch.Generator().manual_seed(5)
+    q = (torch.randn(len(ctx_lens), (nh + 2 * nkv) * hd, generator=g) * 2).bfloat16().to(DEV)
+    kc, vc, tb = k_cache.to(DEV), v_cache.to(DEV), tables.to(DEV)
+    ctx = torch.tensor(ctx_lens, dtype=torch.int32, device=DEV)
+
+    def call():
+        return fast.attention_decode(q, kc, vc, tb, ctx, nh, nkv, hd, hd**-0.5, None, 1024, status, split=128)
+
+    eager = call().clone()
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        captured = call()
+    graph.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(captured, eager)
+    # a call that needs more scratch than any before it: 64 requests whose contexts are bounded (the
+    # bound sizes the grid and the scratch, the contexts themselves stay short) beyond what is there
+    before = fast._scratch[torch.cuda.current_device()]
+    bound = (before["part_o"].numel() // (64 * nh * hd) + 2) * fast.MIN_SPLIT
+    big_ctx = [100] * 64
+    bk, bv, bt, _, _ = paged_setup(big_ctx, nkv, hd, ps, torch.bfloat16, seed=22)
+    bq = torch.randn(64, (nh + 2 * nkv) * hd, generator=g).bfloat16().to(DEV)
+    fast.attention_decode(bq, bk.to(DEV), bv.to(DEV), bt.to(DEV), torch.tensor(big_ctx, dtype=torch.int32, device=DEV),
+                          nh, nkv, hd, hd**-0.5, None, bound, status)
+    assert fast._scratch[torch.cuda.current_device()] is not before, "the larger call was meant to outgrow the scratch"
+    # whatever the allocator hands out now must not be the memory the graph still uses
+    junk = [torch.full((1 << 20,), 7.0, device=DEV) for _ in range(12)] + [torch.full((1 << 14,), 3, dtype=torch.int32, device=DEV) for _ in range(8)]
+    torch.cuda.synchronize()
+    captured.zero_()
+    for _ in range(3):
+        graph.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(captured, eager)
+    assert all(float(t.float().min()) == float(t.float().max()) for t in junk)  # and the graph wrote into none of it
+    ops.raise_on_status(status)
+
+
 def test_attention_decode_finds_one_far_key(ops, status, fast):
     nh, nkv, hd, ps, ctx = 4, 1, 64, 16, 1000
     for far in (3, 255, 256, 777, 999):

@@ -1,0 +1,308 @@
+"""The layer sizes that the benchmark times (Qwen2.5-1.5B: hidden 1536, 12 query and 2 KV heads of 128,
+feed-forward 8960, vocabulary 151936, tied head) against the plain implementation, in float32 and
+bfloat16.  At these sizes the product path takes kernels and schedules that the tiny configurations
+never reach: products whose inner dimension is split over thread-block clusters, the norm split over
+two products' epilogues, the logits product that walks 1,187 weight tiles, decode attention with two
+KV heads of 128 in its two- and three-CTA forms, captured decode graphs per batch bucket (8, 32, 64
+rows, some of them padding) and per context tier (a request that grows past 1,024 tokens moves the
+step to the next tier's graph).
+
+Two of the 28 layers are built (every size of a layer is the real one; the layer count is not a size
+of any kernel), plus, once, all 28 layers in float32 on one short prompt.  The reference gates on the
+real model in the same way (``tests/test_hf_equivalence.py:99-105``, ``174-218``).  Random weights
+with the q and k projections scaled up, so that attention is peaked and a key that is missed,
+misplaced or merged with a wrong weight moves the logits beyond the tolerance.
+"""
+
+import json
+
+import pytest
+import torch
+
+from tests.plain import qwen2_plain as plain
+from tests.test_replay_gpu import check
+from tests.trace_tools import TraceBuilder, cut, round_up, run_trace
+
+pytestmark = pytest.mark.gpu
+
+SHAPE = "qwen2.5-1.5b"
+PAGE = 16
+SHARPEN = 3.0
+
+
+def real_config(num_layers: int) -> dict:
+    from clockwork_b200 import models  # noqa: F401  (registers the architecture and its named sizes)
+    from clockwork_b200.config.registry import shape_config
+
+    return shape_config(SHAPE, num_layers)
+
+
+def tokens(n: int, salt: int, vocab: int = 151936) -> list[int]:
+    state, out = (2654435761 * (salt + 1) + 97 * n) & 0x7FFFFFFF, []
+    for _ in range(n):
+        state = (1103515245 * state + 12345) & 0x7FFFFFFF
+        out.append((state >> 8) % vocab)
+    return out
+
+
+def write_sharp_model(folder, config: dict, seed: int):
+    """config.json + model.safetensors with random bfloat16 weights, q and k projections scaled up."""
+    from clockwork_b200.config.registry import spec_from_raw
+    from clockwork_b200.parts.model import tensor_decls_for_spec
+    from clockwork_b200.weights import save_safetensors
+    from clockwork_b200.weights.random_init import draw_tensor
+
+    tensors = {}
+    for decl in tensor_decls_for_spec(spec_from_raw(config)):
+        if decl.optional:
+            continue
+        t = draw_tensor(decl, seed)
+        if ".q_proj." in decl.name or ".k_proj." in decl.name:
+            t = t * SHARPEN
+        tensors[decl.name] = t.to(torch.bfloat16)
+    (folder / "config.json").write_text(json.dumps(config))
+    save_safetensors(folder / "model.safetensors", tensors)
+    return folder
+
+
+@pytest.fixture(scope="module")
+def two_layer_dir(tmp_path_factory):
+    return write_sharp_model(tmp_path_factory.mktemp("real_2_of_28"), real_config(2), seed=11)
+
+
+@pytest.fixture(scope="module")
+def references(two_layer_dir):
+    """Logits of the plain implementation at the asked positions: for a bfloat16 run (float32, the same
+    with activations rounded to bfloat16); for a float32 run (float64, float32).  With inner dimensions
+    of 1,536 and 8,960 and peaked attention, float32 arithmetic alone moves these logits by more than
+    1e-5 (the plain implementation in float32 differs from itself in float64 by 2e-5), so the float32
+    engine is held to the derived rule too: at most 2.5 times as far from the float64 result as the
+    plain float32 result is."""
+    config, weights32 = plain.read_model_dir(two_layer_dir)
+    weights64 = {k: v.double() for k, v in weights32.items()}
+    hidden = {}
+
+    def get(toks, rows, dtype):
+        key = (tuple(toks), dtype)
+        if key not in hidden:
+            if dtype == "float32":
+                hidden[key] = (plain.final_hidden_states(config, weights64, toks),
+                               plain.final_hidden_states(config, weights32, toks).double())
+            else:
+                hidden[key] = (plain.final_hidden_states(config, weights32, toks),
+                               plain.final_hidden_states(config, weights32, toks, rnd=plain.to_bfloat16_and_back))
+        index = torch.as_tensor(rows, dtype=torch.long)
+        exact, rounded = hidden[key]
+        head64 = plain.output_head(config, weights64).T
+        head32 = plain.output_head(config, weights32).T
+        if dtype == "float32":
+            return (exact[index] @ head64).float(), (rounded[index].float() @ head32)
+        return exact[index] @ head32, rounded[index] @ head32
+
+    return get
+
+
+class SparseTrace(TraceBuilder):
+    """A trace that wants logits at chosen places only (a row of 151,936 floats is 600 KB)."""
+
+    def __init__(self) -> None:
+        super().__init__()
+        self.wanted: dict[str, list[int]] = {}  # request -> positions whose logits were asked for, in order
+
+    def sparse_step(self, portions, end=(), fork=()):
+        """portions: (request, tokens, places among them whose logits are wanted)."""
+        super().step([(rid, toks, False) for rid, toks, _ in portions], end=end, fork=fork)
+        record, starts = self.steps[-1], self._starts[-1]
+        for entry, (rid, toks, want) in zip(record["entries"], portions):
+            entry["want"] = sorted(want)
+            self.wanted.setdefault(rid, []).extend(starts[rid] + w for w in sorted(want))
+
+    def gather_wanted(self, outputs, rid):
+        where = {}
+        for record, starts in zip(self.steps, self._starts):
+            row = 0
+            for e in record["entries"]:
+                for w in e["want"]:
+                    if e["id"] == rid:
+                        where[starts[rid] + w] = (record["step"], row)
+                    row += 1
+        rows = [outputs[where[pos][0]][where[pos][1]] for pos in self.wanted[rid]]
+        return torch.from_numpy(__import__("numpy").stack(rows))
+
+
+def some_places(n: int, every: int = 37) -> list[int]:
+    """The first, the last and every ``every``-th place of a portion."""
+    return sorted({0, n - 1, *range(every - 1, n, every)})
+
+
+def compare(trace: SparseTrace, out, seqs: dict, references, dtype: str, what: str) -> None:
+    for rid, toks in seqs.items():
+        if rid in trace.wanted:
+            check(trace.gather_wanted(out, rid), references(toks, trace.wanted[rid], dtype), dtype, f"{what} {dtype} {rid}",
+                  derived_float32=True)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_replay_families_at_real_layer_sizes_2_of_28_layers(dtype, two_layer_dir, references, tmp_path):
+    """Whole; most in one step and the tail one by one across the 1,024-token tier of the decode graphs;
+    portions of changing size down to two tokens; and four live requests mixed in a pool that reuses pages."""
+    seqs = {"whole": tokens(600, 1), "tail": tokens(1052, 2), "cuts": tokens(900, 3)}
+    tr = SparseTrace()
+    tr.sparse_step([("whole", seqs["whole"], some_places(600) + [63, 64, 127, 128, 255, 256, 511, 512])], end=["whole"])
+    tr.sparse_step([("tail", seqs["tail"][:1004], [0, 500, 1003])])
+    for i, t in enumerate(seqs["tail"][1004:]):   # 48 single tokens: contexts 1,005 .. 1,052 (graphs of two tiers)
+        tr.sparse_step([("tail", [t], [0])], end=["tail"] if 1004 + i == 1051 else [])
+    portions = cut(seqs["cuts"], [130, 2, 257, 7, 64, 2, 129, 1, 16, 300])
+    for i, portion in enumerate(portions):
+        tr.sparse_step([("cuts", portion, some_places(len(portion)))], end=["cuts"] if i == len(portions) - 1 else [])
+    # mixed: six requests, at most four live, portions beside single tokens, requests sitting steps out
+    lengths = [300, 170, 410, 220, 140, 260]
+    mixed = {f"m{i}": tokens(n, 10 + i) for i, n in enumerate(lengths)}
+    sizes = {"m0": [90, 2, 130], "m1": [33, 2, 60], "m2": [2, 257, 3, 64], "m3": [129, 50], "m4": [40, 2, 25], "m5": [200, 2, 7]}
+    waiting, live = list(mixed), []
+    pos = {rid: 0 for rid in mixed}
+    turn = {rid: 0 for rid in mixed}
+    peak, n = 0, 0
+    while waiting or live:
+        while waiting and len(live) < 4 and (n % 3 == 0 or not live):
+            live.append(waiting.pop(0))
+        step, ended = [], []
+        for k, rid in enumerate(list(live)):
+            if (n + k) % 5 == 4 and len(live) > 1:
+                continue
+            left = len(mixed[rid]) - pos[rid]
+            size = 1 if left <= 16 else min(sizes[rid][turn[rid] % len(sizes[rid])], left - 16)
+            turn[rid] += 1
+            step.append((rid, mixed[rid][pos[rid] : pos[rid] + size], some_places(size, 29)))
+            pos[rid] += size
+            if pos[rid] == len(mixed[rid]):
+                ended.append(rid)
+        peak = max(peak, sum(round_up(pos[r], 64) for r in live))
+        tr.sparse_step(step, end=ended)
+        for rid in ended:
+            live.remove(rid)
+        n += 1
+    assert peak < sum(round_up(n, 64) for n in lengths)  # so pages are used again
+    seqs.update(mixed)
+    budget = max(round_up(1052, 64), peak)
+    out = run_trace(two_layer_dir, dtype, budget, tr.steps, tmp_path / "out", 151936, PAGE, timeout=900)
+    compare(tr, out, seqs, references, dtype, "real sizes")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_captured_decode_graphs_at_real_layer_sizes_2_of_28_layers(dtype, two_layer_dir, references, tmp_path):
+    """Single-token steps of 8, then 20, then 40 live requests replay the captured graphs of the 8-, 32-
+    and 64-row buckets (the last two with padding rows, and with the three-CTA attention variant that is
+    taken from 17 requests on).  Three requests start below 1,024 tokens and grow past it at different
+    steps, so the step moves to the next tier's graph while the other rows stay short; requests join
+    (their prompts ride in a step beside the others' single tokens) and leave, so rows change owners."""
+    long_lens = {"L0": 1000, "L1": 1012, "L2": 1019}
+    seqs = {rid: tokens(n + 45, 50 + i) for i, (rid, n) in enumerate(long_lens.items())}
+    short_ids = [f"s{i}" for i in range(37)]
+    for i, rid in enumerate(short_ids):
+        seqs[rid] = tokens(30 + (i * 13) % 70 + 45, 100 + i)
+    prompt_len = {**long_lens, **{rid: len(seqs[rid]) - 45 for rid in short_ids}}
+    tr = SparseTrace()
+    pos = {rid: 0 for rid in seqs}
+    live: list[str] = []
+    counter = [0]
+    crossings = []  # (live requests, longest context) of every single-token step
+
+    def prompt(rid):
+        n = prompt_len[rid]
+        pos[rid] = n
+        return (rid, seqs[rid][:n], [n - 1])
+
+    def single(rid):
+        # the long requests' logits are always wanted, those of the others every sixth step in turn
+        k = counter[0] + sum(map(ord, rid))
+        want = [0] if rid.startswith("L") or k % 6 == 0 else []
+        p = pos[rid]
+        pos[rid] += 1
+        return (rid, [seqs[rid][p]], want)
+
+    def decode(steps, leaving=()):
+        for i in range(steps):
+            tr.sparse_step([single(rid) for rid in live], end=list(leaving) if i == steps - 1 else [])
+            crossings.append((len(live), max(pos[rid] for rid in live)))
+            counter[0] += 1
+        for rid in leaving:
+            live.remove(rid)
+
+    def join(new):
+        tr.sparse_step([single(rid) for rid in live] + [prompt(rid) for rid in new])  # prompts beside single tokens
+        counter[0] += 1
+        live.extend(new)
+
+    for rid in long_lens:                       # the long prompts, one step each
+        tr.sparse_step([prompt(rid)])
+        live.append(rid)
+    tr.sparse_step([prompt(rid) for rid in short_ids[:5]])
+    live += short_ids[:5]
+    decode(6, leaving=["L2"])                   # 8 live: the 8-row bucket; L2 passes 1,024 tokens in it
+    join(short_ids[5:17])
+    assert len(live) == 19
+    decode(8, leaving=short_ids[1:3] + ["L1"])  # 19 live: the 32-row bucket, 13 rows of padding; L1 passes 1,024
+    join(short_ids[17:37])
+    assert len(live) == 36
+    decode(10, leaving=short_ids[20:26])        # 36 live: the 64-row bucket; L0 passes 1,024
+    decode(12)                                  # 30 live, rows have moved up
+    tr.steps[-1]["end"] = list(live)
+    for bucket_low, bucket_high in ((1, 8), (17, 32), (33, 64)):  # each bucket runs below and above the tier's edge
+        ctxs = [c for n, c in crossings if bucket_low <= n <= bucket_high]
+        assert min(ctxs) <= 1024 < max(ctxs), (bucket_low, bucket_high, ctxs)
+    used = {rid: toks[: pos[rid]] for rid, toks in seqs.items()}
+    assert all(pos[rid] <= len(seqs[rid]) for rid in seqs)
+    budget = sum(round_up(p, 64) for p in pos.values())
+    out = run_trace(two_layer_dir, dtype, budget, tr.steps, tmp_path / "out", 151936, PAGE, timeout=900,
+                    extra_args=("--max-live", "64"))
+    compare(tr, out, used, references, dtype, "decode graphs at real sizes")
+
+
+def test_all_28_layers_in_float32_on_one_prompt(tmp_path):
+    """Once, the whole depth: all 28 layers in true float32 on a 64-token prompt, every position's logits
+    against the plain implementation in float64, at most 2.5 times as far from it as the plain
+    implementation in float32 is (the reference's own gate on the real model is equal greedy tokens)."""
+    folder = write_sharp_model(tmp_path, real_config(28), seed=12)
+    toks = tokens(64, 7)
+    tb = TraceBuilder()
+    tb.step([("a", toks, True)], end=["a"])
+    out = run_trace(folder, "float32", 64, tb.steps, tmp_path / "out", 151936, PAGE, timeout=1200)
+    config, weights = plain.read_model_dir(folder)
+    in_float32 = plain.all_position_logits(config, weights, toks)
+    weights = {k: v.double() for k, v in weights.items()}
+    in_float64 = plain.all_position_logits(config, weights, toks)
+    check(tb.gather(out, "a", 64), (in_float64, in_float32), "float32", "all 28 layers, float32", derived_float32=True)
+
+
+def test_overlapping_kernels_change_nothing_2_of_28_layers(two_layer_dir):
+    """The kernels of a step are launched so that each may begin while its predecessor drains
+    (programmatic dependent launch) and wait, inside, for what they read.  A step must give bit for
+    bit what it gives with that overlap switched off, every time: 40 runs of a 257-token portion
+    behind 132 cached tokens (token tiles whose last one holds a single row, products on CTA pairs
+    and on the persistent kernel), in bfloat16.  A kernel that reads a buffer too early, or reuses a
+    staging buffer that a copy in flight still reads, shows here as a run that differs."""
+    from clockwork_b200.engine.step import StepEntry
+    from clockwork_b200.engine.trace import TraceSession
+    from clockwork_b200.ops.library import library
+
+    toks = tokens(400, 3)
+    session = TraceSession(two_layer_dir, "bfloat16", 512, PAGE, graphs=False)
+    lib = library()
+
+    def run():
+        session.cache.open("c")
+        session.runner.step([StepEntry("c", toks[:130], [])])
+        session.runner.step([StepEntry("c", toks[130:132], [])])
+        out = session.runner.step([StepEntry("c", toks[132:389], [0, 127, 128, 255, 256])]).clone()
+        session.cache.close("c")
+        return out
+
+    try:
+        lib.cw_set_pdl(0)
+        serial = run()
+    finally:
+        lib.cw_set_pdl(1)
+    differing = [i for i in range(40) if not torch.equal(run(), serial)]
+    session.runner.check_status()
+    assert not differing, f"runs {differing} of 40 differ from the run without overlap"
