@@ -446,6 +446,7 @@ def main() -> int:
             if sampler is not None and not dev_ms:
                 sampler.mark()
             l0 = launch_count() + runner.graph_kernel_launches
+            up0 = runner.uploaded_bytes
             t0 = time.perf_counter()
             for _ in range(steps):
                 outs = engine.step()
@@ -453,7 +454,7 @@ def main() -> int:
             torch.cuda.synchronize()
             e2e_s = time.perf_counter() - t0
             e2e_launches = launch_count() + runner.graph_kernel_launches - l0
-            h2d = engine.runner.last_upload_bytes
+            h2d = (runner.uploaded_bytes - up0) / steps  # (steps that only go on from device state upload nothing)
             # ---- device-timed: the same kind of steps enqueued back to back ---------------------------------
             tokens = [[rng.randrange(vocab)] for _ in range(batch)]
             ctx_now = cache.get(ids[0]).num_computed
@@ -568,7 +569,7 @@ def main() -> int:
                              max_num_seqs=decodes + portions)
         runner, cache = engine.runner, engine.cache
         ids = fill(engine, decodes, reps + 4, prompt_len=ctx - 4)
-        engine._ahead = None
+        engine._launched = None
         times = []
         for rep in range(reps + 2):
             entries = [StepEntry(rid, [rng.randrange(vocab)], [0]) for rid in ids]

@@ -68,9 +68,21 @@ class RequestCache:
     writable_len: int = 0  # positions below this need neither a new page nor a copy: the request owns their pages alone
 
 
+REQUEST_STATE_FIELDS = ("position", "last_token", "draws", "seed_lo", "seed_hi", "temperature", "top_k", "top_p")
+
+
 class StateSlots:
-    """Fixed-size per-request state: one row per request in a tensor per cache layer, zeroed
-    when a request takes the slot.  Present (with zero layers) even when no mixer asks for it."""
+    """Per-request state of fixed size.  Every request that holds cache also holds one slot, which
+    names its column in
+
+    * ``request``: an int32 table ``[fields, slots]`` on the device with the request's progress and
+      sampling state, ``{position, last_token, draws, seed (two words), temperature, top_k, top_p}``
+      (floats as their bits).  Single-token steps read their inputs from it and the sampling kernels
+      write the new token back (``csrc/request_state.cu``), so that such a step does not wait for the
+      host.  The reference keeps the same on the host (``clockwork/engine/model_runner.py:46``,
+      ``139-145``: Sequence fields and a CPU generator per request).
+    * one tensor ``[slots, *shape]`` per cache layer whose mixer asked for state of its own
+      (``SlotStateNeed``), zeroed when a request takes the slot.  This architecture has none."""
 
     def __init__(self, needs: dict[int, SlotStateNeed], num_slots: int, device) -> None:
         self.num_slots = num_slots
@@ -78,9 +90,11 @@ class StateSlots:
         self._free = list(range(num_slots - 1, -1, -1))
         self._owner: dict[int, str] = {}
         self.tensors: dict[int, torch.Tensor] = {}
+        self.request: torch.Tensor | None = None
         if device is not None:
             for layer, need in needs.items():
                 self.tensors[layer] = torch.zeros((num_slots, *need.shape), dtype=need.dtype, device=device)
+            self.request = torch.zeros((len(REQUEST_STATE_FIELDS), num_slots), dtype=torch.int32, device=device)
 
     @property
     def num_free(self) -> int:
@@ -156,8 +170,7 @@ class CacheManager:
             req.shared_prefix_pages = len(shared_prefix)
             req.num_tokens = len(shared_prefix) * self.page_size
             req.num_computed = req.num_tokens
-        if self.state.needs:
-            req.state_slot = self.state.take(request_id)
+        req.state_slot = self.state.take(request_id)
         self.requests[request_id] = req
         return req
 
@@ -198,7 +211,7 @@ class CacheManager:
     def can_open(self, num_tokens: int, shared_pages: int = 0) -> bool:
         """Whether a new request of ``num_tokens`` could be given its pages and a state slot with
         the watermark left free."""
-        if self.state.needs and self.state.num_free == 0:
+        if self.state.num_free == 0:
             return False
         need = max(0, self._blocks_for(num_tokens) - shared_pages)
         return all(g.allocator.num_free - need >= self.watermark_pages for g in self.groups)
@@ -275,9 +288,8 @@ class CacheManager:
                 if page != NO_PAGE:
                     group.allocator.incref(page)
         parent.writable_len = 0  # its pages are shared now: the next write must look (and copy)
-        if self.state.needs:
-            child.state_slot = self.state.take(child_id)
-            self.state.copy(parent.state_slot, child.state_slot)
+        child.state_slot = self.state.take(child_id)
+        self.state.copy(parent.state_slot, child.state_slot)
         self.requests[child_id] = child
         return child
 

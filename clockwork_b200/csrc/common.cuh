@@ -31,6 +31,18 @@
 
 typedef __nv_bfloat16 bf16;
 
+// Per-request state on the device (request_state.cu): an int32 table [CW_RS_FIELDS][num_slots], one
+// column per request slot; the float fields are stored as their bits.
+#define CW_RS_POSITION 0     // tokens of the request whose keys and values are in the cache = position of its next token
+#define CW_RS_LAST_TOKEN 1   // the token to feed next (the one sampled last)
+#define CW_RS_DRAWS 2        // tokens sampled so far: the counter of the request's random numbers
+#define CW_RS_SEED_LO 3      // the request's 64-bit seed
+#define CW_RS_SEED_HI 4
+#define CW_RS_TEMPERATURE 5  // float; 0: greedy
+#define CW_RS_TOP_K 6        // 0: off
+#define CW_RS_TOP_P 7        // float
+#define CW_RS_FIELDS 8
+
 __device__ __forceinline__ void cw_report(int* status, int code, int a, int b) {
     if (status != nullptr && atomicCAS(&status[0], 0, code) == 0) {
         status[1] = a;

@@ -20,8 +20,25 @@ __device__ __forceinline__ unsigned ordered_key(float f) {
     return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
 }
 
+// A sampled token leaves through here.  With a request-state table given (request_state.cu) the token
+// also becomes the request's `last token`, and its position and draw counter advance by one: the next
+// step can then be launched before the host has read this one's tokens.
+__device__ __forceinline__ void emit_token(int row, int token, int* __restrict__ out, const int* __restrict__ row_slot,
+                                           int* __restrict__ state, int num_slots) {
+    out[row] = token;
+    if (state != nullptr) {
+        const int slot = row_slot[row];
+        if (slot >= 0 && slot < num_slots) {
+            state[CW_RS_LAST_TOKEN * num_slots + slot] = token;
+            state[CW_RS_POSITION * num_slots + slot] += 1;
+            state[CW_RS_DRAWS * num_slots + slot] += 1;
+        }
+    }
+}
+
 __global__ void __launch_bounds__(ST)
-argmax_kernel(const float* __restrict__ logits, int* __restrict__ out, int V, size_t row_stride) {
+argmax_kernel(const float* __restrict__ logits, int* __restrict__ out, int V, size_t row_stride,
+              const int* __restrict__ row_slot, int* __restrict__ state, int num_slots) {
     __shared__ float bv[32];
     __shared__ int bi[32];
     pdl_launch_dependents();
@@ -51,15 +68,22 @@ argmax_kernel(const float* __restrict__ logits, int* __restrict__ out, int V, si
             const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
             if (ov > best || (ov == best && oi < idx)) { best = ov; idx = oi; }
         }
-        if (lane == 0) out[blockIdx.x] = (idx == 0x7fffffff) ? 0 : idx;
+        if (lane == 0) emit_token(blockIdx.x, (idx == 0x7fffffff) ? 0 : idx, out, row_slot, state, num_slots);
     }
+}
+
+// row_slot / state (both or neither): see emit_token.
+extern "C" int cw_argmax_state(const float* logits, int* out, int R, int V, long long row_stride, const int* row_slot,
+                               int* state, int num_slots, cudaStream_t stream) {
+    if (R == 0) return CW_OK;
+    if (R < 0 || V <= 0 || row_stride < V || (state != nullptr && (row_slot == nullptr || num_slots <= 0))) return CW_ERR_BAD_SIZE;
+    return cw_launch(argmax_kernel, dim3(R), dim3(ST), 0, stream, 1, logits, out, V, (size_t)row_stride, row_slot, state,
+                     num_slots);
 }
 
 extern "C" int cw_argmax(const float* logits, int* out, int R, int V, long long row_stride,
                          cudaStream_t stream) {
-    if (R == 0) return CW_OK;
-    if (R < 0 || V <= 0 || row_stride < V) return CW_ERR_BAD_SIZE;
-    return cw_launch(argmax_kernel, dim3(R), dim3(ST), 0, stream, 1, logits, out, V, (size_t)row_stride);
+    return cw_argmax_state(logits, out, R, V, row_stride, nullptr, nullptr, 0, stream);
 }
 
 __device__ __forceinline__ float block_sum_1024(float v, float* scratch) { return block_sum(v, scratch); }
@@ -67,7 +91,8 @@ __device__ __forceinline__ float block_sum_1024(float v, float* scratch) { retur
 __global__ void __launch_bounds__(ST)
 sample_kernel(const float* __restrict__ logits, const float* __restrict__ temperature,
               const int* __restrict__ top_k, const float* __restrict__ top_p,
-              const float* __restrict__ uniform, int* __restrict__ out, int V, size_t row_stride) {
+              const float* __restrict__ uniform, int* __restrict__ out, int V, size_t row_stride,
+              const int* __restrict__ row_slot, int* __restrict__ state, int num_slots) {
     __shared__ float scratch[33];
     __shared__ float warp_tot[32];
     __shared__ int first_thread, last_thread;
@@ -89,7 +114,7 @@ sample_kernel(const float* __restrict__ logits, const float* __restrict__ temper
         __syncthreads();
         atomicMin(&first_thread, cand);
         __syncthreads();
-        if (tid == 0) out[r] = first_thread == 0x7fffffff ? 0 : first_thread;
+        if (tid == 0) emit_token(r, first_thread == 0x7fffffff ? 0 : first_thread, out, row_slot, state, num_slots);
         return;
     }
     // pass 1: maximum of the scaled logits
@@ -167,7 +192,7 @@ sample_kernel(const float* __restrict__ logits, const float* __restrict__ temper
     // when rounding leaves the target beyond the last kept token, the last owner takes it
     const int owner = first_thread != 0x7fffffff ? first_thread : last_thread;
     if (owner < 0) {
-        if (tid == 0) out[r] = 0;
+        if (tid == 0) emit_token(r, 0, out, row_slot, state, num_slots);
         return;
     }
     if (tid == owner) {
@@ -181,17 +206,23 @@ sample_kernel(const float* __restrict__ logits, const float* __restrict__ temper
                 if (run > target) { pick = i; break; }
             }
         }
-        out[r] = pick >= 0 ? pick : last_kept;
+        emit_token(r, pick >= 0 ? pick : last_kept, out, row_slot, state, num_slots);
     }
+}
+
+extern "C" int cw_sample_state(const float* logits, const float* temperature, const int* top_k, const float* top_p,
+                               const float* uniform, int* out, int R, int V, long long row_stride, const int* row_slot,
+                               int* state, int num_slots, cudaStream_t stream) {
+    if (R == 0) return CW_OK;
+    if (R < 0 || V <= 0 || row_stride < V || (state != nullptr && (row_slot == nullptr || num_slots <= 0))) return CW_ERR_BAD_SIZE;
+    return cw_launch(sample_kernel, dim3(R), dim3(ST), 0, stream, 1, logits, temperature, top_k, top_p, uniform, out, V,
+                     (size_t)row_stride, row_slot, state, num_slots);
 }
 
 extern "C" int cw_sample(const float* logits, const float* temperature, const int* top_k,
                          const float* top_p, const float* uniform, int* out, int R, int V,
                          long long row_stride, cudaStream_t stream) {
-    if (R == 0) return CW_OK;
-    if (R < 0 || V <= 0 || row_stride < V) return CW_ERR_BAD_SIZE;
-    return cw_launch(sample_kernel, dim3(R), dim3(ST), 0, stream, 1, logits, temperature, top_k, top_p, uniform, out, V,
-                     (size_t)row_stride);
+    return cw_sample_state(logits, temperature, top_k, top_p, uniform, out, R, V, row_stride, nullptr, nullptr, 0, stream);
 }
 
 CW_TRACE_TU(sampling)

@@ -1,31 +1,37 @@
-"""Continuous-batching scheduler: decode first, first-come-first-served admission, prompts cut
-into portions under a token budget, preemption by recompute when pages run out.
+"""Continuous batching: which requests run in the next step, and with how many tokens each.
 
-Rules taken from the reference's ``clockwork/scheduler/scheduler.py``:
+The rules are the reference's (``clockwork/scheduler/scheduler.py``), plus portions:
 
-* priority is (arrival, order of adding) and nothing else, so the same inputs give the same
-  schedule (``:57-58``);
-* every running sequence that has a token to decode gets its slot before anything is admitted
-  (``:149-155``); if a slot needs a page and none is free, the latest-arrived running sequence
-  not yet granted a slot this step is preempted, and if none is left the sequence preempts
-  itself (``:98-118``).  Preemption frees its pages, resets its progress, keeps its tokens, and
-  puts it at the front of the waiting queue, first come first served among the preempted
-  (``:79-96``);
-* admission looks at the head of the waiting queue only (``:159-166``): the prefix cache is
-  consulted first, then the sequence needs room in the token budget and pages for all its
-  tokens with the watermark left free; a refused admission undoes the prefix match
-  (``:120-147``);
-* finished and aborted sequences give everything back (``:172-197``).
+* A request's rank is (arrival, order of adding) and nothing else, so equal inputs give equal
+  schedules (``:57-58``).
+* Requests that are running come first (``:149-155``).  One that has a single token left to compute
+  (a decode) gets the slot for it before anything else is decided; if that slot needs a page and
+  the pool has none, the running request of the latest rank that has not been granted its slot yet
+  in this step is preempted, and if no such request is left, the request itself (``:98-118``).
+* Preemption gives the request's pages back, drops its progress, keeps its tokens, and lets it wait
+  in front of every request that has never run, in rank order among the preempted (``:79-96``).
+* Admission is strictly in order: only the first waiting request is looked at (``:159-166``).  The
+  prefix cache is asked first; the request then needs room in the step's token budget and pages for
+  all of its tokens with the watermark left free; if it does not get in, what the prefix cache lent
+  is handed back (``:120-147``).
+* A request that finishes or is aborted gives everything back (``:172-197``).
 
-What differs: the reference admits a prompt whole or not at all, so a prompt longer than the
-budget can never run.  Here a prompt is cut into portions: an admitted sequence takes as many
-of its uncomputed tokens as the step's remaining budget (and ``prefill_chunk_size``) allows, and
-stays running with the rest, which later steps take, before new admissions, in priority order.
-A sequence produces a token only in the step that computes its last uncomputed token.
+What the reference does not have: it admits a prompt whole or not at all, so a prompt longer than
+the budget never runs.  Here a request takes as many of its uncomputed tokens as the rest of the
+budget (and ``prefill_chunk_size``) allows and keeps running with the remainder, which later steps
+take before anybody new is admitted.  A token is sampled only in the step that computes a request's
+last uncomputed token.
+
+How it is kept: ``running`` is always in rank order (a request is inserted at its place when it is
+admitted), requests that wait to be resumed after a preemption are a rank-ordered list of their
+own in front of the first-come queue of requests that have never run, and a dictionary finds a
+request by its id; counters are plain integers read into a ``SchedulerStats`` on demand.
 """
 
 from __future__ import annotations
 
+from bisect import insort
+from collections import deque
 from dataclasses import dataclass, field
 
 from ..cache.manager import CacheManager
@@ -51,7 +57,12 @@ class SchedulerOutput:
     num_batched_tokens: int = 0
 
     def is_empty(self) -> bool:
-        return not (self.portions or self.preempted)
+        return len(self.portions) + len(self.preempted) == 0
+
+    def give(self, seq: Sequence, start: int, count: int, decode: bool) -> None:
+        self.portions.append(ScheduledPortion(seq, start, count, start + count == len(seq)))
+        (self.decode_seqs if decode else self.prefill_seqs).append(seq)
+        self.num_batched_tokens += count
 
 
 @dataclass
@@ -69,227 +80,198 @@ class Scheduler:
         self.cfg = cfg
         self.cache = cache
         self.prefix_cache = prefix_cache
-        self.waiting: list[Sequence] = []
-        self.running: list[Sequence] = []
-        self.stats = SchedulerStats()
-        self._arrival_order: dict[str, int] = {}
-        self._arrival_counter = 0
+        self.running: list[Sequence] = []                     # in rank order
+        self._resuming: list[tuple[tuple, Sequence]] = []     # preempted, waiting to run again: (rank, request), sorted
+        self._arrivals: deque[Sequence] = deque()             # never ran yet, first come first
+        self._rank: dict[str, tuple[float, int]] = {}         # by request id, for everything queued or running
+        self._added = 0
+        self._preemptions = self._batches = self._prompt_tokens = self._cached_tokens = 0
 
-    # ---- queues -------------------------------------------------------------------------------
-    def _priority(self, seq: Sequence) -> tuple[float, int]:
-        return (seq.arrival_time, self._arrival_order.get(seq.seq_id, 0))
+    # ---- what the outside reads ----------------------------------------------------------------------
+    @property
+    def waiting(self) -> list[Sequence]:
+        """Everything that waits, in the order in which it will be looked at."""
+        return [seq for _, seq in self._resuming] + list(self._arrivals)
 
-    def add_seq(self, seq: Sequence) -> None:
-        self._arrival_order[seq.seq_id] = self._arrival_counter
-        self._arrival_counter += 1
-        seq.status = SequenceStatus.WAITING
-        self.waiting.append(seq)
-        self._refresh_counts()
+    @property
+    def stats(self) -> SchedulerStats:
+        return SchedulerStats(len(self._resuming) + len(self._arrivals), len(self.running), self._preemptions,
+                              self._batches, self._prompt_tokens, self._cached_tokens)
 
     def has_unfinished(self) -> bool:
-        return bool(self.waiting or self.running)
+        return bool(self.running or self._arrivals or self._resuming)
 
-    def _refresh_counts(self) -> None:
-        self.stats.num_waiting = len(self.waiting)
-        self.stats.num_running = len(self.running)
+    def add_seq(self, seq: Sequence) -> None:
+        self._rank[seq.seq_id] = (seq.arrival_time, self._added)
+        self._added += 1
+        seq.status = SequenceStatus.WAITING
+        self._arrivals.append(seq)
 
-    # ---- giving memory back ----------------------------------------------------------------------
-    def _free_resources(self, seq: Sequence) -> None:
-        if seq.seq_id not in self.cache.requests:
-            return
-        shared = self.cache.close(seq.seq_id)
-        if shared and self.prefix_cache is not None:
-            self.prefix_cache.release(shared)
+    # ---- letting go ----------------------------------------------------------------------------------
+    def _release(self, seq: Sequence) -> None:
+        """Everything the request holds goes back: its own pages to the pool, borrowed ones to the prefix cache."""
+        if seq.seq_id in self.cache.requests:
+            borrowed = self.cache.close(seq.seq_id)
+            if borrowed and self.prefix_cache is not None:
+                self.prefix_cache.release(borrowed)
 
-    def _preempt(self, seq: Sequence) -> None:
-        self._free_resources(seq)
-        seq.reset_for_recompute()
-        seq.num_cached_tokens = 0
-        seq.status = SequenceStatus.PREEMPTED
-        key = self._priority(seq)
-        i = 0
-        while (i < len(self.waiting) and self.waiting[i].status is SequenceStatus.PREEMPTED
-               and self._priority(self.waiting[i]) < key):
-            i += 1
-        self.waiting.insert(i, seq)
-        self.stats.num_preempted_total += 1
+    def _preempt(self, seq: Sequence, plan: SchedulerOutput) -> None:
+        self._release(seq)
+        seq.rewind()
+        insort(self._resuming, (self._rank[seq.seq_id], seq), key=lambda entry: entry[0])
+        self._preemptions += 1
+        plan.preempted.append(seq)
 
-    # ---- one step's plan -------------------------------------------------------------------------
-    def _chunk(self, uncomputed: int, budget_left: int) -> int:
-        n = min(uncomputed, budget_left)
-        if self.cfg.prefill_chunk_size:
-            n = min(n, self.cfg.prefill_chunk_size)
-        return max(n, 0)
-
-    def _all_decode(self, ordered: list[Sequence], out: SchedulerOutput) -> bool:
-        """The common step of a running batch, decided without the general machinery: every running
-        sequence decodes one token, and the pages for that are there (mostly the token's slot lies in
-        a page the sequence already owns alone; the others get their page here).  Makes the plan the
-        general path would make; returns False, with nothing planned, when a sequence is in the
-        middle of its prompt or the pages run out (the general path then decides whom to preempt;
-        reservations made here stay and are what it would have made first)."""
-        cache = self.cache
-        requests = cache.requests
-        portions = []
-        for seq in ordered:
-            n = len(seq.prompt_token_ids) + len(seq.output_token_ids)
-            req = requests.get(seq.seq_id)
-            if req is None or seq.status is not SequenceStatus.RUNNING or n - seq.num_computed_tokens != 1:
-                return False
-            if n <= req.writable_len:
-                if n > req.num_tokens:
-                    req.num_tokens = n  # what CacheManager.reserve does when nothing has to be allocated
-            elif cache.can_reserve(req, n):
-                cache.reserve(req, n)
+    def free_finished(self) -> None:
+        still = []
+        for seq in self.running:
+            if seq.status.finished:
+                self._release(seq)
+                self._rank.pop(seq.seq_id, None)
             else:
-                return False
-            portions.append(ScheduledPortion(seq, n - 1, 1, True))
-        out.portions.extend(portions)
-        out.decode_seqs.extend(ordered)
-        out.num_batched_tokens += len(ordered)
+                still.append(seq)
+        self.running = still
+
+    def abort(self, seq_id: str) -> None:
+        if seq_id not in self._rank:
+            return
+        del self._rank[seq_id]
+        for i, seq in enumerate(self.running):
+            if seq.seq_id == seq_id:
+                self._release(seq)
+                del self.running[i]
+                seq.status = SequenceStatus.FINISHED_ABORTED
+                return
+        for i, (_, seq) in enumerate(self._resuming):
+            if seq.seq_id == seq_id:
+                del self._resuming[i]
+                seq.status = SequenceStatus.FINISHED_ABORTED
+                return
+        for seq in self._arrivals:
+            if seq.seq_id == seq_id:
+                self._arrivals.remove(seq)
+                seq.status = SequenceStatus.FINISHED_ABORTED
+                return
+
+    # ---- one step's plan -------------------------------------------------------------------------------
+    def _portion(self, uncomputed: int, plan: SchedulerOutput) -> int:
+        """How many of a request's uncomputed tokens this step can still take."""
+        room = self.cfg.max_num_batched_tokens - plan.num_batched_tokens
+        if self.cfg.prefill_chunk_size:
+            room = min(room, self.cfg.prefill_chunk_size)
+        return max(0, min(uncomputed, room))
+
+    def _decode_slot(self, seq: Sequence, total: int) -> bool:
+        """Make sure position ``total - 1`` of a running request has its slot.  Most steps it lies in a
+        page the request owns alone and nothing has to be looked up."""
+        req = self.cache.requests[seq.seq_id]
+        if total <= req.writable_len:
+            if total > req.num_tokens:
+                req.num_tokens = total  # what CacheManager.reserve does when nothing has to be allocated
+            return True
+        if not self.cache.can_reserve(req, total):
+            return False
+        self.cache.reserve(req, total)
         return True
 
-    def plan_next_decode(self, max_model_len: int) -> SchedulerOutput | None:
-        """Called while a decode step of every running sequence is in flight and its tokens are not
-        known yet: the plan of the step after it, under the assumption that no sequence ends and
-        nothing arrives, with the pages it needs reserved; None when that assumption is known to fail
-        (a sequence ends by length, something waits, a sequence is in its prompt, pages run out).
-        The engine drops the plan if the assumption fails after all; the reservations are then
-        what the general path would have made, or belong to sequences that are freed."""
-        if self.waiting or not self.running:
-            return None
-        ordered = sorted(self.running, key=self._priority)
-        cache = self.cache
-        out = SchedulerOutput()
-        for seq in ordered:
-            n = len(seq.prompt_token_ids) + len(seq.output_token_ids)  # without the token in flight
-            req = cache.requests.get(seq.seq_id)
-            if (req is None or seq.status is not SequenceStatus.RUNNING or n - seq.num_computed_tokens != 1
-                    or len(seq.output_token_ids) + 1 >= seq.sampling_params.max_tokens or n + 1 >= max_model_len):
-                return None
-            if n + 1 > req.writable_len:
-                if not cache.can_reserve(req, n + 1):
-                    return None
-                cache.reserve(req, n + 1)
-            elif n + 1 > req.num_tokens:
-                req.num_tokens = n + 1
-            out.portions.append(ScheduledPortion(seq, n, 1, True))
-        out.decode_seqs.extend(ordered)
-        out.num_batched_tokens = len(ordered)
-        return out
+    def _all_decode(self, plan: SchedulerOutput) -> bool:
+        """The common step of a running batch: every running request has exactly one token to compute and
+        the pages for it are there.  Plans what the general path would plan; False, with nothing planned,
+        when a request is in the middle of its prompt or a page is missing (the general path then decides
+        whom to preempt; slots granted here stay granted and are what it would have granted first)."""
+        grants = []
+        for seq in self.running:
+            total = len(seq)
+            if (seq.status is not SequenceStatus.RUNNING or total - seq.num_computed_tokens != 1
+                    or seq.seq_id not in self.cache.requests or not self._decode_slot(seq, total)):
+                return False
+            grants.append((seq, total - 1))
+        for seq, position in grants:
+            plan.give(seq, position, 1, decode=True)
+        return True
 
-    def accept_plan(self, out: SchedulerOutput) -> None:
-        """Bookkeeping of a plan made by ``plan_next_decode`` that the engine now runs as a step."""
-        self.stats.num_scheduled_batches += 1
-        self._refresh_counts()
-
-    def _schedule_running(self, out: SchedulerOutput) -> list[Sequence]:
-        ordered = sorted(self.running, key=self._priority)
-        if ordered and self._all_decode(ordered, out):
-            return ordered
-        kept: list[Sequence] = []
-        # pass 1: decodes, in priority order, each reserving its slot at once so that a later
-        # sequence sees the true pool
-        pending = [s for s in ordered]
-        decodes = [s for s in pending if s.num_uncomputed_tokens() == 1]
-        others = [s for s in pending if s.num_uncomputed_tokens() != 1]
-        victims_pool = list(ordered)  # candidates for preemption, latest arrival last
+    def _plan_running(self, plan: SchedulerOutput) -> None:
+        if self.running and self._all_decode(plan):
+            return
+        # decodes first, in rank order; each takes its slot at once, so that the next sees the true pool
         granted: set[str] = set()
-        for seq in decodes:
-            if seq.status is SequenceStatus.PREEMPTED:
+        for seq in list(self.running):
+            if seq.status is not SequenceStatus.RUNNING or seq.num_uncomputed_tokens() != 1:
                 continue
-            req = self.cache.get(seq.seq_id)
-            while not self.cache.can_reserve(req, len(seq)):
-                victim = None
-                for cand in reversed(victims_pool):
-                    if cand.seq_id not in granted and cand is not seq and cand.status is SequenceStatus.RUNNING:
-                        victim = cand
-                        break
-                if victim is None:
-                    victim = seq
-                victims_pool.remove(victim)
-                self._preempt(victim)
-                out.preempted.append(victim)
+            while not self._decode_slot(seq, len(seq)):
+                victim = next((other for other in reversed(self.running)
+                               if other is not seq and other.status is SequenceStatus.RUNNING and other.seq_id not in granted), seq)
+                self._preempt(victim, plan)
                 if victim is seq:
                     break
-            if seq.status is SequenceStatus.PREEMPTED:
-                continue
-            self.cache.reserve(req, len(seq))
-            granted.add(seq.seq_id)
-            out.portions.append(ScheduledPortion(seq, seq.num_computed_tokens, 1, True))
-            out.decode_seqs.append(seq)
-            out.num_batched_tokens += 1
-        # pass 2: sequences in the middle of their prompt take portions of the remaining budget
-        for seq in others:
-            if seq.status is SequenceStatus.PREEMPTED:
-                continue
-            n = self._chunk(seq.num_uncomputed_tokens(), self.cfg.max_num_batched_tokens - out.num_batched_tokens)
-            if n > 0:
-                out.portions.append(ScheduledPortion(seq, seq.num_computed_tokens, n,
-                                                     n == seq.num_uncomputed_tokens()))
-                out.prefill_seqs.append(seq)
-                out.num_batched_tokens += n
-        for seq in ordered:
             if seq.status is SequenceStatus.RUNNING:
-                kept.append(seq)
-        return kept
+                granted.add(seq.seq_id)
+                plan.give(seq, seq.num_computed_tokens, 1, decode=True)
+        # then the requests that are in the middle of their prompts share what is left of the budget
+        for seq in self.running:
+            if seq.status is SequenceStatus.RUNNING and seq.seq_id not in granted:
+                count = self._portion(seq.num_uncomputed_tokens(), plan)
+                if count:
+                    plan.give(seq, seq.num_computed_tokens, count, decode=False)
+        self.running = [seq for seq in self.running if seq.status is SequenceStatus.RUNNING]
 
-    def _try_admit(self, seq: Sequence, out: SchedulerOutput) -> bool:
-        matched_pages: list[int] = []
-        matched_tokens = 0
+    def _admit_first_waiting(self, plan: SchedulerOutput) -> bool:
+        seq = self._resuming[0][1] if self._resuming else self._arrivals[0]
+        total = len(seq)
+        borrowed, cached = [], 0
         if self.prefix_cache is not None:
-            match = self.prefix_cache.match(seq.token_ids())
-            matched_pages, matched_tokens = match.pages, match.num_tokens
-        uncomputed = len(seq) - matched_tokens
-        n = self._chunk(uncomputed, self.cfg.max_num_batched_tokens - out.num_batched_tokens)
-        fits = n > 0 and self.cache.can_open(len(seq), len(matched_pages))
-        if not fits:
-            if matched_pages and self.prefix_cache is not None:
-                self.prefix_cache.release(matched_pages)
+            hit = self.prefix_cache.match(seq.token_ids())
+            borrowed, cached = hit.pages, hit.num_tokens
+        count = self._portion(total - cached, plan)
+        if count == 0 or not self.cache.can_open(total, len(borrowed)):
+            if borrowed:
+                self.prefix_cache.release(borrowed)  # not admitted: nothing of the look-up stays
             return False
-        req = self.cache.open(seq.seq_id, shared_prefix=matched_pages)
-        self.cache.reserve(req, len(seq))
-        seq.num_cached_tokens = matched_tokens
-        seq.num_computed_tokens = matched_tokens
-        seq.status = SequenceStatus.RUNNING
-        self.stats.total_prompt_tokens += len(seq)
-        self.stats.total_cached_tokens += matched_tokens
-        out.portions.append(ScheduledPortion(seq, matched_tokens, n, n == uncomputed))
-        out.prefill_seqs.append(seq)
-        out.num_batched_tokens += n
+        self.cache.reserve(self.cache.open(seq.seq_id, shared_prefix=borrowed), total)
+        seq.admit(cached)
+        self._prompt_tokens += total
+        self._cached_tokens += cached
+        plan.give(seq, cached, count, decode=False)
+        if self._resuming:
+            self._resuming.pop(0)
+        else:
+            self._arrivals.popleft()
+        insort(self.running, seq, key=lambda s: self._rank[s.seq_id])
         return True
 
     def schedule(self) -> SchedulerOutput:
-        out = SchedulerOutput()
-        self.running = self._schedule_running(out)
-        while self.waiting and len(self.running) < self.cfg.max_num_seqs:
-            seq = self.waiting[0]
-            if not self._try_admit(seq, out):
+        plan = SchedulerOutput()
+        self._plan_running(plan)
+        while (self._resuming or self._arrivals) and len(self.running) < self.cfg.max_num_seqs:
+            if not self._admit_first_waiting(plan):
                 break
-            self.waiting.pop(0)
-            self.running.append(seq)
-        if not out.is_empty():
-            self.stats.num_scheduled_batches += 1
-        self._refresh_counts()
-        return out
+        if not plan.is_empty():
+            self._batches += 1
+        return plan
 
-    # ---- after a step -----------------------------------------------------------------------------
-    def free_finished(self) -> None:
+    # ---- planning one step ahead -------------------------------------------------------------------------
+    def plan_next_decode(self, max_model_len: int) -> SchedulerOutput | None:
+        """Called while a step in which every running request decodes is in flight and its tokens are not
+        known yet: the plan of the step after it, if no request ends and nothing arrives, with the slots it
+        needs granted; None when that cannot be (a request ends by length, something waits, a request is
+        in its prompt, a page is missing).  The engine drops the plan if a request ends after all; the
+        slots granted here are then what the general path would have granted, or belong to requests
+        that are being freed."""
+        if self._arrivals or self._resuming or not self.running:
+            return None
+        plan = SchedulerOutput()
         for seq in self.running:
-            if seq.is_finished():
-                self._free_resources(seq)
-                self._arrival_order.pop(seq.seq_id, None)
-        self.running = [s for s in self.running if not s.is_finished()]
-        self._refresh_counts()
+            total = len(seq) + 1  # with the token that is in flight
+            if (seq.status is not SequenceStatus.RUNNING or total - 1 - seq.num_computed_tokens != 1
+                    or seq.seq_id not in self.cache.requests
+                    or len(seq.output_token_ids) + 1 >= seq.sampling_params.max_tokens or total >= max_model_len
+                    or not self._decode_slot(seq, total)):
+                return None
+            plan.portions.append(ScheduledPortion(seq, total - 1, 1, True))
+        plan.decode_seqs.extend(self.running)
+        plan.num_batched_tokens = len(self.running)
+        return plan
 
-    def abort(self, seq_id: str) -> None:
-        for queue in (self.waiting, self.running):
-            for i, seq in enumerate(queue):
-                if seq.seq_id == seq_id:
-                    if queue is self.running:
-                        self._free_resources(seq)
-                    queue.pop(i)
-                    seq.status = SequenceStatus.FINISHED_ABORTED
-                    self._arrival_order.pop(seq_id, None)
-                    self._refresh_counts()
-                    return
+    def accept_plan(self, plan: SchedulerOutput) -> None:
+        """A plan made by ``plan_next_decode`` is now run as a step."""
+        self._batches += 1

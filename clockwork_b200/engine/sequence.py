@@ -1,13 +1,15 @@
-"""Per-request state shared by the scheduler and the engine.
+"""A request as the scheduler and the engine see it, and what the engine reports about it.
 
-Same fields and meanings as the reference's ``clockwork/engine/sequence.py:10-96``; the block
-table lives in the cache manager (``clockwork_b200/cache/manager.py``) instead of here.
-"""
+The field names and the states are those of the reference's request object
+(``clockwork/engine/sequence.py:10-96``), because the scheduler's rules, the tests and the users of
+``RequestOutput`` speak in them; the block table is not here but in the cache manager
+(``clockwork_b200/cache/manager.py``), and progress is kept as one number that only three verbs
+change: ``admit`` (a prefix came from the cache), ``advance`` (a step computed tokens) and
+``rewind`` (preemption by recompute)."""
 
 from __future__ import annotations
 
 import time
-from dataclasses import dataclass
 from enum import Enum
 
 from ..sampling.params import SamplingParams
@@ -21,62 +23,78 @@ class SequenceStatus(Enum):
     FINISHED_LENGTH = "finished_length"
     FINISHED_ABORTED = "finished_aborted"
 
+    @property
+    def finished(self) -> bool:
+        return self.name.startswith("FINISHED")
 
-_FINISHED = frozenset(
-    {SequenceStatus.FINISHED_STOPPED, SequenceStatus.FINISHED_LENGTH, SequenceStatus.FINISHED_ABORTED}
-)
+    @property
+    def finish_reason(self) -> str | None:
+        return {"FINISHED_STOPPED": "stop", "FINISHED_LENGTH": "length", "FINISHED_ABORTED": "abort"}.get(self.name)
 
 
 class Sequence:
-    """One request's tokens and its progress through the cache."""
+    """One request: its prompt, what it has generated, and how far the cache has got with it."""
+
+    __slots__ = ("seq_id", "prompt_token_ids", "output_token_ids", "sampling_params", "status", "arrival_time",
+                 "num_computed_tokens", "num_cached_tokens", "stop_ids", "length_limit", "state_slot")
 
     def __init__(self, seq_id: str, prompt_token_ids: list[int], sampling_params: SamplingParams | None = None,
                  arrival_time: float | None = None) -> None:
         self.seq_id = seq_id
         self.prompt_token_ids = list(prompt_token_ids)
         self.output_token_ids: list[int] = []
-        self.sampling_params = sampling_params if sampling_params is not None else SamplingParams()
+        self.sampling_params = sampling_params or SamplingParams()
         self.status = SequenceStatus.WAITING
-        self.num_computed_tokens = 0  # tokens whose keys/values are in the cache
-        self.num_cached_tokens = 0  # of those, how many came from the prefix cache at admission
         self.arrival_time = time.monotonic() if arrival_time is None else arrival_time
-        # set by the engine when the request is added: the token ids that end it (None: none does) and
-        # the number of generated tokens at which it ends by length
+        self.num_computed_tokens = 0  # tokens whose keys and values are in the cache
+        self.num_cached_tokens = 0    # how many of them the prefix cache supplied at the last admission
+        # filled in by the engine: the token ids that end the request (None: none does), and the number
+        # of generated tokens at which it ends by length
         self.stop_ids: frozenset[int] | None = None
         self.length_limit: int | None = None
+        self.state_slot: int | None = None  # the request's row in the engine's per-request device state
 
-    def token_ids(self) -> list[int]:
-        return self.prompt_token_ids + self.output_token_ids
-
+    # ---- tokens ------------------------------------------------------------------------------------
     def __len__(self) -> int:
         return len(self.prompt_token_ids) + len(self.output_token_ids)
 
+    def token_ids(self) -> list[int]:
+        return [*self.prompt_token_ids, *self.output_token_ids]
+
     def tokens_between(self, start: int, end: int) -> list[int]:
-        n_prompt = len(self.prompt_token_ids)
-        if end <= n_prompt:
-            return self.prompt_token_ids[start:end]
-        if start >= n_prompt:
-            return self.output_token_ids[start - n_prompt : end - n_prompt]
-        return self.prompt_token_ids[start:] + self.output_token_ids[: end - n_prompt]
+        """Tokens at positions [start, end), wherever the border between prompt and output lies."""
+        border = len(self.prompt_token_ids)
+        head = self.prompt_token_ids[start:end] if start < border else []
+        tail = self.output_token_ids[max(start - border, 0) : end - border] if end > border else []
+        return head + tail if head and tail else (head or tail)
 
     def append_token(self, token_id: int) -> None:
         self.output_token_ids.append(token_id)
 
-    def is_finished(self) -> bool:
-        return self.status in _FINISHED
-
+    # ---- progress ----------------------------------------------------------------------------------
     def num_uncomputed_tokens(self) -> int:
         return len(self) - self.num_computed_tokens
 
-    def reset_for_recompute(self) -> None:
-        """Preemption by recompute keeps the tokens and drops the cache progress
-        (``clockwork/engine/sequence.py:79-82``)."""
-        self.num_computed_tokens = 0
+    def admit(self, cached_tokens: int) -> None:
+        """The request starts (or starts again) running with this many leading tokens already cached."""
+        self.num_cached_tokens = self.num_computed_tokens = cached_tokens
+        self.status = SequenceStatus.RUNNING
+
+    def rewind(self) -> None:
+        """Preemption by recompute: the tokens stay, the cache's progress is dropped, so the next
+        admission computes prompt and output so far again (``clockwork/engine/sequence.py:79-82``)."""
+        self.num_computed_tokens = self.num_cached_tokens = 0
+        self.status = SequenceStatus.PREEMPTED
+
+    reset_for_recompute = rewind
+
+    def is_finished(self) -> bool:
+        return self.status.finished
 
 
 class RequestOutput:
-    """What ``LLMEngine.step`` reports for a request that sampled a token (the reference's
-    ``clockwork/engine/sequence.py`` RequestOutput: ids, text, finish state, counts).
+    """What ``LLMEngine.step`` reports for a request that sampled a token: ids, text, whether and why
+    it finished, counts (the fields of the reference's ``RequestOutput``).
 
     An output holds what was true when it was made (how many tokens were generated, whether and why
     the request finished, the text) and reads the rest from its sequence: ``prompt_token_ids`` is the

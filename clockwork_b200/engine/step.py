@@ -164,43 +164,65 @@ class StepBuilder:
             self.cache.release_behind_window(r, end)
 
 
+def fresh_row(position: int, last_token: int, draws: int = 0, seed: int = 0, temperature: float = 0.0,
+              top_k: int = 0, top_p: float = 1.0) -> tuple:
+    """One request's column of the device state table, in the table's field order, as int32 words."""
+    seed &= (1 << 64) - 1
+    bits = np.array([temperature, top_p], dtype=np.float32).view(np.int32)
+    lo, hi = seed & 0xFFFFFFFF, seed >> 32
+    return (position, last_token, draws, lo - (1 << 32) if lo >= 1 << 31 else lo, hi - (1 << 32) if hi >= 1 << 31 else hi,
+            int(bits[0]), max(0, int(top_k)), int(bits[1]))
+
+
 class DecodeGraph:
-    """One captured CUDA graph of the model's forward pass plus sampling for a fixed number of
-    single-token requests.  Its inputs live in one static int32 buffer that is refilled (one upload)
-    before every replay; rows beyond the live requests are padding (context length 0, slot -1)."""
+    """One captured CUDA graph of a single-token step for a fixed number of rows: the step's inputs are
+    derived on the device from the per-request state table (``csrc/request_state.cu``), then the
+    model's forward pass, then sampling, which writes the new tokens back into the table.
+
+    What the host supplies lives in the front part of one int32 buffer, uploaded in one copy and only
+    when something in it changed: which state slot each row belongs to (< 0: padding), the block-table
+    rows, the parts' per-step scalars, and for rows flagged ``fresh`` the column that overwrites the
+    request's state first (after a prompt or a preemption, or when the caller supplies the token).  A
+    step that only advances the same requests by one token needs no upload."""
 
     def __init__(self, runner: "ModelRunner", batch: int, max_ctx: int, greedy: bool) -> None:
         cache, model = runner.cache, runner.model
         self.batch, self.greedy = batch, greedy
         self.max_blocks = (max_ctx + cache.page_size - 1) // cache.page_size
         G = len(cache.groups)
-        seg, off = {}, 0
+        F = len(ops.REQUEST_STATE_FIELDS)
         # values that the parts' kernels read from device memory and that change with the live requests
-        # (``Part.step_scalars``): one word each, refreshed before every replay
+        # (``Part.step_scalars``): one word each
         self._scalar_rules = model.step_scalars()
-        for name, size in (("tokens", batch), ("positions", batch), ("tok_seq", batch), ("q_start", batch + 1),
-                           ("ctx_lens", batch), ("rows", batch), ("temperature", batch), ("top_k", batch),
-                           ("top_p", batch), ("uniform", batch), *((f"scalar:{name}", 1) for name in self._scalar_rules)):
+        uploaded = [("row_slot", batch), ("fresh", batch), ("fresh_values", F * batch),
+                    *((f"scalar:{name}", 1) for name in self._scalar_rules),
+                    *((f"tables{g}", batch * self.max_blocks) for g in range(G))]
+        derived = [("tokens", batch), ("positions", batch), ("tok_seq", batch), ("ctx_lens", batch), ("temperature", batch),
+                   ("top_k", batch), ("top_p", batch), ("uniform", batch), *((f"slots{g}", batch) for g in range(G)),
+                   ("q_start", batch + 1), ("rows", batch)]
+        seg, off = {}, 0
+        for name, size in uploaded:
             seg[name] = (off, size)
             off += _pad4(size)
-        for g in range(G):
-            seg[f"slots{g}"] = (off, batch)
-            off += _pad4(batch)
-            seg[f"tables{g}"] = (off, batch * self.max_blocks)
-            off += _pad4(batch * self.max_blocks)
+        self.upload_words = off
+        for name, size in derived:
+            seg[name] = (off, size)
+            off += _pad4(size)
         self.seg, self.size = seg, off
-        self.host = torch.zeros(off, dtype=torch.int32, pin_memory=True)
+        self.host = torch.zeros(self.upload_words, dtype=torch.int32, pin_memory=True)
         self.dev = torch.zeros(off, dtype=torch.int32, device=runner.device)
         h = self.host.numpy()
-        self.h = {name: h[o : o + n] for name, (o, n) in seg.items()}
-        self.hf = {name: h[o : o + n].view(np.float32) for name, (o, n) in seg.items()
-                   if name in ("temperature", "top_p", "uniform")}
+        self.h = {name: h[o : o + n] for name, (o, n) in seg.items() if o < self.upload_words}
+        self.h["fresh_values"] = self.h["fresh_values"].reshape(F, batch)
         for g in range(G):
             self.h[f"tables{g}"] = self.h[f"tables{g}"].reshape(batch, self.max_blocks)
-        self.h["q_start"][:] = np.arange(batch + 1)
-        self.h["rows"][:] = np.arange(batch)
-        self.upload_bytes = off * 4
+            self.h[f"tables{g}"][:] = NO_PAGE
+        self.h["row_slot"][:] = -1
+        self.upload_bytes = self.upload_words * 4
+        self.uploads = 0  # how many replays needed an upload
         self._uploaded = torch.cuda.Event()
+        self._dirty = True
+        self._filled = 0
         # which request's table each row holds and how much of it, so that a step writes only the
         # pages a request gained since its last step
         self._row_owner: list[list] = [[None] * batch for _ in range(G)]  # per group and row: (request, table length held, its table_epoch)
@@ -209,28 +231,38 @@ class DecodeGraph:
             o, n = seg[name]
             return self.dev[o : o + n]
 
+        view("q_start").copy_(torch.arange(batch + 1, dtype=torch.int32))
+        view("rows").copy_(torch.arange(batch, dtype=torch.int32))
         ctx = StepContext(
             dtype=model.dtype, device=runner.device, status=runner.status, num_tokens=batch, num_seqs=batch,
             positions=view("positions"), tok_seq=view("tok_seq"), q_start=view("q_start"), ctx_lens=view("ctx_lens"),
             q_lens_host=[1] * batch, ctx_lens_host=[max_ctx] * batch, max_q_len=1, max_ctx_len=max_ctx,
+            inputs_from_device=True,
         )
-        ctx.views = cache.views([view(f"tables{g}").view(batch, self.max_blocks) for g in range(G)],
-                                [view(f"slots{g}") for g in range(G)], None, [])
+        tables = [view(f"tables{g}").view(batch, self.max_blocks) for g in range(G)]
+        kv_slots = [view(f"slots{g}") for g in range(G)]
+        ctx.views = cache.views(tables, kv_slots, None, [])
         for name, rule in self._scalar_rules.items():
             ctx.extras[name] = view(f"scalar:{name}")
             self.h[f"scalar:{name}"][0] = rule(batch, max_ctx)
+        state = cache.state.request
+        as_float = lambda name: view(name).view(torch.float32)  # noqa: E731
 
         def run():
+            ops.step_from_state(view("row_slot"), view("fresh"), view("fresh_values").view(F, batch), state, tables, kv_slots,
+                                cache.page_size, cache.num_pages, view("tokens"), view("positions"), view("ctx_lens"),
+                                view("tok_seq"), as_float("temperature"), view("top_k"), as_float("top_p"),
+                                as_float("uniform"), runner.status)
             # the logits of every row stay readable after a replay (trace replay reads them; generation
             # reads the sampled tokens only)
             logits = self.logits = model.forward(ctx, view("tokens"), view("rows"))
+            into_state = (view("row_slot"), state)
             if greedy:
-                return ops.argmax(logits)
-            return ops.sample(logits, view("temperature").view(torch.float32), view("top_k"),
-                              view("top_p").view(torch.float32), view("uniform").view(torch.float32))
+                return ops.argmax(logits, into_state=into_state)
+            return ops.sample(logits, as_float("temperature"), view("top_k"), as_float("top_p"), as_float("uniform"),
+                              into_state=into_state)
 
-        self._fill_padding(0)
-        self.dev.copy_(self.host)
+        self.dev[: self.upload_words].copy_(self.host)  # all rows padding: the warm-up and the capture touch no request
         before = launch_count()
         run()  # eager warm-up: scratch buffers and kernel attributes are set up outside the capture
         self.kernels = launch_count() - before
@@ -240,37 +272,31 @@ class DecodeGraph:
             self.out = run()
         torch.cuda.synchronize()
 
-    def _fill_padding(self, live: int) -> None:
-        h = self.h
-        h["tokens"][live:] = 0
-        h["positions"][live:] = 0
-        h["tok_seq"][live:] = -1
-        h["ctx_lens"][live:] = 0
-        for name in h:
-            if name.startswith("slots"):
-                h[name][live:] = -1
-
-    def replay(self, cache: CacheManager, reqs, tokens: list[int], sampling=None) -> torch.Tensor:
-        """Refill the inputs for these requests (each brings one token, its slot already
-        reserved), upload them in one copy, replay.  ``sampling``: (temperature, top_k, top_p,
-        uniform) lists for a graph that samples.  Returns the sampled tokens of the live rows."""
-        self.fill(cache, reqs, sampling)
-        return self.launch(tokens)
-
-    def fill(self, cache: CacheManager, reqs, sampling=None) -> None:
-        """Everything of a step's inputs but the token ids, written into the pinned buffer: it depends
-        on the requests' positions and pages only, so it can be done while the step before is still
-        running (its upload has long left the buffer)."""
+    def fill(self, cache: CacheManager, reqs, fresh_rows: list[tuple] | None) -> None:
+        """What the host supplies for a step of these requests, one row each, written into the pinned
+        buffer (it depends on the requests' positions and pages only, so it can be done while the step
+        before is still running).  ``fresh_rows``: per row the column that replaces the request's device
+        state first (``fresh_row``), or None when every row just goes on from the step before."""
         n = self._filled = len(reqs)
         self._uploaded.synchronize()  # the last upload has left the pinned buffer
         h, ps = self.h, cache.page_size
+        dirty = False
+        slots = np.fromiter((r.state_slot for r in reqs), dtype=np.int32, count=n)
+        if (h["row_slot"][:n] != slots).any() or (h["row_slot"][n:] != -1).any():
+            # (state is kept by slot, not by row: requests may change rows, or graphs, and go on)
+            h["row_slot"][:n] = slots
+            h["row_slot"][n:] = -1
+            dirty = True
+        if h["fresh"].any():
+            h["fresh"][:] = 0  # (cleared on the device by the step that used them)
+        if fresh_rows is not None:
+            h["fresh"][:n] = 1
+            h["fresh_values"][:, :n] = np.array(fresh_rows, dtype=np.int64).T.astype(np.int32)
+            dirty = True
         pos = np.fromiter((r.num_computed for r in reqs), dtype=np.int32, count=n)
-        h["positions"][:n] = pos
-        h["tok_seq"][:n] = np.arange(n, dtype=np.int32)
-        h["ctx_lens"][:n] = pos + 1
         rows = np.arange(n)
         for g in range(len(cache.groups)):
-            tables, slots = h[f"tables{g}"], h[f"slots{g}"]
+            tables = h[f"tables{g}"]
             owners = self._row_owner[g]
             for i, r in enumerate(reqs):
                 # a row is rewritten only from where the request's table grew since the row last held it
@@ -283,31 +309,31 @@ class DecodeGraph:
                 have = owner[1] if same else 0
                 tables[i, have : len(table)] = table[have:]
                 owners[i] = (r, len(table), r.table_epoch)
+                dirty = True
             pages = tables[rows, pos // ps]
             if (pages == NO_PAGE).any():
                 bad = reqs[int(np.argmax(pages == NO_PAGE))]
                 raise RuntimeError(f"request {bad.request_id!r}: a token lands in a page that was given back")
-            slots[:n] = pages * ps + pos % ps
-        if sampling is not None:
-            temperature, top_k, top_p, uniform = sampling
-            self.hf["temperature"][:n] = temperature
-            h["top_k"][:n] = top_k
-            self.hf["top_p"][:n] = top_p
-            self.hf["uniform"][:n] = uniform
-            self.hf["temperature"][n:] = 0.0
-        self._fill_padding(n)
         longest = int(pos.max()) + 1
         for name, rule in self._scalar_rules.items():
-            h[f"scalar:{name}"][0] = rule(n, longest)
+            value = rule(n, longest)
+            if h[f"scalar:{name}"][0] != value:
+                h[f"scalar:{name}"][0] = value
+                dirty = True
+        self._dirty = self._dirty or dirty
 
-    def launch(self, tokens: list[int]) -> torch.Tensor:
-        """The token ids of the filled step, one upload, the replay.  Returns the sampled tokens."""
-        n = self._filled
-        self.h["tokens"][:n] = tokens
-        self.dev.copy_(self.host, non_blocking=True)
-        self._uploaded.record()
+    def launch(self) -> torch.Tensor:
+        """The upload, if the host's part changed, and the replay.  Returns the sampled tokens of the live rows."""
+        if self._dirty:
+            self.dev[: self.upload_words].copy_(self.host, non_blocking=True)
+            self._uploaded.record()
+            self._dirty = False
+            self.uploads += 1
+            self.last_upload_bytes = self.upload_bytes
+        else:
+            self.last_upload_bytes = 0
         self.graph.replay()
-        return self.out[:n]
+        return self.out[: self._filled]
 
 
 class ModelRunner:
@@ -329,6 +355,7 @@ class ModelRunner:
         self.graph_kernel_launches = 0  # kernels replayed through graphs (for accounting)
         self.last_graph: DecodeGraph | None = None  # the graph of the last captured step that ran
         self.last_upload_bytes = 0
+        self.uploaded_bytes = 0  # host-to-device bytes of all steps so far
 
     def enable_graphs(self, max_ctx: int, max_batch: int) -> bool:
         """Let steps in which every request brings exactly one token replay a captured CUDA graph
@@ -343,16 +370,26 @@ class ModelRunner:
         return (self.graph_max_batch > 0 and 0 < len(entries) <= self.graph_max_batch
                 and all(len(e.tokens) == 1 for e in entries))
 
-    def decode_with_graph(self, entries: list[StepEntry], sampling=None) -> torch.Tensor:
-        """One single-token step for every entry through the captured graph, sampling included.
-        Returns the sampled tokens (device int32 [len(entries)])."""
-        prepared = self.prepare_decode([e.request_id for e in entries], sampling)
-        return self.launch_decode(prepared, [e.tokens[0] for e in entries])
+    def decode_with_graph(self, entries: list[StepEntry], sampling_rows: list[tuple] | None = None) -> torch.Tensor:
+        """One single-token step for every entry through the captured graph, sampling included, the
+        tokens given by the caller.  ``sampling_rows``: per entry (temperature, top_k, top_p, seed, draws),
+        or None for greedy.  Returns the sampled tokens (device int32 [len(entries)])."""
+        cache = self.cache
+        fresh = []
+        for i, e in enumerate(entries):
+            position = cache.get(e.request_id).num_computed
+            if sampling_rows is None:
+                fresh.append(fresh_row(position, e.tokens[0]))
+            else:
+                temperature, top_k, top_p, seed, draws = sampling_rows[i]
+                fresh.append(fresh_row(position, e.tokens[0], draws, seed, temperature, top_k, top_p))
+        return self.launch_decode(self.prepare_decode([e.request_id for e in entries], fresh, greedy=sampling_rows is None))
 
-    def prepare_decode(self, request_ids: list[str], sampling=None):
-        """The first half of ``decode_with_graph``: slots reserved, graph chosen, every input but the
-        token ids written.  It needs the requests' positions only, so the engine may call it for step
-        N+1 while step N runs (after step N's launch: positions are advanced at launch)."""
+    def prepare_decode(self, request_ids: list[str], fresh_rows: list[tuple] | None, greedy: bool = True):
+        """The first half of a captured step: slots reserved, graph chosen, the host's part of its inputs
+        written.  It needs the requests' positions only, so the engine may call it for step N+1 while
+        step N runs (after step N's launch: positions are advanced at launch).  ``fresh_rows``: see
+        ``DecodeGraph.fill``."""
         cache = self.cache
         reqs = []
         for rid in request_ids:
@@ -375,21 +412,24 @@ class ModelRunner:
         while tier < longest:
             tier *= 2
         tier = min(tier, self.graph_max_ctx)
-        key = (bucket, sampling is None, tier)
+        key = (bucket, greedy, tier)
         graph = self.graphs.get(key)
         if graph is None:
-            graph = self.graphs[key] = DecodeGraph(self, bucket, tier, greedy=sampling is None)
-        graph.fill(cache, reqs, sampling)
+            graph = self.graphs[key] = DecodeGraph(self, bucket, tier, greedy=greedy)
+        graph.fill(cache, reqs, fresh_rows)
         return graph, reqs
 
-    def launch_decode(self, prepared, tokens: list[int]) -> torch.Tensor:
-        """The second half: the token ids, the upload, the replay; positions advance."""
+    def launch_decode(self, prepared) -> torch.Tensor:
+        """The second half: the upload (if the host's part of the inputs changed), the replay; positions
+        advance.  Returns the sampled tokens on the device (the graph's own output buffer: the next
+        replay of the same graph overwrites it)."""
         graph, reqs = prepared
         cache = self.cache
-        out = graph.launch(tokens)
+        out = graph.launch()
         self.last_graph = graph
         self.graph_kernel_launches += graph.kernels
-        self.last_upload_bytes = graph.upload_bytes
+        self.last_upload_bytes = graph.last_upload_bytes
+        self.uploaded_bytes += graph.last_upload_bytes
         for r in reqs:
             r.num_computed += 1
             cache.release_behind_window(r, r.num_computed)
@@ -406,6 +446,7 @@ class ModelRunner:
         logits = self.model.forward(prepared.ctx, prepared.token_ids, prepared.logit_rows)
         self.builder.commit(prepared)
         self.last_upload_bytes = self.builder.last_upload_bytes
+        self.uploaded_bytes += self.builder.last_upload_bytes
         self.steps_run += 1
         return logits
 

@@ -6,12 +6,13 @@ from __future__ import annotations
 
 import torch
 
-from .library import KernelLibraryError, check, library
+from .library import KernelLibraryError, check, library, serial_launch, set_pdl
 
 __all__ = [
     "KernelLibraryError", "library", "dtype_code", "new_status", "device_status", "raise_on_status",
     "embed", "add_rmsnorm", "rmsnorm_rows", "silu_mul", "add_to_residual", "gemm_ref",
-    "gemm_ref_swiglu", "rope_store", "copy_pages", "attention_ref", "argmax", "sample",
+    "gemm_ref_swiglu", "rope_store", "copy_pages", "attention_ref", "argmax", "sample", "step_from_state",
+    "REQUEST_STATE_FIELDS",
 ]
 
 STATUS_MESSAGES = {
@@ -81,13 +82,23 @@ def raise_on_status(status: torch.Tensor) -> None:
         raise RuntimeError("kernel status: " + STATUS_MESSAGES.get(code, f"code {code}").format(a=a, b=b))
 
 
-def embed(table: torch.Tensor, ids: torch.Tensor, status: torch.Tensor) -> torch.Tensor:
-    """float32 [N, H] rows of ``table`` (float32 or bfloat16 [V, H]) for int32 ``ids`` [N]."""
+def embed(table: torch.Tensor, ids: torch.Tensor, status: torch.Tensor, serial: bool = False) -> torch.Tensor:
+    """float32 [N, H] rows of ``table`` (float32 or bfloat16 [V, H]) for int32 ``ids`` [N].  ``serial``: the
+    kernel starts only when everything before it on the stream has finished (for a step whose inputs a
+    kernel has just written: the step's later kernels read them before they wait for anything)."""
     _need(table, None, "table", 2)
     _need(ids, torch.int32, "ids", 1)
     n, (v, h) = ids.shape[0], table.shape
     out = torch.empty((n, h), dtype=torch.float32, device=table.device)
-    check(library().cw_embed(_ptr(out), _ptr(table), _ptr(ids), n, h, v, dtype_code(table.dtype), _ptr(status), _stream()), "embed")
+
+    def launch():
+        check(library().cw_embed(_ptr(out), _ptr(table), _ptr(ids), n, h, v, dtype_code(table.dtype), _ptr(status), _stream()), "embed")
+
+    if serial:
+        with serial_launch():
+            launch()
+    else:
+        launch()
     return out
 
 
@@ -256,18 +267,77 @@ def attention_ref(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
     return out
 
 
-def argmax(logits: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+REQUEST_STATE_FIELDS = ("position", "last_token", "draws", "seed_lo", "seed_hi", "temperature", "top_k", "top_p")
+
+
+def _state_args(into_state) -> tuple:
+    """``into_state`` = (row_slot int32 [R], state int32 [fields, slots]) or None."""
+    if into_state is None:
+        return None, None, 0
+    row_slot, state = into_state
+    _need(row_slot, torch.int32, "row_slot", 1)
+    _need(state, torch.int32, "state", 2)
+    if state.shape[0] != len(REQUEST_STATE_FIELDS):
+        raise ValueError(f"the request-state table has {len(REQUEST_STATE_FIELDS)} fields, got {state.shape[0]} rows")
+    return _ptr(row_slot), _ptr(state), state.shape[1]
+
+
+def argmax(logits: torch.Tensor, out: torch.Tensor | None = None, into_state=None) -> torch.Tensor:
+    """First maximal index per row.  ``into_state`` = (row_slot, state table): the token also becomes the
+    request's last token in the table and its position and draw counter advance (``step_from_state``)."""
     _need(logits, torch.float32, "logits", 2)
     r, v = logits.shape
     if out is None:
         out = torch.empty((r,), dtype=torch.int32, device=logits.device)
-    check(library().cw_argmax(_ptr(logits), _ptr(out), r, v, v, _stream()), "argmax")
+    slot_ptr, state_ptr, slots = _state_args(into_state)
+    if into_state is not None and into_state[0].shape[0] < r:
+        raise ValueError("row_slot must have an entry per logits row")
+    check(library().cw_argmax_state(_ptr(logits), _ptr(out), r, v, v, slot_ptr, state_ptr, slots, _stream()), "argmax")
     return out
 
 
+def step_from_state(row_slot: torch.Tensor, fresh: torch.Tensor, fresh_values: torch.Tensor, state: torch.Tensor,
+                    tables: list[torch.Tensor], kv_slots: list[torch.Tensor], page_size: int, num_pages: int,
+                    tokens: torch.Tensor, positions: torch.Tensor, ctx_lens: torch.Tensor, tok_seq: torch.Tensor,
+                    temperature: torch.Tensor, top_k: torch.Tensor, top_p: torch.Tensor, uniform: torch.Tensor,
+                    status: torch.Tensor) -> None:
+    """The inputs of a single-token step from the per-request state table: row r of the step belongs to
+    the request in slot ``row_slot[r]`` (< 0: padding).  Rows flagged in ``fresh`` first take their column
+    from ``fresh_values`` [fields, B] (the flag is cleared).  Written: the token to feed, position,
+    context length, the row's request index, the cache slot per page group (from ``tables`` [B, max_blocks]
+    each), and the sampling parameters with the draw's uniform number."""
+    import ctypes
+
+    b = row_slot.shape[0]
+    for name, t in (("row_slot", row_slot), ("fresh", fresh), ("tokens", tokens), ("positions", positions),
+                    ("ctx_lens", ctx_lens), ("tok_seq", tok_seq), ("top_k", top_k)):
+        _need(t, torch.int32, name, 1)
+    for name, t in (("temperature", temperature), ("top_p", top_p), ("uniform", uniform)):
+        _need(t, torch.float32, name, 1)
+    _need(fresh_values, torch.int32, "fresh_values", 2)
+    _need(state, torch.int32, "state", 2)
+    if state.shape[0] != len(REQUEST_STATE_FIELDS) or tuple(fresh_values.shape) != (len(REQUEST_STATE_FIELDS), b):
+        raise ValueError("state must be [fields, slots] and fresh_values [fields, B]")
+    if len(tables) != len(kv_slots):
+        raise ValueError("one block table and one slot array per page group")
+    max_blocks = 1
+    for t, k in zip(tables, kv_slots):
+        _need(t, torch.int32, "tables", 2)
+        _need(k, torch.int32, "kv_slots", 1)
+        max_blocks = t.shape[1]
+    g = len(tables)
+    table_ptrs = (ctypes.c_void_p * max(g, 1))(*[t.data_ptr() for t in tables])
+    slot_ptrs = (ctypes.c_void_p * max(g, 1))(*[k.data_ptr() for k in kv_slots])
+    check(library().cw_step_from_state(
+        _ptr(row_slot), _ptr(fresh), _ptr(fresh_values), _ptr(state), state.shape[1], b, int(page_size), int(max_blocks),
+        int(num_pages), g, ctypes.cast(table_ptrs, ctypes.c_void_p), ctypes.cast(slot_ptrs, ctypes.c_void_p), _ptr(tokens),
+        _ptr(positions), _ptr(ctx_lens), _ptr(tok_seq), _ptr(temperature), _ptr(top_k), _ptr(top_p), _ptr(uniform),
+        _ptr(status), _stream()), "step_from_state")
+
+
 def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor, top_p: torch.Tensor,
-           uniform: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
-    """One token per row; rows with temperature 0 are greedy."""
+           uniform: torch.Tensor, out: torch.Tensor | None = None, into_state=None) -> torch.Tensor:
+    """One token per row; rows with temperature 0 are greedy.  ``into_state``: as for ``argmax``."""
     _need(logits, torch.float32, "logits", 2)
     r, v = logits.shape
     for name, t, dt in (("temperature", temperature, torch.float32), ("top_k", top_k, torch.int32),
@@ -277,6 +347,7 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor,
             raise ValueError(f"{name} must have one entry per row")
     if out is None:
         out = torch.empty((r,), dtype=torch.int32, device=logits.device)
-    check(library().cw_sample(_ptr(logits), _ptr(temperature), _ptr(top_k), _ptr(top_p), _ptr(uniform), _ptr(out),
-                              r, v, v, _stream()), "sample")
+    slot_ptr, state_ptr, slots = _state_args(into_state)
+    check(library().cw_sample_state(_ptr(logits), _ptr(temperature), _ptr(top_k), _ptr(top_p), _ptr(uniform), _ptr(out),
+                                    r, v, v, slot_ptr, state_ptr, slots, _stream()), "sample")
     return out

@@ -24,6 +24,9 @@ _SIGNATURES: dict[str, list] = {
     "cw_attention_ref": [P, I, P, P, P, P, P, P, I, I, I, I, I, I, I, F, I, I, P, P],
     "cw_argmax": [P, P, I, I, LL, P],
     "cw_sample": [P, P, P, P, P, P, I, I, LL, P],
+    "cw_argmax_state": [P, P, I, I, LL, P, P, I, P],
+    "cw_sample_state": [P, P, P, P, P, P, I, I, LL, P, P, I, P],
+    "cw_step_from_state": [P, P, P, P, I, I, I, I, I, I, P, P, P, P, P, P, P, P, P, P, P, P],
 }
 _OPTIONAL: dict[str, list] = {}
 
@@ -73,6 +76,29 @@ ERROR_NAMES = {-1: "refused size", -2: "unknown dtype code", -3: "unsupported co
 
 
 _launches = 0
+_pdl_on = True
+
+
+def set_pdl(on: bool) -> None:
+    """Whether kernels are launched so that each may begin while its predecessor drains (programmatic
+    dependent launch; the default) or strictly one after the other."""
+    global _pdl_on
+    library().cw_set_pdl(1 if on else 0)
+    _pdl_on = bool(on)
+
+
+class serial_launch:
+    """Launches inside this block start only after everything before them on the stream has finished."""
+
+    def __enter__(self):
+        self.was = _pdl_on
+        if self.was:
+            set_pdl(False)
+
+    def __exit__(self, *exc):
+        if self.was:
+            set_pdl(True)
+
 
 
 def launch_count() -> int:

@@ -94,6 +94,7 @@ class StepContext:
     max_q_len: int
     max_ctx_len: int
     views: dict[int, PagedView | StateView] = field(default_factory=dict)  # by cache layer
+    inputs_from_device: bool = False  # a kernel launched just before the forward pass wrote the arrays above
     extras: dict = field(default_factory=dict)  # scratch that kernels share within a step
 
     @property

@@ -118,7 +118,9 @@ class DecoderModel:
     def forward(self, ctx: StepContext, token_ids: torch.Tensor, logit_rows: torch.Tensor | None) -> torch.Tensor | None:
         """token_ids int32 [N]; logit_rows int32 [R] (rows of the flat batch whose logits are
         wanted).  Returns float32 [R, vocab], or None when no row is wanted."""
-        stream = ResidualStream(ops.embed(self.embedding, token_ids, ctx.status))
+        # (kernels of a step read its inputs before they wait for their predecessors; when a kernel has
+        # only just written those inputs, the first kernel here must not start before it has finished)
+        stream = ResidualStream(ops.embed(self.embedding, token_ids, ctx.status, serial=ctx.inputs_from_device))
         schedule = self.spec.schedule
         for i, step in enumerate(schedule):
             view = ctx.views.get(step.resolved_cache_layer())

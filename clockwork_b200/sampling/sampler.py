@@ -37,18 +37,14 @@ class Sampler:
         """One token per row of ``logits`` (float32 [R, vocab], on the device)."""
         return self.sample_device(logits, params, draw_indices).tolist()
 
-    def host_params(self, params: list[SamplingParams], draw_indices: list[int]):
-        """(temperature, top_k, top_p, uniform) lists for a batch, or None when every row is greedy."""
+    def state_rows(self, params: list[SamplingParams], draw_indices: list[int]) -> list[tuple] | None:
+        """Per request (temperature, top_k, top_p, seed, draws): what a request's column of the device
+        state table holds about sampling (the kernels derive the draw's uniform number from seed and
+        draws exactly as ``uniform_for`` does).  None when every request is greedy."""
         if all(p.greedy for p in params):
             return None
-        temps, ks, ps, us = [], [], [], []
-        for p, k in zip(params, draw_indices):
-            seed = p.seed if p.seed is not None else self.default_seed
-            temps.append(p.temperature)
-            ks.append(p.top_k if p.top_k and p.top_k > 0 else 0)
-            ps.append(p.top_p)
-            us.append(uniform_for(seed, k))
-        return temps, ks, ps, us
+        return [(p.temperature, p.top_k if p.top_k and p.top_k > 0 else 0, p.top_p,
+                 p.seed if p.seed is not None else self.default_seed, k) for p, k in zip(params, draw_indices)]
 
     def sample_device(self, logits: torch.Tensor, params: list[SamplingParams], draw_indices: list[int]) -> torch.Tensor:
         if logits.shape[0] != len(params):

@@ -154,8 +154,12 @@ def test_state_slots():
     m.close("a")
     assert m.can_open(1) and m.open("d").state_slot == freed
     m.check_invariants()
-    # a model without fixed-size state still has the (empty) slot pool
-    assert manager().state.num_free == 64 and manager().open("x").state_slot is None
+    # a model whose mixers keep no state of their own still has the slot pool: every request takes a
+    # slot (the column of its progress and sampling state on the device) and gives it back
+    plain = manager()
+    assert plain.state.num_free == 64 and plain.open("x").state_slot == 0 and plain.state.num_free == 63
+    plain.close("x")
+    assert plain.state.num_free == 64
 
 
 def test_shared_prefix_needs_a_single_full_group():

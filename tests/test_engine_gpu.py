@@ -315,35 +315,47 @@ def test_a_wait_that_gave_up_in_a_product_kernel_stops_generation(models, model_
     eng.step()
     gemm_tc.status("cuda:0").copy_(torch.tensor([4, 2, 1, 0], dtype=torch.int32))  # CW_ST_WAIT_TIMEOUT as a kernel writes it
     with pytest.raises(RuntimeError, match="device-side wait ran out"):
-        for _ in range(LLMEngine.STATUS_CHECK_EVERY + 1):
+        for _ in range(3):  # (the words travel to the host with every step's tokens)
             eng.step()
     eng.abort_request("r")
 
 
-def test_steps_planned_ahead_change_nothing(models, model_dirs):
-    """While a decode step runs, the engine plans and prepares the next one; a sequence that ends, a
-    request that arrives and an abort drop that plan.  Same tokens with and without, sampling included."""
-    def run(plan_ahead):
-        eng = engine(models, model_dirs, "B", max_num_seqs=4, max_num_batched_tokens=32, max_model_len=96)
-        eng.plan_ahead = plan_ahead
+def test_steps_run_ahead_change_nothing(models, model_dirs):
+    """A step in which every request decodes is launched before the tokens of the step before it have
+    been read (its inputs come from the requests' state on the device); a sequence that ends by a stop
+    token has then computed a token too many, which is dropped; a request that arrives and an abort end
+    the running ahead.  Same tokens with and without, sampling and stop tokens included."""
+    def run(run_ahead, stop_id=None):
+        eng = engine(models, model_dirs, "B", max_num_seqs=5, max_num_batched_tokens=32, max_model_len=96)
+        eng.run_ahead = run_ahead
         got = {}
         eng.add_request("greedy", prompt_token_ids=tokens_for("B", 9, 1), sampling_params=SamplingParams(max_tokens=30, ignore_eos=True))
         eng.add_request("short", prompt_token_ids=tokens_for("B", 5, 2), sampling_params=SamplingParams(max_tokens=7, ignore_eos=True))
         eng.add_request("sampled", prompt_token_ids=tokens_for("B", 12, 3),
                         sampling_params=SamplingParams(max_tokens=25, temperature=0.9, top_k=20, seed=7, ignore_eos=True))
         eng.add_request("gone", prompt_token_ids=tokens_for("B", 6, 4), sampling_params=SamplingParams(max_tokens=40, ignore_eos=True))
+        if stop_id is not None:  # the first request once more, ended by one of its own tokens
+            eng.add_request("stopped", prompt_token_ids=tokens_for("B", 9, 1),
+                            sampling_params=SamplingParams(max_tokens=30, stop_token_ids=[stop_id], ignore_eos=True))
         steps = 0
         while eng.has_unfinished_requests():
             for out in eng.step():
-                got[out.request_id] = list(out.token_ids)
+                got[out.request_id] = (list(out.token_ids), out.finish_reason)
             steps += 1
             if steps == 12:
                 eng.abort_request("gone")
             if steps == 15:
                 eng.add_request("late", prompt_token_ids=tokens_for("B", 7, 5), sampling_params=SamplingParams(max_tokens=9, ignore_eos=True))
-        return got, eng.steps_planned_ahead
+        assert eng.cache.requests == {} and eng.cache.state.num_free == eng.cache.state.num_slots
+        eng.cache.check_invariants(eng.prefix_cache.references())
+        return got, eng.steps_run_ahead
 
-    with_plan, planned = run(True)
-    without, none_planned = run(False)
-    assert planned > 10 and none_planned == 0
-    assert with_plan == without
+    plain_run, none_ahead = run(False)
+    stop_id = plain_run["greedy"][0][5]
+    ahead, count = run(True, stop_id)
+    behind, none_ahead_2 = run(False, stop_id)
+    assert count > 10 and none_ahead == 0 and none_ahead_2 == 0
+    assert ahead == behind
+    tokens, reason = ahead["stopped"]
+    assert reason == "stop" and tokens[-1] == stop_id and tokens == plain_run["greedy"][0][: len(tokens)] and len(tokens) <= 6
+    assert {k: v for k, v in ahead.items() if k != "stopped"} == plain_run

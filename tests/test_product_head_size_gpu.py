@@ -52,10 +52,14 @@ def model_dir(tmp_path_factory):
 
 @pytest.fixture(scope="module")
 def references(model_dir):
+    """(exact, rounded as a bfloat16 run stores activations).  The exact logits are computed in float64:
+    over 1,500 tokens of peaked attention the plain implementation's own float32 rounding reaches the
+    1e-5 that the float32 engine is held to, and the gate is against the exact result."""
     config, weights = plain.read_model_dir(model_dir)
+    weights64 = {k: v.double() for k, v in weights.items()}
 
     def get(toks):
-        return (plain.all_position_logits(config, weights, toks),
+        return (plain.all_position_logits(config, weights64, toks).float(),
                 plain.all_position_logits(config, weights, toks, rnd=plain.to_bfloat16_and_back))
 
     return get

@@ -284,11 +284,10 @@ def test_overlapping_kernels_change_nothing_2_of_28_layers(two_layer_dir):
     staging buffer that a copy in flight still reads, shows here as a run that differs."""
     from clockwork_b200.engine.step import StepEntry
     from clockwork_b200.engine.trace import TraceSession
-    from clockwork_b200.ops.library import library
+    from clockwork_b200 import ops
 
     toks = tokens(400, 3)
     session = TraceSession(two_layer_dir, "bfloat16", 512, PAGE, graphs=False)
-    lib = library()
 
     def run():
         session.cache.open("c")
@@ -299,10 +298,10 @@ def test_overlapping_kernels_change_nothing_2_of_28_layers(two_layer_dir):
         return out
 
     try:
-        lib.cw_set_pdl(0)
+        ops.set_pdl(False)
         serial = run()
     finally:
-        lib.cw_set_pdl(1)
+        ops.set_pdl(True)
     differing = [i for i in range(40) if not torch.equal(run(), serial)]
     session.runner.check_status()
     assert not differing, f"runs {differing} of 40 differ from the run without overlap"
