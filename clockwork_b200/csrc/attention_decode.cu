@@ -25,6 +25,8 @@ struct DecodeParams {
     bf16* out;
     const bf16* k_cache; const bf16* v_cache;
     const int* block_tables; const int* ctx_lens;
+    const int* q_start;  // null: request s owns row s of q and out.  Else [S + 1]: request s owns rows q_start[s] ..
+                         // q_start[s + 1] of a flat batch; only requests with exactly one row are served here
     int nh, nkv, qgroups, page_size, page_shift, max_blocks, num_pages;
     float scale; int window;
     float* part_o;   // [S, nh, max_splits, HD]
@@ -100,12 +102,17 @@ attn_decode_kernel(const DecodeParams p) {
     const int G = p.nh / p.nkv;
     const int h0 = kvh * G + qg * 16;
     const int rows = min(16, G - qg * 16);
+    int row = s;  // the request's row in q, kv_new, slots and out
+    if (p.q_start != nullptr) {
+        row = p.q_start[s];
+        if (p.q_start[s + 1] - row != 1) return;  // a prompt portion: the prefill kernel's work
+    }
     const int ctx = p.ctx_lens[s];
     if (ctx <= 0) {  // a padding row of a fixed-shape batch
         pdl_wait();
         if (sp == 0)
             for (int i = tid; i < rows * HD; i += blockDim.x)
-                p.out[((size_t)s * p.nh + h0 + i / HD) * HD + i % HD] = __float2bfloat16_rn(0.f);
+                p.out[((size_t)row * p.nh + h0 + i / HD) * HD + i % HD] = __float2bfloat16_rn(0.f);
         return;
     }
     const int SPLIT = p.split_ptr != nullptr ? *p.split_ptr : p.split;
@@ -205,13 +212,13 @@ attn_decode_kernel(const DecodeParams p) {
             if (u >= q_units + k_units) {  // the new v: a plain copy
                 const int c = u - q_units - k_units;
                 *reinterpret_cast<uint4*>(new_s + HD + c * 8) = *reinterpret_cast<const uint4*>(
-                    p.kv_new + (size_t)s * p.q_stride + (size_t)(p.nh + p.nkv + kvh) * HD + c * 8);
+                    p.kv_new + (size_t)row * p.q_stride + (size_t)(p.nh + p.nkv + kvh) * HD + c * 8);
                 continue;
             }
             const bool is_q = u < q_units;
             const int r = is_q ? u / HC : 0, c = is_q ? u % HC : u - q_units;
-            const bf16* src = is_q ? p.q + (size_t)s * p.q_stride + (size_t)(h0 + r) * HD
-                                   : p.kv_new + (size_t)s * p.q_stride + (size_t)(p.nh + kvh) * HD;
+            const bf16* src = is_q ? p.q + (size_t)row * p.q_stride + (size_t)(h0 + r) * HD
+                                   : p.kv_new + (size_t)row * p.q_stride + (size_t)(p.nh + kvh) * HD;
             bf16* dst = is_q ? Qs + r * LD : new_s;
             uint4 lo = *reinterpret_cast<const uint4*>(src + c * 8);
             uint4 hi = *reinterpret_cast<const uint4*>(src + HD / 2 + c * 8);
@@ -233,14 +240,14 @@ attn_decode_kernel(const DecodeParams p) {
     for (int i = tid; i < 16 * CH; i += blockDim.x) {
         const int r = i / CH, c = i % CH;
         uint4 v = make_uint4(0, 0, 0, 0);
-        if (r < rows) v = *reinterpret_cast<const uint4*>(p.q + (size_t)s * p.q_stride + (size_t)(h0 + r) * HD + c * 8);
+        if (r < rows) v = *reinterpret_cast<const uint4*>(p.q + (size_t)row * p.q_stride + (size_t)(h0 + r) * HD + c * 8);
         *reinterpret_cast<uint4*>(Qs + r * LD + c * 8) = v;
     }
     // ---- the newest token's k and v: from the [q|k|v] row (rotating k, storing both) or from the cache
     if (has_newest) {
         if (p.kv_new != nullptr) {
-            const bf16* krow = p.kv_new + (size_t)s * p.q_stride + (size_t)(p.nh + kvh) * HD;
-            const bf16* vrow = p.kv_new + (size_t)s * p.q_stride + (size_t)(p.nh + p.nkv + kvh) * HD;
+            const bf16* krow = p.kv_new + (size_t)row * p.q_stride + (size_t)(p.nh + kvh) * HD;
+            const bf16* vrow = p.kv_new + (size_t)row * p.q_stride + (size_t)(p.nh + p.nkv + kvh) * HD;
             for (int i = tid; i < 2 * CH; i += blockDim.x) {
                 const bf16* src = (i < CH ? krow : vrow) + (i % CH) * 8;
                 *reinterpret_cast<uint4*>(new_s + (i < CH ? 0 : HD) + (i % CH) * 8) = *reinterpret_cast<const uint4*>(src);
@@ -276,7 +283,7 @@ attn_decode_kernel(const DecodeParams p) {
     }  // (not rotate_on_load)
     if (p.kv_new != nullptr && has_newest && qg == 0) {
         // one CTA per (request, KV head) stores the new token
-        const int slot = p.slots != nullptr ? p.slots[s] : -1;
+        const int slot = p.slots != nullptr ? p.slots[row] : -1;
         if (slot >= p.num_slots) {
             if (tid == 0) cw_report(p.status, CW_ST_SLOT_RANGE, s, slot);
         } else if (slot >= 0) {
@@ -427,7 +434,7 @@ attn_decode_kernel(const DecodeParams p) {
             uint2 o;
             o.x = pack_bf16(val.x, val.y);
             o.y = pack_bf16(val.z, val.w);
-            *reinterpret_cast<uint2*>(p.out + ((size_t)s * p.nh + h) * HD + d) = o;
+            *reinterpret_cast<uint2*>(p.out + ((size_t)row * p.nh + h) * HD + d) = o;
         } else {
             *reinterpret_cast<float4*>(p.part_o + (((size_t)s * p.nh + h) * p.max_splits + sp) * HD + d) = val;
             if (d == 0) p.part_lse[((size_t)s * p.nh + h) * p.max_splits + sp] = w_s[r][NWARPS];
@@ -501,7 +508,7 @@ attn_decode_kernel(const DecodeParams p) {
         uint2 o;
         o.x = pack_bf16(acc.x * inv, acc.y * inv);
         o.y = pack_bf16(acc.z * inv, acc.w * inv);
-        *reinterpret_cast<uint2*>(p.out + ((size_t)s * p.nh + h0 + r) * HD + d) = o;
+        *reinterpret_cast<uint2*>(p.out + ((size_t)row * p.nh + h0 + r) * HD + d) = o;
     }
     cw_trace_end();
 }
@@ -548,12 +555,23 @@ extern "C" int cw_attention_decode_workspace(int S, int nh, int nkv, int hd, int
 // q: [S, >= nh*hd] rows (row stride q_stride), one query token per request; out: [S, nh*hd].
 // max_ctx bounds every ctx_lens[s]; it fixes the grid, not the result.  split (or *split_ptr): tokens
 // per CTA, a multiple of 64 and at least 128.
+extern "C" int cw_attention_decode_rows(const void* q, int q_stride, void* out, void* k_cache, void* v_cache,
+                                        const int* block_tables, const int* ctx_lens, const int* q_start, int S, int nh,
+                                        int nkv, int hd, int page_size, int max_blocks, int num_pages, float scale,
+                                        int window, int max_ctx, int split, const int* split_ptr, float* part_o,
+                                        float* part_lse, int* counters, int fuse_store, const float* inv_freq,
+                                        int rotary_dim, const int* slots, int stages, int* status, cudaStream_t stream);
+
 extern "C" int cw_attention_decode_fused(const void* q, int q_stride, void* out, void* k_cache, void* v_cache,
                                          const int* block_tables, const int* ctx_lens, int S, int nh, int nkv, int hd,
                                          int page_size, int max_blocks, int num_pages, float scale, int window,
                                          int max_ctx, int split, const int* split_ptr, float* part_o, float* part_lse,
                                          int* counters, int fuse_store, const float* inv_freq, int rotary_dim,
-                                         const int* slots, int stages, int* status, cudaStream_t stream);
+                                         const int* slots, int stages, int* status, cudaStream_t stream) {
+    return cw_attention_decode_rows(q, q_stride, out, k_cache, v_cache, block_tables, ctx_lens, nullptr, S, nh, nkv, hd,
+                                    page_size, max_blocks, num_pages, scale, window, max_ctx, split, split_ptr, part_o,
+                                    part_lse, counters, fuse_store, inv_freq, rotary_dim, slots, stages, status, stream);
+}
 
 extern "C" int cw_attention_decode(const void* q, int q_stride, void* out, const void* k_cache, const void* v_cache,
                                    const int* block_tables, const int* ctx_lens, int S, int nh, int nkv, int hd,
@@ -567,12 +585,15 @@ extern "C" int cw_attention_decode(const void* q, int q_stride, void* out, const
 // As cw_attention_decode; with fuse_store != 0, q is the [q | k | v] row buffer that the QKV product
 // wrote (raw): q and the new k are rotated here (inv_freq null: left alone) and the new token's k and
 // v are stored at slots[s] before they are used, so no separate position/cache-write kernel runs.
-extern "C" int cw_attention_decode_fused(const void* q, int q_stride, void* out, void* k_cache, void* v_cache,
-                                         const int* block_tables, const int* ctx_lens, int S, int nh, int nkv, int hd,
-                                         int page_size, int max_blocks, int num_pages, float scale, int window,
-                                         int max_ctx, int split, const int* split_ptr, float* part_o, float* part_lse,
-                                         int* counters, int fuse_store, const float* inv_freq, int rotary_dim,
-                                         const int* slots, int stages, int* status, cudaStream_t stream) {
+// With q_start ([S + 1], may be null) the S requests are those of a flat batch that also holds prompt
+// portions: request s owns rows q_start[s] .. q_start[s + 1] of q and out, and only the requests with
+// exactly one row are served (the others are the prefill kernel's work); slots is then per row.
+extern "C" int cw_attention_decode_rows(const void* q, int q_stride, void* out, void* k_cache, void* v_cache,
+                                        const int* block_tables, const int* ctx_lens, const int* q_start, int S, int nh,
+                                        int nkv, int hd, int page_size, int max_blocks, int num_pages, float scale,
+                                        int window, int max_ctx, int split, const int* split_ptr, float* part_o,
+                                        float* part_lse, int* counters, int fuse_store, const float* inv_freq,
+                                        int rotary_dim, const int* slots, int stages, int* status, cudaStream_t stream) {
     if (S == 0) return CW_OK;
     if (S < 0 || nh <= 0 || nkv <= 0 || nh % nkv != 0 || page_size <= 0 || max_blocks <= 0 || max_ctx <= 0)
         return CW_ERR_BAD_SIZE;
@@ -582,7 +603,7 @@ extern "C" int cw_attention_decode_fused(const void* q, int q_stride, void* out,
     DecodeParams p;
     p.q = (const bf16*)q; p.q_stride = q_stride; p.out = (bf16*)out;
     p.k_cache = (const bf16*)k_cache; p.v_cache = (const bf16*)v_cache;
-    p.block_tables = block_tables; p.ctx_lens = ctx_lens;
+    p.block_tables = block_tables; p.ctx_lens = ctx_lens; p.q_start = q_start;
     p.nh = nh; p.nkv = nkv; p.qgroups = (nh / nkv + 15) / 16;
     p.page_size = page_size; p.page_shift = (page_size & (page_size - 1)) == 0 ? __builtin_ctz(page_size) : -1; p.max_blocks = max_blocks; p.num_pages = num_pages;
     p.scale = scale; p.window = window;

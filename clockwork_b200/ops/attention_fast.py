@@ -37,6 +37,8 @@ def _configure() -> None:
     lib.cw_attention_decode.restype = c_int
     lib.cw_attention_decode_fused.argtypes = [P, I, P, P, P, P, P, I, I, I, I, I, I, I, F, I, I, I, P, P, P, P, I, P, I, P, I, P, P]
     lib.cw_attention_decode_fused.restype = c_int
+    lib.cw_attention_decode_rows.argtypes = [P, I, P, P, P, P, P, P, I, I, I, I, I, I, I, F, I, I, I, P, P, P, P, I, P, I, P, I, P, P]
+    lib.cw_attention_decode_rows.restype = c_int
     lib.cw_attention_decode_workspace.argtypes = [I, I, I, I, I, POINTER(LL), POINTER(LL), POINTER(I)]
     lib.cw_attention_decode_workspace.restype = c_int
     lib.cw_attention_prefill.argtypes = [P, I, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, I, P, P]
@@ -156,13 +158,18 @@ class _Decode:
 
 def attention_decode(q, k_cache, v_cache, block_tables, ctx_lens, num_heads, num_kv_heads, head_dim, scale, window,
                      max_ctx: int, status, split: int | None = None, split_dev: torch.Tensor | None = None,
-                     fused: tuple | None = None, stages: int = 0) -> torch.Tensor:
+                     fused: tuple | None = None, stages: int = 0, q_start: torch.Tensor | None = None,
+                     out: torch.Tensor | None = None) -> torch.Tensor:
     """One query token per request: ``q`` [S, >= nh*hd] (row s belongs to request s), ``ctx_lens`` [S]
     the tokens of each request in the cache (its own included).  ``split``: tokens per CTA (a multiple
     of 64, at least 128; default: chosen by ``decode_split``), or ``split_dev``, the same as an int32
     device scalar.  ``fused``: (inv_freq or None, rotary_dim, slots): ``q`` is then the raw [q | k | v]
     rows; q and the new k are rotated inside the kernel and the new token's k and v stored at ``slots``
-    (so no separate position-encoding / cache-write kernel is needed).  Returns [S, nh*hd]."""
+    (so no separate position-encoding / cache-write kernel is needed).  Returns [S, nh*hd].
+
+    ``q_start`` (int32 [S + 1]) with ``out`` ([N, nh*hd]): the requests are those of a flat batch of N rows
+    that also holds prompt portions; request s owns rows q_start[s]:q_start[s+1] of ``q`` and ``out``, and
+    only the requests with exactly one row are served (rows of the others are left alone)."""
     _configure()
     if q.dtype != torch.bfloat16 or q.dim() != 2 or q.stride(1) != 1:
         raise ValueError("q must be a 2-d bfloat16 tensor with unit column stride")
@@ -173,12 +180,20 @@ def attention_decode(q, k_cache, v_cache, block_tables, ctx_lens, num_heads, num
     if head_dim not in DECODE_HEAD_DIMS:
         raise ValueError(f"head_dim {head_dim} is not one of {DECODE_HEAD_DIMS}")
     s = q.shape[0]
+    if q_start is not None:
+        _need(q_start, torch.int32, "q_start", 1)
+        s = q_start.shape[0] - 1
+        if out is None or fused is not None:
+            raise ValueError("a flat batch needs the output tensor and runs without the fused position encoding")
     if split_dev is None and split is None:
         split = decode_split(s, num_heads, num_kv_heads, max_ctx, q.device, head_dim)
     po, pl, pc = c_longlong(0), c_longlong(0), c_int(0)
     library().cw_attention_decode_workspace(s, num_heads, num_kv_heads, head_dim, max_ctx, byref(po), byref(pl), byref(pc))
     st = _decode_scratch(q.device, po.value, pl.value, pc.value)
-    out = torch.empty((s, num_heads * head_dim), dtype=torch.bfloat16, device=q.device)
+    if out is None:
+        out = torch.empty((s, num_heads * head_dim), dtype=torch.bfloat16, device=q.device)
+    elif out.dtype != torch.bfloat16 or out.shape[1] != num_heads * head_dim or not out.is_contiguous():
+        raise ValueError("out must be a contiguous bfloat16 [rows, nh*hd] tensor")
     inv_freq, rotary_dim, slots = fused if fused is not None else (None, 0, None)
     if fused is not None:
         if q.shape[1] != (num_heads + 2 * num_kv_heads) * head_dim:
@@ -188,8 +203,8 @@ def attention_decode(q, k_cache, v_cache, block_tables, ctx_lens, num_heads, num
             _need(inv_freq, torch.float32, "inv_freq", 1)
             if inv_freq.shape[0] * 2 != rotary_dim:
                 raise ValueError("inv_freq must hold rotary_dim/2 frequencies")
-    check(library().cw_attention_decode_fused(
-        _ptr(q), q.stride(0), _ptr(out), _ptr(k_cache), _ptr(v_cache), _ptr(block_tables), _ptr(ctx_lens), s, num_heads,
+    check(library().cw_attention_decode_rows(
+        _ptr(q), q.stride(0), _ptr(out), _ptr(k_cache), _ptr(v_cache), _ptr(block_tables), _ptr(ctx_lens), _ptr(q_start), s, num_heads,
         num_kv_heads, head_dim, k_cache.shape[1], block_tables.shape[1], k_cache.shape[0], float(scale), int(window or 0),
         int(max_ctx), int(split or 0), _ptr(split_dev), _ptr(st["part_o"]), _ptr(st["part_lse"]), _ptr(st["counters"]),
         1 if fused is not None else 0, _ptr(inv_freq), int(rotary_dim), _ptr(slots), int(stages), _ptr(status), _stream()), "attention_decode")
@@ -200,7 +215,8 @@ MIN_PART_KEYS = 4 * QUERY_TILE  # no part of a cut row of keys is shorter than t
 MAX_PARTS = 8                   # (the kernel's limit)
 
 
-def prefill_work_items(q_lens, ctx_lens, num_heads: int = 0, sm_count: int = 0) -> tuple[list[int], list[int], list[int]]:
+def prefill_work_items(q_lens, ctx_lens, num_heads: int = 0, sm_count: int = 0,
+                       skip_single: bool = False) -> tuple[list[int], list[int], list[int]]:
     """Work items of a step's portions: (request index, first query row, split word) per 128 query rows,
     longest first (CTAs are handed to SMs in this order, so the short ones fill the tail).
 
@@ -212,6 +228,8 @@ def prefill_work_items(q_lens, ctx_lens, num_heads: int = 0, sm_count: int = 0) 
     (index of the tile's first item) << 8 | parts."""
     groups = []  # [keys the tile's last row sees, request, first row, parts]
     for s, (n, c) in enumerate(zip(q_lens, ctx_lens)):
+        if skip_single and n == 1:
+            continue  # (requests that bring a single token are the decode kernel's)
         for q0 in range(0, n, QUERY_TILE):
             groups.append([c - n + min(q0 + QUERY_TILE, n), s, q0, 1])
     if num_heads > 0 and sm_count > 0 and groups:
@@ -234,6 +252,15 @@ def prefill_work_items(q_lens, ctx_lens, num_heads: int = 0, sm_count: int = 0) 
 
 
 _cut_long_rows = True
+_route_single_tokens = True
+
+
+def set_route_single_tokens(on: bool) -> None:
+    """In a step that mixes prompt portions with requests that bring one token, those requests are served
+    by the decode kernel by default; ``False`` leaves them to the prefill kernel (for measurements)."""
+    global _route_single_tokens
+    _route_single_tokens = bool(on)
+
 
 
 def set_cut_long_rows(on: bool) -> None:
@@ -243,13 +270,14 @@ def set_cut_long_rows(on: bool) -> None:
     _cut_long_rows = bool(on)
 
 
-def _work_items(ctx, num_heads: int) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor | None, int]:
+def _work_items(ctx, num_heads: int, skip_single: bool = False) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor | None, int]:
     """The step's work items on the device; built once per step and head count (``num_heads`` 0: no
     cuts) and shared by the layers."""
-    key = ("prefill_items", num_heads)
+    key = ("prefill_items", num_heads, skip_single)
     cached = ctx.extras.get(key)
     if cached is None:
-        seqs, q0s, words = prefill_work_items(ctx.q_lens_host, ctx.ctx_lens_host, num_heads, _sm_count(ctx.device) if num_heads else 0)
+        seqs, q0s, words = prefill_work_items(ctx.q_lens_host, ctx.ctx_lens_host, num_heads,
+                                              _sm_count(ctx.device) if num_heads else 0, skip_single)
         cut = any(w & 0xFF != 1 for w in words)
         host = torch.from_numpy(np.array([seqs, q0s, words], dtype=np.int32))
         dev = host.to(ctx.device, non_blocking=False)
@@ -284,11 +312,23 @@ class _Prefill:
 
     @staticmethod
     def run(ctx, qkv, view, num_heads, num_kv_heads, head_dim, scale, window) -> torch.Tensor:
+        # Requests that bring a single token go to the decode kernel (a context split over CTAs, the query
+        # heads of a KV head sharing every tile) instead of taking a 128-row query tile per head here; the
+        # two kernels fill one output tensor.
+        singles = sum(1 for n in ctx.q_lens_host if n == 1) if _route_single_tokens and head_dim in DECODE_HEAD_DIMS else 0
         item_seq, item_q0, item_split, items = _work_items(
-            ctx, num_heads if _cut_long_rows and prefill_tc_takes(head_dim, view.k_cache.shape[1]) else 0)
-        return attention_prefill(qkv, view.k_cache, view.v_cache, view.block_tables, ctx.q_start, ctx.ctx_lens,
-                                 item_seq, item_q0, items, num_heads, num_kv_heads, head_dim, scale, window, ctx.status,
-                                 item_split=item_split)
+            ctx, num_heads if _cut_long_rows and prefill_tc_takes(head_dim, view.k_cache.shape[1]) else 0, singles > 0)
+        out = attention_prefill(qkv, view.k_cache, view.v_cache, view.block_tables, ctx.q_start, ctx.ctx_lens,
+                                item_seq, item_q0, items, num_heads, num_kv_heads, head_dim, scale, window, ctx.status,
+                                item_split=item_split)
+        if singles:
+            longest = max(c for n, c in zip(ctx.q_lens_host, ctx.ctx_lens_host) if n == 1)
+            attention_decode(qkv, view.k_cache, view.v_cache, view.block_tables, ctx.ctx_lens, num_heads, num_kv_heads,
+                             head_dim, scale, window, longest, ctx.status,
+                             split=decode_split(singles, num_heads, num_kv_heads, longest, qkv.device, head_dim),
+                             stages=decode_stages(singles, num_heads, num_kv_heads, longest, qkv.device, head_dim),
+                             q_start=ctx.q_start, out=out)
+        return out
 
 
 def attention_prefill(q, k_cache, v_cache, block_tables, q_start, ctx_lens, item_seq, item_q0, items, num_heads,

@@ -590,6 +590,44 @@ def test_attention_prefill_kernel_mixed_batch(ops, status, fast, kernel, nh, nkv
         row += q.shape[0]
 
 
+@pytest.mark.parametrize("nh,nkv,hd,ps,window", [(12, 2, 128, 16, None), (5, 5, 48, 8, None), (8, 1, 16, 4, 37), (28, 4, 128, 16, None)])
+def test_single_tokens_of_a_mixed_batch_go_to_the_decode_kernel(ops, status, fast, nh, nkv, hd, ps, window):
+    """A flat batch of prompt portions and requests that bring one token: the prefill kernel takes the
+    portions (its work items leave the single tokens out), the decode kernel takes the requests with
+    exactly one row (it finds their rows through q_start and leaves the others' rows alone), and the two
+    fill one output tensor.  Single tokens first, last and between portions; contexts of one token, of a
+    few splits and of many."""
+    ctx_lens, q_lens = [700, 150, 1, 333, 41, 1300, 2000, 64, 129], [1, 23, 1, 1, 41, 1, 130, 1, 128]
+    dtype = torch.bfloat16
+    k_cache, v_cache, tables, ks, vs = paged_setup(ctx_lens, nkv, hd, ps, dtype, seed=15)
+    scale = hd**-0.5
+    g = torch.Generator().manual_seed(16)
+    qs = [(torch.randn(q, nh, hd, generator=g) * 2).to(dtype).float() for q in q_lens]
+    n = sum(q_lens)
+    wide = torch.zeros(n, (nh + 2 * nkv) * hd)
+    wide[:, : nh * hd] = torch.cat(qs).view(n, nh * hd)
+    q_start = torch.tensor([0] + torch.tensor(q_lens).cumsum(0).tolist(), dtype=torch.int32).to(DEV)
+    seqs, q0s, _ = fast.prefill_work_items(q_lens, ctx_lens, skip_single=True)
+    assert sorted(set(seqs)) == [i for i, q in enumerate(q_lens) if q > 1]
+    qd, kd, vd, td = wide.to(dtype).to(DEV), k_cache.to(DEV), v_cache.to(DEV), tables.to(DEV)
+    cd = torch.tensor(ctx_lens, dtype=torch.int32, device=DEV)
+    out = fast.attention_prefill(qd, kd, vd, td, q_start, cd, torch.tensor(seqs, dtype=torch.int32, device=DEV),
+                                 torch.tensor(q0s, dtype=torch.int32, device=DEV), len(seqs), nh, nkv, hd, scale, window, status)
+    single_rows = [int(q_start[i]) for i, q in enumerate(q_lens) if q == 1]
+    out[single_rows] = 77.0  # whatever the prefill kernel left there must be overwritten
+    longest = max(c for c, q in zip(ctx_lens, q_lens) if q == 1)
+    for kw in (dict(split=128), dict(split=256, stages=2), dict()):
+        got = fast.attention_decode(qd, kd, vd, td, cd, nh, nkv, hd, scale, window, longest, status, q_start=q_start,
+                                    out=out.clone(), **kw).float().cpu().view(n, nh, hd)
+        ops.raise_on_status(status)
+        row = 0
+        for i, (q, k, v) in enumerate(zip(qs, ks, vs)):
+            want = plain.causal_attention(q, k, v, scale, window=window)
+            torch.testing.assert_close(got[row : row + q.shape[0]], want, rtol=2e-2, atol=2e-2,
+                                       msg=lambda m: f"{kw} request {i} (context {ctx_lens[i]}, {q_lens[i]} queries): {m}")
+            row += q.shape[0]
+
+
 @pytest.mark.parametrize("nh,nkv,hd,ps,window", [(12, 2, 128, 16, None), (3, 1, 64, 32, None), (4, 2, 128, 8, 200)])
 def test_attention_prefill_cuts_long_rows_of_keys(ops, status, fast, nh, nkv, hd, ps, window):
     """Query tiles with long rows of keys can be walked by several CTAs, whose partial results the
