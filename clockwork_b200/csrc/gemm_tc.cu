@@ -64,6 +64,7 @@ struct GemmParams {
     const float* emit_g;      // [N] or null
     bf16* emit_x;             // [T, N]
     float* emit_part;         // [T, gridDim.x]
+    int* split_flags;         // CTA-pair kernel with splits > 1: two words per tile, zero between launches
 };
 
 #include "gemm_tc_pair.cuh"
@@ -743,6 +744,47 @@ static int balanced_bn(int T, int N, bool swiglu, int sm_count) {
 
 static int g_pair_enabled = 1;
 static int g_forced_bn = 0;
+static int* g_split_flags = nullptr;  // device words for the CTA-pair kernel's split products (zero between launches)
+static int g_split_flags_n = 0;
+// Gives the CTA-pair kernel the device memory through which the splits of a tile take turns (n int32
+// words, zeroed by the caller once; the kernel leaves them zero).  Without it no product is split.
+extern "C" int cw_gemm_tc_set_split_flags(int* words, int n) {
+    g_split_flags = words;
+    g_split_flags_n = words != nullptr ? n : 0;
+    return CW_OK;
+}
+
+// How many ways the inner dimension of a CTA-pair product that adds into its output is split: as many
+// as leave no pair idle, dividing the k-blocks evenly, at least 16 k-blocks each, at most 8.
+static int pair_splits(int tiles, int num_kb, int sm_count) {
+    const int pairs = sm_count / 2;
+    if (g_split_flags == nullptr || 2 * tiles > g_split_flags_n || tiles * 2 > pairs) return 1;
+    int best = 1;
+    for (int d = 2; d <= 8 && d * tiles <= pairs; ++d)
+        if (num_kb % d == 0 && num_kb / d >= 16) best = d;
+    return best;
+}
+
+// Token-tile width for a CTA-pair product that may be split over K.  Measured: a pair's k-block costs
+// about 330 + 0.2 bn nanoseconds whatever the tile's width (the stages in flight bound it), and the
+// splits of a tile store one after the other, each taking about 1000 + 25 bn nanoseconds (a turn of
+// the flag, bn / 16 chunks of stores).
+static int balanced_bn_pair_split(int T, int N, int num_kb, int sm_count) {
+    const int m_tiles = (N + 2 * BM - 1) / (2 * BM), pairs = sm_count / 2;
+    long long best_cost = -1;
+    int best = 256;
+    for (int bn = 256; bn >= 64; bn -= 16) {
+        const int tiles = m_tiles * ((T + bn - 1) / bn);
+        const int splits = pair_splits(tiles, num_kb, sm_count);
+        const long long rounds = ((long long)tiles * splits + pairs - 1) / pairs;
+        const long long cost = rounds * (num_kb / splits) * (330 + bn / 5) + splits * (1000LL + 25 * bn);
+        if (best_cost < 0 || cost < best_cost) {
+            best_cost = cost;
+            best = bn;
+        }
+    }
+    return best;
+}
 // Forces the token-tile width of the prompt-portion kernels (0: chosen automatically); for measurements.
 extern "C" int cw_gemm_tc_set_tile(int bn) {
     if (bn != 0 && (bn < 64 || bn > 256 || bn % 16 != 0)) return CW_ERR_BAD_SIZE;
@@ -755,7 +797,7 @@ static int g_stream_enabled = 1;
 // Switches the persistent form of few-token products over very many weight tiles off or on (measurements).
 extern "C" int cw_gemm_tc_set_stream(int on) { g_stream_enabled = on ? 1 : 0; return CW_OK; }
 
-static Plan make_plan(int T, int N, int K, bool swiglu, int sm_count, bool c_by_tma = true) {
+static Plan make_plan(int T, int N, int K, bool swiglu, int sm_count, bool c_by_tma = true, bool adds = false) {
     Plan pl;
     const int cap = swiglu ? 128 : 256;
     pl.persistent = T > 256 && sm_count > 0 && c_by_tma;  // its epilogue has no other way out than TMA
@@ -785,6 +827,15 @@ static Plan make_plan(int T, int N, int K, bool swiglu, int sm_count, bool c_by_
     }
     pl.kb_per_split = (num_kb + splits - 1) / splits;
     pl.splits = (num_kb + pl.kb_per_split - 1) / pl.kb_per_split;  // no empty split
+    if (pl.pair && adds && g_forced_bn == 0) {
+        // products that add into their output may be split over K when the tiles leave pairs idle
+        pl.bn = balanced_bn_pair_split(T, N, num_kb, sm_count);
+        pl.tiles = ((N + 2 * BM - 1) / (2 * BM)) * ((T + pl.bn - 1) / pl.bn);
+    }
+    if (pl.pair && adds) {
+        pl.splits = pair_splits(pl.tiles, num_kb, sm_count);
+        pl.kb_per_split = num_kb / pl.splits;
+    }
     return pl;
 }
 
@@ -825,7 +876,7 @@ extern "C" int cw_gemm_tc_plan(int T, int N, int K, int swiglu, int sm_count, in
     const Plan pl = make_plan(T, N, K, swiglu != 0, sm_count);
     *bn = pl.bn;
     *splits = pl.splits;
-    *ctas = pl.pair ? 2 * pl.tiles : pl.tiles * pl.splits;
+    *ctas = pl.pair ? 2 * pl.tiles * pl.splits : pl.tiles * pl.splits;
     return CW_OK;
 }
 
@@ -868,7 +919,7 @@ extern "C" int cw_gemm_tc_norm(const void* X, const void* W, const void* W2, con
     const bool c_by_tma = c_row_bytes % 16 == 0 && ((uintptr_t)C & 15) == 0;
     const bool emits = emit_x != nullptr;
     // (a product that finishes or begins a norm has no way out through TMA alone)
-    const Plan pl = make_plan(T, N, K, swiglu, sm_count, c_by_tma && scale_part == nullptr && !emits);
+    const Plan pl = make_plan(T, N, K, swiglu, sm_count, c_by_tma && scale_part == nullptr && !emits, !swiglu && epilogue == 1);
     if (scale_part != nullptr || emits) {
         if (pl.persistent || pl.bn > 128) return CW_ERR_UNSUPPORTED;
         if (scale_part != nullptr && (scale_parts <= 0 || scale_dim <= 0)) return CW_ERR_BAD_SIZE;
@@ -878,7 +929,7 @@ extern "C" int cw_gemm_tc_norm(const void* X, const void* W, const void* W2, con
     if (make_map(&mw, W, N, K, K, BM) != 0) return CW_ERR_UNSUPPORTED;
     if (make_map(&mw2, swiglu ? W2 : W, N, K, K, BM) != 0) return CW_ERR_UNSUPPORTED;
     if (make_map(&mx, X, T, K, ldx, pl.pair ? pl.bn / 2 : pl.bn) != 0) return CW_ERR_UNSUPPORTED;
-    const bool tma_store = pl.splits == 1 && c_by_tma && !emits;  // beginning a norm needs the new values in hand
+    const bool tma_store = (pl.splits == 1 || pl.pair) && c_by_tma && !emits;  // beginning a norm needs the new values in hand
     // prompt portions: the persistent kernel, whose epilogue overlaps the next tile's MMAs
     const bool persistent = pl.persistent;
     CUtensorMap mc = mx;
@@ -890,6 +941,7 @@ extern "C" int cw_gemm_tc_norm(const void* X, const void* W, const void* W2, con
     p.bias = bias; p.C = C; p.status = status; p.bn = pl.bn;
     p.scale_part = scale_part; p.scale_parts = scale_parts; p.scale_eps = scale_eps; p.scale_dim = scale_dim;
     p.emit_g = emit_g; p.emit_x = (bf16*)emit_x; p.emit_part = emit_part;
+    p.split_flags = g_split_flags;
     dim3 grid((N + BM - 1) / BM, (T + pl.bn - 1) / pl.bn, pl.splits);
     if (grid.y > 65535) return CW_ERR_BAD_SIZE;
     if (pl.pair) {
@@ -900,7 +952,8 @@ extern "C" int cw_gemm_tc_norm(const void* X, const void* W, const void* W2, con
                 return (int)cudaGetLastError();
             configured = true;
         }
-        const int pairs = pl.tiles < sm_count / 2 ? pl.tiles : sm_count / 2;
+        const int units = pl.tiles * pl.splits;
+        const int pairs = units < sm_count / 2 ? units : sm_count / 2;
         return cw_launch(gemm_tc_pair_kernel, dim3(2 * pairs), dim3(PAIR_THREADS), PairCfg::SMEM_BYTES, stream, 1, mw, mx, mc, p);
     }
     if (persistent) {

@@ -14,6 +14,16 @@
 // `acc_empty[b]` lives in the leader and counts one arrival per CTA's epilogue.  Every wait is
 // bounded; a CTA that gives up records CW_ST_WAIT_TIMEOUT, and both CTAs meet at the cluster
 // barrier before tensor memory is freed.
+//
+// Few tiles and a long inner dimension (a few hundred tokens against K = 8960): a pair streams its
+// weight rows at the rate its six stages in flight allow (about 3 k-blocks per microsecond), so
+// with fewer tiles than pairs the product's time is K's, whatever the tile's width.  The products
+// that add into the residual are then split over K (p.splits > 1): a unit of work is (tile, split),
+// every split adds its partial tile into the residual with the same TMA reduce-add, and the splits
+// of a tile add in split order: split k waits, before its first store, until split k - 1 has
+// published (p.split_flags[tile] == k) that its stores are complete.  Units are handed out in the
+// order (tile, split) to pairs that all run at once and take their units in ascending order, so the
+// unit waited for is always running or done.
 #pragma once
 #include "tc_common.cuh"
 
@@ -94,7 +104,8 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     const uint32_t accf0 = smem_u32(bars + 2 * C::STAGES), acce0 = smem_u32(bars + 2 * C::STAGES + 2);
     const int bn = p.bn, half_bn = bn >> 1;
     const int m_tiles = (p.N + 2 * BM - 1) / (2 * BM), n_tiles = (p.T + bn - 1) / bn;
-    const int tiles = m_tiles * n_tiles;
+    const int splits = p.splits, nkb = p.kb_per_split;  // splits * nkb == p.num_kb
+    const int tiles = m_tiles * n_tiles * splits;       // units of work: unit u is split u % splits of tile u / splits
     const int pair = blockIdx.x >> 1, pairs = gridDim.x >> 1;
 
     if (tid == 0) {
@@ -120,7 +131,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         // ---- TMA producer (both CTAs): own rows of W, own half of the token tile ------------------------
         const uint32_t stage_tx = C::A_BYTES + half_bn * BK * 2;
         const int my_tiles = pair < tiles ? (tiles - pair + pairs - 1) / pairs : 0;
-        const int total = my_tiles * p.num_kb;  // k-blocks of all this pair's tiles, in order
+        const int total = my_tiles * nkb;  // k-blocks of all this pair's units, in order
         const int early = min(total, C::STAGES);
         bool ok = true;
         int i = 0;
@@ -128,7 +139,8 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         for (int phase = 0; phase < 2; ++phase) {
             if (phase == 1) pdl_wait();
             for (i = 0; i < early; ++i) {
-                const int ts = i / p.num_kb, kb = i - ts * p.num_kb, tile = pair + ts * pairs;
+                const int ts = i / nkb, unit = pair + ts * pairs, tile = unit / splits;
+                const int kb = (unit - tile * splits) * nkb + (i - ts * nkb);  // k-block within K
                 const int m0 = (tile % m_tiles) * 2 * BM + (int)rank * BM;
                 const int n0 = (tile / m_tiles) * bn + (int)rank * half_bn;
                 const uint32_t a_dst = smem_u32(smem + i * C::STAGE_BYTES);
@@ -142,19 +154,20 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             }
         }
         // the rest runs ahead over tiles, bounded by the ring only
-        int kb = early % p.num_kb;
-        for (int tile = pair + (early / p.num_kb) * pairs; tile < tiles && ok; tile += pairs, kb = 0) {
+        int kb = early % nkb;
+        for (int unit = pair + (early / nkb) * pairs; unit < tiles && ok; unit += pairs, kb = 0) {
+            const int tile = unit / splits, kb0 = (unit - tile * splits) * nkb;
             const int m0 = (tile % m_tiles) * 2 * BM + (int)rank * BM;
             const int n0 = (tile / m_tiles) * bn + (int)rank * half_bn;
-            for (; kb < p.num_kb; ++kb, ++i) {
+            for (; kb < nkb; ++kb, ++i) {
                 const int s = i % C::STAGES;
                 ok = mbar_wait(empty0 + 8 * s, ((i / C::STAGES) & 1) ^ 1, give_up);
                 if (!ok) break;
                 const uint32_t a_dst = smem_u32(smem + s * C::STAGE_BYTES);
                 const uint32_t bar = dsmem_addr(full0 + 8 * s, 0);  // the leader's barrier
                 mbar_expect_tx_cluster(bar, stage_tx);
-                tma_load_2d_pair(a_dst, &map_w, kb * BK, m0, bar);
-                tma_load_2d_pair(a_dst + C::A_BYTES, &map_x, kb * BK, n0, bar);
+                tma_load_2d_pair(a_dst, &map_w, (kb0 + kb) * BK, m0, bar);
+                tma_load_2d_pair(a_dst + C::A_BYTES, &map_x, (kb0 + kb) * BK, n0, bar);
             }
         }
         if (*give_up) {
@@ -176,7 +189,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             if (!ok) break;
             tc_fence_after();
             const uint32_t acc = tmem_base + buf * C::BN_MAX;
-            for (int kb = 0; kb < p.num_kb; ++kb, ++i) {
+            for (int kb = 0; kb < nkb; ++kb, ++i) {
                 const int s = i % C::STAGES;
                 ok = mbar_wait(full0 + 8 * s, (i / C::STAGES) & 1, give_up);
                 if (!ok) break;
@@ -201,11 +214,13 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         const uint32_t acce_leader = dsmem_addr(acce0, 0);
         int it = 0, chunk_no = 0;
         bool ok = true;
-        for (int tile = pair; tile < tiles && ok; tile += pairs, ++it) {
+        for (int unit = pair; unit < tiles && ok; unit += pairs, ++it) {
             const int buf = it & 1;
+            const int tile = unit / splits, ks = unit - tile * splits;
             const int m0 = (tile % m_tiles) * 2 * BM + (int)rank * BM;
             const int n0 = (tile / m_tiles) * bn;
             const int f = m0 + row;
+            bool my_turn = ks == 0;  // (a split's stores come after those of the split before it)
             ok = mbar_wait(accf0 + 8 * buf, (it >> 1) & 1, give_up);
             {
                 // one decision for all 128 threads: they meet at named barriers below
@@ -220,7 +235,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             if (!ok) break;
             tc_fence_after();
             const uint32_t taddr = tmem_base + buf * C::BN_MAX + ((uint32_t)(quarter * 32) << 16);
-            const float bias = (p.bias != nullptr && f < p.N) ? p.bias[f] : 0.f;
+            const float bias = (p.bias != nullptr && f < p.N && ks == 0) ? p.bias[f] : 0.f;
             // Only chunks that hold tokens are read out and stored, and every chunk that runs commits exactly
             // one bulk group (an empty one when this CTA's features lie beyond N), so that `wait_group.read 1`
             // below means what it says: the store that read this staging buffer two chunks ago is done with it.
@@ -249,6 +264,16 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 asm volatile("bar.sync 1, 128;" ::: "memory");
                 if (etid == 0) {
+                    if (!my_turn) {
+                        // both CTAs of the pair hold the same tile: each waits for itself
+                        const long long t0 = clock64();
+                        int seen;
+                        do {
+                            asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(seen) : "l"(p.split_flags + 2 * tile + rank) : "memory");
+                        } while (seen != ks && clock64() - t0 < WAIT_CYCLES);
+                        if (seen != ks) *give_up = 1;
+                        my_turn = true;
+                    }
                     if (m0 < p.N) {
                         if (p.epilogue == 1)
                             asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.bulk_group [%0, {%2, %3}], [%1];"
@@ -259,6 +284,13 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                     }
                     asm volatile("cp.async.bulk.commit_group;" ::: "memory");
                 }
+            }
+            if (splits > 1 && etid == 0) {
+                // this split's adds are complete: the next split of the tile may add (the last one leaves
+                // the flag at zero for the next launch)
+                asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+                const int next = ks + 1 == splits ? 0 : ks + 1;
+                asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(p.split_flags + 2 * tile + rank), "r"(next) : "memory");
             }
         }
         if (etid == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");  // all stores done before exit

@@ -16,6 +16,7 @@ from .library import check, library
 
 _state: dict[int, dict] = {}
 _configured = False
+SPLIT_FLAG_WORDS = 8192
 
 
 def _configure() -> None:
@@ -36,6 +37,8 @@ def _configure() -> None:
     lib.cw_gemm_tc_set_stream.restype = c_int
     lib.cw_gemm_tc_set_tile.argtypes = [I]
     lib.cw_gemm_tc_set_tile.restype = c_int
+    lib.cw_gemm_tc_set_split_flags.argtypes = [P, I]
+    lib.cw_gemm_tc_set_split_flags.restype = c_int
     _configured = True
 
 
@@ -66,8 +69,13 @@ def _device_state(device: torch.device) -> dict:
         st = {
             "status": device_status(device),  # the word the engine reads after its steps
             "sms": torch.cuda.get_device_properties(device).multi_processor_count,
+            # the words through which the splits of a tile take turns when a prompt-portion product is
+            # split over its inner dimension; zero between launches, never freed
+            "split_flags": torch.zeros(SPLIT_FLAG_WORDS, dtype=torch.int32, device=device),
         }
         _state[index] = st
+        _configure()
+        library().cw_gemm_tc_set_split_flags(_ptr(st["split_flags"]), SPLIT_FLAG_WORDS)
     return st
 
 

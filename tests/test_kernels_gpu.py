@@ -333,6 +333,29 @@ def test_gemm_tc_single_cta_persistent_kernel(ops, gemm_tc, t, n, k):
         gemm_tc.set_pair_kernel(True)
 
 
+@pytest.mark.parametrize("t,n,k", [(300, 1536, 8960), (1056, 1536, 8960), (520, 1000, 2048), (700, 300, 4104), (2048, 1536, 8960)])
+def test_gemm_tc_pair_kernel_adds_in_split_order(ops, gemm_tc, t, n, k):
+    """Prompt-portion products that add into the residual: with few tiles and a long inner dimension
+    the CTA-pair kernel splits K over pairs, whose partial tiles add into the output in split order.
+    Against float64, and bit for bit the same on every run."""
+    g = torch.Generator().manual_seed(t + n + k)
+    x = torch.randn(t, k, generator=g).bfloat16()
+    w = (torch.randn(n, k, generator=g) * 0.05).bfloat16()
+    bias = torch.randn(n, generator=g)
+    res0 = torch.randn(t, n, generator=g)
+    want = (res0.double() + x.double() @ w.double().T + bias.double()).float()
+    xd, wd, bd = x.to(DEV), w.to(DEV), bias.to(DEV)
+    outs = []
+    for _ in range(4):
+        out = res0.to(DEV).clone()
+        gemm_tc.gemm(xd, wd, bd, out=out, epilogue=ops.EPILOGUE_ADD_F32)
+        outs.append(out.cpu())
+    torch.testing.assert_close(outs[0], want, rtol=1e-4, atol=1e-5 * max(1.0, float(want.abs().max())))
+    assert all(torch.equal(o, outs[0]) for o in outs[1:])
+    assert int(gemm_tc._device_state(torch.device(DEV))["split_flags"].abs().sum()) == 0  # left at zero for the next launch
+    ops.raise_on_status(gemm_tc.status(DEV))
+
+
 @pytest.mark.parametrize("t,n,k", [(1, 57000, 128), (8, 56840, 264), (50, 57096, 136), (64, 60000, 64)])
 def test_gemm_tc_few_tokens_over_many_weight_tiles(ops, gemm_tc, t, n, k):
     """A logits-like product (three rounds of weight tiles or more) walks its tiles with one CTA per
