@@ -82,7 +82,8 @@ class StateSlots:
       host.  The reference keeps the same on the host (``clockwork/engine/model_runner.py:46``,
       ``139-145``: Sequence fields and a CPU generator per request).
     * one tensor ``[slots, *shape]`` per cache layer whose mixer asked for state of its own
-      (``SlotStateNeed``), zeroed when a request takes the slot.  This architecture has none."""
+      (``SlotStateNeed``), zeroed when a request takes the slot, plus one scratch row for the padding
+      rows of captured steps.  This architecture has none."""
 
     def __init__(self, needs: dict[int, SlotStateNeed], num_slots: int, device) -> None:
         self.num_slots = num_slots
@@ -91,9 +92,10 @@ class StateSlots:
         self._owner: dict[int, str] = {}
         self.tensors: dict[int, torch.Tensor] = {}
         self.request: torch.Tensor | None = None
+        self.scratch_slot = num_slots  # a row beyond the requests' rows: where padding rows of a fixed-shape step read and write
         if device is not None:
             for layer, need in needs.items():
-                self.tensors[layer] = torch.zeros((num_slots, *need.shape), dtype=need.dtype, device=device)
+                self.tensors[layer] = torch.zeros((num_slots + 1, *need.shape), dtype=need.dtype, device=device)
             self.request = torch.zeros((len(REQUEST_STATE_FIELDS), num_slots), dtype=torch.int32, device=device)
 
     @property

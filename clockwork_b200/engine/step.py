@@ -241,7 +241,9 @@ class DecodeGraph:
         )
         tables = [view(f"tables{g}").view(batch, self.max_blocks) for g in range(G)]
         kv_slots = [view(f"slots{g}") for g in range(G)]
-        ctx.views = cache.views(tables, kv_slots, None, [])
+        # mixers with state of their own: row r's state is in slot row_slot[r] (padding rows use the scratch row)
+        state_rows = torch.zeros(batch, dtype=torch.int64, device=runner.device) if cache.state.needs else None
+        ctx.views = cache.views(tables, kv_slots, state_rows, [])
         for name, rule in self._scalar_rules.items():
             ctx.extras[name] = view(f"scalar:{name}")
             self.h[f"scalar:{name}"][0] = rule(batch, max_ctx)
@@ -249,6 +251,9 @@ class DecodeGraph:
         as_float = lambda name: view(name).view(torch.float32)  # noqa: E731
 
         def run():
+            if state_rows is not None:
+                row_slot = view("row_slot")
+                state_rows.copy_(torch.where(row_slot < 0, cache.state.scratch_slot, row_slot))
             ops.step_from_state(view("row_slot"), view("fresh"), view("fresh_values").view(F, batch), state, tables, kv_slots,
                                 cache.page_size, cache.num_pages, view("tokens"), view("positions"), view("ctx_lens"),
                                 view("tok_seq"), as_float("temperature"), view("top_k"), as_float("top_p"),
@@ -359,8 +364,9 @@ class ModelRunner:
 
     def enable_graphs(self, max_ctx: int, max_batch: int) -> bool:
         """Let steps in which every request brings exactly one token replay a captured CUDA graph
-        (one per batch-size bucket).  Only for models whose parts are all safe to capture."""
-        if not self.model.graph_safe() or self.cache.state.needs:
+        (one per batch-size bucket).  Only for models whose parts are all safe to capture (a mixer with
+        state of its own is, if it finds its rows through the device-side slot list of its view)."""
+        if not self.model.graph_safe():
             return False
         self.graph_max_ctx, self.graph_max_batch = max_ctx, max_batch
         self.model.reserve_for_steps(max_batch, max_ctx)  # scratch that captured graphs point at is set up once

@@ -70,9 +70,9 @@ class PagedView:
 class StateView:
     """One layer's fixed-size states: ``state[slots[s]]`` belongs to request ``s`` of the step."""
 
-    state: torch.Tensor  # [num_slots, *shape]
-    slots: torch.Tensor  # int64 [S]
-    slots_host: list[int] = field(default_factory=list)
+    state: torch.Tensor  # [num_slots + 1, *shape] (the last row: scratch for padding rows)
+    slots: torch.Tensor  # int64 [S] on the device
+    slots_host: list[int] = field(default_factory=list)  # the same on the host (empty in a captured step)
 
 
 @dataclass
@@ -156,8 +156,9 @@ class Part:
     def name(self, suffix: str) -> str:
         return f"{self.prefix}.{suffix}" if self.prefix else suffix
 
-    graph_safe = False  # True when forward only launches kernels on the current stream (no host
-    # reads of device data, no Python-side loops over step contents): it may be captured in a CUDA graph
+    graph_safe = False  # True when, in a step in which every request brings one token, forward only launches
+    # kernels on the current stream (no host reads of device data, no Python-side use of the step's
+    # host-side lists, which hold the capture's placeholders): such a step may be captured in a CUDA graph
 
     def tensor_decls(self) -> Iterable[TensorDecl]:
         return ()

@@ -51,6 +51,22 @@ class DecayingSumMixer(Mixer):
         return (out @ self.w_out.float().T).to(self.dtype)  # a delta: the next norm adds it
 
 
+class CapturedDecayingSumMixer(DecayingSumMixer):
+    """The same mixer, able to run inside a captured single-token step: there it finds its rows through the
+    view's device-side slot list (padding rows of the captured batch land in the scratch row) and uses no
+    host-side list.  Steps with prompt portions take the loop above."""
+
+    graph_safe = True
+
+    def forward(self, ctx, x, view, stream):
+        if not ctx.all_single_token:
+            return super().forward(ctx, x, view, stream)
+        u = x.float() @ self.w_in.float().T  # [S, d]: one token per request
+        state = view.state.index_select(0, view.slots) * self.decay + u
+        view.state.index_copy_(0, view.slots, state)
+        return (state @ self.w_out.float().T).to(self.dtype)
+
+
 class ToyArchitecture:
     name = "ToyStateLM"
 
@@ -67,7 +83,7 @@ class ToyArchitecture:
                                               o_bias=True, scale=0.3, window=window,
                                               position=PartSpec("rope_neox", {"theta": 100.0, "rotary_dim": 8})))
 
-        mixers = [attention(None), PartSpec("toy_decaying_sum", dict(hidden_size=h, state_size=raw["state"], decay=0.9)),
+        mixers = [attention(None), PartSpec(raw.get("mixer_kind", "toy_decaying_sum"), dict(hidden_size=h, state_size=raw["state"], decay=0.9)),
                   attention(raw["window"])]
         layers = [LayerSpec("prenorm_residual", m, ffn, norm, norm, f"model.layers.{i}") for i, m in enumerate(mixers)]
         schedule = [ExecStep(0), ExecStep(1), ExecStep(2), ExecStep(0, cache_layer=0, write_cache=False)]
@@ -80,6 +96,7 @@ RAW = dict(architectures=["ToyStateLM"], hidden_size=48, vocab_size=90, eps=1e-5
 @pytest.fixture(scope="module")
 def toy_dir(tmp_path_factory):
     register_mixer("toy_decaying_sum", DecayingSumMixer, replace=True)
+    register_mixer("toy_decaying_sum_captured", CapturedDecayingSumMixer, replace=True)
     register_architecture(ToyArchitecture(), replace=True)
     import json
 
@@ -210,3 +227,29 @@ def test_toy_model_generates_through_the_engine(toy_dir):
             ids.append(int(plain_toy_logits(toy_dir, ids)[-1].argmax()))
         assert out.token_ids == ids[len(prompt):]
     assert eng.cache.state.num_free == 2
+
+
+def test_toy_model_with_state_runs_in_captured_steps(toy_dir, tmp_path):
+    """A mixer with state of its own whose single-token path uses device-side data only is captured in the
+    decode graphs like the framework's own parts (its state rows follow the requests' slots, padding rows
+    use the scratch row), steps run ahead of the host, and the tokens are those of the plain form."""
+    import json
+    import shutil
+
+    config = json.loads((toy_dir / "config.json").read_text())
+    config["mixer_kind"] = "toy_decaying_sum_captured"
+    (tmp_path / "config.json").write_text(json.dumps(config))
+    shutil.copy(toy_dir / "model.safetensors", tmp_path / "model.safetensors")
+    cfg = EngineConfig.defaults(str(tmp_path), dtype="float32", block_size=4, num_blocks=48, max_num_seqs=4,
+                                max_num_batched_tokens=16, max_model_len=128)
+    eng = LLMEngine(cfg)
+    assert eng.uses_graphs and not eng.prefix_cache.enabled
+    prompts = [tokens(19, 3), tokens(6, 4), tokens(11, 5)]
+    outs = eng.generate(prompts, [SamplingParams(max_tokens=n, ignore_eos=True) for n in (9, 14, 6)])
+    assert eng.runner.graphs and eng.steps_run_ahead > 0
+    for prompt, out in zip(prompts, outs):
+        ids = list(prompt)
+        for _ in range(out.num_generated_tokens):
+            ids.append(int(plain_toy_logits(toy_dir, ids)[-1].argmax()))
+        assert out.token_ids == ids[len(prompt):]
+    assert eng.cache.state.num_free == 4 and eng.cache.requests == {}
