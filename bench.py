@@ -370,6 +370,8 @@ def main() -> int:
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the shape has (reported in config)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--shape", default="qwen2.5-1.5b",
+                    help="with --only: another size that the architecture knows by name (qwen2.5-7b, qwen2.5-32b)")
     ap.add_argument("--skip-points", action="store_true", help="leave out the points and the prefill (quick runs)")
     ap.add_argument("--only", choices=["decode", "prefill", "mixed", "shared-prefix"], default=None,
                     help="run one part only, once, and print its figures (for profiling runs under ncu)")
@@ -394,10 +396,13 @@ def main() -> int:
 
     assert torch.cuda.is_available(), "bench.py needs a CUDA device"
     torch.cuda.set_device(0)
-    raw = shape_config("qwen2.5-1.5b", args.layers)
+    if args.shape != "qwen2.5-1.5b" and args.only is None:
+        print("bench.py: the benchmark line is that of qwen2.5-1.5b; other shapes run with --only")
+        return 2
+    raw = shape_config(args.shape, args.layers)
     registered = shape_config("qwen2.5-1.5b")
     assert all(registered[k] == v for k, v in QWEN25_1P5B.items()), "the two arms would not run the same shape"
-    full_layers = registered["num_hidden_layers"]
+    full_layers = shape_config(args.shape)["num_hidden_layers"]
     model = random_model(raw, seed=0, dtype="bfloat16", device="cuda:0")
     vocab = raw["vocab_size"]
     rng = random.Random(0)
