@@ -14,7 +14,27 @@
 // merged by the CTA that finishes last, in split order.
 //
 // Scores, softmax and accumulation are float32; probabilities are rounded to bfloat16 for P.V.
+//
+// How the splits of a (request, KV head) group meet, two forms.  Through a thread-block cluster (the
+// usual one, up to 16 splits): the splits of a group are the CTAs of one cluster; each pushes its
+// normalised partial output, cut into as many slices as there are splits, into the others' shared
+// memory (slice j to CTA j) with its log-sum-exps, arrives on their barriers, waits for theirs, and
+// merges and stores its own slice, sources in split order: no global scratch, no counter, no second
+// pass by one CTA.  Through global memory (grids of more splits than a cluster holds, and the entry
+// point with caller-given scratch): partials and log-sum-exps go to a float32 workspace and the CTA
+// that arrives last at the group's counter merges them, in split order too.
 #include "attention_mma.cuh"
+
+#define MAX_CLUSTER 16
+
+__device__ __forceinline__ uint32_t peer_smem(uint32_t local_addr, uint32_t rank) {
+    uint32_t remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
+    return remote;
+}
+__device__ __forceinline__ void cluster_barrier() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
 
 #define TILE 64
 #define MIN_SPLIT 128  // smallest context split (tokens per CTA); the grid's z extent is sized for it
@@ -37,6 +57,8 @@ struct DecodeParams {
     int max_split_pages;  // page ids a split may need (sizes the shared-memory page list)
     int stages;           // tiles in flight per CTA: 4 (default) or 2
     int swizzle;          // with 2 tiles in flight: the unpadded, swizzled K/V layout (three CTAs per SM)
+    int cluster;          // > 1: the grid's z extent is one cluster of this many CTAs and the splits meet through it
+    int max_ctx;          // the bound on every context that sized the grid
     int* counters;   // [S * nkv * qgroups]
     int* status;
     // Fused position encoding and cache write (kv_new != null): q, and the new token's k and v, are
@@ -68,7 +90,7 @@ __device__ __forceinline__ bool mine_newest(int newest, int t0, int t1, int kv_b
 // division's instruction sequence exists once in the kernel instead of at every use.
 __device__ __noinline__ int2 block_and_offset(int pos, int page_size) { return make_int2(pos / page_size, pos % page_size); }
 
-template <int HD, int ST, bool SWIZZLE>
+template <int HD, int ST, bool SWIZZLE, bool CL>
 __global__ void __launch_bounds__(NWARPS * 32)
 attn_decode_kernel(const DecodeParams p) {
     constexpr int LD = HD + 8;  // padded q row (elements): consecutive rows fall into different banks
@@ -89,6 +111,11 @@ attn_decode_kernel(const DecodeParams p) {
     __shared__ __align__(16) bf16 new_s[2 * HD]; // the newest token's k and v
     __shared__ float cs_s[HD];                  // cos, sin of the newest position (fused rotation)
     __shared__ int last_flag;
+    // cluster merge: the slices of this CTA's share that the splits of the group push here, by source
+    // (a source's slice is `quota` groups of four outputs), their log-sum-exps, and the barrier they arrive on
+    __shared__ float4 inbox_s[CL ? 16 * HD / 4 + MAX_CLUSTER : 1];
+    __shared__ float lse_all[CL ? MAX_CLUSTER : 1][16];
+    __shared__ __align__(8) unsigned long long merge_bar;
 
     // Nothing below reads what the preceding kernels of this step wrote until pdl_wait(): context
     // lengths, block tables, positions and the split size are inputs of the step, and cached keys and
@@ -103,11 +130,32 @@ attn_decode_kernel(const DecodeParams p) {
     const int h0 = kvh * G + qg * 16;
     const int rows = min(16, G - qg * 16);
     int row = s;  // the request's row in q, kv_new, slots and out
+    bool mine = true;
     if (p.q_start != nullptr) {
         row = p.q_start[s];
-        if (p.q_start[s + 1] - row != 1) return;  // a prompt portion: the prefill kernel's work
+        mine = p.q_start[s + 1] - row == 1;  // (a prompt portion is the prefill kernel's work)
     }
-    const int ctx = p.ctx_lens[s];
+    const int ctx = mine ? p.ctx_lens[s] : 0;
+    int SPLIT = p.split_ptr != nullptr ? *p.split_ptr : p.split;
+    if (CL) {
+        // no more splits than the cluster has CTAs, whatever the step's policy asked for
+        const int least = ((p.max_ctx + p.cluster - 1) / p.cluster + TILE - 1) / TILE * TILE;
+        SPLIT = max(SPLIT, least);
+    }
+    const int kv_begin = p.window > 0 ? max(0, ctx - p.window) : 0;
+    const int nsplits = ctx > 0 ? (ctx + SPLIT - 1) / SPLIT : 0;
+    const int first_split = kv_begin / SPLIT;
+    const int active = nsplits - first_split;  // the splits of this group that have keys
+    if (CL) {
+        // Every CTA of the cluster, also one with nothing to do, passes this barrier; behind it the
+        // barriers that the group's splits arrive on exist, each expecting the other active splits.
+        if (tid == 0) {
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(&merge_bar)), "r"(max(1, active - 1)) : "memory");
+            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        }
+        cluster_barrier();
+    }
+    if (!mine) return;
     if (ctx <= 0) {  // a padding row of a fixed-shape batch
         pdl_wait();
         if (sp == 0)
@@ -115,10 +163,6 @@ attn_decode_kernel(const DecodeParams p) {
                 p.out[((size_t)row * p.nh + h0 + i / HD) * HD + i % HD] = __float2bfloat16_rn(0.f);
         return;
     }
-    const int SPLIT = p.split_ptr != nullptr ? *p.split_ptr : p.split;
-    const int kv_begin = p.window > 0 ? max(0, ctx - p.window) : 0;
-    const int nsplits = (ctx + SPLIT - 1) / SPLIT;
-    const int first_split = kv_begin / SPLIT;
     if (sp < first_split || sp >= nsplits) return;  // (no end record: these CTAs do nothing)
     const int t0 = sp * SPLIT, t1 = min(ctx, t0 + SPLIT);
     const int* table = p.block_tables + (size_t)s * p.max_blocks;
@@ -399,7 +443,6 @@ attn_decode_kernel(const DecodeParams p) {
         base[(g + 8) * HD + nt * 8 + 2 * t + 1] = o_acc[nt][3];
     }
     __syncthreads();
-    const int active = nsplits - first_split;
     // per query row: the warps' shares (normalised) and the split's log2-sum-exp, computed once
     if (tid < 16) {
         const int r = tid;
@@ -435,12 +478,84 @@ attn_decode_kernel(const DecodeParams p) {
             o.x = pack_bf16(val.x, val.y);
             o.y = pack_bf16(val.z, val.w);
             *reinterpret_cast<uint2*>(p.out + ((size_t)row * p.nh + h) * HD + d) = o;
+        } else if (CL) {
+            // group `item` of four outputs belongs to the slice of split (item % active): into that CTA's
+            // inbox, in this split's row of it
+            const int me = sp - first_split, owner = item % active;
+            const int quota = (rows * (HD / 4) + active - 1) / active;
+            float4* dst = &inbox_s[me * quota + item / active];
+            if (owner == me)
+                *dst = val;
+            else
+                asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(peer_smem(smem_addr(dst), first_split + owner)),
+                             "f"(val.x), "f"(val.y), "f"(val.z), "f"(val.w) : "memory");
         } else {
             *reinterpret_cast<float4*>(p.part_o + (((size_t)s * p.nh + h) * p.max_splits + sp) * HD + d) = val;
             if (d == 0) p.part_lse[((size_t)s * p.nh + h) * p.max_splits + sp] = w_s[r][NWARPS];
         }
     }
     if (active == 1) {
+        cw_trace_end();
+        return;
+    }
+    if (CL) {
+        // ---- the splits exchange slices through the cluster and each merges its own ---------------------
+        const int me = sp - first_split;
+        const int items = rows * (HD / 4), quota = (items + active - 1) / active;
+        for (int i = tid; i < rows * active; i += blockDim.x) {  // this split's log-sum-exps, to every split of the group
+            const int k = i / rows, r = i - k * rows;
+            float* dst = &lse_all[me][r];
+            if (k == me)
+                *dst = w_s[r][NWARPS];
+            else
+                asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(peer_smem(smem_addr(dst), first_split + k)), "f"(w_s[r][NWARPS]) : "memory");
+        }
+        __syncthreads();  // all of this CTA's pushes are issued and ordered before thread 0's arrivals
+        if (tid == 0) {
+            asm volatile("fence.acq_rel.cluster;" ::: "memory");
+            for (int k = 0; k < active; ++k)
+                if (k != me)
+                    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];"
+                                 ::"r"(peer_smem(smem_addr(&merge_bar), first_split + k)) : "memory");
+            // the other splits' pushes have landed when all of them have arrived here
+            const long long t_begin = clock64();
+            uint32_t done = 0;
+            while (!done) {
+                asm volatile(
+                    "{\n\t.reg .pred p;\n\t"
+                    "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], 0;\n\t"
+                    "selp.u32 %0, 1, 0, p;\n\t}"
+                    : "=r"(done) : "r"(smem_addr(&merge_bar)) : "memory");
+                if (!done && clock64() - t_begin > 2000000000LL) {
+                    cw_report(p.status, CW_ST_WAIT_TIMEOUT, 100 + s, sp);
+                    break;
+                }
+            }
+        }
+        __syncthreads();
+        for (int slot = tid; slot < quota; slot += blockDim.x) {
+            const int item = slot * active + me;
+            if (item >= items) continue;
+            const int r = item / (HD / 4), d = (item % (HD / 4)) * 4;
+            float m = -INFINITY, W = 0.f;
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 1
+            for (int k = 0; k < active; ++k) m = fmaxf(m, lse_all[k][r]);
+#pragma unroll 4
+            for (int k = 0; k < active; ++k) {  // sources in split order
+                const float lk = lse_all[k][r];
+                const float4 x = inbox_s[k * quota + slot];
+                const float w = (lk == -INFINITY) ? 0.f : fast_exp2(lk - m);
+                W += w;
+                acc.x = fmaf(w, x.x, acc.x); acc.y = fmaf(w, x.y, acc.y);
+                acc.z = fmaf(w, x.z, acc.z); acc.w = fmaf(w, x.w, acc.w);
+            }
+            const float inv = W > 0.f ? 1.f / W : 0.f;
+            uint2 o;
+            o.x = pack_bf16(acc.x * inv, acc.y * inv);
+            o.y = pack_bf16(acc.z * inv, acc.w * inv);
+            *reinterpret_cast<uint2*>(p.out + ((size_t)row * p.nh + h0 + r) * HD + d) = o;
+        }
         cw_trace_end();
         return;
     }
@@ -513,8 +628,8 @@ attn_decode_kernel(const DecodeParams p) {
     cw_trace_end();
 }
 
-template <int HD, int ST, bool SWIZZLE>
-static int launch_decode_st(const DecodeParams& p, int S, int splits, cudaStream_t stream) {
+template <int HD, int ST, bool SWIZZLE, bool CL>
+static int launch_decode_cl(const DecodeParams& p, int S, int splits, cudaStream_t stream) {
     constexpr int LD = HD + 8;
     constexpr int LDK = (SWIZZLE && HD % 64 == 0) ? HD : HD + 8;
     const int SMEM = (16 * LD + 2 * ST * TILE * LDK) * 2 + p.max_split_pages * 4;
@@ -523,12 +638,21 @@ static int launch_decode_st(const DecodeParams& p, int S, int splits, cudaStream
     static int configured = 0;
     if (SMEM > configured) {
         if (SMEM > 48 * 1024 &&
-            cudaFuncSetAttribute(attn_decode_kernel<HD, ST, SWIZZLE>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess)
+            cudaFuncSetAttribute(attn_decode_kernel<HD, ST, SWIZZLE, CL>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess)
+            return (int)cudaGetLastError();
+        if (CL && cudaFuncSetAttribute(attn_decode_kernel<HD, ST, SWIZZLE, CL>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) != cudaSuccess)
             return (int)cudaGetLastError();
         configured = SMEM;
     }
     dim3 grid(p.nkv * p.qgroups, S, splits);
-    return cw_launch(attn_decode_kernel<HD, ST, SWIZZLE>, grid, dim3(NWARPS * 32), SMEM, stream, 1, p);
+    return cw_launch(attn_decode_kernel<HD, ST, SWIZZLE, CL>, grid, dim3(NWARPS * 32), SMEM, stream, CL ? (unsigned)splits : 1u, p);
+}
+
+template <int HD, int ST, bool SWIZZLE>
+static int launch_decode_st(const DecodeParams& p, int S, int splits, cudaStream_t stream) {
+    // (the cluster form for head sizes up to 128: the larger ones have no room for its inbox beside their tiles)
+    if (HD <= 128 && p.cluster > 1) return launch_decode_cl<HD, ST, SWIZZLE, (HD <= 128)>(p, S, splits, stream);
+    return launch_decode_cl<HD, ST, SWIZZLE, false>(p, S, splits, stream);
 }
 
 template <int HD>
@@ -616,13 +740,26 @@ extern "C" int cw_attention_decode_rows(const void* q, int q_stride, void* out, 
     p.num_slots = num_pages * page_size;
     p.stages = stages & 0xFF;        // tiles in flight
     p.swizzle = (stages >> 8) & 1;   // bit 8: the unpadded, swizzled K/V layout (with two tiles in flight)
+    // bits 16..20: the splits of a group meet through a cluster of this many CTAs (2..16); 0: through the
+    // workspace.  The grid's z extent is then the cluster and the kernel never cuts finer than it allows.
+    p.cluster = (stages >> 16) & 0x1F;
+    p.max_ctx = max_ctx;
+    if (p.cluster > MAX_CLUSTER || hd > 128) p.cluster = 0;
     // the grid is sized for the smallest split; a larger run-time split leaves the later CTAs idle
     if (split_ptr == nullptr && (split < MIN_SPLIT || split % TILE != 0)) return CW_ERR_BAD_SIZE;
-    const int splits = (max_ctx + MIN_SPLIT - 1) / MIN_SPLIT;
+    int splits = (max_ctx + MIN_SPLIT - 1) / MIN_SPLIT;
+    if (p.cluster > 1)
+        splits = p.cluster;
+    else
+        p.cluster = 0;
+    if (!p.cluster && splits > 1 && (part_o == nullptr || part_lse == nullptr || counters == nullptr)) return CW_ERR_BAD_SIZE;
     p.max_splits = splits;
     p.split = split; p.split_ptr = split_ptr;
     // a split may span the whole context when split_ptr decides at run time
-    const int span = split_ptr != nullptr ? max_ctx : (split < max_ctx ? split : max_ctx);
+    // (a cluster makes the kernel cut no finer than the context bound divided by its size)
+    const int least = p.cluster ? ((max_ctx + p.cluster - 1) / p.cluster + TILE - 1) / TILE * TILE : 0;
+    const int host_split = split > least ? split : least;
+    const int span = split_ptr != nullptr ? max_ctx : (host_split < max_ctx ? host_split : max_ctx);
     p.max_split_pages = (span + page_size - 1) / page_size + 1;
     if (splits > 65535) return CW_ERR_BAD_SIZE;
     switch (hd) {

@@ -497,9 +497,14 @@ def test_attention_decode_kernel(ops, status, fast, nh, nkv, hd, ps, window):
     assert torch.equal(again, out)
     # other ways of cutting the contexts (coarser, whole, chosen by the policy, given on the device)
     # ... and the other variants of the kernel: two tiles in flight, padded and swizzled K/V tiles
+    # ... and the splits meeting through thread-block clusters of 16, 8 and 2 CTAs instead of the workspace
+    # (a cluster of 2 over contexts bounded by 2,048 makes the kernel cut no finer than 1,024 tokens)
+    cl = fast.CLUSTER_SHIFT
     for kw in (dict(split=512), dict(split=1344), dict(), dict(split_dev=torch.tensor([320], dtype=torch.int32, device=DEV)),
                dict(split=128, stages=2), dict(split=128, stages=2 | fast.SWIZZLED), dict(split=384, stages=2 | fast.SWIZZLED),
-               dict(stages=2 | fast.SWIZZLED)):
+               dict(stages=2 | fast.SWIZZLED), dict(split=128, stages=16 << cl), dict(split=128, stages=2 | 16 << cl),
+               dict(split=256, stages=2 | fast.SWIZZLED | 8 << cl), dict(stages=4 | 2 << cl),
+               dict(split_dev=torch.tensor([192], dtype=torch.int32, device=DEV), stages=2 | 16 << cl)):
         other = fast.attention_decode(wide.to(dtype).to(DEV), k_cache.to(DEV), v_cache.to(DEV), tables.to(DEV),
                                       torch.tensor(ctx_lens, dtype=torch.int32, device=DEV), nh, nkv, hd, scale, window,
                                       2048, status, **kw).float().cpu().view(len(ctx_lens), nh, hd)
