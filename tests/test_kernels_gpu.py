@@ -290,6 +290,74 @@ def test_sample_matches_the_plain_rule(ops, temperature, top_k, top_p):
     assert got == want
 
 
+def test_step_inputs_from_the_request_state_table(ops, status):
+    """``step_from_state``: rows name slots of the state table; fresh rows overwrite their column first;
+    token, position, context length, cache slot (through the row's block table, two page groups) and the
+    sampling parameters come out of the table; the uniform number is the host's ``uniform_for`` of the
+    column's seed and draw counter, bit for bit; padding rows and a page outside the pool are handled.
+    Then ``argmax`` with the table: the token lands in the column and position and draws advance."""
+    import numpy as np
+
+    from clockwork_b200.engine.step import fresh_row
+    from clockwork_b200.sampling import uniform_for
+
+    slots, b, ps, max_blocks, pages = 7, 5, 8, 6, 40
+    fields = len(ops.REQUEST_STATE_FIELDS)
+    state = torch.zeros(fields, slots, dtype=torch.int32)
+    # slot 3 goes on from what the table holds; slots 5 and 0 get fresh columns; row 3 is padding; slot 6 has a bad page
+    held = fresh_row(position=19, last_token=77, draws=4, seed=(1 << 63) + 12345, temperature=0.7, top_k=11, top_p=0.9)
+    state[:, 3] = torch.tensor(held, dtype=torch.int64).to(torch.int32)
+    state[:, 6] = torch.tensor(fresh_row(position=9, last_token=5), dtype=torch.int64).to(torch.int32)
+    rows = [3, 5, 0, -1, 6]
+    fresh_cols = {1: fresh_row(33, 1234, 2, 99, 1.25, 0, 1.0), 2: fresh_row(0, 9)}
+    fresh = torch.tensor([0, 1, 1, 0, 0], dtype=torch.int32)
+    fresh_values = torch.zeros(fields, b, dtype=torch.int32)
+    for r, col in fresh_cols.items():
+        fresh_values[:, r] = torch.tensor(col, dtype=torch.int64).to(torch.int32)
+    g = torch.Generator().manual_seed(3)
+    tables = [torch.randint(0, pages, (b, max_blocks), generator=g, dtype=torch.int32) for _ in range(2)]
+    tables[1][4, 1] = pages + 3  # the page of row 4's position 9 in group 1 lies outside the pool
+    dev = lambda t: t.to(DEV)  # noqa: E731
+    state_d, fresh_d = dev(state), dev(fresh)
+    out_i = {k: torch.full((b,), -7, dtype=torch.int32, device=DEV) for k in ("tokens", "positions", "ctx_lens", "tok_seq", "top_k")}
+    out_f = {k: torch.full((b,), -7.0, device=DEV) for k in ("temperature", "top_p", "uniform")}
+    kv = [torch.full((b,), -7, dtype=torch.int32, device=DEV) for _ in range(2)]
+    ops.step_from_state(dev(torch.tensor(rows, dtype=torch.int32)), fresh_d, dev(fresh_values), state_d, [dev(t) for t in tables], kv,
+                        ps, pages, out_i["tokens"], out_i["positions"], out_i["ctx_lens"], out_i["tok_seq"],
+                        out_f["temperature"], out_i["top_k"], out_f["top_p"], out_f["uniform"], status)
+    torch.cuda.synchronize()
+    with pytest.raises(RuntimeError, match="page id outside the pool"):
+        ops.raise_on_status(status)
+    assert fresh_d.tolist() == [0, 0, 0, 0, 0]  # used and cleared
+    cols = {0: held, 1: fresh_cols[1], 2: fresh_cols[2], 4: fresh_row(9, 5)}
+    for r, col in cols.items():
+        pos, tok, draws, lo, hi, temp_bits, top_k, top_p_bits = col
+        seed = ((hi & 0xFFFFFFFF) << 32) | (lo & 0xFFFFFFFF)
+        assert out_i["tokens"][r].item() == tok and out_i["positions"][r].item() == pos and out_i["ctx_lens"][r].item() == pos + 1
+        assert out_i["tok_seq"][r].item() == r and out_i["top_k"][r].item() == top_k
+        assert out_f["temperature"][r].item() == np.array([temp_bits], dtype=np.int32).view(np.float32)[0]
+        assert out_f["top_p"][r].item() == np.array([top_p_bits], dtype=np.int32).view(np.float32)[0]
+        assert out_f["uniform"][r].item() == np.float32(uniform_for(seed, draws))
+        for grp in range(2):
+            page = int(tables[grp][r, pos // ps])
+            want = page * ps + pos % ps if page < pages else -1
+            assert kv[grp][r].item() == want
+    assert out_i["tok_seq"][3].item() == -1 and out_i["ctx_lens"][3].item() == 0 and kv[0][3].item() == -1
+    assert state_d[:, 5].tolist() == list(fresh_cols[1]) and state_d[:, 0].tolist() == list(fresh_cols[2])
+    # sampling writes back: the token becomes the column's last token, position and draws advance
+    logits = torch.randn(b, 50, generator=g).to(DEV)
+    before = state_d.clone()
+    picked = ops.argmax(logits, into_state=(dev(torch.tensor(rows, dtype=torch.int32)), state_d))
+    assert picked.tolist() == logits.argmax(dim=1).tolist()
+    for r, slot in enumerate(rows):
+        if slot < 0:
+            continue
+        assert state_d[1, slot].item() == picked[r].item()
+        assert state_d[0, slot].item() == before[0, slot].item() + 1 and state_d[2, slot].item() == before[2, slot].item() + 1
+        assert state_d[3:, slot].tolist() == before[3:, slot].tolist()
+    assert state_d[:, [1, 2, 4]].tolist() == before[:, [1, 2, 4]].tolist()  # slots of no row are untouched
+
+
 def test_sample_rows_carry_their_own_parameters(ops):
     r, v = 6, 320
     logits = rand(r, v, scale=3.0, seed=9)

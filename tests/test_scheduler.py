@@ -171,6 +171,33 @@ def test_abort_in_every_state():
     assert not sched.has_unfinished()
 
 
+def test_preempted_requests_wait_in_rank_order_before_the_arrivals_and_can_be_aborted():
+    """Two requests preempted in different steps come back in the order of their arrival, both ahead of a
+    request that has never run; aborting one of them while it waits leaves nothing behind."""
+    sched, cache, _ = make(num_pages=6, page_size=4, budget=64)
+    a, b, c = seq("a", 8, 0), seq("b", 7, 1), seq("c", 7, 2)
+    for s in (a, b, c):
+        sched.add_seq(s)
+    fake_step(sched, cache, None, sched.schedule())           # 2 + 2 + 2 pages: the pool is full
+    out = sched.schedule()                                     # a needs a third page: c goes
+    assert [s.seq_id for s in out.preempted] == ["c"]
+    fake_step(sched, cache, None, out)
+    for _ in range(3):
+        fake_step(sched, cache, None, sched.schedule())        # a and b fill the pages they have
+    out = sched.schedule()                                     # now a needs a fourth page: b goes
+    assert [s.seq_id for s in out.preempted] == ["b"] and [s.seq_id for s in sched.running] == ["a"]
+    sched.add_seq(seq("d", 3, 3))
+    assert [s.seq_id for s in sched.waiting] == ["b", "c", "d"]  # by arrival among the preempted, d behind them
+    assert sched.stats.num_waiting == 3 and sched.stats.num_running == 1 and sched.stats.num_preempted_total == 2
+    sched.abort("b")
+    assert b.status is SequenceStatus.FINISHED_ABORTED and [s.seq_id for s in sched.waiting] == ["c", "d"]
+    fake_step(sched, cache, None, out, finish={"a"})
+    out = sched.schedule()
+    assert [p.seq.seq_id for p in out.portions] == ["c", "d"] and c.num_computed_tokens == 0
+    fake_step(sched, cache, None, out, finish={"c", "d"})
+    assert not sched.has_unfinished() and cache.num_free_pages() == [6] and cache.state.num_free == cache.state.num_slots
+
+
 def test_a_scripted_session_is_deterministic():
     def run():
         sched, cache, pc = make(num_pages=12, page_size=4, budget=16, chunk=6, prefix=True, max_num_seqs=3)
