@@ -375,6 +375,8 @@ def main() -> int:
     ap.add_argument("--skip-points", action="store_true", help="leave out the points and the prefill (quick runs)")
     ap.add_argument("--only", choices=["decode", "prefill", "mixed", "shared-prefix"], default=None,
                     help="run one part only, once, and print its figures (for profiling runs under ncu)")
+    ap.add_argument("--prompt-len", type=int, default=None,
+                    help="with --only decode: prompts of this many tokens instead of 1,024 (decoding at other context lengths)")
     ap.add_argument("--timeline", action="store_true",
                     help="with --only decode: also print one step's kernel timeline (device-side records, ops/trace.py)")
     args = ap.parse_args()
@@ -408,16 +410,20 @@ def main() -> int:
     rng = random.Random(0)
     peak, peak_kind = peaks()
     once = args.only is not None
+    if args.prompt_len is not None and args.only != "decode":
+        print("bench.py: --prompt-len goes with --only decode")
+        return 2
+    prompt_len = args.prompt_len or PROMPT_LEN
 
     def make_engine(batch: int, steps: int, **overrides) -> LLMEngine:
-        tokens_per_seq = PROMPT_LEN + 2 * (steps + args.warmup) + 2 * PAGE
+        tokens_per_seq = prompt_len + 2 * (steps + args.warmup) + 2 * PAGE
         num_blocks = max(batch * ((tokens_per_seq + PAGE - 1) // PAGE) + 8, (PREFILL_LEN + PAGE) // PAGE + 8)
-        settings = dict(dtype="bfloat16", block_size=PAGE, num_blocks=num_blocks, max_model_len=MAX_MODEL_LEN,
+        settings = dict(dtype="bfloat16", block_size=PAGE, num_blocks=num_blocks, max_model_len=max(MAX_MODEL_LEN, tokens_per_seq),
                         max_num_seqs=max(batch, 1), max_num_batched_tokens=4096, enable_prefix_cache=False, watermark=0.0)
         settings.update(overrides)
         return LLMEngine(EngineConfig.defaults("random", **settings), model=model)
 
-    def fill(engine: LLMEngine, batch: int, steps: int, prompt_len: int = PROMPT_LEN) -> list[str]:
+    def fill(engine: LLMEngine, batch: int, steps: int, prompt_len: int = prompt_len) -> list[str]:
         """Admit ``batch`` requests with prompts of ``prompt_len`` tokens and run their prefill."""
         params = SamplingParams(max_tokens=4 * (steps + args.warmup) + GENERATED, ignore_eos=True)
         for i in range(batch):
@@ -659,8 +665,9 @@ def main() -> int:
         clocks.wait_for_first_line()
         main_run = time_decode(args.batch, args.steps, args.warmup, clocks)
     if args.only == "decode":
-        print(json.dumps({"impl": "ours", "batch": args.batch, "ms_per_step": main_run["ms_per_step"],
-                          "tok_s": main_run["tok_s"], "e2e_tok_s": main_run["e2e_tok_s"], "launches": main_run["launches"]}))
+        print(json.dumps({"impl": "ours", "batch": args.batch, "context": main_run["ctx_mid"], "ms_per_step": main_run["ms_per_step"],
+                          "tok_s": main_run["tok_s"], "e2e_tok_s": main_run["e2e_tok_s"], "launches": main_run["launches"],
+                          "hbm_frac": main_run["bytes"] / (main_run["ms_per_step"] / 1e3) / 1e9 / peak["hbm_gbs"]}))
         return 0
     hbm_frac = main_run["bytes"] / (main_run["ms_per_step"] / 1e3) / 1e9 / peak["hbm_gbs"]
     out = {

@@ -24,6 +24,7 @@
 // point with caller-given scratch): partials and log-sum-exps go to a float32 workspace and the CTA
 // that arrives last at the group's counter merges them, in split order too.
 #include "attention_mma.cuh"
+#include "tc_common.cuh"
 
 #define MAX_CLUSTER 16
 
@@ -57,6 +58,7 @@ struct DecodeParams {
     int max_split_pages;  // page ids a split may need (sizes the shared-memory page list)
     int stages;           // tiles in flight per CTA: 4 (default) or 2
     int swizzle;          // with 2 tiles in flight: the unpadded, swizzled K/V layout (three CTAs per SM)
+    int tma;              // K/V tiles arrive as one TMA copy per page and operand (head sizes of 64n, pages of 8..64 tokens)
     int cluster;          // > 1: the grid's z extent is one cluster of this many CTAs and the splits meet through it
     int max_ctx;          // the bound on every context that sized the grid
     int* counters;   // [S * nkv * qgroups]
@@ -90,22 +92,50 @@ __device__ __forceinline__ bool mine_newest(int newest, int t0, int t1, int kv_b
 // division's instruction sequence exists once in the kernel instead of at every use.
 __device__ __noinline__ int2 block_and_offset(int pos, int page_size) { return make_int2(pos / page_size, pos % page_size); }
 
-template <int HD, int ST, bool SWIZZLE, bool CL>
+__device__ __forceinline__ void tma_page_4d(uint32_t dst, const CUtensorMap* map, int x, int y, int z, int w, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y), "r"(z), "r"(w)
+        : "memory");
+}
+
+// LAYOUT: how a K/V tile lies in shared memory and how it gets there (see the kernel's first lines).
+#define KV_PADDED 0
+#define KV_SWIZZLED 1
+#define KV_TMA 2
+
+template <int HD, int ST, int LAYOUT, bool CL>
 __global__ void __launch_bounds__(NWARPS * 32)
-attn_decode_kernel(const DecodeParams p) {
+attn_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, const DecodeParams p) {
     constexpr int LD = HD + 8;  // padded q row (elements): consecutive rows fall into different banks
-    // K/V tiles, two layouts.  Padded rows (as for q): plain addressing, the smallest instruction count,
-    // for steps with few CTAs.  SWIZZLE (head sizes that are multiples of 64): unpadded rows with their
+    // K/V tiles, three layouts.  Padded rows (as for q): plain addressing, the smallest instruction count,
+    // for steps with few CTAs.  Swizzled (head sizes that are multiples of 64): unpadded rows with their
     // 16-byte chunks XOR-swizzled by the row (chunk c of row r lies at chunk c ^ (r & 7)), as free of
-    // bank conflicts and small enough for three CTAs per SM, for steps with many CTAs.
-    constexpr bool SWZ = SWIZZLE && HD % 64 == 0;
+    // bank conflicts and small enough for three CTAs per SM, for steps with many CTAs.  Both are filled
+    // by 16-byte cp.async, 2,048 of them per tile.  TMA (the same head sizes, pages of 8 to 64 tokens): a
+    // tile lies page by page, [page][64-column block][token][128 bytes] with the hardware's 128-byte
+    // swizzle (the same XOR, within a block), and one warp fetches it with one copy per page and
+    // operand, completion counted by an mbarrier per stage; rows that no visible key owns arrive with
+    // whatever the pages hold and are masked (scores) or cleared (values) in shared memory.
+    constexpr bool TMA = LAYOUT == KV_TMA;
+    constexpr bool SWZ = LAYOUT != KV_PADDED && HD % 64 == 0;
+    static_assert(!TMA || HD % 64 == 0, "TMA tiles are made of 64-column blocks");
     constexpr int LDK = SWZ ? HD : HD + 8;
-    auto kv_off = [](int r, int c) -> int { return r * LDK + (SWZ ? ((c ^ (r & 7)) << 3) : (c << 3)); };
-    extern __shared__ __align__(16) uint8_t smem_raw[];
-    bf16* Qs = (bf16*)smem_raw;                  // [16][LD]
-    bf16* Ks = Qs + 16 * LD;                     // [ST][TILE][LDK]
-    bf16* Vs = Ks + ST * TILE * LDK;             // [ST][TILE][LDK]
-    int* page_s = (int*)(Vs + ST * TILE * LDK);  // [max_split_pages] page of every block of this split
+    constexpr int CB = HD / 64;
+    const int ps_shift = p.page_shift;
+    auto kv_off = [&](int r, int c) -> int {
+        if (TMA)
+            return (((((r >> ps_shift) * CB + (c >> 3)) << ps_shift) + (r & (p.page_size - 1))) << 6) + (((c & 7) ^ (r & 7)) << 3);
+        return r * LDK + (SWZ ? ((c ^ (r & 7)) << 3) : (c << 3));
+    };
+    // (the swizzled TMA tiles need a 1024-byte aligned base: they come first, and the kernel checks)
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    bf16* Qs = TMA ? (bf16*)smem_raw + 2 * ST * TILE * LDK : (bf16*)smem_raw;   // [16][LD]
+    bf16* Ks = TMA ? (bf16*)smem_raw : Qs + 16 * LD;                            // [ST][TILE][LDK]
+    bf16* Vs = Ks + ST * TILE * LDK;                                            // [ST][TILE][LDK]
+    int* page_s = (int*)((TMA ? Qs : Vs + ST * TILE * LDK) + (TMA ? 16 * LD : 0));  // [max_split_pages] page of every block of this split
+    __shared__ __align__(8) unsigned long long full_bar[TMA ? ST : 1];  // TMA: the copies of a stage have landed
+    __shared__ int give_up;
     __shared__ float ml_s[NWARPS][16][2];
     __shared__ float w_s[16][16];               // final merge: weight of each split per query row
     __shared__ __align__(16) bf16 new_s[2 * HD]; // the newest token's k and v
@@ -168,9 +198,28 @@ attn_decode_kernel(const DecodeParams p) {
     const int* table = p.block_tables + (size_t)s * p.max_blocks;
     const float scale_log2 = p.scale * 1.4426950408889634f;  // softmax in base 2: exp(x) = 2^(x log2 e)
 
+    if (TMA) {
+        if (smem_addr(smem_raw) & 1023) {
+            if (tid == 0) cw_report(p.status, CW_ST_SMEM_ALIGN, blockIdx.x, (int)(smem_addr(smem_raw) & 1023));
+            return;
+        }
+        if (tid == 0) {
+            for (int i = 0; i < ST; ++i) mbar_init(smem_addr(&full_bar[i]), 1);
+            give_up = 0;
+            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        }
+        if (warp == 0 && lane < 2) asm volatile("prefetch.tensormap [%0];" ::"l"(lane == 0 ? &map_k : &map_v) : "memory");
+    }
     // page ids of the split's blocks, looked up once: tile loads then depend on shared memory only
     const int blk0 = p.page_shift >= 0 ? t0 >> p.page_shift : t0 / p.page_size;
     const int blk1 = p.page_shift >= 0 ? (t1 - 1) >> p.page_shift : (t1 - 1) / p.page_size;
+    if ((min(SPLIT, p.max_ctx) + p.page_size - 1) / p.page_size + 1 > p.max_split_pages) {
+        // The split read from the device is longer than the bound that sized the page list.  The test
+        // is the same in every CTA of the launch: all of them leave, and no group's counter is touched.
+        if (tid == 0) cw_report(p.status, CW_ST_SPLIT_BOUND, s, SPLIT);
+        return;
+    }
     for (int i = tid; i <= blk1 - blk0 && i < p.max_split_pages; i += blockDim.x) {
         const int blk = blk0 + i;
         int page = blk < p.max_blocks ? table[blk] : -1;
@@ -215,6 +264,29 @@ attn_decode_kernel(const DecodeParams p) {
         bf16* kd = Ks + (tile_idx % ST) * TILE * LDK;
         bf16* vd = Vs + (tile_idx % ST) * TILE * LDK;
         const int pos0 = t0 + tile_idx * TILE;
+        if (TMA) {
+            // lanes 0 .. pages-1 of warp 0 fetch the K pages of the tile, the next lanes its V pages; a
+            // page that the split does not own (past its end, or dropped behind the window) is read
+            // from page 0: nothing of it is used
+            if (warp == 0) {
+                const int pages = TILE >> ps_shift;
+                const uint32_t bar = smem_addr(&full_bar[tile_idx % ST]);
+                if (lane == 0) mbar_expect_tx(bar, 2 * TILE * HD * 2);
+                __syncwarp();
+                if (lane < 2 * pages) {
+                    const bool is_v = lane >= pages;
+                    const int j = is_v ? lane - pages : lane;
+                    const int i = (pos0 >> ps_shift) + j - blk0;
+                    int page = (i <= blk1 - blk0 && i < p.max_split_pages) ? page_s[i] : 0;
+                    if (page < 0) page = 0;
+                    // what this stage held was read, and in places written, by ordinary loads and stores
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    tma_page_4d(smem_addr((is_v ? vd : kd) + ((j * CB) << (ps_shift + 6))), is_v ? &map_v : &map_k, 0,
+                                page << ps_shift, 0, kvh, bar);
+                }
+            }
+            return;
+        }
         if (EVEN) {
             const int c = tid % CH, r0 = tid / CH;
 #pragma unroll 2
@@ -351,7 +423,22 @@ attn_decode_kernel(const DecodeParams p) {
 
     for (int it = 0; it < ntiles; ++it) {
         const int buf = it % ST;
-        cp_async_wait_upto(min(ntiles - it - 1, ST - 1));  // tile `it` has landed; later ones may fly
+        if (TMA) {
+            // (a wait that runs out is recorded and the kernel goes on: every thread keeps meeting the barriers below)
+            mbar_wait(smem_addr(&full_bar[buf]), (it / ST) & 1, &give_up);
+            const int pos0 = t0 + it * TILE;
+            if (pos0 + TILE > t1 || pos0 < kv_begin) {
+                // values of rows that are no visible key: their probabilities are zero, and zero times
+                // whatever the page held there must be zero
+                for (int i = tid; i < TILE * CH; i += blockDim.x) {
+                    const int r = i / CH, pos = pos0 + r;
+                    if (pos >= t1 || pos < kv_begin)
+                        *reinterpret_cast<uint4*>(Vs + buf * TILE * LDK + kv_off(r, i % CH)) = make_uint4(0, 0, 0, 0);
+                }
+            }
+        } else {
+            cp_async_wait_upto(min(ntiles - it - 1, ST - 1));  // tile `it` has landed; later ones may fly
+        }
         if (it == newest_tile) {
             const int r = newest - t0 - it * TILE;
             for (int i = tid; i < 2 * CH; i += blockDim.x)
@@ -359,15 +446,16 @@ attn_decode_kernel(const DecodeParams p) {
                     *reinterpret_cast<const uint4*>(new_s + (i < CH ? 0 : HD) + (i % CH) * 8);
         }
         __syncthreads();
-        const bf16* kt = Ks + buf * TILE * LDK + warp * 16 * LDK;  // (16 rows: a row's swizzle is the same from here)
-        const bf16* vt = Vs + buf * TILE * LDK + warp * 16 * LDK;
+        const bf16* kt = Ks + buf * TILE * LDK;
+        const bf16* vt = Vs + buf * TILE * LDK;
+        const int wr = warp * 16;  // this warp's 16 rows of the tile
         const int tok0 = t0 + it * TILE + warp * 16;  // first token of this warp's 16
         if (tok0 < t1) {
             float sc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
 #pragma unroll
             for (int ks = 0; ks < HD / 16; ++ks) {
                 uint32_t b0, b1, b2, b3;
-                ldmatrix_x4(smem_addr(kt + kv_off((lane & 7) + 8 * (lane >> 4), 2 * ks + ((lane >> 3) & 1))),
+                ldmatrix_x4(smem_addr(kt + kv_off(wr + (lane & 7) + 8 * (lane >> 4), 2 * ks + ((lane >> 3) & 1))),
                             b0, b1, b2, b3);
                 mma_bf16(sc[0], qa[ks], b0, b1);
                 mma_bf16(sc[1], qa[ks], b2, b3);
@@ -410,7 +498,7 @@ attn_decode_kernel(const DecodeParams p) {
 #pragma unroll
             for (int n2 = 0; n2 < HD / 16; ++n2) {
                 uint32_t v0, v1, v2, v3;
-                ldmatrix_x4_trans(smem_addr(vt + kv_off((lane & 7) + 8 * ((lane >> 3) & 1), 2 * n2 + (lane >> 4))),
+                ldmatrix_x4_trans(smem_addr(vt + kv_off(wr + (lane & 7) + 8 * ((lane >> 3) & 1), 2 * n2 + (lane >> 4))),
                                   v0, v1, v2, v3);
                 float* oa = o_acc[2 * n2];
                 float* ob = o_acc[2 * n2 + 1];
@@ -422,6 +510,19 @@ attn_decode_kernel(const DecodeParams p) {
         }
         __syncthreads();  // everyone is done with this buffer before it is refilled
         if (it + ST < ntiles) load_tile(it + ST);
+    }
+    if (TMA && give_up) {
+        // a wait ran out: say so, and give the copies still in flight a bounded time to land before
+        // the merge below writes over the tiles
+        if (tid == 0) {
+            cw_report(p.status, CW_ST_WAIT_TIMEOUT, blockIdx.x, -3);
+            for (int k = max(0, ntiles - ST); k < ntiles; ++k) {
+                const long long t_begin = clock64();
+                while (!mbar_try_wait(smem_addr(&full_bar[k % ST]), (k / ST) & 1) && clock64() - t_begin < WAIT_CYCLES) {
+                }
+            }
+        }
+        __syncthreads();
     }
     // ---- merge the four warps (each saw a quarter of every tile) -----------------------------------
 #pragma unroll
@@ -577,9 +678,10 @@ attn_decode_kernel(const DecodeParams p) {
         return;
     }
     // Every thread merges groups of four outputs: weights w_k = 2^(lse_k - max) and the weighted sum of
-    // the splits' partials, divided by the sum of the weights at the end, splits in order.  Up to 12
-    // splits, all loads (the row's log-sum-exps and the partials) are issued before any is used: one
-    // trip to the L2.  More splits take the loop form below (small code: it runs once per group).
+    // the splits' partials, divided by the sum of the weights at the end, splits in order.  The splits
+    // are taken twelve at a time, and all loads of a round (the row's log-sum-exps and the partials) are
+    // issued before any is used: one trip to the L2 per round.  Between rounds the sum so far is
+    // rescaled to the new maximum, as in the online softmax.
     constexpr int Q4 = HD / 4;
     constexpr int KC = 12;
     for (int item = tid; item < rows * Q4; item += blockDim.x) {
@@ -589,34 +691,30 @@ attn_decode_kernel(const DecodeParams p) {
             p.part_o + (((size_t)s * p.nh + h0 + r) * p.max_splits + first_split) * HD + d);
         float m = -INFINITY, W = 0.f;
         float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (active <= KC) {
+#pragma unroll 1
+        for (int k0 = 0; k0 < active; k0 += KC) {
             float l[KC];
             float4 v[KC];
 #pragma unroll
             for (int k = 0; k < KC; ++k) {
-                l[k] = k < active ? __ldcg(lp + k) : -INFINITY;
-                v[k] = k < active ? __ldcg(po + (size_t)k * Q4) : make_float4(0.f, 0.f, 0.f, 0.f);
+                l[k] = k0 + k < active ? __ldcg(lp + k0 + k) : -INFINITY;
+                v[k] = k0 + k < active ? __ldcg(po + (size_t)(k0 + k) * Q4) : make_float4(0.f, 0.f, 0.f, 0.f);
             }
+            float m_new = m;
 #pragma unroll
-            for (int k = 0; k < KC; ++k) m = fmaxf(m, l[k]);
+            for (int k = 0; k < KC; ++k) m_new = fmaxf(m_new, l[k]);
+            if (k0 > 0) {
+                const float keep = (m == -INFINITY) ? 0.f : fast_exp2(m - m_new);
+                W *= keep;
+                acc.x *= keep; acc.y *= keep; acc.z *= keep; acc.w *= keep;
+            }
+            m = m_new;
 #pragma unroll
             for (int k = 0; k < KC; ++k) {
                 const float w = (l[k] == -INFINITY) ? 0.f : fast_exp2(l[k] - m);
                 W += w;
                 acc.x = fmaf(w, v[k].x, acc.x); acc.y = fmaf(w, v[k].y, acc.y);
                 acc.z = fmaf(w, v[k].z, acc.z); acc.w = fmaf(w, v[k].w, acc.w);
-            }
-        } else {
-#pragma unroll 1
-            for (int k = 0; k < active; ++k) m = fmaxf(m, __ldcg(lp + k));
-#pragma unroll 4
-            for (int k = 0; k < active; ++k) {
-                const float lk = __ldcg(lp + k);
-                const float4 x = __ldcg(po + (size_t)k * Q4);
-                const float w = (lk == -INFINITY) ? 0.f : fast_exp2(lk - m);
-                W += w;
-                acc.x = fmaf(w, x.x, acc.x); acc.y = fmaf(w, x.y, acc.y);
-                acc.z = fmaf(w, x.z, acc.z); acc.w = fmaf(w, x.w, acc.w);
             }
         }
         const float inv = W > 0.f ? 1.f / W : 0.f;
@@ -628,31 +726,54 @@ attn_decode_kernel(const DecodeParams p) {
     cw_trace_end();
 }
 
-template <int HD, int ST, bool SWIZZLE, bool CL>
-static int launch_decode_cl(const DecodeParams& p, int S, int splits, cudaStream_t stream) {
+static CUtensorMap g_no_map;  // what the variants without TMA are given
+
+template <int HD, int ST, int LAYOUT, bool CL>
+static int launch_decode_cl(const DecodeParams& p, int S, int splits, cudaStream_t stream, const CUtensorMap& mk = g_no_map,
+                            const CUtensorMap& mv = g_no_map) {
     constexpr int LD = HD + 8;
-    constexpr int LDK = (SWIZZLE && HD % 64 == 0) ? HD : HD + 8;
+    constexpr int LDK = (LAYOUT != KV_PADDED && HD % 64 == 0) ? HD : HD + 8;
     const int SMEM = (16 * LD + 2 * ST * TILE * LDK) * 2 + p.max_split_pages * 4;
     constexpr int MERGE = NWARPS * 16 * HD * 4;
     static_assert(MERGE <= 2 * ST * TILE * LDK * 2, "the merge buffer must fit over the K and V buffers");
     static int configured = 0;
     if (SMEM > configured) {
         if (SMEM > 48 * 1024 &&
-            cudaFuncSetAttribute(attn_decode_kernel<HD, ST, SWIZZLE, CL>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess)
+            cudaFuncSetAttribute(attn_decode_kernel<HD, ST, LAYOUT, CL>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess)
             return (int)cudaGetLastError();
-        if (CL && cudaFuncSetAttribute(attn_decode_kernel<HD, ST, SWIZZLE, CL>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) != cudaSuccess)
+        if (CL && cudaFuncSetAttribute(attn_decode_kernel<HD, ST, LAYOUT, CL>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) != cudaSuccess)
             return (int)cudaGetLastError();
         configured = SMEM;
     }
     dim3 grid(p.nkv * p.qgroups, S, splits);
-    return cw_launch(attn_decode_kernel<HD, ST, SWIZZLE, CL>, grid, dim3(NWARPS * 32), SMEM, stream, CL ? (unsigned)splits : 1u, p);
+    return cw_launch(attn_decode_kernel<HD, ST, LAYOUT, CL>, grid, dim3(NWARPS * 32), SMEM, stream, CL ? (unsigned)splits : 1u, mk, mv, p);
 }
 
-template <int HD, int ST, bool SWIZZLE>
+template <int HD, int ST, int LAYOUT>
 static int launch_decode_st(const DecodeParams& p, int S, int splits, cudaStream_t stream) {
     // (the cluster form for head sizes up to 128: the larger ones have no room for its inbox beside their tiles)
-    if (HD <= 128 && p.cluster > 1) return launch_decode_cl<HD, ST, SWIZZLE, (HD <= 128)>(p, S, splits, stream);
-    return launch_decode_cl<HD, ST, SWIZZLE, false>(p, S, splits, stream);
+    if (HD <= 128 && p.cluster > 1) return launch_decode_cl<HD, ST, LAYOUT, (HD <= 128)>(p, S, splits, stream);
+    return launch_decode_cl<HD, ST, LAYOUT, false>(p, S, splits, stream);
+}
+
+// The cache as [64 elements][slot][64-element block][kv head]: a box is one page of one head with all its
+// blocks, which land one after the other ([block][token][128 bytes], 128-byte swizzle).
+static int page_map(CUtensorMap* map, const void* cache, int num_pages, int page_size, int nkv, int hd) {
+    const cuuint64_t dims[4] = {64, (cuuint64_t)num_pages * page_size, (cuuint64_t)(hd / 64), (cuuint64_t)nkv};
+    const cuuint64_t strides[3] = {(cuuint64_t)nkv * hd * 2, 128, (cuuint64_t)hd * 2};
+    const cuuint32_t box[4] = {64, (cuuint32_t)page_size, (cuuint32_t)(hd / 64), 1};
+    const cuuint32_t elem[4] = {1, 1, 1, 1};
+    return g_encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(cache), dims, strides, box, elem,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS ? 0 : -1;
+}
+
+template <int HD, int ST>
+static int launch_decode_tma(const DecodeParams& p, int S, int splits, cudaStream_t stream) {
+    CUtensorMap mk, mv;
+    if (page_map(&mk, p.k_cache, p.num_pages, p.page_size, p.nkv, HD) != 0 || page_map(&mv, p.v_cache, p.num_pages, p.page_size, p.nkv, HD) != 0)
+        return CW_ERR_UNSUPPORTED;
+    return launch_decode_cl<HD, ST, KV_TMA, false>(p, S, splits, stream, mk, mv);
 }
 
 template <int HD>
@@ -660,9 +781,13 @@ static int launch_decode(const DecodeParams& p, int S, int splits, cudaStream_t 
     // Four tiles in flight per CTA (one CTA per SM) suit steps with few CTAs, where latency is
     // everything; with many CTAs two tiles in flight leave room for two or three CTAs per SM, and
     // the warps of the others cover each CTA's stalls.
-    if (HD <= 128 && p.stages != 2) return launch_decode_st<HD, (HD <= 128 ? 4 : 2), false>(p, S, splits, stream);
-    if (HD % 64 == 0 && p.swizzle) return launch_decode_st<HD, 2, (HD % 64 == 0)>(p, S, splits, stream);
-    return launch_decode_st<HD, 2, false>(p, S, splits, stream);
+    if (HD % 64 == 0 && p.tma) {
+        if (HD <= 128 && p.stages != 2) return launch_decode_tma<(HD % 64 == 0 ? HD : 64), (HD <= 128 ? 4 : 2)>(p, S, splits, stream);
+        return launch_decode_tma<(HD % 64 == 0 ? HD : 64), 2>(p, S, splits, stream);
+    }
+    if (HD <= 128 && p.stages != 2) return launch_decode_st<HD, (HD <= 128 ? 4 : 2), KV_PADDED>(p, S, splits, stream);
+    if (HD % 64 == 0 && p.swizzle) return launch_decode_st<HD, 2, (HD % 64 == 0 ? KV_SWIZZLED : KV_PADDED)>(p, S, splits, stream);
+    return launch_decode_st<HD, 2, KV_PADDED>(p, S, splits, stream);
 }
 
 // Workspace a call needs: part_o floats, part_lse floats, counters.
@@ -678,7 +803,8 @@ extern "C" int cw_attention_decode_workspace(int S, int nh, int nkv, int hd, int
 
 // q: [S, >= nh*hd] rows (row stride q_stride), one query token per request; out: [S, nh*hd].
 // max_ctx bounds every ctx_lens[s]; it fixes the grid, not the result.  split (or *split_ptr): tokens
-// per CTA, a multiple of 64 and at least 128.
+// per CTA, a multiple of 64 and at least 128; with split_ptr, split is 0 or an upper bound on *split_ptr
+// (a smaller page list in shared memory: more CTAs per SM at long contexts).
 extern "C" int cw_attention_decode_rows(const void* q, int q_stride, void* out, void* k_cache, void* v_cache,
                                         const int* block_tables, const int* ctx_lens, const int* q_start, int S, int nh,
                                         int nkv, int hd, int page_size, int max_blocks, int num_pages, float scale,
@@ -745,8 +871,10 @@ extern "C" int cw_attention_decode_rows(const void* q, int q_stride, void* out, 
     p.cluster = (stages >> 16) & 0x1F;
     p.max_ctx = max_ctx;
     if (p.cluster > MAX_CLUSTER || hd > 128) p.cluster = 0;
+    // bit 9: tiles by TMA, where the sizes allow it (else the variants above, with the same result)
+    p.tma = ((stages >> 9) & 1) && hd % 64 == 0 && p.page_shift >= 3 && page_size <= TILE && !p.cluster && load_encode() == 0;
     // the grid is sized for the smallest split; a larger run-time split leaves the later CTAs idle
-    if (split_ptr == nullptr && (split < MIN_SPLIT || split % TILE != 0)) return CW_ERR_BAD_SIZE;
+    if ((split_ptr == nullptr || split != 0) && (split < MIN_SPLIT || split % TILE != 0)) return CW_ERR_BAD_SIZE;
     int splits = (max_ctx + MIN_SPLIT - 1) / MIN_SPLIT;
     if (p.cluster > 1)
         splits = p.cluster;
@@ -755,11 +883,12 @@ extern "C" int cw_attention_decode_rows(const void* q, int q_stride, void* out, 
     if (!p.cluster && splits > 1 && (part_o == nullptr || part_lse == nullptr || counters == nullptr)) return CW_ERR_BAD_SIZE;
     p.max_splits = splits;
     p.split = split; p.split_ptr = split_ptr;
-    // a split may span the whole context when split_ptr decides at run time
-    // (a cluster makes the kernel cut no finer than the context bound divided by its size)
+    // when split_ptr decides at run time, `split` (if not 0) bounds what it may say, else a split may
+    // span the whole context (a cluster makes the kernel cut no finer than the context bound divided
+    // by its size); the bound sizes the page list in shared memory, and the kernel checks it
     const int least = p.cluster ? ((max_ctx + p.cluster - 1) / p.cluster + TILE - 1) / TILE * TILE : 0;
     const int host_split = split > least ? split : least;
-    const int span = split_ptr != nullptr ? max_ctx : (host_split < max_ctx ? host_split : max_ctx);
+    const int span = split_ptr != nullptr && split == 0 ? max_ctx : (host_split < max_ctx ? host_split : max_ctx);
     p.max_split_pages = (span + page_size - 1) / page_size + 1;
     if (splits > 65535) return CW_ERR_BAD_SIZE;
     switch (hd) {

@@ -28,6 +28,7 @@
 #define CW_ST_ROW_RANGE 5
 #define CW_ST_SMEM_ALIGN 6
 #define CW_ST_SPLIT_RANGE 7
+#define CW_ST_SPLIT_BOUND 8
 
 typedef __nv_bfloat16 bf16;
 

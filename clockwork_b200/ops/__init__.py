@@ -23,6 +23,7 @@ STATUS_MESSAGES = {
     5: "row index outside the batch (row {a}, index {b})",
     6: "shared memory of block {a} is not 1024-byte aligned (offset {b})",
     7: "work item {a} names a cut of its keys that the kernel does not take (word {b})",
+    8: "the context split of a decode step is longer than the bound its page list was sized for (request {a}, split {b})",
 }
 
 

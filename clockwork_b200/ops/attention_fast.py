@@ -83,6 +83,7 @@ def reserve_decode_scratch(device, max_seqs: int, num_heads: int, num_kv_heads: 
 
 MIN_SPLIT = 128
 SWIZZLED = 0x100  # flag in the `stages` argument of the decode kernel
+TMA_TILES = 0x200  # flag in the same argument: K/V tiles by TMA, one copy per page and operand
 _SMS: dict[int, int] = {}
 
 
@@ -108,11 +109,17 @@ def _resident_ctas(head_dim: int, stages: int = 2, swizzled: bool = True) -> int
     return max(1, min(3, (227 * 1024) // smem))
 
 
+def _unpadded(head_dim: int, pairs: int) -> bool:
+    """Whether a step that cuts contexts into more than two tiles per CTA runs on unpadded K/V tiles
+    (swizzled or by TMA: head sizes of 64n), which lets a third CTA share the SM."""
+    return head_dim % 64 == 0 and (pairs > 16 or _tma_tiles)
+
+
 def _splits_wanted(num_seqs: int, num_heads: int, num_kv_heads: int, device=None, head_dim: int = 128) -> int:
     """Context splits per request that fill the SMs once with resident CTAs of the two-tile variant:
     a CTA that has to wait for a slot starts a whole CTA-time late."""
     pairs = _pairs(num_seqs, num_heads, num_kv_heads)
-    return max(1, _resident_ctas(head_dim, swizzled=pairs > 16) * _sm_count(device) // pairs)
+    return max(1, _resident_ctas(head_dim, swizzled=_unpadded(head_dim, pairs)) * _sm_count(device) // pairs)
 
 
 def decode_split(num_seqs: int, num_heads: int, num_kv_heads: int, max_live_ctx: int, device=None,
@@ -124,18 +131,43 @@ def decode_split(num_seqs: int, num_heads: int, num_kv_heads: int, max_live_ctx:
     return max(MIN_SPLIT, -(-split // 64) * 64)
 
 
+def decode_split_bound(max_seqs: int, num_heads: int, num_kv_heads: int, max_ctx: int, device=None, head_dim: int = 128) -> int:
+    """The largest ``decode_split`` of any step of up to ``max_seqs`` requests with contexts up to ``max_ctx``."""
+    return max(decode_split(n, num_heads, num_kv_heads, max_ctx, device, head_dim) for n in range(1, max_seqs + 1))
+
+
 def decode_stages(num_seqs: int, num_heads: int, num_kv_heads: int, max_ctx: int | None = None, device=None,
                   head_dim: int = 128) -> int:
-    """Tiles of 64 tokens in flight per CTA.  Two when the step has many CTAs (from 16 requests of two
-    KV heads on: room for several CTAs per SM), and when no context up to ``max_ctx`` makes a split
-    longer than two tiles (then two hold a whole split, and the CTA is small enough to start beside
-    a CTA of the preceding product); else four."""
-    if _pairs(num_seqs, num_heads, num_kv_heads) > 16:
-        # many CTAs: the unpadded, swizzled K/V tiles (flag 0x100) make room for a third CTA per SM
-        return 2 | SWIZZLED if head_dim % 64 == 0 else 2
-    if max_ctx is not None and decode_split(num_seqs, num_heads, num_kv_heads, max_ctx, device, head_dim) <= 2 * 64:
+    """The decode kernel's variant for a step: tiles of 64 tokens in flight per CTA, with flags for the
+    layout of the tiles and the way they are fetched.  Whatever is chosen leaves as many CTAs resident
+    per SM as ``decode_split`` counts on, so that all CTAs of a step run at once.
+
+    * Many CTAs (from 16 requests of two KV heads on): two tiles in flight, unpadded tiles (swizzled,
+      and fetched by TMA where the sizes allow it), three CTAs per SM at head size 128.
+    * Few CTAs and contexts up to ``max_ctx`` that fit as CTAs of 128 tokens: two padded tiles filled by
+      ``cp.async`` hold a whole split, with the shortest way from the CTA's start to its first product.
+    * Few CTAs and longer contexts: a CTA walks several tiles; by TMA with two in flight and three CTAs
+      per SM, or, for head sizes without that variant, four padded tiles in flight where they leave as
+      many CTAs per SM as two would."""
+    pairs = _pairs(num_seqs, num_heads, num_kv_heads)
+    unpadded = 2 | SWIZZLED | (TMA_TILES if _tma_tiles else 0)
+    if pairs > 16:
+        return unpadded if head_dim % 64 == 0 else 2
+    if max_ctx is not None and -(-max_ctx // MIN_SPLIT) * pairs <= _resident_ctas(head_dim, swizzled=False) * _sm_count(device):
         return 2
-    return 4
+    if _unpadded(head_dim, pairs):
+        return unpadded
+    return 4 if _resident_ctas(head_dim, 4, False) >= _resident_ctas(head_dim, 2, False) else 2
+
+
+_tma_tiles = True
+
+
+def set_tma_tiles(on: bool) -> None:
+    """Whether the decode kernel fetches K/V tiles by TMA (one copy per page and operand, counted by an
+    mbarrier) where head and page sizes allow it, or by 16-byte ``cp.async`` as everywhere else."""
+    global _tma_tiles
+    _tma_tiles = bool(on)
 
 
 _cluster_merge = False
@@ -178,7 +210,9 @@ class _Decode:
             fused_position=None) -> torch.Tensor:
         # a device scalar that a captured step refreshes before every replay, when there is one
         split_dev = ctx.extras.get(dispatch.decode_split_name(num_heads, num_kv_heads, head_dim))
-        split = None if split_dev is not None else decode_split(ctx.num_seqs, num_heads, num_kv_heads, ctx.max_ctx_len, qkv.device, head_dim)
+        # (with the device scalar: the largest value it can take for up to this many requests and this context bound)
+        split = (decode_split_bound if split_dev is not None else decode_split)(
+            ctx.num_seqs, num_heads, num_kv_heads, max_ctx or ctx.max_ctx_len, qkv.device, head_dim)
         return attention_decode(qkv, view.k_cache, view.v_cache, view.block_tables, ctx.ctx_lens, num_heads,
                                 num_kv_heads, head_dim, scale, window, max_ctx or ctx.max_ctx_len, ctx.status,
                                 split=split, split_dev=split_dev,
@@ -194,7 +228,7 @@ def attention_decode(q, k_cache, v_cache, block_tables, ctx_lens, num_heads, num
     """One query token per request: ``q`` [S, >= nh*hd] (row s belongs to request s), ``ctx_lens`` [S]
     the tokens of each request in the cache (its own included).  ``split``: tokens per CTA (a multiple
     of 64, at least 128; default: chosen by ``decode_split``), or ``split_dev``, the same as an int32
-    device scalar.  ``fused``: (inv_freq or None, rotary_dim, slots): ``q`` is then the raw [q | k | v]
+    device scalar (``split`` is then an upper bound on it, or None: the whole context).  ``fused``: (inv_freq or None, rotary_dim, slots): ``q`` is then the raw [q | k | v]
     rows; q and the new k are rotated inside the kernel and the new token's k and v stored at ``slots``
     (so no separate position-encoding / cache-write kernel is needed).  Returns [S, nh*hd].
 

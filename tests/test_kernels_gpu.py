@@ -170,15 +170,15 @@ def test_rope_store(ops, status, dtype, nh, nkv, hd, rot):
         ops.raise_on_status(status)
 
 
-def paged_setup(seq_lens, nkv, hd, ps, dtype, seed=0, extra_pages=3):
+def paged_setup(seq_lens, nkv, hd, ps, dtype, seed=0, extra_pages=3, fill=100.0):
     """Random K/V for several requests scattered over shuffled pages; padding filled with 100.0
-    (the reference's poison trick, tests/test_triton_kernel.py:33-34)."""
+    (the reference's poison trick, tests/test_triton_kernel.py:33-34) or with ``fill``."""
     g = torch.Generator().manual_seed(seed)
     blocks = [(n + ps - 1) // ps for n in seq_lens]
     total = sum(blocks) + extra_pages
     order = torch.randperm(total, generator=g).tolist()
-    k_cache = torch.full((total, ps, nkv, hd), 100.0)
-    v_cache = torch.full((total, ps, nkv, hd), 100.0)
+    k_cache = torch.full((total, ps, nkv, hd), fill)
+    v_cache = torch.full((total, ps, nkv, hd), fill)
     tables = torch.full((len(seq_lens), max(blocks) + 1), -1, dtype=torch.int32)
     ks, vs = [], []
     for s, n in enumerate(seq_lens):
@@ -585,6 +585,50 @@ def test_attention_decode_kernel(ops, status, fast, nh, nkv, hd, ps, window):
                                 6000, status, split=256).float().cpu().view(len(ctx_lens), nh, hd)
     assert torch.equal(far, out)
     ops.raise_on_status(status)
+
+
+@pytest.mark.parametrize("nh,nkv,hd,ps,window", [(12, 2, 128, 16, None), (32, 1, 64, 8, None), (4, 2, 128, 32, 300),
+                                                (3, 1, 256, 64, None), (6, 3, 192, 16, 500), (8, 2, 64, 64, 70)])
+def test_attention_decode_tiles_by_tma(ops, status, fast, nh, nkv, hd, ps, window):
+    """K/V tiles fetched by TMA (a copy per page and operand, the hardware's swizzle) against the plain
+    formula, and bit for bit against the same variant fed by cp.async: only the way into shared memory
+    differs.  What the pages hold beyond a context is NaN here: a whole page arrives, and nothing of
+    its unused rows may reach a result."""
+    ctx_lens = [1, 17, 64, 65, 256, 257, 700, 1300, 0]
+    dtype = torch.bfloat16
+    real = [c for c in ctx_lens if c > 0]
+    k_cache, v_cache, tables, ks, vs = paged_setup(real, nkv, hd, ps, dtype, seed=13, fill=float("nan"))
+    tables = torch.cat([tables, torch.full((1, tables.shape[1]), -1, dtype=torch.int32)])
+    g = torch.Generator().manual_seed(4)
+    scale = hd**-0.5
+    qs = [(torch.randn(1, nh, hd, generator=g) * 2).to(dtype).float() for _ in ctx_lens]
+    wide = torch.zeros(len(ctx_lens), (nh + 2 * nkv) * hd)
+    wide[:, : nh * hd] = torch.cat(qs).view(len(ctx_lens), -1)
+    args = (wide.to(dtype).to(DEV), k_cache.to(DEV), v_cache.to(DEV), tables.to(DEV),
+            torch.tensor(ctx_lens, dtype=torch.int32, device=DEV), nh, nkv, hd, scale, window, 2048, status)
+    deep = 4 if hd <= 128 else 2  # (the larger heads have two tiles in flight whatever is asked for)
+    for kw in (dict(split=128, stages=2), dict(split=384, stages=2 | fast.SWIZZLED), dict(stages=2 | fast.SWIZZLED),
+               dict(split=256, stages=deep), dict(split=1344, stages=deep), dict(stages=deep),
+               dict(split_dev=torch.tensor([192], dtype=torch.int32, device=DEV), stages=2)):
+        by_tma = fast.attention_decode(*args, **{**kw, "stages": kw["stages"] | fast.TMA_TILES}).float().cpu().view(len(ctx_lens), nh, hd)
+        by_cp_async = fast.attention_decode(*args, **kw).float().cpu().view(len(ctx_lens), nh, hd)
+        ops.raise_on_status(status)
+        assert torch.isfinite(by_tma).all(), kw
+        for i, n in enumerate(real):
+            want = plain.causal_attention(qs[i], ks[i], vs[i], scale, window=window)[0]
+            torch.testing.assert_close(by_tma[i], want, rtol=2e-2, atol=2e-2, msg=lambda m: f"{kw}, context {n}: {m}")
+        assert torch.equal(by_tma, by_cp_async), kw
+        assert float(by_tma[-1].abs().max()) == 0.0
+    # a split read from the device may come with a bound that sizes the page list in shared memory ...
+    on_device = torch.tensor([192], dtype=torch.int32, device=DEV)
+    bounded = fast.attention_decode(*args, split=256, split_dev=on_device, stages=2 | fast.TMA_TILES).float().cpu().view(len(ctx_lens), nh, hd)
+    free = fast.attention_decode(*args, split_dev=on_device, stages=2 | fast.TMA_TILES).float().cpu().view(len(ctx_lens), nh, hd)
+    ops.raise_on_status(status)
+    assert torch.equal(bounded, free)
+    # ... and a split beyond the bound is refused by the kernel, loudly
+    fast.attention_decode(*args, split=128, split_dev=on_device, stages=2 | fast.TMA_TILES)
+    with pytest.raises(RuntimeError, match="longer than the bound"):
+        ops.raise_on_status(status)
 
 
 def test_attention_decode_scratch_outlives_captured_graphs(ops, status, fast):

@@ -92,3 +92,22 @@ def test_long_contexts_at_head_size_128(dtype, model_dir, references, tmp_path):
                     CONFIG["vocab_size"], PAGE)
     check(tb.gather(out, "a", len(a)), references(a), dtype, f"head size 128, {dtype}, the long request")
     check(tb.gather(out, "b", len(b)), references(b), dtype, f"head size 128, {dtype}, the request beside it")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_decoding_at_4400_tokens_beside_a_short_request(dtype, model_dir, references, tmp_path):
+    """A context long enough that the captured decode step of the 8,192-token tier cuts it into many
+    splits (merged in rounds), fetches its tiles by TMA and sizes its page list by the bound on the
+    split, decoded beside a request of a few hundred tokens whose rows ride in the same graph."""
+    a, b = tokens(4440, 3), tokens(260, 4)
+    tb = TraceBuilder()
+    tb.step([("a", a[:2048], False)])
+    tb.step([("a", a[2048:4096], False)])
+    tb.step([("a", a[4096:4400], True), ("b", b[:220], True)])
+    for i in range(40):
+        tb.step([("a", [a[4400 + i]], True), ("b", [b[220 + i]], True)], end=["a", "b"] if i == 39 else [])
+    out = run_trace(model_dir, dtype, round_up(4440, 64) + round_up(260, 64), tb.steps, tmp_path / "out",
+                    CONFIG["vocab_size"], PAGE)
+    exact, rounded = references(a)
+    check(tb.gather(out, "a", len(a), first=4096), (exact[4096:], rounded[4096:]), dtype, f"head size 128, {dtype}, 4,400 tokens")
+    check(tb.gather(out, "b", len(b)), references(b), dtype, f"head size 128, {dtype}, the short request beside them")
