@@ -15,14 +15,16 @@
 //
 // Scores, softmax and accumulation are float32; probabilities are rounded to bfloat16 for P.V.
 //
-// How the splits of a (request, KV head) group meet, two forms.  Through a thread-block cluster (the
-// usual one, up to 16 splits): the splits of a group are the CTAs of one cluster; each pushes its
-// normalised partial output, cut into as many slices as there are splits, into the others' shared
-// memory (slice j to CTA j) with its log-sum-exps, arrives on their barriers, waits for theirs, and
-// merges and stores its own slice, sources in split order: no global scratch, no counter, no second
-// pass by one CTA.  Through global memory (grids of more splits than a cluster holds, and the entry
-// point with caller-given scratch): partials and log-sum-exps go to a float32 workspace and the CTA
-// that arrives last at the group's counter merges them, in split order too.
+// How the splits of a (request, KV head) group meet, two forms.  Through global memory (the usual one):
+// partials and log-sum-exps go to a float32 workspace and the CTA that arrives last at the group's
+// counter merges them, in split order; more than 36 splits meet in two levels (twelve splits share a
+// counter, the last of them merges the twelve, the last of these mergers merges their results).
+// Through a thread-block cluster (on request, up to 16 splits): the splits of a group are the CTAs of
+// one cluster; each pushes its normalised partial output, cut into as many slices as there are
+// splits, into the others' shared memory (slice j to CTA j) with its log-sum-exps, arrives on their
+// barriers, waits for theirs, and merges and stores its own slice, sources in split order: no global
+// scratch, no counter, no second pass by one CTA; measured slower inside a step, because a cluster
+// starts only when all of its CTAs find room at once.
 #include "attention_mma.cuh"
 #include "tc_common.cuh"
 
@@ -59,6 +61,7 @@ struct DecodeParams {
     int stages;           // tiles in flight per CTA: 4 (default) or 2
     int swizzle;          // with 2 tiles in flight: the unpadded, swizzled K/V layout (three CTAs per SM)
     int tma;              // K/V tiles arrive as one TMA copy per page and operand (head sizes of 64n, pages of 8..64 tokens)
+    int tree;             // the variant that merges more than 36 splits in two levels (two tiles in flight, no cluster)
     int cluster;          // > 1: the grid's z extent is one cluster of this many CTAs and the splits meet through it
     int max_ctx;          // the bound on every context that sized the grid
     int* counters;   // [S * nkv * qgroups]
@@ -104,7 +107,7 @@ __device__ __forceinline__ void tma_page_4d(uint32_t dst, const CUtensorMap* map
 #define KV_SWIZZLED 1
 #define KV_TMA 2
 
-template <int HD, int ST, int LAYOUT, bool CL>
+template <int HD, int ST, int LAYOUT, bool CL, bool TREE>
 __global__ void __launch_bounds__(NWARPS * 32)
 attn_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, const DecodeParams p) {
     constexpr int LD = HD + 8;  // padded q row (elements): consecutive rows fall into different banks
@@ -661,6 +664,93 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
         return;
     }
     // ---- the CTA that finishes last merges the splits, in split order ------------------------------
+    // Up to 36 splits meet at the group's counter and the last one merges them all (further down).
+    // More splits (a long context of few requests) meet in two levels, so that the merge is not one
+    // CTA's walk over hundreds of partials: twelve consecutive splits share a counter of their own, the
+    // last of them merges the twelve into the first one's place in the workspace (a normalised partial
+    // with its log-sum-exp, like those it read), and the last of these mergers to arrive at the group's
+    // counter merges their results.  The order of the additions depends on the number of splits only,
+    // never on who arrives last.  (TREE: a variant of its own, launched for the few requests with long
+    // contexts that can make so many splits; the kernel of the usual step does not hold this code, since a
+    // decode CTA's time is made of the instructions it has to fetch.)
+    constexpr int Q4 = HD / 4;
+    constexpr int KC = 12;
+    if (TREE && active > 3 * KC) {
+        const size_t group = ((size_t)s * p.nkv + kvh) * p.qgroups + qg;
+        const int sub = (sp - first_split) / KC, max_subs = (p.max_splits + KC - 1) / KC;
+        // the partials this CTA merges if it is the last to arrive: first, first + stride, ..
+        int first = sub * KC, count = min(KC, active - first), stride = 1;
+        int* counter = p.counters + (size_t)gridDim.x * gridDim.y + group * max_subs + sub;
+        bool final = false;
+#pragma unroll 1
+        for (;;) {
+            __syncthreads();
+            if (tid == 0) {
+                int prev;
+                asm volatile("atom.add.acq_rel.gpu.global.s32 %0, [%1], 1;" : "=r"(prev) : "l"(counter) : "memory");
+                last_flag = (prev == count - 1);
+                if (last_flag) *counter = 0;
+            }
+            __syncthreads();
+            if (!last_flag) break;
+            for (int item = tid; item < rows * Q4; item += blockDim.x) {
+                const int r = item / Q4, d = (item % Q4) * 4;
+                float* lp = p.part_lse + ((size_t)s * p.nh + h0 + r) * p.max_splits + first_split + first;
+                float4* po = reinterpret_cast<float4*>(
+                    p.part_o + (((size_t)s * p.nh + h0 + r) * p.max_splits + first_split + first) * HD + d);
+                float m = -INFINITY, W = 0.f;
+                float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 1
+                for (int k0 = 0; k0 < count; k0 += KC) {
+                    float l[KC];
+                    float4 v[KC];
+#pragma unroll
+                    for (int k = 0; k < KC; ++k) {
+                        l[k] = k0 + k < count ? __ldcg(lp + (k0 + k) * stride) : -INFINITY;
+                        v[k] = k0 + k < count ? __ldcg(po + (size_t)(k0 + k) * stride * Q4) : make_float4(0.f, 0.f, 0.f, 0.f);
+                    }
+                    float m_new = m;
+#pragma unroll
+                    for (int k = 0; k < KC; ++k) m_new = fmaxf(m_new, l[k]);
+                    if (k0 > 0) {
+                        const float keep = (m == -INFINITY) ? 0.f : fast_exp2(m - m_new);
+                        W *= keep;
+                        acc.x *= keep; acc.y *= keep; acc.z *= keep; acc.w *= keep;
+                    }
+                    m = m_new;
+#pragma unroll
+                    for (int k = 0; k < KC; ++k) {
+                        const float w = (l[k] == -INFINITY) ? 0.f : fast_exp2(l[k] - m);
+                        W += w;
+                        acc.x = fmaf(w, v[k].x, acc.x); acc.y = fmaf(w, v[k].y, acc.y);
+                        acc.z = fmaf(w, v[k].z, acc.z); acc.w = fmaf(w, v[k].w, acc.w);
+                    }
+                }
+                const float inv = W > 0.f ? 1.f / W : 0.f;
+                if (final) {
+                    uint2 o;
+                    o.x = pack_bf16(acc.x * inv, acc.y * inv);
+                    o.y = pack_bf16(acc.z * inv, acc.w * inv);
+                    *reinterpret_cast<uint2*>(p.out + ((size_t)row * p.nh + h0 + r) * HD + d) = o;
+                } else {
+                    // over the first of the twelve: this thread alone reads and writes these four outputs
+                    *po = make_float4(acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv);
+                    if (d == 0) w_s[r][0] = W > 0.f ? m + log2f(W) : -INFINITY;
+                }
+            }
+            if (final) break;
+            // the merged log-sum-exps go over the first split's once every thread has read those
+            __syncthreads();
+            if (tid < rows) p.part_lse[((size_t)s * p.nh + h0 + tid) * p.max_splits + first_split + first] = w_s[tid][0];
+            count = (active + KC - 1) / KC;
+            first = 0;
+            stride = KC;
+            counter = p.counters + group;
+            final = true;
+        }
+        cw_trace_end();
+        return;
+    }
     // Release / acquire through the counter: the barrier orders every thread's partial stores before
     // thread 0's release at GPU scope, and the last CTA's acquire, followed by its barrier, orders its
     // threads' loads after all groups' stores.  (One scoped atomic instead of a fence in every thread.)
@@ -682,8 +772,6 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
     // are taken twelve at a time, and all loads of a round (the row's log-sum-exps and the partials) are
     // issued before any is used: one trip to the L2 per round.  Between rounds the sum so far is
     // rescaled to the new maximum, as in the online softmax.
-    constexpr int Q4 = HD / 4;
-    constexpr int KC = 12;
     for (int item = tid; item < rows * Q4; item += blockDim.x) {
         const int r = item / Q4, d = (item % Q4) * 4;
         const float* lp = p.part_lse + ((size_t)s * p.nh + h0 + r) * p.max_splits + first_split;
@@ -728,7 +816,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
 
 static CUtensorMap g_no_map;  // what the variants without TMA are given
 
-template <int HD, int ST, int LAYOUT, bool CL>
+template <int HD, int ST, int LAYOUT, bool CL, bool TREE = false>
 static int launch_decode_cl(const DecodeParams& p, int S, int splits, cudaStream_t stream, const CUtensorMap& mk = g_no_map,
                             const CUtensorMap& mv = g_no_map) {
     constexpr int LD = HD + 8;
@@ -739,20 +827,21 @@ static int launch_decode_cl(const DecodeParams& p, int S, int splits, cudaStream
     static int configured = 0;
     if (SMEM > configured) {
         if (SMEM > 48 * 1024 &&
-            cudaFuncSetAttribute(attn_decode_kernel<HD, ST, LAYOUT, CL>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess)
+            cudaFuncSetAttribute(attn_decode_kernel<HD, ST, LAYOUT, CL, TREE>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess)
             return (int)cudaGetLastError();
-        if (CL && cudaFuncSetAttribute(attn_decode_kernel<HD, ST, LAYOUT, CL>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) != cudaSuccess)
+        if (CL && cudaFuncSetAttribute(attn_decode_kernel<HD, ST, LAYOUT, CL, TREE>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) != cudaSuccess)
             return (int)cudaGetLastError();
         configured = SMEM;
     }
     dim3 grid(p.nkv * p.qgroups, S, splits);
-    return cw_launch(attn_decode_kernel<HD, ST, LAYOUT, CL>, grid, dim3(NWARPS * 32), SMEM, stream, CL ? (unsigned)splits : 1u, mk, mv, p);
+    return cw_launch(attn_decode_kernel<HD, ST, LAYOUT, CL, TREE>, grid, dim3(NWARPS * 32), SMEM, stream, CL ? (unsigned)splits : 1u, mk, mv, p);
 }
 
 template <int HD, int ST, int LAYOUT>
 static int launch_decode_st(const DecodeParams& p, int S, int splits, cudaStream_t stream) {
     // (the cluster form for head sizes up to 128: the larger ones have no room for its inbox beside their tiles)
     if (HD <= 128 && p.cluster > 1) return launch_decode_cl<HD, ST, LAYOUT, (HD <= 128)>(p, S, splits, stream);
+    if (ST == 2 && p.tree) return launch_decode_cl<HD, ST, LAYOUT, false, (ST == 2)>(p, S, splits, stream);
     return launch_decode_cl<HD, ST, LAYOUT, false>(p, S, splits, stream);
 }
 
@@ -773,6 +862,7 @@ static int launch_decode_tma(const DecodeParams& p, int S, int splits, cudaStrea
     CUtensorMap mk, mv;
     if (page_map(&mk, p.k_cache, p.num_pages, p.page_size, p.nkv, HD) != 0 || page_map(&mv, p.v_cache, p.num_pages, p.page_size, p.nkv, HD) != 0)
         return CW_ERR_UNSUPPORTED;
+    if (ST == 2 && p.tree) return launch_decode_cl<HD, ST, KV_TMA, false, (ST == 2)>(p, S, splits, stream, mk, mv);
     return launch_decode_cl<HD, ST, KV_TMA, false>(p, S, splits, stream, mk, mv);
 }
 
@@ -790,14 +880,21 @@ static int launch_decode(const DecodeParams& p, int S, int splits, cudaStream_t 
     return launch_decode_st<HD, 2, KV_PADDED>(p, S, splits, stream);
 }
 
-// Workspace a call needs: part_o floats, part_lse floats, counters.
-extern "C" int cw_attention_decode_workspace(int S, int nh, int nkv, int hd, int max_ctx, long long* part_o_floats,
-                                             long long* part_lse_floats, int* counters) {
+// Workspace a call needs: part_o floats, part_lse floats, counters (one per (request, KV head, group of
+// 16 query heads); with `two_levels`, one more per twelve splits of each, for the variant that merges
+// many splits in two levels).
+static void decode_workspace(int S, int nh, int nkv, int hd, int max_ctx, bool two_levels, long long* part_o_floats,
+                             long long* part_lse_floats, int* counters) {
     const int splits = (max_ctx + MIN_SPLIT - 1) / MIN_SPLIT;
     const int G = nh / (nkv > 0 ? nkv : 1);
     *part_o_floats = (long long)S * nh * splits * hd;
     *part_lse_floats = (long long)S * nh * splits;
-    *counters = S * nkv * ((G + 15) / 16);
+    *counters = S * nkv * ((G + 15) / 16) * (two_levels ? 1 + (splits + 11) / 12 : 1);
+}
+
+extern "C" int cw_attention_decode_workspace(int S, int nh, int nkv, int hd, int max_ctx, long long* part_o_floats,
+                                             long long* part_lse_floats, int* counters) {
+    decode_workspace(S, nh, nkv, hd, max_ctx, true, part_o_floats, part_lse_floats, counters);
     return CW_OK;
 }
 
@@ -882,6 +979,8 @@ extern "C" int cw_attention_decode_rows(const void* q, int q_stride, void* out, 
         p.cluster = 0;
     if (!p.cluster && splits > 1 && (part_o == nullptr || part_lse == nullptr || counters == nullptr)) return CW_ERR_BAD_SIZE;
     p.max_splits = splits;
+    // few groups with contexts that can make more than 36 splits: the variant with the two-level merge
+    p.tree = splits > 36 && S * nkv * p.qgroups <= 16 && !p.cluster && p.stages == 2;
     p.split = split; p.split_ptr = split_ptr;
     // when split_ptr decides at run time, `split` (if not 0) bounds what it may say, else a split may
     // span the whole context (a cluster makes the kernel cut no finer than the context bound divided
@@ -939,7 +1038,8 @@ static void noalloc_layout(int S, int nh, int nkv, int hd, int max_ctx, size_t* 
                            size_t* o_bytes) {
     long long part_o_floats = 0, part_lse_floats = 0;
     int counters = 0;
-    cw_attention_decode_workspace(S, nh, nkv, hd, max_ctx, &part_o_floats, &part_lse_floats, &counters);
+    // (this entry point asks for four tiles in flight: never the variant with the two-level merge)
+    decode_workspace(S, nh, nkv, hd, max_ctx, false, &part_o_floats, &part_lse_floats, &counters);
     *counters_bytes = align256((size_t)counters * sizeof(int));
     *lse_bytes = align256((size_t)part_lse_floats * sizeof(float));
     *o_bytes = align256((size_t)part_o_floats * sizeof(float));

@@ -631,6 +631,35 @@ def test_attention_decode_tiles_by_tma(ops, status, fast, nh, nkv, hd, ps, windo
         ops.raise_on_status(status)
 
 
+@pytest.mark.parametrize("window", [None, 5000])
+def test_attention_decode_merges_many_splits_in_two_levels(ops, status, fast, window):
+    """Contexts cut into 51, 37 and 36 splits of 128 tokens: more than 36 meet in two levels (twelve
+    splits share a counter, their last merges them, the last merger merges the results; the last group
+    of the 37 holds a single split), 36 at one counter.  With a window the first splits hold no key
+    and the groups of twelve start at the first split that does.  A second call gives the same bits:
+    every counter is back at zero."""
+    nh, nkv, hd, ps = 12, 2, 128, 16
+    ctx_lens = [6500, 4700, 4608, 1]
+    dtype = torch.bfloat16
+    k_cache, v_cache, tables, ks, vs = paged_setup(ctx_lens, nkv, hd, ps, dtype, seed=17)
+    g = torch.Generator().manual_seed(6)
+    scale = hd**-0.5
+    qs = [(torch.randn(1, nh, hd, generator=g) * 2).to(dtype).float() for _ in ctx_lens]
+    wide = torch.zeros(len(ctx_lens), (nh + 2 * nkv) * hd)
+    wide[:, : nh * hd] = torch.cat(qs).view(len(ctx_lens), -1)
+    args = (wide.to(dtype).to(DEV), k_cache.to(DEV), v_cache.to(DEV), tables.to(DEV),
+            torch.tensor(ctx_lens, dtype=torch.int32, device=DEV), nh, nkv, hd, scale, window, 8192, status)
+    outs = []
+    for stages in (2, 2 | fast.SWIZZLED | fast.TMA_TILES, 2):
+        out = fast.attention_decode(*args, split=128, stages=stages).float().cpu().view(len(ctx_lens), nh, hd)
+        ops.raise_on_status(status)
+        for i, n in enumerate(ctx_lens):
+            want = plain.causal_attention(qs[i], ks[i], vs[i], scale, window=window)[0]
+            torch.testing.assert_close(out[i], want, rtol=2e-2, atol=2e-2, msg=lambda m: f"stages {stages:#x}, context {n}: {m}")
+        outs.append(out)
+    assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
+
+
 def test_attention_decode_scratch_outlives_captured_graphs(ops, status, fast):
     """A captured graph has the addresses of the split-merge scratch baked in.  A later, larger call
     makes the module take a larger scratch set; the set the graph points at must stay alive and its
