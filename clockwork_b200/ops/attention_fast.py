@@ -1,4 +1,4 @@
-"""Python faces of the bfloat16 attention kernels: split-context decode (``csrc/attention_decode.cu``)
+"""Python faces of the bfloat16 attention kernels: split-context decode (``csrc/attention_decode_kernel.cuh``, entry points in ``csrc/attention_decode.cu``)
 and prefill on the tensor cores (``csrc/attention_prefill_tc.cu``: tcgen05, head sizes 64 and 128;
 ``csrc/attention_prefill.cu``: mma.sync, the other sizes).  ``ops.attention.paged_attention`` picks
 them when a step's sizes allow."""

@@ -18,7 +18,7 @@ import torch
 
 from .library import check, library
 
-_TUS = ("attention_decode", "attention_prefill", "attention_prefill_tc", "attention_ref", "embed_norm", "gemm_ref",
+_TUS = ("attention_decode", "attention_decode_large", "attention_decode_mid", "attention_prefill", "attention_prefill_tc", "attention_ref", "embed_norm", "gemm_ref",
         "gemm_tc", "rope_cache", "sampling")
 _WORDS = 8
 _buf: torch.Tensor | None = None
