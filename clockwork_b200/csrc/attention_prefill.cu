@@ -40,6 +40,7 @@ attn_prefill_kernel(const PrefillParams p) {
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g = lane >> 2, t = lane & 3;
     const int s = p.item_seq[blockIdx.x], q0 = p.item_q0[blockIdx.x];
+    if (s < 0) return;  // an unused entry of a work list of fixed length (captured steps)
     const int h = blockIdx.y, kvh = h / (p.nh / p.nkv);
     const int row0 = p.q_start[s], q_len = p.q_start[s + 1] - row0;
     const int ctx = p.ctx_lens[s];

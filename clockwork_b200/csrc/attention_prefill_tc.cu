@@ -213,6 +213,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int h = blockIdx.x, item = blockIdx.y;
     const int s = p.item_seq[item], q0 = p.item_q0[item];
+    if (s < 0) return;  // an unused entry of a work list of fixed length (captured steps): nothing is set up yet
     const int kvh = h / (p.nh / p.nkv);
     const int row0 = p.q_start[s], q_len = p.q_start[s + 1] - row0;
     const int ctx = p.ctx_lens[s];

@@ -155,6 +155,9 @@ __device__ __forceinline__ void cw_trace_end() {
     rec[3] = now;
     rec[4] = (unsigned long long)gridDim.x | ((unsigned long long)gridDim.y << 20) | ((unsigned long long)gridDim.z << 40);
     rec[5] = (unsigned long long)blockIdx.x | ((unsigned long long)blockIdx.y << 20) | ((unsigned long long)blockIdx.z << 40);
+    unsigned smid;
+    asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+    rec[6] = smid;
 }
 static inline int cw_trace_set_tu(void* buf) {
     return (int)cudaMemcpyToSymbol(cw_trace_ptr, &buf, sizeof(buf));

@@ -797,11 +797,20 @@ static int g_stream_enabled = 1;
 // Switches the persistent form of few-token products over very many weight tiles off or on (measurements).
 extern "C" int cw_gemm_tc_set_stream(int on) { g_stream_enabled = on ? 1 : 0; return CW_OK; }
 
+static int g_persistent_from = 129;
+// From how many tokens on the persistent kernels run (measurements; the default is the measured crossover).
+extern "C" int cw_gemm_tc_set_persistent_from(int tokens) {
+    if (tokens < 129) return CW_ERR_BAD_SIZE;
+    g_persistent_from = tokens;
+    return CW_OK;
+}
+
 static Plan make_plan(int T, int N, int K, bool swiglu, int sm_count, bool c_by_tma = true, bool adds = false) {
     Plan pl;
-    const int cap = swiglu ? 128 : 256;
-    pl.persistent = T > 256 && sm_count > 0 && c_by_tma;  // its epilogue has no other way out than TMA
-    pl.bn = T <= 16 ? 16 : (T <= 32 ? 32 : (T <= 64 ? 64 : (T <= 128 ? 128 : cap)));
+    pl.persistent = T >= g_persistent_from && sm_count > 0 && c_by_tma;  // its epilogue has no other way out than TMA
+    // (token tiles of the one-tile-per-CTA kernel are at most 128 wide: wider ones cannot be split over K,
+    // and a product of a few hundred tokens has too few tiles to do without)
+    pl.bn = T <= 16 ? 16 : (T <= 32 ? 32 : (T <= 64 ? 64 : 128));
     pl.pair = pl.persistent && !swiglu && sm_count >= 2 && g_pair_enabled;
     // Few tokens against so many weight tiles that one CTA per tile would run in three rounds or more
     // (the logits product): one CTA per SM walks the tiles instead, its loads running on into the

@@ -65,7 +65,9 @@ class StepBuilder:
             self._pinned = torch.empty(max(n_ints, 4096), dtype=torch.int32, pin_memory=True)
         return self._pinned
 
-    def prepare(self, entries: list[StepEntry]) -> PreparedStep:
+    def requests_of(self, entries: list[StepEntry]) -> list:
+        """The entries' requests, with room reserved for the tokens they bring; refuses a request that
+        appears twice and wanted places outside an entry's tokens."""
         cache = self.cache
         reqs = []
         seen = set()
@@ -79,7 +81,11 @@ class StepBuilder:
             bad = [w for w in e.want if not 0 <= w < len(e.tokens)]
             if bad:
                 raise ValueError(f"request {e.request_id!r}: wanted places {bad} outside its {len(e.tokens)} tokens")
+        return reqs
 
+    def prepare(self, entries: list[StepEntry]) -> PreparedStep:
+        cache = self.cache
+        reqs = self.requests_of(entries)
         S = len(entries)
         q_lens = [len(e.tokens) for e in entries]
         N = sum(q_lens)
@@ -341,6 +347,152 @@ class DecodeGraph:
         return self.out[: self._filled]
 
 
+class PortionGraph:
+    """One captured CUDA graph of a step that holds prompt portions: up to ``tokens`` tokens of up to
+    ``seqs`` requests with contexts up to ``max_ctx``, logits at up to ``rows`` places.  Such a step's
+    kernels are many and small when the portions are short (a prompt of a few hundred tokens, a portion
+    beside decoded tokens), and launching them one by one from the host takes longer than they run.
+
+    Everything the step's kernels need to know about its contents lives in one int32 device buffer,
+    written on the host and uploaded in one copy before every replay: the arrays of an uncaptured step
+    (``StepBuilder.prepare``) at fixed lengths, the parts' per-step scalars and the parts' per-step
+    arrays (``Part.step_arrays``).  Unused token rows carry token 0 at position 0 with no cache slot,
+    belong to no request, and are computed and ignored; unused requests have no tokens.  ``singles``:
+    whether the steps that replay this graph hold requests that bring one token (parts may serve those
+    apart from the portions, as attention does with its decode kernel)."""
+
+    def __init__(self, runner: "ModelRunner", tokens: int, seqs: int, rows: int, max_ctx: int, singles: bool) -> None:
+        cache, model = runner.cache, runner.model
+        self.tokens, self.seqs, self.rows, self.max_ctx, self.singles = tokens, seqs, rows, max_ctx, singles
+        self.max_blocks = (max_ctx + cache.page_size - 1) // cache.page_size
+        G = len(cache.groups)
+        self._scalar_rules = model.step_scalars()
+        self._arrays = model.step_arrays(tokens, seqs, cache.page_size)
+        layout = [("tokens", tokens), ("positions", tokens), ("tok_seq", tokens), ("q_start", seqs + 1), ("ctx_lens", seqs),
+                  ("rows", rows), ("state", seqs), *((f"scalar:{name}", 1) for name in self._scalar_rules),
+                  *((("array", key), words) for key, (words, _, _) in self._arrays.items())]
+        for g in range(G):
+            layout += [(f"slots{g}", tokens), (f"tables{g}", seqs * self.max_blocks)]
+        seg, off = {}, 0
+        for name, size in layout:
+            seg[name] = (off, size)
+            off += _pad4(size)
+        self.seg, self.size = seg, off
+        self.host = torch.zeros(off, dtype=torch.int32, pin_memory=True)
+        self.dev = torch.zeros(off, dtype=torch.int32, device=runner.device)
+        h = self.host.numpy()
+        self.h = {name: h[o : o + n] for name, (o, n) in seg.items()}
+        for g in range(G):
+            self.h[f"tables{g}"] = self.h[f"tables{g}"].reshape(seqs, self.max_blocks)
+        self.upload_bytes = off * 4
+        self._uploaded = torch.cuda.Event()
+        self._filled_rows = 0
+
+        def view(name):
+            o, n = seg[name]
+            return self.dev[o : o + n]
+
+        ctx = StepContext(
+            dtype=model.dtype, device=runner.device, status=runner.status, num_tokens=tokens, num_seqs=seqs,
+            positions=view("positions"), tok_seq=view("tok_seq"), q_start=view("q_start"), ctx_lens=view("ctx_lens"),
+            q_lens_host=[], ctx_lens_host=[], max_q_len=tokens, max_ctx_len=max_ctx,
+        )
+        ctx.extras["captured_portions"] = {"singles": singles}
+        for name in self._scalar_rules:
+            ctx.extras[name] = view(f"scalar:{name}")
+        for key, (_, _, present) in self._arrays.items():
+            ctx.extras[key] = present(view(("array", key)))
+        tables = [view(f"tables{g}").view(seqs, self.max_blocks) for g in range(G)]
+        kv_slots = [view(f"slots{g}") for g in range(G)]
+        state_rows = torch.zeros(seqs, dtype=torch.int64, device=runner.device) if cache.state.needs else None
+        ctx.views = cache.views(tables, kv_slots, state_rows, [])
+
+        def run():
+            if state_rows is not None:
+                state_rows.copy_(view("state"))
+            return model.forward(ctx, view("tokens"), view("rows"))
+
+        self._write_padding(cache, 0, 0, 0)
+        self.dev.copy_(self.host)  # no request at all: the warm-up and the capture touch no cache slot
+        before = launch_count()
+        run()  # eager warm-up: scratch buffers and kernel attributes are set up outside the capture
+        self.kernels = launch_count() - before
+        torch.cuda.synchronize()
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph):
+            self.logits = run()
+        torch.cuda.synchronize()
+
+    def _write_padding(self, cache: CacheManager, n: int, s: int, r: int) -> None:
+        """Everything behind the first ``n`` tokens, ``s`` requests and ``r`` wanted rows."""
+        h = self.h
+        h["tokens"][n:] = 0
+        h["positions"][n:] = 0
+        h["tok_seq"][n:] = -1
+        h["q_start"][s + 1 :] = n
+        h["ctx_lens"][s:] = 0
+        h["rows"][r:] = 0
+        h["state"][s:] = cache.state.scratch_slot
+        for g in range(len(cache.groups)):
+            h[f"slots{g}"][n:] = -1
+            h[f"tables{g}"][s:] = NO_PAGE
+        if n == 0:  # (the capture: no request, no work)
+            h["q_start"][:] = 0
+            for name in self._scalar_rules:
+                h[f"scalar:{name}"][0] = self._scalar_rules[name](1, 1)
+            for key, (_, fill, _) in self._arrays.items():
+                h[("array", key)][:] = fill([], [])
+
+    def fill(self, cache: CacheManager, entries: list[StepEntry], reqs: list) -> list[int]:
+        """The step's description written into the pinned buffer.  Returns the context lengths after the step."""
+        self._uploaded.synchronize()  # the last upload has left the pinned buffer
+        h, ps = self.h, cache.page_size
+        S = len(entries)
+        q_lens = [len(e.tokens) for e in entries]
+        N = sum(q_lens)
+        starts = [r.num_computed for r in reqs]
+        ctx_lens = [a + q for a, q in zip(starts, q_lens)]
+        rows = [w for e in entries for w in e.want]
+        R = len(rows)
+        h["tokens"][:N] = np.fromiter((t for e in entries for t in e.tokens), dtype=np.int64, count=N)
+        h["positions"][:N] = np.concatenate([np.arange(a, a + q, dtype=np.int32) for a, q in zip(starts, q_lens)])
+        h["tok_seq"][:N] = np.repeat(np.arange(S, dtype=np.int32), q_lens)
+        q_start = np.zeros(S + 1, dtype=np.int32)
+        np.cumsum(q_lens, out=q_start[1:])
+        h["q_start"][: S + 1] = q_start
+        h["ctx_lens"][:S] = ctx_lens
+        h["rows"][:R] = [int(q_start[i]) + w for i, e in enumerate(entries) for w in e.want]
+        h["state"][:S] = [r.state_slot if r.state_slot is not None else cache.state.scratch_slot for r in reqs]
+        for g in range(len(cache.groups)):
+            slots, tables = h[f"slots{g}"], h[f"tables{g}"]
+            tables[:S] = NO_PAGE
+            for i, r in enumerate(reqs):
+                table = np.asarray(r.tables[g], dtype=np.int32)
+                tables[i, : len(table)] = table
+                pos = np.arange(starts[i], ctx_lens[i], dtype=np.int32)
+                pages = table[pos // ps]
+                if (pages == NO_PAGE).any():
+                    raise RuntimeError(f"request {r.request_id!r}: a token lands in a page that was given back")
+                slots[q_start[i] : q_start[i + 1]] = pages * ps + pos % ps
+        self._write_padding(cache, N, S, R)
+        single_ctx = [c for q, c in zip(q_lens, ctx_lens) if q == 1]
+        for name, rule in self._scalar_rules.items():
+            # (the scalars speak of the requests that bring one token: the decode kernel's share of the step)
+            h[f"scalar:{name}"][0] = rule(max(1, len(single_ctx)), max(single_ctx, default=1))
+        for key, (_, fill, _) in self._arrays.items():
+            h[("array", key)][:] = fill(q_lens, ctx_lens)
+        self._filled_rows = R
+        return ctx_lens
+
+    def launch(self) -> torch.Tensor | None:
+        """The upload and the replay.  Returns the logits of the wanted rows (a view of the graph's own
+        output buffer: the next replay of the same graph overwrites it), or None when none is wanted."""
+        self.dev.copy_(self.host, non_blocking=True)
+        self._uploaded.record()
+        self.graph.replay()
+        return self.logits[: self._filled_rows] if self._filled_rows else None
+
+
 class ModelRunner:
     """The step function over a model and a cache manager."""
 
@@ -356,9 +508,12 @@ class ModelRunner:
         self.steps_run = 0
         self.graphs: dict[tuple[int, bool, int], DecodeGraph] = {}  # (batch bucket, greedy, context tier)
         self.graph_max_ctx = 0  # set by enable_graphs
+        self.portions_captured = False  # whether short steps with prompt portions replay captured graphs too
         self.graph_max_batch = 0
         self.graph_kernel_launches = 0  # kernels replayed through graphs (for accounting)
         self.last_graph: DecodeGraph | None = None  # the graph of the last captured step that ran
+        self.portion_graphs: dict[tuple, PortionGraph] = {}  # (tokens, requests, rows, context tier, singles apart)
+        self.portion_graph_steps = 0  # steps with prompt portions that replayed a captured graph
         self.last_upload_bytes = 0
         self.uploaded_bytes = 0  # host-to-device bytes of all steps so far
 
@@ -370,6 +525,7 @@ class ModelRunner:
             return False
         self.graph_max_ctx, self.graph_max_batch = max_ctx, max_batch
         self.model.reserve_for_steps(max_batch, max_ctx)  # scratch that captured graphs point at is set up once
+        self.portions_captured = self.model.dtype == torch.bfloat16 and self.model.graph_safe_portions()
         return True
 
     def can_use_graph(self, entries: list[StepEntry]) -> bool:
@@ -448,11 +604,53 @@ class ModelRunner:
         entries = [e for e in entries if e.tokens]
         if not entries:
             return None
+        graph_key = self._portion_graph_key(entries)
+        if graph_key is not None:
+            return self._step_with_portion_graph(entries, graph_key)
         prepared = self.builder.prepare(entries)
         logits = self.model.forward(prepared.ctx, prepared.token_ids, prepared.logit_rows)
         self.builder.commit(prepared)
         self.last_upload_bytes = self.builder.last_upload_bytes
         self.uploaded_bytes += self.builder.last_upload_bytes
+        self.steps_run += 1
+        return logits
+
+    # A step with prompt portions replays a captured graph when it is short enough to be bound by the
+    # host's launches: at most PORTION_TOKEN_BUCKETS[-1] tokens of at most PORTION_SEQS requests.
+    PORTION_TOKEN_BUCKETS = (128, 256, 512, 1024)
+    PORTION_SEQS = 8
+
+    def _portion_graph_key(self, entries: list[StepEntry]) -> tuple | None:
+        if not self.portions_captured or len(entries) > self.PORTION_SEQS:
+            return None
+        tokens = sum(len(e.tokens) for e in entries)
+        if tokens > self.PORTION_TOKEN_BUCKETS[-1] or tokens == len(entries):  # (all single tokens: the decode graphs' steps)
+            return None
+        longest = max(self.cache.get(e.request_id).num_computed + len(e.tokens) for e in entries)
+        if longest > self.graph_max_ctx:
+            return None
+        bucket = next(b for b in self.PORTION_TOKEN_BUCKETS if b >= tokens)
+        wanted = sum(len(e.want) for e in entries)
+        rows = self.PORTION_SEQS if wanted <= self.PORTION_SEQS else bucket  # one row per request, or any rows
+        tier = 1024
+        while tier < longest:
+            tier *= 2
+        tier = min(tier, self.graph_max_ctx)
+        singles = any(len(e.tokens) == 1 for e in entries)
+        return bucket, self.PORTION_SEQS, rows, tier, singles
+
+    def _step_with_portion_graph(self, entries: list[StepEntry], key: tuple) -> torch.Tensor | None:
+        reqs = self.builder.requests_of(entries)
+        graph = self.portion_graphs.get(key)
+        if graph is None:
+            graph = self.portion_graphs[key] = PortionGraph(self, *key)
+        ctx_lens = graph.fill(self.cache, entries, reqs)
+        logits = graph.launch()
+        self.builder.commit(PreparedStep(None, None, None, reqs, ctx_lens))
+        self.graph_kernel_launches += graph.kernels
+        self.portion_graph_steps += 1
+        self.last_upload_bytes = graph.upload_bytes
+        self.uploaded_bytes += graph.upload_bytes
         self.steps_run += 1
         return logits
 

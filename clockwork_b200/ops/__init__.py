@@ -35,7 +35,15 @@ def dtype_code(dtype: torch.dtype) -> int:
     raise ValueError(f"unsupported dtype {dtype}; the kernels take float32 and bfloat16")
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+_raw_device = getattr(torch._C, "_cuda_getDevice", None)
+
+
 def _stream() -> int:
+    """The current CUDA stream's handle.  Asked of torch's C layer directly: the Python-level
+    ``torch.cuda.current_stream()`` costs more than the launch it is asked for."""
+    if _raw_stream is not None and _raw_device is not None:
+        return _raw_stream(_raw_device())
     return torch.cuda.current_stream().cuda_stream
 
 

@@ -335,6 +335,40 @@ def set_cut_long_rows(on: bool) -> None:
     _cut_long_rows = bool(on)
 
 
+def _cuts_for(num_heads: int, head_dim: int, page_size: int) -> int:
+    """The head count that ``prefill_work_items`` cuts long rows of keys for: 0 when they are not cut."""
+    return num_heads if _cut_long_rows and prefill_tc_takes(head_dim, page_size) else 0
+
+
+def portion_step_arrays(num_heads: int, head_dim: int, page_size: int, max_tokens: int, max_seqs: int, device) -> dict:
+    """The prefill kernel's work list as an array of a captured step (``Part.step_arrays``): three rows
+    (request, first query row, split word) of fixed length, unused entries naming request -1.  Two keys,
+    for steps captured with and without their single-token requests served apart."""
+    if head_dim not in PREFILL_HEAD_DIMS:
+        return {}
+    cuts = _cuts_for(num_heads, head_dim, page_size)
+    sms = _sm_count(torch.device(device)) if cuts else 0
+    # a tile per 128 rows and one more per request; cuts add parts until the CTAs fill the SMs once
+    cap = max_tokens // QUERY_TILE + max_seqs + (sms // num_heads if cuts else 0)
+
+    def fill(q_lens, ctx_lens, apart: bool) -> np.ndarray:
+        seqs, q0s, words = prefill_work_items(q_lens, ctx_lens, cuts, sms, apart)
+        if len(seqs) > cap:
+            raise RuntimeError(f"{len(seqs)} work items for a step captured with room for {cap}")
+        out = np.zeros((3, cap), dtype=np.int32)
+        out[0, :] = -1
+        out[2, :] = 1  # (a whole tile: part 1 of 1)
+        n = len(seqs)
+        out[0, :n], out[1, :n], out[2, :n] = seqs, q0s, words
+        return out.reshape(-1)
+
+    def present(view: torch.Tensor):
+        return view[:cap], view[cap : 2 * cap], (view[2 * cap :] if cuts else None), cap
+
+    return {("prefill_items", cuts, apart): (3 * cap, lambda q, c, apart=apart: fill(q, c, apart), present)
+            for apart in (False, True)}
+
+
 def _work_items(ctx, num_heads: int, skip_single: bool = False) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor | None, int]:
     """The step's work items on the device; built once per step and head count (``num_heads`` 0: no
     cuts) and shared by the layers."""
@@ -356,11 +390,14 @@ _prefill_scratch_by_device: dict[int, dict] = {}
 
 def _prefill_scratch(device: torch.device, items: int, num_heads: int, head_dim: int) -> dict:
     """Partial results of cut work items (float32 O, (m, l) per row) and their arrival counters, kept
-    per device and grown when a step needs more; the counters are zero between launches."""
+    per device and grown when a step needs more; the counters are zero between launches.  A set that is
+    outgrown is kept alive: captured steps may point at it."""
     index = device.index if device.index is not None else torch.cuda.current_device()
     slots = items * num_heads
     st = _prefill_scratch_by_device.get(index)
     if st is None or st["part_o"].numel() < slots * QUERY_TILE * head_dim or st["counters"].numel() < slots:
+        if st is not None:
+            _retired_scratch.append(st)
         st = {
             "part_o": torch.empty(slots * QUERY_TILE * head_dim, dtype=torch.float32, device=device),
             "part_ml": torch.empty(slots * QUERY_TILE * 2, dtype=torch.float32, device=device),
@@ -380,13 +417,28 @@ class _Prefill:
         # Requests that bring a single token go to the decode kernel (a context split over CTAs, the query
         # heads of a KV head sharing every tile) instead of taking a 128-row query tile per head here; the
         # two kernels fill one output tensor.
-        singles = sum(1 for n in ctx.q_lens_host if n == 1) if _route_single_tokens and head_dim in DECODE_HEAD_DIMS else 0
-        item_seq, item_q0, item_split, items = _work_items(
-            ctx, num_heads if _cut_long_rows and prefill_tc_takes(head_dim, view.k_cache.shape[1]) else 0, singles > 0)
+        captured = ctx.extras.get("captured_portions")
+        if captured is not None:
+            # a captured step: how its tokens are divided is not known here; the work list is an array of
+            # the step, and whether single tokens are served apart was fixed when the step was captured
+            singles = ctx.num_seqs if captured["singles"] and _route_single_tokens and head_dim in DECODE_HEAD_DIMS else 0
+        else:
+            singles = sum(1 for n in ctx.q_lens_host if n == 1) if _route_single_tokens and head_dim in DECODE_HEAD_DIMS else 0
+        item_seq, item_q0, item_split, items = _work_items(ctx, _cuts_for(num_heads, head_dim, view.k_cache.shape[1]), singles > 0)
         out = attention_prefill(qkv, view.k_cache, view.v_cache, view.block_tables, ctx.q_start, ctx.ctx_lens,
                                 item_seq, item_q0, items, num_heads, num_kv_heads, head_dim, scale, window, ctx.status,
                                 item_split=item_split)
-        if singles:
+        if singles and captured is not None:
+            # any of the step's requests may be one that brings a single token, with a context up to the
+            # step's bound; how finely contexts are cut is a device scalar of the step
+            split_dev = ctx.extras[dispatch.decode_split_name(num_heads, num_kv_heads, head_dim)]
+            attention_decode(qkv, view.k_cache, view.v_cache, view.block_tables, ctx.ctx_lens, num_heads, num_kv_heads,
+                             head_dim, scale, window, ctx.max_ctx_len, ctx.status,
+                             split=decode_split_bound(singles, num_heads, num_kv_heads, ctx.max_ctx_len, qkv.device, head_dim),
+                             split_dev=split_dev,
+                             stages=decode_stages(singles, num_heads, num_kv_heads, ctx.max_ctx_len, qkv.device, head_dim),
+                             q_start=ctx.q_start, out=out)
+        elif singles:
             longest = max(c for n, c in zip(ctx.q_lens_host, ctx.ctx_lens_host) if n == 1)
             attention_decode(qkv, view.k_cache, view.v_cache, view.block_tables, ctx.ctx_lens, num_heads, num_kv_heads,
                              head_dim, scale, window, longest, ctx.status,

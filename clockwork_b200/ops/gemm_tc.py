@@ -31,6 +31,8 @@ def _configure() -> None:
     lib.cw_gemm_tc_norm.restype = c_int
     lib.cw_gemm_tc_plan.argtypes = [I, I, I, I, I, POINTER(c_int), POINTER(c_int), POINTER(c_int)]
     lib.cw_gemm_tc_plan.restype = c_int
+    lib.cw_gemm_tc_set_persistent_from.argtypes = [I]
+    lib.cw_gemm_tc_set_persistent_from.restype = c_int
     lib.cw_gemm_tc_set_pair.argtypes = [I]
     lib.cw_gemm_tc_set_pair.restype = c_int
     lib.cw_gemm_tc_set_stream.argtypes = [I]
@@ -53,6 +55,12 @@ def set_pair_kernel(on: bool) -> None:
     on the single-CTA persistent kernel (for measurements and for testing that kernel)."""
     _configure()
     library().cw_gemm_tc_set_pair(1 if on else 0)
+
+
+def set_persistent_from(tokens: int) -> None:
+    """From how many tokens on a product runs on the persistent kernels (for measurements)."""
+    _configure()
+    check(library().cw_gemm_tc_set_persistent_from(int(tokens)), "gemm_tc_set_persistent_from")
 
 
 def set_stream_kernel(on: bool) -> None:

@@ -55,7 +55,8 @@ def reset() -> None:
 
 
 def records() -> torch.Tensor:
-    """[n, 8] int64: start, first release, last release, end (ns), gridDim packed (20 bits each), blockIdx packed."""
+    """[n, 8] int64: start, first release, last release, end (ns), gridDim packed (20 bits each), blockIdx packed,
+    the SM the CTA ran on."""
     torch.cuda.synchronize()
     n = min(int(_buf[0]), int(_buf[1]))
     return _buf[_WORDS : _WORDS * (1 + n)].view(n, _WORDS).cpu()

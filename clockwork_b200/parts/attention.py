@@ -44,6 +44,7 @@ class Attention(Mixer):
             raise ValueError("window must be positive or None")
         self.position = build_part("position", p["position"], prefix, dtype, device)
         self.graph_safe = bool(self.position.graph_safe)
+        self.graph_safe_portions = bool(getattr(self.position, "graph_safe_portions", False))
         self.qkv: Linear | None = None
         self.o: Linear | None = None
 
@@ -57,6 +58,13 @@ class Attention(Mixer):
             return {}
         return {attention_ops.decode_split_name(nh, nkv, hd):
                 lambda num_seqs, max_ctx: attention_ops.decode_split(num_seqs, nh, nkv, max_ctx, device, hd)}
+
+    def step_arrays(self, max_tokens: int, max_seqs: int, page_size: int) -> dict:
+        """The work list of the prefill kernel (which 128 query rows of which request, cut how) depends on
+        how a step's tokens are divided among its requests."""
+        if self.dtype != torch.bfloat16:
+            return {}
+        return attention_ops.portion_step_arrays(self.num_heads, self.head_dim, page_size, max_tokens, max_seqs, self.device)
 
     def reserve_for_steps(self, max_seqs: int, max_ctx: int) -> None:
         if self.dtype == torch.bfloat16:

@@ -175,6 +175,22 @@ class Part:
         computes the value on the host.  Parts that want the same value use the same name."""
         return {}
 
+    graph_safe_portions = False  # True when forward, in a step that holds prompt portions, also only launches
+    # kernels on the current stream and takes what it needs about the portions from device memory (the
+    # step's arrays and ``step_arrays`` below), never from the host-side lists: such a step may be captured too
+
+    def step_arrays(self, max_tokens: int, max_seqs: int, page_size: int) -> dict:
+        """int32 arrays that the part's kernels read from device memory in a step of prompt portions and
+        that depend on how the step's tokens are divided among its requests: ``key -> (words,
+        fill(q_lens, ctx_lens) -> numpy int32 [words], present(device view) -> object)``.  A captured
+        step of up to ``max_tokens`` tokens of up to ``max_seqs`` requests keeps ``words`` words per key
+        in its input buffer, fills them before every replay and hands ``present(view)`` to the parts as
+        ``ctx.extras[key]``; ``ctx.extras["captured_portions"]`` then holds ``{"singles": bool}``
+        (whether the steps that replay this graph hold requests that bring a single token).  In an
+        uncaptured step the key is absent and the part builds the array from the step's host-side
+        lists."""
+        return {}
+
     def reserve_for_steps(self, max_seqs: int, max_ctx: int) -> None:
         """Called once before steps are captured: set up whatever scratch memory a single-token step
         of up to ``max_seqs`` requests with contexts up to ``max_ctx`` needs, so that no buffer a

@@ -53,6 +53,10 @@ class DecoderModel:
         """Whether a step of this model may be captured in a CUDA graph."""
         return all(block.graph_safe for block in self.blocks) and self.final_norm.graph_safe
 
+    def graph_safe_portions(self) -> bool:
+        """Whether a step of this model that holds prompt portions may be captured in a CUDA graph."""
+        return all(part.graph_safe_portions for part in self.all_parts())
+
     def all_parts(self):
         """Every part of every block, and the final norm."""
         for block in self.blocks:
@@ -66,6 +70,14 @@ class DecoderModel:
             for name, rule in part.step_scalars().items():
                 scalars.setdefault(name, rule)
         return scalars
+
+    def step_arrays(self, max_tokens: int, max_seqs: int, page_size: int) -> dict:
+        """The per-step device arrays that the model's parts declare (``Part.step_arrays``), by key."""
+        arrays: dict = {}
+        for part in self.all_parts():
+            for key, decl in part.step_arrays(max_tokens, max_seqs, page_size).items():
+                arrays.setdefault(key, decl)
+        return arrays
 
     def reserve_for_steps(self, max_seqs: int, max_ctx: int) -> None:
         for part in self.all_parts():

@@ -18,6 +18,7 @@ from .registry import register_norm
 
 class RMSNorm(Norm):
     graph_safe = True
+    graph_safe_portions = True
 
     def __init__(self, spec, prefix, dtype, device) -> None:
         super().__init__(spec, prefix, dtype, device)

@@ -20,6 +20,7 @@ from .registry import register_position
 
 class RotaryNeox(PositionEncoding):
     graph_safe = True
+    graph_safe_portions = True
 
     def __init__(self, spec, prefix, dtype, device) -> None:
         super().__init__(spec, prefix, dtype, device)
@@ -48,6 +49,7 @@ class RotaryNeox(PositionEncoding):
 
 class NoPosition(PositionEncoding):
     graph_safe = True
+    graph_safe_portions = True
 
     def fused_decode_args(self, head_dim: int):
         return (None, 0)

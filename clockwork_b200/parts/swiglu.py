@@ -17,6 +17,7 @@ from .registry import register_ffn
 
 class SwiGLU(FeedForward):
     graph_safe = True
+    graph_safe_portions = True
     takes_half_normed = True  # x only feeds the gate/up product
 
     def __init__(self, spec, prefix, dtype, device) -> None:

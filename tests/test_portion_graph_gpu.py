@@ -1,0 +1,96 @@
+"""Short steps that hold prompt portions replay captured CUDA graphs (``engine/step.py:PortionGraph``):
+that they do, that what they compute is what the uncaptured step computes (both against the plain
+implementation), whatever the step holds (one prompt, several, portions deep in a context, single tokens
+beside portions, logits wanted at every place or at one per request), and that steps which are too long,
+hold too many requests, run in float32 or through parts that do not declare themselves safe stay
+uncaptured."""
+
+import pytest
+import torch
+
+from clockwork_b200 import EngineConfig
+from clockwork_b200.engine import LLMEngine, StepEntry, load_model
+from tests.plain import qwen2_plain as plain
+from tests.test_replay_gpu import check
+from tests.tiny_configs import TINY, tokens_for
+
+pytestmark = pytest.mark.gpu
+
+
+def runner_for(folder, name, dtype, graphs=True, max_model_len=2048, seqs=16):
+    page = TINY[name][2]
+    cfg = EngineConfig.defaults(str(folder), dtype=dtype, block_size=page, num_blocks=(seqs * max_model_len) // page // 4 + 64,
+                                max_model_len=max_model_len, max_num_seqs=seqs, max_num_batched_tokens=4096,
+                                enable_prefix_cache=False, cuda_graphs=graphs)
+    eng = LLMEngine(cfg, model=load_model(folder, cfg.model.dtype))
+    return eng, eng.runner, eng.cache
+
+
+class Replayed:
+    """Feeds requests through a runner portion by portion and keeps every position's logits."""
+
+    def __init__(self, runner, cache):
+        self.runner, self.cache = runner, cache
+        self.done: dict[str, int] = {}
+        self.logits: dict[str, list] = {}
+
+    def step(self, portions: dict[str, list[int]], want_all=True) -> None:
+        entries = []
+        for rid, toks in portions.items():
+            if rid not in self.done:
+                self.cache.open(rid)
+                self.done[rid], self.logits[rid] = 0, []
+            entries.append(StepEntry(rid, toks, list(range(len(toks))) if want_all else [len(toks) - 1]))
+        out = self.runner.step(entries).float().cpu()
+        row = 0
+        for e in entries:
+            for w in e.want:
+                self.logits[e.request_id].append((self.done[e.request_id] + w, out[row].clone()))
+                row += 1
+            self.done[e.request_id] += len(e.tokens)
+        self.runner.check_status()
+
+    def of(self, rid):
+        rows = sorted(self.logits[rid], key=lambda pair: pair[0])
+        return [p for p, _ in rows], torch.stack([r for _, r in rows])
+
+
+@pytest.mark.parametrize("name", sorted(TINY))
+def test_short_steps_with_portions_replay_captured_graphs(name, sharp_dirs):
+    folder = sharp_dirs[name]
+    config, weights = plain.read_model_dir(folder)
+    _eng, runner, cache = runner_for(folder, name, "bfloat16")
+    assert runner.portions_captured
+    toks = {rid: tokens_for(name, n, salt=40 + i) for i, (rid, n) in enumerate(
+        {"a": 150, "b": 90, "c": 61, "d": 300, "e": 1200, **{f"m{i}": 20 + i for i in range(9)}}.items())}
+    run = Replayed(runner, cache)
+    run.step({"a": toks["a"]})                                        # one prompt, logits everywhere
+    assert runner.portion_graph_steps == 1
+    run.step({"b": toks["b"][:37], "c": toks["c"][:60]})              # two prompts' first portions
+    run.step({"b": toks["b"][37:88], "c": toks["c"][60:], "d": toks["d"][:130]}, want_all=False)  # one row per request
+    run.step({"b": toks["b"][88:89], "d": toks["d"][130:299]})        # a single token beside a portion deep in a context
+    run.step({"b": toks["b"][89:], "d": toks["d"][299:]})             # two single tokens: the decode steps' business
+    assert runner.portion_graph_steps == 4
+    keys = set(runner.portion_graphs)
+    assert {k[4] for k in keys} == {False, True}, keys                # captured with and without single tokens beside the portions
+    assert {k[2] for k in keys} == {runner.PORTION_SEQS, 256, 128}, keys   # rows: one per request, or every place of the bucket
+    run.step({"e": toks["e"][:1100]}, want_all=False)                 # too long for the largest bucket
+    run.step({"e": toks["e"][1100:]}, want_all=False)                 # short again, at a context beyond 1,024: the next tier
+    assert runner.portion_graph_steps == 5 and any(k[3] == 2048 for k in runner.portion_graphs)
+    run.step({f"m{i}": toks[f"m{i}"] for i in range(9)})              # more requests than a captured step holds
+    assert runner.portion_graph_steps == 5
+    for rid in ("a", "b", "c", "d", "e", "m0", "m8"):
+        places, got = run.of(rid)
+        exact = plain.all_position_logits(config, weights, toks[rid])
+        rounded = plain.all_position_logits(config, weights, toks[rid], rnd=plain.to_bfloat16_and_back)
+        check(got, (exact[places], rounded[places]), "bfloat16", f"{name} {rid}")
+
+
+def test_float32_steps_and_uncaptured_engines_take_the_plain_step(sharp_dirs):
+    folder = sharp_dirs["A"]
+    for dtype, graphs in (("float32", True), ("bfloat16", False)):
+        _eng, runner, cache = runner_for(folder, "A", dtype, graphs=graphs)
+        assert not runner.portions_captured
+        run = Replayed(runner, cache)
+        run.step({"a": tokens_for("A", 40, salt=3)})
+        assert runner.portion_graph_steps == 0 and not runner.portion_graphs

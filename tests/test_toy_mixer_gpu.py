@@ -247,6 +247,9 @@ def test_toy_model_with_state_runs_in_captured_steps(toy_dir, tmp_path):
     prompts = [tokens(19, 3), tokens(6, 4), tokens(11, 5)]
     outs = eng.generate(prompts, [SamplingParams(max_tokens=n, ignore_eos=True) for n in (9, 14, 6)])
     assert eng.runner.graphs and eng.steps_run_ahead > 0
+    # (its steps with prompt portions ran uncaptured: the toy mixer walks the step's host-side lists there
+    # and does not declare ``graph_safe_portions``)
+    assert not eng.runner.portions_captured and eng.runner.portion_graph_steps == 0
     for prompt, out in zip(prompts, outs):
         ids = list(prompt)
         for _ in range(out.num_generated_tokens):
