@@ -376,7 +376,8 @@ def main() -> int:
     ap.add_argument("--only", choices=["decode", "prefill", "mixed", "shared-prefix"], default=None,
                     help="run one part only, once, and print its figures (for profiling runs under ncu)")
     ap.add_argument("--prompt-len", type=int, default=None,
-                    help="with --only decode: prompts of this many tokens instead of 1,024 (decoding at other context lengths)")
+                    help="with --only decode: prompts of this many tokens instead of 1,024 (decoding at other context "
+                         "lengths); with --only prefill: a prompt of this many tokens instead of 2,048")
     ap.add_argument("--timeline", action="store_true",
                     help="with --only decode: also print one step's kernel timeline (device-side records, ops/trace.py)")
     args = ap.parse_args()
@@ -410,8 +411,8 @@ def main() -> int:
     rng = random.Random(0)
     peak, peak_kind = peaks()
     once = args.only is not None
-    if args.prompt_len is not None and args.only != "decode":
-        print("bench.py: --prompt-len goes with --only decode")
+    if args.prompt_len is not None and args.only not in ("decode", "prefill"):
+        print("bench.py: --prompt-len goes with --only decode or --only prefill")
         return 2
     prompt_len = args.prompt_len or PROMPT_LEN
 
@@ -545,18 +546,20 @@ def main() -> int:
             print(f"# {str(l['grid']):15s} {l['ctas']:4d}  {f('start_first'):9.2f}..{f('start_last'):9.2f}  "
                   f"{f('released_first'):9.2f}..{f('released_last'):9.2f}  {f('end_first'):9.2f}..{f('end_last'):9.2f}")
 
-    def time_prefill(reps: int = 5) -> dict:
+    def time_prefill(reps: int = 5, tokens: int = PREFILL_LEN) -> dict:
+        """One prompt of ``tokens`` tokens through the step function, wall clock of the device (events around
+        the call: a short prompt's step is a captured graph, and the host's share of a step counts)."""
         engine = make_engine(1, 1)
         runner, cache = engine.runner, engine.cache
         times = []
         for rep in range(reps + 2):
             rid = f"p{rep}"
             cache.open(rid)
-            toks = [rng.randrange(vocab) for _ in range(PREFILL_LEN)]
+            toks = [rng.randrange(vocab) for _ in range(tokens)]
             start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             torch.cuda.synchronize()
             start.record()
-            logits = runner.step([StepEntry(rid, toks, [PREFILL_LEN - 1])])
+            logits = runner.step([StepEntry(rid, toks, [tokens - 1])])
             end.record()
             torch.cuda.synchronize()
             assert logits.shape == (1, vocab)
@@ -565,10 +568,10 @@ def main() -> int:
             cache.close(rid)
         runner.check_status()
         ms = statistics.median(times)
-        flops = prefill_flops(raw, PREFILL_LEN)
+        flops = prefill_flops(raw, tokens)
         del engine
         torch.cuda.empty_cache()
-        return {"value": PREFILL_LEN / (ms / 1e3), "tokens": PREFILL_LEN, "ms": ms,
+        return {"value": tokens / (ms / 1e3), "tokens": tokens, "ms": ms,
                 "frac": flops / (ms / 1e3) / (peak["bf16_tflops"] * 1e12), "tflops": flops / (ms / 1e3) / 1e12,
                 "repeats": spread(times)}
 
@@ -653,7 +656,8 @@ def main() -> int:
                 "decode_tok_s": requests * decode_steps / (t2 - t1), "decode_steps": decode_steps, "total_s": t2 - t0}
 
     if args.only == "prefill":
-        print(json.dumps({"impl": "ours", "prefill": time_prefill(reps=1)}))
+        print(json.dumps({"impl": "ours", "prefill": time_prefill(reps=1 if args.prompt_len is None else 5,
+                                                                   tokens=args.prompt_len or PREFILL_LEN)}))
         return 0
     if args.only == "mixed":
         print(json.dumps({"impl": "ours", "mixed": time_mixed(reps=1)}))
@@ -695,6 +699,10 @@ def main() -> int:
         span = time_span(args.batch)
         points["decode_span_1024_1280"] = span["tok_s"]
         points["decode_span_1024_1280_hbm_frac"] = span["hbm_frac"]
+        for tokens in (128, 512):
+            points[f"prefill_{tokens}_ms"] = time_prefill(tokens=tokens)["ms"]
+        small = time_mixed(decodes=7, ctx=1024, portions=1, portion_len=256)
+        points["mixed_7x1024_1x256_ms"] = small["ms"]
         mixed = time_mixed()
         points["mixed_32x2048_2x512_tok_s"] = mixed["tok_s"]
         points["mixed_32x2048_2x512_ms"] = mixed["ms"]

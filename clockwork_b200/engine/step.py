@@ -616,12 +616,12 @@ class ModelRunner:
         return logits
 
     # A step with prompt portions replays a captured graph when it is short enough to be bound by the
-    # host's launches: at most PORTION_TOKEN_BUCKETS[-1] tokens of at most PORTION_SEQS requests.
-    PORTION_TOKEN_BUCKETS = (128, 256, 512, 1024)
-    PORTION_SEQS = 8
+    # host's launches: at most PORTION_TOKEN_BUCKETS[-1] tokens of at most PORTION_SEQ_BUCKETS[-1] requests.
+    PORTION_TOKEN_BUCKETS = (128, 192, 256, 384, 512, 768, 1024)
+    PORTION_SEQ_BUCKETS = (8, 64)
 
     def _portion_graph_key(self, entries: list[StepEntry]) -> tuple | None:
-        if not self.portions_captured or len(entries) > self.PORTION_SEQS:
+        if not self.portions_captured or len(entries) > self.PORTION_SEQ_BUCKETS[-1]:
             return None
         tokens = sum(len(e.tokens) for e in entries)
         if tokens > self.PORTION_TOKEN_BUCKETS[-1] or tokens == len(entries):  # (all single tokens: the decode graphs' steps)
@@ -630,14 +630,15 @@ class ModelRunner:
         if longest > self.graph_max_ctx:
             return None
         bucket = next(b for b in self.PORTION_TOKEN_BUCKETS if b >= tokens)
+        seqs = next(b for b in self.PORTION_SEQ_BUCKETS if b >= len(entries))
         wanted = sum(len(e.want) for e in entries)
-        rows = self.PORTION_SEQS if wanted <= self.PORTION_SEQS else bucket  # one row per request, or any rows
+        rows = seqs if wanted <= seqs else max(seqs, bucket)  # one row per request, or any rows
         tier = 1024
         while tier < longest:
             tier *= 2
         tier = min(tier, self.graph_max_ctx)
         singles = any(len(e.tokens) == 1 for e in entries)
-        return bucket, self.PORTION_SEQS, rows, tier, singles
+        return bucket, seqs, rows, tier, singles
 
     def _step_with_portion_graph(self, entries: list[StepEntry], key: tuple) -> torch.Tensor | None:
         reqs = self.builder.requests_of(entries)

@@ -2,8 +2,7 @@
 that they do, that what they compute is what the uncaptured step computes (both against the plain
 implementation), whatever the step holds (one prompt, several, portions deep in a context, single tokens
 beside portions, logits wanted at every place or at one per request), and that steps which are too long,
-hold too many requests, run in float32 or through parts that do not declare themselves safe stay
-uncaptured."""
+run in float32 or through parts that do not declare themselves safe stay uncaptured."""
 
 import pytest
 import torch
@@ -73,12 +72,12 @@ def test_short_steps_with_portions_replay_captured_graphs(name, sharp_dirs):
     assert runner.portion_graph_steps == 4
     keys = set(runner.portion_graphs)
     assert {k[4] for k in keys} == {False, True}, keys                # captured with and without single tokens beside the portions
-    assert {k[2] for k in keys} == {runner.PORTION_SEQS, 256, 128}, keys   # rows: one per request, or every place of the bucket
+    assert {k[2] for k in keys} == {8, 192, 128}, keys                # rows: one per request, or every place of the bucket
     run.step({"e": toks["e"][:1100]}, want_all=False)                 # too long for the largest bucket
     run.step({"e": toks["e"][1100:]}, want_all=False)                 # short again, at a context beyond 1,024: the next tier
     assert runner.portion_graph_steps == 5 and any(k[3] == 2048 for k in runner.portion_graphs)
-    run.step({f"m{i}": toks[f"m{i}"] for i in range(9)})              # more requests than a captured step holds
-    assert runner.portion_graph_steps == 5
+    run.step({f"m{i}": toks[f"m{i}"] for i in range(9)})              # more requests than the small bucket holds: the next one
+    assert runner.portion_graph_steps == 6 and any(k[1] == 64 for k in runner.portion_graphs)
     for rid in ("a", "b", "c", "d", "e", "m0", "m8"):
         places, got = run.of(rid)
         exact = plain.all_position_logits(config, weights, toks[rid])
