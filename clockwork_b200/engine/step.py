@@ -615,24 +615,40 @@ class ModelRunner:
         self.steps_run += 1
         return logits
 
-    # A step with prompt portions replays a captured graph when it is short enough to be bound by the
-    # host's launches: at most PORTION_TOKEN_BUCKETS[-1] tokens of at most PORTION_SEQ_BUCKETS[-1] requests.
+    # A step with prompt portions replays a captured graph: always when it is short enough to be bound by
+    # the host's launches (up to PORTION_TOKEN_BUCKETS[-1] tokens, padded to the next bucket), and up to
+    # PORTION_MAX_TOKENS when a multiple of PORTION_LONG_STEP tokens is at most PORTION_LONG_WASTE above its
+    # size (the gaps between launches cost a long step about 5 %; more padding than that would cost more).
     PORTION_TOKEN_BUCKETS = (128, 192, 256, 384, 512, 768, 1024)
+    PORTION_MAX_TOKENS = 4096
+    PORTION_LONG_STEP = 256
+    PORTION_LONG_WASTE = 0.04
     PORTION_SEQ_BUCKETS = (8, 64)
+    PORTION_MAX_LOGITS = 1 << 28  # float32 logits that a captured step may keep (1 GiB)
+
+    def _portion_token_bucket(self, tokens: int) -> int | None:
+        if tokens <= self.PORTION_TOKEN_BUCKETS[-1]:
+            return next(b for b in self.PORTION_TOKEN_BUCKETS if b >= tokens)
+        bucket = -(-tokens // self.PORTION_LONG_STEP) * self.PORTION_LONG_STEP
+        if bucket <= self.PORTION_MAX_TOKENS and bucket <= tokens * (1 + self.PORTION_LONG_WASTE):
+            return bucket
+        return None
 
     def _portion_graph_key(self, entries: list[StepEntry]) -> tuple | None:
         if not self.portions_captured or len(entries) > self.PORTION_SEQ_BUCKETS[-1]:
             return None
         tokens = sum(len(e.tokens) for e in entries)
-        if tokens > self.PORTION_TOKEN_BUCKETS[-1] or tokens == len(entries):  # (all single tokens: the decode graphs' steps)
+        bucket = self._portion_token_bucket(tokens)
+        if bucket is None or tokens == len(entries):  # (all single tokens: the decode graphs' steps)
             return None
         longest = max(self.cache.get(e.request_id).num_computed + len(e.tokens) for e in entries)
         if longest > self.graph_max_ctx:
             return None
-        bucket = next(b for b in self.PORTION_TOKEN_BUCKETS if b >= tokens)
         seqs = next(b for b in self.PORTION_SEQ_BUCKETS if b >= len(entries))
         wanted = sum(len(e.want) for e in entries)
         rows = seqs if wanted <= seqs else max(seqs, bucket)  # one row per request, or any rows
+        if rows * self.model.spec.vocab_size > self.PORTION_MAX_LOGITS:
+            return None  # (logits at many places of a long step: the graph would hold gigabytes for them)
         tier = 1024
         while tier < longest:
             tier *= 2

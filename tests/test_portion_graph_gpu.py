@@ -1,8 +1,8 @@
 """Short steps that hold prompt portions replay captured CUDA graphs (``engine/step.py:PortionGraph``):
 that they do, that what they compute is what the uncaptured step computes (both against the plain
 implementation), whatever the step holds (one prompt, several, portions deep in a context, single tokens
-beside portions, logits wanted at every place or at one per request), and that steps which are too long,
-run in float32 or through parts that do not declare themselves safe stay uncaptured."""
+beside portions, logits wanted at every place or at one per request), and that long steps which would need
+much padding, steps in float32 and steps through parts that do not declare themselves safe stay uncaptured."""
 
 import pytest
 import torch
@@ -61,7 +61,7 @@ def test_short_steps_with_portions_replay_captured_graphs(name, sharp_dirs):
     _eng, runner, cache = runner_for(folder, name, "bfloat16")
     assert runner.portions_captured
     toks = {rid: tokens_for(name, n, salt=40 + i) for i, (rid, n) in enumerate(
-        {"a": 150, "b": 90, "c": 61, "d": 300, "e": 1200, **{f"m{i}": 20 + i for i in range(9)}}.items())}
+        {"a": 150, "b": 90, "c": 61, "d": 300, "e": 1200, "f": 2040, **{f"m{i}": 20 + i for i in range(9)}}.items())}
     run = Replayed(runner, cache)
     run.step({"a": toks["a"]})                                        # one prompt, logits everywhere
     assert runner.portion_graph_steps == 1
@@ -73,12 +73,14 @@ def test_short_steps_with_portions_replay_captured_graphs(name, sharp_dirs):
     keys = set(runner.portion_graphs)
     assert {k[4] for k in keys} == {False, True}, keys                # captured with and without single tokens beside the portions
     assert {k[2] for k in keys} == {8, 192, 128}, keys                # rows: one per request, or every place of the bucket
-    run.step({"e": toks["e"][:1100]}, want_all=False)                 # too long for the largest bucket
+    run.step({"e": toks["e"][:1100]}, want_all=False)                 # a long step far from a multiple of 256 tokens: not padded
     run.step({"e": toks["e"][1100:]}, want_all=False)                 # short again, at a context beyond 1,024: the next tier
     assert runner.portion_graph_steps == 5 and any(k[3] == 2048 for k in runner.portion_graphs)
     run.step({f"m{i}": toks[f"m{i}"] for i in range(9)})              # more requests than the small bucket holds: the next one
     assert runner.portion_graph_steps == 6 and any(k[1] == 64 for k in runner.portion_graphs)
-    for rid in ("a", "b", "c", "d", "e", "m0", "m8"):
+    run.step({"f": toks["f"]}, want_all=False)                        # a long step just below a multiple of 256 tokens
+    assert runner.portion_graph_steps == 7 and any(k[0] == 2048 for k in runner.portion_graphs)
+    for rid in ("a", "b", "c", "d", "e", "f", "m0", "m8"):
         places, got = run.of(rid)
         exact = plain.all_position_logits(config, weights, toks[rid])
         rounded = plain.all_position_logits(config, weights, toks[rid], rnd=plain.to_bfloat16_and_back)
