@@ -706,14 +706,16 @@ struct Plan {
 
 // Token-tile width for CTA pairs: per k-block a pair-tile costs about max(2 bn, 256 + bn) cycles (MMA
 // time, shared-memory traffic) and the pairs run ceil(tiles / pairs) rounds.
-static int balanced_bn_pair(int T, int N, int sm_count) {
+static int balanced_bn_pair(int T, int N, int sm_count, bool swiglu = false) {
     const int m_tiles = (N + 2 * BM - 1) / (2 * BM), pairs = sm_count / 2;
     long long best_cost = -1;
-    int best = 256;
-    for (int bn = 256; bn >= 64; bn -= 16) {
+    const int cap = swiglu ? 128 : 256;  // (SwiGLU: two accumulators per tile, two weight tiles per k-block)
+    int best = cap;
+    for (int bn = cap; bn >= 64; bn -= 16) {
         const long long tiles = (long long)m_tiles * ((T + bn - 1) / bn);
         const long long rounds = (tiles + pairs - 1) / pairs;
-        const long long cost = rounds * (2 * bn > 256 + bn ? 2 * bn : 256 + bn);
+        const long long cost = swiglu ? rounds * (4 * bn > 512 + bn ? 4 * bn : 512 + bn)
+                                      : rounds * (2 * bn > 256 + bn ? 2 * bn : 256 + bn);
         if (best_cost < 0 || cost < best_cost) {
             best_cost = cost;
             best = bn;
@@ -743,6 +745,11 @@ static int balanced_bn(int T, int N, bool swiglu, int sm_count) {
 }
 
 static int g_pair_enabled = 1;
+static int g_pair_swiglu = 0;
+// Whether the SwiGLU product of prompt portions runs on CTA pairs too.  Off: measured equal to the
+// single-CTA persistent kernel within 2 % from 256 to 4,096 tokens (under the power cap the product's
+// rate is a matter of energy per FLOP, not of shared-memory traffic per tile).
+extern "C" int cw_gemm_tc_set_pair_swiglu(int on) { g_pair_swiglu = on ? 1 : 0; return CW_OK; }
 static int g_forced_bn = 0;
 static int* g_split_flags = nullptr;  // device words for the CTA-pair kernel's split products (zero between launches)
 static int g_split_flags_n = 0;
@@ -811,14 +818,14 @@ static Plan make_plan(int T, int N, int K, bool swiglu, int sm_count, bool c_by_
     // (token tiles of the one-tile-per-CTA kernel are at most 128 wide: wider ones cannot be split over K,
     // and a product of a few hundred tokens has too few tiles to do without)
     pl.bn = T <= 16 ? 16 : (T <= 32 ? 32 : (T <= 64 ? 64 : 128));
-    pl.pair = pl.persistent && !swiglu && sm_count >= 2 && g_pair_enabled;
+    pl.pair = pl.persistent && (!swiglu || g_pair_swiglu) && sm_count >= 2 && g_pair_enabled;
     // Few tokens against so many weight tiles that one CTA per tile would run in three rounds or more
     // (the logits product): one CTA per SM walks the tiles instead, its loads running on into the
     // next tile while the epilogue of the last one drains, and no round is left part-filled.
     pl.stream = !pl.persistent && !swiglu && T <= 64 && sm_count > 0 && c_by_tma &&
                 (long long)((N + BM - 1) / BM) >= 3LL * sm_count && g_stream_enabled;
     if (pl.stream) pl.persistent = true;
-    if (pl.persistent && !pl.stream) pl.bn = pl.pair ? balanced_bn_pair(T, N, sm_count) : balanced_bn(T, N, swiglu, sm_count);
+    if (pl.persistent && !pl.stream) pl.bn = pl.pair ? balanced_bn_pair(T, N, sm_count, swiglu) : balanced_bn(T, N, swiglu, sm_count);
     if (pl.persistent && !pl.stream && g_forced_bn != 0 && (!swiglu || g_forced_bn <= 128)) pl.bn = g_forced_bn;
     pl.tiles = pl.pair ? ((N + 2 * BM - 1) / (2 * BM)) * ((T + pl.bn - 1) / pl.bn) : ((N + BM - 1) / BM) * ((T + pl.bn - 1) / pl.bn);
     const int num_kb = (K + BK - 1) / BK;
@@ -863,6 +870,19 @@ static int launch(const CUtensorMap& mw, const CUtensorMap& mw2, const CUtensorM
         configured = true;
     }
     return cw_launch(gemm_tc_kernel<BN, SWIGLU>, grid, dim3(THREADS), C::SMEM_BYTES, stream, grid.z, mw, mw2, mx, mc, p);
+}
+
+template <bool SWIGLU>
+static int launch_pair(const CUtensorMap& mw, const CUtensorMap& mw2, const CUtensorMap& mx, const CUtensorMap& mc,
+                       const GemmParams& p, int pairs, cudaStream_t stream) {
+    using C = PairCfgT<SWIGLU>;
+    static bool configured = false;
+    if (!configured) {
+        if (cudaFuncSetAttribute(gemm_tc_pair_kernel<SWIGLU>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES) != cudaSuccess)
+            return (int)cudaGetLastError();
+        configured = true;
+    }
+    return cw_launch(gemm_tc_pair_kernel<SWIGLU>, dim3(2 * pairs), dim3(PAIR_THREADS), C::SMEM_BYTES, stream, 1, mw, mw2, mx, mc, p);
 }
 
 template <int BN, bool SWIGLU>
@@ -954,16 +974,9 @@ extern "C" int cw_gemm_tc_norm(const void* X, const void* W, const void* W2, con
     dim3 grid((N + BM - 1) / BM, (T + pl.bn - 1) / pl.bn, pl.splits);
     if (grid.y > 65535) return CW_ERR_BAD_SIZE;
     if (pl.pair) {
-        static bool configured = false;
-        if (!configured) {
-            if (cudaFuncSetAttribute(gemm_tc_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PairCfg::SMEM_BYTES) !=
-                cudaSuccess)
-                return (int)cudaGetLastError();
-            configured = true;
-        }
         const int units = pl.tiles * pl.splits;
         const int pairs = units < sm_count / 2 ? units : sm_count / 2;
-        return cw_launch(gemm_tc_pair_kernel, dim3(2 * pairs), dim3(PAIR_THREADS), PairCfg::SMEM_BYTES, stream, 1, mw, mx, mc, p);
+        return swiglu ? launch_pair<true>(mw, mw2, mx, mc, p, pairs, stream) : launch_pair<false>(mw, mw2, mx, mc, p, pairs, stream);
     }
     if (persistent) {
         const int ctas = pl.tiles < sm_count ? pl.tiles : sm_count;

@@ -31,17 +31,23 @@
 #define PAIR_CHUNK 16            // tokens per epilogue store
 #define PAIR_MAX_SMEM (227 * 1024)
 
-struct PairCfg {
-    static constexpr int BN_MAX = 256;                           // BM = 128 and BK = 64 as in the single-CTA kernels
-    static constexpr int A_BYTES = BM * BK * 2;                  // this CTA's 128 rows of W
+// SWIGLU: two weight matrices (gate and up) against the same token tile, two accumulators per tile, and
+// silu(gate) * up in the epilogue; token tiles are then at most 128 wide (tensor memory holds two
+// buffers of two accumulators).
+template <bool SWIGLU>
+struct PairCfgT {
+    static constexpr int BN_MAX = SWIGLU ? 128 : 256;            // BM = 128 and BK = 64 as in the single-CTA kernels
+    static constexpr int ACC_STRIDE = 256;                       // tensor-memory columns per buffer (SWIGLU: gate at 0, up at 128)
+    static constexpr int A_BYTES = BM * BK * 2;                  // this CTA's 128 rows of W (of each W)
     static constexpr int B_BYTES = (BN_MAX / 2) * BK * 2;        // its half of the token tile
-    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    static constexpr int STAGE_BYTES = (SWIGLU ? 2 : 1) * A_BYTES + B_BYTES;
     static constexpr int OUT_BYTES = 2 * PAIR_CHUNK * BM * 4;    // two staging buffers of [16 tokens][128 features]
     static constexpr int STAGES = (PAIR_MAX_SMEM - 2048 - OUT_BYTES) / STAGE_BYTES;
     static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + OUT_BYTES + 1024 + 1024;
-    static constexpr int TMEM_COLS = 512;                        // two accumulators of up to 256 columns
+    static constexpr int TMEM_COLS = 512;                        // two buffers of up to 256 columns
     static_assert(STAGES >= 4, "too few operand stages");
 };
+using PairCfg = PairCfgT<false>;
 
 __device__ __forceinline__ void tmem_alloc_pair(uint32_t result_slot, uint32_t cols) {
     asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(result_slot), "r"(cols) : "memory");
@@ -82,10 +88,12 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar) {
 
 // Tiles: 256 features x p.bn tokens per pair; p.bn is a multiple of 16 (each CTA holds p.bn / 2 token
 // rows, whole swizzle atoms of 8).  map_x's box is p.bn / 2 rows, map_c's box [16 tokens][128 features].
+template <bool SWIGLU>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1)
-gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
-                    const __grid_constant__ CUtensorMap map_c, const GemmParams p) {
-    using C = PairCfg;
+gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_w2,
+                    const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_c, const GemmParams p) {
+    using C = PairCfgT<SWIGLU>;
+    constexpr int B_OFF = (SWIGLU ? 2 : 1) * C::A_BYTES;  // the token rows' place in a stage
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t* out_s = smem + C::STAGES * C::STAGE_BYTES;
@@ -129,7 +137,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
 
     if (warp == 0 && lane == 0) {
         // ---- TMA producer (both CTAs): own rows of W, own half of the token tile ------------------------
-        const uint32_t stage_tx = C::A_BYTES + half_bn * BK * 2;
+        const uint32_t stage_tx = B_OFF + half_bn * BK * 2;
         const int my_tiles = pair < tiles ? (tiles - pair + pairs - 1) / pairs : 0;
         const int total = my_tiles * nkb;  // k-blocks of all this pair's units, in order
         const int early = min(total, C::STAGES);
@@ -148,8 +156,9 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                 if (phase == 0) {
                     mbar_expect_tx_cluster(bar, stage_tx);
                     tma_load_2d_pair(a_dst, &map_w, kb * BK, m0, bar);
+                    if (SWIGLU) tma_load_2d_pair(a_dst + C::A_BYTES, &map_w2, kb * BK, m0, bar);
                 } else {
-                    tma_load_2d_pair(a_dst + C::A_BYTES, &map_x, kb * BK, n0, bar);
+                    tma_load_2d_pair(a_dst + B_OFF, &map_x, kb * BK, n0, bar);
                 }
             }
         }
@@ -167,7 +176,8 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                 const uint32_t bar = dsmem_addr(full0 + 8 * s, 0);  // the leader's barrier
                 mbar_expect_tx_cluster(bar, stage_tx);
                 tma_load_2d_pair(a_dst, &map_w, (kb0 + kb) * BK, m0, bar);
-                tma_load_2d_pair(a_dst + C::A_BYTES, &map_x, (kb0 + kb) * BK, n0, bar);
+                if (SWIGLU) tma_load_2d_pair(a_dst + C::A_BYTES, &map_w2, (kb0 + kb) * BK, m0, bar);
+                tma_load_2d_pair(a_dst + B_OFF, &map_x, (kb0 + kb) * BK, n0, bar);
             }
         }
         if (*give_up) {
@@ -188,7 +198,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             ok = mbar_wait(acce0 + 8 * buf, ((it >> 1) & 1) ^ 1, give_up);  // both epilogues have drained it
             if (!ok) break;
             tc_fence_after();
-            const uint32_t acc = tmem_base + buf * C::BN_MAX;
+            const uint32_t acc = tmem_base + buf * C::ACC_STRIDE;
             for (int kb = 0; kb < nkb; ++kb, ++i) {
                 const int s = i % C::STAGES;
                 ok = mbar_wait(full0 + 8 * s, (i / C::STAGES) & 1, give_up);
@@ -196,10 +206,16 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                 tc_fence_after();
                 const uint32_t a_addr = smem_u32(smem + s * C::STAGE_BYTES);
                 const uint64_t adesc = smem_desc_sw128(a_addr);
-                const uint64_t bdesc = smem_desc_sw128(a_addr + C::A_BYTES);
+                const uint64_t bdesc = smem_desc_sw128(a_addr + B_OFF);
 #pragma unroll
                 for (int k = 0; k < BK / 16; ++k)
                     umma_bf16_pair(acc, adesc + 2 * k, bdesc + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                if (SWIGLU) {
+                    const uint64_t udesc = smem_desc_sw128(a_addr + C::A_BYTES);
+#pragma unroll
+                    for (int k = 0; k < BK / 16; ++k)
+                        umma_bf16_pair(acc + C::ACC_STRIDE / 2, udesc + 2 * k, bdesc + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                }
                 umma_commit_pair(empty0 + 8 * s);  // the stage is free in both CTAs
             }
             if (ok) umma_commit_pair(accf0 + 8 * buf);
@@ -210,7 +226,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         const int quarter = warp & 3;
         const int row = quarter * 32 + lane;
         const int etid = tid - 64;
-        const bool wide = p.epilogue != 0;
+        const bool wide = !SWIGLU && p.epilogue != 0;
         const uint32_t acce_leader = dsmem_addr(acce0, 0);
         int it = 0, chunk_no = 0;
         bool ok = true;
@@ -234,7 +250,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             }
             if (!ok) break;
             tc_fence_after();
-            const uint32_t taddr = tmem_base + buf * C::BN_MAX + ((uint32_t)(quarter * 32) << 16);
+            const uint32_t taddr = tmem_base + buf * C::ACC_STRIDE + ((uint32_t)(quarter * 32) << 16);
             const float bias = (p.bias != nullptr && f < p.N && ks == 0) ? p.bias[f] : 0.f;
             // Only chunks that hold tokens are read out and stored, and every chunk that runs commits exactly
             // one bulk group (an empty one when this CTA's features lie beyond N), so that `wait_group.read 1`
@@ -243,6 +259,12 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             for (int c = 0; c < c_end; c += PAIR_CHUNK, ++chunk_no) {
                 float g[16];
                 tmem_ld16(taddr + c, g);
+                if (SWIGLU) {
+                    float u[16];
+                    tmem_ld16(taddr + C::ACC_STRIDE / 2 + c, u);
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) g[j] = __fdividef(g[j], 1.0f + __expf(-g[j])) * u[j];
+                }
                 if (c + PAIR_CHUNK >= c_end) {
                     // the accumulator has been read out: hand the buffer back to the leader's MMA thread
                     tc_fence_before();

@@ -462,13 +462,23 @@ def test_gemm_tc_against_float64(ops, gemm_tc, t, n, k):
 
 
 @pytest.mark.parametrize("t,n,k", [(8, 8960, 1536), (33, 200, 96), (64, 1000, 1536), (700, 520, 256),
-                                   (2100, 5000, 264)])
+                                   (2100, 5000, 264), (300, 8960, 1536), (129, 130, 72)])
 def test_gemm_tc_swiglu(ops, gemm_tc, t, n, k):
+    """Above 128 tokens the product runs on CTA pairs (two weight tiles per stage, two accumulators) or,
+    switched, on the single-CTA persistent kernel: both against the formula."""
     x = rand(t, k, dtype=torch.bfloat16)
     wg, wu = rand(n, k, dtype=torch.bfloat16, scale=0.05, seed=1), rand(n, k, dtype=torch.bfloat16, scale=0.05, seed=2)
     want = torch.nn.functional.silu(bf16_product(x, wg)) * bf16_product(x, wu)
-    got = gemm_tc.gemm_swiglu(x.to(DEV), wg.to(DEV), wu.to(DEV))
-    torch.testing.assert_close(got.float().cpu(), want, rtol=1e-2, atol=1e-2 * max(1.0, float(want.abs().max())))
+    xd, gd, ud = x.to(DEV), wg.to(DEV), wu.to(DEV)
+    try:
+        for pairs in (True, False):
+            gemm_tc.set_pair_swiglu(pairs)
+            got = gemm_tc.gemm_swiglu(xd, gd, ud)
+            torch.testing.assert_close(got.float().cpu(), want, rtol=1e-2, atol=1e-2 * max(1.0, float(want.abs().max())),
+                                       msg=lambda m: f"on CTA pairs: {pairs}: {m}")
+            assert torch.equal(gemm_tc.gemm_swiglu(xd, gd, ud), got)  # twice in a row gives the same bits
+    finally:
+        gemm_tc.set_pair_swiglu(False)
     ops.raise_on_status(gemm_tc.status(DEV))
 
 
