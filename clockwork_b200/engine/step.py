@@ -625,6 +625,7 @@ class ModelRunner:
     PORTION_LONG_WASTE = 0.04
     PORTION_SEQ_BUCKETS = (8, 64)
     PORTION_MAX_LOGITS = 1 << 28  # float32 logits that a captured step may keep (1 GiB)
+    PORTION_MAX_GRAPHS = 32       # captured steps kept at a time
 
     def _portion_token_bucket(self, tokens: int) -> int | None:
         if tokens <= self.PORTION_TOKEN_BUCKETS[-1]:
@@ -658,9 +659,13 @@ class ModelRunner:
 
     def _step_with_portion_graph(self, entries: list[StepEntry], key: tuple) -> torch.Tensor | None:
         reqs = self.builder.requests_of(entries)
-        graph = self.portion_graphs.get(key)
+        graph = self.portion_graphs.pop(key, None)
         if graph is None:
-            graph = self.portion_graphs[key] = PortionGraph(self, *key)
+            # every captured step keeps its own activations: the least recently used ones make room
+            while len(self.portion_graphs) >= self.PORTION_MAX_GRAPHS:
+                del self.portion_graphs[next(iter(self.portion_graphs))]
+            graph = PortionGraph(self, *key)
+        self.portion_graphs[key] = graph  # (the dictionary's order is the order of last use)
         ctx_lens = graph.fill(self.cache, entries, reqs)
         logits = graph.launch()
         self.builder.commit(PreparedStep(None, None, None, reqs, ctx_lens))

@@ -87,6 +87,24 @@ def test_short_steps_with_portions_replay_captured_graphs(name, sharp_dirs):
         check(got, (exact[places], rounded[places]), "bfloat16", f"{name} {rid}")
 
 
+def test_captured_steps_are_kept_up_to_a_number_and_the_least_recently_used_go(sharp_dirs, monkeypatch):
+    folder = sharp_dirs["B"]
+    config, weights = plain.read_model_dir(folder)
+    _eng, runner, cache = runner_for(folder, "B", "bfloat16")
+    monkeypatch.setattr(type(runner), "PORTION_MAX_GRAPHS", 2)
+    run = Replayed(runner, cache)
+    toks = {rid: tokens_for("B", n, salt=70 + i) for i, (rid, n) in enumerate({"a": 100, "b": 180, "c": 250, "d": 120}.items())}
+    for rid in ("a", "b", "c", "d"):   # buckets 128, 192, 256, then 128 again: captured anew, 192 has gone by then
+        run.step({rid: toks[rid]})
+        assert len(runner.portion_graphs) <= 2
+    assert [k[0] for k in runner.portion_graphs] == [256, 128] and runner.portion_graph_steps == 4
+    for rid in toks:
+        places, got = run.of(rid)
+        exact = plain.all_position_logits(config, weights, toks[rid])
+        rounded = plain.all_position_logits(config, weights, toks[rid], rnd=plain.to_bfloat16_and_back)
+        check(got, (exact[places], rounded[places]), "bfloat16", f"B {rid}")
+
+
 def test_float32_steps_and_uncaptured_engines_take_the_plain_step(sharp_dirs):
     folder = sharp_dirs["A"]
     for dtype, graphs in (("float32", True), ("bfloat16", False)):
