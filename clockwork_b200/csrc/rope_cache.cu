@@ -20,20 +20,19 @@ __global__ void rope_store_kernel(T* __restrict__ qkv, const int* __restrict__ p
                                   int hd, int rotary_dim, int num_slots, int write_cache,
                                   int* status) {
     extern __shared__ float cs[];  // cos[half], sin[half]
+    // Positions, slots and frequencies are inputs of the step, written before its first kernel; only the
+    // q/k/v rows come from the preceding kernel.  So the angles are worked out while that one finishes.
     pdl_launch_dependents();
-    pdl_wait();
     const int t = blockIdx.x;
     const int half = rotary_dim >> 1;
     if (inv_freq != nullptr) {
         const float pos = (float)positions[t];
-        for (int j = threadIdx.x; j < half; j += blockDim.x) {
-            const float ang = pos * inv_freq[j];
-            cs[j] = cosf(ang);
-            cs[half + j] = sinf(ang);
-        }
+        for (int j = threadIdx.x; j < half; j += blockDim.x)
+            sincosf(pos * inv_freq[j], &cs[half + j], &cs[j]);  // one argument reduction for both
     }
-    __syncthreads();
     int slot = slots ? slots[t] : -1;
+    __syncthreads();
+    pdl_wait();
     if (!write_cache) slot = -1;
     if (slot >= num_slots) {
         if (threadIdx.x == 0) cw_report(status, CW_ST_SLOT_RANGE, t, slot);
@@ -98,20 +97,19 @@ __global__ void rope_store_vec_kernel(T* __restrict__ qkv, const int* __restrict
                                       int hd, int rotary_dim, int num_slots, int write_cache, int* status) {
     constexpr int VEC = RowVec<T>::N;
     extern __shared__ float cs[];  // cos[half], sin[half]
+    // Positions, slots and frequencies are inputs of the step, written before its first kernel; only the
+    // q/k/v rows come from the preceding kernel.  So the angles are worked out while that one finishes.
     pdl_launch_dependents();
-    pdl_wait();
     const int t = blockIdx.x;
     const int half = rotary_dim >> 1;
     if (inv_freq != nullptr) {
         const float pos = (float)positions[t];
-        for (int j = threadIdx.x; j < half; j += blockDim.x) {
-            const float ang = pos * inv_freq[j];
-            cs[j] = cosf(ang);
-            cs[half + j] = sinf(ang);
-        }
+        for (int j = threadIdx.x; j < half; j += blockDim.x)
+            sincosf(pos * inv_freq[j], &cs[half + j], &cs[j]);  // one argument reduction for both
     }
-    __syncthreads();
     int slot = slots ? slots[t] : -1;
+    __syncthreads();
+    pdl_wait();
     if (!write_cache) slot = -1;
     if (slot >= num_slots) {
         if (threadIdx.x == 0) cw_report(status, CW_ST_SLOT_RANGE, t, slot);
