@@ -145,6 +145,14 @@ class LLMEngine:
         self._texts[request_id] = ""
         self.scheduler.add_seq(seq)
 
+    def capture_graphs_ahead(self, decode_batches=(1, 8), prompt_tokens=(128, 512, 2048), max_ctx: int = 1024,
+                             greedy: bool = True) -> int:
+        """Captures the CUDA graphs of the usual steps now instead of at their first use (see
+        ``ModelRunner.capture_ahead``).  Returns how many were captured; 0 when graphs are off."""
+        if not self.uses_graphs:
+            return 0
+        return self.runner.capture_ahead(decode_batches, prompt_tokens, max_ctx, greedy)
+
     def has_unfinished_requests(self) -> bool:
         return self.scheduler.has_unfinished()
 

@@ -657,6 +657,36 @@ class ModelRunner:
         singles = any(len(e.tokens) == 1 for e in entries)
         return bucket, seqs, rows, tier, singles
 
+    def capture_ahead(self, decode_batches=(), prompt_tokens=(), max_ctx: int = 1024, greedy: bool = True) -> int:
+        """Captures, before any request needs them, the graphs of single-token steps of these batch sizes
+        and of one-prompt steps of these token counts, for contexts up to ``max_ctx`` (a graph is otherwise
+        captured at its first use, a few tenths of a second that this one step pays for).  Touches no
+        request and no cache slot.  Returns the number of graphs captured."""
+        if not self.graph_max_batch:
+            return 0
+        tier = 1024
+        while tier < max_ctx:
+            tier *= 2
+        tier = min(tier, self.graph_max_ctx)
+        made = 0
+        for n in decode_batches:
+            bucket = 1
+            while bucket < n:
+                bucket *= 2
+            key = (min(bucket, max(self.graph_max_batch, n)), greedy, tier)
+            if key not in self.graphs:
+                self.graphs[key] = DecodeGraph(self, key[0], tier, greedy=greedy)
+                made += 1
+        for tokens in prompt_tokens:
+            bucket = self._portion_token_bucket(tokens) if self.portions_captured else None
+            if bucket is None:
+                continue
+            key = (bucket, self.PORTION_SEQ_BUCKETS[0], self.PORTION_SEQ_BUCKETS[0], tier, False)
+            if key not in self.portion_graphs and len(self.portion_graphs) < self.PORTION_MAX_GRAPHS:
+                self.portion_graphs[key] = PortionGraph(self, *key)
+                made += 1
+        return made
+
     def _step_with_portion_graph(self, entries: list[StepEntry], key: tuple) -> torch.Tensor | None:
         reqs = self.builder.requests_of(entries)
         graph = self.portion_graphs.pop(key, None)

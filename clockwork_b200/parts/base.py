@@ -89,8 +89,8 @@ class StepContext:
     tok_seq: torch.Tensor  # int32 [N] index of the token's request within this step (-1: padding)
     q_start: torch.Tensor  # int32 [S+1]
     ctx_lens: torch.Tensor  # int32 [S] tokens of the request that are in the cache after this step
-    q_lens_host: list[int]
-    ctx_lens_host: list[int]
+    q_lens_host: list[int]   # per request: tokens it brings / tokens in the cache after the step, on the host; the
+    ctx_lens_host: list[int]  # capture's placeholders in a captured step (empty in one that holds portions)
     max_q_len: int
     max_ctx_len: int
     views: dict[int, PagedView | StateView] = field(default_factory=dict)  # by cache layer

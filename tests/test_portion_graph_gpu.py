@@ -105,6 +105,20 @@ def test_captured_steps_are_kept_up_to_a_number_and_the_least_recently_used_go(s
         check(got, (exact[places], rounded[places]), "bfloat16", f"B {rid}")
 
 
+def test_graphs_captured_ahead_are_the_ones_the_steps_then_replay(sharp_dirs):
+    folder = sharp_dirs["A"]
+    eng, runner, cache = runner_for(folder, "A", "bfloat16")
+    made = eng.capture_graphs_ahead(decode_batches=(1, 3), prompt_tokens=(100, 300), max_ctx=1024)
+    assert made == 4 and set(runner.graphs) == {(1, True, 1024), (4, True, 1024)}
+    assert {k[0] for k in runner.portion_graphs} == {128, 384}
+    assert eng.capture_graphs_ahead(decode_batches=(1, 3), prompt_tokens=(100, 300), max_ctx=1024) == 0
+    from clockwork_b200.sampling import SamplingParams
+    prompts = [tokens_for("A", 100, salt=5), tokens_for("A", 90, salt=6), tokens_for("A", 110, salt=7)]
+    outs = eng.generate(prompts[:1], SamplingParams(max_tokens=4, ignore_eos=True))   # one prompt, then single-token steps of one
+    assert len(outs[0].token_ids) == 4 and len(runner.portion_graphs) == 2 and len(runner.graphs) == 2
+    assert runner.portion_graph_steps == 1
+
+
 def test_float32_steps_and_uncaptured_engines_take_the_plain_step(sharp_dirs):
     folder = sharp_dirs["A"]
     for dtype, graphs in (("float32", True), ("bfloat16", False)):
