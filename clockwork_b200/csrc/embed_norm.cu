@@ -177,6 +177,89 @@ extern "C" int cw_add_rmsnorm(float* resid, const void* delta, const float* weig
     return CW_ERR_BAD_DTYPE;
 }
 
+// resid[r] += parts[0][r] + parts[1][r] + .. (in this order: the splits of a product over K that were
+// kept apart), then, with `out`, out[r] = resid[r] normalised as above.  A warp per row, the row in
+// registers between the two passes.
+template <typename T, int NV>
+__global__ void __launch_bounds__(256)
+add_parts_rmsnorm_kernel(float* __restrict__ resid, const float* __restrict__ parts, int num_parts, size_t part_stride,
+                         const float* __restrict__ weight, T* __restrict__ out, int num_rows, float eps, int H) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int lane = threadIdx.x & 31;
+    const int r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (r >= num_rows) return;
+    float* x = resid + (size_t)r * H;
+    float4 v[NV];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        const int c = (i * 32 + lane) * 4;
+        if (c < H) v[i] = Vec4<float>::load(x + c);
+    }
+    for (int k = 0; k < num_parts; ++k) {
+        const float* d = parts + k * part_stride + (size_t)r * H;
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+            const int c = (i * 32 + lane) * 4;
+            if (c < H) {
+                const float4 dv = Vec4<float>::load(d + c);
+                v[i].x += dv.x; v[i].y += dv.y; v[i].z += dv.z; v[i].w += dv.w;
+            }
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        const int c = (i * 32 + lane) * 4;
+        if (c < H) {
+            Vec4<float>::store(x + c, v[i]);
+            ss = fmaf(v[i].x, v[i].x, ss); ss = fmaf(v[i].y, v[i].y, ss);
+            ss = fmaf(v[i].z, v[i].z, ss); ss = fmaf(v[i].w, v[i].w, ss);
+        }
+    }
+    if (out == nullptr) return;
+    ss = warp_sum(ss);
+    const float inv = 1.0f / sqrtf(ss / (float)H + eps);
+    T* o = out + (size_t)r * H;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        const int c = (i * 32 + lane) * 4;
+        if (c < H) {
+            const float4 w = Vec4<float>::load(weight + c);
+            Vec4<T>::store(o + c, make_float4(w.x * (v[i].x * inv), w.y * (v[i].y * inv), w.z * (v[i].z * inv), w.w * (v[i].w * inv)));
+        }
+    }
+}
+
+template <typename T>
+static int launch_add_parts(float* resid, const float* parts, int num_parts, size_t part_stride, const float* weight, T* out,
+                            int rows, int H, float eps, cudaStream_t stream) {
+    const int warps = 8;
+    const dim3 grid((rows + warps - 1) / warps), block(warps * 32);
+    const int nv = (H + 127) / 128;
+#define CW_NV(n) \
+    if (nv <= n) return cw_launch(add_parts_rmsnorm_kernel<T, n>, grid, block, 0, stream, 1, resid, parts, num_parts, part_stride, weight, out, rows, eps, H);
+    CW_NV(4) CW_NV(8) CW_NV(12) CW_NV(16) CW_NV(24) CW_NV(32)
+#undef CW_NV
+    return CW_ERR_UNSUPPORTED;
+}
+
+// parts: float32 [num_parts][part_rows][H] (part_rows >= rows); out null: only the sum.  H a multiple of 4,
+// at most 4096; 16-byte aligned pointers; CW_ERR_UNSUPPORTED otherwise.
+extern "C" int cw_add_parts_rmsnorm(float* resid, const float* parts, int num_parts, int part_rows, const float* weight,
+                                    void* out, int rows, int H, float eps, int dtype, cudaStream_t stream) {
+    if (rows == 0) return CW_OK;
+    if (rows < 0 || H <= 0 || num_parts < 1 || part_rows < rows) return CW_ERR_BAD_SIZE;
+    if (H % 4 != 0 || H > 4096 || ((uintptr_t)resid & 15) || ((uintptr_t)parts & 15) || ((uintptr_t)weight & 15) ||
+        ((uintptr_t)out & 15))
+        return CW_ERR_UNSUPPORTED;
+    const size_t stride = (size_t)part_rows * H;
+    if (out == nullptr || dtype == 0)
+        return launch_add_parts<float>(resid, parts, num_parts, stride, weight, (float*)out, rows, H, eps, stream);
+    if (dtype == 1) return launch_add_parts<bf16>(resid, parts, num_parts, stride, weight, (bf16*)out, rows, H, eps, stream);
+    return CW_ERR_BAD_DTYPE;
+}
+
 // out = silu(gate) * up, gate and up being the two halves of each row of `gate_up` [N, 2*I]
 // (clockwork/engine/model.py:62-63).  Used where the product is not fused into the GEMM.
 template <typename T>

@@ -43,7 +43,9 @@
 struct GemmParams {
     int T, N, K;          // tokens, output features, inner size
     int ldc;              // row stride of C in elements
-    int epilogue;         // 0 bf16 store, 1 float32 add, 2 float32 store (ignored for SWIGLU)
+    int epilogue;         // 0 bf16 store, 1 float32 add, 2 float32 store (ignored for SWIGLU);
+                          // 3 (CTA-pair kernel): float32 store of split ks at rows ks * part_rows .. of C
+    int part_rows;        // epilogue 3: rows per split in C (the token count rounded up to the store's 16 rows)
     int num_kb;           // ceil(K / 64)
     int kb_per_split;     // k-blocks per blockIdx.z
     int splits;
@@ -792,6 +794,37 @@ static int balanced_bn_pair_split(int T, int N, int num_kb, int sm_count) {
     }
     return best;
 }
+// A product whose splits over K are kept apart (epilogue 3): every split stores its partial tile in a
+// slab of its own and whoever reads the result next adds the slabs, in split order (the RMSNorm that
+// follows a product into the residual reads the residual anyway).  Nothing takes turns, so splits may
+// outnumber the pairs and run in rounds.  Cost as measured for the CTA-pair kernel: a k-block about
+// 330 + 0.2 bn ns, a tile's store 1000 + 25 bn ns once, and each further slab costs its reader about
+// T N / 500 ns (its bytes, written and read again).
+// Measured in the step (Qwen2.5-1.5B sizes, K = 8,960): 15 % of a 256-token prompt's time, 10 % at 512, 4 % at
+// 1,024; from 1,056 tokens on the slabs cost what the splits save (a mixed step of 1,056 tokens 5 % slower),
+// so longer products add into their output with splits that take turns, as before.
+#define PARTS_MAX_TOKENS 1024
+static void parts_plan(int T, int N, int K, int sm_count, int* splits_out, int* bn_out) {
+    const int m_tiles = (N + 2 * BM - 1) / (2 * BM), pairs = sm_count / 2, num_kb = (K + BK - 1) / BK;
+    long long best_cost = -1;
+    int best_d = 1, best_bn = 256;
+    for (int bn = 256; bn >= 64; bn -= 16) {
+        const int tiles = m_tiles * ((T + bn - 1) / bn);
+        for (int d = 1; d <= 8; ++d) {
+            if (num_kb % d != 0 || (d > 1 && num_kb / d < 8)) continue;
+            const long long rounds = ((long long)tiles * d + pairs - 1) / pairs;
+            const long long cost = rounds * (num_kb / d) * (330 + bn / 5) + 1000 + 25 * bn + (long long)(d - 1) * T * N / 500;
+            if (best_cost < 0 || cost < best_cost) {
+                best_cost = cost;
+                best_d = d;
+                best_bn = bn;
+            }
+        }
+    }
+    *splits_out = best_d;
+    *bn_out = best_bn;
+}
+
 // Forces the token-tile width of the prompt-portion kernels (0: chosen automatically); for measurements.
 extern "C" int cw_gemm_tc_set_tile(int bn) {
     if (bn != 0 && (bn < 64 || bn > 256 || bn % 16 != 0)) return CW_ERR_BAD_SIZE;
@@ -998,6 +1031,47 @@ extern "C" int cw_gemm_tc_norm(const void* X, const void* W, const void* W2, con
     }
 #undef CW_CASE
     return CW_ERR_UNSUPPORTED;
+}
+
+// How cw_gemm_tc_parts would split a product over K (1: not worth it, or too few tokens for the CTA-pair kernel).
+extern "C" int cw_gemm_tc_parts_plan(int T, int N, int K, int sm_count, int* splits) {
+    int bn = 0;
+    *splits = 1;
+    if (T <= 128 || T > PARTS_MAX_TOKENS || sm_count < 2 || !g_pair_enabled || T < g_persistent_from) return CW_OK;
+    parts_plan(T, N, K, sm_count, splits, &bn);
+    return CW_OK;
+}
+
+// parts[ks][t][n] = the part of X W^T that split ks of K contributes (float32, [splits][part_rows][N],
+// part_rows >= T a multiple of 16; rows from T on are written too, with what the tile's last store
+// holds).  `splits` as cw_gemm_tc_parts_plan gave it.
+extern "C" int cw_gemm_tc_parts(const void* X, const void* W, float* parts, int T, int N, int K, int ldx, int part_rows,
+                                int splits, int sm_count, int* status, cudaStream_t stream) {
+    if (T == 0 || N == 0) return CW_OK;
+    if (T < 0 || N < 0 || K <= 0 || ldx < K || part_rows < T || part_rows % P_CHUNK != 0) return CW_ERR_BAD_SIZE;
+    if (K % 8 != 0 || ldx % 8 != 0 || N % 4 != 0 || ((uintptr_t)X & 15) || ((uintptr_t)W & 15) || ((uintptr_t)parts & 15))
+        return CW_ERR_UNSUPPORTED;
+    if (load_encode() != 0) return CW_ERR_UNSUPPORTED;
+    int want = 1, bn = 0;
+    if (T <= 128 || T > PARTS_MAX_TOKENS || sm_count < 2 || !g_pair_enabled || T < g_persistent_from) return CW_ERR_UNSUPPORTED;
+    parts_plan(T, N, K, sm_count, &want, &bn);
+    if (splits != want || splits < 1) return CW_ERR_BAD_SIZE;
+    if (g_forced_bn != 0) bn = g_forced_bn;
+    const int num_kb = (K + BK - 1) / BK;
+    CUtensorMap mw, mx, mc;
+    if (make_map(&mw, W, N, K, K, BM) != 0) return CW_ERR_UNSUPPORTED;
+    if (make_map(&mx, X, T, K, ldx, bn / 2) != 0) return CW_ERR_UNSUPPORTED;
+    if (make_map_c(&mc, parts, splits * part_rows, N, N, P_CHUNK, true) != 0) return CW_ERR_UNSUPPORTED;
+    GemmParams p = {};
+    p.tma_store = 1;
+    p.T = T; p.N = N; p.K = K; p.ldc = N; p.epilogue = 3; p.part_rows = part_rows;
+    p.num_kb = num_kb; p.kb_per_split = num_kb / splits; p.splits = splits;
+    p.bias = nullptr; p.C = parts; p.status = status; p.bn = bn;
+    p.split_flags = nullptr;
+    const int tiles = ((N + 2 * BM - 1) / (2 * BM)) * ((T + bn - 1) / bn);
+    const int units = tiles * splits;
+    const int pairs = units < sm_count / 2 ? units : sm_count / 2;
+    return launch_pair<false>(mw, mw, mx, mc, p, pairs, stream);
 }
 
 CW_TRACE_TU(gemm_tc)

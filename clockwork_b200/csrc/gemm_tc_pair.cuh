@@ -236,7 +236,11 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             const int m0 = (tile % m_tiles) * 2 * BM + (int)rank * BM;
             const int n0 = (tile / m_tiles) * bn;
             const int f = m0 + row;
-            bool my_turn = ks == 0;  // (a split's stores come after those of the split before it)
+            // (a split's adds come after those of the split before it; splits that are kept apart, epilogue
+            // 3, store into slabs of their own and wait for nobody)
+            const bool apart = p.epilogue == 3;
+            bool my_turn = ks == 0 || apart;
+            const int y0 = (apart ? ks * p.part_rows : 0) + n0;  // the tile's first row in C
             ok = mbar_wait(accf0 + 8 * buf, (it >> 1) & 1, give_up);
             {
                 // one decision for all 128 threads: they meet at named barriers below
@@ -299,15 +303,15 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                     if (m0 < p.N) {
                         if (p.epilogue == 1)
                             asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.bulk_group [%0, {%2, %3}], [%1];"
-                                         ::"l"(&map_c), "r"(smem_u32(st32)), "r"(m0), "r"(n0 + c) : "memory");
+                                         ::"l"(&map_c), "r"(smem_u32(st32)), "r"(m0), "r"(y0 + c) : "memory");
                         else
                             asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
-                                         ::"l"(&map_c), "r"(smem_u32(st32)), "r"(m0), "r"(n0 + c) : "memory");
+                                         ::"l"(&map_c), "r"(smem_u32(st32)), "r"(m0), "r"(y0 + c) : "memory");
                     }
                     asm volatile("cp.async.bulk.commit_group;" ::: "memory");
                 }
             }
-            if (splits > 1 && etid == 0) {
+            if (splits > 1 && !apart && etid == 0) {
                 // this split's adds are complete: the next split of the tile may add (the last one leaves
                 // the flag at zero for the next launch)
                 asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");

@@ -111,14 +111,42 @@ def embed(table: torch.Tensor, ids: torch.Tensor, status: torch.Tensor, serial: 
     return out
 
 
-def add_rmsnorm(resid: torch.Tensor, delta: torch.Tensor | None, weight: torch.Tensor, eps: float,
+class PartialSums:
+    """A product that was split over its inner dimension with the splits kept apart: ``slabs`` float32
+    [splits, slab_rows, N], of which rows [0, rows) of every slab count; the product is their sum, taken
+    in slab order by whoever adds it to the residual (``add_rmsnorm``, ``add_to_residual``)."""
+
+    __slots__ = ("slabs", "rows")
+
+    def __init__(self, slabs: torch.Tensor, rows: int) -> None:
+        self.slabs, self.rows = slabs, rows
+
+
+def _add_partial_sums(resid: torch.Tensor, parts: PartialSums, weight: torch.Tensor | None, eps: float,
+                      out: torch.Tensor | None) -> None:
+    _need(parts.slabs, torch.float32, "partial sums", 3)
+    n, h = resid.shape
+    splits, slab_rows, width = parts.slabs.shape
+    if width != h or parts.rows != n or slab_rows < n:
+        raise ValueError(f"partial sums {tuple(parts.slabs.shape)} of {parts.rows} rows do not match residual {tuple(resid.shape)}")
+    check(library().cw_add_parts_rmsnorm(_ptr(resid), _ptr(parts.slabs), splits, slab_rows, _ptr(weight), _ptr(out), n, h,
+                                         float(eps), 0 if out is None else dtype_code(out.dtype), _stream()), "add_parts_rmsnorm")
+
+
+def add_rmsnorm(resid: torch.Tensor, delta, weight: torch.Tensor, eps: float,
                 out_dtype: torch.dtype, status: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
-    """``resid += delta`` (if given), then returns ``weight * rmsnorm(resid)`` as ``out_dtype``."""
+    """``resid += delta`` (if given: a tensor, or the ``PartialSums`` of a product), then returns
+    ``weight * rmsnorm(resid)`` as ``out_dtype``."""
     _need(resid, torch.float32, "resid", 2)
     _need(weight, torch.float32, "weight", 1)
     n, h = resid.shape
     if weight.shape[0] != h:
         raise ValueError(f"norm weight has {weight.shape[0]} elements, rows have {h}")
+    if isinstance(delta, PartialSums):
+        if out is None:
+            out = torch.empty((n, h), dtype=out_dtype, device=resid.device)
+        _add_partial_sums(resid, delta, weight, eps, out)
+        return out
     if delta is not None:
         _need(delta, out_dtype, "delta", 2)
         if delta.shape != resid.shape:
@@ -154,8 +182,11 @@ def silu_mul(gate_up: torch.Tensor) -> torch.Tensor:
     return out
 
 
-def add_to_residual(resid: torch.Tensor, delta: torch.Tensor) -> None:
+def add_to_residual(resid: torch.Tensor, delta) -> None:
     _need(resid, torch.float32, "resid", 2)
+    if isinstance(delta, PartialSums):
+        _add_partial_sums(resid, delta, None, 0.0, None)
+        return
     _need(delta, None, "delta", 2)
     if delta.shape != resid.shape:
         raise ValueError("delta and residual shapes differ")

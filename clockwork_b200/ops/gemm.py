@@ -83,6 +83,20 @@ def linear_add_into(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None,
     return None
 
 
+def linear_partial_sums(x: torch.Tensor, w: torch.Tensor):
+    """x W^T as ``ops.PartialSums`` when the product is one whose inner dimension is worth splitting with
+    the splits kept apart (a few hundred tokens against a long K: few tiles, and splits that add into
+    the residual one after the other would take turns), else None.  The width must suit the kernel
+    that adds the slabs up (a multiple of 4, at most 4096)."""
+    n = w.shape[0]
+    if not _use_tc(x, w) or n % 4 or n > 4096 or x.stride(1) != 1:
+        return None
+    splits = _tc.partial_sums_splits(x.shape[0], n, x.shape[1], x.device)
+    if splits <= 1:
+        return None
+    return _tc.gemm_partial_sums(x, w, splits)
+
+
 def linear_f32(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None) -> torch.Tensor:
     if _use_tc(x, w):
         return _tc.gemm(x, w, bias, epilogue=EPILOGUE_STORE_F32)

@@ -31,6 +31,10 @@ def _configure() -> None:
     lib.cw_gemm_tc_norm.restype = c_int
     lib.cw_gemm_tc_plan.argtypes = [I, I, I, I, I, POINTER(c_int), POINTER(c_int), POINTER(c_int)]
     lib.cw_gemm_tc_plan.restype = c_int
+    lib.cw_gemm_tc_parts_plan.argtypes = [I, I, I, I, POINTER(c_int)]
+    lib.cw_gemm_tc_parts_plan.restype = c_int
+    lib.cw_gemm_tc_parts.argtypes = [P, P, P, I, I, I, I, I, I, I, P, P]
+    lib.cw_gemm_tc_parts.restype = c_int
     lib.cw_gemm_tc_set_persistent_from.argtypes = [I]
     lib.cw_gemm_tc_set_persistent_from.restype = c_int
     lib.cw_gemm_tc_set_pair_swiglu.argtypes = [I]
@@ -158,6 +162,33 @@ def _run(x, w, w2, bias, out, epilogue, row_scale=None, emit=None) -> None:
         _ptr(x), _ptr(w), _ptr(w2), _ptr(bias), _ptr(out), t, n, k, ldx, out.stride(0), epilogue, st["sms"],
         _ptr(parts), 0 if parts is None else parts.shape[1], float(eps), int(dim), _ptr(g), _ptr(ex), _ptr(ep),
         _ptr(st["status"]), _stream()), "gemm_tc_norm")
+
+
+def partial_sums_splits(t: int, n: int, k: int, device) -> int:
+    """Into how many slabs ``gemm_partial_sums`` would split a product of these sizes over K: 1 when
+    splitting does not pay (many tiles already, a short inner dimension, or too few tokens for the
+    CTA-pair kernel), and then the product is better added into its output directly."""
+    _configure()
+    splits = c_int(1)
+    check(library().cw_gemm_tc_parts_plan(t, n, k, _device_state(torch.device(device))["sms"], byref(splits)), "gemm_tc_parts_plan")
+    return splits.value
+
+
+def gemm_partial_sums(x: torch.Tensor, w: torch.Tensor, splits: int):
+    """``x [T,K] @ w[N,K]^T`` as ``splits`` float32 slabs whose sum, in slab order, is the product
+    (``ops.PartialSums``): every split of K stores its part at once, nothing takes turns, and the
+    kernel that reads the result next adds the slabs up."""
+    from . import PartialSums
+
+    _configure()
+    st = _device_state(x.device)
+    t, k = x.shape
+    n = w.shape[0]
+    slab_rows = -(-t // 16) * 16
+    slabs = torch.empty((splits, slab_rows, n), dtype=torch.float32, device=x.device)
+    check(library().cw_gemm_tc_parts(_ptr(x), _ptr(w), _ptr(slabs), t, n, k, x.stride(0), slab_rows, splits, st["sms"],
+                                     _ptr(st["status"]), _stream()), "gemm_tc_parts")
+    return PartialSums(slabs, t)
 
 
 def gemm(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None, *, out: torch.Tensor | None = None,

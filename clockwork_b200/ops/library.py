@@ -17,6 +17,7 @@ _SIGNATURES: dict[str, list] = {
     "cw_add_rmsnorm": [P, P, P, P, P, I, I, I, F, I, P, P],
     "cw_silu_mul": [P, P, I, I, I, P],
     "cw_add_to_residual": [P, P, I, I, I, P],
+    "cw_add_parts_rmsnorm": [P, P, I, I, P, P, I, I, F, I, P],
     "cw_gemm_ref": [P, P, P, P, I, I, I, I, I, I, I, P],
     "cw_gemm_ref_swiglu": [P, P, P, P, I, I, I, I, P],
     "cw_rope_store": [P, P, P, P, P, P, I, I, I, I, I, I, I, I, P, P],

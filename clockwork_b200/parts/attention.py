@@ -104,8 +104,7 @@ class Attention(Mixer):
             self.position.apply_and_store(ctx, qkv, view, self.num_heads, self.num_kv_heads, self.head_dim)
         out = attention_ops.paged_attention(ctx, qkv, view, self.num_heads, self.num_kv_heads,
                                             self.head_dim, self.scale, self.window, fused_position=fused)
-        self.o.add_into(out, stream.residual_after_flush(), stream)
-        return None
+        return self.o.add_or_defer(out, stream)
 
 
 register_mixer("attention", Attention, replace=True)

@@ -112,7 +112,7 @@ class ResidualStream:
 
     def __init__(self, residual: torch.Tensor) -> None:
         self.residual = residual
-        self.pending: torch.Tensor | None = None
+        self.pending = None     # a tensor [N, H], or the ``ops.PartialSums`` of a product (for norms that take them)
         self.next_norm = None   # the Norm part that will read the residual next, if the block knows it
         self.half_norm = None   # (norm weight, x * weight in bfloat16, per-row partial sums of squares)
 

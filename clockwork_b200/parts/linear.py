@@ -29,6 +29,18 @@ class Linear:
         if stream is not None:
             stream.half_norm = None if half is None else (begin, *half)
 
+    def add_or_defer(self, x: torch.Tensor, stream):
+        """The product's contribution to the residual stream: added into the residual here (returns None),
+        or, when the product is better split with its splits kept apart and the norm that reads the
+        residual next can add them up, returned as ``ops.PartialSums`` for the stream to hold."""
+        norm = stream.next_norm
+        if self.bias is None and norm is not None and getattr(norm, "takes_partial_sums", False):
+            parts = gemm_ops.linear_partial_sums(x, self.weight)
+            if parts is not None:
+                return parts
+        self.add_into(x, stream.residual_after_flush(), stream)
+        return None
+
     def to_float32(self, x: torch.Tensor) -> torch.Tensor:
         """x W^T as float32 (logits)."""
         return gemm_ops.linear_f32(x, self.weight, self.bias)

@@ -19,6 +19,7 @@ from .registry import register_norm
 class RMSNorm(Norm):
     graph_safe = True
     graph_safe_portions = True
+    takes_partial_sums = True  # ``forward`` hands whatever the stream holds to ``ops.add_rmsnorm``, slabs included
 
     def __init__(self, spec, prefix, dtype, device) -> None:
         super().__init__(spec, prefix, dtype, device)

@@ -40,8 +40,7 @@ class SwiGLU(FeedForward):
 
     def forward(self, ctx: StepContext, x, stream: ResidualStream):
         act = gemm_ops.swiglu(x, self.w_gate, self.w_up)
-        self.down.add_into(act, stream.residual_after_flush(), stream)
-        return None
+        return self.down.add_or_defer(act, stream)
 
 
 register_ffn("swiglu", SwiGLU, replace=True)

@@ -461,6 +461,38 @@ def test_gemm_tc_against_float64(ops, gemm_tc, t, n, k):
     ops.raise_on_status(gemm_tc.status(DEV))
 
 
+@pytest.mark.parametrize("t,n,k", [(256, 1536, 8960), (300, 520, 4480), (1000, 1536, 8960), (129, 264, 1024)])
+def test_gemm_tc_partial_sums_and_the_norm_that_adds_them(ops, gemm_tc, t, n, k):
+    """A product split over K with the splits kept apart: the slabs' sum is the product, twice in a row
+    the same bits; the RMSNorm kernel that takes the slabs adds them into the residual in slab order
+    and normalises, as the plain formulas say; without a norm the slabs are only added."""
+    x, w = rand(t, k, dtype=torch.bfloat16), rand(n, k, dtype=torch.bfloat16, scale=0.05, seed=1)
+    xd, wd = x.to(DEV), w.to(DEV)
+    splits = gemm_tc.partial_sums_splits(t, n, k, DEV)
+    assert splits >= 1 and (k < 4096 or splits > 1), splits
+    if splits == 1:
+        return
+    parts = gemm_tc.gemm_partial_sums(xd, wd, splits)
+    assert parts.slabs.shape[0] == splits and parts.rows == t
+    want = bf16_product(x, w)
+    total = parts.slabs[:, :t].double().sum(0).float().cpu()
+    torch.testing.assert_close(total, want, rtol=1e-4, atol=1e-5 * max(1.0, float(want.abs().max())))
+    assert torch.equal(gemm_tc.gemm_partial_sums(xd, wd, splits).slabs[:, :t], parts.slabs[:, :t])
+    base, g = rand(t, n, seed=3), rand(n, seed=4) + 1.0
+    resid = base.to(DEV).clone()
+    out = ops.add_rmsnorm(resid, parts, g.to(DEV), 1e-6, torch.bfloat16, gemm_tc.status(DEV))
+    summed = base.clone()
+    for s in range(splits):  # (float32 additions in slab order, as the kernel does them)
+        summed += parts.slabs[s, :t].cpu()
+    assert torch.equal(resid.cpu(), summed)
+    normed = summed * torch.rsqrt((summed.double() ** 2).mean(-1, keepdim=True) + 1e-6).float() * g
+    torch.testing.assert_close(out.float().cpu(), normed, rtol=1e-2, atol=1e-2)
+    again = base.to(DEV).clone()
+    ops.add_to_residual(again, parts)
+    assert torch.equal(again.cpu(), summed)
+    ops.raise_on_status(gemm_tc.status(DEV))
+
+
 @pytest.mark.parametrize("t,n,k", [(8, 8960, 1536), (33, 200, 96), (64, 1000, 1536), (700, 520, 256),
                                    (2100, 5000, 264), (300, 8960, 1536), (129, 130, 72)])
 def test_gemm_tc_swiglu(ops, gemm_tc, t, n, k):
