@@ -367,7 +367,8 @@ class PortionGraph:
         self.max_blocks = (max_ctx + cache.page_size - 1) // cache.page_size
         G = len(cache.groups)
         self._scalar_rules = model.step_scalars()
-        self._arrays = model.step_arrays(tokens, seqs, cache.page_size)
+        # (with single tokens in the step, at most PORTION_MAX_PORTIONS requests bring more: see _portion_graph_key)
+        self._arrays = model.step_arrays(tokens, seqs, cache.page_size, runner.PORTION_MAX_PORTIONS if singles else None)
         layout = [("tokens", tokens), ("positions", tokens), ("tok_seq", tokens), ("q_start", seqs + 1), ("ctx_lens", seqs),
                   ("rows", rows), ("state", seqs), *((f"scalar:{name}", 1) for name in self._scalar_rules),
                   *((("array", key), words) for key, (words, _, _) in self._arrays.items())]
@@ -626,6 +627,7 @@ class ModelRunner:
     PORTION_SEQ_BUCKETS = (8, 64)
     PORTION_MAX_LOGITS = 1 << 28  # float32 logits that a captured step may keep (1 GiB)
     PORTION_MAX_GRAPHS = 32       # captured steps kept at a time
+    PORTION_MAX_PORTIONS = 8      # requests with more than one token in a captured step that also holds single tokens
 
     def _portion_token_bucket(self, tokens: int) -> int | None:
         if tokens <= self.PORTION_TOKEN_BUCKETS[-1]:
@@ -655,6 +657,8 @@ class ModelRunner:
             tier *= 2
         tier = min(tier, self.graph_max_ctx)
         singles = any(len(e.tokens) == 1 for e in entries)
+        if singles and sum(1 for e in entries if len(e.tokens) > 1) > self.PORTION_MAX_PORTIONS:
+            return None  # (a captured step with single tokens has work lists for this many portions)
         return bucket, seqs, rows, tier, singles
 
     def capture_ahead(self, decode_batches=(), prompt_tokens=(), max_ctx: int = 1024, greedy: bool = True) -> int:

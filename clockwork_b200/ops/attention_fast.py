@@ -340,18 +340,24 @@ def _cuts_for(num_heads: int, head_dim: int, page_size: int) -> int:
     return num_heads if _cut_long_rows and prefill_tc_takes(head_dim, page_size) else 0
 
 
-def portion_step_arrays(num_heads: int, head_dim: int, page_size: int, max_tokens: int, max_seqs: int, device) -> dict:
+def portion_step_arrays(num_heads: int, head_dim: int, page_size: int, max_tokens: int, max_seqs: int, device,
+                        max_portions: int | None = None) -> dict:
     """The prefill kernel's work list as an array of a captured step (``Part.step_arrays``): three rows
     (request, first query row, split word) of fixed length, unused entries naming request -1.  Two keys,
-    for steps captured with and without their single-token requests served apart."""
+    for steps captured with and without their single-token requests served apart; with them apart only
+    the ``max_portions`` requests that bring more than one token have items (every unused item is a CTA
+    per head that starts and leaves)."""
     if head_dim not in PREFILL_HEAD_DIMS:
         return {}
     cuts = _cuts_for(num_heads, head_dim, page_size)
     sms = _sm_count(torch.device(device)) if cuts else 0
-    # a tile per 128 rows and one more per request; cuts add parts until the CTAs fill the SMs once
-    cap = max_tokens // QUERY_TILE + max_seqs + (sms // num_heads if cuts else 0)
+    # a tile per 128 rows and one more per request with items; cuts add parts until the CTAs fill the SMs once
+    portions = max_seqs if max_portions is None else min(max_seqs, max_portions)
+    caps = {False: max_tokens // QUERY_TILE + max_seqs + (sms // num_heads if cuts else 0),
+            True: max_tokens // QUERY_TILE + portions + (sms // num_heads if cuts else 0)}
 
     def fill(q_lens, ctx_lens, apart: bool) -> np.ndarray:
+        cap = caps[apart]
         seqs, q0s, words = prefill_work_items(q_lens, ctx_lens, cuts, sms, apart)
         if len(seqs) > cap:
             raise RuntimeError(f"{len(seqs)} work items for a step captured with room for {cap}")
@@ -362,10 +368,11 @@ def portion_step_arrays(num_heads: int, head_dim: int, page_size: int, max_token
         out[0, :n], out[1, :n], out[2, :n] = seqs, q0s, words
         return out.reshape(-1)
 
-    def present(view: torch.Tensor):
+    def present(view: torch.Tensor, cap: int):
         return view[:cap], view[cap : 2 * cap], (view[2 * cap :] if cuts else None), cap
 
-    return {("prefill_items", cuts, apart): (3 * cap, lambda q, c, apart=apart: fill(q, c, apart), present)
+    return {("prefill_items", cuts, apart): (3 * caps[apart], lambda q, c, apart=apart: fill(q, c, apart),
+                                             lambda view, apart=apart: present(view, caps[apart]))
             for apart in (False, True)}
 
 
