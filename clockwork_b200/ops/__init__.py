@@ -4,6 +4,8 @@ nothing here has a CPU path."""
 
 from __future__ import annotations
 
+import ctypes
+
 import torch
 
 from .library import KernelLibraryError, check, library, serial_launch, set_pdl
@@ -375,9 +377,28 @@ def step_from_state(row_slot: torch.Tensor, fresh: torch.Tensor, fresh_values: t
         _ptr(status), _stream()), "step_from_state")
 
 
+_sample_work: dict[int, torch.Tensor] = {}
+_sample_work_retired: list[torch.Tensor] = []  # outgrown workspaces: captured graphs may still point at them
+
+
+def _sample_workspace(device: torch.device, rows: int) -> torch.Tensor:
+    index = device.index if device.index is not None else torch.cuda.current_device()
+    fn = library().cw_sample_workspace_words
+    fn.restype = ctypes.c_longlong
+    words = int(fn(rows))
+    work = _sample_work.get(index)
+    if work is None or work.numel() < words:
+        if work is not None:
+            _sample_work_retired.append(work)
+        work = _sample_work[index] = torch.zeros(max(words, int(fn(8))), dtype=torch.int64, device=device)
+    return work
+
+
 def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor, top_p: torch.Tensor,
-           uniform: torch.Tensor, out: torch.Tensor | None = None, into_state=None) -> torch.Tensor:
-    """One token per row; rows with temperature 0 are greedy.  ``into_state``: as for ``argmax``."""
+           uniform: torch.Tensor, out: torch.Tensor | None = None, into_state=None, one_block: bool = False) -> torch.Tensor:
+    """One token per row; rows with temperature 0 are greedy.  ``into_state``: as for ``argmax``.
+    ``one_block``: the kernel that walks a row with a single thread block (the same rule, much slower for a
+    large vocabulary; kept for comparison) instead of the chain of kernels over many blocks per row."""
     _need(logits, torch.float32, "logits", 2)
     r, v = logits.shape
     for name, t, dt in (("temperature", temperature, torch.float32), ("top_k", top_k, torch.int32),
@@ -388,6 +409,11 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor,
     if out is None:
         out = torch.empty((r,), dtype=torch.int32, device=logits.device)
     slot_ptr, state_ptr, slots = _state_args(into_state)
-    check(library().cw_sample_state(_ptr(logits), _ptr(temperature), _ptr(top_k), _ptr(top_p), _ptr(uniform), _ptr(out),
-                                    r, v, v, slot_ptr, state_ptr, slots, _stream()), "sample")
+    if one_block:
+        check(library().cw_sample_state(_ptr(logits), _ptr(temperature), _ptr(top_k), _ptr(top_p), _ptr(uniform), _ptr(out),
+                                        r, v, v, slot_ptr, state_ptr, slots, _stream()), "sample")
+        return out
+    work = _sample_workspace(logits.device, r)
+    check(library().cw_sample_rows(_ptr(logits), _ptr(temperature), _ptr(top_k), _ptr(top_p), _ptr(uniform), _ptr(out),
+                                   r, v, v, slot_ptr, state_ptr, slots, _ptr(work), _stream()), "sample_rows")
     return out

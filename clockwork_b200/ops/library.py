@@ -27,6 +27,8 @@ _SIGNATURES: dict[str, list] = {
     "cw_sample": [P, P, P, P, P, P, I, I, LL, P],
     "cw_argmax_state": [P, P, I, I, LL, P, P, I, P],
     "cw_sample_state": [P, P, P, P, P, P, I, I, LL, P, P, I, P],
+    "cw_sample_rows": [P, P, P, P, P, P, I, I, LL, P, P, I, P, P],
+    "cw_sample_workspace_words": [I],
     "cw_step_from_state": [P, P, P, P, I, I, I, I, I, I, P, P, P, P, P, P, P, P, P, P, P, P],
 }
 _OPTIONAL: dict[str, list] = {}

@@ -290,6 +290,30 @@ def test_sample_matches_the_plain_rule(ops, temperature, top_k, top_p):
     assert got == want
 
 
+def test_sample_over_many_blocks_per_row_at_the_real_vocabulary(ops):
+    """The chain of kernels that cuts a row over many thread blocks (radix selections over integer
+    histograms) against the kernel that walks it with one block, at 151,936 logits: rows with every mix
+    of parameters (greedy rows among them, top-k of one and of nearly all, a top-p that keeps one token, a
+    peaked and a flat row); the same tokens, and the same again on a second run."""
+    r, v = 20, 151936
+    logits = rand(r, v, scale=3.0, seed=21)
+    logits[3] *= 4.0          # peaked
+    logits[4] *= 0.01         # nearly flat
+    logits[5, 777] = 60.0     # one token holds all the mass
+    temps = torch.tensor([0.0, 0.7, 1.0, 0.9, 1.0, 0.8, 1.3, 0.5, 1.0, 0.0, 0.6, 1.0, 2.0, 0.7, 1.0, 0.9, 1.1, 0.3, 1.0, 0.85])
+    ks = torch.tensor([0, 0, 50, 0, 5, 0, 1, 100000, 0, 7, 40, 1000, 0, 3, 151935, 0, 20, 0, 64, 0], dtype=torch.int32)
+    ps = torch.tensor([1.0, 1.0, 1.0, 0.9, 0.5, 0.3, 1.0, 0.95, 0.999, 0.5, 0.9, 0.8, 0.7, 1.0, 0.6, 1e-6, 0.99, 0.2, 1.0, 0.0])
+    dev = lambda t: t.to(DEV)
+    for salt in (0.123, 0.5, 0.987):
+        u = ((torch.arange(r, dtype=torch.float32) * 0.61803 + salt) % 1.0)
+        args = (dev(logits), dev(temps), dev(ks), dev(ps), dev(u))
+        many = ops.sample(*args).cpu().tolist()
+        one = ops.sample(*args, one_block=True).cpu().tolist()
+        assert many == one, [(i, a, b) for i, (a, b) in enumerate(zip(many, one)) if a != b]
+        assert ops.sample(*args).cpu().tolist() == many
+    assert many[0] == int(logits[0].argmax()) and many[9] == int(logits[9].argmax()) and many[5] == 777
+
+
 def test_step_inputs_from_the_request_state_table(ops, status):
     """``step_from_state``: rows name slots of the state table; fresh rows overwrite their column first;
     token, position, context length, cache slot (through the row's block table, two page groups) and the
