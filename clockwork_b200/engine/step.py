@@ -313,13 +313,14 @@ class DecodeGraph:
                 # a row is rewritten only from where the request's table grew since the row last held it
                 # (most steps: nowhere)
                 table = r.tables[g]
+                held = min(len(table), self.max_blocks)  # (pages beyond the graph's context bound are not this step's)
                 owner = owners[i]
-                if owner is not None and owner[0] is r and owner[1] == len(table) and owner[2] == r.table_epoch:
+                if owner is not None and owner[0] is r and owner[1] == held and owner[2] == r.table_epoch:
                     continue
-                same = owner is not None and owner[0] is r and owner[2] == r.table_epoch and owner[1] <= len(table)
+                same = owner is not None and owner[0] is r and owner[2] == r.table_epoch and owner[1] <= held
                 have = owner[1] if same else 0
-                tables[i, have : len(table)] = table[have:]
-                owners[i] = (r, len(table), r.table_epoch)
+                tables[i, have:held] = table[have:held]
+                owners[i] = (r, held, r.table_epoch)
                 dirty = True
             pages = tables[rows, pos // ps]
             if (pages == NO_PAGE).any():
@@ -469,7 +470,10 @@ class PortionGraph:
             tables[:S] = NO_PAGE
             for i, r in enumerate(reqs):
                 table = np.asarray(r.tables[g], dtype=np.int32)
-                tables[i, : len(table)] = table
+                # (a request may hold pages for tokens far beyond this step's: the scheduler reserves a
+                # whole prompt's at admission; the step reads the table up to its context bound only)
+                held = min(len(table), self.max_blocks)
+                tables[i, :held] = table[:held]
                 pos = np.arange(starts[i], ctx_lens[i], dtype=np.int32)
                 pages = table[pos // ps]
                 if (pages == NO_PAGE).any():

@@ -119,6 +119,26 @@ def test_graphs_captured_ahead_are_the_ones_the_steps_then_replay(sharp_dirs):
     assert runner.portion_graph_steps == 1
 
 
+def test_a_long_prompt_under_a_small_token_budget_through_the_engine(sharp_dirs):
+    """The scheduler reserves the pages of a whole prompt when it admits it, so the first portions of a long
+    prompt run in a captured step whose context bound (and block-table width) is far below the request's
+    table; beside it a short request decodes.  Greedy tokens against the plain implementation."""
+    from clockwork_b200.sampling import SamplingParams
+    from tests.test_engine_gpu import assert_greedy
+
+    folder = sharp_dirs["B"]
+    page = TINY["B"][2]
+    cfg = EngineConfig.defaults(str(folder), dtype="bfloat16", block_size=page, num_blocks=600, max_model_len=2048, max_num_seqs=4,
+                                max_num_batched_tokens=192, enable_prefix_cache=False)
+    eng = LLMEngine(cfg, model=load_model(folder, cfg.model.dtype))
+    prompts = [tokens_for("B", 1500, salt=91), tokens_for("B", 40, salt=92)]
+    outs = eng.generate(prompts, [SamplingParams(max_tokens=6, ignore_eos=True), SamplingParams(max_tokens=30, ignore_eos=True)])
+    assert eng.runner.portion_graph_steps >= 8 and {k[3] for k in eng.runner.portion_graphs} >= {1024, 2048}
+    plain_model = plain.read_model_dir(folder)
+    for prompt, out in zip(prompts, outs):
+        assert_greedy(plain_model, prompt, list(out.token_ids), exact=False)
+
+
 def test_float32_steps_and_uncaptured_engines_take_the_plain_step(sharp_dirs):
     folder = sharp_dirs["A"]
     for dtype, graphs in (("float32", True), ("bfloat16", False)):
