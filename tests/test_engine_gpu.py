@@ -359,3 +359,46 @@ def test_steps_run_ahead_change_nothing(models, model_dirs):
     tokens, reason = ahead["stopped"]
     assert reason == "stop" and tokens[-1] == stop_id and tokens == plain_run["greedy"][0][: len(tokens)] and len(tokens) <= 6
     assert {k: v for k, v in ahead.items() if k != "stopped"} == plain_run
+
+
+@pytest.mark.parametrize("seed", [1, 2])
+def test_a_random_churn_of_requests(seed, models, model_dirs, plain_models):
+    """Ninety requests of random lengths (one token to more than a thousand, some behind a shared prefix),
+    random limits and every kind of sampling, added a few at a time while others run, in a pool small
+    enough that requests are preempted now and then, with the prefix cache and the captured steps on:
+    every request finishes with as many tokens as it asked for, no kernel reports anything, every page and
+    state slot comes back, and the greedy requests' tokens are within rounding of the plain
+    implementation's best."""
+    import random
+
+    name = "B"
+    rng = random.Random(seed)
+    eng = engine(models, model_dirs, name, "bfloat16", num_blocks=330, max_model_len=2048, max_num_seqs=12,
+                 max_num_batched_tokens=320, enable_prefix_cache=True)
+    vocab = TINY[name][0]["vocab_size"]
+    shared = [rng.randrange(vocab) for _ in range(300)]
+    pending, asked, prompts = [], {}, {}
+    for i in range(90):
+        n = rng.choice([1, 2, 7, 30, 100, 129, 200, 513, 700, 1100])
+        prompt = shared[: rng.choice([0, 0, 80, 300])] + [rng.randrange(vocab) for _ in range(n)]
+        kind = rng.choice([dict(temperature=0.0), dict(temperature=0.0), dict(temperature=0.8, seed=i), dict(temperature=1.0, top_k=20, seed=i),
+                           dict(temperature=0.7, top_p=0.9, seed=i), dict(temperature=0.9, top_k=50, top_p=0.95, seed=i)])
+        limit = rng.choice([1, 2, 8, 40])
+        pending.append((f"r{i}", prompt, SamplingParams(max_tokens=limit, ignore_eos=True, **kind)))
+        asked[f"r{i}"], prompts[f"r{i}"] = (limit, kind["temperature"] == 0.0), prompt
+    done = {}
+    while pending or eng.has_unfinished_requests():
+        for _ in range(rng.choice([0, 0, 1, 3])):
+            if pending:
+                rid, prompt, params = pending.pop()
+                eng.add_request(rid, prompt_token_ids=prompt, sampling_params=params)
+        for out in eng.step():
+            if out.finished:
+                done[out.request_id] = list(out.token_ids)
+    eng.runner.check_status()
+    assert set(done) == set(asked) and all(len(done[rid]) == asked[rid][0] for rid in asked)
+    assert eng.cache.requests == {} and eng.cache.state.num_free == 12
+    assert eng.runner.portion_graph_steps > 20 and eng.runner.graphs
+    greedy = [rid for rid in sorted(asked) if asked[rid][1] and len(prompts[rid]) <= 400][:5]
+    for rid in greedy:
+        assert_greedy(plain_models[name], prompts[rid], done[rid], exact=False)
