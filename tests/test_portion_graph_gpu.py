@@ -139,6 +139,55 @@ def test_a_long_prompt_under_a_small_token_budget_through_the_engine(sharp_dirs)
         assert_greedy(plain_model, prompt, list(out.token_ids), exact=False)
 
 
+@pytest.mark.parametrize("dtype", ["bfloat16", "float32"])
+@pytest.mark.parametrize("seed", [0, 1, 2])
+def test_random_compositions_of_steps(seed, dtype, sharp_dirs):
+    """Seven requests of lengths that sit on and beside page and tile edges, at most four live, every step
+    a random choice of who takes part and with how many tokens (one, a few, a hundred), requests joining
+    and leaving in between: every position's logits against the plain implementation (float64 for the
+    float32 run: at these lengths float32 sums alone move the sharpened model's logits by 1e-5)."""
+    import random
+
+    name = "B"
+    folder = sharp_dirs[name]
+    config, weights = plain.read_model_dir(folder)
+    if dtype == "float32":
+        weights64 = {k: v.double() for k, v in weights.items()}
+    rng = random.Random(seed)
+    _eng, runner, cache = runner_for(folder, name, dtype, max_model_len=1024, seqs=8)
+    total = {f"q{i}": tokens_for(name, rng.choice([1, 3, 17, 64, 65, 130, 257, 400]), salt=seed * 10 + i) for i in range(7)}
+    run = Replayed(runner, cache)
+    waiting, live = list(total), {}
+    while waiting or live:
+        while waiting and len(live) < 4 and rng.random() < 0.6:
+            live[waiting.pop()] = 0
+        portions = {}
+        for rid in list(live):
+            if rng.random() < 0.2:
+                continue  # sits this step out
+            n = min(len(total[rid]) - live[rid], rng.choice([1, 1, 1, 2, 3, 8, 16, 33, 64, 128, 200]))
+            portions[rid] = total[rid][live[rid] : live[rid] + n]
+        if not portions:
+            continue
+        run.step(portions)
+        for rid, toks in portions.items():
+            live[rid] += len(toks)
+            if live[rid] == len(total[rid]):
+                cache.close(rid)
+                del live[rid]
+    for rid, toks in total.items():
+        _places, got = run.of(rid)
+        if dtype == "float32":
+            exact = plain.all_position_logits(config, weights64, toks).float()
+            check(got, (exact, exact), dtype, f"{name} {dtype} seed {seed} {rid}")
+        else:
+            exact = plain.all_position_logits(config, weights, toks)
+            rounded = plain.all_position_logits(config, weights, toks, rnd=plain.to_bfloat16_and_back)
+            check(got, (exact, rounded), dtype, f"{name} {dtype} seed {seed} {rid}")
+    if dtype == "bfloat16":
+        assert runner.portion_graph_steps > 3
+
+
 def test_float32_steps_and_uncaptured_engines_take_the_plain_step(sharp_dirs):
     folder = sharp_dirs["A"]
     for dtype, graphs in (("float32", True), ("bfloat16", False)):
