@@ -111,3 +111,53 @@ def test_decoding_at_4400_tokens_beside_a_short_request(dtype, model_dir, refere
     exact, rounded = references(a)
     check(tb.gather(out, "a", len(a), first=4096), (exact[4096:], rounded[4096:]), dtype, f"head size 128, {dtype}, 4,400 tokens")
     check(tb.gather(out, "b", len(b)), references(b), dtype, f"head size 128, {dtype}, the short request beside them")
+
+
+@pytest.mark.parametrize("dtype,seed", [("bfloat16", 0), ("bfloat16", 1), ("float32", 0)])
+def test_random_compositions_of_steps_at_head_size_128(dtype, seed, model_dir, references):
+    """Nine requests of 1 to 2,300 tokens, at most six live, every step a random choice of who takes part
+    and with how many tokens (one, a few, a query tile, over a thousand), through the step function with
+    its captured steps: logits at a few places of every portion against the plain implementation."""
+    import random
+
+    from clockwork_b200 import EngineConfig
+    from clockwork_b200.engine import LLMEngine, StepEntry, load_model
+
+    rng = random.Random(seed)
+    cfg = EngineConfig.defaults(str(model_dir), dtype=dtype, block_size=PAGE, num_blocks=900, max_model_len=4096, max_num_seqs=12,
+                                max_num_batched_tokens=8192, enable_prefix_cache=False)
+    eng = LLMEngine(cfg, model=load_model(model_dir, cfg.model.dtype))
+    runner, cache = eng.runner, eng.cache
+    total = {f"q{i}": tokens(rng.choice([1, 5, 127, 128, 129, 300, 640, 1100, 1500, 2300]), seed * 20 + i) for i in range(9)}
+    waiting, live = list(total), {}
+    got = {rid: [] for rid in total}
+    places = {rid: [] for rid in total}
+    while waiting or live:
+        while waiting and len(live) < 6 and rng.random() < 0.6:
+            rid = waiting.pop()
+            cache.open(rid)
+            live[rid] = 0
+        entries = []
+        for rid in list(live):
+            if rng.random() < 0.15:
+                continue  # sits this step out
+            n = min(len(total[rid]) - live[rid], rng.choice([1, 1, 1, 1, 2, 7, 16, 100, 128, 130, 400, 700, 1300]))
+            entries.append(StepEntry(rid, total[rid][live[rid] : live[rid] + n], sorted(set(rng.sample(range(n), min(n, 3)) + [n - 1]))))
+        if not entries:
+            continue
+        out = runner.step(entries).float().cpu()
+        row = 0
+        for e in entries:
+            for w in e.want:
+                got[e.request_id].append(out[row].clone())
+                places[e.request_id].append(live[e.request_id] + w)
+                row += 1
+            live[e.request_id] += len(e.tokens)
+            if live[e.request_id] == len(total[e.request_id]):
+                cache.close(e.request_id)
+                del live[e.request_id]
+        runner.check_status()
+    for rid, toks in total.items():
+        exact, rounded = references(toks)
+        check(torch.stack(got[rid]), (exact[places[rid]], rounded[places[rid]]), dtype, f"{dtype} seed {seed} {rid} ({len(toks)} tokens)")
+    assert (runner.portion_graph_steps > 3) == (dtype == "bfloat16")
