@@ -7,7 +7,9 @@
 // threshold stays (:153-163); the token is then drawn from the softmax of what is left.
 // The reference draws with torch.multinomial from a per-request generator; here the caller
 // supplies one uniform number u in [0,1) per row and the token is the first index whose
-// cumulative probability (in index order) exceeds u.
+// cumulative probability (in index order) exceeds u.  Equal logits are kept or dropped together: under
+// top-p a token stays iff the mass of the logits strictly above it does not exceed top_p (the reference's
+// sort may cut between equal logits, in an order it does not define; every token it could keep stays here).
 //
 // Nothing is sorted: the k-th largest value and the top-p cut-off are found by a bitwise search
 // over an order-preserving integer image of the logits (32 counting passes each).
@@ -16,7 +18,8 @@
 #define ST 1024
 
 __device__ __forceinline__ unsigned ordered_key(float f) {
-    const unsigned b = __float_as_uint(f);
+    unsigned b = __float_as_uint(f);
+    b = (b == 0x80000000u) ? 0u : b;  // -0.0 and +0.0 compare equal as floats: one image for both
     return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
 }
 

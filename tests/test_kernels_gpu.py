@@ -394,6 +394,70 @@ def test_sample_rows_carry_their_own_parameters(ops):
     assert got == want
 
 
+@pytest.mark.parametrize("v", [3, 33, 4097])
+def test_sample_with_equal_logits_and_zeros_of_both_signs(ops, v):
+    """Logits rounded to halves, so that many are equal and some are -0.0 beside +0.0 (equal as floats,
+    different as bits): a greedy row takes the first of the largest, and top-k keeps every logit that is
+    not below the k-th largest (model_runner.py:136-137, :150-152).  Both forms of the sampler against
+    the plain rule."""
+    r = 12
+    logits = (rand(r, v, scale=1.5, seed=40 + v) * 2).round() / 2
+    logits[0, 0], logits[0, 1:] = -0.0, 0.0                    # greedy: index 0 although the bits of -0.0 are `smaller'
+    logits[1] = -logits[1].abs() - 0.5
+    logits[1, v // 2], logits[1, v - 1] = -0.0, 0.0            # the largest value twice, -0.0 first
+    logits[2] = 1.5                                            # all equal
+    assert v < 33 or (logits[3:] == 0).logical_and(torch.signbit(logits[3:])).any()
+    temps = torch.tensor([0.0, 0.0, 0.0, 1.0, 0.7, 1.0, 0.0, 1.3, 1.0, 0.5, 1.0, 2.0])
+    ks = torch.tensor([0, 0, 0, 1, 2, v, 5, 3, v + 5, 1, 0, max(v - 1, 1)], dtype=torch.int32)
+    ps = torch.ones(r)
+    dev = lambda t: t.to(DEV)  # noqa: E731
+    for salt in (0.05, 0.51, 0.93):
+        u = (torch.arange(r, dtype=torch.float32) * 0.61803 + salt) % 1.0
+        args = (dev(logits), dev(temps), dev(ks), dev(ps), dev(u))
+        many = ops.sample(*args).cpu().tolist()
+        one = ops.sample(*args, one_block=True).cpu().tolist()
+        want = [plain.sample_with_uniform(logits[i], float(temps[i]), int(ks[i]) or -1, float(ps[i]), float(u[i])) for i in range(r)]
+        assert many == want and one == want, (many, one, want)
+    assert many[0] == 0 and many[1] == v // 2 and many[2] == 0
+
+
+def _draw_keeping_equal_logits_together(logits, temperature, top_k, top_p, u):
+    """The rule of model_runner.py:147-164 where equal logits are told apart by nothing: a token stays under
+    top-p iff the softmax mass of the logits strictly above it does not exceed top_p (the reference's sort puts
+    equal logits in an order it does not define and may cut between them; the kernels keep or drop them
+    together, which keeps every token the reference could keep)."""
+    l = (logits.to(torch.float32) / temperature).double()
+    if 0 < top_k < l.numel():
+        l = l.masked_fill(l < torch.topk(l, top_k).values[-1], float("-inf"))
+    probs = torch.softmax(l, dim=-1)
+    if top_p < 1.0:
+        values, inverse = torch.unique(l, return_inverse=True)              # ascending
+        mass = torch.zeros_like(values).index_add_(0, inverse, probs)
+        above = mass.flip(0).cumsum(0).flip(0) - mass                          # mass strictly above each value
+        probs = probs.masked_fill((above > top_p)[inverse], 0.0)
+    cdf = probs.cumsum(0)
+    return int((cdf > u * float(cdf[-1])).nonzero()[0])
+
+
+@pytest.mark.parametrize("v", [33, 1003, 50000])
+def test_sample_top_p_with_equal_logits(ops, v):
+    """Top-p over logits rounded to halves: the cut falls inside a group of equal logits in most rows."""
+    r = 16
+    logits = (rand(r, v, scale=1.5, seed=70 + v) * 2).round() / 2
+    logits[1] = 1.5
+    temps = torch.tensor([1.0, 1.0, 0.7, 1.3, 1.0, 0.5, 2.0, 1.0, 0.9, 1.0, 1.5, 0.7, 1.0, 1.0, 0.8, 1.0])
+    ks = torch.tensor([0, 0, 0, 10, v, 0, 0, 3, 0, v // 2, 0, 0, 7, 0, 0, 1], dtype=torch.int32)
+    ps = torch.tensor([0.9, 0.5, 0.0, 0.8, 0.999, 1e-4, 0.3, 0.6, 0.95, 0.7, 0.1, 0.99, 0.2, 0.4, 0.85, 0.5])
+    dev = lambda t: t.to(DEV)  # noqa: E731
+    for salt in (0.05, 0.51, 0.93):
+        u = (torch.arange(r, dtype=torch.float32) * 0.61803 + salt) % 1.0
+        args = (dev(logits), dev(temps), dev(ks), dev(ps), dev(u))
+        many = ops.sample(*args).cpu().tolist()
+        one = ops.sample(*args, one_block=True).cpu().tolist()
+        want = [_draw_keeping_equal_logits_together(logits[i], float(temps[i]), int(ks[i]), float(ps[i]), float(u[i])) for i in range(r)]
+        assert many == want and one == want, (many, one, want)
+
+
 # ---- tcgen05 matrix products -------------------------------------------------------------------------
 TC_SHAPES = [
     # T, N, K: decode sizes (inner dimension split over CTAs), ragged edges, prefill sizes
