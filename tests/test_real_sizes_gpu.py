@@ -72,30 +72,39 @@ def two_layer_dir(tmp_path_factory):
 
 @pytest.fixture(scope="module")
 def references(two_layer_dir):
+    return plain_references(two_layer_dir)
+
+
+def plain_references(model_dir):
     """Logits of the plain implementation at the asked positions: for a bfloat16 run (float32, the same
     with activations rounded to bfloat16); for a float32 run (float64, float32).  With inner dimensions
     of 1,536 and 8,960 and peaked attention, float32 arithmetic alone moves these logits by more than
     1e-5 (the plain implementation in float32 differs from itself in float64 by 2e-5), so the float32
     engine is held to the derived rule too: at most 2.5 times as far from the float64 result as the
     plain float32 result is."""
-    config, weights32 = plain.read_model_dir(two_layer_dir)
-    weights64 = {k: v.double() for k, v in weights32.items()}
+    config, weights32 = plain.read_model_dir(model_dir)
+    doubled = []  # the float64 copy of the weights, made when a float32 run first asks
     hidden = {}
+
+    def weights_in_float64():
+        if not doubled:
+            doubled.append({k: v.double() for k, v in weights32.items()})
+        return doubled[0]
 
     def get(toks, rows, dtype):
         key = (tuple(toks), dtype)
         if key not in hidden:
             if dtype == "float32":
-                hidden[key] = (plain.final_hidden_states(config, weights64, toks),
+                hidden[key] = (plain.final_hidden_states(config, weights_in_float64(), toks),
                                plain.final_hidden_states(config, weights32, toks).double())
             else:
                 hidden[key] = (plain.final_hidden_states(config, weights32, toks),
                                plain.final_hidden_states(config, weights32, toks, rnd=plain.to_bfloat16_and_back))
         index = torch.as_tensor(rows, dtype=torch.long)
         exact, rounded = hidden[key]
-        head64 = plain.output_head(config, weights64).T
         head32 = plain.output_head(config, weights32).T
         if dtype == "float32":
+            head64 = plain.output_head(config, weights_in_float64()).T
             return (exact[index] @ head64).float(), (rounded[index].float() @ head32)
         return exact[index] @ head32, rounded[index] @ head32
 
