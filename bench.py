@@ -373,11 +373,12 @@ def main() -> int:
     ap.add_argument("--shape", default="qwen2.5-1.5b",
                     help="with --only: another size that the architecture knows by name (qwen2.5-7b, qwen2.5-32b)")
     ap.add_argument("--skip-points", action="store_true", help="leave out the points and the prefill (quick runs)")
-    ap.add_argument("--only", choices=["decode", "prefill", "mixed", "shared-prefix"], default=None,
+    ap.add_argument("--only", choices=["decode", "prefill", "mixed", "shared-prefix", "long-prompt"], default=None,
                     help="run one part only, once, and print its figures (for profiling runs under ncu)")
     ap.add_argument("--prompt-len", type=int, default=None,
                     help="with --only decode: prompts of this many tokens instead of 1,024 (decoding at other context "
-                         "lengths); with --only prefill: a prompt of this many tokens instead of 2,048")
+                         "lengths); with --only prefill: a prompt of this many tokens instead of 2,048; with --only long-prompt: "
+                         "a prompt of this many tokens instead of 32,768, in portions of 2,048")
     ap.add_argument("--timeline", action="store_true",
                     help="with --only decode: also print one step's kernel timeline (device-side records, ops/trace.py)")
     args = ap.parse_args()
@@ -411,8 +412,8 @@ def main() -> int:
     rng = random.Random(0)
     peak, peak_kind = peaks()
     once = args.only is not None
-    if args.prompt_len is not None and args.only not in ("decode", "prefill"):
-        print("bench.py: --prompt-len goes with --only decode or --only prefill")
+    if args.prompt_len is not None and args.only not in ("decode", "prefill", "long-prompt"):
+        print("bench.py: --prompt-len goes with --only decode, --only prefill or --only long-prompt")
         return 2
     prompt_len = args.prompt_len or PROMPT_LEN
 
@@ -661,6 +662,40 @@ def main() -> int:
                 "cached_tokens": stats["total_cached_tokens"] - cached0, "prompt_tokens": stats["total_prompt_tokens"] - prompt0,
                 "decode_tok_s": requests * decode_steps / (t2 - t1), "decode_steps": decode_steps, "total_s": t2 - t0}
 
+    def time_long_prompt(total: int = 32768, portion: int = PREFILL_LEN, reps: int = 2) -> dict:
+        """One prompt of ``total`` tokens through the step function in portions of ``portion`` tokens, as the
+        scheduler cuts it under its token budget: device time of the whole prompt and of its last portion."""
+        engine = make_engine(1, 1, num_blocks=(total + PAGE) // PAGE + 8, max_model_len=total + PAGE)
+        runner, cache = engine.runner, engine.cache
+        whole, last = [], []
+        for rep in range(reps + 1):
+            rid = f"long{rep}"
+            cache.open(rid)
+            per_step = []
+            for first in range(0, total, portion):
+                toks = [rng.randrange(vocab) for _ in range(min(portion, total - first))]
+                start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                torch.cuda.synchronize()
+                start.record()
+                runner.step([StepEntry(rid, toks, [len(toks) - 1])])
+                end.record()
+                torch.cuda.synchronize()
+                per_step.append(start.elapsed_time(end))
+            cache.close(rid)
+            if rep >= 1:
+                whole.append(sum(per_step))
+                last.append(per_step[-1])
+        runner.check_status()
+        ms = statistics.median(whole)
+        flops = prefill_flops(raw, total) + 2 * raw["hidden_size"] * vocab * (-(-total // portion) - 1)
+        del engine
+        torch.cuda.empty_cache()
+        return {"tokens": total, "portion": portion, "ms": ms, "tok_s": total / (ms / 1e3), "last_portion_ms": statistics.median(last),
+                "flops_frac": flops / (ms / 1e3) / (peak["bf16_tflops"] * 1e12)}
+
+    if args.only == "long-prompt":
+        print(json.dumps({"impl": "ours", "long_prompt": time_long_prompt(total=args.prompt_len or 32768)}))
+        return 0
     if args.only == "prefill":
         print(json.dumps({"impl": "ours", "prefill": time_prefill(reps=1 if args.prompt_len is None else 5,
                                                                    tokens=args.prompt_len or PREFILL_LEN)}))
@@ -709,6 +744,10 @@ def main() -> int:
             points[f"prefill_{tokens}_ms"] = time_prefill(tokens=tokens)["ms"]
         small = time_mixed(decodes=7, ctx=1024, portions=1, portion_len=256)
         points["mixed_7x1024_1x256_ms"] = small["ms"]
+        long_prompt = time_long_prompt()
+        points["long_prompt_32768_tok_s"] = long_prompt["tok_s"]
+        points["long_prompt_32768_flops_frac"] = long_prompt["flops_frac"]
+        points["prefill_2048_behind_30720_ms"] = long_prompt["last_portion_ms"]
         mixed = time_mixed()
         points["mixed_32x2048_2x512_tok_s"] = mixed["tok_s"]
         points["mixed_32x2048_2x512_ms"] = mixed["ms"]

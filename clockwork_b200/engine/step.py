@@ -369,7 +369,7 @@ class PortionGraph:
         G = len(cache.groups)
         self._scalar_rules = model.step_scalars()
         # (with single tokens in the step, at most PORTION_MAX_PORTIONS requests bring more: see _portion_graph_key)
-        self._arrays = model.step_arrays(tokens, seqs, cache.page_size, runner.PORTION_MAX_PORTIONS if singles else None)
+        self._arrays = model.step_arrays(tokens, seqs, cache.page_size, runner.PORTION_MAX_PORTIONS if singles else None, max_ctx)
         layout = [("tokens", tokens), ("positions", tokens), ("tok_seq", tokens), ("q_start", seqs + 1), ("ctx_lens", seqs),
                   ("rows", rows), ("state", seqs), *((f"scalar:{name}", 1) for name in self._scalar_rules),
                   *((("array", key), words) for key, (words, _, _) in self._arrays.items())]

@@ -34,11 +34,12 @@ def decode_split(num_seqs: int, num_heads: int, num_kv_heads: int, max_ctx: int,
 
 
 def portion_step_arrays(num_heads: int, head_dim: int, page_size: int, max_tokens: int, max_seqs: int, device,
-                        max_portions: int | None = None) -> dict:
+                        max_portions: int | None = None, max_ctx: int | None = None) -> dict:
     """What ``Part.step_arrays`` of an attention layer of these sizes returns: the prefill kernel's work
     list, for captured steps that hold prompt portions (empty when the bfloat16 kernels do not take the
     head size: such a model's steps are not captured)."""
-    return _attention_fast_module.portion_step_arrays(num_heads, head_dim, page_size, max_tokens, max_seqs, device, max_portions)
+    return _attention_fast_module.portion_step_arrays(num_heads, head_dim, page_size, max_tokens, max_seqs, device, max_portions,
+                                                      max_ctx)
 
 
 def reserve_decode_scratch(device, max_seqs: int, num_heads: int, num_kv_heads: int, head_dim: int, max_ctx: int) -> None:

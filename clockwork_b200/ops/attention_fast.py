@@ -281,7 +281,7 @@ MAX_PARTS = 8                   # (the kernel's limit)
 
 
 def prefill_work_items(q_lens, ctx_lens, num_heads: int = 0, sm_count: int = 0,
-                       skip_single: bool = False) -> tuple[list[int], list[int], list[int]]:
+                       skip_single: bool = False, max_items: int | None = None) -> tuple[list[int], list[int], list[int]]:
     """Work items of a step's portions: (request index, first query row, split word) per 128 query rows,
     longest first (CTAs are handed to SMs in this order, so the short ones fill the tail).
 
@@ -289,8 +289,9 @@ def prefill_work_items(q_lens, ctx_lens, num_heads: int = 0, sm_count: int = 0,
     of its longest tiles cut into parts, each walked by a CTA of its own and merged by the last to
     finish: the tile with the most keys per part gets one more part until the CTAs fill the SMs once
     (a CTA costs several microseconds besides its keys, so a second round of CTAs would cost more
-    than it saves).  A part's item repeats its tile's (request, row); the split word is
-    (index of the tile's first item) << 8 | parts."""
+    than it saves).  A step with more tiles x heads than SMs has its rows cut when that evens out the
+    rounds of CTAs (``_cut_for_even_rounds``; never more than ``max_items`` items then).  A part's item repeats its tile's (request, row); the split
+    word is (index of the tile's first item) << 8 | parts."""
     groups = []  # [keys the tile's last row sees, request, first row, parts]
     for s, (n, c) in enumerate(zip(q_lens, ctx_lens)):
         if skip_single and n == 1:
@@ -305,6 +306,8 @@ def prefill_work_items(q_lens, ctx_lens, num_heads: int = 0, sm_count: int = 0,
                 break
             g[3] += 1
             room -= 1
+        if _even_rounds and len(groups) * num_heads > sm_count:
+            _cut_for_even_rounds(groups, num_heads, sm_count, ROUNDS_MAX_ITEMS if max_items is None else max_items)
     groups.sort(key=lambda g: -(g[0] / g[3]))
     seqs, q0s, words = [], [], []
     for _, s, q0, parts in groups:
@@ -316,8 +319,85 @@ def prefill_work_items(q_lens, ctx_lens, num_heads: int = 0, sm_count: int = 0,
     return seqs, q0s, words
 
 
+ROUNDS_CTA_TILES = 7        # what a CTA costs besides its key tiles, in tiles' time (launch, look-ups, first loads, last store)
+ROUNDS_MERGE_TILES = 3      # what a part adds to its CTA: the partial result written, and read again by the merger
+ROUNDS_MIN_PART_TILES = 8   # no part shorter than this when rows are cut to even out rounds of CTAs
+ROUNDS_MIN_GAIN = 0.05      # rows are cut only for an estimated gain of this much
+ROUNDS_MAX_ITEMS = 64       # and into no more items than this (an unused item of a captured step's list is a CTA per head
+                            # that starts and leaves; each item holds 128 x head size floats per head of scratch)
+ROUNDS_MIN_CTX = 8192       # rows no longer than this are not cut for even rounds (measured: no gain below, 3 % at 10,240 keys,
+                            # 8 % at 18,432, 12 % at 30,720 for a 2,048-token portion of 12 heads; two to three parts are best)
+
+
+def rounds_max_parts(max_ctx: int | None) -> int:
+    """The most parts that ``_cut_for_even_rounds`` gives a row of up to ``max_ctx`` keys."""
+    if not _even_rounds or (max_ctx is not None and max_ctx <= ROUNDS_MIN_CTX):
+        return 1
+    return MAX_PARTS
+
+
+def _rounds_estimate(costs: np.ndarray, sm_count: int) -> float:
+    """The time, in tiles, that CTAs of these costs (longest first) take when SMs pick them up in order as they
+    become free: estimated by dealing them out in rounds, every other round in reverse."""
+    rounds = -(-len(costs) // sm_count)
+    table = np.zeros(rounds * sm_count, dtype=np.float64)
+    table[: len(costs)] = costs
+    table = table.reshape(rounds, sm_count)
+    table[1::2] = table[1::2, ::-1]
+    return float(table.sum(axis=0).max())
+
+
+def _cut_for_even_rounds(groups: list[list], num_heads: int, sm_count: int, max_items: int) -> None:
+    """More CTAs than SMs: when they are few and long (a portion behind a long context: 16 tiles x 12 heads of
+    250 key tiles each on 148 SMs take two rounds for the work of 1.3), rows of keys are cut into parts of
+    about equal length so that the rounds come out even.  The grain (tiles per part) is the longest row cut
+    into 1, 2, ... parts; the one with the smallest estimated time wins, and nothing is cut for less than
+    ``ROUNDS_MIN_GAIN`` or into more than ``max_items`` items.  Sets ``g[3]`` of the groups."""
+    tiles = np.array([-(-g[0] // QUERY_TILE) for g in groups], dtype=np.int64)
+    longest = int(tiles.max())
+
+    def estimate(parts: np.ndarray) -> float:
+        per = -(-tiles // parts)                                     # the kernel's division: every part `per` tiles,
+        costs = np.repeat(per, parts)                                # the last what is left (it may be nothing)
+        costs[np.cumsum(parts) - 1] = np.maximum(tiles - (parts - 1) * per, 0)
+        costs = costs + np.repeat(ROUNDS_CTA_TILES + ROUNDS_MERGE_TILES * (parts > 1), parts)
+        return _rounds_estimate(np.repeat(np.sort(costs)[::-1], num_heads), sm_count)
+
+    if longest * QUERY_TILE <= ROUNDS_MIN_CTX:
+        return  # (parts would cost about what they walk)
+    # which grain: first by the rule for CTAs of equal length (rounds x a part's cost), then the winner as above
+    tile_list = tiles.tolist()
+    best = -(-len(tile_list) * num_heads // sm_count) * (longest + ROUNDS_CTA_TILES) * (1.0 - ROUNDS_MIN_GAIN)
+    best_parts = None
+    for most in range(2, MAX_PARTS + 1):
+        grain = -(-longest // most)
+        if grain < ROUNDS_MIN_PART_TILES:
+            break
+        parts = [min(MAX_PARTS, -(-t // grain)) for t in tile_list]
+        total = sum(parts)
+        if total > max_items:
+            break
+        time = -(-total * num_heads // sm_count) * (grain + ROUNDS_CTA_TILES + ROUNDS_MERGE_TILES)
+        if time < best:
+            best, best_parts = time, parts
+    if best_parts is None:
+        return
+    best_parts = np.array(best_parts, dtype=np.int64)
+    if estimate(best_parts) < estimate(np.ones_like(tiles)) * (1.0 - ROUNDS_MIN_GAIN):
+        for g, n in zip(groups, best_parts.tolist()):
+            g[3] = max(g[3], int(n))
+
+
 _cut_long_rows = True
+_even_rounds = True
 _route_single_tokens = True
+
+
+def set_even_rounds(on: bool) -> None:
+    """Steps with more query tiles x heads than SMs cut their rows of keys when that evens out the rounds of
+    CTAs, by default; ``False`` leaves them whole (for measurements; set before steps are captured)."""
+    global _even_rounds
+    _even_rounds = bool(on)
 
 
 def set_route_single_tokens(on: bool) -> None:
@@ -341,7 +421,7 @@ def _cuts_for(num_heads: int, head_dim: int, page_size: int) -> int:
 
 
 def portion_step_arrays(num_heads: int, head_dim: int, page_size: int, max_tokens: int, max_seqs: int, device,
-                        max_portions: int | None = None) -> dict:
+                        max_portions: int | None = None, max_ctx: int | None = None) -> dict:
     """The prefill kernel's work list as an array of a captured step (``Part.step_arrays``): three rows
     (request, first query row, split word) of fixed length, unused entries naming request -1.  Two keys,
     for steps captured with and without their single-token requests served apart; with them apart only
@@ -353,12 +433,16 @@ def portion_step_arrays(num_heads: int, head_dim: int, page_size: int, max_token
     sms = _sm_count(torch.device(device)) if cuts else 0
     # a tile per 128 rows and one more per request with items; cuts add parts until the CTAs fill the SMs once
     portions = max_seqs if max_portions is None else min(max_seqs, max_portions)
-    caps = {False: max_tokens // QUERY_TILE + max_seqs + (sms // num_heads if cuts else 0),
-            True: max_tokens // QUERY_TILE + portions + (sms // num_heads if cuts else 0)}
+    # (or, with more tiles than that, up to ``rounds_max_parts`` parts per tile for contexts up to ``max_ctx``)
+    most = rounds_max_parts(max_ctx) if cuts else 1
+    caps = {False: max(max_tokens // QUERY_TILE + max_seqs + (sms // num_heads if cuts else 0),
+                       min((max_tokens // QUERY_TILE + max_seqs) * most, ROUNDS_MAX_ITEMS)),
+            True: max(max_tokens // QUERY_TILE + portions + (sms // num_heads if cuts else 0),
+                      min((max_tokens // QUERY_TILE + portions) * most, ROUNDS_MAX_ITEMS))}
 
     def fill(q_lens, ctx_lens, apart: bool) -> np.ndarray:
         cap = caps[apart]
-        seqs, q0s, words = prefill_work_items(q_lens, ctx_lens, cuts, sms, apart)
+        seqs, q0s, words = prefill_work_items(q_lens, ctx_lens, cuts, sms, apart, cap)
         if len(seqs) > cap:
             raise RuntimeError(f"{len(seqs)} work items for a step captured with room for {cap}")
         out = np.zeros((3, cap), dtype=np.int32)

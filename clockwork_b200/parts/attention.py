@@ -59,13 +59,14 @@ class Attention(Mixer):
         return {attention_ops.decode_split_name(nh, nkv, hd):
                 lambda num_seqs, max_ctx: attention_ops.decode_split(num_seqs, nh, nkv, max_ctx, device, hd)}
 
-    def step_arrays(self, max_tokens: int, max_seqs: int, page_size: int, max_portions: int | None = None) -> dict:
+    def step_arrays(self, max_tokens: int, max_seqs: int, page_size: int, max_portions: int | None = None,
+                    max_ctx: int | None = None) -> dict:
         """The work list of the prefill kernel (which 128 query rows of which request, cut how) depends on
         how a step's tokens are divided among its requests."""
         if self.dtype != torch.bfloat16:
             return {}
         return attention_ops.portion_step_arrays(self.num_heads, self.head_dim, page_size, max_tokens, max_seqs, self.device,
-                                                 max_portions)
+                                                 max_portions, max_ctx)
 
     def reserve_for_steps(self, max_seqs: int, max_ctx: int) -> None:
         if self.dtype == torch.bfloat16:

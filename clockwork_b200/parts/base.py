@@ -179,12 +179,13 @@ class Part:
     # kernels on the current stream and takes what it needs about the portions from device memory (the
     # step's arrays and ``step_arrays`` below), never from the host-side lists: such a step may be captured too
 
-    def step_arrays(self, max_tokens: int, max_seqs: int, page_size: int, max_portions: int | None = None) -> dict:
+    def step_arrays(self, max_tokens: int, max_seqs: int, page_size: int, max_portions: int | None = None,
+                    max_ctx: int | None = None) -> dict:
         """int32 arrays that the part's kernels read from device memory in a step of prompt portions and
         that depend on how the step's tokens are divided among its requests: ``key -> (words,
         fill(q_lens, ctx_lens) -> numpy int32 [words], present(device view) -> object)``.  A captured
-        step of up to ``max_tokens`` tokens of up to ``max_seqs`` requests, of which at most
-        ``max_portions`` (None: all) bring more than one token, keeps ``words`` words per key
+        step of up to ``max_tokens`` tokens of up to ``max_seqs`` requests with contexts up to ``max_ctx``
+        (None: any), of which at most ``max_portions`` (None: all) bring more than one token, keeps ``words`` words per key
         in its input buffer, fills them before every replay and hands ``present(view)`` to the parts as
         ``ctx.extras[key]``; ``ctx.extras["captured_portions"]`` then holds ``{"singles": bool}``
         (whether the steps that replay this graph hold requests that bring a single token).  In an

@@ -71,11 +71,12 @@ class DecoderModel:
                 scalars.setdefault(name, rule)
         return scalars
 
-    def step_arrays(self, max_tokens: int, max_seqs: int, page_size: int, max_portions: int | None = None) -> dict:
+    def step_arrays(self, max_tokens: int, max_seqs: int, page_size: int, max_portions: int | None = None,
+                    max_ctx: int | None = None) -> dict:
         """The per-step device arrays that the model's parts declare (``Part.step_arrays``), by key."""
         arrays: dict = {}
         for part in self.all_parts():
-            for key, decl in part.step_arrays(max_tokens, max_seqs, page_size, max_portions).items():
+            for key, decl in part.step_arrays(max_tokens, max_seqs, page_size, max_portions, max_ctx).items():
                 arrays.setdefault(key, decl)
         return arrays
 

@@ -976,6 +976,42 @@ def test_attention_prefill_cuts_long_rows_of_keys(ops, status, fast, nh, nkv, hd
         row += q.shape[0]
 
 
+def test_attention_prefill_with_rows_cut_to_even_out_rounds_of_ctas(ops, status, fast):
+    """A portion behind a long context has more tiles x heads than SMs, all of about the same length; the
+    work list cuts every row into parts so that the rounds of CTAs come out even (here 13 tiles x 12 heads
+    in three parts each).  The same values as plain attention, and one far key per head is found."""
+    nh, nkv, hd, ps = 12, 2, 128, 16
+    ctx_lens, q_lens = [9000], [1600]
+    dtype = torch.bfloat16
+    k_cache, v_cache, tables, ks, vs = paged_setup(ctx_lens, nkv, hd, ps, dtype, seed=25)
+    scale = hd**-0.5
+    g = torch.Generator().manual_seed(26)
+    qs = [(torch.randn(q, nh, hd, generator=g) * 2).to(dtype).float() for q in q_lens]
+    kc = k_cache.float()
+    far = 5000  # (in the second of three parts) outweighs all other keys for the first head of KV head 1
+    page, off = int(tables[0, far // ps]), far % ps
+    kc[page, off, 1, :] = 0.0
+    kc[page, off, 1, 9] = 24.0
+    qs[0][:, 6, :] = 0.0
+    qs[0][:, 6, 9] = 24.0
+    ks[0][far, 1, :] = kc[page, off, 1, :]
+    n = sum(q_lens)
+    wide = torch.zeros(n, (nh + 2 * nkv) * hd)
+    wide[:, : nh * hd] = torch.cat(qs).view(n, nh * hd)
+    q_start = torch.tensor([0, n], dtype=torch.int32)
+    seqs, q0s, words = fast.prefill_work_items(q_lens, ctx_lens, nh, 148)
+    assert len(seqs) * nh > 148 and {w & 0xFF for w in words} == {3}
+    dev = lambda x: torch.tensor(x, dtype=torch.int32, device=DEV)  # noqa: E731
+    out = fast.attention_prefill(wide.to(dtype).to(DEV), kc.to(dtype).to(DEV), v_cache.to(DEV), tables.to(DEV), q_start.to(DEV),
+                                 dev(ctx_lens), dev(seqs), dev(q0s), len(seqs), nh, nkv, hd, scale, None, status,
+                                 item_split=dev(words))
+    ops.raise_on_status(status)
+    out = out.float().cpu().view(n, nh, hd)
+    want = plain.causal_attention(qs[0], ks[0], vs[0], scale)
+    torch.testing.assert_close(out, want, rtol=2e-2, atol=2e-2)
+    torch.testing.assert_close(out[:, 6], vs[0][far, 1].expand(n, hd), rtol=2e-2, atol=2e-2)
+
+
 def test_attention_prefill_refuses_a_bad_cut(ops, status, fast):
     nh, nkv, hd, ps = 2, 1, 64, 16
     k_cache, v_cache, tables, _, _ = paged_setup([200], nkv, hd, ps, torch.bfloat16, seed=1)

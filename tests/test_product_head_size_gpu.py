@@ -161,3 +161,47 @@ def test_random_compositions_of_steps_at_head_size_128(dtype, seed, model_dir, r
         exact, rounded = references(toks)
         check(torch.stack(got[rid]), (exact[places[rid]], rounded[places[rid]]), dtype, f"{dtype} seed {seed} {rid} ({len(toks)} tokens)")
     assert (runner.portion_graph_steps > 3) == (dtype == "bfloat16")
+
+
+@pytest.mark.parametrize("captured", [True, False])
+def test_portions_behind_a_long_context_with_rows_cut_for_even_rounds(captured, model_dir, references, monkeypatch):
+    """More query tiles x heads than SMs, all with long rows of keys: the work list cuts the rows so that the
+    rounds of CTAs come out even.  With four heads that takes more tokens than a step holds, so the policy is
+    told of 20 SMs and of parts that cost nothing; the cuts it then makes (three parts per row from the
+    third portion on) go through the captured step's arrays of fixed length, or the uncaptured step's own,
+    and the logits are held against the plain implementation."""
+    from clockwork_b200 import EngineConfig
+    from clockwork_b200.engine import LLMEngine, StepEntry, load_model
+    from clockwork_b200.ops import attention_fast
+
+    monkeypatch.setattr(attention_fast, "_sm_count", lambda device=None: 20)
+    for name, value in (("ROUNDS_MIN_CTX", 1024), ("ROUNDS_CTA_TILES", 0), ("ROUNDS_MERGE_TILES", 0), ("ROUNDS_MIN_PART_TILES", 2)):
+        monkeypatch.setattr(attention_fast, name, value)
+    seen = []
+    inner = attention_fast.prefill_work_items
+
+    def spy(*args, **kwargs):
+        result = inner(*args, **kwargs)
+        seen.append((len(result[0]), max((w & 0xFF for w in result[2]), default=1)))
+        return result
+
+    monkeypatch.setattr(attention_fast, "prefill_work_items", spy)
+    cfg = EngineConfig.defaults(str(model_dir), dtype="bfloat16", block_size=PAGE, num_blocks=300, max_model_len=4096, max_num_seqs=8,
+                                max_num_batched_tokens=4096, enable_prefix_cache=False)
+    eng = LLMEngine(cfg, model=load_model(model_dir, cfg.model.dtype))
+    runner, cache = eng.runner, eng.cache
+    runner.portions_captured = captured
+    toks = tokens(4024, 77)
+    cache.open("r")
+    got, places, done = [], [], 0
+    for n in (1024, 1024, 1024, 952):
+        want = [0, 63, 64, 500, n - 1]
+        out = runner.step([StepEntry("r", toks[done : done + n], want)]).float().cpu()
+        runner.check_status()
+        got += list(out)
+        places += [done + w for w in want]
+        done += n
+    assert (runner.portion_graph_steps == 4) == captured
+    assert max(parts for _, parts in seen) >= 3 and max(items for items, _ in seen) * CONFIG["num_attention_heads"] > 20, seen
+    exact, rounded = references(toks)
+    check(torch.stack(got), (exact[places], rounded[places]), "bfloat16", f"rows cut for even rounds, captured={captured}")

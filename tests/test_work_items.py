@@ -1,12 +1,13 @@
 """Work items of the prefill attention kernel (host side, no GPU): every query tile is there once per
-part, the parts of a tile are consecutive and name their first, tiles are cut only while the step's
-CTAs leave SMs idle, the longest first, and items come longest part first."""
+part, the parts of a tile are consecutive and name their first, tiles are cut while the step's
+CTAs leave SMs idle, the longest first, or when more CTAs than SMs come out in uneven rounds, and items come
+longest part first."""
 
 from clockwork_b200.ops import attention_fast as fast
 
 
-def check(q_lens, ctx_lens, num_heads=0, sm_count=0):
-    seqs, q0s, words = fast.prefill_work_items(q_lens, ctx_lens, num_heads, sm_count)
+def check(q_lens, ctx_lens, num_heads=0, sm_count=0, max_items=None):
+    seqs, q0s, words = fast.prefill_work_items(q_lens, ctx_lens, num_heads, sm_count, max_items=max_items)
     assert len(seqs) == len(q0s) == len(words)
     seen, i = {}, 0
     while i < len(words):
@@ -44,3 +45,23 @@ def test_few_tiles_with_many_keys_are_cut_until_the_sms_are_full():
     assert seen[(1, 0)] == 8 and seen[(2, 0)] == 1
     seen, _ = check([5, 1], [300, 400], num_heads=2, sm_count=148)  # nothing is worth cutting
     assert set(seen.values()) == {1}
+
+
+def test_more_ctas_than_sms_are_cut_when_that_evens_out_the_rounds():
+    """A 2,048-token portion behind 30,720 tokens: 16 tiles x 12 heads of about 250 key tiles each take two
+    rounds on 148 SMs for the work of 1.3; in three parts each they take four rounds of a third."""
+    seen, _ = check([2048], [32768], num_heads=12, sm_count=148)
+    assert set(seen.values()) == {3}
+    seen, _ = check([2048], [32768], num_heads=12, sm_count=148, max_items=40)  # room for two parts each only
+    assert set(seen.values()) == {2}
+    seen, _ = check([2048], [32768], num_heads=12, sm_count=148, max_items=20)  # no room
+    assert set(seen.values()) == {1}
+    # a first portion (rows of 128 to 2,048 keys: the short ones fill the second round) and a portion behind a short
+    # context (a part would cost about what it walks) stay whole; so does a step whose rounds are even already
+    for q, c in (([2048], [2048]), ([2048], [4096]), ([2048], [8192]), ([4096], [16384])):
+        seen, _ = check(q, c, num_heads=12, sm_count=148)
+        assert set(seen.values()) == {1}, (q, c)
+    # two portions of different requests at different contexts beside single tokens: parts of about equal length
+    seen, keys = check([1024, 1024, 1], [20000, 9000, 5000], num_heads=28, sm_count=148)
+    assert all(seen[(0, q0)] == 2 for q0 in range(0, 1024, 128)) and all(seen[(1, q0)] == 1 for q0 in range(0, 1024, 128))
+    assert fast.rounds_max_parts(8192) == 1 and fast.rounds_max_parts(16384) == fast.rounds_max_parts(None) == fast.MAX_PARTS
