@@ -314,3 +314,55 @@ def test_overlapping_kernels_change_nothing_2_of_28_layers(two_layer_dir):
     differing = [i for i in range(40) if not torch.equal(run(), serial)]
     session.runner.check_status()
     assert not differing, f"runs {differing} of 40 differ from the run without overlap"
+
+
+@pytest.mark.parametrize("dtype,seed", [("bfloat16", 0), ("bfloat16", 2), ("bfloat16", 11), ("float32", 3)])
+def test_random_compositions_of_steps_at_real_layer_sizes_2_of_28_layers(dtype, seed, two_layer_dir, references):
+    """Eight requests of 1 to 1,500 tokens, at most six live, every step a random choice of who takes part and
+    with how many tokens (one, a few, a query tile and one more, 257, over a thousand), through the step function
+    with its captured steps: the products at token counts of every kind (one-tile, split over K with the norm
+    adding the slabs, persistent), portions beside single tokens, logits at a few places of every portion
+    against the plain implementation."""
+    import random
+
+    from clockwork_b200 import EngineConfig
+    from clockwork_b200.engine import LLMEngine, StepEntry, load_model
+
+    rng = random.Random(seed)
+    cfg = EngineConfig.defaults(str(two_layer_dir), dtype=dtype, block_size=PAGE, num_blocks=900, max_model_len=4096,
+                                max_num_seqs=12, max_num_batched_tokens=8192, enable_prefix_cache=False)
+    eng = LLMEngine(cfg, model=load_model(two_layer_dir, cfg.model.dtype))
+    runner, cache = eng.runner, eng.cache
+    total = {f"q{i}": tokens(rng.choice([1, 5, 127, 128, 129, 300, 640, 1100, 1500]), seed * 20 + i) for i in range(8)}
+    waiting, live = list(total), {}
+    got = {rid: [] for rid in total}
+    places = {rid: [] for rid in total}
+    while waiting or live:
+        while waiting and len(live) < 6 and rng.random() < 0.6:
+            rid = waiting.pop()
+            cache.open(rid)
+            live[rid] = 0
+        entries = []
+        for rid in list(live):
+            if rng.random() < 0.15:
+                continue  # sits this step out
+            n = min(len(total[rid]) - live[rid], rng.choice([1, 1, 1, 1, 2, 7, 16, 100, 128, 130, 257, 400, 700, 1300]))
+            entries.append(StepEntry(rid, total[rid][live[rid] : live[rid] + n], sorted(set(rng.sample(range(n), min(n, 2)) + [n - 1]))))
+        if not entries:
+            continue
+        out = runner.step(entries).float().cpu()
+        row = 0
+        for e in entries:
+            for w in e.want:
+                got[e.request_id].append(out[row].clone())
+                places[e.request_id].append(live[e.request_id] + w)
+                row += 1
+            live[e.request_id] += len(e.tokens)
+            if live[e.request_id] == len(total[e.request_id]):
+                cache.close(e.request_id)
+                del live[e.request_id]
+        runner.check_status()
+    for rid, toks in total.items():
+        check(torch.stack(got[rid]), references(toks, places[rid], dtype), dtype, f"{dtype} seed {seed} {rid} ({len(toks)} tokens)",
+              derived_float32=True)
+    assert (runner.portion_graph_steps > 3) == (dtype == "bfloat16")
