@@ -368,6 +368,11 @@ def main() -> int:
     ap.add_argument("--steps", type=int, default=128)
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--temperature", type=float, default=0.0,
+                    help="with --only decode: the requests sample with this temperature (and --top-k, --top-p) in the end-to-end "
+                         "steps; the device-timed steps stay greedy")
+    ap.add_argument("--top-k", type=int, default=-1)
+    ap.add_argument("--top-p", type=float, default=1.0)
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the shape has (reported in config)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--shape", default="qwen2.5-1.5b",
@@ -412,6 +417,9 @@ def main() -> int:
     rng = random.Random(0)
     peak, peak_kind = peaks()
     once = args.only is not None
+    if (args.temperature != 0.0 or args.top_k != -1 or args.top_p != 1.0) and args.only != "decode":
+        print("bench.py: --temperature, --top-k and --top-p go with --only decode")
+        return 2
     if args.prompt_len is not None and args.only not in ("decode", "prefill", "long-prompt"):
         print("bench.py: --prompt-len goes with --only decode, --only prefill or --only long-prompt")
         return 2
@@ -427,8 +435,9 @@ def main() -> int:
 
     def fill(engine: LLMEngine, batch: int, steps: int, prompt_len: int = prompt_len) -> list[str]:
         """Admit ``batch`` requests with prompts of ``prompt_len`` tokens and run their prefill."""
-        params = SamplingParams(max_tokens=4 * (steps + args.warmup) + GENERATED, ignore_eos=True)
         for i in range(batch):
+            params = SamplingParams(max_tokens=4 * (steps + args.warmup) + GENERATED, ignore_eos=True, temperature=args.temperature,
+                                    top_k=args.top_k, top_p=args.top_p, seed=i if args.temperature > 0 else None)
             engine.add_request(f"b{i}", prompt_token_ids=[rng.randrange(vocab) for _ in range(prompt_len)], sampling_params=params)
         while any(s.num_uncomputed_tokens() > 1 for s in engine.scheduler.running) or engine.scheduler.waiting:
             engine.step()
