@@ -395,6 +395,16 @@ def main() -> int:
     if args.warmup < 3:
         args.warmup = 3
 
+    if (args.temperature != 0.0 or args.top_k != -1 or args.top_p != 1.0) and args.only != "decode":
+        print("bench.py: --temperature, --top-k and --top-p go with --only decode")
+        return 2
+    if args.prompt_len is not None and args.only not in ("decode", "prefill", "long-prompt"):
+        print("bench.py: --prompt-len goes with --only decode, --only prefill or --only long-prompt")
+        return 2
+    if args.shape != "qwen2.5-1.5b" and args.only is None:
+        print("bench.py: the benchmark line is that of qwen2.5-1.5b; other shapes run with --only")
+        return 2
+
     import torch
 
     from clockwork_b200 import EngineConfig
@@ -405,9 +415,6 @@ def main() -> int:
 
     assert torch.cuda.is_available(), "bench.py needs a CUDA device"
     torch.cuda.set_device(0)
-    if args.shape != "qwen2.5-1.5b" and args.only is None:
-        print("bench.py: the benchmark line is that of qwen2.5-1.5b; other shapes run with --only")
-        return 2
     raw = shape_config(args.shape, args.layers)
     registered = shape_config("qwen2.5-1.5b")
     assert all(registered[k] == v for k, v in QWEN25_1P5B.items()), "the two arms would not run the same shape"
@@ -417,12 +424,6 @@ def main() -> int:
     rng = random.Random(0)
     peak, peak_kind = peaks()
     once = args.only is not None
-    if (args.temperature != 0.0 or args.top_k != -1 or args.top_p != 1.0) and args.only != "decode":
-        print("bench.py: --temperature, --top-k and --top-p go with --only decode")
-        return 2
-    if args.prompt_len is not None and args.only not in ("decode", "prefill", "long-prompt"):
-        print("bench.py: --prompt-len goes with --only decode, --only prefill or --only long-prompt")
-        return 2
     prompt_len = args.prompt_len or PROMPT_LEN
 
     def make_engine(batch: int, steps: int, **overrides) -> LLMEngine:
