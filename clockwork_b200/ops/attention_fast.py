@@ -306,7 +306,7 @@ def prefill_work_items(q_lens, ctx_lens, num_heads: int = 0, sm_count: int = 0,
                 break
             g[3] += 1
             room -= 1
-        if _even_rounds and len(groups) * num_heads > sm_count:
+        if _even_rounds and sm_count < len(groups) * num_heads <= ROUNDS_MAX_UNCUT * sm_count:
             _cut_for_even_rounds(groups, num_heads, sm_count, ROUNDS_MAX_ITEMS if max_items is None else max_items)
     groups.sort(key=lambda g: -(g[0] / g[3]))
     seqs, q0s, words = [], [], []
@@ -325,6 +325,8 @@ ROUNDS_MIN_PART_TILES = 8   # no part shorter than this when rows are cut to eve
 ROUNDS_MIN_GAIN = 0.05      # rows are cut only for an estimated gain of this much
 ROUNDS_MAX_ITEMS = 64       # and into no more items than this (an unused item of a captured step's list is a CTA per head
                             # that starts and leaves; each item holds 128 x head size floats per head of scratch)
+ROUNDS_MAX_UNCUT = 2        # only steps of at most this many rounds of whole CTAs are cut (measured: 448 CTAs of 28 heads, three
+                            # rounds, gain 4 % behind 30,720 tokens and lose 3 % behind 18,432; 640 CTAs of 40 heads gain nothing)
 ROUNDS_MIN_CTX = 8192       # rows no longer than this are not cut for even rounds (measured: no gain below, 3 % at 10,240 keys,
                             # 8 % at 18,432, 12 % at 30,720 for a 2,048-token portion of 12 heads; two to three parts are best)
 
@@ -348,7 +350,7 @@ def _rounds_estimate(costs: np.ndarray, sm_count: int) -> float:
 
 
 def _cut_for_even_rounds(groups: list[list], num_heads: int, sm_count: int, max_items: int) -> None:
-    """More CTAs than SMs: when they are few and long (a portion behind a long context: 16 tiles x 12 heads of
+    """More CTAs than SMs, up to ``ROUNDS_MAX_UNCUT`` times: when they are few and long (a portion behind a long context: 16 tiles x 12 heads of
     250 key tiles each on 148 SMs take two rounds for the work of 1.3), rows of keys are cut into parts of
     about equal length so that the rounds come out even.  The grain (tiles per part) is the longest row cut
     into 1, 2, ... parts; the one with the smallest estimated time wins, and nothing is cut for less than
