@@ -425,10 +425,10 @@ def _cuts_for(num_heads: int, head_dim: int, page_size: int) -> int:
 def portion_step_arrays(num_heads: int, head_dim: int, page_size: int, max_tokens: int, max_seqs: int, device,
                         max_portions: int | None = None, max_ctx: int | None = None) -> dict:
     """The prefill kernel's work list as an array of a captured step (``Part.step_arrays``): three rows
-    (request, first query row, split word) of fixed length, unused entries naming request -1.  Two keys,
-    for steps captured with and without their single-token requests served apart; with them apart only
-    the ``max_portions`` requests that bring more than one token have items (every unused item is a CTA
-    per head that starts and leaves)."""
+    (request, first query row, split word) of fixed length, unused entries naming request -1.  The key
+    says whether the step's single-token requests are served apart; with them apart only the
+    ``max_portions`` requests that bring more than one token have items (every unused item is a CTA per
+    head that starts and leaves)."""
     if head_dim not in PREFILL_HEAD_DIMS:
         return {}
     cuts = _cuts_for(num_heads, head_dim, page_size)
@@ -457,9 +457,10 @@ def portion_step_arrays(num_heads: int, head_dim: int, page_size: int, max_token
     def present(view: torch.Tensor, cap: int):
         return view[:cap], view[cap : 2 * cap], (view[2 * cap :] if cuts else None), cap
 
-    return {("prefill_items", cuts, apart): (3 * caps[apart], lambda q, c, apart=apart: fill(q, c, apart),
-                                             lambda view, apart=apart: present(view, caps[apart]))
-            for apart in (False, True)}
+    # the one list that a step captured with these bounds reads: its single-token requests are served apart
+    # (by the decode kernel) when it holds any, which is when the caller bounds its portions
+    apart = max_portions is not None and _route_single_tokens and head_dim in DECODE_HEAD_DIMS
+    return {("prefill_items", cuts, apart): (3 * caps[apart], lambda q, c: fill(q, c, apart), lambda view: present(view, caps[apart]))}
 
 
 def _work_items(ctx, num_heads: int, skip_single: bool = False) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor | None, int]:
@@ -468,6 +469,8 @@ def _work_items(ctx, num_heads: int, skip_single: bool = False) -> tuple[torch.T
     key = ("prefill_items", num_heads, skip_single)
     cached = ctx.extras.get(key)
     if cached is None:
+        if ctx.extras.get("captured_portions") is not None:
+            raise RuntimeError(f"a captured step without the work list {key}: its graph was captured for another kind of step")
         seqs, q0s, words = prefill_work_items(ctx.q_lens_host, ctx.ctx_lens_host, num_heads,
                                               _sm_count(ctx.device) if num_heads else 0, skip_single)
         cut = any(w & 0xFF != 1 for w in words)
