@@ -68,3 +68,54 @@ def test_more_ctas_than_sms_are_cut_when_that_evens_out_the_rounds():
     seen, keys = check([1024, 1024, 1], [20000, 9000, 5000], num_heads=28, sm_count=148)
     assert set(seen.values()) == {1}
     assert fast.rounds_max_parts(8192) == 1 and fast.rounds_max_parts(16384) == fast.rounds_max_parts(None) == fast.MAX_PARTS
+
+
+def test_a_captured_step_s_list_always_has_room(monkeypatch):
+    """Whatever a step of up to the captured bounds holds (random divisions of its tokens among its requests,
+    random contexts up to the tier's bound, with and without single tokens served apart), the work list fits
+    the fixed length that the captured step reserved, unused entries name no request, and the entries are a
+    valid list of parts."""
+    import random
+
+    import numpy as np
+
+    monkeypatch.setattr(fast, "_sm_count", lambda device=None: 148)
+    rng = random.Random(7)
+    for trial in range(300):
+        heads = rng.choice([2, 4, 12, 14, 28, 40])
+        max_tokens = rng.choice([128, 256, 512, 1024, 2048, 2560, 4096])
+        max_seqs = rng.choice([8, 64])
+        max_ctx = rng.choice([1024, 2048, 8192, 16384, 32768])
+        singles = rng.random() < 0.5
+        decl = fast.portion_step_arrays(heads, 128, 16, max_tokens, max_seqs, "cuda:0", 8 if singles else None, max_ctx)
+        (key, (words, fill, present)), = decl.items()
+        assert key[2] == singles
+        # a step within the bounds: portions (at most 8 beside single tokens), then single tokens if it holds any
+        q_lens, left = [], max_tokens
+        for _ in range(rng.randint(1, 8 if singles else min(max_seqs, 12))):
+            if left < 2:
+                break
+            n = rng.choice([2, 7, 100, 128, 129, 300, 1000, left])
+            n = max(2, min(n, left))
+            q_lens.append(n)
+            left -= n
+        if singles:
+            q_lens += [1] * min(left, max_seqs - len(q_lens), rng.randint(1, 40))
+        ctx_lens = [rng.randint(n, max(n, max_ctx)) for n in q_lens]
+        if rng.random() < 0.5:  # all behind long contexts: the case that cuts the most
+            ctx_lens = [max(n, max_ctx - rng.randint(0, 64)) for n in q_lens]
+        flat = fill(q_lens, ctx_lens)
+        assert flat.dtype == np.int32 and flat.shape == (words,)
+        cap = words // 3
+        seqs, q0s, split = flat[:cap], flat[cap : 2 * cap], flat[2 * cap :]
+        used = int((seqs >= 0).sum())
+        assert (seqs[:used] >= 0).all() and (seqs[used:] == -1).all()
+        i, tiles = 0, set()
+        while i < used:
+            first, parts = int(split[i]) >> 8, int(split[i]) & 0xFF
+            assert first == i and 1 <= parts <= fast.MAX_PARTS and i + parts <= used
+            assert all((seqs[i + k], q0s[i + k], split[i + k]) == (seqs[i], q0s[i], split[i]) for k in range(parts))
+            tiles.add((int(seqs[i]), int(q0s[i])))
+            i += parts
+        want = {(s, q0) for s, n in enumerate(q_lens) if not (singles and n == 1) for q0 in range(0, n, fast.QUERY_TILE)}
+        assert tiles == want, (trial, q_lens, ctx_lens)
