@@ -624,7 +624,9 @@ class ModelRunner:
     # the host's launches (up to PORTION_TOKEN_BUCKETS[-1] tokens, padded to the next bucket), and up to
     # PORTION_MAX_TOKENS when a multiple of PORTION_LONG_STEP tokens is at most PORTION_LONG_WASTE above its
     # size (the gaps between launches cost a long step about 5 %; more padding than that would cost more).
-    PORTION_TOKEN_BUCKETS = (128, 192, 256, 384, 512, 768, 1024)
+    # The small buckets are those of the products' token tiles: a prompt of 8 to 64 tokens, or the rest of one
+    # behind a prefix-cache hit, costs 1.4 to 1.8 ms at the 1.5B sizes instead of the 2.2 ms of 128 tokens.
+    PORTION_TOKEN_BUCKETS = (16, 32, 64, 128, 192, 256, 384, 512, 768, 1024)
     PORTION_MAX_TOKENS = 4096
     PORTION_LONG_STEP = 256
     PORTION_LONG_WASTE = 0.04
