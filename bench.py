@@ -750,7 +750,7 @@ def main() -> int:
         span = time_span(args.batch)
         points["decode_span_1024_1280"] = span["tok_s"]
         points["decode_span_1024_1280_hbm_frac"] = span["hbm_frac"]
-        for tokens in (128, 512):
+        for tokens in (32, 128, 512):
             points[f"prefill_{tokens}_ms"] = time_prefill(tokens=tokens)["ms"]
         small = time_mixed(decodes=7, ctx=1024, portions=1, portion_len=256)
         points["mixed_7x1024_1x256_ms"] = small["ms"]
