@@ -76,11 +76,17 @@ def test_short_steps_with_portions_replay_captured_graphs(name, sharp_dirs):
     run.step({"e": toks["e"][:1100]}, want_all=False)                 # a long step far from a multiple of 256 tokens: not padded
     run.step({"e": toks["e"][1100:]}, want_all=False)                 # short again, at a context beyond 1,024: the next tier
     assert runner.portion_graph_steps == 5 and any(k[3] == 2048 for k in runner.portion_graphs)
-    run.step({f"m{i}": toks[f"m{i}"] for i in range(9)})              # more requests than the small bucket holds: the next one
+    run.step({f"m{i}": toks[f"m{i}"][:-2] for i in range(9)})         # more requests than the small bucket holds: the next one
     assert runner.portion_graph_steps == 6 and any(k[1] == 64 for k in runner.portion_graphs)
     run.step({"f": toks["f"]}, want_all=False)                        # a long step just below a multiple of 256 tokens
     assert runner.portion_graph_steps == 7 and any(k[0] == 2048 for k in runner.portion_graphs)
-    for rid in ("a", "b", "c", "d", "e", "f", "m0", "m8"):
+    # fewer tokens than the step has room for requests: nine single tokens beside a new prompt of three (bucket of 16
+    # tokens, 64 requests), then nine beside its last two tokens
+    toks["n"] = tokens_for(name, 5, salt=99)
+    run.step({**{f"m{i}": toks[f"m{i}"][-2:-1] for i in range(9)}, "n": toks["n"][:3]})
+    run.step({**{f"m{i}": toks[f"m{i}"][-1:] for i in range(9)}, "n": toks["n"][3:]})
+    assert runner.portion_graph_steps == 9 and any(k[0] == 16 and k[1] == 64 for k in runner.portion_graphs)
+    for rid in ("a", "b", "c", "d", "e", "f", "m0", "m4", "m8", "n"):
         places, got = run.of(rid)
         exact = plain.all_position_logits(config, weights, toks[rid])
         rounded = plain.all_position_logits(config, weights, toks[rid], rnd=plain.to_bfloat16_and_back)
